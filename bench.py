@@ -1,0 +1,399 @@
+#!/usr/bin/env python
+"""Benchmark of the CWICK attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2|c5a|c1|c4]
+
+Default workload `c2` is BASELINE.json's config 2: MLA absorbed decode, batch 1,
+64 heads, 512-d latent + 64-d rope key, 8192 cached tokens, BF16. One *step* is
+one decode call on each of ROT distinct sequences (each call batch 1, its own
+cache), so consecutive calls never find their cache in L2 (ROT x 9.4 MB > 126 MB).
+`value` is tokens/s with everything resident in HBM (the ROT calls replayed as one
+CUDA graph); `e2e` is the same work through the host-buffer entry point
+(cwk_mla_decode_host: pinned staging, H2D of q, D2H of the output, one sync per
+call). With N > 1 every rank runs the same step on its own sequences (weak
+scaling, no collective: sequences are independent).
+
+`--impl reference` times the reference's own CPU attention (oracle/_ref, the
+unmodified cwick_attention_mla_decode latent path over a bf16 cache) on the
+host cores, or the CPU oracle when that library is absent.
+"""
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+NH, L, R = 64, 512, 64
+DK = L + R
+SCALE = 1.0 / math.sqrt(192.0)
+ROT = 32                      # distinct sequences per step
+L2_BYTES = 126 * 1024 * 1024
+
+WORKLOADS = {
+    # name: (sequences per call, cached tokens, calls per step)
+    "c2": dict(B=1, T=8192, calls=ROT, desc="config 2: MLA absorbed decode, batch 1, 64 heads, 512+64 bf16, 8192 cached tokens"),
+    "c5a": dict(B=64, T=32768, calls=1, desc="config 5a on one GPU: 64 sequences x 32768 cached tokens, one batched call"),
+}
+
+
+def algorithmic_bytes(B, T):
+    """Bytes one decode call must move: cache once + q + out (bf16)."""
+    return B * (T * DK * 2 + NH * DK * 2 + NH * L * 2)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_reference(seconds_budget=15.0, tokens=8192):
+    """Times the reference's CPU attention on config-2-shaped data.
+
+    Preferred: oracle/_ref (the reference's own cwick_attention_mla_decode, latent path,
+    bf16 cache via CWICK_LATENT_BF16=1). Its latent path is rope-free, so the 576-wide row
+    is handed to it as one 576-d latent: the score pass is the same 576-d dot per (head,
+    key) as config 2, the value pass accumulates 576 instead of 512 columns (12.5 % more).
+    One thread per sequence, as many threads as host cores (the reference runs its
+    attention reductions on the calling thread by default, src/attention.c:356-374).
+    Fallback: the CPU oracle port. Returns (tokens_per_s, info)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import orc
+    from cwick_b200 import synth
+    cores = os.cpu_count() or 1
+    nthreads = max(1, min(cores, ROT))
+    os.environ["CWICK_LATENT_BF16"] = "1"
+    os.environ["CWICK_THREADS"] = "1"
+    ref = orc.ref()
+    seed = synth.DEFAULT_SEED
+    H, nope, vdim, q_lora, kv_lora = 64, 16, 16, 64, DK
+    caches = [synth.normal_bf16(seed, 1000 + t, (tokens, kv_lora)) for t in range(nthreads)]
+    done = [0] * nthreads
+    stop_at = [0.0]
+
+    if ref is not None:
+        kind = "reference"
+        W = dict(qa=synth.normal_bf16(seed, 1, (q_lora, H), 0.1), qb=synth.normal_bf16(seed, 2, (NH * nope, q_lora), 0.1),
+                 kva=synth.normal_bf16(seed, 3, (kv_lora, H), 0.1),
+                 kvb=synth.normal_bf16(seed, 4, (NH * (nope + vdim), kv_lora), 0.1),
+                 o=synth.normal_bf16(seed, 5, (H, NH * vdim), 0.1), qa_n=synth.f32_to_bf16(np.ones(q_lora, np.float32)),
+                 kva_n=synth.f32_to_bf16(np.ones(kv_lora, np.float32)))
+        x = synth.normal(seed, 6, H)
+
+        def one(t):
+            out = np.empty(H, np.float32)
+            ref.refdrv_mla_latent_layer(H, NH, nope, vdim, q_lora, kv_lora, 1e-6,
+                                        *[orc.vp(W[k]) for k in ("qa", "qb", "kva", "kvb", "o", "qa_n", "kva_n")],
+                                        orc.vp(caches[t]), tokens, tokens - 1, orc.P(x, orc.f32p), orc.P(out, orc.f32p))
+    else:
+        kind = "port"
+        qs = [synth.bf16_to_f32(synth.normal_bf16(seed, 2000 + t, (NH, DK))) for t in range(nthreads)]
+
+        def one(t):
+            orc.mla_decode(qs[t], caches[t], tokens, L, R, SCALE)
+
+    def worker(t):
+        while time.perf_counter() < stop_at[0]:
+            one(t)
+            done[t] += 1
+
+    one(0)                                   # warm-up (page-in, LUTs)
+    t0 = time.perf_counter()
+    one(0)
+    single = time.perf_counter() - t0
+    stop_at[0] = time.perf_counter() + max(2.0 * single, seconds_budget)
+    t0 = time.perf_counter()
+    th = [threading.Thread(target=worker, args=(t,)) for t in range(nthreads)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    dt = time.perf_counter() - t0
+    n = sum(done)
+    info = {"kind": kind, "cores": nthreads,
+            "sample": f"{n} single-token decodes of the {tokens}-token config-2 cache ({kind}), "
+                      f"{nthreads} threads x one sequence each, {dt:.1f} s wall"}
+    return n / dt, info
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tps, info = cpu_reference(seconds_budget=max(5.0, 4.0 * args.steps))
+    line = {"impl": "reference", "metric": "mla_decode_tokens_per_s", "value": tps, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 * ROT / tps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOADS["c2"]["desc"], "rotation": ROT},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", **info},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from cwick_b200 import build
+    build.build()
+    from cwick_b200.ops import Attn
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU path for --impl ours")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+
+    wl = WORKLOADS[args.workload]
+    B, T, calls = wl["B"], wl["T"], wl["calls"]
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    attn = Attn(local)                       # binds the context to `stream`
+
+    g = torch.Generator(device=dev).manual_seed(20261125 + rank)
+    caches, qs, outs = [], [], []
+    for _ in range(calls):
+        caches.append(torch.randn(B, T, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16))
+        qs.append(torch.randn(B, NH, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16))
+        outs.append(torch.empty(B, NH, L, device=dev, dtype=torch.bfloat16))
+    lens = torch.full((B,), T, dtype=torch.int32, device=dev)
+    total_cache_bytes = calls * B * T * DK * 2
+    flush = None
+    if total_cache_bytes <= 2 * L2_BYTES:    # inputs do not exceed L2 by themselves: flush between steps
+        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+
+    def step_device():
+        for i in range(calls):
+            attn.mla_decode(qs[i], caches[i], lens, max_kv_len=T, scale=SCALE, out=outs[i])
+
+    # warm-up outside capture (scratch allocation, function attributes), then capture one step
+    step_device()
+    stream.synchronize()
+    l0 = attn.ctx.launches
+    step_device()
+    launches_per_step = attn.ctx.launches - l0
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step_device()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            if flush is not None:
+                flush.fill_(1)
+            fn()
+        barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
+        e0 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        e1 = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            if flush is not None:
+                flush.fill_(i & 1)
+            e0[i].record(stream)
+            fn()
+            e1[i].record(stream)
+        barrier()
+        clocks = sampler.stop()
+        ms = sum(a.elapsed_time(b) for a, b in zip(e0, e1))
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, clocks
+
+    steps, warmup = args.steps, max(3, args.warmup)
+    ms_total, clocks = timed(graph.replay, steps, warmup)
+    ms_step = ms_total / steps
+    tokens_per_step = calls * B * world
+    value = tokens_per_step / (ms_step / 1e3)
+    kv_gbs = world * calls * algorithmic_bytes(B, T) / (ms_step / 1e3) / 1e9
+
+    # ---- roofline: main kernel's own duration, CUDA events on the launching stream ----
+    attn.ctx.profile(True)
+    for _ in range(max(1, min(steps, 20))):
+        step_device()
+    k_ms, k_n = attn.ctx.profile_read()
+    attn.ctx.profile(False)
+    peak, peak_kind = peaks()
+    per_launch_bytes = algorithmic_bytes(B, T)
+    achieved = per_launch_bytes / (k_ms / k_n / 1e3) / 1e9 if k_n else 0.0
+    path = int(attn.lib.cwk_mla_decode_path(attn.ctx.h, NH, L, R))
+    kernel_name = {2: "mla_decode_tc_kernel (tcgen05+TMA)", 1: "flash_rows_kernel<MLA> (mma.sync)", 0: "mla_decode_general_kernel"}[path]
+    roofline = {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBps_spec": achieved / 8000.0,
+                "algorithmic_bytes_per_launch": per_launch_bytes, "avg_launch_us": 1e3 * k_ms / max(1, k_n),
+                "launches_timed": k_n, "traffic": None}
+    tp = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tp):
+        try:
+            roofline["traffic"] = json.load(open(tp)).get(args.workload, {}).get("dram_bytes_per_launch")
+        except (OSError, ValueError):
+            pass
+
+    # ---- end to end through the host-buffer entry point --------------------------------
+    qh = [q.cpu().pin_memory() for q in qs]
+    oh = [torch.empty(B, NH, L, dtype=torch.bfloat16).pin_memory() for _ in range(calls)]
+    lens_h = torch.full((B,), T, dtype=torch.int32)
+
+    def step_host():
+        for i in range(calls):
+            attn.mla_decode_host(qh[i], caches[i], lens_h, L, R, SCALE, oh[i])
+
+    e_steps = max(3, min(steps, 20))
+    e_ms, _ = timed(step_host, e_steps, 3)
+    e2e_value = tokens_per_step / (e_ms / e_steps / 1e3)
+    h2d = calls * (B * NH * DK * 2 + B * 4)
+    d2h = calls * B * NH * L * 2
+    # sanity: both paths computed the same thing
+    assert torch.equal(oh[0], outs[0].cpu()), "host and device entry points disagree"
+
+    line = {"metric": "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl["desc"], "calls_per_step": calls, "sequences_per_call": B, "cached_tokens": T,
+                       "heads": NH, "latent": L, "rope": R,
+                       "l2": "flush between steps" if flush is not None else "inputs larger than L2 (%d MB per step)" % (total_cache_bytes >> 20),
+                       "parallelism": f"{world} x independent sequences"},
+            "kv_hbm_gbs": kv_gbs, "kv_hbm_frac_of_measured_peak": kv_gbs / (peak * world),
+            "roofline": roofline, "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": "cwk_mla_decode_host"},
+            "gpu_launches": int(launches_per_step * steps)}
+
+    if rank == 0 and world == 1 and not args.no_extra:
+        extra = {}
+        if args.workload == "c2":
+            try:
+                del caches, qs, outs
+                torch.cuda.empty_cache()
+                extra["c5a_64x32768"] = side_measure(attn, dev, stream, 64, 32768, peak)
+            except Exception as e:  # noqa: BLE001
+                extra["c5a_64x32768"] = {"error": str(e)[:200]}
+        line["extra"] = extra
+        tps, info = cpu_reference(seconds_budget=12.0)
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", **info}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def side_measure(attn, dev, stream, B, T, peak):
+    """Config 5a on one GPU: the batched call whose cache (2.4 GB) dwarfs L2."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(7)
+    cache = torch.empty(B, T, DK, device=dev, dtype=torch.bfloat16)
+    for b in range(B):
+        cache[b] = torch.randn(T, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    q = torch.randn(B, NH, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    lens = torch.full((B,), T, dtype=torch.int32, device=dev)
+    out = torch.empty(B, NH, L, device=dev, dtype=torch.bfloat16)
+    for _ in range(3):
+        attn.mla_decode(q, cache, lens, max_kv_len=T, scale=SCALE, out=out)
+    attn.ctx.profile(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    n = 10
+    for _ in range(n):
+        attn.mla_decode(q, cache, lens, max_kv_len=T, scale=SCALE, out=out)
+    e1.record(stream)
+    k_ms, k_n = attn.ctx.profile_read()
+    attn.ctx.profile(False)
+    ms = e0.elapsed_time(e1) / n
+    by = algorithmic_bytes(B, T)
+    return {"ms_per_call": ms, "tokens_per_s": B / (ms / 1e3), "kv_hbm_gbs": by / (ms / 1e3) / 1e9,
+            "kernel_gbs": by / (k_ms / k_n / 1e3) / 1e9, "kernel_frac_of_measured_peak": by / (k_ms / k_n / 1e3) / 1e9 / peak}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

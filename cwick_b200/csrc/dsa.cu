@@ -1,0 +1,202 @@
+// dsa.cu -- DSA lightning indexer: exact-order scores over FP8 keys and exact
+// top-k selection with the reference's ordering rule.
+#include "cwk_common.cuh"
+
+__device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
+    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    float mag;
+    if (e == 0) mag = (float)m * 0.001953125f;                        // m * 2^-9
+    else if (e == 15 && m == 7) mag = __int_as_float(0x7fc00000);
+    else mag = __uint_as_float(((e + 120u) << 23) | (m << 20));      // (1+m/8) * 2^(e-7)
+    return (b & 0x80u) ? -mag : mag;
+}
+
+// One thread per key. The dequantised key row lives in shared memory (row
+// stride 132 floats: 16-byte aligned and conflict-free for float4 reads), q in
+// shared memory as float4 broadcast reads. The arithmetic is the reference's:
+// per head four strided f32 accumulators with separate multiply and add (no
+// fused multiply-add), combined (s0+s1)+(s2+s3); ReLU; times the head weight;
+// heads summed in order.
+template <int HD>
+__global__ void __launch_bounds__(128) indexer_scores_fp8_kernel(
+    const uint8_t *keys, const float *kscale, int64_t key_stride, const float *q, const float *wt,
+    const int32_t *n, int ih, float *sc) {
+    constexpr int KS = HD + 4;
+    extern __shared__ __align__(16) float sm[];
+    float *sk = sm;                      // [128][KS]
+    float *sq = sm + 128 * KS;           // [ih][HD]
+    float *sw = sq + ih * HD;            // [ih]
+    const int b = blockIdx.y, tid = threadIdx.x;
+    const int nb = n[b];
+    const int c0 = blockIdx.x * 128;
+    if (c0 >= nb) return;
+    for (int i = tid; i < ih * HD; i += 128) sq[i] = q[(int64_t)b * ih * HD + i];
+    for (int i = tid; i < ih; i += 128) sw[i] = wt[(int64_t)b * ih + i];
+    // 128 keys x HD codes, 16 bytes per load
+    const uint8_t *kb = keys + ((int64_t)b * key_stride + c0) * HD;
+    for (int i = tid; i < 128 * (HD / 16); i += 128) {
+        const int r = i / (HD / 16), ch = i % (HD / 16);
+        if (c0 + r < nb) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(kb + (int64_t)r * HD + ch * 16);
+            const float s = kscale[(int64_t)b * key_stride + c0 + r];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    sk[r * KS + ch * 16 + k * 4 + j] = __fmul_rn(e4m3_to_f32((w[k] >> (8 * j)) & 0xffu), s);
+        }
+    }
+    __syncthreads();
+    const int c = c0 + tid;
+    if (c >= nb) return;
+    const float4 *kr = reinterpret_cast<const float4 *>(sk + tid * KS);
+    float total = 0.f;
+    for (int h = 0; h < ih; h++) {
+        const float4 *qh = reinterpret_cast<const float4 *>(sq + h * HD);
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < HD / 4; i++) {
+            const float4 kv = kr[i], qv = qh[i];
+            s0 = __fadd_rn(s0, __fmul_rn(kv.x, qv.x));
+            s1 = __fadd_rn(s1, __fmul_rn(kv.y, qv.y));
+            s2 = __fadd_rn(s2, __fmul_rn(kv.z, qv.z));
+            s3 = __fadd_rn(s3, __fmul_rn(kv.w, qv.w));
+        }
+        float d = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
+        if (d < 0.f) d = 0.f;
+        total = __fadd_rn(total, __fmul_rn(d, sw[h]));
+    }
+    sc[(int64_t)b * key_stride + c] = total;
+}
+
+// ---- exact top-k ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t order_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One block of 1024 threads per sequence. Radix select (4 passes of 8 bits over
+// an order-preserving integer image of the score) finds the want-th largest
+// value exactly; an ordered compaction then writes the rows above it in index
+// order followed by the rows equal to it in index order, `want` in all.
+__global__ void __launch_bounds__(1024) topk_select_kernel(const float *sc, int64_t sc_stride,
+                                                           const int32_t *n, int want, int keep_self,
+                                                           int32_t *sel, int64_t sel_ld, int32_t *nsel) {
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int nb = n[b];
+    const float *s = sc + (int64_t)b * sc_stride;
+    int32_t *out = sel + (int64_t)b * sel_ld;
+    if (nb <= want) {                       // the whole prefix is the top-k
+        for (int i = tid; i < nb; i += 1024) out[i] = i;
+        if (tid == 0) nsel[b] = nb;
+        return;
+    }
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t s_prefix, s_remaining;
+    __shared__ int s_warp[32][2];
+    __shared__ int s_base[2];
+    uint32_t prefix = 0, mask = 0;
+    int remaining = want;                    // rank still to find inside the current bucket
+    for (int pass = 0; pass < 4; pass++) {
+        const int shift = 24 - 8 * pass;
+        for (int i = tid; i < 256; i += 1024) hist[i] = 0;
+        __syncthreads();
+        for (int i = tid; i < nb; i += 1024) {
+            const uint32_t k = order_key(s[i]);
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int r = remaining;
+            int d = 255;
+            for (; d > 0; d--) {
+                const int c = (int)hist[d];
+                if (r <= c) break;
+                r -= c;
+            }
+            s_prefix = prefix | ((uint32_t)d << shift);
+            s_remaining = (uint32_t)r;
+        }
+        __syncthreads();
+        prefix = s_prefix;
+        remaining = (int)s_remaining;
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    // prefix is now the integer image of the threshold; `remaining` rows equal to
+    // it are wanted (the first ones in index order).
+    const uint32_t thr = prefix;
+    const int need_eq = remaining;
+    // count rows above the threshold (= want - need_eq by construction)
+    const int n_gt = want - need_eq;
+    if (tid == 0) { s_base[0] = 0; s_base[1] = 0; }
+    __syncthreads();
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int c0 = 0; c0 < nb; c0 += 1024) {
+        const int i = c0 + tid;
+        uint32_t k = 0;
+        bool gt = false, eq = false;
+        if (i < nb) {
+            k = order_key(s[i]);
+            gt = k > thr;
+            eq = k == thr;
+        }
+        const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
+        if (lane == 0) { s_warp[warp][0] = __popc(bg); s_warp[warp][1] = __popc(be); }
+        __syncthreads();
+        int og = s_base[0], oe = s_base[1];
+        for (int w = 0; w < warp; w++) { og += s_warp[w][0]; oe += s_warp[w][1]; }
+        og += __popc(bg & ((1u << lane) - 1u));
+        oe += __popc(be & ((1u << lane) - 1u));
+        if (gt) out[og] = i;
+        if (eq && oe < need_eq) out[n_gt + oe] = i;
+        __syncthreads();
+        if (tid == 0) {
+            int tg = 0, te = 0;
+            for (int w = 0; w < 32; w++) { tg += s_warp[w][0]; te += s_warp[w][1]; }
+            s_base[0] += tg;
+            s_base[1] += te;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        int cnt = want;
+        if (keep_self && out[cnt - 1] != nb - 1) out[cnt++] = nb - 1;
+        nsel[b] = cnt;
+    }
+}
+
+extern "C" {
+
+int cwk_indexer_scores_fp8(cwk_ctx *ctx, const void *keys, const float *kscale, int64_t key_stride,
+                           const float *q, const float *wt, const int32_t *n, int max_n, int B, int ih,
+                           int hd, float *sc) {
+    if (!ctx || !keys || !kscale || !q || !wt || !n || !sc || B <= 0 || ih <= 0 || max_n < 0)
+        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "indexer_scores: bad argument");
+    if (hd != 128) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "indexer_scores: head dim %d not built (128)", hd);
+    if (((uintptr_t)keys % 16) != 0) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "indexer_scores: keys must be 16-byte aligned");
+    CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (max_n == 0) return CWK_OK;
+    const size_t smem = (size_t)(128 * (128 + 4) + ih * 128 + ih) * sizeof(float);
+    auto kern = indexer_scores_fp8_kernel<128>;
+    if (smem > 48 * 1024) CWK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CwkKernelTimer timer(ctx);
+    kern<<<dim3((max_n + 127) / 128, B), 128, smem, ctx->stream>>>((const uint8_t *)keys, kscale, key_stride, q, wt, n, ih, sc);
+    CWK_LAUNCH_CHECK(ctx, "indexer_scores_fp8_kernel");
+    return CWK_OK;
+}
+
+int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int max_n, int B,
+                    int want, int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel) {
+    if (!ctx || !sc || !n || !sel || !nsel || B <= 0 || want <= 0 || sel_ld < want + 1)
+        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "topk_select: bad argument");
+    (void)max_n;
+    CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    CwkKernelTimer timer(ctx);
+    topk_select_kernel<<<B, 1024, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel);
+    CWK_LAUNCH_CHECK(ctx, "topk_select_kernel");
+    return CWK_OK;
+}
+
+}  // extern "C"

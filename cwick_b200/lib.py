@@ -1,0 +1,111 @@
+"""ctypes binding of libcwk_attn.so -- the only way this package computes.
+
+There is no CPU or eager fallback: if the shared library is missing or the
+process has no CUDA device, `load()` / `Context()` raise.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcwk_attn.so")
+
+OK, ERR_MEMORY, ERR_STATE, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA = 0, 4, 5, 6, 7, 100
+
+vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+# name -> (restype, argtypes); mirrors include/cwk_attn.h one to one
+SIGNATURES = {
+    "cwk_ctx_create": (i32, [i32, C.POINTER(vp)]),
+    "cwk_ctx_destroy": (None, [vp]),
+    "cwk_ctx_set_stream": (i32, [vp, vp]),
+    "cwk_ctx_sync": (i32, [vp]),
+    "cwk_last_error": (C.c_char_p, [vp]),
+    "cwk_ctx_launch_count": (C.c_uint64, [vp]),
+    "cwk_ctx_sm_count": (i32, [vp]),
+    "cwk_ctx_profile": (i32, [vp, i32]),
+    "cwk_ctx_profile_read": (i32, [vp, C.POINTER(C.c_double), C.POINTER(i32)]),
+    "cwk_mla_decode_path": (i32, [vp, i32, i32, i32]),
+    "cwk_ctx_force_mla_path": (i32, [vp, i32]),
+    "cwk_mla_decode": (i32, [vp, vp, vp, i64, i64, vp, i32, vp, i64, i32, i32, i32, i32, f32, vp, i32]),
+    "cwk_mla_decode_host": (i32, [vp, vp, vp, i64, i64, vp, vp, i64, i32, i32, i32, i32, f32, vp, i32]),
+    "cwk_mla_decode_partial": (i32, [vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, vp]),
+    "cwk_lse_combine": (i32, [vp, vp, i32, i32, i32, vp]),
+    "cwk_indexer_scores_fp8": (i32, [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "cwk_topk_select": (i32, [vp, vp, i64, vp, i32, i32, i32, i32, vp, i64, vp]),
+    "cwk_gqa_decode": (i32, [vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, f32, vp, i32]),
+    "cwk_gqa_prefill": (i32, [vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, vp]),
+    "cwk_fp8_linear": (i32, [vp, vp, vp, vp, i64, i64, i64, vp, i32]),
+}
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m cwick_b200.build` "
+                "(there is no fallback implementation)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)          # AttributeError if the header and the library drift
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+class CwkError(RuntimeError):
+    def __init__(self, status, msg):
+        super().__init__(f"cwk status {status}: {msg}")
+        self.status = status
+
+
+class Context:
+    """One cwk_ctx: a device, a stream, split scratch."""
+
+    def __init__(self, device=0, stream=None):
+        self.lib = load()
+        h = vp()
+        st = self.lib.cwk_ctx_create(device, C.byref(h))
+        if st != OK:
+            raise CwkError(st, "cwk_ctx_create failed (no CUDA device, or not an sm_100 part)")
+        self.h = h
+        if stream is not None:
+            self.check(self.lib.cwk_ctx_set_stream(self.h, vp(stream)))
+
+    def check(self, st):
+        if st != OK:
+            raise CwkError(st, self.lib.cwk_last_error(self.h).decode())
+
+    def sync(self):
+        self.check(self.lib.cwk_ctx_sync(self.h))
+
+    @property
+    def launches(self):
+        return int(self.lib.cwk_ctx_launch_count(self.h))
+
+    @property
+    def sm_count(self):
+        return int(self.lib.cwk_ctx_sm_count(self.h))
+
+    def profile(self, on):
+        self.check(self.lib.cwk_ctx_profile(self.h, 1 if on else 0))
+
+    def profile_read(self):
+        """(summed main-kernel milliseconds, bracketed launches) since the last read."""
+        ms, n = C.c_double(0.0), i32(0)
+        self.check(self.lib.cwk_ctx_profile_read(self.h, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.cwk_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,155 @@
+"""Tensor-level mirror of the C entry points, for tests and the benchmark.
+
+torch is used for device memory and streams only; every computation is a call
+into libcwk_attn.so through `lib.Context`. Argument names and meanings follow
+include/cwk_attn.h.
+"""
+import math
+
+import torch
+
+from . import lib as _lib
+
+
+def _p(t):
+    return None if t is None else _lib.vp(t.data_ptr())
+
+
+def _bf16(t):
+    assert t.dtype == torch.bfloat16 and t.is_cuda and t.is_contiguous()
+    return t
+
+
+class Attn:
+    def __init__(self, device=0):
+        torch.cuda.set_device(device)
+        self.device = device
+        self.ctx = _lib.Context(device, stream=torch.cuda.current_stream(device).cuda_stream)
+        self.lib = self.ctx.lib
+
+    # ---- MLA ---------------------------------------------------------------
+    def mla_decode(self, q, cache, kv_len, max_kv_len=None, sel=None, scale=None, seq_stride=None,
+                   n_splits=0, out=None):
+        """q [B][nh][L+R] bf16; cache [B][rows][ld] or [rows][ld] bf16 (then seq_stride 0);
+        kv_len int32 [B] cuda; sel optional int32 [B][sel_ld] cuda. Returns [B][nh][L] bf16."""
+        _bf16(q), _bf16(cache)
+        B, nh, dk = q.shape
+        ld = cache.shape[-1]
+        R = 64 if dk == 576 else 0
+        L = dk - R
+        if seq_stride is None:
+            seq_stride = cache.shape[-2] * ld if cache.dim() == 3 else 0
+        if max_kv_len is None:
+            max_kv_len = int(kv_len.max().item())
+        if scale is None:
+            scale = 1.0 / math.sqrt(192.0 if R else L)
+        if out is None:
+            out = torch.empty(B, nh, L, dtype=torch.bfloat16, device=q.device)
+        sel_ld = sel.shape[-1] if sel is not None else 0
+        self.ctx.check(self.lib.cwk_mla_decode(self.ctx.h, _p(q), _p(cache), seq_stride, ld, _p(kv_len),
+                                               max_kv_len, _p(sel), sel_ld, B, nh, L, R, scale, _p(out),
+                                               n_splits))
+        return out
+
+    def mla_decode_dims(self, q, cache, kv_len, L, R, scale, max_kv_len=None, sel=None, seq_stride=None,
+                        n_splits=0):
+        """As mla_decode with explicit (L, R)."""
+        _bf16(q), _bf16(cache)
+        B, nh, dk = q.shape
+        assert dk == L + R
+        ld = cache.shape[-1]
+        if seq_stride is None:
+            seq_stride = cache.shape[-2] * ld if cache.dim() == 3 else 0
+        if max_kv_len is None:
+            max_kv_len = int(kv_len.max().item())
+        out = torch.empty(B, nh, L, dtype=torch.bfloat16, device=q.device)
+        sel_ld = sel.shape[-1] if sel is not None else 0
+        self.ctx.check(self.lib.cwk_mla_decode(self.ctx.h, _p(q), _p(cache), seq_stride, ld, _p(kv_len),
+                                               max_kv_len, _p(sel), sel_ld, B, nh, L, R, scale, _p(out),
+                                               n_splits))
+        return out
+
+    def mla_decode_host(self, q_host, cache, kv_len_host, L, R, scale, out_host, sel_host=None, seq_stride=None,
+                        n_splits=0):
+        """q_host/out_host/kv_len_host: CPU tensors (any memory); cache: cuda bf16."""
+        B, nh, dk = q_host.shape
+        ld = cache.shape[-1]
+        if seq_stride is None:
+            seq_stride = cache.shape[-2] * ld if cache.dim() == 3 else 0
+        sel_ld = sel_host.shape[-1] if sel_host is not None else 0
+        self.ctx.check(self.lib.cwk_mla_decode_host(
+            self.ctx.h, _p(q_host), _p(cache), seq_stride, ld, _p(kv_len_host), _p(sel_host), sel_ld, B, nh,
+            L, R, scale, _p(out_host), n_splits))
+        return out_host
+
+    def mla_decode_partial(self, q, cache, row0, rows, L, R, scale, partial=None):
+        """q [nh][L+R] bf16, cache [rows_total][ld] bf16 -> f32 [nh*(L+2)] un-normalised record."""
+        nh = q.shape[-2]
+        if partial is None:
+            partial = torch.empty(nh * (L + 2), dtype=torch.float32, device=q.device)
+        self.ctx.check(self.lib.cwk_mla_decode_partial(self.ctx.h, _p(q), _p(cache), cache.shape[-1], row0,
+                                                       rows, nh, L, R, scale, _p(partial)))
+        return partial
+
+    def lse_combine(self, partials, nh, L):
+        G = partials.shape[0]
+        out = torch.empty(nh, L, dtype=torch.bfloat16, device=partials.device)
+        self.ctx.check(self.lib.cwk_lse_combine(self.ctx.h, _p(partials), G, nh, L, _p(out)))
+        return out
+
+    # ---- DSA -----------------------------------------------------------------
+    def indexer_scores_fp8(self, keys, kscale, q, wt, n, max_n=None):
+        """keys uint8 [B][T][hd]; kscale f32 [B][T]; q f32 [B][ih][hd]; wt f32 [B][ih]; n int32 [B]."""
+        B, T, hd = keys.shape
+        ih = q.shape[1]
+        if max_n is None:
+            max_n = int(n.max().item())
+        sc = torch.zeros(B, T, dtype=torch.float32, device=keys.device)
+        self.ctx.check(self.lib.cwk_indexer_scores_fp8(self.ctx.h, _p(keys), _p(kscale), T, _p(q), _p(wt), _p(n),
+                                                       max_n, B, ih, hd, _p(sc)))
+        return sc
+
+    def topk_select(self, sc, n, want, keep_self=False, max_n=None):
+        B, T = sc.shape
+        sel = torch.full((B, want + 1), -1, dtype=torch.int32, device=sc.device)
+        nsel = torch.zeros(B, dtype=torch.int32, device=sc.device)
+        self.ctx.check(self.lib.cwk_topk_select(self.ctx.h, _p(sc), T, _p(n), max_n or T, B, want,
+                                                1 if keep_self else 0, _p(sel), want + 1, _p(nsel)))
+        return sel, nsel
+
+    # ---- GQA -----------------------------------------------------------------
+    def gqa_decode(self, q, K, V, kv_len, scale=None, max_kv_len=None, n_splits=0):
+        """q [B][nh][hd]; K,V [B][T][nkv][hd] bf16; kv_len int32 [B]."""
+        _bf16(q), _bf16(K), _bf16(V)
+        B, nh, hd = q.shape
+        T, nkv = K.shape[1], K.shape[2]
+        if scale is None:
+            scale = 1.0 / math.sqrt(hd)
+        if max_kv_len is None:
+            max_kv_len = int(kv_len.max().item())
+        out = torch.empty(B, nh, hd, dtype=torch.bfloat16, device=q.device)
+        self.ctx.check(self.lib.cwk_gqa_decode(self.ctx.h, _p(q), _p(K), _p(V), T * nkv * hd, _p(kv_len),
+                                               max_kv_len, B, nh, nkv, hd, scale, _p(out), n_splits))
+        return out
+
+    def gqa_prefill(self, Q, K, V, pos, scale=None):
+        """Q [n][nh][hd]; K,V [pos+n][nkv][hd] bf16."""
+        _bf16(Q), _bf16(K), _bf16(V)
+        n, nh, hd = Q.shape
+        nkv = K.shape[1]
+        if scale is None:
+            scale = 1.0 / math.sqrt(hd)
+        out = torch.empty(n, nh, hd, dtype=torch.bfloat16, device=Q.device)
+        self.ctx.check(self.lib.cwk_gqa_prefill(self.ctx.h, _p(Q), _p(K), _p(V), pos, n, nh, nkv, hd, scale,
+                                                _p(out)))
+        return out
+
+    # ---- FP8 projection ------------------------------------------------------------
+    def fp8_linear(self, X, W, scale_inv, out_bf16=False):
+        """X [n][k] bf16; W uint8 [cols][k] (E4M3 codes); scale_inv f32 [cols/128][k/128]."""
+        n, k = X.shape
+        cols = W.shape[0]
+        Y = torch.empty(n, cols, dtype=torch.bfloat16 if out_bf16 else torch.float32, device=X.device)
+        self.ctx.check(self.lib.cwk_fp8_linear(self.ctx.h, _p(X), _p(W), _p(scale_inv), n, k, cols, _p(Y),
+                                               1 if out_bf16 else 0))
+        return Y

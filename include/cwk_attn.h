@@ -1,0 +1,170 @@
+/* cwk_attn.h -- C ABI of the B200 attention engine (libcwk_attn.so).
+ *
+ * Plain C: opaque context, raw pointers, sizes. No C++ or framework types cross
+ * this boundary. Unless a function says "host", every data pointer is a DEVICE
+ * pointer on the context's device and the call is asynchronous on the
+ * context's stream. Every function returns a cwk_status; the numeric values of
+ * the first nine are those of the reference's cwick_status (src/cwick.h:39-49)
+ * so a caller can hand them through unchanged. Nothing here falls back to the
+ * CPU: without a usable CUDA device cwk_ctx_create fails and no other entry
+ * point can be reached.
+ *
+ * Layout conventions (row-major, innermost last):
+ *   latent cache   bf16 [rows][ld]          row = [L latent | R rope key], ld >= L+R
+ *   MLA query      bf16 [B][nh][L+R]        q_nope already absorbed through W_k
+ *   MLA output     bf16 [B][nh][L]          softmax-weighted latent
+ *   GQA cache      bf16 [rows][nkv][hd]     K and V separate
+ *   partial        f32  {m[nh], l[nh], o[nh][L]}  o UN-normalised: sum e^(s-m) c
+ */
+#ifndef CWK_ATTN_H
+#define CWK_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CWK_API __attribute__((visibility("default")))
+#else
+#define CWK_API
+#endif
+
+typedef enum cwk_status {
+    CWK_OK = 0,
+    CWK_ERR_IO = 1,
+    CWK_ERR_PARSE = 2,
+    CWK_ERR_CONTRACT = 3,
+    CWK_ERR_MEMORY = 4,
+    CWK_ERR_STATE = 5,
+    CWK_ERR_ARGUMENT = 6,
+    CWK_ERR_UNSUPPORTED = 7,
+    CWK_ERR_NOT_FOUND = 8,
+    CWK_ERR_CUDA = 100 /* a CUDA runtime call failed; text in cwk_last_error */
+} cwk_status;
+
+typedef struct cwk_ctx cwk_ctx;
+
+/* ---- context -------------------------------------------------------------
+ * One context per engine slot (the reference runs one request thread per slot,
+ * src/engine.c:78-88): it owns a stream, the split-KV scratch and the last
+ * error text. Not thread-safe; use one per thread. */
+CWK_API int cwk_ctx_create(int device, cwk_ctx **out);
+CWK_API void cwk_ctx_destroy(cwk_ctx *ctx);
+/* Run on a caller-owned cudaStream_t instead of the context's own. */
+CWK_API int cwk_ctx_set_stream(cwk_ctx *ctx, void *cuda_stream);
+CWK_API int cwk_ctx_sync(cwk_ctx *ctx);
+CWK_API const char *cwk_last_error(const cwk_ctx *ctx);
+/* Number of kernel launches this context has issued (for launch accounting). */
+CWK_API uint64_t cwk_ctx_launch_count(const cwk_ctx *ctx);
+/* How many SMs the context's device has (grid sizing is a multiple of it). */
+CWK_API int cwk_ctx_sm_count(const cwk_ctx *ctx);
+/* Kernel timing for roofline accounting. While on, every entry point brackets
+ * its MAIN kernel (not the split merge) with CUDA events on the context's
+ * stream. cwk_ctx_profile_read synchronises, returns the summed milliseconds and
+ * the number of bracketed launches since the last read, and clears them. Do not
+ * turn it on inside a stream capture. */
+CWK_API int cwk_ctx_profile(cwk_ctx *ctx, int on);
+CWK_API int cwk_ctx_profile_read(cwk_ctx *ctx, double *total_ms, int *launches);
+/* Which implementation the next cwk_mla_decode call would take for these
+ * dimensions: 2 = tcgen05/TMA kernel, 1 = mma.sync kernel, 0 = generic. */
+CWK_API int cwk_mla_decode_path(const cwk_ctx *ctx, int nh, int L, int R);
+/* Force a path (same codes; -1 = automatic). For A/B measurement and tests. */
+CWK_API int cwk_ctx_force_mla_path(cwk_ctx *ctx, int path);
+
+/* ---- MLA absorbed decode ---------------------------------------------------
+ * Replaces the attention reduction inside mla_latent_decode
+ * (src/attention.c:746-811: score loop, cwick_softmax, c_acc loop), for B
+ * independent sequences in one launch -- the batched form of the serial
+ * per-slot loop in cwick_forward_group (src/engine.c:1373-1383). The rope term
+ * and scale follow the expanded path (src/attention.c:1051, :1108-1112).
+ *   q        bf16 [B][nh][L+R]
+ *   cache    bf16, sequence b starts at cache + b*seq_stride elements; rows of
+ *            ld elements. seq_stride may be 0 (all queries read one cache: the
+ *            causal-prefill use, kv_len[b] = position of query b + 1).
+ *   kv_len   int32 [B] on the device; max_kv_len >= every kv_len[b] (host value,
+ *            used only to size the launch).
+ *   sel      optional int32 [B][sel_ld] row indices (DSA sparse gather,
+ *            src/attention.c:757 `sel ? sel[i] : i`); then kv_len[b] counts
+ *            selected rows. NULL = rows 0..kv_len[b]-1.
+ *   out      bf16 [B][nh][L].  kv_len[b] == 0 writes zeros.
+ * n_splits: 0 = choose from the SM count. */
+CWK_API int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride,
+                   int64_t ld, const int32_t *kv_len, int max_kv_len, const int32_t *sel,
+                   int64_t sel_ld, int B, int nh, int L, int R, float scale, void *out,
+                   int n_splits);
+
+/* Same inputs in HOST memory (q, kv_len, sel, out host; cache stays a device
+ * pointer: the cache lives on the GPU across steps, as the reference's lives
+ * in engine memory across calls, src/engine.c:2889-2905). Copies in, runs,
+ * copies out and synchronises: the per-token call a CPU-resident engine makes. */
+CWK_API int cwk_mla_decode_host(cwk_ctx *ctx, const void *q_host, const void *cache_dev,
+                        int64_t seq_stride, int64_t ld, const int32_t *kv_len_host,
+                        const int32_t *sel_host, int64_t sel_ld, int B, int nh, int L,
+                        int R, float scale, void *out_host, int n_splits);
+
+/* One KV range [row0, row0+rows) of one sequence -> an un-normalised partial
+ * (f32, nh*(L+2) floats, layout above). No reference counterpart as a
+ * function; it is the per-slice accumulator of dec_out_slices
+ * (src/q35_model.c:1486-1506) generalised to carry (m, l). */
+CWK_API int cwk_mla_decode_partial(cwk_ctx *ctx, const void *q, const void *cache, int64_t ld,
+                           int64_t row0, int64_t rows, int nh, int L, int R, float scale,
+                           float *partial);
+
+/* Merge G partials [G][nh*(L+2)] f32 -> out bf16 [nh][L]:
+ * out = sum_g e^(m_g-M) o_g / sum_g e^(m_g-M) l_g. Replaces the slice sum at
+ * src/q35_model.c:1693-1701. Partials with l == 0 are ignored. */
+CWK_API int cwk_lse_combine(cwk_ctx *ctx, const float *partials, int G, int nh, int L, void *out);
+
+/* ---- DSA lightning indexer -------------------------------------------------
+ * Scores: sc[b][c] = sum_h wt[b][h] * ReLU(q[b][h] . k[b][c]) in the
+ * reference's exact f32 order (src/attention.c:573-582 with dot_f32's
+ * four-accumulator grouping, :249-258), so that selections are reproducible
+ * bit for bit.
+ *   keys   E4M3 [B][key_stride rows][hd], kscale f32 [B][key_stride]: element =
+ *          e4m3(code) * kscale (f32 product) before the dot.
+ *   q      f32 [B][ih][hd];  wt f32 [B][ih] (already multiplied by
+ *          1/sqrt(hd*ih), :564-565);  n int32 [B] device;  sc f32 [B][key_stride]. */
+CWK_API int cwk_indexer_scores_fp8(cwk_ctx *ctx, const void *keys, const float *kscale,
+                           int64_t key_stride, const float *q, const float *wt,
+                           const int32_t *n, int max_n, int B, int ih, int hd, float *sc);
+
+/* Exact top-`want` per sequence with the reference's ordering
+ * (src/attention.c:592-598): scores above the want-th largest in index order,
+ * then scores equal to it in index order, `want` entries in all. keep_self != 0
+ * appends row n-1 when absent (:618-621). n[b] <= want selects rows 0..n-1
+ * (:556). sel int32 [B][sel_ld], nsel int32 [B]; sel_ld >= want+1. */
+CWK_API int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n,
+                    int max_n, int B, int want, int keep_self, int32_t *sel,
+                    int64_t sel_ld, int32_t *nsel);
+
+/* ---- Qwen3.5-style GQA -----------------------------------------------------
+ * Single-query decode. Replaces dec_scores / dec_softmax / dec_out_slices and
+ * the slice sum (src/q35_model.c:1460-1518, :1656-1712).
+ *   q bf16 [B][nh][hd]; K,V bf16, sequence b at +b*seq_stride elements, rows of
+ *   nkv*hd; kv_len int32 [B] device; out bf16 [B][nh][hd]. */
+CWK_API int cwk_gqa_decode(cwk_ctx *ctx, const void *q, const void *K, const void *V,
+                   int64_t seq_stride, const int32_t *kv_len, int max_kv_len, int B, int nh,
+                   int nkv, int hd, float scale, void *out, int n_splits);
+
+/* Causal prefill of n queries at positions pos..pos+n-1 against pos+n cached
+ * rows. Replaces the per-(head, 128-query tile) QK^T / masked softmax / SV of
+ * mixer_attn (src/q35_model.c:1713-1746).
+ *   Q bf16 [n][nh][hd]; K,V bf16 [pos+n][nkv][hd]; out bf16 [n][nh][hd]. */
+CWK_API int cwk_gqa_prefill(cwk_ctx *ctx, const void *Q, const void *K, const void *V, int64_t pos,
+                    int n, int nh, int nkv, int hd, float scale, void *out);
+
+/* ---- FP8 block-scaled projection -------------------------------------------
+ * Y[n][cols] = X[n][k] . W[cols][k]^T with W in E4M3 and one F32 multiplier
+ * per 128x128 block (scale_inv [ceil(cols/128)][ceil(k/128)]). Replaces
+ * cwick_linear's FP8 branch (src/tensor.c:745-765 -> cwick_gemm_fp8 :715-742,
+ * cwick_gemv_fp8 :674-691). X bf16, Y f32 (out_bf16 == 0) or bf16. */
+CWK_API int cwk_fp8_linear(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv,
+                   int64_t n, int64_t k, int64_t cols, void *Y, int out_bf16);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CWK_ATTN_H */
