@@ -268,6 +268,13 @@ def run_ours(args):
             fn()
             e1[i].record(stream)
         barrier()
+        # nvidia-smi needs ~0.1 s per sample: if the timed region was shorter than a few
+        # samples, keep the SAME load running (untimed) until the sampler has seen it.
+        t_end = time.perf_counter() + 1.5
+        while len(sampler.lines) < 6 and time.perf_counter() < t_end:
+            for _ in range(8):
+                fn()
+            torch.cuda.synchronize(dev)
         clocks = sampler.stop()
         ms = sum(a.elapsed_time(b) for a, b in zip(e0, e1))
         if world > 1:
@@ -383,7 +390,7 @@ def side_measure(attn, dev, stream, B, T, peak):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))

@@ -22,7 +22,8 @@ struct FlashRowsParams {
     const uint16_t *v;        // == k for MODE_MLA
     int64_t seq_stride;       // elements between sequences in k / v
     int64_t ld;               // elements per cached row
-    const int32_t *kv_len;    // [B] device (MLA, GQA_DEC)
+    const int32_t *kv_len;    // [B] device (MLA, GQA_DEC); NULL -> kv_len_imm for every sequence
+    int kv_len_imm;
     const int32_t *sel;       // optional row gather (MLA)
     int64_t sel_ld;
     int nh, nkv, group;
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
         tile_begin = 0;
         tile_end = (kmax + TK - 1) / TK;
     } else {
-        limit_uniform = p.kv_len[b];
+        limit_uniform = p.kv_len ? p.kv_len[b] : p.kv_len_imm;
         int ntiles = (limit_uniform + TK - 1) / TK;
         tile_begin = (int)((int64_t)ntiles * split / p.nsplit);
         tile_end = (int)((int64_t)ntiles * (split + 1) / p.nsplit);

@@ -23,10 +23,10 @@ bool cwk_mla_decode_tc_available();
 __global__ void __launch_bounds__(128) mla_decode_general_kernel(
     const uint16_t *q, const uint16_t *cache, int64_t seq_stride, int64_t ld, const int32_t *kv_len,
     const int32_t *sel, int64_t sel_ld, int nh, int L, int R, float scale, float *partial,
-    int nsplit) {
+    int nsplit, int kv_len_imm) {
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n = kv_len[b];
+    const int n = kv_len ? kv_len[b] : kv_len_imm;
     const int t0 = (int)((int64_t)n * split / nsplit), t1 = (int)((int64_t)n * (split + 1) / nsplit);
     const int DKq = L + R;
     const uint16_t *qh = q + ((int64_t)b * nh + h) * DKq;
@@ -102,7 +102,7 @@ using MlaSmem = FlashRowsSmem<64, 576, 512, 64, 8, false>;
 static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
                       const int32_t *kv_len, int max_kv_len, const int32_t *sel, int64_t sel_ld, int B,
                       int nh, int L, int R, float scale, void *out, float *partial_out, int n_splits) {
-    if (!ctx || !q || !cache || !kv_len || (!out && !partial_out)) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: null argument");
+    if (!ctx || !q || !cache || (!kv_len && !partial_out) || (!out && !partial_out)) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: null argument");
     if (B <= 0 || nh <= 0 || L <= 0 || R < 0 || max_kv_len < 0 || ld < L + R)
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: bad dimensions B=%d nh=%d L=%d R=%d ld=%lld", B, nh, L, R, (long long)ld);
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -142,7 +142,7 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
         }
         FlashRowsParams p{};
         p.q = (const uint16_t *)q; p.k = (const uint16_t *)cache; p.v = p.k;
-        p.seq_stride = seq_stride; p.ld = ld; p.kv_len = kv_len; p.sel = sel; p.sel_ld = sel_ld;
+        p.seq_stride = seq_stride; p.ld = ld; p.kv_len = kv_len; p.kv_len_imm = max_kv_len; p.sel = sel; p.sel_ld = sel_ld;
         p.nh = nh; p.nkv = 1; p.group = nh; p.scale_log2 = scale * 1.4426950408889634f;
         p.partial = partial; p.out = nullptr; p.nsplit = ns; p.direct = 0;
         kern<<<dim3(ns, hblocks, B), 256, MlaSmem::TOTAL, ctx->stream>>>(p);
@@ -150,7 +150,7 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     } else {
         mla_decode_general_kernel<<<dim3(ns, nh, B), 128, 0, ctx->stream>>>(
             (const uint16_t *)q, (const uint16_t *)cache, seq_stride, ld, kv_len, sel, sel_ld, nh, L, R,
-            scale, partial, ns);
+            scale, partial, ns, max_kv_len);
         CWK_LAUNCH_CHECK(ctx, "mla_decode_general_kernel");
     }
     }
@@ -218,14 +218,9 @@ int cwk_mla_decode_partial(cwk_ctx *ctx, const void *q, const void *cache, int64
                            int64_t rows, int nh, int L, int R, float scale, float *partial) {
     if (!ctx || !partial || rows < 0 || row0 < 0) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode_partial: bad argument");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
-    // The range length travels through the staging buffer's first word.
-    int s = cwk_reserve_stage(ctx, 256, 256);
-    if (s != CWK_OK) return s;
-    *(int32_t *)ctx->stage_pin = (int32_t)rows;
-    CWK_CUDA(ctx, cudaMemcpyAsync(ctx->stage_dev, ctx->stage_pin, 4, cudaMemcpyHostToDevice, ctx->stream));
     // Split inside the GPU as usual, then fold the splits into ONE un-normalised record.
     const uint16_t *base = (const uint16_t *)cache + row0 * ld;
-    return mla_launch(ctx, q, base, 0, ld, (const int32_t *)ctx->stage_dev, (int)rows, nullptr, 0, 1, nh, L, R,
+    return mla_launch(ctx, q, base, 0, ld, nullptr, (int)rows, nullptr, 0, 1, nh, L, R,
                       scale, nullptr, partial, 0);
 }
 
