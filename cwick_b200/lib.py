@@ -28,6 +28,7 @@ SIGNATURES = {
     "cwk_ctx_force_mla_path": (i32, [vp, i32]),
     "cwk_mla_decode": (i32, [vp, vp, vp, i64, i64, vp, i32, vp, i64, i32, i32, i32, i32, f32, vp, i32]),
     "cwk_mla_decode_host": (i32, [vp, vp, vp, i64, i64, vp, vp, i64, i32, i32, i32, i32, f32, vp, i32]),
+    "cwk_mla_decode_noalloc": (i32, [vp, vp, vp, i64, i64, vp, i32, i32, i32, f32, vp, C.c_char_p, C.c_size_t]),
     "cwk_mla_decode_partial": (i32, [vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, vp]),
     "cwk_lse_combine": (i32, [vp, vp, i32, i32, i32, vp]),
     "cwk_indexer_scores_fp8": (i32, [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, vp]),

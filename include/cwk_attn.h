@@ -105,6 +105,32 @@ CWK_API int cwk_mla_decode_host(cwk_ctx *ctx, const void *q_host, const void *ca
                         const int32_t *sel_host, int64_t sel_ld, int B, int nh, int L,
                         int R, float scale, void *out_host, int n_splits);
 
+/* MLA absorbed decode that allocates nothing. No counterpart in the reference
+ * (its attention mallocs and frees scratch on every call, src/attention.c:666-671
+ * and :900-901). For hosts that cannot call cudaMalloc when they need attention:
+ * a server whose own arena owns the whole device and forbids later driver
+ * allocations, a latency-bound request thread that cannot afford the device-wide
+ * synchronisation an allocation implies, or code running where allocation calls
+ * are not allowed at all. Same arithmetic and layouts as cwk_mla_decode for
+ * L = 512, R = 64 without a gather list; no context: it runs on `cuda_stream` of
+ * the CURRENT device, which must be the one holding the buffers.
+ *   - The split records go to a 16 MiB array built into the library (held by every
+ *     GPU that loads it, until the process exits) instead of a grown buffer: that
+ *     is room for 127 records at 64 heads. B sequences need at least B records;
+ *     more than fit is refused with CWK_ERR_ARGUMENT and a message in `err`
+ *     (nothing is launched); fewer splits per sequence are used when B is large.
+ *   - It calls no cudaMalloc, cudaFree or allocating library routine, on any call.
+ *   - The FIRST call on each device also resolves the array's device address and
+ *     sets one kernel attribute; make that first call before any stream capture.
+ *   - All calls on a device share the one array and it keeps the last call's
+ *     contents: two calls that overlap on the GPU (different streams, no ordering)
+ *     race on it. Calls on one stream are ordered and safe.
+ *   err may be NULL; otherwise it receives a NUL-terminated message on failure. */
+CWK_API int cwk_mla_decode_noalloc(void *cuda_stream, const void *q, const void *cache,
+                                   int64_t seq_stride, int64_t ld, const int32_t *kv_len,
+                                   int max_kv_len, int B, int nh, float scale, void *out,
+                                   char *err, size_t err_cap);
+
 /* One KV range [row0, row0+rows) of one sequence -> an un-normalised partial
  * (f32, nh*(L+2) floats, layout above). No reference counterpart as a
  * function; it is the per-slice accumulator of dec_out_slices
