@@ -29,6 +29,8 @@ struct cwk_ctx {
     bool profiling = false;
     std::vector<cudaEvent_t> ev;      // pool, pairs (2i, 2i+1)
     size_t ev_used = 0;
+    // device word written by kernels whose bounded waits gave up (0 = fine)
+    int *dev_err = nullptr;
     char err[512] = {0};
 };
 
@@ -36,6 +38,8 @@ int cwk_fail(cwk_ctx *ctx, int status, const char *fmt, ...);
 int cwk_check_cuda(cwk_ctx *ctx, cudaError_t e, const char *what);
 int cwk_reserve_scratch(cwk_ctx *ctx, size_t bytes);
 int cwk_reserve_stage(cwk_ctx *ctx, size_t dev_bytes, size_t pin_bytes);
+// After a stream synchronise: turn a kernel-side give-up code into CWK_ERR_STATE.
+int cwk_check_device_error(cwk_ctx *ctx);
 
 // Brackets a main-kernel launch with events when profiling is on.
 struct CwkKernelTimer {

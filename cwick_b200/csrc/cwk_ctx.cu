@@ -57,6 +57,15 @@ int cwk_reserve_stage(cwk_ctx *ctx, size_t dev_bytes, size_t pin_bytes) {
     return CWK_OK;
 }
 
+int cwk_check_device_error(cwk_ctx *ctx) {
+    if (!ctx->dev_err) return CWK_OK;
+    int code = 0;
+    CWK_CUDA(ctx, cudaMemcpy(&code, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (code == 0) return CWK_OK;
+    cudaMemset(ctx->dev_err, 0, sizeof(int));
+    return cwk_fail(ctx, CWK_ERR_STATE, "a kernel gave up a bounded wait (code %d); its results are invalid", code);
+}
+
 extern "C" {
 
 int cwk_ctx_create(int device, cwk_ctx **out) {
@@ -88,6 +97,7 @@ void cwk_ctx_destroy(cwk_ctx *ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage_dev) cudaFree(ctx->stage_dev);
     if (ctx->stage_pin) cudaFreeHost(ctx->stage_pin);
+    if (ctx->dev_err) cudaFree(ctx->dev_err);
     for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -107,7 +117,7 @@ int cwk_ctx_set_stream(cwk_ctx *ctx, void *cuda_stream) {
 int cwk_ctx_sync(cwk_ctx *ctx) {
     if (!ctx) return CWK_ERR_ARGUMENT;
     CWK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return CWK_OK;
+    return cwk_check_device_error(ctx);
 }
 
 const char *cwk_last_error(const cwk_ctx *ctx) { return ctx ? ctx->err : "no context"; }

@@ -210,6 +210,8 @@ int cwk_mla_decode_host(cwk_ctx *ctx, const void *q_host, const void *cache_dev,
     if (s != CWK_OK) return s;
     CWK_CUDA(ctx, cudaMemcpyAsync(pin + o_o, dev + o_o, ob, cudaMemcpyDeviceToHost, ctx->stream));
     CWK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    s = cwk_check_device_error(ctx);
+    if (s != CWK_OK) return s;
     memcpy(out_host, pin + o_o, ob);
     return CWK_OK;
 }

@@ -1,9 +1,459 @@
-// mla_decode_tc.cu -- tcgen05/TMA MLA decode (placeholder until the kernel lands).
+// mla_decode_tc.cu -- MLA absorbed decode on the Blackwell tensor path:
+// TMA-staged cache tiles, tcgen05.mma with accumulators in tensor memory.
+//
+// Shape: 64 heads, 512-d latent + 64-d rope key, bf16. The 64 heads are too few
+// rows for a full-rate MMA (M = 128), so both products are issued transposed,
+// with the 128 TOKENS of a tile as the MMA's M dimension:
+//
+//   S^T[128 tok][64 heads] = K[128 tok][576] . Q[64 heads][576]^T        (A, B K-major)
+//   O^T[512 dv ][64 heads] += V^T[512 dv][128 tok] . P^T[128 tok][64 heads]   (A, B MN-major)
+//
+// K and V are the same shared-memory bytes: a tile is nine [128 tok][64 dim]
+// blocks (8 latent + 1 rope) written by TMA with the 128-byte swizzle, read
+// K-major for the first product and MN-major for the second. P^T (bf16) is
+// written by the softmax warps into the rope block's slot, which is dead once
+// S^T is complete. Tensor memory holds O^T (4 x 64 columns) and S^T (64).
+//
+// One tile is resident at a time (Q 72 KB + tile 144 KB of the 227 KB), and its
+// blocks are recycled as soon as the second product has consumed them, so the
+// next tile streams in behind the MMAs of this one.
+//
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps
+// 4..7 = softmax / correction / epilogue (TMEM lane quarter = warp % 4).
+// Every mbarrier wait is bounded; a wait that gives up records a code in a
+// device word and the block tears down (TMEM freed, copies drained).
+#include <cuda.h>
+
+#include <algorithm>
+
 #include "cwk_common.cuh"
 
-bool cwk_mla_decode_tc_available() { return false; }
+namespace {
 
-int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *, const void *, int64_t, int64_t, const int32_t *,
-                             int, int, int, float, float *, int) {
-    return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode not built");
+constexpr int NH = 64, L = 512, DK = 576;
+constexpr int TILE = 128;                       // tokens per tile = MMA M
+constexpr int NBLK = 9;                         // 64-element column blocks per row
+constexpr int RP = 8;                           // index of the rope block / P^T slot
+constexpr int KV_BLK = TILE * 128;              // 16384 B
+constexpr int Q_BLK = NH * 128;                 // 8192 B
+constexpr int OFF_Q = 0;
+constexpr int OFF_KV = NBLK * Q_BLK;            // 73728
+constexpr int OFF_BAR = OFF_KV + NBLK * KV_BLK; // 221184
+constexpr int OFF_MISC = OFF_BAR + 256;
+constexpr int SMEM_USED = OFF_MISC + 2048;
+constexpr int SMEM_TOTAL = SMEM_USED + 1024;    // slack to align the base to 1024 B
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_O = 0, COL_S = 256;
+
+// barrier slots (8 bytes each) inside OFF_BAR
+enum { B_FULL = 0, B_EMPTY_L = 9, B_EMPTY_RP = 13, B_QFULL = 14, B_SFULL = 15, B_PFULL = 16, B_COUNT = 17 };
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (and records `code`) when it gives up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *err, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+        if (mbar_try(bar, parity)) return true;
+    atomicCAS(err, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tm, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tm, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (Blackwell).
+// addr / lbo / sbo in bytes. bits [0,14) addr>>4, [16,30) lbo>>4, [32,46) sbo>>4,
+// [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor for kind::f16: f32 accumulate, bf16 A and B.
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+#define TMEM_LD16(arr, off, taddr)                                                                          \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];" \
+                 : "=r"(arr[off + 0]), "=r"(arr[off + 1]), "=r"(arr[off + 2]), "=r"(arr[off + 3]),          \
+                   "=r"(arr[off + 4]), "=r"(arr[off + 5]), "=r"(arr[off + 6]), "=r"(arr[off + 7]),          \
+                   "=r"(arr[off + 8]), "=r"(arr[off + 9]), "=r"(arr[off + 10]), "=r"(arr[off + 11]),        \
+                   "=r"(arr[off + 12]), "=r"(arr[off + 13]), "=r"(arr[off + 14]), "=r"(arr[off + 15])       \
+                 : "r"(taddr))
+#define TMEM_ST16(arr, off, taddr)                                                                          \
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};" \
+                 ::"r"(arr[off + 0]), "r"(arr[off + 1]), "r"(arr[off + 2]), "r"(arr[off + 3]),              \
+                   "r"(arr[off + 4]), "r"(arr[off + 5]), "r"(arr[off + 6]), "r"(arr[off + 7]),              \
+                   "r"(arr[off + 8]), "r"(arr[off + 9]), "r"(arr[off + 10]), "r"(arr[off + 11]),            \
+                   "r"(arr[off + 12]), "r"(arr[off + 13]), "r"(arr[off + 14]), "r"(arr[off + 15]),          \
+                   "r"(taddr)                                                                               \
+                 : "memory")
+
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ float warp_max_f32(float x) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+struct TcParams {
+    const int32_t *kv_len;
+    float *partial;        // [B][nsplit][NH*(L+2)]
+    int nsplit;
+    float scale_log2;
+    int *err;              // device word, 0 = fine
+    int batch_coord_zero;  // all sequences read cache slice 0 (shared cache)
+};
+
+__global__ void __launch_bounds__(256, 1)
+mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+                     const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;             // 1024-byte aligned (swizzle atom)
+    uint8_t *sm = smem_raw + (base - raw);
+    const uint32_t bar0 = base + OFF_BAR;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + OFF_MISC);
+    int *s_flag = reinterpret_cast<int *>(sm + OFF_MISC + 16);        // [2][4]
+    float *s_mref = reinterpret_cast<float *>(sm + OFF_MISC + 64);    // [64]
+    float *s_alpha = s_mref + 64;                                     // [64]
+    float *s_w = s_alpha + 64;                                        // [4][64] per-warp max / sum
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, b = blockIdx.y;
+    const int kv = p.kv_len[b];
+    const int ntiles = (kv + TILE - 1) / TILE;
+    const int t0 = (int)((int64_t)ntiles * split / p.nsplit);
+    const int t1 = (int)((int64_t)ntiles * (split + 1) / p.nsplit);
+    const int n = t1 - t0;
+    float *rec = p.partial + ((int64_t)b * p.nsplit + split) * (int64_t)(NH * (L + 2));
+
+    if (n <= 0) {                       // empty split: a record the merge ignores
+        for (int i = tid; i < NH * (L + 2); i += 256) rec[i] = (i < NH) ? -INFINITY : 0.f;
+        return;
+    }
+
+    if (tid == 0) {
+        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), i == B_PFULL ? 128u : 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+    const int bz = p.batch_coord_zero ? 0 : b;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            bool ok = true;
+            mbar_expect_tx(bar(B_QFULL), NBLK * Q_BLK);
+            for (int k = 0; k < NBLK; k++) tma_load_2d(base + OFF_Q + k * Q_BLK, &tm_q, k * 64, b * NH, bar(B_QFULL));
+            int issued_it[NBLK];
+            for (int k = 0; k < NBLK; k++) issued_it[k] = -1;
+            for (int it = 0; it < n && ok; it++) {
+                const uint32_t par_free = (uint32_t)((it & 1) ^ 1);
+                const int row = (t0 + it) * TILE;
+                for (int k = 0; k < NBLK && ok; k++) {
+                    if (k == RP) ok = mbar_wait(bar(B_EMPTY_RP), par_free, p.err, 101);
+                    else if ((k & 1) == 0) ok = mbar_wait(bar(B_EMPTY_L + (k >> 1)), par_free, p.err, 102);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(B_FULL + k), KV_BLK);
+                    tma_load_3d(base + OFF_KV + k * KV_BLK, &tm_kv, k * 64, row, bz, bar(B_FULL + k));
+                    issued_it[k] = it;
+                }
+            }
+            if (!ok) {      // drain: do not leave the block with bulk copies in flight
+                mbar_wait(bar(B_QFULL), 0, p.err, 103);
+                for (int k = 0; k < NBLK; k++)
+                    if (issued_it[k] >= 0) mbar_wait(bar(B_FULL + k), (uint32_t)(issued_it[k] & 1), p.err, 104);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t ID_QK = idesc_bf16(128, 64, 0, 0);
+            constexpr uint32_t ID_PV = idesc_bf16(128, 64, 1, 1);
+            bool ok = mbar_wait(bar(B_QFULL), 0, p.err, 201);
+            for (int it = 0; it < n && ok; it++) {
+                const uint32_t par = (uint32_t)(it & 1);
+                // S^T = K Q^T over the nine column blocks (4 k-steps of 16 each)
+                for (int k = 0; k < NBLK && ok; k++) {
+                    ok = mbar_wait(bar(B_FULL + k), par, p.err, 202);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a0 = base + OFF_KV + k * KV_BLK, b0 = base + OFF_Q + k * Q_BLK;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        umma_bf16(tmem + COL_S, smem_desc(a0 + ks * 32, 16, 1024), smem_desc(b0 + ks * 32, 16, 1024),
+                                  ID_QK, (k | ks) != 0);
+                }
+                if (!ok) break;
+                umma_commit(bar(B_SFULL));
+                // O^T += V^T P^T, four 128-row blocks of dv, 8 k-steps of 16 tokens each
+                ok = mbar_wait(bar(B_PFULL), par, p.err, 203);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t pb = base + OFF_KV + RP * KV_BLK;
+                for (int mb = 0; mb < 4; mb++) {
+                    const uint32_t va = base + OFF_KV + (2 * mb) * KV_BLK;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)
+                        umma_bf16(tmem + COL_O + mb * 64, smem_desc(va + ks * 2048, KV_BLK, 1024),
+                                  smem_desc(pb + ks * 2048, KV_BLK, 1024), ID_PV, (it | ks) != 0);
+                    umma_commit(bar(B_EMPTY_L + mb));
+                }
+                umma_commit(bar(B_EMPTY_RP));
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------ softmax / correction / epilogue
+        const int q = warp & 3;                       // TMEM lane quarter
+        const int row = q * 32 + lane;                // token row inside the tile == TMEM lane
+        const int st = tid - 128;                     // 0..127
+        const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
+        float lpart[NH];
+#pragma unroll
+        for (int h = 0; h < NH; h++) lpart[h] = 0.f;
+        bool ok = true;
+        for (int it = 0; it < n; it++) {
+            ok = mbar_wait(bar(B_SFULL), (uint32_t)(it & 1), p.err, 301);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sr[NH];
+            TMEM_LD16(sr, 0, tlane + COL_S);
+            TMEM_LD16(sr, 16, tlane + COL_S + 16);
+            TMEM_LD16(sr, 32, tlane + COL_S + 32);
+            TMEM_LD16(sr, 48, tlane + COL_S + 48);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const bool valid = (t0 + it) * TILE + row < kv;
+            float s[NH];
+#pragma unroll
+            for (int h = 0; h < NH; h++) s[h] = valid ? __uint_as_float(sr[h]) * p.scale_log2 : -INFINITY;
+
+            // does any score outrun the reference maximum by more than 2^8?
+            bool need = (it == 0);
+            if (it > 0) {
+                bool ex = false;
+#pragma unroll
+                for (int h = 0; h < NH; h += 4) {
+                    const float4 mr = *reinterpret_cast<const float4 *>(s_mref + h);
+                    ex |= (s[h] > mr.x + 8.f) | (s[h + 1] > mr.y + 8.f) | (s[h + 2] > mr.z + 8.f) | (s[h + 3] > mr.w + 8.f);
+                }
+                const int any = __any_sync(0xffffffffu, ex);
+                if (lane == 0) s_flag[(it & 1) * 4 + q] = any;
+                softmax_bar();
+                need = (s_flag[(it & 1) * 4] | s_flag[(it & 1) * 4 + 1] | s_flag[(it & 1) * 4 + 2] | s_flag[(it & 1) * 4 + 3]) != 0;
+            }
+            if (need) {
+                // exact column maxima over the 128 tokens, new reference, rescale what exists
+#pragma unroll
+                for (int h = 0; h < NH; h++) {
+                    const float r = warp_max_f32(s[h]);
+                    if ((h & 31) == lane) s_w[q * 64 + h] = r;
+                }
+                softmax_bar();
+                if (st < NH) {
+                    const float M = fmaxf(fmaxf(s_w[st], s_w[64 + st]), fmaxf(s_w[128 + st], s_w[192 + st]));
+                    const float mo = s_mref[st];
+                    const float mn = (it == 0) ? M : fmaxf(mo, M);
+                    s_alpha[st] = (it == 0) ? 1.f : exp2f(mo - mn);
+                    s_mref[st] = mn;
+                }
+                softmax_bar();
+                if (it > 0) {
+#pragma unroll
+                    for (int h = 0; h < NH; h++) lpart[h] *= s_alpha[h];
+                    // O^T columns are heads: scale column h of every dv block by alpha[h]
+                    for (int cb = 0; cb < 16; cb++) {          // 16 chunks of 16 columns = 4 dv blocks x 64 heads
+                        uint32_t o[16];
+                        const uint32_t ta = tlane + COL_O + cb * 16;
+                        TMEM_LD16(o, 0, ta);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            o[j] = __float_as_uint(__uint_as_float(o[j]) * s_alpha[(cb & 3) * 16 + j]);
+                        TMEM_ST16(o, 0, ta);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            }
+            // P^T row of this token -> the rope block's slot, MN-major, 128-byte swizzle
+            uint8_t *prow = sm + OFF_KV + RP * KV_BLK + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                float pv[8];
+                const float4 m0 = *reinterpret_cast<const float4 *>(s_mref + c * 8);
+                const float4 m1 = *reinterpret_cast<const float4 *>(s_mref + c * 8 + 4);
+                pv[0] = exp2f(s[c * 8 + 0] - m0.x); pv[1] = exp2f(s[c * 8 + 1] - m0.y);
+                pv[2] = exp2f(s[c * 8 + 2] - m0.z); pv[3] = exp2f(s[c * 8 + 3] - m0.w);
+                pv[4] = exp2f(s[c * 8 + 4] - m1.x); pv[5] = exp2f(s[c * 8 + 5] - m1.y);
+                pv[6] = exp2f(s[c * 8 + 6] - m1.z); pv[7] = exp2f(s[c * 8 + 7] - m1.w);
+#pragma unroll
+                for (int j = 0; j < 8; j++) lpart[c * 8 + j] += pv[j];
+                uint4 w;
+                w.x = pack_bf16x2(pv[0], pv[1]); w.y = pack_bf16x2(pv[2], pv[3]);
+                w.z = pack_bf16x2(pv[4], pv[5]); w.w = pack_bf16x2(pv[6], pv[7]);
+                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) << 4)) = w;
+            }
+            if (!valid) {       // rows past the sequence end hold whatever the cache holds: 0 x NaN would poison O
+                const uint4 z = make_uint4(0, 0, 0, 0);
+                for (int k = 0; k < 8; k++) {
+                    uint8_t *vrow = sm + OFF_KV + k * KV_BLK + row * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(vrow + (c << 4)) = z;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar(B_PFULL));
+        }
+        // ---- epilogue: wait for the last P.V, then write the un-normalised record
+        if (ok) ok = mbar_wait(bar(B_EMPTY_RP), (uint32_t)((n - 1) & 1), p.err, 302);
+        if (ok) {
+            tc_fence_after();
+#pragma unroll
+            for (int h = 0; h < NH; h++) {
+                float v = lpart[h];
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                if ((h & 31) == lane) s_w[q * 64 + h] = v;
+            }
+            softmax_bar();
+            if (st < NH) {
+                rec[st] = s_mref[st] * 0.6931471805599453f;
+                rec[NH + st] = s_w[st] + s_w[64 + st] + s_w[128 + st] + s_w[192 + st];
+            }
+            for (int cb = 0; cb < 16; cb++) {
+                uint32_t o[16];
+                TMEM_LD16(o, 0, tlane + COL_O + cb * 16);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                // column cb*16+j = (dv block cb>>2, head (cb&3)*16+j); o[h][dv], dv = block*128 + row
+                float *dst = rec + 2 * NH + (cb >> 2) * 128 + row + (int64_t)((cb & 3) * 16) * L;
+#pragma unroll
+                for (int j = 0; j < 16; j++) dst[j * L] = __uint_as_float(o[j]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+}  // namespace
+
+bool cwk_mla_decode_tc_available() { return true; }
+
+int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
+                             const int32_t *kv_len, int max_kv_len, int B, int nh, float scale, float *partial,
+                             int nsplit) {
+    if (nh != NH) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode is built for 64 heads");
+    if (max_kv_len <= 0) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode needs a non-empty cache");
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
+    if (!ctx->dev_err) {
+        CWK_CUDA(ctx, cudaMalloc(&ctx->dev_err, sizeof(int)));
+        CWK_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
+    }
+    CUtensorMap tm_q, tm_kv;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)DK, (cuuint64_t)B * NH};
+        cuuint64_t strides[1] = {(cuuint64_t)DK * 2};
+        cuuint32_t box[2] = {64, NH};
+        cuuint32_t es[2] = {1, 1};
+        CUresult r = enc(&tm_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(q), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(q) failed: %d", (int)r);
+    }
+    const bool shared_cache = (seq_stride == 0);
+    {
+        const cuuint64_t nb = shared_cache ? 1 : (cuuint64_t)B;
+        cuuint64_t dims[3] = {(cuuint64_t)DK, (cuuint64_t)max_kv_len, nb};
+        cuuint64_t strides[2] = {(cuuint64_t)ld * 2,
+                                 shared_cache ? (cuuint64_t)ld * 2 * (cuuint64_t)max_kv_len : (cuuint64_t)seq_stride * 2};
+        cuuint32_t box[3] = {64, TILE, 1};
+        cuuint32_t es[3] = {1, 1, 1};
+        CUresult r = enc(&tm_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(cache), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(cache) failed: %d", (int)r);
+    }
+    static bool attr_set[16] = {false};
+    if (!attr_set[ctx->device & 15]) {
+        CWK_CUDA(ctx, cudaFuncSetAttribute(mla_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        attr_set[ctx->device & 15] = true;
+    }
+    TcParams p;
+    p.kv_len = kv_len; p.partial = partial; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f;
+    p.err = ctx->dev_err; p.batch_coord_zero = shared_cache ? 1 : 0;
+    mla_decode_tc_kernel<<<dim3(nsplit, B), 256, SMEM_TOTAL, ctx->stream>>>(tm_q, tm_kv, p);
+    CWK_LAUNCH_CHECK(ctx, "mla_decode_tc_kernel");
+    return CWK_OK;
 }

@@ -43,13 +43,14 @@ def oracle_out(q, cache, lens, l=L, r=R, scale=SCALE, sel=None):
 
 
 @pytest.mark.parametrize("T", [1, 63, 64, 65, 200, 1000])
-@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("path", [2, 1, 0])
 def test_single_sequence_sizes(attn, T, path):
     q, cache = make_case(10 + T, 1, 64, T)
     lens = np.array([T], np.int32)
     attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, path)
     try:
         got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+        attn.ctx.sync()          # also surfaces a kernel-side bounded-wait give-up
     finally:
         attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
     close(bf16_to_np(got), oracle_out(q, cache, lens))
@@ -96,12 +97,39 @@ def test_sparse_gather(attn):
     close(bf16_to_np(got), oracle_out(q, cache, lens, sel=sel.astype(np.int64)))
 
 
-def test_config2_full_size(attn):
-    """BASELINE config 2: batch 1, 64 heads, 8192 cached tokens."""
+@pytest.mark.parametrize("path", [2, 1])
+def test_config2_full_size(attn, path):
+    """BASELINE config 2: batch 1, 64 heads, 8192 cached tokens, on both tensor-core kernels."""
     q, cache = make_case(synth.DEFAULT_SEED, 1, 64, 8192)
     lens = np.array([8192], np.int32)
-    got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, path)
+    try:
+        got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+        attn.ctx.sync()
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
     close(bf16_to_np(got), oracle_out(q, cache, lens))
+
+
+def test_scores_that_outgrow_the_running_maximum(attn):
+    """Keys whose scores rise steeply along the sequence force the running-maximum correction
+    (later tiles beat the first tile's maximum by far more than the lazy threshold)."""
+    T = 1500
+    q, cache = make_case(123, 1, 64, T)
+    cf = synth.bf16_to_f32(cache)
+    ramp = (1.0 + 6.0 * np.arange(T, dtype=np.float32) / T)[None, :, None]
+    qf = synth.bf16_to_f32(q)
+    cf[:, :, :L] = np.abs(cf[:, :, :L]) * ramp * np.sign(qf[:, :1, :L] + 1e-6)   # align keys with head 0's query
+    cache = synth.f32_to_bf16(cf).reshape(cache.shape)
+    lens = np.array([T], np.int32)
+    for path in (2, 1):
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, path)
+        try:
+            got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+            attn.ctx.sync()
+        finally:
+            attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
+        close(bf16_to_np(got), oracle_out(q, cache, lens))
 
 
 def test_host_entry_point_matches_device_entry_point(attn):
