@@ -2,7 +2,7 @@
 """Benchmark of the CWICK attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2|c5a|c1|c4]
+                    [--workload c2|c5a|c5a8]
 
 Default workload `c2` is BASELINE.json's config 2: MLA absorbed decode, batch 1,
 64 heads, 512-d latent + 64-d rope key, 8192 cached tokens, BF16. One *step* is
@@ -44,6 +44,7 @@ WORKLOADS = {
     # name: (sequences per call, cached tokens, calls per step)
     "c2": dict(B=1, T=8192, calls=ROT, desc="config 2: MLA absorbed decode, batch 1, 64 heads, 512+64 bf16, 8192 cached tokens"),
     "c5a": dict(B=64, T=32768, calls=1, desc="config 5a on one GPU: 64 sequences x 32768 cached tokens, one batched call"),
+    "c5a8": dict(B=8, T=32768, calls=1, desc="config 5a, one GPU's share at 8 GPUs: 8 sequences x 32768 cached tokens, one batched call"),
 }
 
 
