@@ -31,6 +31,8 @@ struct cwk_ctx {
     size_t ev_used = 0;
     // device word written by kernels whose bounded waits gave up (0 = fine)
     int *dev_err = nullptr;
+    // optional device buffer for the tcgen05 kernel's phase stamps (developer aid, see cwk_ctx_debug_trace)
+    void *tc_trace = nullptr;
     char err[512] = {0};
 };
 

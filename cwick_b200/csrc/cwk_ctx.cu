@@ -145,6 +145,12 @@ int cwk_ctx_profile_read(cwk_ctx *ctx, double *total_ms, int *launches) {
     return CWK_OK;
 }
 
+int cwk_ctx_debug_trace(cwk_ctx *ctx, void *device_buffer) {
+    if (!ctx) return CWK_ERR_ARGUMENT;
+    ctx->tc_trace = device_buffer;
+    return CWK_OK;
+}
+
 int cwk_ctx_force_mla_path(cwk_ctx *ctx, int path) {
     if (!ctx || path < -1 || path > 2) return CWK_ERR_ARGUMENT;
     ctx->force_mla_path = path;

@@ -330,60 +330,78 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
 }
 
 // ---------------------------------------------------------------------------
-// Split merge. grid (nh, B), 128 threads.
+// Split merge. grid (nh, B), 128 threads. Weights e^(m_s-M) are computed once
+// into shared memory; the value pass then streams each record's row once with
+// float2 loads. FOLD = false: normalised bf16 rows out[b][h][D].
+// FOLD = true: one un-normalised record (same layout as the inputs) at rec_out.
 // ---------------------------------------------------------------------------
-static __global__ void __launch_bounds__(128) lse_combine_kernel(const float *partial, int nsplit, int nh,
-                                                          int D, uint16_t *out) {
-    const int h = blockIdx.x, b = blockIdx.y;
+constexpr int CWK_MAX_SPLITS = 512;
+
+template <bool FOLD>
+static __global__ void __launch_bounds__(128) lse_merge_kernel(const float *partial, int nsplit, int nh, int D,
+                                                               uint16_t *out, float *rec_out) {
+    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
     const int64_t rec_sz = (int64_t)nh * (D + 2);
     const float *base = partial + (int64_t)b * nsplit * rec_sz;
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; s++) {
+    __shared__ float sw[CWK_MAX_SPLITS];
+    __shared__ float red[128];
+    float mloc = -INFINITY;
+    for (int s = tid; s < nsplit; s += 128) {
         const float l = base[s * rec_sz + nh + h];
-        if (l > 0.f) M = fmaxf(M, base[s * rec_sz + h]);
+        const float m = base[s * rec_sz + h];
+        sw[s] = (l > 0.f) ? m : -INFINITY;
+        if (l > 0.f) mloc = fmaxf(mloc, m);
     }
-    float den = 0.f;
-    for (int s = 0; s < nsplit; s++) {
-        const float l = base[s * rec_sz + nh + h];
-        if (l > 0.f) den += l * __expf(base[s * rec_sz + h] - M);
+    red[tid] = mloc;
+    __syncthreads();
+    for (int o = 64; o > 0; o >>= 1) {
+        if (tid < o) red[tid] = fmaxf(red[tid], red[tid + o]);
+        __syncthreads();
     }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    for (int i = threadIdx.x * 2; i < D; i += 256) {
+    const float M = red[0];
+    __syncthreads();
+    float dloc = 0.f;
+    for (int s = tid; s < nsplit; s += 128) {
+        const float m = sw[s];
+        const float w = (m == -INFINITY) ? 0.f : __expf(m - M);
+        sw[s] = w;
+        dloc += w * base[s * rec_sz + nh + h];
+    }
+    red[tid] = dloc;
+    __syncthreads();
+    for (int o = 64; o > 0; o >>= 1) {
+        if (tid < o) red[tid] += red[tid + o];
+        __syncthreads();
+    }
+    const float den = red[0];
+    const float inv = FOLD ? 1.f : (den > 0.f ? 1.f / den : 0.f);
+    if (FOLD && tid == 0) {
+        rec_out[h] = M;
+        rec_out[nh + h] = den;
+    }
+    const float *orow = base + 2 * nh + (int64_t)h * D;
+    for (int i = tid * 2; i < D; i += 256) {
         float a0 = 0.f, a1 = 0.f;
+#pragma unroll 4
         for (int s = 0; s < nsplit; s++) {
-            const float l = base[s * rec_sz + nh + h];
-            if (l > 0.f) {
-                const float w = __expf(base[s * rec_sz + h] - M);
-                const float2 o = *reinterpret_cast<const float2 *>(base + s * rec_sz + 2 * nh + (int64_t)h * D + i);
-                a0 += w * o.x;
-                a1 += w * o.y;
-            }
+            const float w = sw[s];
+            const float2 o = *reinterpret_cast<const float2 *>(orow + s * rec_sz + i);
+            a0 += w * o.x;
+            a1 += w * o.y;
         }
-        *reinterpret_cast<uint32_t *>(out + ((int64_t)b * nh + h) * D + i) = pack_bf16x2(a0 * inv, a1 * inv);
+        if (FOLD) {
+            rec_out[2 * nh + (int64_t)h * D + i] = a0;
+            rec_out[2 * nh + (int64_t)h * D + i + 1] = a1;
+        } else {
+            *reinterpret_cast<uint32_t *>(out + ((int64_t)b * nh + h) * D + i) = pack_bf16x2(a0 * inv, a1 * inv);
+        }
     }
 }
 
-// Fold `nsplit` partial records into ONE un-normalised record (same layout):
-// m = max, l = sum e^(m_s-m) l_s, o = sum e^(m_s-m) o_s. grid (nh), 128 threads.
-static __global__ void __launch_bounds__(128) lse_fold_kernel(const float *partial, int nsplit, int nh, int D,
-                                                       float *rec_out) {
-    const int h = blockIdx.x;
-    const int64_t rec_sz = (int64_t)nh * (D + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; s++)
-        if (partial[s * rec_sz + nh + h] > 0.f) M = fmaxf(M, partial[s * rec_sz + h]);
-    float lt = 0.f;
-    for (int s = 0; s < nsplit; s++) {
-        const float l = partial[s * rec_sz + nh + h];
-        if (l > 0.f) lt += l * __expf(partial[s * rec_sz + h] - M);
-    }
-    if (threadIdx.x == 0) { rec_out[h] = M; rec_out[nh + h] = lt; }
-    for (int i = threadIdx.x; i < D; i += 128) {
-        float a = 0.f;
-        for (int s = 0; s < nsplit; s++)
-            if (partial[s * rec_sz + nh + h] > 0.f)
-                a += __expf(partial[s * rec_sz + h] - M) * partial[s * rec_sz + 2 * nh + (int64_t)h * D + i];
-        rec_out[2 * nh + (int64_t)h * D + i] = a;
-    }
+static inline void lse_combine_launch(cudaStream_t st, const float *partial, int nsplit, int nh, int D, int B,
+                                      uint16_t *out) {
+    lse_merge_kernel<false><<<dim3(nh, B), 128, 0, st>>>(partial, nsplit, nh, D, out, nullptr);
 }
-
+static inline void lse_fold_launch(cudaStream_t st, const float *partial, int nsplit, int nh, int D, float *rec_out) {
+    lse_merge_kernel<true><<<dim3(nh, 1), 128, 0, st>>>(partial, nsplit, nh, D, nullptr, rec_out);
+}

@@ -1,5 +1,5 @@
 // gqa.cu -- Qwen3.5-style grouped-query attention: single-query decode
-// (split over the key range, merged by lse_combine_kernel) and causal prefill.
+// (split over the key range, merged by lse_merge_kernel) and causal prefill.
 // Both run flash_rows_kernel with K and V as separate streams.
 #include <algorithm>
 #include <cmath>
@@ -49,7 +49,7 @@ int cwk_gqa_decode(cwk_ctx *ctx, const void *q, const void *K, const void *V, in
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "gqa_decode: pointers must be 16-byte aligned");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     const int max_tiles = std::max(1, (max_kv_len + 63) / 64);
-    int ns = n_splits > 0 ? std::min(n_splits, max_tiles) : 1;
+    int ns = n_splits > 0 ? std::min(std::min(n_splits, max_tiles), CWK_MAX_SPLITS) : 1;
     if (n_splits <= 0) {
         double best = 1e30;
         for (int c = 1; c <= std::min(max_tiles, 256); c++) {
@@ -70,8 +70,8 @@ int cwk_gqa_decode(cwk_ctx *ctx, const void *q, const void *K, const void *V, in
         s = (hd == 256) ? gqa_decode_launch<256>(ctx, p, B, nkv, ns) : gqa_decode_launch<128>(ctx, p, B, nkv, ns);
     }
     if (s != CWK_OK) return s;
-    lse_combine_kernel<<<dim3(nh, B), 128, 0, ctx->stream>>>(ctx->scratch, ns, nh, hd, (uint16_t *)out);
-    CWK_LAUNCH_CHECK(ctx, "lse_combine_kernel");
+    lse_combine_launch(ctx->stream, ctx->scratch, ns, nh, hd, B, (uint16_t *)out);
+    CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel");
     return CWK_OK;
 }
 

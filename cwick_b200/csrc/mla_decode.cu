@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(128) mla_decode_general_kernel(
 // with a small charge per split for the partial it writes and the merge reads.
 static int plan_splits(int sm_count, int blocks_per_split, int max_tiles, int requested) {
     if (max_tiles < 1) max_tiles = 1;
-    if (requested > 0) return std::min(requested, max_tiles);
+    if (requested > 0) return std::min(std::min(requested, max_tiles), CWK_MAX_SPLITS);
     int best = 1;
     double best_cost = 1e30;
     const int cap = std::min(max_tiles, 256);
@@ -109,7 +109,7 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
 
     int path = (L == 512 && R == 64 && (ld % 8) == 0 && (seq_stride % 8) == 0 &&
                 ((uintptr_t)cache % 16) == 0 && ((uintptr_t)q % 16) == 0) ? 1 : 0;
-    if (path == 1 && !sel && nh == 64 && cwk_mla_decode_tc_available()) path = 2;
+    if (path == 1 && !sel && nh == 64 && max_kv_len > 0 && cwk_mla_decode_tc_available()) path = 2;
     if (ctx->force_mla_path >= 0) {
         if (ctx->force_mla_path > path) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mla_decode: forced path %d not applicable (best %d)", ctx->force_mla_path, path);
         path = ctx->force_mla_path;
@@ -155,12 +155,12 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     }
     }
     if (out) {
-        lse_combine_kernel<<<dim3(nh, B), 128, 0, ctx->stream>>>(partial, ns, nh, L, (uint16_t *)out);
-        CWK_LAUNCH_CHECK(ctx, "lse_combine_kernel");
+        lse_combine_launch(ctx->stream, partial, ns, nh, L, B, (uint16_t *)out);
+        CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel");
     }
     if (partial_out) {          // B == 1 here
-        lse_fold_kernel<<<dim3(nh), 128, 0, ctx->stream>>>(partial, ns, nh, L, partial_out);
-        CWK_LAUNCH_CHECK(ctx, "lse_fold_kernel");
+        lse_fold_launch(ctx->stream, partial, ns, nh, L, partial_out);
+        CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel<fold>");
     }
     return CWK_OK;
 }
@@ -227,11 +227,11 @@ int cwk_mla_decode_partial(cwk_ctx *ctx, const void *q, const void *cache, int64
 }
 
 int cwk_lse_combine(cwk_ctx *ctx, const float *partials, int G, int nh, int L, void *out) {
-    if (!ctx || !partials || !out || G <= 0 || nh <= 0 || L <= 0 || (L & 1))
+    if (!ctx || !partials || !out || G <= 0 || G > CWK_MAX_SPLITS || nh <= 0 || L <= 0 || (L & 1))
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "lse_combine: bad argument");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
-    lse_combine_kernel<<<dim3(nh, 1), 128, 0, ctx->stream>>>(partials, G, nh, L, (uint16_t *)out);
-    CWK_LAUNCH_CHECK(ctx, "lse_combine_kernel");
+    lse_combine_launch(ctx->stream, partials, G, nh, L, 1, (uint16_t *)out);
+    CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel");
     return CWK_OK;
 }
 

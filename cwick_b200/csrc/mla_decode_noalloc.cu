@@ -112,8 +112,8 @@ extern "C" int cwk_mla_decode_noalloc(void *cuda_stream, const void *q, const vo
     flash_rows_kernel<MODE_MLA, 64, 576, 512, 64, 8, false><<<dim3(ns, hblocks, B), 256, Smem::TOTAL, stream>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(err, err_cap, CWK_ERR_CUDA, "flash_rows_kernel launch: %s", cudaGetErrorString(e));
-    lse_combine_kernel<<<dim3(nh, B), 128, 0, stream>>>(scratch, ns, nh, L, (uint16_t *)out);
+    lse_combine_launch(stream, scratch, ns, nh, L, B, (uint16_t *)out);
     e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(err, err_cap, CWK_ERR_CUDA, "lse_combine_kernel launch: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail(err, err_cap, CWK_ERR_CUDA, "lse_merge_kernel launch: %s", cudaGetErrorString(e));
     return CWK_OK;
 }

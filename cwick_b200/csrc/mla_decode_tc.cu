@@ -19,7 +19,8 @@
 // next tile streams in behind the MMAs of this one.
 //
 // Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps
-// 4..7 = softmax / correction / epilogue (TMEM lane quarter = warp % 4).
+// 4..11 = softmax / correction / epilogue: two groups of four warps, 32 heads
+// each (TMEM lane quarter = warp % 4).
 // Every mbarrier wait is bounded; a wait that gives up records a code in a
 // device word and the block tears down (TMEM freed, copies drained).
 #include <cuda.h>
@@ -45,6 +46,9 @@ constexpr int SMEM_TOTAL = SMEM_USED + 1024;    // slack to align the base to 10
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0, COL_S = 256;
+constexpr int HG = 32;                          // heads per softmax warp group
+constexpr float LAZY_LOG2 = 16.f;               // a score may outrun the reference exponent by 2^16 before a rescale
+constexpr int NTHREADS = 384;
 
 // barrier slots (8 bytes each) inside OFF_BAR
 enum { B_FULL = 0, B_EMPTY_L = 9, B_EMPTY_RP = 13, B_QFULL = 14, B_SFULL = 15, B_PFULL = 16, B_COUNT = 17 };
@@ -126,23 +130,37 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
                    "r"(taddr)                                                                               \
                  : "memory")
 
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ float warp_max_f32(float x) {
-    float r;
-    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
-    return r;
-}
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
+// v[0..31] per lane -> lane L returns the reduction over the 32 lanes of v[L] (31 shuffles,
+// halving the live values each stage instead of reducing every value on its own).
+template <bool IS_MAX>
+__device__ __forceinline__ float warp_transpose_reduce(float (&v)[32], int lane) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const bool hi = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < off; i++) {
+            const float send = hi ? v[i] : v[i + off];
+            const float keep = hi ? v[i + off] : v[i];
+            const float recv = __shfl_xor_sync(0xffffffffu, send, off);
+            v[i] = IS_MAX ? fmaxf(keep, recv) : keep + recv;
+        }
+    }
+    return v[0];
+}
 struct TcParams {
-    const int32_t *kv_len;
+    const int32_t *kv_len; // [B] device, or NULL: every sequence has kv_len_imm rows
+    int kv_len_imm;
     float *partial;        // [B][nsplit][NH*(L+2)]
     int nsplit;
     float scale_log2;
     int *err;              // device word, 0 = fine
     int batch_coord_zero;  // all sequences read cache slice 0 (shared cache)
+    long long *trace;      // optional: per-phase clock64 stamps of block (0,0); NULL = off
 };
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(NTHREADS, 1)
 mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                      const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -152,14 +170,14 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t bar0 = base + OFF_BAR;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + OFF_MISC);
-    int *s_flag = reinterpret_cast<int *>(sm + OFF_MISC + 16);        // [2][4]
-    float *s_mref = reinterpret_cast<float *>(sm + OFF_MISC + 64);    // [64]
+    int *s_flag = reinterpret_cast<int *>(sm + OFF_MISC + 16);        // [2][8]
+    float *s_mref = reinterpret_cast<float *>(sm + OFF_MISC + 128);   // [64]
     float *s_alpha = s_mref + 64;                                     // [64]
-    float *s_w = s_alpha + 64;                                        // [4][64] per-warp max / sum
+    float *s_w = s_alpha + 64;                                        // [8 warps][32] per-warp max / sum
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y;
-    const int kv = p.kv_len[b];
+    const int kv = p.kv_len ? p.kv_len[b] : p.kv_len_imm;
     const int ntiles = (kv + TILE - 1) / TILE;
     const int t0 = (int)((int64_t)ntiles * split / p.nsplit);
     const int t1 = (int)((int64_t)ntiles * (split + 1) / p.nsplit);
@@ -167,13 +185,25 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     float *rec = p.partial + ((int64_t)b * p.nsplit + split) * (int64_t)(NH * (L + 2));
 
     if (n <= 0) {                       // empty split: a record the merge ignores
-        for (int i = tid; i < NH * (L + 2); i += 256) rec[i] = (i < NH) ? -INFINITY : 0.f;
+        for (int i = tid; i < NH * (L + 2); i += NTHREADS) rec[i] = (i < NH) ? -INFINITY : 0.f;
         return;
     }
 
+    const int bz = p.batch_coord_zero ? 0 : b;
     if (tid == 0) {
-        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), i == B_PFULL ? 128u : 1u);
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kv) : "memory");
+        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), i == B_PFULL ? 256u : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The first tile's loads go out before the block-wide set-up (TMEM allocation, the
+        // barrier below): nothing they touch depends on it, and their latency is the longest
+        // single item of a short call.
+        mbar_expect_tx(bar(B_QFULL), NBLK * Q_BLK);
+        for (int k = 0; k < NBLK; k++) tma_load_2d(base + OFF_Q + k * Q_BLK, &tm_q, k * 64, b * NH, bar(B_QFULL));
+        for (int k = 0; k < NBLK; k++) {
+            mbar_expect_tx(bar(B_FULL + k), KV_BLK);
+            tma_load_3d(base + OFF_KV + k * KV_BLK, &tm_kv, k * 64, t0 * TILE, bz, bar(B_FULL + k));
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TMEM_COLS) : "memory");
@@ -183,23 +213,26 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    const int bz = p.batch_coord_zero ? 0 : b;
+    // trace slots: [role][tile][event]; only block (0,0) writes
+    long long *tr = (p.trace && split == 0 && b == 0) ? p.trace : nullptr;
+#define TRACE(role, it, ev) do { if (tr && (it) < 16) tr[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
+    if (tr && tid == 0) tr[3 * 16 * 8] = clock64();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             bool ok = true;
-            mbar_expect_tx(bar(B_QFULL), NBLK * Q_BLK);
-            for (int k = 0; k < NBLK; k++) tma_load_2d(base + OFF_Q + k * Q_BLK, &tm_q, k * 64, b * NH, bar(B_QFULL));
             int issued_it[NBLK];
-            for (int k = 0; k < NBLK; k++) issued_it[k] = -1;
-            for (int it = 0; it < n && ok; it++) {
+            for (int k = 0; k < NBLK; k++) issued_it[k] = 0;      // tile 0 went out during set-up
+            for (int it = 1; it < n && ok; it++) {
                 const uint32_t par_free = (uint32_t)((it & 1) ^ 1);
                 const int row = (t0 + it) * TILE;
                 for (int k = 0; k < NBLK && ok; k++) {
                     if (k == RP) ok = mbar_wait(bar(B_EMPTY_RP), par_free, p.err, 101);
                     else if ((k & 1) == 0) ok = mbar_wait(bar(B_EMPTY_L + (k >> 1)), par_free, p.err, 102);
                     if (!ok) break;
+                    if (k == 0) TRACE(0, it, 0);
+                    if (k == RP) TRACE(0, it, 1);
                     mbar_expect_tx(bar(B_FULL + k), KV_BLK);
                     tma_load_3d(base + OFF_KV + k * KV_BLK, &tm_kv, k * 64, row, bz, bar(B_FULL + k));
                     issued_it[k] = it;
@@ -223,6 +256,8 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 for (int k = 0; k < NBLK && ok; k++) {
                     ok = mbar_wait(bar(B_FULL + k), par, p.err, 202);
                     if (!ok) break;
+                    if (k == 0) TRACE(1, it, 0);
+                    if (k == RP) TRACE(1, it, 1);
                     tc_fence_after();
                     const uint32_t a0 = base + OFF_KV + k * KV_BLK, b0 = base + OFF_Q + k * Q_BLK;
 #pragma unroll
@@ -232,9 +267,11 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
                 if (!ok) break;
                 umma_commit(bar(B_SFULL));
+                TRACE(1, it, 2);
                 // O^T += V^T P^T, four 128-row blocks of dv, 8 k-steps of 16 tokens each
                 ok = mbar_wait(bar(B_PFULL), par, p.err, 203);
                 if (!ok) break;
+                TRACE(1, it, 3);
                 tc_fence_after();
                 const uint32_t pb = base + OFF_KV + RP * KV_BLK;
                 for (int mb = 0; mb < 4; mb++) {
@@ -246,75 +283,89 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     umma_commit(bar(B_EMPTY_L + mb));
                 }
                 umma_commit(bar(B_EMPTY_RP));
+                TRACE(1, it, 4);
             }
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ softmax / correction / epilogue
+        // Two groups of four warps: group g owns heads [32g, 32g+32) (S^T / O^T columns); inside a
+        // group, warp w owns TMEM lanes 32*(w%4).. = token rows (S^T) or dv rows (O^T).
         const int q = warp & 3;                       // TMEM lane quarter
+        const int g = (warp - 4) >> 2;                // head group
+        const int hb = g * HG;                        // first head of the group
         const int row = q * 32 + lane;                // token row inside the tile == TMEM lane
-        const int st = tid - 128;                     // 0..127
+        const int st = tid - 128;                     // 0..255
         const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
-        float lpart[NH];
+        float lpart[HG];
 #pragma unroll
-        for (int h = 0; h < NH; h++) lpart[h] = 0.f;
+        for (int h = 0; h < HG; h++) lpart[h] = 0.f;
         bool ok = true;
         for (int it = 0; it < n; it++) {
             ok = mbar_wait(bar(B_SFULL), (uint32_t)(it & 1), p.err, 301);
             if (!ok) break;
+            if (st == 0) TRACE(2, it, 0);
             tc_fence_after();
-            uint32_t sr[NH];
-            TMEM_LD16(sr, 0, tlane + COL_S);
-            TMEM_LD16(sr, 16, tlane + COL_S + 16);
-            TMEM_LD16(sr, 32, tlane + COL_S + 32);
-            TMEM_LD16(sr, 48, tlane + COL_S + 48);
+            uint32_t sr[HG];
+            TMEM_LD16(sr, 0, tlane + COL_S + hb);
+            TMEM_LD16(sr, 16, tlane + COL_S + hb + 16);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             const bool valid = (t0 + it) * TILE + row < kv;
-            float s[NH];
+            float s[HG];
 #pragma unroll
-            for (int h = 0; h < NH; h++) s[h] = valid ? __uint_as_float(sr[h]) * p.scale_log2 : -INFINITY;
+            for (int h = 0; h < HG; h++) s[h] = valid ? __uint_as_float(sr[h]) * p.scale_log2 : -INFINITY;
 
-            // does any score outrun the reference maximum by more than 2^8?
-            bool need = (it == 0);
-            if (it > 0) {
-                bool ex = false;
+            if (it == 0) {
+                // Reference exponent per head: the score of the tile's first token. Any value works
+                // as long as no score outruns it by more than 2^LAZY_LOG2 (checked next, every tile).
+                if (row == 0) {
 #pragma unroll
-                for (int h = 0; h < NH; h += 4) {
-                    const float4 mr = *reinterpret_cast<const float4 *>(s_mref + h);
-                    ex |= (s[h] > mr.x + 8.f) | (s[h + 1] > mr.y + 8.f) | (s[h + 2] > mr.z + 8.f) | (s[h + 3] > mr.w + 8.f);
+                    for (int h = 0; h < HG; h++) s_mref[hb + h] = s[h];
                 }
-                const int any = __any_sync(0xffffffffu, ex);
-                if (lane == 0) s_flag[(it & 1) * 4 + q] = any;
                 softmax_bar();
-                need = (s_flag[(it & 1) * 4] | s_flag[(it & 1) * 4 + 1] | s_flag[(it & 1) * 4 + 2] | s_flag[(it & 1) * 4 + 3]) != 0;
             }
+            bool ex = false;
+#pragma unroll
+            for (int h = 0; h < HG; h += 4) {
+                const float4 mr = *reinterpret_cast<const float4 *>(s_mref + hb + h);
+                ex |= (s[h] > mr.x + LAZY_LOG2) | (s[h + 1] > mr.y + LAZY_LOG2) | (s[h + 2] > mr.z + LAZY_LOG2) |
+                      (s[h + 3] > mr.w + LAZY_LOG2);
+            }
+            const int any = __any_sync(0xffffffffu, ex);
+            if (lane == 0) s_flag[(it & 1) * 8 + (warp - 4)] = any;
+            softmax_bar();
+            int need = 0;
+#pragma unroll
+            for (int w = 0; w < 8; w++) need |= s_flag[(it & 1) * 8 + w];
             if (need) {
                 // exact column maxima over the 128 tokens, new reference, rescale what exists
+                float v[HG];
 #pragma unroll
-                for (int h = 0; h < NH; h++) {
-                    const float r = warp_max_f32(s[h]);
-                    if ((h & 31) == lane) s_w[q * 64 + h] = r;
-                }
+                for (int h = 0; h < HG; h++) v[h] = s[h];
+                const float mine = warp_transpose_reduce<true>(v, lane);     // lane L: max of head hb+L over this warp's rows
+                s_w[(warp - 4) * HG + lane] = mine;
                 softmax_bar();
                 if (st < NH) {
-                    const float M = fmaxf(fmaxf(s_w[st], s_w[64 + st]), fmaxf(s_w[128 + st], s_w[192 + st]));
+                    const int gg = st >> 5, hh = st & 31;
+                    const float *w4 = s_w + gg * 4 * HG + hh;
+                    const float M = fmaxf(fmaxf(w4[0], w4[HG]), fmaxf(w4[2 * HG], w4[3 * HG]));
                     const float mo = s_mref[st];
-                    const float mn = (it == 0) ? M : fmaxf(mo, M);
-                    s_alpha[st] = (it == 0) ? 1.f : exp2f(mo - mn);
+                    const float mn = fmaxf(mo, M);
+                    s_alpha[st] = exp2f(mo - mn);
                     s_mref[st] = mn;
                 }
                 softmax_bar();
-                if (it > 0) {
 #pragma unroll
-                    for (int h = 0; h < NH; h++) lpart[h] *= s_alpha[h];
+                for (int h = 0; h < HG; h++) lpart[h] *= s_alpha[hb + h];
+                if (it > 0) {
                     // O^T columns are heads: scale column h of every dv block by alpha[h]
-                    for (int cb = 0; cb < 16; cb++) {          // 16 chunks of 16 columns = 4 dv blocks x 64 heads
+                    for (int cb = 0; cb < 8; cb++) {
                         uint32_t o[16];
-                        const uint32_t ta = tlane + COL_O + cb * 16;
+                        const uint32_t ta = tlane + COL_O + (cb >> 1) * 64 + hb + (cb & 1) * 16;
                         TMEM_LD16(o, 0, ta);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int j = 0; j < 16; j++)
-                            o[j] = __float_as_uint(__uint_as_float(o[j]) * s_alpha[(cb & 3) * 16 + j]);
+                            o[j] = __float_as_uint(__uint_as_float(o[j]) * s_alpha[hb + (cb & 1) * 16 + j]);
                         TMEM_ST16(o, 0, ta);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -323,10 +374,10 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             // P^T row of this token -> the rope block's slot, MN-major, 128-byte swizzle
             uint8_t *prow = sm + OFF_KV + RP * KV_BLK + row * 128;
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
+            for (int c = 0; c < HG / 8; c++) {
                 float pv[8];
-                const float4 m0 = *reinterpret_cast<const float4 *>(s_mref + c * 8);
-                const float4 m1 = *reinterpret_cast<const float4 *>(s_mref + c * 8 + 4);
+                const float4 m0 = *reinterpret_cast<const float4 *>(s_mref + hb + c * 8);
+                const float4 m1 = *reinterpret_cast<const float4 *>(s_mref + hb + c * 8 + 4);
                 pv[0] = exp2f(s[c * 8 + 0] - m0.x); pv[1] = exp2f(s[c * 8 + 1] - m0.y);
                 pv[2] = exp2f(s[c * 8 + 2] - m0.z); pv[3] = exp2f(s[c * 8 + 3] - m0.w);
                 pv[4] = exp2f(s[c * 8 + 4] - m1.x); pv[5] = exp2f(s[c * 8 + 5] - m1.y);
@@ -336,11 +387,11 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 uint4 w;
                 w.x = pack_bf16x2(pv[0], pv[1]); w.y = pack_bf16x2(pv[2], pv[3]);
                 w.z = pack_bf16x2(pv[4], pv[5]); w.w = pack_bf16x2(pv[6], pv[7]);
-                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) << 4)) = w;
+                *reinterpret_cast<uint4 *>(prow + (((g * (HG / 8) + c) ^ (row & 7)) << 4)) = w;
             }
             if (!valid) {       // rows past the sequence end hold whatever the cache holds: 0 x NaN would poison O
                 const uint4 z = make_uint4(0, 0, 0, 0);
-                for (int k = 0; k < 8; k++) {
+                for (int k = g * 4; k < g * 4 + 4; k++) {
                     uint8_t *vrow = sm + OFF_KV + k * KV_BLK + row * 128;
 #pragma unroll
                     for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(vrow + (c << 4)) = z;
@@ -349,37 +400,36 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             mbar_arrive(bar(B_PFULL));
+            if (st == 0) TRACE(2, it, 1);
         }
         // ---- epilogue: wait for the last P.V, then write the un-normalised record
         if (ok) ok = mbar_wait(bar(B_EMPTY_RP), (uint32_t)((n - 1) & 1), p.err, 302);
         if (ok) {
+            if (st == 0) TRACE(2, 15, 2);
             tc_fence_after();
-#pragma unroll
-            for (int h = 0; h < NH; h++) {
-                float v = lpart[h];
-                v += __shfl_xor_sync(0xffffffffu, v, 16);
-                v += __shfl_xor_sync(0xffffffffu, v, 8);
-                v += __shfl_xor_sync(0xffffffffu, v, 4);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                if ((h & 31) == lane) s_w[q * 64 + h] = v;
-            }
+            const float mine = warp_transpose_reduce<false>(lpart, lane);    // lane L: sum of head hb+L over this warp's rows
+            s_w[(warp - 4) * HG + lane] = mine;
+            if (st == 0) TRACE(2, 15, 3);
             softmax_bar();
             if (st < NH) {
+                const int gg = st >> 5, hh = st & 31;
+                const float *w4 = s_w + gg * 4 * HG + hh;
                 rec[st] = s_mref[st] * 0.6931471805599453f;
-                rec[NH + st] = s_w[st] + s_w[64 + st] + s_w[128 + st] + s_w[192 + st];
+                rec[NH + st] = (w4[0] + w4[HG]) + (w4[2 * HG] + w4[3 * HG]);
             }
-            for (int cb = 0; cb < 16; cb++) {
+            if (st == 0) TRACE(2, 15, 4);
+            for (int cb = 0; cb < 8; cb++) {
                 uint32_t o[16];
-                TMEM_LD16(o, 0, tlane + COL_O + cb * 16);
+                const int mb = cb >> 1, h0 = hb + (cb & 1) * 16;
+                TMEM_LD16(o, 0, tlane + COL_O + mb * 64 + h0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                // column cb*16+j = (dv block cb>>2, head (cb&3)*16+j); o[h][dv], dv = block*128 + row
-                float *dst = rec + 2 * NH + (cb >> 2) * 128 + row + (int64_t)((cb & 3) * 16) * L;
+                float *dst = rec + 2 * NH + mb * 128 + row + (int64_t)h0 * L;      // o[h][dv], dv = mb*128 + row
 #pragma unroll
                 for (int j = 0; j < 16; j++) dst[j * L] = __uint_as_float(o[j]);
             }
         }
     }
+    if (tr && tid == 128) tr[3 * 16 * 8 + 1] = clock64();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -451,9 +501,10 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
         attr_set[ctx->device & 15] = true;
     }
     TcParams p;
-    p.kv_len = kv_len; p.partial = partial; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f;
+    p.kv_len = kv_len; p.kv_len_imm = max_kv_len; p.partial = partial; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f;
     p.err = ctx->dev_err; p.batch_coord_zero = shared_cache ? 1 : 0;
-    mla_decode_tc_kernel<<<dim3(nsplit, B), 256, SMEM_TOTAL, ctx->stream>>>(tm_q, tm_kv, p);
+    p.trace = (long long *)ctx->tc_trace;
+    mla_decode_tc_kernel<<<dim3(nsplit, B), NTHREADS, SMEM_TOTAL, ctx->stream>>>(tm_q, tm_kv, p);
     CWK_LAUNCH_CHECK(ctx, "mla_decode_tc_kernel");
     return CWK_OK;
 }

@@ -14,7 +14,9 @@
  *   MLA query      bf16 [B][nh][L+R]        q_nope already absorbed through W_k
  *   MLA output     bf16 [B][nh][L]          softmax-weighted latent
  *   GQA cache      bf16 [rows][nkv][hd]     K and V separate
- *   partial        f32  {m[nh], l[nh], o[nh][L]}  o UN-normalised: sum e^(s-m) c
+ *   partial        f32  {m[nh], l[nh], o[nh][L]}  l = sum e^(s-m), o = sum e^(s-m) c, un-normalised;
+ *                  m is a per-head reference exponent (close to, not always equal to, the
+ *                  maximum score): only m + log(l) and o/l are meaningful on their own
  */
 #ifndef CWK_ATTN_H
 #define CWK_ATTN_H
@@ -68,6 +70,10 @@ CWK_API int cwk_ctx_sm_count(const cwk_ctx *ctx);
  * turn it on inside a stream capture. */
 CWK_API int cwk_ctx_profile(cwk_ctx *ctx, int on);
 CWK_API int cwk_ctx_profile_read(cwk_ctx *ctx, double *total_ms, int *launches);
+/* Developer aid: a device buffer of at least 4096 bytes that block (0,0) of the
+ * tcgen05 MLA decode kernel fills with clock64() stamps of its pipeline phases
+ * ([role 0..2][tile 0..15][event 0..7] as int64). NULL turns it off. */
+CWK_API int cwk_ctx_debug_trace(cwk_ctx *ctx, void *device_buffer);
 /* Which implementation the next cwk_mla_decode call would take for these
  * dimensions: 2 = tcgen05/TMA kernel, 1 = mma.sync kernel, 0 = generic. */
 CWK_API int cwk_mla_decode_path(const cwk_ctx *ctx, int nh, int L, int R);
