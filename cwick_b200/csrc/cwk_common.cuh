@@ -18,6 +18,9 @@ struct cwk_ctx {
     // split-KV scratch: [B*heads_blocks][n_splits] partials, grown on demand
     float *scratch = nullptr;
     size_t scratch_bytes = 0;
+    // workspace of the composite entry points (prefill): separate from the split scratch
+    void *work = nullptr;
+    size_t work_bytes = 0;
     // staging for the *_host entry points
     void *stage_dev = nullptr;
     size_t stage_dev_bytes = 0;
@@ -40,6 +43,7 @@ int cwk_fail(cwk_ctx *ctx, int status, const char *fmt, ...);
 int cwk_check_cuda(cwk_ctx *ctx, cudaError_t e, const char *what);
 int cwk_reserve_scratch(cwk_ctx *ctx, size_t bytes);
 int cwk_reserve_stage(cwk_ctx *ctx, size_t dev_bytes, size_t pin_bytes);
+int cwk_reserve_work(cwk_ctx *ctx, size_t bytes);
 // After a stream synchronise: turn a kernel-side give-up code into CWK_ERR_STATE.
 int cwk_check_device_error(cwk_ctx *ctx);
 

@@ -33,6 +33,19 @@ int cwk_reserve_scratch(cwk_ctx *ctx, size_t bytes) {
     return CWK_OK;
 }
 
+int cwk_reserve_work(cwk_ctx *ctx, size_t bytes) {
+    if (bytes <= ctx->work_bytes) return CWK_OK;
+    if (ctx->work) {
+        CWK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        CWK_CUDA(ctx, cudaFree(ctx->work));
+        ctx->work = nullptr;
+        ctx->work_bytes = 0;
+    }
+    CWK_CUDA(ctx, cudaMalloc(&ctx->work, bytes));
+    ctx->work_bytes = bytes;
+    return CWK_OK;
+}
+
 int cwk_reserve_stage(cwk_ctx *ctx, size_t dev_bytes, size_t pin_bytes) {
     if (dev_bytes > ctx->stage_dev_bytes) {
         if (ctx->stage_dev) {
@@ -96,6 +109,7 @@ void cwk_ctx_destroy(cwk_ctx *ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage_dev) cudaFree(ctx->stage_dev);
+    if (ctx->work) cudaFree(ctx->work);
     if (ctx->stage_pin) cudaFreeHost(ctx->stage_pin);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
     for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);

@@ -12,7 +12,7 @@
 // not apply so the caller can take the mma.sync path.
 int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride,
                              int64_t ld, const int32_t *kv_len, int max_kv_len, int B, int nh,
-                             float scale, float *partial, int nsplit);
+                             float scale, float *partial, int nsplit, void *out_direct);
 bool cwk_mla_decode_tc_available();
 
 // ---------------------------------------------------------------------------
@@ -121,8 +121,10 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     const int max_tiles = (max_kv_len + tile - 1) / tile;
     const int hblocks = (path == 0) ? nh : (nh + 63) / 64;
     int ns = plan_splits(ctx->sm_count, B * hblocks, max_tiles, n_splits);
+    // One split per sequence needs no records at all: the kernel normalises and writes bf16.
+    const bool direct = (ns == 1 && out && !partial_out && path != 0);
     const size_t rec = (size_t)nh * (L + 2) * sizeof(float);
-    {
+    if (!direct) {
         int s = cwk_reserve_scratch(ctx, rec * ns * B);
         if (s != CWK_OK) return s;
     }
@@ -131,7 +133,8 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     {
     CwkKernelTimer timer(ctx);
     if (path == 2) {
-        int s = cwk_mla_decode_tc_launch(ctx, q, cache, seq_stride, ld, kv_len, max_kv_len, B, nh, scale, partial, ns);
+        int s = cwk_mla_decode_tc_launch(ctx, q, cache, seq_stride, ld, kv_len, max_kv_len, B, nh, scale, partial, ns,
+                                         direct ? out : nullptr);
         if (s != CWK_OK) return s;
     } else if (path == 1) {
         static bool attr_set[16] = {false};
@@ -144,7 +147,7 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
         p.q = (const uint16_t *)q; p.k = (const uint16_t *)cache; p.v = p.k;
         p.seq_stride = seq_stride; p.ld = ld; p.kv_len = kv_len; p.kv_len_imm = max_kv_len; p.sel = sel; p.sel_ld = sel_ld;
         p.nh = nh; p.nkv = 1; p.group = nh; p.scale_log2 = scale * 1.4426950408889634f;
-        p.partial = partial; p.out = nullptr; p.nsplit = ns; p.direct = 0;
+        p.partial = partial; p.out = direct ? (uint16_t *)out : nullptr; p.nsplit = ns; p.direct = direct ? 1 : 0;
         kern<<<dim3(ns, hblocks, B), 256, MlaSmem::TOTAL, ctx->stream>>>(p);
         CWK_LAUNCH_CHECK(ctx, "flash_rows_kernel<MLA>");
     } else {
@@ -154,7 +157,7 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
         CWK_LAUNCH_CHECK(ctx, "mla_decode_general_kernel");
     }
     }
-    if (out) {
+    if (out && !direct) {
         lse_combine_launch(ctx->stream, partial, ns, nh, L, B, (uint16_t *)out);
         CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel");
     }

@@ -157,6 +157,8 @@ struct TcParams {
     float scale_log2;
     int *err;              // device word, 0 = fine
     int batch_coord_zero;  // all sequences read cache slice 0 (shared cache)
+    uint16_t *out;         // direct mode (nsplit == 1): normalised bf16 [B][NH][L]; NULL = write partial records
+    int reverse_b;         // schedule sequences last-to-first (causal prefill: longest first)
     long long *trace;      // optional: per-phase clock64 stamps of block (0,0); NULL = off
 };
 
@@ -176,7 +178,7 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     float *s_w = s_alpha + 64;                                        // [8 warps][32] per-warp max / sum
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int split = blockIdx.x, b = blockIdx.y;
+    const int split = blockIdx.x, b = p.reverse_b ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
     const int kv = p.kv_len ? p.kv_len[b] : p.kv_len_imm;
     const int ntiles = (kv + TILE - 1) / TILE;
     const int t0 = (int)((int64_t)ntiles * split / p.nsplit);
@@ -184,8 +186,12 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int n = t1 - t0;
     float *rec = p.partial + ((int64_t)b * p.nsplit + split) * (int64_t)(NH * (L + 2));
 
-    if (n <= 0) {                       // empty split: a record the merge ignores
-        for (int i = tid; i < NH * (L + 2); i += NTHREADS) rec[i] = (i < NH) ? -INFINITY : 0.f;
+    if (n <= 0) {                       // empty split: a record the merge ignores (direct mode: zeros)
+        if (p.out) {
+            for (int i = tid; i < NH * L / 2; i += NTHREADS) reinterpret_cast<uint32_t *>(p.out + (int64_t)b * NH * L)[i] = 0u;
+        } else {
+            for (int i = tid; i < NH * (L + 2); i += NTHREADS) rec[i] = (i < NH) ? -INFINITY : 0.f;
+        }
         return;
     }
 
@@ -414,18 +420,31 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (st < NH) {
                 const int gg = st >> 5, hh = st & 31;
                 const float *w4 = s_w + gg * 4 * HG + hh;
-                rec[st] = s_mref[st] * 0.6931471805599453f;
-                rec[NH + st] = (w4[0] + w4[HG]) + (w4[2 * HG] + w4[3 * HG]);
+                const float lsum = (w4[0] + w4[HG]) + (w4[2 * HG] + w4[3 * HG]);
+                if (p.out) {
+                    s_alpha[st] = lsum > 0.f ? 1.f / lsum : 0.f;
+                } else {
+                    rec[st] = s_mref[st] * 0.6931471805599453f;
+                    rec[NH + st] = lsum;
+                }
             }
+            if (p.out) softmax_bar();
             if (st == 0) TRACE(2, 15, 4);
             for (int cb = 0; cb < 8; cb++) {
                 uint32_t o[16];
                 const int mb = cb >> 1, h0 = hb + (cb & 1) * 16;
                 TMEM_LD16(o, 0, tlane + COL_O + mb * 64 + h0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float *dst = rec + 2 * NH + mb * 128 + row + (int64_t)h0 * L;      // o[h][dv], dv = mb*128 + row
+                if (p.out) {
+                    uint16_t *dst = p.out + ((int64_t)b * NH + h0) * L + mb * 128 + row;
 #pragma unroll
-                for (int j = 0; j < 16; j++) dst[j * L] = __uint_as_float(o[j]);
+                    for (int j = 0; j < 16; j++)
+                        dst[j * L] = (uint16_t)(pack_bf16x2(__uint_as_float(o[j]) * s_alpha[h0 + j], 0.f) & 0xffffu);
+                } else {
+                    float *dst = rec + 2 * NH + mb * 128 + row + (int64_t)h0 * L;      // o[h][dv], dv = mb*128 + row
+#pragma unroll
+                    for (int j = 0; j < 16; j++) dst[j * L] = __uint_as_float(o[j]);
+                }
             }
         }
     }
@@ -462,7 +481,7 @@ bool cwk_mla_decode_tc_available() { return true; }
 
 int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
                              const int32_t *kv_len, int max_kv_len, int B, int nh, float scale, float *partial,
-                             int nsplit) {
+                             int nsplit, void *out_direct) {
     if (nh != NH) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode is built for 64 heads");
     if (max_kv_len <= 0) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode needs a non-empty cache");
     EncodeTiledFn enc = encode_fn();
@@ -504,6 +523,8 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     p.kv_len = kv_len; p.kv_len_imm = max_kv_len; p.partial = partial; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f;
     p.err = ctx->dev_err; p.batch_coord_zero = shared_cache ? 1 : 0;
     p.trace = (long long *)ctx->tc_trace;
+    p.out = (uint16_t *)out_direct;
+    p.reverse_b = shared_cache ? 1 : 0;
     mla_decode_tc_kernel<<<dim3(nsplit, B), NTHREADS, SMEM_TOTAL, ctx->stream>>>(tm_q, tm_kv, p);
     CWK_LAUNCH_CHECK(ctx, "mla_decode_tc_kernel");
     return CWK_OK;

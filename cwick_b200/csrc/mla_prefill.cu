@@ -1,0 +1,175 @@
+// mla_prefill.cu -- MLA causal prefill of a chunk of n tokens: FP8 block-scaled
+// q/kv projections, RMS norms, RoPE on the 64 rope dims, the absorb of q_nope
+// through W_uk, the latent-cache rows, and causal absorbed attention.
+//
+// The reference does this per token (cwick_attention_mla_prefill_chunk,
+// src/attention.c:943-1024: three projection GEMMs, per-token norms and latent
+// writes, then mla_latent_decode per token). Here every stage is one batched
+// kernel over the chunk, and the attention is one launch in which query i sees
+// cache rows 0..pos0+i.
+#include "cwk_common.cuh"
+
+extern "C" int cwk_fp8_linear(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv, int64_t n,
+                              int64_t k, int64_t cols, void *Y, int out_bf16);
+extern "C" int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
+                              const int32_t *kv_len, int max_kv_len, const int32_t *sel, int64_t sel_ld, int B,
+                              int nh, int L, int R, float scale, void *out, int n_splits);
+
+// Row-wise RMS norm of an f32 matrix (sum of squares in double, as
+// cwick_rms_norm does, src/tensor.c:780-791), times a bf16 weight
+// (apply_bf16_vec, src/attention.c:70-73), written as bf16. Columns
+// [norm_cols, cols) are not normalised: they get the adjacent-pair RoPE of
+// src/attention.c:60-68 at position pos0 + row when rope_cols > 0, else are
+// copied. One block of 256 threads per row.
+__global__ void __launch_bounds__(256) norm_rope_rows_kernel(const float *in, int64_t in_ld, int norm_cols,
+                                                             int rope_cols, const uint16_t *weight, float eps,
+                                                             float rope_base, int64_t pos0, uint16_t *out,
+                                                             int64_t out_ld, int *kv_len_out) {
+    const int64_t r = blockIdx.x;
+    const float *x = in + r * in_ld;
+    __shared__ double red[256];
+    double ss = 0.0;
+    for (int i = threadIdx.x; i < norm_cols; i += 256) ss += (double)x[i] * (double)x[i];
+    red[threadIdx.x] = ss;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    const float inv = 1.0f / (float)sqrt(red[0] / (double)norm_cols + (double)eps);
+    uint16_t *y = out + r * out_ld;
+    for (int i = threadIdx.x; i < norm_cols; i += 256) {
+        const float v = x[i] * inv * bf16_bits_to_f32(weight[i]);
+        y[i] = (uint16_t)(pack_bf16x2(v, 0.f) & 0xffffu);
+    }
+    for (int i = threadIdx.x; i < rope_cols / 2; i += 256) {
+        const float ang = (float)(pos0 + r) / powf(rope_base, 2.0f * (float)i / (float)rope_cols);
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        const float a = x[norm_cols + 2 * i], b = x[norm_cols + 2 * i + 1];
+        *reinterpret_cast<uint32_t *>(y + norm_cols + 2 * i) = pack_bf16x2(a * cs - b * sn, b * cs + a * sn);
+    }
+    if (kv_len_out && threadIdx.x == 0) kv_len_out[r] = (int)(pos0 + r + 1);
+}
+
+// Absorb: Qfull[t][h][0:L] = q[t][h][0:nope] . W_uk[h] ([nope][L] row-major bf16), and
+// Qfull[t][h][L:L+rope] = RoPE(q[t][h][nope:nope+rope], pos0+t). The identity is
+// q_abs = W_k^T q of src/attention.c:741-744 (gemv_bf16_t), batched over tokens.
+// Block = 64 tokens x one head; 8 warps as 4 (16-row blocks) x 2 (halves of L = 512).
+constexpr int AB_NOPE = 128, AB_L = 512, AB_ROPE = 64;
+constexpr int AB_SMEM = 64 * AB_NOPE * 2 + AB_NOPE * AB_L * 2;   // 16 KB + 128 KB
+
+__global__ void __launch_bounds__(256, 1) absorb_kernel(const uint16_t *q, int n, int nh, const uint16_t *wuk,
+                                                        float rope_base, int64_t pos0, uint16_t *qfull) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t *sA = smem;                       // [64][128] bf16, 16 chunks per row, swizzled
+    uint8_t *sB = smem + 64 * AB_NOPE * 2;    // [128][512] bf16, 64 chunks per row, swizzled
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp & 3, wn = warp >> 2;
+    const int t0 = blockIdx.x * 64, h = blockIdx.y;
+    const int qd = AB_NOPE + AB_ROPE;
+    for (int i = tid; i < 64 * 16; i += 256) {
+        const int r = i >> 4, c = i & 15;
+        const bool ok = t0 + r < n;
+        cp_async16(smem_u32(sA + r * 256 + ((c ^ (r & 7)) << 4)),
+                   ok ? (const void *)(q + ((int64_t)(t0 + r) * nh + h) * qd + c * 8) : (const void *)q, ok);
+    }
+    const uint16_t *wb = wuk + (int64_t)h * AB_NOPE * AB_L;
+    for (int i = tid; i < AB_NOPE * 64; i += 256) {
+        const int r = i >> 6, c = i & 63;
+        cp_async16(smem_u32(sB + r * 1024 + ((c ^ (r & 7)) << 4)), wb + (int64_t)r * AB_L + c * 8, true);
+    }
+    cp_async_commit();
+    // rope tail while the tiles arrive
+    for (int i = tid; i < 64 * (AB_ROPE / 2); i += 256) {
+        const int r = i / (AB_ROPE / 2), j = i % (AB_ROPE / 2);
+        if (t0 + r < n) {
+            const uint16_t *src = q + ((int64_t)(t0 + r) * nh + h) * qd + AB_NOPE + 2 * j;
+            const float a = bf16_bits_to_f32(src[0]), b = bf16_bits_to_f32(src[1]);
+            const float ang = (float)(pos0 + t0 + r) / powf(rope_base, 2.0f * (float)j / (float)AB_ROPE);
+            float sn, cs;
+            sincosf(ang, &sn, &cs);
+            *reinterpret_cast<uint32_t *>(qfull + ((int64_t)(t0 + r) * nh + h) * (AB_L + AB_ROPE) + AB_L + 2 * j) =
+                pack_bf16x2(a * cs - b * sn, b * cs + a * sn);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    float acc[32][4];
+#pragma unroll
+    for (int i = 0; i < 32; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    const int arow = wm * 16 + (lane & 15);
+#pragma unroll
+    for (int kt = 0; kt < AB_NOPE / 16; kt++) {
+        uint32_t a[4];
+        ldmatrix_x4(a[0], a[1], a[2], a[3], smem_u32(sA + arow * 256) + (((kt * 2 + (lane >> 4)) ^ (arow & 7)) << 4));
+        const int brow = kt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        const uint32_t bbase = smem_u32(sB + brow * 1024);
+#pragma unroll
+        for (int np = 0; np < 16; np++) {
+            const int chunk = wn * 32 + np * 2 + (lane >> 4);
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, bbase + ((chunk ^ (brow & 7)) << 4));
+            mma_bf16_16816(acc[np * 2], a, b0, b1);
+            mma_bf16_16816(acc[np * 2 + 1], a, b2, b3);
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int r = wm * 16 + (lane >> 2) + half * 8;
+        if (t0 + r >= n) continue;
+        uint16_t *o = qfull + ((int64_t)(t0 + r) * nh + h) * (AB_L + AB_ROPE) + wn * 256 + (lane & 3) * 2;
+#pragma unroll
+        for (int nt = 0; nt < 32; nt++)
+            *reinterpret_cast<uint32_t *>(o + nt * 8) = pack_bf16x2(acc[nt][half * 2], acc[nt][half * 2 + 1]);
+    }
+}
+
+extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, const float *Sqa, const void *Wqb,
+                               const float *Sqb, const void *Wkva, const float *Skva, const void *qa_norm,
+                               const void *kva_norm, const void *Wuk, void *cache, int64_t pos0, int n, int H,
+                               int q_lora, int nh, int nope, int rope, int kv_lora, float eps, float rope_base,
+                               float scale, void *out) {
+    if (!ctx || !X || !Wqa || !Sqa || !Wqb || !Sqb || !Wkva || !Skva || !qa_norm || !kva_norm || !Wuk || !cache || !out)
+        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_prefill: null argument");
+    if (n <= 0 || pos0 < 0 || H <= 0 || q_lora <= 0 || nh <= 0) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_prefill: bad dimensions");
+    if (nope != AB_NOPE || rope != AB_ROPE || kv_lora != AB_L)
+        return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mla_prefill is built for nope 128, rope 64, kv_lora 512 (got %d/%d/%d)", nope, rope, kv_lora);
+    CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int qd = nope + rope, row = kv_lora + rope;
+    // workspace: QA f32 [n][q_lora], QAn bf16 [n][q_lora], KVA f32 [n][row], Q bf16 [n][nh*qd],
+    // Qfull bf16 [n][nh][row], kv_len int32 [n]
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t b_qa = up((size_t)n * q_lora * 4), b_qan = up((size_t)n * q_lora * 2), b_kva = up((size_t)n * row * 4);
+    const size_t b_q = up((size_t)n * nh * qd * 2), b_qf = up((size_t)n * nh * row * 2), b_len = up((size_t)n * 4);
+    int s = cwk_reserve_work(ctx, b_qa + b_qan + b_kva + b_q + b_qf + b_len);
+    if (s != CWK_OK) return s;
+    uint8_t *w = (uint8_t *)ctx->work;
+    float *QA = (float *)w;
+    uint16_t *QAn = (uint16_t *)(w + b_qa);
+    float *KVA = (float *)(w + b_qa + b_qan);
+    uint16_t *Q = (uint16_t *)(w + b_qa + b_qan + b_kva);
+    uint16_t *Qf = (uint16_t *)(w + b_qa + b_qan + b_kva + b_q);
+    int32_t *len = (int32_t *)(w + b_qa + b_qan + b_kva + b_q + b_qf);
+
+    s = cwk_fp8_linear(ctx, X, Wqa, Sqa, n, H, q_lora, QA, 0);
+    if (s != CWK_OK) return s;
+    norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(QA, q_lora, q_lora, 0, (const uint16_t *)qa_norm, eps, rope_base,
+                                                      pos0, QAn, q_lora, nullptr);
+    CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(q_a)");
+    s = cwk_fp8_linear(ctx, QAn, Wqb, Sqb, n, q_lora, (int64_t)nh * qd, Q, 1);
+    if (s != CWK_OK) return s;
+    s = cwk_fp8_linear(ctx, X, Wkva, Skva, n, H, row, KVA, 0);
+    if (s != CWK_OK) return s;
+    norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(KVA, row, kv_lora, rope, (const uint16_t *)kva_norm, eps, rope_base,
+                                                      pos0, (uint16_t *)cache + pos0 * row, row, len);
+    CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(kv_a)");
+    static bool attr_set[16] = {false};
+    if (!attr_set[ctx->device & 15]) {
+        CWK_CUDA(ctx, cudaFuncSetAttribute(absorb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AB_SMEM));
+        attr_set[ctx->device & 15] = true;
+    }
+    absorb_kernel<<<dim3((n + 63) / 64, nh), 256, AB_SMEM, ctx->stream>>>(Q, n, nh, (const uint16_t *)Wuk, rope_base, pos0, Qf);
+    CWK_LAUNCH_CHECK(ctx, "absorb_kernel");
+    return cwk_mla_decode(ctx, Qf, cache, 0, row, len, (int)(pos0 + n), nullptr, 0, n, nh, kv_lora, rope, scale, out, 0);
+}

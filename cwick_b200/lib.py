@@ -36,6 +36,7 @@ SIGNATURES = {
     "cwk_topk_select": (i32, [vp, vp, i64, vp, i32, i32, i32, i32, vp, i64, vp]),
     "cwk_gqa_decode": (i32, [vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, f32, vp, i32]),
     "cwk_gqa_prefill": (i32, [vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, vp]),
+    "cwk_mla_prefill": (i32, [vp] * 12 + [i64] + [i32] * 7 + [f32, f32, f32, vp]),
     "cwk_fp8_linear": (i32, [vp, vp, vp, vp, i64, i64, i64, vp, i32]),
 }
 

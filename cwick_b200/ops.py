@@ -153,3 +153,18 @@ class Attn:
         self.ctx.check(self.lib.cwk_fp8_linear(self.ctx.h, _p(X), _p(W), _p(scale_inv), n, k, cols, _p(Y),
                                                1 if out_bf16 else 0))
         return Y
+
+    # ---- MLA prefill -----------------------------------------------------------------
+    def mla_prefill(self, X, Wqa, Sqa, Wqb, Sqb, Wkva, Skva, qa_norm, kva_norm, Wuk, cache, pos0, nh,
+                    nope=128, rope=64, kv_lora=512, eps=1e-6, rope_base=10000.0, scale=None):
+        """X bf16 [n][H]; weights uint8 E4M3 + f32 scales; norms bf16; Wuk bf16 [nh][nope][kv_lora];
+        cache bf16 [rows][kv_lora+rope] (rows pos0..pos0+n-1 written). Returns bf16 [n][nh][kv_lora]."""
+        n, H = X.shape
+        q_lora = Wqa.shape[0]
+        if scale is None:
+            scale = 1.0 / math.sqrt(nope + rope)
+        out = torch.empty(n, nh, kv_lora, dtype=torch.bfloat16, device=X.device)
+        self.ctx.check(self.lib.cwk_mla_prefill(
+            self.ctx.h, _p(X), _p(Wqa), _p(Sqa), _p(Wqb), _p(Sqb), _p(Wkva), _p(Skva), _p(qa_norm), _p(kva_norm),
+            _p(Wuk), _p(cache), pos0, n, H, q_lora, nh, nope, rope, kv_lora, eps, rope_base, scale, _p(out)))
+        return out

@@ -196,6 +196,29 @@ CWK_API int cwk_gqa_prefill(cwk_ctx *ctx, const void *Q, const void *K, const vo
 CWK_API int cwk_fp8_linear(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv,
                    int64_t n, int64_t k, int64_t cols, void *Y, int out_bf16);
 
+/* ---- MLA causal prefill of a chunk ---------------------------------------
+ * Replaces cwick_attention_mla_prefill_chunk up to the attention output
+ * (src/attention.c:943-1019) for FP8-E4M3 block-scaled q_a / q_b / kv_a
+ * projections -- the case for which the reference refuses the chunk path
+ * (CWICK_ERR_UNSUPPORTED, :958-963) and runs token by token.
+ *   X        bf16 [n][H]                 hidden rows of the chunk
+ *   Wqa/Sqa  E4M3 [q_lora][H] + f32 [q_lora/128][H/128]
+ *   Wqb/Sqb  E4M3 [nh*(nope+rope)][q_lora] + scales
+ *   Wkva/Skva E4M3 [kv_lora+rope][H] + scales
+ *   qa_norm  bf16 [q_lora], kva_norm bf16 [kv_lora]   (q_a_layernorm, kv_a_layernorm)
+ *   Wuk      bf16 [nh][nope][kv_lora]    the W_k slice of kv_b_proj (:737-744)
+ *   cache    bf16 [>= pos0+n][kv_lora+rope]; rows pos0..pos0+n-1 are WRITTEN
+ *            (normalised latent | RoPE'd key tail); rows < pos0 are read
+ *   out      bf16 [n][nh][kv_lora]       softmax-weighted latent per query
+ * RoPE (adjacent pairs, src/attention.c:60-68) is applied to the key tail and
+ * to the query tail at the query's position. Built for nope 128, rope 64,
+ * kv_lora 512. */
+CWK_API int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, const float *Sqa,
+                            const void *Wqb, const float *Sqb, const void *Wkva, const float *Skva,
+                            const void *qa_norm, const void *kva_norm, const void *Wuk, void *cache,
+                            int64_t pos0, int n, int H, int q_lora, int nh, int nope, int rope,
+                            int kv_lora, float eps, float rope_base, float scale, void *out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -830,3 +830,60 @@ ORC_API void orc_mla_decode_ranges(const float *q, const uint16_t *cache, int64_
     orc_lse_combine(m, l, o, threads, nh, L, out);
     free(o); free(l); free(m); free(jobs); free(th);
 }
+
+/* ------------------------------------------------------------------ */
+/* MLA causal prefill, token by token                                  */
+/* ------------------------------------------------------------------ */
+
+/* The per-token path the reference falls back to for FP8 checkpoints
+ * (src/engine.c:2422-2430 -> cwick_attention_mla_decode per token), restated
+ * for the 512+64 layout: q_a = fp8 GEMV (rows == 1 path, src/tensor.c:674-691)
+ * -> rms_norm -> * q_a_layernorm; q = fp8 GEMV; kv_a = fp8 GEMV, rms_norm over
+ * the first L columns, * kv_a_layernorm (src/attention.c:1070-1079); the latent
+ * row is stored bf16 with the reference's own narrowing (:703-705). RoPE
+ * (src/attention.c:60-68, base as given) is applied to the key tail as the
+ * reference does (:1096-1099) AND to the query tail at the query's position --
+ * a deliberate deviation: the reference's expanded path leaves q unrotated
+ * (:1070-1074), which is not a relative-position encoding; the benchmark
+ * configuration asks for RoPE "on the 64 rope dims". q_nope is absorbed
+ * through W_uk [nh][nope][L] with gemv_bf16_t (:741-744); attention over rows
+ * 0..pos is orc_mla_decode. All n cache rows are written; outputs are
+ * produced only for the `nrows` query rows listed in `rows` (chunk-relative). */
+ORC_API void orc_mla_prefill(const float *X, const uint8_t *Wqa, const float *Sqa,
+                             const uint8_t *Wqb, const float *Sqb, const uint8_t *Wkva,
+                             const float *Skva, const uint16_t *qa_n, const uint16_t *kva_n,
+                             const uint16_t *Wuk, uint16_t *cache, int64_t pos0, int n, int H,
+                             int q_lora, int nh, int nope, int rope, int L, float eps,
+                             float rope_base, float scale, const int32_t *rows, int nrows,
+                             float *out) {
+    const int row = L + rope, qd = nope + rope;
+    float *kv_a = malloc(sizeof(float) * (size_t)row);
+    for (int t = 0; t < n; t++) {
+        orc_gemv_fp8(kv_a, H, row, X + (size_t)t * H, Wkva, Skva, H / 128);
+        orc_rms_norm(kv_a, kv_a, L, NULL, eps);
+        orc_scale_bf16(kv_a, kva_n, L);
+        orc_rope_adjacent(kv_a + L, rope, pos0 + t, rope_base);
+        for (int i = 0; i < row; i++) cache[(size_t)(pos0 + t) * row + i] = orc_f32_to_bf16(kv_a[i]);
+    }
+    float *q_a = malloc(sizeof(float) * (size_t)q_lora);
+    float *q = malloc(sizeof(float) * (size_t)nh * qd);
+    float *qf = malloc(sizeof(float) * (size_t)nh * row);
+    for (int r = 0; r < nrows; r++) {
+        const int t = rows[r];
+        const int64_t npos = pos0 + t + 1;
+        orc_gemv_fp8(q_a, H, q_lora, X + (size_t)t * H, Wqa, Sqa, H / 128);
+        orc_rms_norm(q_a, q_a, q_lora, NULL, eps);
+        orc_scale_bf16(q_a, qa_n, q_lora);
+        orc_gemv_fp8(q, q_lora, (int64_t)nh * qd, q_a, Wqb, Sqb, q_lora / 128);
+        for (int h = 0; h < nh; h++) {
+            orc_gemv_bf16_t(qf + (size_t)h * row, nope, L, q + (size_t)h * qd, Wuk + (size_t)h * nope * L);
+            memcpy(qf + (size_t)h * row + L, q + (size_t)h * qd + nope, sizeof(float) * (size_t)rope);
+            orc_rope_adjacent(qf + (size_t)h * row + L, rope, pos0 + t, rope_base);
+        }
+        float *scores = malloc(sizeof(float) * (size_t)nh * (size_t)npos);
+        orc_mla_decode(qf, cache, row, NULL, npos, nh, L, rope, scale, scores,
+                       out + (size_t)r * nh * L, NULL, NULL);
+        free(scores);
+    }
+    free(qf); free(q); free(q_a); free(kv_a);
+}

@@ -79,6 +79,9 @@ def oracle():
                                      C.c_float, f32p, f32p]
         L.orc_gqa_prefill.argtypes = [f32p, u16p, u16p, C.c_int64, C.c_int, C.c_int, C.c_int,
                                       C.c_int, C.c_float, f32p]
+        L.orc_mla_prefill.argtypes = [f32p, u8p, f32p, u8p, f32p, u8p, f32p, u16p, u16p, u16p, u16p, C.c_int64,
+                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float,
+                                      C.c_float, C.c_float, i32p, C.c_int, f32p]
         L.orc_mla_decode_batch.argtypes = [u16p, u16p, C.c_int64, C.c_int64, i32p, C.c_int, C.c_int,
                                            C.c_int, C.c_int, C.c_float, f32p, C.c_int]
         L.orc_mla_decode_ranges.argtypes = [f32p, u16p, C.c_int64, C.c_int64, C.c_int, C.c_int,
