@@ -9,6 +9,28 @@
 // cache rows 0..pos0+i.
 #include "cwk_common.cuh"
 
+// cos/sin of the reference's rope angle, pos / powf(base, 2i/n) (src/attention.c:62), formed the
+// way a correctly rounding float libm forms it: the power in double rounded once to float, an
+// IEEE float division, then cos/sin of that float angle in double. (The library is compiled
+// with fast-math; at positions in the thousands its approximate powf/sincosf would move the
+// angle by more than a bf16 step of the result.)
+__device__ __forceinline__ void rope_cos_sin(int64_t pos, int i, int n_rope, float base, float &cs, float &sn) {
+    const float den = (float)pow((double)base, (double)(2.0f * (float)i / (float)n_rope));
+    const float ang = __fdiv_rn((float)pos, den);
+    double s, c;
+    sincos((double)ang, &s, &c);
+    cs = (float)c;
+    sn = (float)s;
+}
+
+// f32 -> bf16 exactly as the reference narrows a latent-cache row (cwick_f32_to_bf16,
+// src/util.c:202-210: add bit15 + lsb, keep the top half -- in effect a truncation). Used for
+// the cache rows so that a cache written here is bit-compatible with one the reference wrote.
+__device__ __forceinline__ uint16_t narrow_bf16_like_reference(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (uint16_t)((u + ((u >> 15) & 1u) + ((u >> 16) & 1u)) >> 16);
+}
+
 extern "C" int cwk_fp8_linear(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv, int64_t n,
                               int64_t k, int64_t cols, void *Y, int out_bf16);
 extern "C" int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
@@ -24,7 +46,7 @@ extern "C" int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, in
 __global__ void __launch_bounds__(256) norm_rope_rows_kernel(const float *in, int64_t in_ld, int norm_cols,
                                                              int rope_cols, const uint16_t *weight, float eps,
                                                              float rope_base, int64_t pos0, uint16_t *out,
-                                                             int64_t out_ld, int *kv_len_out) {
+                                                             int64_t out_ld, int *kv_len_out, int ref_narrow) {
     const int64_t r = blockIdx.x;
     const float *x = in + r * in_ld;
     __shared__ double red[256];
@@ -36,18 +58,23 @@ __global__ void __launch_bounds__(256) norm_rope_rows_kernel(const float *in, in
         if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
         __syncthreads();
     }
-    const float inv = 1.0f / (float)sqrt(red[0] / (double)norm_cols + (double)eps);
+    const float inv = __fdiv_rn(1.0f, (float)sqrt(red[0] / (double)norm_cols + (double)eps));
     uint16_t *y = out + r * out_ld;
     for (int i = threadIdx.x; i < norm_cols; i += 256) {
         const float v = x[i] * inv * bf16_bits_to_f32(weight[i]);
-        y[i] = (uint16_t)(pack_bf16x2(v, 0.f) & 0xffffu);
+        y[i] = ref_narrow ? narrow_bf16_like_reference(v) : (uint16_t)(pack_bf16x2(v, 0.f) & 0xffffu);
     }
     for (int i = threadIdx.x; i < rope_cols / 2; i += 256) {
-        const float ang = (float)(pos0 + r) / powf(rope_base, 2.0f * (float)i / (float)rope_cols);
         float sn, cs;
-        sincosf(ang, &sn, &cs);
+        rope_cos_sin(pos0 + r, i, rope_cols, rope_base, cs, sn);
         const float a = x[norm_cols + 2 * i], b = x[norm_cols + 2 * i + 1];
-        *reinterpret_cast<uint32_t *>(y + norm_cols + 2 * i) = pack_bf16x2(a * cs - b * sn, b * cs + a * sn);
+        const float r0 = a * cs - b * sn, r1 = b * cs + a * sn;
+        if (ref_narrow) {
+            y[norm_cols + 2 * i] = narrow_bf16_like_reference(r0);
+            y[norm_cols + 2 * i + 1] = narrow_bf16_like_reference(r1);
+        } else {
+            *reinterpret_cast<uint32_t *>(y + norm_cols + 2 * i) = pack_bf16x2(r0, r1);
+        }
     }
     if (kv_len_out && threadIdx.x == 0) kv_len_out[r] = (int)(pos0 + r + 1);
 }
@@ -86,9 +113,8 @@ __global__ void __launch_bounds__(256, 1) absorb_kernel(const uint16_t *q, int n
         if (t0 + r < n) {
             const uint16_t *src = q + ((int64_t)(t0 + r) * nh + h) * qd + AB_NOPE + 2 * j;
             const float a = bf16_bits_to_f32(src[0]), b = bf16_bits_to_f32(src[1]);
-            const float ang = (float)(pos0 + t0 + r) / powf(rope_base, 2.0f * (float)j / (float)AB_ROPE);
             float sn, cs;
-            sincosf(ang, &sn, &cs);
+            rope_cos_sin(pos0 + t0 + r, j, AB_ROPE, rope_base, cs, sn);
             *reinterpret_cast<uint32_t *>(qfull + ((int64_t)(t0 + r) * nh + h) * (AB_L + AB_ROPE) + AB_L + 2 * j) =
                 pack_bf16x2(a * cs - b * sn, b * cs + a * sn);
         }
@@ -155,14 +181,14 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     s = cwk_fp8_linear(ctx, X, Wqa, Sqa, n, H, q_lora, QA, 0);
     if (s != CWK_OK) return s;
     norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(QA, q_lora, q_lora, 0, (const uint16_t *)qa_norm, eps, rope_base,
-                                                      pos0, QAn, q_lora, nullptr);
+                                                      pos0, QAn, q_lora, nullptr, 0);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(q_a)");
     s = cwk_fp8_linear(ctx, QAn, Wqb, Sqb, n, q_lora, (int64_t)nh * qd, Q, 1);
     if (s != CWK_OK) return s;
     s = cwk_fp8_linear(ctx, X, Wkva, Skva, n, H, row, KVA, 0);
     if (s != CWK_OK) return s;
     norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(KVA, row, kv_lora, rope, (const uint16_t *)kva_norm, eps, rope_base,
-                                                      pos0, (uint16_t *)cache + pos0 * row, row, len);
+                                                      pos0, (uint16_t *)cache + pos0 * row, row, len, 1);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(kv_a)");
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
