@@ -352,6 +352,13 @@ def run_ours(args):
                 extra["c5a_64x32768"] = side_measure(attn, dev, stream, 64, 32768, peak)
             except Exception as e:  # noqa: BLE001
                 extra["c5a_64x32768"] = {"error": str(e)[:200]}
+            for name, fn in (("c1_gqa_decode_4096", side_gqa_decode), ("c3_mla_prefill_4096", side_prefill),
+                             ("c4_dsa_8x65536_top2048", side_dsa)):
+                try:
+                    torch.cuda.empty_cache()
+                    extra[name] = fn(attn, dev, stream, peak)
+                except Exception as e:  # noqa: BLE001
+                    extra[name] = {"error": str(e)[:200]}
         line["extra"] = extra
         tps, info = cpu_reference(seconds_budget=12.0)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", **info}
@@ -386,6 +393,116 @@ def side_measure(attn, dev, stream, B, T, peak):
     by = algorithmic_bytes(B, T)
     return {"ms_per_call": ms, "tokens_per_s": B / (ms / 1e3), "kv_hbm_gbs": by / (ms / 1e3) / 1e9,
             "kernel_gbs": by / (k_ms / k_n / 1e3) / 1e9, "kernel_frac_of_measured_peak": by / (k_ms / k_n / 1e3) / 1e9 / peak}
+
+
+def _time_calls(attn, stream, fn, n=20, warm=3):
+    """Mean wall (CUDA events) and mean main-kernel milliseconds of fn() over n calls."""
+    import torch
+    for _ in range(warm):
+        fn()
+    attn.ctx.profile(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(n):
+        fn()
+    e1.record(stream)
+    k_ms, k_n = attn.ctx.profile_read()
+    attn.ctx.profile(False)
+    return e0.elapsed_time(e1) / n, k_ms / n, k_n // n
+
+
+def side_gqa_decode(attn, dev, stream, peak):
+    """Config 1: GQA single-query decode, 16 q heads / 4 kv heads, hd 256, 4096 cached tokens; 16
+    distinct caches in rotation (268 MB > L2)."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(11)
+    nh, nkv, hd, T, rot = 16, 4, 256, 4096, 16
+    K = [torch.randn(1, T, nkv, hd, device=dev, generator=g).to(torch.bfloat16) for _ in range(rot)]
+    V = [torch.randn(1, T, nkv, hd, device=dev, generator=g).to(torch.bfloat16) for _ in range(rot)]
+    q = torch.randn(1, nh, hd, device=dev, generator=g).to(torch.bfloat16)
+    lens = torch.full((1,), T, dtype=torch.int32, device=dev)
+    i = [0]
+
+    def call():
+        attn.gqa_decode(q, K[i[0] % rot], V[i[0] % rot], lens, max_kv_len=T)
+        i[0] += 1
+    ms, k_ms, _ = _time_calls(attn, stream, call, n=64)
+    by = 2 * T * nkv * hd * 2 + 2 * nh * hd * 2
+    return {"us_per_call": 1e3 * ms, "kernel_us": 1e3 * k_ms, "tokens_per_s": 1e3 / ms,
+            "kernel_gbs": by / (k_ms / 1e3) / 1e9, "kernel_frac_of_measured_peak": by / (k_ms / 1e3) / 1e9 / peak,
+            "algorithmic_bytes": by}
+
+
+def side_prefill(attn, dev, stream, peak):
+    """Config 3: MLA causal prefill of 4096 tokens, hidden 4096, FP8 block-scaled q_a/q_b/kv_a."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(12)
+    n, H, q_lora, nh, nope, rope, lat = 4096, 4096, 1536, 64, 128, 64, 512
+
+    def fp8w(rows, cols):
+        w = torch.randint(0, 255, (rows, cols), device=dev, generator=g, dtype=torch.int32).to(torch.uint8)
+        w = torch.where((w & 0x7F) == 0x7F, torch.zeros_like(w), w)          # no NaN codes
+        sc = torch.full(((rows + 127) // 128, cols // 128), 1e-4, device=dev, dtype=torch.float32)
+        return w, sc
+    Wqa, Sqa = fp8w(q_lora, H)
+    Wqb, Sqb = fp8w(nh * (nope + rope), q_lora)
+    Wkva, Skva = fp8w(lat + rope, H)
+    ones_q = torch.ones(q_lora, device=dev, dtype=torch.bfloat16)
+    ones_k = torch.ones(lat, device=dev, dtype=torch.bfloat16)
+    Wuk = (0.02 * torch.randn(nh, nope, lat, device=dev, generator=g)).to(torch.bfloat16)
+    X = torch.randn(n, H, device=dev, generator=g).to(torch.bfloat16)
+    cache = torch.zeros(n, lat + rope, device=dev, dtype=torch.bfloat16)
+
+    def call():
+        attn.mla_prefill(X, Wqa, Sqa, Wqb, Sqb, Wkva, Skva, ones_q, ones_k, Wuk, cache, 0, nh)
+    ms, k_ms, k_n = _time_calls(attn, stream, call, n=5, warm=2)
+    proj = 2.0 * n * (H * q_lora + q_lora * nh * (nope + rope) + H * (lat + rope))
+    absorb = 2.0 * n * nh * nope * lat
+    pairs = n * (n + 1) / 2.0
+    attn_fl = 2.0 * pairs * nh * ((lat + rope) + lat)
+    total = proj + absorb + attn_fl
+    return {"ms_per_prefill": ms, "tokens_per_s": n / (ms / 1e3), "tflops": total / (ms / 1e3) / 1e12,
+            "flops": {"fp8_projections": proj, "absorb": absorb, "causal_attention": attn_fl},
+            "main_kernel_ms": k_ms, "main_kernels_per_call": k_n}
+
+
+def side_dsa(attn, dev, stream, peak):
+    """Config 4: DSA sparse decode, 8 sequences x 65536 cached tokens, 64x128 indexer heads over FP8
+    keys, top 2048, gathered MLA attention."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(13)
+    B, T, ih, hd, want = 8, 65536, 64, 128, 2048
+    keys = torch.randint(0, 255, (B, T, hd), device=dev, generator=g, dtype=torch.int32).to(torch.uint8)
+    keys = torch.where((keys & 0x7F) == 0x7F, torch.zeros_like(keys), keys)
+    ks = torch.full((B, T), 0.01, device=dev, dtype=torch.float32)
+    q = torch.randn(B, ih, hd, device=dev, generator=g)
+    wt = torch.rand(B, ih, device=dev, generator=g) / math.sqrt(hd * ih)
+    n = torch.full((B,), T, dtype=torch.int32, device=dev)
+    mq = torch.randn(B, NH, DK, device=dev, generator=g).to(torch.bfloat16)
+    cache = torch.empty(B, T, DK, device=dev, dtype=torch.bfloat16)
+    for b in range(B):
+        cache[b] = torch.randn(T, DK, device=dev, generator=g).to(torch.bfloat16)
+    out = {}
+
+    def scores():
+        out["sc"] = attn.indexer_scores_fp8(keys, ks, q, wt, n, max_n=T)
+    ms_s, k_s, _ = _time_calls(attn, stream, scores, n=5, warm=2)
+
+    def select():
+        out["sel"], out["nsel"] = attn.topk_select(out["sc"], n, want, False, max_n=T)
+    ms_t, k_t, _ = _time_calls(attn, stream, select, n=10, warm=2)
+
+    def gather():
+        attn.mla_decode(mq, cache, out["nsel"], sel=out["sel"], scale=SCALE, max_kv_len=want + 1)
+    ms_g, k_g, _ = _time_calls(attn, stream, gather, n=20, warm=3)
+    idx_bytes = B * T * (hd + 4)
+    gat_bytes = B * want * DK * 2
+    total_ms = ms_s + ms_t + ms_g
+    return {"ms_per_step": total_ms, "tokens_per_s": B / (total_ms / 1e3),
+            "indexer_ms": ms_s, "indexer_gbs": idx_bytes / (k_s / 1e3) / 1e9,
+            "topk_ms": ms_t, "gather_attention_ms": ms_g, "gather_gbs": gat_bytes / (k_g / 1e3) / 1e9,
+            "indexer_frac_of_measured_peak": idx_bytes / (k_s / 1e3) / 1e9 / peak,
+            "gather_frac_of_measured_peak": gat_bytes / (k_g / 1e3) / 1e9 / peak}
 
 
 def main():

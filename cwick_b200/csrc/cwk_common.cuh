@@ -21,6 +21,9 @@ struct cwk_ctx {
     // workspace of the composite entry points (prefill): separate from the split scratch
     void *work = nullptr;
     size_t work_bytes = 0;
+    // FP8 weights widened to bf16 for the tensor-core projection
+    void *wbf16 = nullptr;
+    size_t wbf16_bytes = 0;
     // staging for the *_host entry points
     void *stage_dev = nullptr;
     size_t stage_dev_bytes = 0;

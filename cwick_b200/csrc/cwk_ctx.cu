@@ -110,6 +110,7 @@ void cwk_ctx_destroy(cwk_ctx *ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage_dev) cudaFree(ctx->stage_dev);
     if (ctx->work) cudaFree(ctx->work);
+    if (ctx->wbf16) cudaFree(ctx->wbf16);
     if (ctx->stage_pin) cudaFreeHost(ctx->stage_pin);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
     for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);

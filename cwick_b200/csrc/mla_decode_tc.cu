@@ -27,7 +27,7 @@
 
 #include <algorithm>
 
-#include "cwk_common.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -43,7 +43,6 @@ constexpr int OFF_BAR = OFF_KV + NBLK * KV_BLK; // 221184
 constexpr int OFF_MISC = OFF_BAR + 256;
 constexpr int SMEM_USED = OFF_MISC + 2048;
 constexpr int SMEM_TOTAL = SMEM_USED + 1024;    // slack to align the base to 1024 B
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0, COL_S = 256;
 constexpr int HG = 32;                          // heads per softmax warp group
@@ -52,83 +51,6 @@ constexpr int NTHREADS = 384;
 
 // barrier slots (8 bytes each) inside OFF_BAR
 enum { B_FULL = 0, B_EMPTY_L = 9, B_EMPTY_RP = 13, B_QFULL = 14, B_SFULL = 15, B_PFULL = 16, B_COUNT = 17 };
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait. Returns false (and records `code`) when it gives up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *err, int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
-        if (mbar_try(bar, parity)) return true;
-    atomicCAS(err, 0, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tm, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tm, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (Blackwell).
-// addr / lbo / sbo in bytes. bits [0,14) addr>>4, [16,30) lbo>>4, [32,46) sbo>>4,
-// [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
-           (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor for kind::f16: f32 accumulate, bf16 A and B.
-__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn, int b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
-           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-#define TMEM_LD16(arr, off, taddr)                                                                          \
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];" \
-                 : "=r"(arr[off + 0]), "=r"(arr[off + 1]), "=r"(arr[off + 2]), "=r"(arr[off + 3]),          \
-                   "=r"(arr[off + 4]), "=r"(arr[off + 5]), "=r"(arr[off + 6]), "=r"(arr[off + 7]),          \
-                   "=r"(arr[off + 8]), "=r"(arr[off + 9]), "=r"(arr[off + 10]), "=r"(arr[off + 11]),        \
-                   "=r"(arr[off + 12]), "=r"(arr[off + 13]), "=r"(arr[off + 14]), "=r"(arr[off + 15])       \
-                 : "r"(taddr))
-#define TMEM_ST16(arr, off, taddr)                                                                          \
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};" \
-                 ::"r"(arr[off + 0]), "r"(arr[off + 1]), "r"(arr[off + 2]), "r"(arr[off + 3]),              \
-                   "r"(arr[off + 4]), "r"(arr[off + 5]), "r"(arr[off + 6]), "r"(arr[off + 7]),              \
-                   "r"(arr[off + 8]), "r"(arr[off + 9]), "r"(arr[off + 10]), "r"(arr[off + 11]),            \
-                   "r"(arr[off + 12]), "r"(arr[off + 13]), "r"(arr[off + 14]), "r"(arr[off + 15]),          \
-                   "r"(taddr)                                                                               \
-                 : "memory")
 
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
@@ -457,24 +379,6 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 }  // namespace
 
 bool cwk_mla_decode_tc_available() { return true; }
@@ -484,7 +388,7 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
                              int nsplit, void *out_direct) {
     if (nh != NH) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode is built for 64 heads");
     if (max_kv_len <= 0) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode needs a non-empty cache");
-    EncodeTiledFn enc = encode_fn();
+    CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
     if (!enc) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
     if (!ctx->dev_err) {
         CWK_CUDA(ctx, cudaMalloc(&ctx->dev_err, sizeof(int)));

@@ -29,11 +29,17 @@ def quantise(seed, cols, k):
 
 @pytest.mark.parametrize("n,k,cols", [(64, 512, 384), (130, 256, 576), (1, 4096, 128), (300, 1536, 256)])
 @pytest.mark.parametrize("out_bf16", [False, True])
-def test_against_per_row_gemv(attn, n, k, cols, out_bf16):
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma.sync"])
+def test_against_per_row_gemv(attn, n, k, cols, out_bf16, kernel):
     o = orc.oracle()
     q, sc = quantise(n + k, cols, k)
     X = synth.normal_bf16(n + k, 2, (n, k))
-    got = attn.fp8_linear(to_bf16_cuda(X), torch.from_numpy(q).cuda(), torch.from_numpy(sc).cuda(), out_bf16)
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1 if kernel == "tcgen05" else 1)   # 1 = no tcgen05 kernels
+    try:
+        got = attn.fp8_linear(to_bf16_cuda(X), torch.from_numpy(q).cuda(), torch.from_numpy(sc).cuda(), out_bf16)
+        attn.ctx.sync()
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
     got = bf16_to_np(got) if out_bf16 else got.cpu().numpy()
     Xf = np.ascontiguousarray(synth.bf16_to_f32(X))
     want = np.empty((n, cols), np.float32)
