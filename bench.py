@@ -2,7 +2,7 @@
 """Benchmark of the CWICK attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2|c5a|c5a8]
+                    [--workload c2|c5a|c5a8|c5b]
 
 Default workload `c2` is BASELINE.json's config 2: MLA absorbed decode, batch 1,
 64 heads, 512-d latent + 64-d rope key, 8192 cached tokens, BF16. One *step* is
@@ -44,6 +44,7 @@ WORKLOADS = {
     # name: (sequences per call, cached tokens, calls per step)
     "c2": dict(B=1, T=8192, calls=ROT, desc="config 2: MLA absorbed decode, batch 1, 64 heads, 512+64 bf16, 8192 cached tokens"),
     "c5a": dict(B=64, T=32768, calls=1, desc="config 5a on one GPU: 64 sequences x 32768 cached tokens, one batched call"),
+    "c5b": dict(B=1, T=131072, calls=1, desc="config 5b: one sequence, 131072 cached tokens, KV rows split across the GPUs, partial records all-gathered (NCCL) and merged"),
     "c5a8": dict(B=8, T=32768, calls=1, desc="config 5a, one GPU's share at 8 GPUs: 8 sequences x 32768 cached tokens, one batched call"),
 }
 
@@ -216,6 +217,8 @@ def run_ours(args):
 
     wl = WORKLOADS[args.workload]
     B, T, calls = wl["B"], wl["T"], wl["calls"]
+    if args.workload == "c5b":
+        return run_kv_split(args, torch, dist, world, rank, local, dev, wl)
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
     attn = Attn(local)                       # binds the context to `stream`
@@ -364,6 +367,70 @@ def run_ours(args):
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", **info}
     if rank == 0:
         print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_kv_split(args, torch, dist, world, rank, local, dev, wl):
+    """Config 5b: strong scaling of ONE long context. Rank r holds rows kv_ranges(T, world)[r]; a step is
+    partial decode over the local rows -> all-gather of the 131,584-byte records -> merge on every rank."""
+    from cwick_b200 import dist as cd
+    from cwick_b200.ops import Attn
+    T = wl["T"]
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    attn = Attn(local)
+    row0, rows = cd.kv_ranges(T, world)[rank]
+    g = torch.Generator(device=dev).manual_seed(20261125 + rank)
+    rot = max(2, (2 * L2_BYTES) // max(1, rows * DK * 2) + 1)         # distinct local caches so a step never hits L2
+    caches = [torch.randn(rows, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(rot)]
+    q = torch.randn(NH, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    i = [0]
+
+    def step():
+        out = cd.mla_decode_kv_split(attn, q, caches[i[0] % rot], rows, L, R, SCALE)
+        i[0] += 1
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = attn.ctx.launches
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    t_end = time.perf_counter() + 1.5
+    while len(sampler.lines) < 6 and time.perf_counter() < t_end:
+        step()
+        torch.cuda.synchronize(dev)
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    peak, peak_kind = peaks()
+    by = algorithmic_bytes(1, T)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "mla_decode_tokens_per_s", "value": 1e3 / ms_step, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl["desc"], "cached_tokens": T, "rows_per_gpu": rows, "heads": NH,
+                       "exchange": "all_gather of %d-byte records" % (NH * (L + 2) * 4),
+                       "l2": "rotation of %d local caches" % rot, "parallelism": f"kv-range x{world}"},
+            "kv_hbm_gbs": by / (ms_step / 1e3) / 1e9, "kv_hbm_frac_of_measured_peak": by / (ms_step / 1e3) / 1e9 / (peak * world),
+            "clocks": clocks, "gpu_launches": int(attn.ctx.launches - l0)}))
     if world > 1:
         dist.destroy_process_group()
 

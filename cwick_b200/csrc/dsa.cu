@@ -11,20 +11,16 @@ __device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
     return (b & 0x80u) ? -mag : mag;
 }
 
-// One thread per key. The dequantised key row lives in shared memory (row
-// stride 132 floats: 16-byte aligned and conflict-free for float4 reads), q in
-// shared memory as float4 broadcast reads. The arithmetic is the reference's:
-// per head four strided f32 accumulators with separate multiply and add (no
-// fused multiply-add), combined (s0+s1)+(s2+s3); ReLU; times the head weight;
-// heads summed in order.
+// One thread per key, the dequantised key row held in registers for all heads; q and the head
+// weights sit in shared memory and are read as float4 broadcasts. The arithmetic is the
+// reference's: per head four strided f32 accumulators with separate multiply and add (no fused
+// multiply-add), combined (s0+s1)+(s2+s3); ReLU; times the head weight; heads summed in order.
 template <int HD>
 __global__ void __launch_bounds__(128) indexer_scores_fp8_kernel(
     const uint8_t *keys, const float *kscale, int64_t key_stride, const float *q, const float *wt,
     const int32_t *n, int ih, float *sc) {
-    constexpr int KS = HD + 4;
     extern __shared__ __align__(16) float sm[];
-    float *sk = sm;                      // [128][KS]
-    float *sq = sm + 128 * KS;           // [ih][HD]
+    float *sq = sm;                      // [ih][HD]
     float *sw = sq + ih * HD;            // [ih]
     const int b = blockIdx.y, tid = threadIdx.x;
     const int nb = n[b];
@@ -32,36 +28,35 @@ __global__ void __launch_bounds__(128) indexer_scores_fp8_kernel(
     if (c0 >= nb) return;
     for (int i = tid; i < ih * HD; i += 128) sq[i] = q[(int64_t)b * ih * HD + i];
     for (int i = tid; i < ih; i += 128) sw[i] = wt[(int64_t)b * ih + i];
-    // 128 keys x HD codes, 16 bytes per load
-    const uint8_t *kb = keys + ((int64_t)b * key_stride + c0) * HD;
-    for (int i = tid; i < 128 * (HD / 16); i += 128) {
-        const int r = i / (HD / 16), ch = i % (HD / 16);
-        if (c0 + r < nb) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(kb + (int64_t)r * HD + ch * 16);
-            const float s = kscale[(int64_t)b * key_stride + c0 + r];
+    __syncthreads();
+    const int c = c0 + tid;
+    if (c >= nb) return;
+    float kf[HD];
+    {
+        const uint4 *kr = reinterpret_cast<const uint4 *>(keys + ((int64_t)b * key_stride + c) * HD);
+        const float s = kscale[(int64_t)b * key_stride + c];
+#pragma unroll
+        for (int ch = 0; ch < HD / 16; ch++) {
+            const uint4 v = kr[ch];
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int k = 0; k < 4; k++)
 #pragma unroll
                 for (int j = 0; j < 4; j++)
-                    sk[r * KS + ch * 16 + k * 4 + j] = __fmul_rn(e4m3_to_f32((w[k] >> (8 * j)) & 0xffu), s);
+                    kf[ch * 16 + k * 4 + j] = __fmul_rn(e4m3_to_f32((w[k] >> (8 * j)) & 0xffu), s);
         }
     }
-    __syncthreads();
-    const int c = c0 + tid;
-    if (c >= nb) return;
-    const float4 *kr = reinterpret_cast<const float4 *>(sk + tid * KS);
     float total = 0.f;
     for (int h = 0; h < ih; h++) {
         const float4 *qh = reinterpret_cast<const float4 *>(sq + h * HD);
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll 8
+#pragma unroll
         for (int i = 0; i < HD / 4; i++) {
-            const float4 kv = kr[i], qv = qh[i];
-            s0 = __fadd_rn(s0, __fmul_rn(kv.x, qv.x));
-            s1 = __fadd_rn(s1, __fmul_rn(kv.y, qv.y));
-            s2 = __fadd_rn(s2, __fmul_rn(kv.z, qv.z));
-            s3 = __fadd_rn(s3, __fmul_rn(kv.w, qv.w));
+            const float4 qv = qh[i];
+            s0 = __fadd_rn(s0, __fmul_rn(kf[4 * i + 0], qv.x));
+            s1 = __fadd_rn(s1, __fmul_rn(kf[4 * i + 1], qv.y));
+            s2 = __fadd_rn(s2, __fmul_rn(kf[4 * i + 2], qv.z));
+            s3 = __fadd_rn(s3, __fmul_rn(kf[4 * i + 3], qv.w));
         }
         float d = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
         if (d < 0.f) d = 0.f;
@@ -178,7 +173,7 @@ int cwk_indexer_scores_fp8(cwk_ctx *ctx, const void *keys, const float *kscale, 
     if (((uintptr_t)keys % 16) != 0) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "indexer_scores: keys must be 16-byte aligned");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     if (max_n == 0) return CWK_OK;
-    const size_t smem = (size_t)(128 * (128 + 4) + ih * 128 + ih) * sizeof(float);
+    const size_t smem = (size_t)(ih * 128 + ih) * sizeof(float);
     auto kern = indexer_scores_fp8_kernel<128>;
     if (smem > 48 * 1024) CWK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     CwkKernelTimer timer(ctx);

@@ -1,0 +1,80 @@
+"""Multi-GPU paths on real devices (skipped with fewer than 2 GPUs): one process per GPU, NCCL.
+
+* KV-range split of one long context: each rank computes the partial record of its rows, the
+  records are all-gathered, every rank merges; the result must equal the one-GPU answer.
+* Sequence sharding: each rank decodes its own sequences; together they equal the batch."""
+import math
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+L, R, NH = 512, 64, 64
+SCALE = 1.0 / math.sqrt(192.0)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, T, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from cwick_b200 import dist as cd
+        from cwick_b200.ops import Attn
+        attn = Attn(rank)
+        g = torch.Generator(device="cuda").manual_seed(77)          # same stream of numbers on every rank
+        q = torch.randn(NH, L + R, device="cuda", generator=g).to(torch.bfloat16)
+        cache = torch.randn(T, L + R, device="cuda", generator=g).to(torch.bfloat16)
+        row0, rows = cd.kv_ranges(T, world)[rank]
+        local = cache[row0:row0 + rows].contiguous() if rows > 0 else cache[:1].contiguous()
+        got = cd.mla_decode_kv_split(attn, q, local, rows, L, R, SCALE)
+        lens = torch.tensor([T], dtype=torch.int32, device="cuda")
+        want = attn.mla_decode(q[None], cache[None], lens, scale=SCALE, max_kv_len=T)[0]
+        attn.ctx.sync()
+        err = float((got.float() - want.float()).abs().max())
+        # sequence sharding: 6 sequences dealt round-robin
+        B, Ts = 6, 700
+        qs = torch.randn(B, NH, L + R, device="cuda", generator=g).to(torch.bfloat16)
+        cs = torch.randn(B, Ts, L + R, device="cuda", generator=g).to(torch.bfloat16)
+        ls = torch.full((B,), Ts, dtype=torch.int32, device="cuda")
+        full = attn.mla_decode(qs, cs, ls, scale=SCALE, max_kv_len=Ts)
+        mine = cd.shard_sequences(B, world, rank)
+        idx = torch.tensor(mine, device="cuda")
+        part = attn.mla_decode(qs[idx].contiguous(), cs[idx].contiguous(), ls[idx].contiguous(), scale=SCALE,
+                               max_kv_len=Ts)
+        attn.ctx.sync()
+        err2 = float((part.float() - full[idx].float()).abs().max())
+        ret[rank] = (err, err2)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("T", [20000, 100])
+def test_kv_range_split_and_sequence_sharding_over_nccl(T):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, T, ret)) for r in range(world)]
+    [p.start() for p in procs]
+    [p.join(300) for p in procs]
+    assert all(p.exitcode == 0 for p in procs)
+    assert len(ret) == world
+    for err, err2 in ret.values():
+        assert err <= 4e-3 and err2 <= 4e-3, (err, err2)
