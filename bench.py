@@ -408,10 +408,11 @@ def run_kv_split(args, torch, dist, world, rank, local, dev, wl):
         step()
     e1.record(stream)
     barrier()
-    t_end = time.perf_counter() + 1.5
-    while len(sampler.lines) < 6 and time.perf_counter() < t_end:
+    # same load, untimed, long enough for nvidia-smi to sample it; a FIXED count so that every
+    # rank issues the same number of collectives
+    for _ in range(4000):
         step()
-        torch.cuda.synchronize(dev)
+    torch.cuda.synchronize(dev)
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
     if world > 1:

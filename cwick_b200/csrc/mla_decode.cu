@@ -12,7 +12,7 @@
 // not apply so the caller can take the mma.sync path.
 int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride,
                              int64_t ld, const int32_t *kv_len, int max_kv_len, int B, int nh,
-                             float scale, float *partial, int nsplit, void *out_direct);
+                             int R, float scale, float *partial, int nsplit, void *out_direct);
 bool cwk_mla_decode_tc_available();
 
 // ---------------------------------------------------------------------------
@@ -102,14 +102,17 @@ using MlaSmem = FlashRowsSmem<64, 576, 512, 64, 8, false>;
 static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
                       const int32_t *kv_len, int max_kv_len, const int32_t *sel, int64_t sel_ld, int B,
                       int nh, int L, int R, float scale, void *out, float *partial_out, int n_splits) {
-    if (!ctx || !q || !cache || (!kv_len && !partial_out) || (!out && !partial_out)) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: null argument");
+    if (!ctx || !q || !cache || (!kv_len && B != 1) || (!out && !partial_out)) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: null argument");
     if (B <= 0 || nh <= 0 || L <= 0 || R < 0 || max_kv_len < 0 || ld < L + R)
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: bad dimensions B=%d nh=%d L=%d R=%d ld=%lld", B, nh, L, R, (long long)ld);
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
 
-    int path = (L == 512 && R == 64 && (ld % 8) == 0 && (seq_stride % 8) == 0 &&
-                ((uintptr_t)cache % 16) == 0 && ((uintptr_t)q % 16) == 0) ? 1 : 0;
-    if (path == 1 && !sel && nh == 64 && max_kv_len > 0 && cwk_mla_decode_tc_available()) path = 2;
+    const bool aligned = (ld % 8) == 0 && (seq_stride % 8) == 0 && ((uintptr_t)cache % 16) == 0 && ((uintptr_t)q % 16) == 0;
+    int path = (L == 512 && R == 64 && aligned) ? 1 : 0;
+    // the tcgen05 kernel also takes the rope-free 512-wide latent: its ninth column block is then
+    // out of the tensor's bounds and arrives as zeros
+    if (L == 512 && (R == 64 || R == 0) && aligned && !sel && nh == 64 && max_kv_len > 0 && cwk_mla_decode_tc_available())
+        path = 2;
     if (ctx->force_mla_path >= 0) {
         if (ctx->force_mla_path > path) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mla_decode: forced path %d not applicable (best %d)", ctx->force_mla_path, path);
         path = ctx->force_mla_path;
@@ -133,7 +136,7 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     {
     CwkKernelTimer timer(ctx);
     if (path == 2) {
-        int s = cwk_mla_decode_tc_launch(ctx, q, cache, seq_stride, ld, kv_len, max_kv_len, B, nh, scale, partial, ns,
+        int s = cwk_mla_decode_tc_launch(ctx, q, cache, seq_stride, ld, kv_len, max_kv_len, B, nh, R, scale, partial, ns,
                                          direct ? out : nullptr);
         if (s != CWK_OK) return s;
     } else if (path == 1) {
@@ -168,12 +171,19 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     return CWK_OK;
 }
 
+// One sequence whose row count is known on the host (no device length array): used by the
+// reference-named decode entry point.
+int cwk_mla_decode_rows(cwk_ctx *ctx, const void *q, const void *cache, int64_t ld, int rows, int nh, int L, int R,
+                        float scale, void *out) {
+    return mla_launch(ctx, q, cache, 0, ld, nullptr, rows, nullptr, 0, 1, nh, L, R, scale, out, nullptr, 0);
+}
+
 extern "C" {
 
 int cwk_mla_decode_path(const cwk_ctx *ctx, int nh, int L, int R) {
     if (!ctx) return -1;
     int path = (L == 512 && R == 64) ? 1 : 0;
-    if (path == 1 && nh == 64 && cwk_mla_decode_tc_available()) path = 2;
+    if (L == 512 && (R == 64 || R == 0) && nh == 64 && cwk_mla_decode_tc_available()) path = 2;
     if (ctx->force_mla_path >= 0 && ctx->force_mla_path <= path) path = ctx->force_mla_path;
     return path;
 }

@@ -384,8 +384,9 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 bool cwk_mla_decode_tc_available() { return true; }
 
 int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
-                             const int32_t *kv_len, int max_kv_len, int B, int nh, float scale, float *partial,
+                             const int32_t *kv_len, int max_kv_len, int B, int nh, int R, float scale, float *partial,
                              int nsplit, void *out_direct) {
+    const int width = L + R;          // 576, or 512 for a rope-free latent (the rope block then reads as zeros)
     if (nh != NH) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode is built for 64 heads");
     if (max_kv_len <= 0) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode needs a non-empty cache");
     CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
@@ -396,8 +397,8 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     }
     CUtensorMap tm_q, tm_kv;
     {
-        cuuint64_t dims[2] = {(cuuint64_t)DK, (cuuint64_t)B * NH};
-        cuuint64_t strides[1] = {(cuuint64_t)DK * 2};
+        cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)B * NH};
+        cuuint64_t strides[1] = {(cuuint64_t)width * 2};
         cuuint32_t box[2] = {64, NH};
         cuuint32_t es[2] = {1, 1};
         CUresult r = enc(&tm_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(q), dims, strides, box, es,
@@ -408,7 +409,7 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     const bool shared_cache = (seq_stride == 0);
     {
         const cuuint64_t nb = shared_cache ? 1 : (cuuint64_t)B;
-        cuuint64_t dims[3] = {(cuuint64_t)DK, (cuuint64_t)max_kv_len, nb};
+        cuuint64_t dims[3] = {(cuuint64_t)width, (cuuint64_t)max_kv_len, nb};
         cuuint64_t strides[2] = {(cuuint64_t)ld * 2,
                                  shared_cache ? (cuuint64_t)ld * 2 * (cuuint64_t)max_kv_len : (cuuint64_t)seq_stride * 2};
         cuuint32_t box[3] = {64, TILE, 1};

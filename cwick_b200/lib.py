@@ -40,6 +40,11 @@ SIGNATURES = {
     "cwk_fp8_linear": (i32, [vp, vp, vp, vp, i64, i64, i64, vp, i32]),
 }
 
+# reference-named entry points (include/cwick_compat.h); bound separately because their
+# arguments are the reference's structs
+COMPAT_SYMBOLS = ["cwick_attention_mla_decode", "cwick_mla_latent_enabled", "cwick_indexer_active",
+                  "cwick_latent_bf16_enabled", "cwick_latent_elem_bytes", "cwk_dropin_reset"]
+
 _lib = None
 
 

