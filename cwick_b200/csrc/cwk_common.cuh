@@ -31,12 +31,16 @@ struct cwk_ctx {
     size_t stage_pin_bytes = 0;
     uint64_t launches = 0;
     int force_mla_path = -1;
+    bool keep_splits = false;   // internal: leave split records in scratch (no merge, no fold)
+    int last_nsplit = 0;
     // optional event pairs around main kernels (cwk_ctx_profile)
     bool profiling = false;
     std::vector<cudaEvent_t> ev;      // pool, pairs (2i, 2i+1)
     size_t ev_used = 0;
     // device word written by kernels whose bounded waits gave up (0 = fine)
     int *dev_err = nullptr;
+    // block ticket of the KV-split push kernel
+    void *ticket = nullptr;
     // optional device buffer for the tcgen05 kernel's phase stamps (developer aid, see cwk_ctx_debug_trace)
     void *tc_trace = nullptr;
     char err[512] = {0};

@@ -113,6 +113,7 @@ void cwk_ctx_destroy(cwk_ctx *ctx) {
     if (ctx->wbf16) cudaFree(ctx->wbf16);
     if (ctx->stage_pin) cudaFreeHost(ctx->stage_pin);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->ticket) cudaFree(ctx->ticket);
     for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;

@@ -102,7 +102,7 @@ using MlaSmem = FlashRowsSmem<64, 576, 512, 64, 8, false>;
 static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
                       const int32_t *kv_len, int max_kv_len, const int32_t *sel, int64_t sel_ld, int B,
                       int nh, int L, int R, float scale, void *out, float *partial_out, int n_splits) {
-    if (!ctx || !q || !cache || (!kv_len && B != 1) || (!out && !partial_out)) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: null argument");
+    if (!ctx || !q || !cache || (!kv_len && B != 1) || (!out && !partial_out && !ctx->keep_splits)) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: null argument");
     if (B <= 0 || nh <= 0 || L <= 0 || R < 0 || max_kv_len < 0 || ld < L + R)
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: bad dimensions B=%d nh=%d L=%d R=%d ld=%lld", B, nh, L, R, (long long)ld);
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -164,7 +164,8 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
         lse_combine_launch(ctx->stream, partial, ns, nh, L, B, (uint16_t *)out);
         CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel");
     }
-    if (partial_out) {          // B == 1 here
+    ctx->last_nsplit = ns;
+    if (partial_out && !ctx->keep_splits) {          // B == 1 here
         lse_fold_launch(ctx->stream, partial, ns, nh, L, partial_out);
         CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel<fold>");
     }
@@ -176,6 +177,18 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
 int cwk_mla_decode_rows(cwk_ctx *ctx, const void *q, const void *cache, int64_t ld, int rows, int nh, int L, int R,
                         float scale, void *out) {
     return mla_launch(ctx, q, cache, 0, ld, nullptr, rows, nullptr, 0, 1, nh, L, R, scale, out, nullptr, 0);
+}
+
+// Split-KV decode of one sequence whose result stays as split records in the context's scratch
+// (the KV-range exchange folds and ships them itself).
+int cwk_mla_launch_splits(cwk_ctx *ctx, const void *q, const void *cache, int64_t ld, int rows, int nh, int L, int R,
+                          float scale, float **partial_out, int *nsplit_out) {
+    ctx->keep_splits = true;
+    int s = mla_launch(ctx, q, cache, 0, ld, nullptr, rows, nullptr, 0, 1, nh, L, R, scale, nullptr, nullptr, 0);
+    ctx->keep_splits = false;
+    *partial_out = ctx->scratch;
+    *nsplit_out = ctx->last_nsplit;
+    return s;
 }
 
 extern "C" {

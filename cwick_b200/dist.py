@@ -48,3 +48,61 @@ def mla_decode_kv_split(attn, q, local_cache, local_rows: int, L: int, R: int, s
     rec = attn.mla_decode_partial(q, local_cache, 0, local_rows, L, R, scale)
     allrec = exchange_partials(rec, group)
     return attn.lse_combine(allrec.contiguous(), nh, L)
+
+
+class KvSplitExchange:
+    """Peer-memory exchange for the KV-range split (cwk_xchg_* / cwk_mla_decode_kv_split): each rank
+    allocates a window, the 64-byte IPC handles travel once through the process group, and from
+    then on a step is three kernel launches per rank and no collective call."""
+
+    def __init__(self, attn, nh: int, L: int, group=None):
+        import ctypes as C
+        self.attn, self.nh, self.L, self.group = attn, nh, L, group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        lib, ctx = attn.lib, attn.ctx
+        self.own = C.c_void_p()
+        ctx.check(lib.cwk_xchg_create(ctx.h, nh, L, self.world, C.byref(self.own), None))
+        handle = (C.c_uint8 * 64)()
+        ctx.check(lib.cwk_xchg_export(ctx.h, self.own, handle))
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, bytes(handle), group=group)
+        else:
+            handles[0] = bytes(handle)
+        self.windows = (C.c_void_p * self.world)()
+        self.opened = []
+        for g in range(self.world):
+            if g == self.rank:
+                self.windows[g] = self.own.value
+            else:
+                p = C.c_void_p()
+                buf = (C.c_uint8 * 64).from_buffer_copy(handles[g])
+                ctx.check(lib.cwk_xchg_open(ctx.h, buf, C.byref(p)))
+                self.windows[g] = p.value
+                self.opened.append(p)
+        self.epoch = 0
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    def decode(self, q, local_cache, local_rows: int, R: int, scale: float, out=None):
+        """q [nh][L+R] bf16 (replicated), local_cache [rows][ld] bf16 -> bf16 [nh][L] on every rank."""
+        import ctypes as C
+        if out is None:
+            out = torch.empty(self.nh, self.L, dtype=torch.bfloat16, device=q.device)
+        self.epoch += 1
+        a = self.attn
+        a.ctx.check(a.lib.cwk_mla_decode_kv_split(
+            a.ctx.h, C.c_void_p(q.data_ptr()), C.c_void_p(local_cache.data_ptr()), local_cache.shape[-1], local_rows,
+            self.nh, self.L, R, scale, self.windows, self.rank, self.world, self.epoch, C.c_void_p(out.data_ptr())))
+        return out
+
+    def close(self):
+        lib, ctx = self.attn.lib, self.attn.ctx
+        ctx.sync()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for p in self.opened:
+            lib.cwk_xchg_close(ctx.h, p)
+        lib.cwk_xchg_destroy(ctx.h, self.own)
+        self.opened = []

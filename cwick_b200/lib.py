@@ -32,6 +32,12 @@ SIGNATURES = {
     "cwk_mla_decode_noalloc": (i32, [vp, vp, vp, i64, i64, vp, i32, i32, i32, f32, vp, C.c_char_p, C.c_size_t]),
     "cwk_mla_decode_partial": (i32, [vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, vp]),
     "cwk_lse_combine": (i32, [vp, vp, i32, i32, i32, vp]),
+    "cwk_xchg_create": (i32, [vp, i32, i32, i32, C.POINTER(vp), C.POINTER(C.c_size_t)]),
+    "cwk_xchg_export": (i32, [vp, vp, vp]),
+    "cwk_xchg_open": (i32, [vp, vp, C.POINTER(vp)]),
+    "cwk_xchg_close": (i32, [vp, vp]),
+    "cwk_xchg_destroy": (i32, [vp, vp]),
+    "cwk_mla_decode_kv_split": (i32, [vp, vp, vp, i64, i64, i32, i32, i32, f32, C.POINTER(vp), i32, i32, C.c_uint32, vp]),
     "cwk_indexer_scores_fp8": (i32, [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, vp]),
     "cwk_topk_select": (i32, [vp, vp, i64, vp, i32, i32, i32, i32, vp, i64, vp]),
     "cwk_gqa_decode": (i32, [vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, f32, vp, i32]),

@@ -150,6 +150,31 @@ CWK_API int cwk_mla_decode_partial(cwk_ctx *ctx, const void *q, const void *cach
  * src/q35_model.c:1693-1701. Partials with l == 0 are ignored. */
 CWK_API int cwk_lse_combine(cwk_ctx *ctx, const float *partials, int G, int nh, int L, void *out);
 
+/* ---- one long context split by KV range across the GPUs of a node -----------
+ * No reference counterpart (the reference is one process on one device). Rank r
+ * holds a contiguous range of the cache rows and calls cwk_mla_decode_kv_split
+ * once per step; the partial-softmax exchange is done by the kernels themselves
+ * with stores into the peers' windows over NVLink, so a step contains no
+ * collective-library call. Set-up, once:
+ *   cwk_xchg_create  allocates this rank's window (two parities x `world` record
+ *                    slots + epoch words) with cudaMalloc;
+ *   cwk_xchg_export  gives its 64-byte CUDA IPC handle, to be sent to the peers by
+ *                    any host channel; cwk_xchg_open maps a peer's handle.
+ * windows[g] is this rank's pointer to rank g's window (its own at index rank).
+ * `epoch` must be 1, 2, 3, ... identically on every rank. The merge waits at most
+ * about a second for the peers' records; a peer that never publishes shows up as
+ * CWK_ERR_STATE at the next cwk_ctx_sync, the context stays usable.
+ *   q bf16 [nh][L+R] (same on every rank); cache = the LOCAL rows, bf16 [rows][ld];
+ *   out bf16 [nh][L] (every rank gets the full result). */
+CWK_API int cwk_xchg_create(cwk_ctx *ctx, int nh, int L, int world, void **window, size_t *bytes);
+CWK_API int cwk_xchg_export(cwk_ctx *ctx, void *window, void *handle64);
+CWK_API int cwk_xchg_open(cwk_ctx *ctx, const void *handle64, void **peer_window);
+CWK_API int cwk_xchg_close(cwk_ctx *ctx, void *peer_window);
+CWK_API int cwk_xchg_destroy(cwk_ctx *ctx, void *window);
+CWK_API int cwk_mla_decode_kv_split(cwk_ctx *ctx, const void *q, const void *cache, int64_t ld, int64_t rows,
+                                    int nh, int L, int R, float scale, void *const *windows, int rank,
+                                    int world, uint32_t epoch, void *out);
+
 /* ---- DSA lightning indexer -------------------------------------------------
  * Scores: sc[b][c] = sum_h wt[b][h] * ReLU(q[b][h] . k[b][c]) in the
  * reference's exact f32 order (src/attention.c:573-582 with dot_f32's

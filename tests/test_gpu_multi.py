@@ -41,6 +41,14 @@ def _worker(rank, world, port, T, ret):
         row0, rows = cd.kv_ranges(T, world)[rank]
         local = cache[row0:row0 + rows].contiguous() if rows > 0 else cache[:1].contiguous()
         got = cd.mla_decode_kv_split(attn, q, local, rows, L, R, SCALE)
+        # the same split with the exchange done by the kernels over peer memory, several steps in a row
+        x = cd.KvSplitExchange(attn, NH, L)
+        errp = 0.0
+        for step in range(5):
+            gp = x.decode(q, local, rows, R, SCALE)
+            attn.ctx.sync()
+            errp = max(errp, float((gp.float() - got.float()).abs().max()))
+        x.close()
         lens = torch.tensor([T], dtype=torch.int32, device="cuda")
         want = attn.mla_decode(q[None], cache[None], lens, scale=SCALE, max_kv_len=T)[0]
         attn.ctx.sync()
@@ -57,7 +65,7 @@ def _worker(rank, world, port, T, ret):
                                max_kv_len=Ts)
         attn.ctx.sync()
         err2 = float((part.float() - full[idx].float()).abs().max())
-        ret[rank] = (err, err2)
+        ret[rank] = (err, err2, errp)
     finally:
         dist.destroy_process_group()
 
@@ -79,6 +87,25 @@ def test_kv_range_split_and_sequence_sharding_over_nccl(T):
             p.terminate()
     assert all(p.exitcode == 0 for p in procs)
     assert len(ret) == world
-    for err, err2 in ret.values():
+    for err, err2, errp in ret.values():
         # two roundings of the same value may differ by one bf16 step of an O(1) output
-        assert err <= 2e-2 and err2 <= 2e-2, (err, err2)
+        assert err <= 2e-2 and err2 <= 2e-2 and errp <= 2e-2, (err, err2, errp)
+
+
+def test_peer_exchange_entry_point_on_one_gpu():
+    """world = 1: the same three launches with the rank pushing into its own window."""
+    from cwick_b200 import dist as cd
+    from cwick_b200.ops import Attn
+    attn = Attn(0)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    T = 3000
+    q = torch.randn(NH, L + R, device="cuda", generator=g).to(torch.bfloat16)
+    cache = torch.randn(T, L + R, device="cuda", generator=g).to(torch.bfloat16)
+    x = cd.KvSplitExchange(attn, NH, L)
+    lens = torch.tensor([T], dtype=torch.int32, device="cuda")
+    want = attn.mla_decode(q[None], cache[None], lens, scale=SCALE, max_kv_len=T)[0]
+    for _ in range(3):
+        got = x.decode(q, cache, T, R, SCALE)
+        attn.ctx.sync()
+        assert float((got.float() - want.float()).abs().max()) <= 4e-3
+    x.close()
