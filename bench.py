@@ -386,9 +386,14 @@ def run_kv_split(args, torch, dist, world, rank, local, dev, wl):
     caches = [torch.randn(rows, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(rot)]
     q = torch.randn(NH, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
     i = [0]
+    xchg = cd.KvSplitExchange(attn, NH, L) if args.exchange == "p2p" else None
+    out_buf = torch.empty(NH, L, dtype=torch.bfloat16, device=dev)
 
     def step():
-        out = cd.mla_decode_kv_split(attn, q, caches[i[0] % rot], rows, L, R, SCALE)
+        if xchg is not None:
+            out = xchg.decode(q, caches[i[0] % rot], rows, R, SCALE, out=out_buf)
+        else:
+            out = cd.mla_decode_kv_split(attn, q, caches[i[0] % rot], rows, L, R, SCALE)
         i[0] += 1
         return out
 
@@ -428,10 +433,13 @@ def run_kv_split(args, torch, dist, world, rank, local, dev, wl):
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wl["desc"], "cached_tokens": T, "rows_per_gpu": rows, "heads": NH,
-                       "exchange": "all_gather of %d-byte records" % (NH * (L + 2) * 4),
+                       "exchange": ("peer-memory stores + epoch flags, %d-byte records" if xchg is not None
+                                    else "NCCL all_gather of %d-byte records") % (NH * (L + 2) * 4),
                        "l2": "rotation of %d local caches" % rot, "parallelism": f"kv-range x{world}"},
             "kv_hbm_gbs": by / (ms_step / 1e3) / 1e9, "kv_hbm_frac_of_measured_peak": by / (ms_step / 1e3) / 1e9 / (peak * world),
             "clocks": clocks, "gpu_launches": int(attn.ctx.launches - l0)}))
+    if xchg is not None:
+        xchg.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -580,9 +588,25 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="c5b: how partial records travel")
+    ap.add_argument("--extra-only", default=None, choices=["c1", "c3", "c4", "c5a"],
+                    help="run one side measurement alone and print its JSON (for profiling that kernel)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.extra_only:
+        import torch
+        from cwick_b200 import build
+        build.build()
+        from cwick_b200.ops import Attn
+        dev = torch.device("cuda", 0)
+        stream = torch.cuda.Stream(device=dev)
+        torch.cuda.set_stream(stream)
+        attn = Attn(0)
+        peak, _ = peaks()
+        fn = {"c1": side_gqa_decode, "c3": side_prefill, "c4": side_dsa,
+              "c5a": lambda a, d, s_, p_: side_measure(a, d, s_, 64, 32768, p_)}[args.extra_only]
+        print(json.dumps({args.extra_only: fn(attn, dev, stream, peak)}))
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_ours(args)
