@@ -77,7 +77,7 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 // order followed by the rows equal to it in index order, `want` in all.
 __global__ void __launch_bounds__(1024) topk_select_kernel(const float *sc, int64_t sc_stride,
                                                            const int32_t *n, int want, int keep_self,
-                                                           int32_t *sel, int64_t sel_ld, int32_t *nsel) {
+                                                           int32_t *sel, int64_t sel_ld, int32_t *nsel, int ascending) {
     const int b = blockIdx.x, tid = threadIdx.x;
     const int nb = n[b];
     const float *s = sc + (int64_t)b * sc_stride;
@@ -89,8 +89,8 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float *sc, int6
     }
     __shared__ uint32_t hist[256];
     __shared__ uint32_t s_prefix, s_remaining;
-    __shared__ int s_warp[32][2];
-    __shared__ int s_base[2];
+    __shared__ int s_warp[32][3];
+    __shared__ int s_base[3];
     uint32_t prefix = 0, mask = 0;
     int remaining = want;                    // rank still to find inside the current bucket
     for (int pass = 0; pass < 4; pass++) {
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float *sc, int6
     const int need_eq = remaining;
     // count rows above the threshold (= want - need_eq by construction)
     const int n_gt = want - need_eq;
-    if (tid == 0) { s_base[0] = 0; s_base[1] = 0; }
+    if (tid == 0) { s_base[0] = 0; s_base[1] = 0; s_base[2] = 0; }
     __syncthreads();
     const int lane = tid & 31, warp = tid >> 5;
     for (int c0 = 0; c0 < nb; c0 += 1024) {
@@ -144,14 +144,27 @@ __global__ void __launch_bounds__(1024) topk_select_kernel(const float *sc, int6
         for (int w = 0; w < warp; w++) { og += s_warp[w][0]; oe += s_warp[w][1]; }
         og += __popc(bg & ((1u << lane) - 1u));
         oe += __popc(be & ((1u << lane) - 1u));
-        if (gt) out[og] = i;
-        if (eq && oe < need_eq) out[n_gt + oe] = i;
+        if (!ascending) {
+            if (gt) out[og] = i;
+            if (eq && oe < need_eq) out[n_gt + oe] = i;
+        }
+        // ascending mode: one list in index order (rows above the threshold and the first need_eq ties)
+        const bool take = gt || (eq && oe < need_eq);
+        const uint32_t bt = __ballot_sync(0xffffffffu, take);
+        if (lane == 0) s_warp[warp][2] = __popc(bt);
+        __syncthreads();
+        if (ascending && take) {
+            int ot = s_base[2];
+            for (int w = 0; w < warp; w++) ot += s_warp[w][2];
+            out[ot + __popc(bt & ((1u << lane) - 1u))] = i;
+        }
         __syncthreads();
         if (tid == 0) {
-            int tg = 0, te = 0;
-            for (int w = 0; w < 32; w++) { tg += s_warp[w][0]; te += s_warp[w][1]; }
+            int tg = 0, te = 0, tt = 0;
+            for (int w = 0; w < 32; w++) { tg += s_warp[w][0]; te += s_warp[w][1]; tt += s_warp[w][2]; }
             s_base[0] += tg;
             s_base[1] += te;
+            s_base[2] += tt;
         }
         __syncthreads();
     }
@@ -189,8 +202,19 @@ int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int3
     (void)max_n;
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     CwkKernelTimer timer(ctx);
-    topk_select_kernel<<<B, 1024, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel);
+    topk_select_kernel<<<B, 1024, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel, 0);
     CWK_LAUNCH_CHECK(ctx, "topk_select_kernel");
+    return CWK_OK;
+}
+
+int cwk_ds_topk(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int k, int32_t *out, int64_t out_ld,
+                int32_t *count) {
+    if (!ctx || !sc || !n || !out || !count || B <= 0 || k <= 0 || out_ld < k)
+        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_topk: bad argument");
+    CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    CwkKernelTimer timer(ctx);
+    topk_select_kernel<<<B, 1024, 0, ctx->stream>>>(sc, sc_stride, n, k, 0, out, out_ld, count, 1);
+    CWK_LAUNCH_CHECK(ctx, "topk_select_kernel<ascending>");
     return CWK_OK;
 }
 

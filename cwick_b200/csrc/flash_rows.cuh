@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
 }
 
 // ---------------------------------------------------------------------------
-// Split merge. grid (nh, B), 128 threads. Weights e^(m_s-M) are computed once
+// Split merge. grid (nh, B, ceil(D/128)), 128 threads. Weights e^(m_s-M) are computed once
 // into shared memory; the value pass then streams each record's row once with
 // float2 loads. FOLD = false: normalised bf16 rows out[b][h][D].
 // FOLD = true: one un-normalised record (same layout as the inputs) at rec_out.
@@ -375,33 +375,33 @@ static __global__ void __launch_bounds__(128) lse_merge_kernel(const float *part
     }
     const float den = red[0];
     const float inv = FOLD ? 1.f : (den > 0.f ? 1.f / den : 0.f);
-    if (FOLD && tid == 0) {
+    if (FOLD && tid == 0 && blockIdx.z == 0) {
         rec_out[h] = M;
         rec_out[nh + h] = den;
     }
+    // value pass: blockIdx.z picks a 128-column chunk of the row, one column per thread
     const float *orow = base + 2 * nh + (int64_t)h * D;
-    for (int i = tid * 2; i < D; i += 256) {
-        float a0 = 0.f, a1 = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < nsplit; s++) {
-            const float w = sw[s];
-            const float2 o = *reinterpret_cast<const float2 *>(orow + s * rec_sz + i);
-            a0 += w * o.x;
-            a1 += w * o.y;
+    const int i = blockIdx.z * 128 + tid;
+    if (i < D) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int s = 0;
+        for (; s + 4 <= nsplit; s += 4) {
+            a0 += sw[s] * orow[(int64_t)s * rec_sz + i];
+            a1 += sw[s + 1] * orow[(int64_t)(s + 1) * rec_sz + i];
+            a2 += sw[s + 2] * orow[(int64_t)(s + 2) * rec_sz + i];
+            a3 += sw[s + 3] * orow[(int64_t)(s + 3) * rec_sz + i];
         }
-        if (FOLD) {
-            rec_out[2 * nh + (int64_t)h * D + i] = a0;
-            rec_out[2 * nh + (int64_t)h * D + i + 1] = a1;
-        } else {
-            *reinterpret_cast<uint32_t *>(out + ((int64_t)b * nh + h) * D + i) = pack_bf16x2(a0 * inv, a1 * inv);
-        }
+        for (; s < nsplit; s++) a0 += sw[s] * orow[(int64_t)s * rec_sz + i];
+        const float a = (a0 + a1) + (a2 + a3);
+        if (FOLD) rec_out[2 * nh + (int64_t)h * D + i] = a;
+        else out[((int64_t)b * nh + h) * D + i] = (uint16_t)(pack_bf16x2(a * inv, 0.f) & 0xffffu);
     }
 }
 
 static inline void lse_combine_launch(cudaStream_t st, const float *partial, int nsplit, int nh, int D, int B,
                                       uint16_t *out) {
-    lse_merge_kernel<false><<<dim3(nh, B), 128, 0, st>>>(partial, nsplit, nh, D, out, nullptr);
+    lse_merge_kernel<false><<<dim3(nh, B, (D + 127) / 128), 128, 0, st>>>(partial, nsplit, nh, D, out, nullptr);
 }
 static inline void lse_fold_launch(cudaStream_t st, const float *partial, int nsplit, int nh, int D, float *rec_out) {
-    lse_merge_kernel<true><<<dim3(nh, 1), 128, 0, st>>>(partial, nsplit, nh, D, nullptr, rec_out);
+    lse_merge_kernel<true><<<dim3(nh, 1, (D + 127) / 128), 128, 0, st>>>(partial, nsplit, nh, D, nullptr, rec_out);
 }

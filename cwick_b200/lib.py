@@ -42,6 +42,13 @@ SIGNATURES = {
     "cwk_topk_select": (i32, [vp, vp, i64, vp, i32, i32, i32, i32, vp, i64, vp]),
     "cwk_gqa_decode": (i32, [vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, f32, vp, i32]),
     "cwk_gqa_prefill": (i32, [vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, vp]),
+    "cwk_gqa_qk_prep": (i32, [vp, vp, vp, vp, vp, vp, f32, i32, C.c_double, i64, i32, i32, i32, i32, vp, vp, vp]),
+    "cwk_gqa_gate": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "cwk_indexer_pool_compress": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]),
+    "cwk_ds_sparse_attn": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, f32, vp]),
+    "cwk_ds_indexer_scores": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "cwk_ds_topk": (i32, [vp, vp, i64, vp, i32, i32, vp, i64, vp]),
+    "cwk_ds_lin_q": (i32, [vp, vp, vp, vp, i64, i64, vp]),
     "cwk_mla_prefill": (i32, [vp] * 12 + [i64] + [i32] * 7 + [f32, f32, f32, vp]),
     "cwk_fp8_linear": (i32, [vp, vp, vp, vp, i64, i64, i64, vp, i32]),
 }

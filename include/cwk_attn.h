@@ -221,6 +221,45 @@ CWK_API int cwk_gqa_prefill(cwk_ctx *ctx, const void *Q, const void *K, const vo
 CWK_API int cwk_fp8_linear(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv,
                    int64_t n, int64_t k, int64_t cols, void *Y, int out_bf16);
 
+/* ---- pieces either side of the reductions ------------------------------------
+ * Qwen3.5 per-token preparation (src/q35_model.c:1627-1652): q heads are read from
+ * q_proj rows laid out [q(hd) | gate(hd)] per head, q and k heads get the
+ * RMS norm with (1+w) weights (:112-122) and the rotate-half RoPE on the first
+ * `rot` dims (:144-153, table of :459-477); K and V rows go to the caches at
+ * pos0+t. qg f32 [n][nh][2*hd]; k,v f32 [n][nkv][hd]; q_out bf16 [n][nh][hd];
+ * kcache/vcache bf16 [rows][nkv][hd]. */
+CWK_API int cwk_gqa_qk_prep(cwk_ctx *ctx, const float *qg, const float *k, const float *v, const float *q_norm,
+                            const float *k_norm, float eps, int rot, double theta, int64_t pos0, int n, int nh,
+                            int nkv, int hd, void *q_out, void *kcache, void *vcache);
+/* Sigmoid output gate (src/q35_model.c:1749-1760): out f32 [n][nh][hd] = attn (bf16) * sigmoid(gate half of qg). */
+CWK_API int cwk_gqa_gate(cwk_ctx *ctx, const void *attn, const float *qg, int n, int nh, int hd, float *out);
+/* GLM indexer pool compression (indexer_absorb, src/attention.c:490-525), n_pools closed pools at once:
+ * tail_k, tail_g f32 [n_pools][kp][hd]; ape bf16 [kp][hd]; k_norm, k_norm_b f32 [hd]; pool f32 [n_pools][hd]. */
+CWK_API int cwk_indexer_pool_compress(cwk_ctx *ctx, const float *tail_k, const float *tail_g, const void *ape,
+                                      const float *k_norm, const float *k_norm_b, int n_pools, int kp, int hd,
+                                      float eps, float *pool);
+
+/* ---- DeepSeek-V4 variants ---------------------------------------------------------
+ * Sparse attention over gathered f32 rows with a per-head sink in the denominator
+ * (ds_sparse_attn_heads, src/ds_model.c:917-966). idx int32 [total], negative = skip;
+ * q, o f32 [nh][HD]; kv f32 [rows][HD] (key == value); total <= 1024. */
+CWK_API int cwk_ds_sparse_attn(cwk_ctx *ctx, const float *q, const float *kv, const int32_t *idx, int total, int nh,
+                               int HD, const float *sink, float scale, float *o);
+/* Indexer scores with bf16-rounded head dots (ds_indexer, src/ds_model.c:1108-1121), in the
+ * reference's operation order: keys f32 [n][hd], q f32 [ih][hd], w f32 [ih] -> sc f32 [n]. */
+CWK_API int cwk_ds_indexer_scores(cwk_ctx *ctx, const float *keys, const float *q, const float *w, int n, int ih,
+                                  int hd, float *sc);
+/* The k best scores per row as ASCENDING positions (ds_topk_scores, src/ds_ops.c:310-338). Exact by
+ * value; where several scores tie exactly at the threshold the lowest positions are kept (the
+ * reference's heap keeps a shape-dependent subset of such ties). */
+CWK_API int cwk_ds_topk(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int k,
+                        int32_t *out, int64_t out_ld, int32_t *count);
+/* Quantised projection of one activation row (ds_lin_q, src/ds_model.c:880-885): activations to E4M3
+ * with a power-of-two scale per 32 (src/ds_quant.c:143-159), E4M3 weights [N][K] with E8M0 scales
+ * [N/32][K/32] (src/ds_quant.c:653-742), result rounded to bf16 (kept in f32). */
+CWK_API int cwk_ds_lin_q(cwk_ctx *ctx, const float *x, const void *w, const void *w_scale, int64_t N, int64_t K,
+                         float *out);
+
 /* ---- MLA causal prefill of a chunk ---------------------------------------
  * Replaces cwick_attention_mla_prefill_chunk up to the attention output
  * (src/attention.c:943-1019) for FP8-E4M3 block-scaled q_a / q_b / kv_a

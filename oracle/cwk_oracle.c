@@ -159,7 +159,7 @@ ORC_API void orc_rope_adjacent(float *v, int64_t n_rope, int64_t pos, float base
 ORC_API void orc_rope_half(float *v, int rot, int64_t pos, double theta) {
     int half = rot / 2;
     for (int i = 0; i < half; i++) {
-        double inv = pow(theta, -2.0 * (double)i / (double)rot);
+        double inv = 1.0 / pow(theta, (double)(2 * i) / (double)rot);
         float c = (float)cos((double)pos * inv), s = (float)sin((double)pos * inv);
         float a = v[i], b = v[i + half];
         v[i] = a * c - b * s;
@@ -886,4 +886,124 @@ ORC_API void orc_mla_prefill(const float *X, const uint8_t *Wqa, const float *Sq
         free(scores);
     }
     free(qf); free(q); free(q_a); free(kv_a);
+}
+
+
+/* ------------------------------------------------------------------ */
+/* pieces either side of the attention reductions                      */
+/* ------------------------------------------------------------------ */
+
+/* Qwen3.5 per-head RMS norm with (1 + w) weights: f32 sum of squares in index
+ * order, rstd = 1/sqrtf(mean + eps). src/q35_model.c:112-122 (rms_norm_w). */
+ORC_API void orc_q35_rms_norm_w(float *out, const float *in, int n, const float *w, float eps) {
+    float acc = 0.0f;
+    for (int i = 0; i < n; i++) acc += in[i] * in[i];
+    float rstd = 1.0f / sqrtf(acc / (float)n + eps);
+    for (int i = 0; i < n; i++) out[i] = w ? in[i] * rstd * (1.0f + w[i]) : in[i] * rstd;
+}
+
+/* One token of mixer_attn's preparation (src/q35_model.c:1627-1652): q_proj rows are
+ * [q(hd) | gate(hd)] per head; q and k heads get rms_norm_w and the rotate-half RoPE on the
+ * first `rot` dims at position pos; k and v become the cache row. qg [nh][2*hd], k/v [nkv][hd]
+ * f32 in; q_out [nh][hd], k_out/v_out [nkv][hd] f32. */
+ORC_API void orc_q35_qk_prep(const float *qg, const float *k, const float *v, const float *q_norm,
+                             const float *k_norm, float eps, int rot, int64_t pos, double theta,
+                             int nh, int nkv, int hd, float *q_out, float *k_out, float *v_out) {
+    for (int h = 0; h < nh; h++) {
+        orc_q35_rms_norm_w(q_out + (size_t)h * hd, qg + (size_t)h * 2 * hd, hd, q_norm, eps);
+        orc_rope_half(q_out + (size_t)h * hd, rot, pos, theta);
+    }
+    for (int h = 0; h < nkv; h++) {
+        orc_q35_rms_norm_w(k_out + (size_t)h * hd, k + (size_t)h * hd, hd, k_norm, eps);
+        orc_rope_half(k_out + (size_t)h * hd, rot, pos, theta);
+    }
+    memcpy(v_out, v, sizeof(float) * (size_t)nkv * hd);
+}
+
+/* Sigmoid output gate: o[h][i] *= 1/(1+expf(-gate)), gate = second half of each head's q_proj
+ * slice. src/q35_model.c:1749-1760. */
+ORC_API void orc_q35_gate(float *o, const float *qg, int nh, int hd) {
+    for (int h = 0; h < nh; h++)
+        for (int i = 0; i < hd; i++)
+            o[(size_t)h * hd + i] *= 1.0f / (1.0f + expf(-qg[(size_t)h * 2 * hd + hd + i]));
+}
+
+/* One closed indexer pool -> one compressed key row. src/attention.c:490-525: each of the kp raw
+ * key rows is layer-normalised (mean and variance in double), a softmax over the kp rows with
+ * logits gate + ape weights them per dimension, and the affine k_norm (weight, bias) is applied to
+ * each normalised row before the weighting. tail_k, tail_g [kp][hd]; ape bf16 [kp][hd]. */
+ORC_API void orc_indexer_pool_compress(const float *tail_k, const float *tail_g, const uint16_t *ape,
+                                       const float *k_norm, const float *k_norm_b, int kp, int hd,
+                                       float eps, float *dst) {
+    float mean[8], inv[8];
+    for (int i = 0; i < kp; i++) {
+        const float *row = tail_k + (size_t)i * hd;
+        double s = 0.0;
+        for (int d = 0; d < hd; d++) s += (double)row[d];
+        mean[i] = (float)(s / (double)hd);
+        double v = 0.0;
+        for (int d = 0; d < hd; d++) { double t = (double)row[d] - (double)mean[i]; v += t * t; }
+        inv[i] = 1.0f / sqrtf((float)(v / (double)hd) + eps);
+    }
+    for (int d = 0; d < hd; d++) {
+        float mx = -INFINITY;
+        for (int i = 0; i < kp; i++) {
+            float lg = tail_g[(size_t)i * hd + d] + bf16f(ape[(size_t)i * hd + d]);
+            if (lg > mx) mx = lg;
+        }
+        float den = 0.0f, acc = 0.0f;
+        for (int i = 0; i < kp; i++) {
+            float lg = tail_g[(size_t)i * hd + d] + bf16f(ape[(size_t)i * hd + d]);
+            float p = expf(lg - mx);
+            den += p;
+            float nrm = ((tail_k[(size_t)i * hd + d] - mean[i]) * inv[i]) * k_norm[d] + k_norm_b[d];
+            acc += p * nrm;
+        }
+        dst[d] = den > 0.0f ? acc / den : 0.0f;
+    }
+}
+
+/* DeepSeek quantised projection for one activation row (src/ds_model.c:880-885 ds_lin_q):
+ * the activation is quantised per 32 to E4M3 with a power-of-two scale
+ * (src/ds_quant.c:143-159, amax floor 1e-4, scale 2^ceil(log2(amax/448))), then per output row
+ * acc += (sum_32(e4m3(w)*e4m3(a)) * a_scale) * 2^(w_scale-127) block by block
+ * (src/ds_quant.c:653-666), and the result is rounded to bf16. w E4M3 [N][K], w_scale E8M0
+ * [N/32][K/32]. */
+ORC_API void orc_ds_lin_q(const float *x, const uint8_t *w, const uint8_t *w_scale, int64_t N,
+                          int64_t K, float *out) {
+    const int64_t nb = K / 32;
+    float *af = malloc(sizeof(float) * (size_t)K);
+    float *asf = malloc(sizeof(float) * (size_t)nb);
+    for (int64_t b = 0; b < nb; b++) {
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) { float a = fabsf(x[b * 32 + i]); if (a > amax) amax = a; }
+        if (amax < 1e-4f) amax = 1e-4f;
+        float t = amax * (1.0f / 448.0f);
+        uint32_t u;
+        memcpy(&u, &t, 4);
+        int e = (int)((u >> 23) & 0xFF) - 127 + ((u & 0x7FFFFF) ? 1 : 0);
+        float sc = ldexpf(1.0f, e);
+        asf[b] = sc;
+        for (int i = 0; i < 32; i++) {
+            float qv = x[b * 32 + i] / sc;
+            if (qv > 448.0f) qv = 448.0f;
+            if (qv < -448.0f) qv = -448.0f;
+            af[b * 32 + i] = orc_e4m3_to_f32(orc_f32_to_e4m3_ref(qv));
+        }
+    }
+    for (int64_t n = 0; n < N; n++) {
+        const uint8_t *row = w + n * K;
+        const uint8_t *rs = w_scale + (n / 32) * nb;
+        float acc = 0.0f;
+        for (int64_t b = 0; b < nb; b++) {
+            float part = 0.0f;
+            for (int j = 0; j < 32; j++) part += orc_e4m3_to_f32(row[b * 32 + j]) * af[b * 32 + j];
+            uint32_t sb = (uint32_t)rs[b] << 23;
+            float ws;
+            memcpy(&ws, &sb, 4);
+            acc += (part * asf[b]) * ws;
+        }
+        out[n] = orc_bf16_round(acc);
+    }
+    free(asf); free(af);
 }

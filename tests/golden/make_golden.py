@@ -148,6 +148,32 @@ def main():
     G["idx_cache"], G["idx_out"], G["idx_xlast"] = cache, out, xs[T - 1].copy()
     G["idx_sel"] = sel[:int(nsel[0])].copy()
     G["idx_pool"], G["idx_sc"], G["idx_q"], G["idx_wt"] = pool[:npools], scs[:npools], qo, wto
+    for k_, v in ix.items():
+        G["idx_w_" + k_] = v
+    G["idx_x"] = xs
+    # ---- DeepSeek quantised projection: activation quantiser + fp8 GEMV + bf16 round ---------
+    N, K = 96, 256
+    rng = np.random.default_rng(7)
+    wq = rng.integers(0, 256, size=(N, K), dtype=np.uint8)
+    wq[(wq & 0x7F) == 0x7F] = 0x3C                          # no NaN codes
+    wsc = rng.integers(0x72, 0x7C, size=(N // 32, K // 32), dtype=np.uint8)   # the scale range real checkpoints use
+    xq = synth.normal(SEED, 400, K) * 3
+    xq[32:64] = 0.0                                           # an all-zero block (amax floor)
+    r.ds_act_quant_block.restype = C.c_uint8
+    r.ds_act_quant_block.argtypes = [orc.f32p, orc.u8p]
+    r.ds_fp8_gemv.argtypes = [orc.u8p, orc.u8p, orc.u8p, orc.u8p, C.c_int64, C.c_int64, orc.f32p]
+    aq = np.empty(K, np.uint8)
+    asc = np.empty(K // 32, np.uint8)
+    for b in range(K // 32):
+        blk = np.ascontiguousarray(xq[b * 32:(b + 1) * 32])
+        o8 = np.empty(32, np.uint8)
+        asc[b] = r.ds_act_quant_block(orc.P(blk, orc.f32p), orc.P(o8, orc.u8p))
+        aq[b * 32:(b + 1) * 32] = o8
+    outq = np.empty(N, np.float32)
+    os.environ["DS_GEMV_ROWS"] = "1"
+    r.ds_fp8_gemv(orc.P(aq, orc.u8p), orc.P(asc, orc.u8p), orc.P(wq, orc.u8p), orc.P(wsc, orc.u8p), N, K, orc.P(outq, orc.f32p))
+    outq = np.array([r.ds_bf16_round(float(v)) for v in outq], np.float32)
+    G["dsq_w"], G["dsq_ws"], G["dsq_x"], G["dsq_out"] = wq, wsc, xq, outq
     np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **G)
     print("wrote", os.path.join(HERE, "ref_vectors.npz"), {k: v.shape for k, v in G.items() if k.startswith("idx_s")})
 

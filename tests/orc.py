@@ -82,6 +82,11 @@ def oracle():
         L.orc_mla_prefill.argtypes = [f32p, u8p, f32p, u8p, f32p, u8p, f32p, u16p, u16p, u16p, u16p, C.c_int64,
                                       C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float,
                                       C.c_float, C.c_float, i32p, C.c_int, f32p]
+        L.orc_q35_qk_prep.argtypes = [f32p, f32p, f32p, f32p, f32p, C.c_float, C.c_int, C.c_int64, C.c_double, C.c_int,
+                                      C.c_int, C.c_int, f32p, f32p, f32p]
+        L.orc_q35_gate.argtypes = [f32p, f32p, C.c_int, C.c_int]
+        L.orc_indexer_pool_compress.argtypes = [f32p, f32p, u16p, f32p, f32p, C.c_int, C.c_int, C.c_float, f32p]
+        L.orc_ds_lin_q.argtypes = [f32p, u8p, u8p, C.c_int64, C.c_int64, f32p]
         L.orc_mla_decode_batch.argtypes = [u16p, u16p, C.c_int64, C.c_int64, i32p, C.c_int, C.c_int,
                                            C.c_int, C.c_int, C.c_float, f32p, C.c_int]
         L.orc_mla_decode_ranges.argtypes = [f32p, u16p, C.c_int64, C.c_int64, C.c_int, C.c_int,

@@ -271,6 +271,33 @@ def test_indexed_decode_output_matches(golden):
     assert np.array_equal(out, golden["idx_out"])
 
 
+def test_indexer_pool_rows_bit_exact(golden):
+    """The compressed indexer rows the reference built (indexer_absorb, kpool 1) from the projected
+    key/gate of each position, reproduced from the same weights and inputs."""
+    o = orc.oracle()
+    d = [int(v) for v in golden["idx_dims"]]
+    H, T, ihd, npools = d[0], d[6], d[8], d[10]
+    wk, gate, ape = (np.ascontiguousarray(golden["idx_w_" + k]) for k in ("wk", "gate", "ape"))
+    kn, knb = np.ascontiguousarray(golden["idx_w_k_norm"]), np.ascontiguousarray(golden["idx_w_k_norm_b"])
+    xs = golden["idx_x"]
+    for p_ in range(npools):
+        x = np.ascontiguousarray(xs[p_])
+        tk, tg, row = np.empty(ihd, np.float32), np.empty(ihd, np.float32), np.empty(ihd, np.float32)
+        o.orc_gemv_bf16(P(tk, f32p), H, ihd, P(x, f32p), P(wk, u16p))
+        o.orc_gemv_bf16(P(tg, f32p), H, ihd, P(x, f32p), P(gate, u16p))
+        o.orc_indexer_pool_compress(P(tk, f32p), P(tg, f32p), P(ape, u16p), P(kn, f32p), P(knb, f32p), 1, ihd, 1e-6,
+                                    P(row, f32p))
+        assert np.array_equal(row, golden["idx_pool"][p_]), p_
+
+
+def test_ds_quantised_projection_bit_exact(golden):
+    o = orc.oracle()
+    w, ws, x = (np.ascontiguousarray(golden[k]) for k in ("dsq_w", "dsq_ws", "dsq_x"))
+    out = np.empty(w.shape[0], np.float32)
+    o.orc_ds_lin_q(P(x, f32p), P(w, u8p), P(ws, u8p), w.shape[0], w.shape[1], P(out, f32p))
+    assert np.array_equal(out, golden["dsq_out"])
+
+
 @pytest.mark.skipif(orc.ref() is None, reason="reference build (oracle/_ref) not present")
 def test_live_reference_random_sweeps():
     """With the reference library present, hammer the small pieces on fresh seeds."""
