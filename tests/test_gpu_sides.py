@@ -24,8 +24,21 @@ def dp(t):
     return cl.vp(t.data_ptr())
 
 
+_keep = []
+
+
+def cu_bf16(u16):
+    t = to_bf16_cuda(u16)
+    _keep.append(t)
+    return t
+
+
 def cu(a):
-    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    """Upload and keep alive until the test module ends: the pointer handed to the library must
+    not be recycled by torch's allocator while the call's inputs are still being uploaded."""
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    _keep.append(t)
+    return t
 
 
 def test_q35_qk_prep_and_gate(attn):
@@ -54,7 +67,7 @@ def test_q35_qk_prep_and_gate(attn):
     # gate
     att = synth.normal_bf16(1, 6, (n, nh, hd))
     out = torch.empty(n, nh, hd, dtype=torch.float32, device="cuda")
-    attn.ctx.check(attn.lib.cwk_gqa_gate(attn.ctx.h, dp(to_bf16_cuda(att)), dp(a[0]), n, nh, hd, dp(out)))
+    attn.ctx.check(attn.lib.cwk_gqa_gate(attn.ctx.h, dp(cu_bf16(att)), dp(a[0]), n, nh, hd, dp(out)))
     want = synth.bf16_to_f32(att).copy()
     for t in range(n):
         o.orc_q35_gate(P(want[t], f32p), P(np.ascontiguousarray(qg[t]), f32p), nh, hd)
@@ -70,7 +83,7 @@ def test_indexer_pool_compression(attn):
     kn = (1 + synth.normal(2, 4, hd, 0.1)).astype(np.float32)
     knb = synth.normal(2, 5, hd, 0.1)
     pool = torch.empty(npools, hd, dtype=torch.float32, device="cuda")
-    attn.ctx.check(attn.lib.cwk_indexer_pool_compress(attn.ctx.h, dp(cu(tk)), dp(cu(tg)), dp(to_bf16_cuda(ape)), dp(cu(kn)),
+    attn.ctx.check(attn.lib.cwk_indexer_pool_compress(attn.ctx.h, dp(cu(tk)), dp(cu(tg)), dp(cu_bf16(ape)), dp(cu(kn)),
                                                       dp(cu(knb)), npools, kp, hd, 1e-6, dp(pool)))
     want = np.empty((npools, hd), np.float32)
     for i in range(npools):
