@@ -53,6 +53,8 @@ int cwk_reserve_stage(cwk_ctx *ctx, size_t dev_bytes, size_t pin_bytes);
 int cwk_reserve_work(cwk_ctx *ctx, size_t bytes);
 // After a stream synchronise: turn a kernel-side give-up code into CWK_ERR_STATE.
 int cwk_check_device_error(cwk_ctx *ctx);
+// Allocate the error word on first use: pinned, mapped host memory, so the host reads it without a copy.
+int cwk_ensure_err_word(cwk_ctx *ctx);
 
 // Brackets a main-kernel launch with events when profiling is on.
 struct CwkKernelTimer {

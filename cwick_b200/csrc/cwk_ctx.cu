@@ -70,12 +70,18 @@ int cwk_reserve_stage(cwk_ctx *ctx, size_t dev_bytes, size_t pin_bytes) {
     return CWK_OK;
 }
 
+int cwk_ensure_err_word(cwk_ctx *ctx) {
+    if (ctx->dev_err) return CWK_OK;
+    CWK_CUDA(ctx, cudaHostAlloc((void **)&ctx->dev_err, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
+    *ctx->dev_err = 0;
+    return CWK_OK;
+}
+
 int cwk_check_device_error(cwk_ctx *ctx) {
     if (!ctx->dev_err) return CWK_OK;
-    int code = 0;
-    CWK_CUDA(ctx, cudaMemcpy(&code, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+    const int code = *(volatile int *)ctx->dev_err;      // call after a stream synchronise
     if (code == 0) return CWK_OK;
-    cudaMemset(ctx->dev_err, 0, sizeof(int));
+    *(volatile int *)ctx->dev_err = 0;
     return cwk_fail(ctx, CWK_ERR_STATE, "a kernel gave up a bounded wait (code %d); its results are invalid", code);
 }
 
@@ -112,7 +118,7 @@ void cwk_ctx_destroy(cwk_ctx *ctx) {
     if (ctx->work) cudaFree(ctx->work);
     if (ctx->wbf16) cudaFree(ctx->wbf16);
     if (ctx->stage_pin) cudaFreeHost(ctx->stage_pin);
-    if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->dev_err) cudaFreeHost(ctx->dev_err);
     if (ctx->ticket) cudaFree(ctx->ticket);
     for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);

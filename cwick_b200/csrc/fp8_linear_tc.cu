@@ -215,9 +215,9 @@ int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const f
     if ((cols % 8) != 0 || (k % 128) != 0 || ((uintptr_t)Y % 16) != 0)
         return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 FP8 GEMM needs cols %% 8 == 0 and k %% 128 == 0");
     if (!cwk_encode_tiled_fn()) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
-    if (!ctx->dev_err) {
-        CWK_CUDA(ctx, cudaMalloc(&ctx->dev_err, sizeof(int)));
-        CWK_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
+    {
+        int es = cwk_ensure_err_word(ctx);
+        if (es != CWK_OK) return es;
     }
     // widened weights live in their own buffer (the split scratch and the prefill workspace are in use around this call)
     const size_t wbytes = (size_t)cols * k * 2;

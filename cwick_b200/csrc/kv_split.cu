@@ -201,11 +201,9 @@ int cwk_mla_decode_kv_split(cwk_ctx *ctx, const void *q, const void *cache, int6
     if (!ctx || !q || !cache || !windows || !out || rows < 0 || world <= 0 || world > MAX_WORLD || rank < 0 || rank >= world ||
         epoch == 0 || (L & 1))
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode_kv_split: bad argument (epoch counts from 1)");
-    if (!ctx->ticket || !ctx->dev_err) {
-        if (!ctx->dev_err) {
-            CWK_CUDA(ctx, cudaMalloc(&ctx->dev_err, sizeof(int)));
-            CWK_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
-        }
+    {
+        int es = cwk_ensure_err_word(ctx);
+        if (es != CWK_OK) return es;
         if (!ctx->ticket) return cwk_fail(ctx, CWK_ERR_STATE, "mla_decode_kv_split: create the exchange window first");
     }
     float *partial = nullptr;

@@ -209,6 +209,12 @@ int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_s
                       out, nullptr, n_splits);
 }
 
+static bool is_pinned_host(const void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeHost;
+}
+
 int cwk_mla_decode_host(cwk_ctx *ctx, const void *q_host, const void *cache_dev, int64_t seq_stride,
                         int64_t ld, const int32_t *kv_len_host, const int32_t *sel_host, int64_t sel_ld,
                         int B, int nh, int L, int R, float scale, void *out_host, int n_splits) {
@@ -223,22 +229,32 @@ int cwk_mla_decode_host(cwk_ctx *ctx, const void *q_host, const void *cache_dev,
     if (s != CWK_OK) return s;
     uint8_t *pin = (uint8_t *)ctx->stage_pin, *dev = (uint8_t *)ctx->stage_dev;
     const size_t o_q = 0, o_l = up(qb), o_s = o_l + up(lb), o_o = o_s + up(sb);
-    memcpy(pin + o_q, q_host, qb);
-    memcpy(pin + o_l, kv_len_host, lb);
-    if (sb) memcpy(pin + o_s, sel_host, sb);
+    // Caller buffers that are already page-locked are copied from and to directly; pageable ones
+    // go through the context's pinned staging.
+    const bool q_pinned = is_pinned_host(q_host), o_pinned = is_pinned_host(out_host);
     int max_len = 0;
     for (int i = 0; i < B; i++) max_len = std::max(max_len, (int)kv_len_host[i]);
-    // one upload covers q, lengths and the optional gather list
-    CWK_CUDA(ctx, cudaMemcpyAsync(dev, pin, o_o, cudaMemcpyHostToDevice, ctx->stream));
-    s = mla_launch(ctx, dev + o_q, cache_dev, seq_stride, ld, (const int32_t *)(dev + o_l), max_len,
+    const bool lens_imm = (B == 1);                 // one sequence: its length travels as a kernel argument
+    if (q_pinned) {
+        CWK_CUDA(ctx, cudaMemcpyAsync(dev + o_q, q_host, qb, cudaMemcpyHostToDevice, ctx->stream));
+    } else {
+        memcpy(pin + o_q, q_host, qb);
+        CWK_CUDA(ctx, cudaMemcpyAsync(dev + o_q, pin + o_q, qb, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    if (!lens_imm || sb) {
+        memcpy(pin + o_l, kv_len_host, lb);
+        if (sb) memcpy(pin + o_s, sel_host, sb);
+        CWK_CUDA(ctx, cudaMemcpyAsync(dev + o_l, pin + o_l, o_o - o_l, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    s = mla_launch(ctx, dev + o_q, cache_dev, seq_stride, ld, lens_imm ? nullptr : (const int32_t *)(dev + o_l), max_len,
                    sb ? (const int32_t *)(dev + o_s) : nullptr, sel_ld, B, nh, L, R, scale, dev + o_o,
                    nullptr, n_splits);
     if (s != CWK_OK) return s;
-    CWK_CUDA(ctx, cudaMemcpyAsync(pin + o_o, dev + o_o, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    CWK_CUDA(ctx, cudaMemcpyAsync(o_pinned ? out_host : (void *)(pin + o_o), dev + o_o, ob, cudaMemcpyDeviceToHost, ctx->stream));
     CWK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     s = cwk_check_device_error(ctx);
     if (s != CWK_OK) return s;
-    memcpy(out_host, pin + o_o, ob);
+    if (!o_pinned) memcpy(out_host, pin + o_o, ob);
     return CWK_OK;
 }
 

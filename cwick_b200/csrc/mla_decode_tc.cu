@@ -391,9 +391,9 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     if (max_kv_len <= 0) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode needs a non-empty cache");
     CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
     if (!enc) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
-    if (!ctx->dev_err) {
-        CWK_CUDA(ctx, cudaMalloc(&ctx->dev_err, sizeof(int)));
-        CWK_CUDA(ctx, cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream));
+    {
+        int es = cwk_ensure_err_word(ctx);
+        if (es != CWK_OK) return es;
     }
     CUtensorMap tm_q, tm_kv;
     {
