@@ -568,16 +568,23 @@ def side_dsa(attn, dev, stream, peak):
         out["sel"], out["nsel"] = attn.topk_select(out["sc"], n, want, False, max_n=T)
     ms_t, k_t, _ = _time_calls(attn, stream, select, n=10, warm=2)
 
+    def fused():
+        out["fsel"], out["fnsel"] = attn.dsa_select(keys, ks, q, wt, n, want, False, max_n=T)
+    ms_f, k_f, _ = _time_calls(attn, stream, fused, n=20, warm=3)
+    same = bool(torch.equal(out["fsel"][:, :want], out["sel"][:, :want]))
+
     def gather():
-        attn.mla_decode(mq, cache, out["nsel"], sel=out["sel"], scale=SCALE, max_kv_len=want + 1)
+        attn.mla_decode(mq, cache, out["fnsel"], sel=out["fsel"], scale=SCALE, max_kv_len=want + 1)
     ms_g, k_g, _ = _time_calls(attn, stream, gather, n=20, warm=3)
     idx_bytes = B * T * (hd + 4)
     gat_bytes = B * want * DK * 2
-    total_ms = ms_s + ms_t + ms_g
+    total_ms = ms_f + ms_g
     return {"ms_per_step": total_ms, "tokens_per_s": B / (total_ms / 1e3),
-            "indexer_ms": ms_s, "indexer_gbs": idx_bytes / (k_s / 1e3) / 1e9,
-            "topk_ms": ms_t, "gather_attention_ms": ms_g, "gather_gbs": gat_bytes / (k_g / 1e3) / 1e9,
-            "indexer_frac_of_measured_peak": idx_bytes / (k_s / 1e3) / 1e9 / peak,
+            "select_ms": ms_f, "select_timed_kernels_ms": k_f, "select_gbs": idx_bytes / (ms_f / 1e3) / 1e9,
+            "select_frac_of_measured_peak": idx_bytes / (ms_f / 1e3) / 1e9 / peak,
+            "select_equals_exact_route": same,
+            "exact_route_indexer_ms": ms_s, "exact_route_topk_ms": ms_t,
+            "gather_attention_ms": ms_g, "gather_gbs": gat_bytes / (k_g / 1e3) / 1e9,
             "gather_frac_of_measured_peak": gat_bytes / (k_g / 1e3) / 1e9 / peak}
 
 

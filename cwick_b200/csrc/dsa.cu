@@ -1,6 +1,7 @@
 // dsa.cu -- DSA lightning indexer: exact-order scores over FP8 keys and exact
 // top-k selection with the reference's ordering rule.
 #include "cwk_common.cuh"
+#include "topk_radix.cuh"
 
 __device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
     const uint32_t e = (b >> 3) & 15u, m = b & 7u;
@@ -66,109 +67,117 @@ __global__ void __launch_bounds__(128) indexer_scores_fp8_kernel(
 }
 
 // ---- exact top-k ---------------------------------------------------------------
-__device__ __forceinline__ uint32_t order_key(float f) {
-    const uint32_t u = __float_as_uint(f);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
-// One block of 1024 threads per sequence. Radix select (4 passes of 8 bits over
-// an order-preserving integer image of the score) finds the want-th largest
-// value exactly; an ordered compaction then writes the rows above it in index
-// order followed by the rows equal to it in index order, `want` in all.
-__global__ void __launch_bounds__(1024) topk_select_kernel(const float *sc, int64_t sc_stride,
-                                                           const int32_t *n, int want, int keep_self,
-                                                           int32_t *sel, int64_t sel_ld, int32_t *nsel, int ascending) {
-    const int b = blockIdx.x, tid = threadIdx.x;
+// One cluster of TK_CL blocks of 1024 threads per sequence. Radix select (4 passes of 8 bits over
+// an order-preserving integer image of the score) finds the want-th largest value exactly; an
+// ordered compaction then writes the rows above it in index order followed by the rows equal to
+// it in index order, `want` in all (ascending: one list in index order).
+__global__ void __cluster_dims__(TK_CL, 1, 1) __launch_bounds__(TK_THREADS, 1)
+topk_select_kernel(const float *sc, int64_t sc_stride, const int32_t *n, int want, int keep_self, int32_t *sel, int64_t sel_ld,
+                   int32_t *nsel, int ascending) {
+    cg::cluster_group cl = cg::this_cluster();
+    const unsigned rank = cl.block_rank();
+    const int b = blockIdx.y, tid = threadIdx.x;
     const int nb = n[b];
     const float *s = sc + (int64_t)b * sc_stride;
     int32_t *out = sel + (int64_t)b * sel_ld;
+    const TkSlice sl = tk_slice(nb, rank);
     if (nb <= want) {                       // the whole prefix is the top-k
-        for (int i = tid; i < nb; i += 1024) out[i] = i;
-        if (tid == 0) nsel[b] = nb;
+        for (int i = sl.begin + tid; i < sl.end; i += TK_THREADS) out[i] = i;
+        if (rank == 0 && tid == 0) nsel[b] = nb;
         return;
     }
-    __shared__ uint32_t hist[256];
-    __shared__ uint32_t s_prefix, s_remaining;
-    __shared__ int s_warp[32][3];
-    __shared__ int s_base[3];
-    uint32_t prefix = 0, mask = 0;
-    int remaining = want;                    // rank still to find inside the current bucket
-    for (int pass = 0; pass < 4; pass++) {
-        const int shift = 24 - 8 * pass;
-        for (int i = tid; i < 256; i += 1024) hist[i] = 0;
-        __syncthreads();
-        for (int i = tid; i < nb; i += 1024) {
-            const uint32_t k = order_key(s[i]);
-            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        if (tid == 0) {
-            int r = remaining;
-            int d = 255;
-            for (; d > 0; d--) {
-                const int c = (int)hist[d];
-                if (r <= c) break;
-                r -= c;
-            }
-            s_prefix = prefix | ((uint32_t)d << shift);
-            s_remaining = (uint32_t)r;
-        }
-        __syncthreads();
-        prefix = s_prefix;
-        remaining = (int)s_remaining;
-        mask |= 255u << shift;
-        __syncthreads();
-    }
-    // prefix is now the integer image of the threshold; `remaining` rows equal to
-    // it are wanted (the first ones in index order).
-    const uint32_t thr = prefix;
-    const int need_eq = remaining;
-    // count rows above the threshold (= want - need_eq by construction)
+    __shared__ TkShared sh;
+    uint32_t kc[TK_PT];
+    if (sl.cached) tk_load(s, sl.begin, sl.end, kc);
+    if (tid == 0) sh.pub = 0;
+    uint32_t thr;
+    int need_eq;
+    tk_radix_select(s, sl, kc, want, sh, thr, need_eq);
+    // thr is the integer image of the threshold; need_eq rows equal to it are wanted (the first
+    // ones in index order); want - need_eq rows lie above it.
     const int n_gt = want - need_eq;
-    if (tid == 0) { s_base[0] = 0; s_base[1] = 0; s_base[2] = 0; }
-    __syncthreads();
     const int lane = tid & 31, warp = tid >> 5;
-    for (int c0 = 0; c0 < nb; c0 += 1024) {
-        const int i = c0 + tid;
-        uint32_t k = 0;
-        bool gt = false, eq = false;
-        if (i < nb) {
-            k = order_key(s[i]);
-            gt = k > thr;
-            eq = k == thr;
+    // this block's totals, for the offsets of the blocks after it
+    {
+        unsigned long long mine = 0;
+        for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
+            if (!sl.cached) tk_load(s, c0, sl.end, kc);
+            const int i0 = c0 + tid * TK_PT;
+#pragma unroll
+            for (int j = 0; j < TK_PT; j++)
+                if (i0 + j < sl.end) mine += (kc[j] > thr ? 1ull : 0ull) + (kc[j] == thr ? (1ull << 32) : 0ull);
         }
-        const uint32_t bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
-        if (lane == 0) { s_warp[warp][0] = __popc(bg); s_warp[warp][1] = __popc(be); }
-        __syncthreads();
-        int og = s_base[0], oe = s_base[1];
-        for (int w = 0; w < warp; w++) { og += s_warp[w][0]; oe += s_warp[w][1]; }
-        og += __popc(bg & ((1u << lane) - 1u));
-        oe += __popc(be & ((1u << lane) - 1u));
-        if (!ascending) {
-            if (gt) out[og] = i;
-            if (eq && oe < need_eq) out[n_gt + oe] = i;
-        }
-        // ascending mode: one list in index order (rows above the threshold and the first need_eq ties)
-        const bool take = gt || (eq && oe < need_eq);
-        const uint32_t bt = __ballot_sync(0xffffffffu, take);
-        if (lane == 0) s_warp[warp][2] = __popc(bt);
-        __syncthreads();
-        if (ascending && take) {
-            int ot = s_base[2];
-            for (int w = 0; w < warp; w++) ot += s_warp[w][2];
-            out[ot + __popc(bt & ((1u << lane) - 1u))] = i;
-        }
-        __syncthreads();
-        if (tid == 0) {
-            int tg = 0, te = 0, tt = 0;
-            for (int w = 0; w < 32; w++) { tg += s_warp[w][0]; te += s_warp[w][1]; tt += s_warp[w][2]; }
-            s_base[0] += tg;
-            s_base[1] += te;
-            s_base[2] += tt;
-        }
-        __syncthreads();
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+        if (lane == 0 && mine) atomicAdd(&sh.pub, mine);
     }
+    cl.sync();
     if (tid == 0) {
+        unsigned long long base = 0;
+        int tbase = 0;
+        for (unsigned r = 0; r < rank; r++) {
+            const unsigned long long v = *cl.map_shared_rank(&sh.pub, r);
+            const int g = (int)(v & 0xffffffffull), e = (int)(v >> 32), eb = (int)(base >> 32);
+            tbase += g + max(0, min(e, need_eq - eb));
+            base += v;
+        }
+        sh.base = base;
+        sh.tbase = tbase;
+    }
+    __syncthreads();
+    unsigned long long running = sh.base;
+    const int eq_before_block = (int)(sh.base >> 32);
+    const int tbase = sh.tbase;
+    const int eq_quota = max(0, need_eq - eq_before_block);     // ties this block may still take
+    unsigned long long local = 0;                                // (above | equal) in this block's earlier chunks
+    for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
+        if (!sl.cached) tk_load(s, c0, sl.end, kc);
+        const int i0 = c0 + tid * TK_PT;
+        unsigned long long mine = 0;
+#pragma unroll
+        for (int j = 0; j < TK_PT; j++)
+            if (i0 + j < sl.end) mine += (kc[j] > thr ? 1ull : 0ull) + (kc[j] == thr ? (1ull << 32) : 0ull);
+        unsigned long long incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) sh.cnt[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            const unsigned long long v = sh.cnt[lane];
+            unsigned long long wi = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long t = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= o) wi += t;
+            }
+            sh.off[lane] = wi - v;
+            if (lane == 31) sh.total = wi;
+        }
+        __syncthreads();
+        const unsigned long long before = local + sh.off[warp] + incl - mine;   // within this block
+        int lg = (int)(before & 0xffffffffull), le = (int)(before >> 32);
+        const int og0 = (int)(running & 0xffffffffull), oe0 = (int)(running >> 32);
+#pragma unroll
+        for (int j = 0; j < TK_PT; j++) {
+            if (i0 + j < sl.end) {
+                const bool gt = kc[j] > thr, eq = kc[j] == thr;
+                const bool take = gt || (eq && le < eq_quota);
+                if (take) {
+                    if (ascending) out[tbase + lg + min(le, eq_quota)] = i0 + j;
+                    else if (gt) out[og0 + lg] = i0 + j;
+                    else out[n_gt + oe0 + le] = i0 + j;
+                }
+                lg += gt ? 1 : 0;
+                le += eq ? 1 : 0;
+            }
+        }
+        local += sh.total;
+    }
+    cl.sync();                              // every block's part of the list is written; nobody reads a neighbour's shared memory after this
+    if (rank == 0 && tid == 0) {
         int cnt = want;
         if (keep_self && out[cnt - 1] != nb - 1) out[cnt++] = nb - 1;
         nsel[b] = cnt;
@@ -202,7 +211,7 @@ int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int3
     (void)max_n;
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     CwkKernelTimer timer(ctx);
-    topk_select_kernel<<<B, 1024, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel, 0);
+    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel, 0);
     CWK_LAUNCH_CHECK(ctx, "topk_select_kernel");
     return CWK_OK;
 }
@@ -213,7 +222,7 @@ int cwk_ds_topk(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t 
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_topk: bad argument");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     CwkKernelTimer timer(ctx);
-    topk_select_kernel<<<B, 1024, 0, ctx->stream>>>(sc, sc_stride, n, k, 0, out, out_ld, count, 1);
+    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, k, 0, out, out_ld, count, 1);
     CWK_LAUNCH_CHECK(ctx, "topk_select_kernel<ascending>");
     return CWK_OK;
 }

@@ -1,0 +1,473 @@
+#include <algorithm>
+
+#include <cuda_fp16.h>
+
+#include "tc_common.cuh"
+#include "topk_radix.cuh"
+
+namespace {
+
+constexpr int IT_KEYS = 128, IT_HD = 128, IT_IH = 64;
+constexpr int RAW_STAGES = 4;
+constexpr int RAW_BYTES = IT_KEYS * IT_HD;              // 16384
+constexpr int A_BYTES_I = IT_KEYS * IT_HD * 2;          // 32768: two [128][64] f16 blocks
+constexpr int IT_QROWS = 2 * IT_IH;                      // q split into f16 hi and lo parts: 128 MMA columns
+constexpr int Q_BYTES_I = IT_QROWS * IT_HD * 2;         // 32768: two [128][64] f16 blocks
+constexpr int I_OFF_Q = 0;
+constexpr int I_OFF_A = Q_BYTES_I;                      // 2 buffers
+constexpr int I_OFF_RAW = I_OFF_A + 2 * A_BYTES_I;      // 4 stages
+constexpr int I_OFF_BAR = I_OFF_RAW + RAW_STAGES * RAW_BYTES;
+constexpr int I_OFF_W = I_OFF_BAR + 256;                // head weights f32 [64]
+constexpr int I_SMEM = I_OFF_W + 256 + 1024;
+constexpr int IT_THREADS = 512;                          // TMA, MMA, 2 idle | 8 converter warps | 4 epilogue warps
+constexpr int IT_CONV = 256;
+enum { IB_RAW_FULL = 0, IB_RAW_EMPTY = 4, IB_A_FULL = 8, IB_A_EMPTY = 10, IB_D_FULL = 12, IB_D_EMPTY = 14, IB_COUNT = 16 };
+
+// M x N f16 x f16 -> f32, both operands K-major
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N) {
+    return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// Four E4M3 codes -> four f16 holding code * 2^-8, exactly: an E4M3 magnitude shifted into an f16's
+// exponent and mantissa fields (s eeee mmm -> s 0eeee mmm0000000) keeps its subnormals subnormal
+// and its normals normal, with the exponent bias differing by 8. Integer ALU only.
+__device__ __forceinline__ uint2 e4m3x4_f16x4(uint32_t w) {
+    const uint32_t t0 = __byte_perm(w, 0, 0x1404);                  // code 0 -> byte 1, code 1 -> byte 3
+    const uint32_t t1 = __byte_perm(w, 0, 0x3424);                  // codes 2, 3
+    uint2 r;
+    r.x = (t0 & 0x80008000u) | ((t0 >> 1) & 0x3F803F80u);
+    r.y = (t1 & 0x80008000u) | ((t1 >> 1) & 0x3F803F80u);
+    return r;
+}
+
+struct IdxParams {
+    const float *kscale;      // [B][key_stride]
+    const uint16_t *q;        // f16 [B][128][128]: rows 0-63 the high parts of the scaled f32 queries, 64-127 the low parts
+    const float *wt;          // [B][64]: head weight * 2^8 / the head's query scale
+    const int32_t *n;         // [B]
+    float *sc;                // [B][key_stride]
+    int64_t key_stride;
+    int *err;
+};
+
+__global__ void __launch_bounds__(IT_THREADS, 1)
+indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - raw);
+    const uint32_t bar0 = base + I_OFF_BAR;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + I_OFF_BAR + 8 * IB_COUNT + 8);
+    float *s_w = reinterpret_cast<float *>(sm + I_OFF_W);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // this block's tiles: a contiguous range of ONE sequence (so q and the weights are loaded once)
+    const int blocks_per_seq = gridDim.x;
+    const int b = blockIdx.y;
+    const int nb = p.n[b];
+    const int ntile = (nb + IT_KEYS - 1) / IT_KEYS;
+    const int t_begin = (int)((int64_t)ntile * blockIdx.x / blocks_per_seq);
+    const int t_end = (int)((int64_t)ntile * (blockIdx.x + 1) / blocks_per_seq);
+    const int nt = t_end - t_begin;
+    if (nt <= 0) return;
+
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_keys) : "memory");
+        for (int i = 0; i < IB_COUNT; i++) {
+            uint32_t cnt = 1u;
+            if (i >= IB_RAW_EMPTY && i < IB_A_EMPTY) cnt = IT_CONV;   // raw_empty, a_full: every converter thread
+            if (i >= IB_D_EMPTY) cnt = 128u;                          // d_empty: every epilogue thread
+            mbar_init(bar(i), cnt);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // q of this sequence: [128][128] f16 -> two swizzled [128][64] blocks (plain loads, once per block)
+    for (int i = tid; i < IT_QROWS * 16; i += IT_THREADS) {
+        const int r = i >> 4, c = i & 15;                      // 16-byte chunk c of row r
+        const uint4 v = *reinterpret_cast<const uint4 *>(p.q + ((int64_t)b * IT_QROWS + r) * IT_HD + c * 8);
+        *reinterpret_cast<uint4 *>(sm + I_OFF_Q + (c >> 3) * (IT_QROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+    }
+    if (tid < IT_IH) s_w[tid] = p.wt[(int64_t)b * IT_IH + tid];
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int i = 0; i < nt && ok; i++) {
+                const int r = i % RAW_STAGES, use = i / RAW_STAGES;
+                ok = mbar_wait(bar(IB_RAW_EMPTY + r), (uint32_t)((use & 1) ^ 1), p.err, 801);
+                if (!ok) break;
+                mbar_expect_tx(bar(IB_RAW_FULL + r), RAW_BYTES);
+                tma_load_2d(base + I_OFF_RAW + r * RAW_BYTES, &tm_keys, 0,
+                            (int)((int64_t)b * p.key_stride + (int64_t)(t_begin + i) * IT_KEYS), bar(IB_RAW_FULL + r));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t ID = idesc_f16(128, IT_QROWS);
+            bool ok = true;
+            for (int i = 0; i < nt && ok; i++) {
+                const int ab = i & 1, use = i >> 1;
+                ok = mbar_wait(bar(IB_A_FULL + ab), (uint32_t)(use & 1), p.err, 803);
+                if (ok) ok = mbar_wait(bar(IB_D_EMPTY + ab), (uint32_t)((use & 1) ^ 1), p.err, 804);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a0 = base + I_OFF_A + ab * A_BYTES_I, b0 = base + I_OFF_Q;
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++)
+                    umma_bf16(tmem + ab * 128, smem_desc(a0 + (ks >> 2) * (IT_KEYS * 128) + (ks & 3) * 32, 16, 1024),
+                              smem_desc(b0 + (ks >> 2) * (IT_QROWS * 128) + (ks & 3) * 32, 16, 1024), ID, ks != 0);
+                umma_commit(bar(IB_A_EMPTY + ab));
+                umma_commit(bar(IB_D_FULL + ab));
+            }
+        }
+    } else if (warp >= 4 && warp < 12) {
+        // ---------------- converters: raw E4M3 tile -> f16 K-major blocks
+        const int ct = tid - 128;
+        bool ok = true;
+        for (int i = 0; i < nt; i++) {
+            const int r = i % RAW_STAGES, ruse = i / RAW_STAGES, ab = i & 1, ause = i >> 1;
+            ok = mbar_wait(bar(IB_RAW_FULL + r), (uint32_t)(ruse & 1), p.err, 805);
+            if (ok) ok = mbar_wait(bar(IB_A_EMPTY + ab), (uint32_t)((ause & 1) ^ 1), p.err, 806);
+            if (!ok) break;
+            const uint8_t *src = sm + I_OFF_RAW + r * RAW_BYTES;
+            uint8_t *dst = sm + I_OFF_A + ab * A_BYTES_I;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int row = j * 32 + (ct >> 3), ch = ct & 7;          // 16 codes = dims ch*16 .. +15
+                const uint4 v = *reinterpret_cast<const uint4 *>(src + row * 128 + ch * 16);
+                const uint2 c0 = e4m3x4_f16x4(v.x), c1 = e4m3x4_f16x4(v.y), c2 = e4m3x4_f16x4(v.z), c3 = e4m3x4_f16x4(v.w);
+                const uint4 lo = make_uint4(c0.x, c0.y, c1.x, c1.y), hi = make_uint4(c2.x, c2.y, c3.x, c3.y);
+                uint8_t *blk = dst + (ch >> 2) * (IT_KEYS * 128) + row * 128;       // dims 0-63 | 64-127
+                const int k0 = (ch & 3) * 2;
+                // the threads of the second block store their halves in the other order, so that the eight
+                // threads of a row hit eight different 16-byte bank groups in each store
+                const int sw = ch >> 2;
+                *reinterpret_cast<uint4 *>(blk + (((k0 + sw) ^ (row & 7)) << 4)) = sw ? hi : lo;
+                *reinterpret_cast<uint4 *>(blk + (((k0 + 1 - sw) ^ (row & 7)) << 4)) = sw ? lo : hi;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar(IB_A_FULL + ab));
+            mbar_arrive(bar(IB_RAW_EMPTY + r));
+        }
+    } else if (warp >= 12) {
+        // ---------------- epilogue: hi + lo, ReLU, head weights, key scale
+        const int q4 = warp & 3;
+        const int row = q4 * 32 + lane;
+        const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
+        bool ok = true;
+        for (int i = 0; i < nt; i++) {
+            const int ab = i & 1, use = i >> 1;
+            ok = mbar_wait(bar(IB_D_FULL + ab), (uint32_t)(use & 1), p.err, 807);
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t key = (int64_t)(t_begin + i) * IT_KEYS + row;
+            const float ksc = key < nb ? p.kscale[(int64_t)b * p.key_stride + key] : 0.f;
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t v[16], u[16];
+                TMEM_LD16(v, 0, tlane + ab * 128 + c * 16);            // codes . q_hi
+                TMEM_LD16(u, 0, tlane + ab * 128 + 64 + c * 16);       // codes . q_lo
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    acc0 = fmaf(fmaxf(__uint_as_float(v[j]) + __uint_as_float(u[j]), 0.f), s_w[c * 16 + j], acc0);
+                    acc1 = fmaf(fmaxf(__uint_as_float(v[j + 1]) + __uint_as_float(u[j + 1]), 0.f), s_w[c * 16 + j + 1], acc1);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(IB_D_EMPTY + ab));
+            if (key < nb) p.sc[(int64_t)b * p.key_stride + key] = (acc0 + acc1) * ksc;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    }
+}
+
+__device__ __forceinline__ float e4m3_to_f32_i(uint32_t b) {
+    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    float mag;
+    if (e == 0) mag = (float)m * 0.001953125f;
+    else if (e == 15 && m == 7) mag = __int_as_float(0x7fc00000);
+    else mag = __uint_as_float(((e + 120u) << 23) | (m << 20));
+    return (b & 0x80u) ? -mag : mag;
+}
+
+// One cluster per sequence: the row's largest approximate score, the exact want-th largest
+// approximate score tau, then the classification of every key: certainly selected (refined =
+// +inf), certainly not (refined = -inf), or in the band |a - tau| <= eps, whose indices are appended
+// to band_list (band_count zeroed by the caller).
+__global__ void __cluster_dims__(TK_CL, 1, 1) __launch_bounds__(TK_THREADS, 1)
+band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int want, float *refined, int32_t *band_list,
+                     int32_t *band_count) {
+    cg::cluster_group cl = cg::this_cluster();
+    const unsigned rank = cl.block_rank();
+    const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    const int nb = n[b];
+    const float *s = approx + (int64_t)b * stride;
+    float *f = refined + (int64_t)b * stride;
+    const TkSlice sl = tk_slice(nb, rank);
+    if (nb <= want) {                         // everything is selected: any finite value will do
+        for (int i = sl.begin + tid; i < sl.end; i += TK_THREADS) f[i] = s[i];
+        return;
+    }
+    __shared__ TkShared sh;
+    __shared__ float red[32];
+    uint32_t kc[TK_PT];
+    if (sl.cached) tk_load(s, sl.begin, sl.end, kc);
+    // largest score of this block's slice (scores are sums of non-negative terms)
+    float m = 0.f;
+    for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
+        if (!sl.cached) tk_load(s, c0, sl.end, kc);
+        const int i0 = c0 + tid * TK_PT;
+#pragma unroll
+        for (int j = 0; j < TK_PT; j++)
+            if (i0 + j < sl.end) m = fmaxf(m, fabsf(order_key_inverse(kc[j])));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[tid >> 5] = m;
+    __syncthreads();
+    if (tid < 32) {
+        m = red[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) sh.fmax = m;
+    }
+    uint32_t prefix;
+    int remaining;
+    tk_radix_select(s, sl, kc, want, sh, prefix, remaining);       // its cluster barriers also publish fmax
+    m = 0.f;
+#pragma unroll
+    for (unsigned r = 0; r < TK_CL; r++) m = fmaxf(m, *cl.map_shared_rank(&sh.fmax, r));
+    const float tau = order_key_inverse(prefix);
+    const float eps = 2.0f * 0.001953125f * m;              // 2 * delta, delta = 2^-9 of the row's largest score
+    const float hi = tau + eps, lo = tau - eps;
+    int32_t *list = band_list + (int64_t)b * stride;
+    for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
+        if (!sl.cached) tk_load(s, c0, sl.end, kc);
+        const int i0 = c0 + tid * TK_PT;
+        uint32_t inb = 0;
+        float v[TK_PT];
+#pragma unroll
+        for (int j = 0; j < TK_PT; j++) {
+            const float a = order_key_inverse(kc[j]);
+            v[j] = a > hi ? INFINITY : -INFINITY;
+            if (i0 + j < sl.end && !(a > hi) && !(a < lo)) inb |= 1u << j;     // NaN lands here too and is re-scored exactly
+        }
+        if (i0 + TK_PT <= sl.end && (reinterpret_cast<uintptr_t>(f + i0) & 15u) == 0) {
+            *reinterpret_cast<float4 *>(f + i0) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4 *>(f + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < TK_PT; j++)
+                if (i0 + j < sl.end) f[i0 + j] = v[j];
+        }
+        // band entries: one global atomic per warp (the list's order does not matter; the rescoring
+        // kernel overwrites refined[] at these indices)
+        const int mine = __popc(inb);
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        const int wtot = __shfl_sync(0xffffffffu, incl, 31);
+        int at = 0;
+        if (lane == 31 && wtot) at = atomicAdd(band_count + b, wtot);
+        at = __shfl_sync(0xffffffffu, at, 31) + incl - mine;
+#pragma unroll
+        for (int j = 0; j < TK_PT; j++)
+            if (inb & (1u << j)) list[at++] = i0 + j;
+    }
+    cl.sync();                              // keep this block's shared memory alive until every neighbour has read fmax
+}
+
+// Exact scores (the reference's order: src/attention.c:573-582 with dot_f32's grouping, :249-258)
+// of the keys in the band. Eight lanes share a key: each computes the dots of eight heads in the
+// reference's order, and one lane then adds the 64 weighted terms in head order.
+constexpr int RS_QLD = IT_HD + 4;                            // padded q rows: the eight heads of a key group hit different banks
+constexpr int RS_SMEM = (IT_IH * RS_QLD + IT_IH + 32 * IT_IH) * 4;
+__global__ void __launch_bounds__(256) band_rescore_kernel(const uint8_t *keys, const float *kscale, int64_t key_stride,
+                                                           const float *q, const float *wt, const int32_t *band_list,
+                                                           const int32_t *band_count, float *refined) {
+    extern __shared__ __align__(16) float rs_sm[];
+    float *sq = rs_sm, *sw = rs_sm + IT_IH * RS_QLD, *sp = sw + IT_IH;
+    const int b = blockIdx.y, tid = threadIdx.x;
+    const int cnt = band_count[b];
+    if ((int)blockIdx.x * 32 >= cnt) return;
+    for (int i = tid; i < IT_IH * (IT_HD / 4); i += 256) {
+        const int h = i / (IT_HD / 4), c = i % (IT_HD / 4);
+        *reinterpret_cast<float4 *>(sq + h * RS_QLD + c * 4) = __ldg(reinterpret_cast<const float4 *>(q + ((int64_t)b * IT_IH + h) * IT_HD) + c);
+    }
+    if (tid < IT_IH) sw[tid] = wt[(int64_t)b * IT_IH + tid];
+    __syncthreads();
+    const int g = tid >> 3, l8 = tid & 7;
+    float *pg = sp + g * IT_IH;
+    for (int k = blockIdx.x * 32 + g; k < cnt; k += gridDim.x * 32) {
+        const int c = band_list[(int64_t)b * key_stride + k];
+        const uint8_t *kr = keys + ((int64_t)b * key_stride + c) * IT_HD;
+        const float s = kscale[(int64_t)b * key_stride + c];
+        float kf[IT_HD];
+#pragma unroll
+        for (int ch = 0; ch < IT_HD / 16; ch++) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(kr) + ch);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) kf[ch * 16 + kk * 4 + j] = __fmul_rn(e4m3_to_f32_i((w[kk] >> (8 * j)) & 0xffu), s);
+        }
+        for (int j = 0; j < 8; j++) {
+            const int h = j * 8 + l8;
+            const float4 *qh = reinterpret_cast<const float4 *>(sq + h * RS_QLD);
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < IT_HD / 4; i++) {
+                const float4 qv = qh[i];
+                s0 = __fadd_rn(s0, __fmul_rn(kf[4 * i + 0], qv.x));
+                s1 = __fadd_rn(s1, __fmul_rn(kf[4 * i + 1], qv.y));
+                s2 = __fadd_rn(s2, __fmul_rn(kf[4 * i + 2], qv.z));
+                s3 = __fadd_rn(s3, __fmul_rn(kf[4 * i + 3], qv.w));
+            }
+            float d = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
+            if (d < 0.f) d = 0.f;
+            pg[h] = __fmul_rn(d, sw[h]);
+        }
+        __syncwarp();
+        if (l8 == 0) {
+            float total = 0.f;
+#pragma unroll 8
+            for (int h = 0; h < IT_IH; h++) total = __fadd_rn(total, pg[h]);
+            refined[(int64_t)b * key_stride + c] = total;
+        }
+        __syncwarp();
+    }
+}
+
+// q f32 [B][64][128] -> f16 [B][128][128]: one warp per head. The head is scaled by a power of two
+// that brings its largest magnitude into [2^13, 2^14); rows 0-63 hold the f16 roundings, rows
+// 64-127 the f16 roundings of the remainders (q * scale = hi + lo up to 2^-22 of the head's
+// largest element). wt_out = head weight * 2^8 / scale: the 2^8 undoes the keys' 2^-8.
+__global__ void __launch_bounds__(256) split_q_kernel(const float *q, const float *wt, uint16_t *y, float *wt_out, int B) {
+    const int gw = (int)((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+    if (gw >= B * IT_IH) return;
+    const int b = gw / IT_IH, h = gw % IT_IH;
+    const float4 v = *reinterpret_cast<const float4 *>(q + (int64_t)gw * IT_HD + lane * 4);
+    float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float scale = 1.f, inv = 1.f;
+    if (m > 0.f && m < INFINITY) {
+        const int e = (int)((__float_as_uint(m) >> 23) & 255u) - 127;     // floor(log2 m) for normal m
+        const int sh = max(-100, min(100, 13 - e));
+        scale = __uint_as_float((uint32_t)(127 + sh) << 23);
+        inv = __uint_as_float((uint32_t)(127 - sh) << 23);
+    }
+    const float x[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
+    uint16_t hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const __half hh = __float2half_rn(x[j]);
+        hi[j] = __half_as_ushort(hh);
+        lo[j] = __half_as_ushort(__float2half_rn(x[j] - __half2float(hh)));
+    }
+    uint16_t *yh = y + ((int64_t)b * IT_QROWS + h) * IT_HD + lane * 4;
+    uint16_t *yl = y + ((int64_t)b * IT_QROWS + IT_IH + h) * IT_HD + lane * 4;
+    *reinterpret_cast<uint2 *>(yh) = make_uint2(hi[0] | ((uint32_t)hi[1] << 16), hi[2] | ((uint32_t)hi[3] << 16));
+    *reinterpret_cast<uint2 *>(yl) = make_uint2(lo[0] | ((uint32_t)lo[1] << 16), lo[2] | ((uint32_t)lo[3] << 16));
+    if (lane == 0) wt_out[gw] = wt[gw] * 256.f * inv;
+}
+
+}  // namespace
+
+extern "C" int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int max_n, int B, int want,
+                               int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel);
+extern "C" int cwk_indexer_scores_fp8(cwk_ctx *ctx, const void *keys, const float *kscale, int64_t key_stride, const float *q,
+                                      const float *wt, const int32_t *n, int max_n, int B, int ih, int hd, float *sc);
+
+// The fused DSA selection: approximate scores on tensor cores, exact top-`want`.
+extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscale, int64_t key_stride, const float *q,
+                              const float *wt, const int32_t *n, int max_n, int B, int ih, int hd, int want, int keep_self,
+                              int32_t *sel, int64_t sel_ld, int32_t *nsel, float *scores_out) {
+    if (!ctx || !keys || !kscale || !q || !wt || !n || !sel || !nsel || B <= 0 || want <= 0 || max_n < 0 || sel_ld < want + 1)
+        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "dsa_select: bad argument");
+    CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (max_n == 0) {
+        CWK_CUDA(ctx, cudaMemsetAsync(nsel, 0, (size_t)B * sizeof(int32_t), ctx->stream));
+        return CWK_OK;
+    }
+    const bool tc_ok = ih == IT_IH && hd == IT_HD && ((uintptr_t)keys % 16) == 0 && cwk_encode_tiled_fn() != nullptr &&
+                       ctx->force_mla_path != 0 && ctx->force_mla_path != 1;
+    // workspace: approx f32 [B][stride], refined f32 [B][stride], band list int32 [B][stride], q f16 hi|lo,
+    // scaled head weights, band counts
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t b_sc = up((size_t)B * key_stride * 4), b_q = up((size_t)B * 2 * ih * hd * 2), b_w = up((size_t)B * ih * 4);
+    int s = cwk_reserve_work(ctx, 3 * b_sc + b_q + b_w + up((size_t)B * 4));
+    if (s != CWK_OK) return s;
+    uint8_t *w = (uint8_t *)ctx->work;
+    float *approx = (float *)w, *refined = (float *)(w + b_sc);
+    int32_t *band_list = (int32_t *)(w + 2 * b_sc);
+    uint16_t *qb = (uint16_t *)(w + 3 * b_sc);
+    float *wtx = (float *)(w + 3 * b_sc + b_q);
+    int32_t *band = (int32_t *)(w + 3 * b_sc + b_q + b_w);
+    if (!tc_ok) {
+        // shapes the tensor-core path is not built for: exact scores for every key
+        s = cwk_indexer_scores_fp8(ctx, keys, kscale, key_stride, q, wt, n, max_n, B, ih, hd, scores_out ? scores_out : approx);
+        if (s != CWK_OK) return s;
+        return cwk_topk_select(ctx, scores_out ? scores_out : approx, key_stride, n, max_n, B, want, keep_self, sel, sel_ld, nsel);
+    }
+    s = cwk_ensure_err_word(ctx);
+    if (s != CWK_OK) return s;
+    split_q_kernel<<<(B * ih * 32 + 255) / 256, 256, 0, ctx->stream>>>(q, wt, qb, wtx, B);
+    CWK_LAUNCH_CHECK(ctx, "split_q_kernel");
+    CUtensorMap tm_keys;
+    {
+        CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)B * (cuuint64_t)key_stride};
+        cuuint64_t strides[1] = {(cuuint64_t)hd};
+        cuuint32_t box[2] = {(cuuint32_t)hd, IT_KEYS};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&tm_keys, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(keys), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(keys) failed");
+    }
+    static bool attr_set[16] = {false};
+    if (!attr_set[ctx->device & 15]) {
+        CWK_CUDA(ctx, cudaFuncSetAttribute(indexer_scores_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, I_SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(band_rescore_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_SMEM));
+        attr_set[ctx->device & 15] = true;
+    }
+    IdxParams p;
+    p.kscale = kscale; p.q = qb; p.wt = wtx; p.n = n; p.sc = approx; p.key_stride = key_stride; p.err = ctx->dev_err;
+    const int tiles = (max_n + IT_KEYS - 1) / IT_KEYS;
+    const int bps = std::max(1, std::min(tiles, ctx->sm_count / B));
+    {
+        CwkKernelTimer timer(ctx);
+        indexer_scores_tc_kernel<<<dim3(bps, B), IT_THREADS, I_SMEM, ctx->stream>>>(tm_keys, p);
+        CWK_LAUNCH_CHECK(ctx, "indexer_scores_tc_kernel");
+    }
+    CWK_CUDA(ctx, cudaMemsetAsync(band, 0, (size_t)B * sizeof(int32_t), ctx->stream));
+    band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band);
+    CWK_LAUNCH_CHECK(ctx, "band_classify_kernel");
+    band_rescore_kernel<<<dim3(32, B), 256, RS_SMEM, ctx->stream>>>((const uint8_t *)keys, kscale, key_stride, q, wt, band_list, band,
+                                                                   refined);
+    CWK_LAUNCH_CHECK(ctx, "band_rescore_kernel");
+    if (scores_out) CWK_CUDA(ctx, cudaMemcpyAsync(scores_out, refined, (size_t)B * key_stride * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    return cwk_topk_select(ctx, refined, key_stride, n, max_n, B, want, keep_self, sel, sel_ld, nsel);
+}

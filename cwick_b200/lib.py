@@ -40,6 +40,7 @@ SIGNATURES = {
     "cwk_mla_decode_kv_split": (i32, [vp, vp, vp, i64, i64, i32, i32, i32, f32, C.POINTER(vp), i32, i32, C.c_uint32, vp]),
     "cwk_indexer_scores_fp8": (i32, [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, vp]),
     "cwk_topk_select": (i32, [vp, vp, i64, vp, i32, i32, i32, i32, vp, i64, vp]),
+    "cwk_dsa_select": (i32, [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, i64, vp, vp]),
     "cwk_gqa_decode": (i32, [vp, vp, vp, vp, i64, vp, i32, i32, i32, i32, i32, f32, vp, i32]),
     "cwk_gqa_prefill": (i32, [vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, vp]),
     "cwk_gqa_qk_prep": (i32, [vp, vp, vp, vp, vp, vp, f32, i32, C.c_double, i64, i32, i32, i32, i32, vp, vp, vp]),

@@ -117,6 +117,22 @@ class Attn:
                                                 1 if keep_self else 0, _p(sel), want + 1, _p(nsel)))
         return sel, nsel
 
+    def dsa_select(self, keys, kscale, q, wt, n, want, keep_self=False, max_n=None, return_scores=False):
+        """Indexer scores and exact top-`want` in one call (tensor-core scores, exact re-scoring around
+        the threshold). Returns (sel int32 [B][want+1], nsel int32 [B]) and, on request, the refined
+        score array."""
+        B, T, hd = keys.shape
+        ih = q.shape[1]
+        if max_n is None:
+            max_n = int(n.max().item())
+        sel = torch.full((B, want + 1), -1, dtype=torch.int32, device=keys.device)
+        nsel = torch.zeros(B, dtype=torch.int32, device=keys.device)
+        sc = torch.zeros(B, T, dtype=torch.float32, device=keys.device) if return_scores else None
+        self.ctx.check(self.lib.cwk_dsa_select(self.ctx.h, _p(keys), _p(kscale), T, _p(q), _p(wt), _p(n), max_n, B, ih, hd,
+                                               want, 1 if keep_self else 0, _p(sel), want + 1, _p(nsel),
+                                               _p(sc) if sc is not None else None))
+        return (sel, nsel, sc) if return_scores else (sel, nsel)
+
     # ---- GQA -----------------------------------------------------------------
     def gqa_decode(self, q, K, V, kv_len, scale=None, max_kv_len=None, n_splits=0):
         """q [B][nh][hd]; K,V [B][T][nkv][hd] bf16; kv_len int32 [B]."""

@@ -197,6 +197,25 @@ CWK_API int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, co
                     int max_n, int B, int want, int keep_self, int32_t *sel,
                     int64_t sel_ld, int32_t *nsel);
 
+/* Scores and selection in one call: the selection of indexer_select
+ * (src/attention.c:548-622) without an exact score for every key. A tensor-core
+ * pass scores every key approximately (the E4M3 codes widened exactly to F16,
+ * the F32 query split into two F16 parts, F32 accumulation), a radix select finds the
+ * approximate want-th largest score tau, and only the keys whose approximate
+ * score lies within 2^-8 of the row's largest score around tau are re-scored in
+ * the reference's exact order; keys above the band are certainly selected, keys
+ * below it certainly not, so `sel` and `nsel` equal what cwk_indexer_scores_fp8
+ * followed by cwk_topk_select returns, as long as the tensor-core score of every
+ * key is within 2^-9 of the row's largest score of its exact score (the
+ * contraction's worst case on finite inputs is some 2^-12). Arguments as for
+ * those two calls; ih = 64 and hd = 128 use the tensor cores, other shapes take
+ * the exact route. scores_out (optional, f32 [B][key_stride]) receives the
+ * refined array: the exact score inside the band, +inf above it, -inf below. */
+CWK_API int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscale, int64_t key_stride,
+                   const float *q, const float *wt, const int32_t *n, int max_n, int B, int ih,
+                   int hd, int want, int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel,
+                   float *scores_out);
+
 /* ---- Qwen3.5-style GQA -----------------------------------------------------
  * Single-query decode. Replaces dec_scores / dec_softmax / dec_out_slices and
  * the slice sum (src/q35_model.c:1460-1518, :1656-1712).

@@ -126,3 +126,92 @@ def test_config4_pipeline_full_size_one_sequence(attn):
         ref = sel[b, :want].cpu().numpy().astype(np.int64)
         w = orc.mla_decode(synth.bf16_to_f32(mq[b]), cache[b], want, L, R, 1 / math.sqrt(192.0), sel=ref)
         close(bf16_to_np(got[b]), w)
+
+
+def _select_both_ways(attn, codes, ks, q, wt, lens, want, keep_self):
+    cu = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    dk, dks, dq, dw, dn = cu(codes), cu(ks), cu(q), cu(wt), cu(lens)
+    sel, nsel, refined = attn.dsa_select(dk, dks, dq, dw, dn, want, keep_self, return_scores=True)
+    torch.cuda.synchronize()
+    return sel.cpu().numpy(), nsel.cpu().numpy(), refined.cpu().numpy()
+
+
+@pytest.mark.parametrize("B,T,want,keep_self,exact_q", [(2, 20000, 2048, False, True), (3, 9001, 512, True, False),
+                                                        (8, 4096, 2048, False, False), (1, 300, 2048, True, True)])
+def test_fused_selection_equals_oracle_selection(attn, B, T, want, keep_self, exact_q):
+    """Tensor-core scores + guard band + exact re-scoring: the index lists equal the oracle's
+    selection over the oracle's exact scores, order included. Ragged lengths, n <= want, queries
+    that are and are not exactly representable in BF16, and planted duplicate keys (exact ties on
+    the threshold) are covered."""
+    codes, ks, q, wt = make_index_inputs(300 + T, B, T)
+    if not exact_q:
+        q = (q + synth.normal(5 + T, 9, q.size).reshape(q.shape) * np.float32(1e-3)).astype(np.float32)
+    # duplicate keys: a run of identical rows gives exactly equal scores
+    codes[0, 10:40] = codes[0, 7]
+    ks[0, 10:40] = ks[0, 7]
+    lens = np.array([T - 37 * b for b in range(B)], np.int32)
+    if B >= 3:
+        lens[2] = min(T, want)                 # whole prefix
+    sel, nsel, refined = _select_both_ways(attn, codes, ks, q, wt, lens, want, keep_self)
+    sc = oracle_scores(codes, ks, q, wt)
+    for b in range(B):
+        nb = int(lens[b])
+        ref = oracle_select(sc[b], nb, want, keep_self)
+        if ref is None:
+            assert nsel[b] == nb and np.array_equal(sel[b, :nb], np.arange(nb))
+            continue
+        assert nsel[b] == ref.size
+        assert np.array_equal(sel[b, :nsel[b]].astype(np.int64), ref)
+        # inside the band the refined scores are the oracle's, bit for bit
+        r = refined[b, :nb]
+        band = np.isfinite(r)
+        assert band.sum() < nb // 4 + 64
+        assert np.array_equal(r[band].view(np.uint32), sc[b, :nb][band].view(np.uint32))
+
+
+def test_fused_selection_threshold_tie_run(attn):
+    """The want-th largest score is shared by a run of identical keys: the tie is broken by index,
+    as the reference does (src/attention.c:592-598)."""
+    B, T, want = 1, 6000, 1000
+    codes, ks, q, wt = make_index_inputs(77, B, T)
+    sc = oracle_scores(codes, ks, q, wt)
+    order = np.argsort(-sc[0], kind="stable")
+    pivot = order[want - 5]                    # a key just inside the top set
+    dup = np.arange(2000, 2040)
+    codes[0, dup] = codes[0, pivot]
+    ks[0, dup] = ks[0, pivot]
+    lens = np.array([T], np.int32)
+    sel, nsel, _ = _select_both_ways(attn, codes, ks, q, wt, lens, want, False)
+    sc = oracle_scores(codes, ks, q, wt)
+    ref = oracle_select(sc[0], T, want, False)
+    assert nsel[0] == ref.size and np.array_equal(sel[0, :nsel[0]].astype(np.int64), ref)
+
+
+def test_fused_selection_config4_size(attn):
+    """BASELINE config 4 dimensions on two sequences: 65536 keys, top 2048."""
+    B, T, want = 2, 65536, 2048
+    codes, ks, q, wt = make_index_inputs(synth.DEFAULT_SEED, B, T)
+    lens = np.array([T, T - 1], np.int32)
+    sel, nsel, refined = _select_both_ways(attn, codes, ks, q, wt, lens, want, False)
+    sc = oracle_scores(codes, ks, q, wt)
+    for b in range(B):
+        ref = oracle_select(sc[b], int(lens[b]), want, False)
+        assert np.array_equal(sel[b, :want].astype(np.int64), ref)
+    assert np.isfinite(refined[0]).sum() < 4096
+
+
+@pytest.mark.parametrize("T,want", [(150000, 2048), (65537, 1), (70001, 65000)])
+def test_topk_rows_longer_than_the_register_slice(attn, T, want):
+    """Rows above 65536 scores are re-read chunk by chunk instead of held in registers; odd lengths
+    exercise the unaligned tail loads."""
+    B = 2
+    rng = np.random.default_rng(T)
+    sc = np.abs(rng.standard_normal((B, T))).astype(np.float32)
+    sc[1, 1000:60000:7] = sc[1, 3]
+    lens = np.array([T, T - 3], np.int32)
+    sel, nsel = attn.topk_select(torch.from_numpy(sc).cuda(), torch.from_numpy(lens).cuda(), want, True)
+    sel, nsel = sel.cpu().numpy(), nsel.cpu().numpy()
+    for b in range(B):
+        ref = oracle_select(sc[b], int(lens[b]), want, True)
+        assert nsel[b] == ref.size
+        assert np.array_equal(sel[b, :nsel[b]].astype(np.int64), ref)
