@@ -42,8 +42,8 @@ __device__ __forceinline__ uint2 e4m3x4_f16x4(uint32_t w) {
 
 struct IdxParams {
     const float *kscale;      // [B][key_stride]
-    const uint16_t *q;        // f16 [B][128][128]: rows 0-63 the high parts of the scaled f32 queries, 64-127 the low parts
-    const float *wt;          // [B][64]: head weight * 2^8 / the head's query scale
+    const uint16_t *q;        // f16 [B][128][128]: rows 0-63 the high parts of q * |head weight| * scale, 64-127 the low parts
+    const uint32_t *meta;     // [B][4]: f32 2^8 / scale, sign mask of head weights 0-31, of 32-63, unused
     const int32_t *n;         // [B]
     float *sc;                // [B][key_stride]
     int64_t key_stride;
@@ -59,7 +59,6 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
     const uint32_t bar0 = base + I_OFF_BAR;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + I_OFF_BAR + 8 * IB_COUNT + 8);
-    float *s_w = reinterpret_cast<float *>(sm + I_OFF_W);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // this block's tiles: a contiguous range of ONE sequence (so q and the weights are loaded once)
@@ -92,7 +91,6 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
         const uint4 v = *reinterpret_cast<const uint4 *>(p.q + ((int64_t)b * IT_QROWS + r) * IT_HD + c * 8);
         *reinterpret_cast<uint4 *>(sm + I_OFF_Q + (c >> 3) * (IT_QROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
     }
-    if (tid < IT_IH) s_w[tid] = p.wt[(int64_t)b * IT_IH + tid];
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
     __syncthreads();
@@ -121,11 +119,11 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
                 if (ok) ok = mbar_wait(bar(IB_D_EMPTY + ab), (uint32_t)((use & 1) ^ 1), p.err, 804);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a0 = base + I_OFF_A + ab * A_BYTES_I, b0 = base + I_OFF_Q;
+                const uint64_t da = smem_desc(base + I_OFF_A + ab * A_BYTES_I, 16, 1024), db = smem_desc(base + I_OFF_Q, 16, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)
-                    umma_bf16(tmem + ab * 128, smem_desc(a0 + (ks >> 2) * (IT_KEYS * 128) + (ks & 3) * 32, 16, 1024),
-                              smem_desc(b0 + (ks >> 2) * (IT_QROWS * 128) + (ks & 3) * 32, 16, 1024), ID, ks != 0);
+                    umma_bf16(tmem + ab * 128, da + (uint64_t)(((ks >> 2) * (IT_KEYS * 128) + (ks & 3) * 32) >> 4),
+                              db + (uint64_t)(((ks >> 2) * (IT_QROWS * 128) + (ks & 3) * 32) >> 4), ID, ks != 0);
                 umma_commit(bar(IB_A_EMPTY + ab));
                 umma_commit(bar(IB_D_FULL + ab));
             }
@@ -160,10 +158,13 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
             mbar_arrive(bar(IB_RAW_EMPTY + r));
         }
     } else if (warp >= 12) {
-        // ---------------- epilogue: hi + lo, ReLU, head weights, key scale
+        // ---------------- epilogue: hi + lo, ReLU, signed head sum, key scale
         const int q4 = warp & 3;
         const int row = q4 * 32 + lane;
         const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
+        const float unscale = __uint_as_float(p.meta[b * 4]);
+        const uint32_t neg[2] = {p.meta[b * 4 + 1], p.meta[b * 4 + 2]};
+        const bool any_neg = (neg[0] | neg[1]) != 0;
         bool ok = true;
         for (int i = 0; i < nt; i++) {
             const int ab = i & 1, use = i >> 1;
@@ -174,20 +175,32 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
             const float ksc = key < nb ? p.kscale[(int64_t)b * p.key_stride + key] : 0.f;
             float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[16], u[16];
-                TMEM_LD16(v, 0, tlane + ab * 128 + c * 16);            // codes . q_hi
-                TMEM_LD16(u, 0, tlane + ab * 128 + 64 + c * 16);       // codes . q_lo
+            for (int c = 0; c < 2; c++) {
+                uint32_t v[32], u[32];
+                TMEM_LD16(v, 0, tlane + ab * 128 + c * 32);             // codes . q_hi
+                TMEM_LD16(v, 16, tlane + ab * 128 + c * 32 + 16);
+                TMEM_LD16(u, 0, tlane + ab * 128 + 64 + c * 32);        // codes . q_lo
+                TMEM_LD16(u, 16, tlane + ab * 128 + 64 + c * 32 + 16);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (!any_neg) {
 #pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    acc0 = fmaf(fmaxf(__uint_as_float(v[j]) + __uint_as_float(u[j]), 0.f), s_w[c * 16 + j], acc0);
-                    acc1 = fmaf(fmaxf(__uint_as_float(v[j + 1]) + __uint_as_float(u[j + 1]), 0.f), s_w[c * 16 + j + 1], acc1);
+                    for (int j = 0; j < 32; j += 2) {
+                        acc0 += fmaxf(__uint_as_float(v[j]) + __uint_as_float(u[j]), 0.f);
+                        acc1 += fmaxf(__uint_as_float(v[j + 1]) + __uint_as_float(u[j + 1]), 0.f);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float r0 = fmaxf(__uint_as_float(v[j]) + __uint_as_float(u[j]), 0.f);
+                        const float r1 = fmaxf(__uint_as_float(v[j + 1]) + __uint_as_float(u[j + 1]), 0.f);
+                        acc0 += __uint_as_float(__float_as_uint(r0) ^ (((neg[c] >> j) & 1u) << 31));
+                        acc1 += __uint_as_float(__float_as_uint(r1) ^ (((neg[c] >> (j + 1)) & 1u) << 31));
+                    }
                 }
             }
             tc_fence_before();
             mbar_arrive(bar(IB_D_EMPTY + ab));
-            if (key < nb) p.sc[(int64_t)b * p.key_stride + key] = (acc0 + acc1) * ksc;
+            if (key < nb) p.sc[(int64_t)b * p.key_stride + key] = (acc0 + acc1) * unscale * ksc;
         }
     }
     tc_fence_before();
@@ -359,38 +372,58 @@ __global__ void __launch_bounds__(256) band_rescore_kernel(const uint8_t *keys, 
     }
 }
 
-// q f32 [B][64][128] -> f16 [B][128][128]: one warp per head. The head is scaled by a power of two
-// that brings its largest magnitude into [2^13, 2^14); rows 0-63 hold the f16 roundings, rows
-// 64-127 the f16 roundings of the remainders (q * scale = hi + lo up to 2^-22 of the head's
-// largest element). wt_out = head weight * 2^8 / scale: the 2^8 undoes the keys' 2^-8.
-__global__ void __launch_bounds__(256) split_q_kernel(const float *q, const float *wt, uint16_t *y, float *wt_out, int B) {
-    const int gw = (int)((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
-    if (gw >= B * IT_IH) return;
-    const int b = gw / IT_IH, h = gw % IT_IH;
-    const float4 v = *reinterpret_cast<const float4 *>(q + (int64_t)gw * IT_HD + lane * 4);
-    float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+// q f32 [B][64][128] -> f16 [B][128][128]: one block per sequence. Every element is multiplied by
+// the magnitude of its head's weight (w ReLU(x) = sign(w) ReLU(|w| x)) and by a power of two that
+// brings the sequence's largest product into [2^13, 2^14); rows 0-63 hold the f16 roundings, rows
+// 64-127 the f16 roundings of the remainders. meta = {2^8 / scale (the 2^8 undoes the keys' 2^-8),
+// sign masks of the 64 head weights}.
+__global__ void __launch_bounds__(256) split_q_kernel(const float *q, const float *wt, uint16_t *y, uint32_t *meta) {
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+    __shared__ float red[8];
+    __shared__ float s_scale;
+    float x[32];
+    float m = 0.f;
+    const int h = tid >> 2, d0 = (tid & 3) * 32;
+    const float w = fabsf(wt[(int64_t)b * IT_IH + h]);
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(q + ((int64_t)b * IT_IH + h) * IT_HD + d0 + j);
+        x[j] = v.x * w; x[j + 1] = v.y * w; x[j + 2] = v.z * w; x[j + 3] = v.w * w;
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(x[j]), fabsf(x[j + 1])), fmaxf(fabsf(x[j + 2]), fabsf(x[j + 3]))));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float scale = 1.f, inv = 1.f;
-    if (m > 0.f && m < INFINITY) {
-        const int e = (int)((__float_as_uint(m) >> 23) & 255u) - 127;     // floor(log2 m) for normal m
-        const int sh = max(-100, min(100, 13 - e));
-        scale = __uint_as_float((uint32_t)(127 + sh) << 23);
-        inv = __uint_as_float((uint32_t)(127 - sh) << 23);
+    if (lane == 0) red[tid >> 5] = m;
+    __syncthreads();
+    if (tid == 0) {
+        m = 0.f;
+        for (int i = 0; i < 8; i++) m = fmaxf(m, red[i]);
+        float scale = 1.f, inv = 1.f;
+        if (m > 0.f && m < INFINITY) {
+            const int e = (int)((__float_as_uint(m) >> 23) & 255u) - 127;     // floor(log2 m) for normal m
+            const int sh = max(-100, min(100, 13 - e));
+            scale = __uint_as_float((uint32_t)(127 + sh) << 23);
+            inv = __uint_as_float((uint32_t)(127 - sh) << 23);
+        }
+        s_scale = scale;
+        meta[b * 4] = __float_as_uint(256.f * inv);
     }
-    const float x[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
-    uint16_t hi[4], lo[4];
+    if (tid < 64) {
+        const uint32_t neg = __ballot_sync(0xffffffffu, wt[(int64_t)b * IT_IH + tid] < 0.f);
+        if (lane == 0) meta[b * 4 + 1 + (tid >> 5)] = neg;
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    uint16_t *yh = y + ((int64_t)b * IT_QROWS + h) * IT_HD + d0;
+    uint16_t *yl = y + ((int64_t)b * IT_QROWS + IT_IH + h) * IT_HD + d0;
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const __half hh = __float2half_rn(x[j]);
-        hi[j] = __half_as_ushort(hh);
-        lo[j] = __half_as_ushort(__float2half_rn(x[j] - __half2float(hh)));
+    for (int j = 0; j < 32; j += 2) {
+        const float a0 = x[j] * scale, a1 = x[j + 1] * scale;
+        const __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
+        const __half l0 = __float2half_rn(a0 - __half2float(h0)), l1 = __float2half_rn(a1 - __half2float(h1));
+        *reinterpret_cast<uint32_t *>(yh + j) = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+        *reinterpret_cast<uint32_t *>(yl + j) = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
     }
-    uint16_t *yh = y + ((int64_t)b * IT_QROWS + h) * IT_HD + lane * 4;
-    uint16_t *yl = y + ((int64_t)b * IT_QROWS + IT_IH + h) * IT_HD + lane * 4;
-    *reinterpret_cast<uint2 *>(yh) = make_uint2(hi[0] | ((uint32_t)hi[1] << 16), hi[2] | ((uint32_t)hi[3] << 16));
-    *reinterpret_cast<uint2 *>(yl) = make_uint2(lo[0] | ((uint32_t)lo[1] << 16), lo[2] | ((uint32_t)lo[3] << 16));
-    if (lane == 0) wt_out[gw] = wt[gw] * 256.f * inv;
 }
 
 }  // namespace
@@ -414,16 +447,16 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     const bool tc_ok = ih == IT_IH && hd == IT_HD && ((uintptr_t)keys % 16) == 0 && cwk_encode_tiled_fn() != nullptr &&
                        ctx->force_mla_path != 0 && ctx->force_mla_path != 1;
     // workspace: approx f32 [B][stride], refined f32 [B][stride], band list int32 [B][stride], q f16 hi|lo,
-    // scaled head weights, band counts
+    // per-sequence scale and weight signs, band counts
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-    const size_t b_sc = up((size_t)B * key_stride * 4), b_q = up((size_t)B * 2 * ih * hd * 2), b_w = up((size_t)B * ih * 4);
+    const size_t b_sc = up((size_t)B * key_stride * 4), b_q = up((size_t)B * 2 * ih * hd * 2), b_w = up((size_t)B * 16);
     int s = cwk_reserve_work(ctx, 3 * b_sc + b_q + b_w + up((size_t)B * 4));
     if (s != CWK_OK) return s;
     uint8_t *w = (uint8_t *)ctx->work;
     float *approx = (float *)w, *refined = (float *)(w + b_sc);
     int32_t *band_list = (int32_t *)(w + 2 * b_sc);
     uint16_t *qb = (uint16_t *)(w + 3 * b_sc);
-    float *wtx = (float *)(w + 3 * b_sc + b_q);
+    uint32_t *meta = (uint32_t *)(w + 3 * b_sc + b_q);
     int32_t *band = (int32_t *)(w + 3 * b_sc + b_q + b_w);
     if (!tc_ok) {
         // shapes the tensor-core path is not built for: exact scores for every key
@@ -433,7 +466,7 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     }
     s = cwk_ensure_err_word(ctx);
     if (s != CWK_OK) return s;
-    split_q_kernel<<<(B * ih * 32 + 255) / 256, 256, 0, ctx->stream>>>(q, wt, qb, wtx, B);
+    split_q_kernel<<<B, 256, 0, ctx->stream>>>(q, wt, qb, meta);
     CWK_LAUNCH_CHECK(ctx, "split_q_kernel");
     CUtensorMap tm_keys;
     {
@@ -454,7 +487,7 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
         attr_set[ctx->device & 15] = true;
     }
     IdxParams p;
-    p.kscale = kscale; p.q = qb; p.wt = wtx; p.n = n; p.sc = approx; p.key_stride = key_stride; p.err = ctx->dev_err;
+    p.kscale = kscale; p.q = qb; p.meta = meta; p.n = n; p.sc = approx; p.key_stride = key_stride; p.err = ctx->dev_err;
     const int tiles = (max_n + IT_KEYS - 1) / IT_KEYS;
     const int bps = std::max(1, std::min(tiles, ctx->sm_count / B));
     {
@@ -465,7 +498,7 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     CWK_CUDA(ctx, cudaMemsetAsync(band, 0, (size_t)B * sizeof(int32_t), ctx->stream));
     band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band);
     CWK_LAUNCH_CHECK(ctx, "band_classify_kernel");
-    band_rescore_kernel<<<dim3(32, B), 256, RS_SMEM, ctx->stream>>>((const uint8_t *)keys, kscale, key_stride, q, wt, band_list, band,
+    band_rescore_kernel<<<dim3(std::max(8, std::min(128, 2 * ctx->sm_count / B)), B), 256, RS_SMEM, ctx->stream>>>((const uint8_t *)keys, kscale, key_stride, q, wt, band_list, band,
                                                                    refined);
     CWK_LAUNCH_CHECK(ctx, "band_rescore_kernel");
     if (scores_out) CWK_CUDA(ctx, cudaMemcpyAsync(scores_out, refined, (size_t)B * key_stride * 4, cudaMemcpyDeviceToDevice, ctx->stream));

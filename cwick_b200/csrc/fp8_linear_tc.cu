@@ -131,10 +131,10 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a0 = base + slot * (A_BYTES + B_BYTES), b0 = a0 + A_BYTES;
+                    const uint64_t da = smem_desc(a0, 16, 1024), db = smem_desc(b0, 16, 1024);   // one build per stage, constant adds per MMA
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
-                        umma_bf16(tmem + pb * 128, smem_desc(a0 + ks * 32, 16, 1024), smem_desc(b0 + ks * 32, 16, 1024), ID,
-                                  (h2 | ks) != 0);
+                        umma_bf16(tmem + pb * 128, da + (uint64_t)((ks * 32) >> 4), db + (uint64_t)((ks * 32) >> 4), ID, (h2 | ks) != 0);
                     umma_commit(bar(GB_EMPTY + slot));        // stage may be refilled once these MMAs are done
                 }
                 if (ok) umma_commit(bar(GB_PFULL + pb));
@@ -157,12 +157,15 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
             tc_fence_after();
             const float sc = __ldg(srow + kb);
 #pragma unroll
-            for (int c = 0; c < BN / 16; c++) {
-                uint32_t v[16];
-                TMEM_LD16(v, 0, tlane + pb * 128 + c * 16);
+            for (int c = 0; c < BN / 64; c++) {
+                uint32_t v[64];                              // four loads in flight per wait
+                TMEM_LD16(v, 0, tlane + pb * 128 + c * 64);
+                TMEM_LD16(v, 16, tlane + pb * 128 + c * 64 + 16);
+                TMEM_LD16(v, 32, tlane + pb * 128 + c * 64 + 32);
+                TMEM_LD16(v, 48, tlane + pb * 128 + c * 64 + 48);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < 16; j++) acc[c * 16 + j] = fmaf(__uint_as_float(v[j]), sc, acc[c * 16 + j]);
+                for (int j = 0; j < 64; j++) acc[c * 64 + j] = fmaf(__uint_as_float(v[j]), sc, acc[c * 64 + j]);
             }
             tc_fence_before();
             mbar_arrive(bar(GB_PEMPTY + pb));

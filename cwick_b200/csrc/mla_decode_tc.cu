@@ -16,7 +16,10 @@
 //
 // One tile is resident at a time (Q 72 KB + tile 144 KB of the 227 KB), and its
 // blocks are recycled as soon as the second product has consumed them, so the
-// next tile streams in behind the MMAs of this one.
+// next tile streams in behind the MMAs of this one. A TMA operation costs some
+// 400 cycles however small its box, and operations of one block queue behind one
+// another, so the cache is described as [64][rows][9 blocks] and a tile arrives
+// as four boxes of two column blocks (32 KB) plus the rope block; Q is one box.
 //
 // Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps
 // 4..11 = softmax / correction / epilogue: two groups of four warps, 32 heads
@@ -86,7 +89,7 @@ struct TcParams {
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
-                     const TcParams p) {
+                     const __grid_constant__ CUtensorMap tm_kr, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;             // 1024-byte aligned (swizzle atom)
@@ -121,17 +124,20 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kv) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kr) : "memory");
         for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), i == B_PFULL ? 256u : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // The first tile's loads go out before the block-wide set-up (TMEM allocation, the
         // barrier below): nothing they touch depends on it, and their latency is the longest
         // single item of a short call.
         mbar_expect_tx(bar(B_QFULL), NBLK * Q_BLK);
-        for (int k = 0; k < NBLK; k++) tma_load_2d(base + OFF_Q + k * Q_BLK, &tm_q, k * 64, b * NH, bar(B_QFULL));
-        for (int k = 0; k < NBLK; k++) {
-            mbar_expect_tx(bar(B_FULL + k), KV_BLK);
-            tma_load_3d(base + OFF_KV + k * KV_BLK, &tm_kv, k * 64, t0 * TILE, bz, bar(B_FULL + k));
+        tma_load_3d(base + OFF_Q, &tm_q, 0, b * NH, 0, bar(B_QFULL));
+        for (int k = 0; k < RP; k += 2) {
+            mbar_expect_tx(bar(B_FULL + k), 2 * KV_BLK);
+            tma_load_4d(base + OFF_KV + k * KV_BLK, &tm_kv, 0, t0 * TILE, k, bz, bar(B_FULL + k));
         }
+        mbar_expect_tx(bar(B_FULL + RP), KV_BLK);
+        tma_load_4d(base + OFF_KV + RP * KV_BLK, &tm_kr, 0, t0 * TILE, RP, bz, bar(B_FULL + RP));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TMEM_COLS) : "memory");
@@ -142,7 +148,7 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
     // trace slots: [role][tile][event]; only block (0,0) writes
-    long long *tr = (p.trace && split == 0 && b == 0) ? p.trace : nullptr;
+    long long *tr = (p.trace && split == 0 && blockIdx.y == 0) ? p.trace : nullptr;
 #define TRACE(role, it, ev) do { if (tr && (it) < 16) tr[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
     if (tr && tid == 0) tr[3 * 16 * 8] = clock64();
 
@@ -155,20 +161,28 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             for (int it = 1; it < n && ok; it++) {
                 const uint32_t par_free = (uint32_t)((it & 1) ^ 1);
                 const int row = (t0 + it) * TILE;
-                for (int k = 0; k < NBLK && ok; k++) {
+                for (int k = 0; k < NBLK && ok; k += 2) {
                     if (k == RP) ok = mbar_wait(bar(B_EMPTY_RP), par_free, p.err, 101);
-                    else if ((k & 1) == 0) ok = mbar_wait(bar(B_EMPTY_L + (k >> 1)), par_free, p.err, 102);
+                    else ok = mbar_wait(bar(B_EMPTY_L + (k >> 1)), par_free, p.err, 102);
                     if (!ok) break;
                     if (k == 0) TRACE(0, it, 0);
                     if (k == RP) TRACE(0, it, 1);
-                    mbar_expect_tx(bar(B_FULL + k), KV_BLK);
-                    tma_load_3d(base + OFF_KV + k * KV_BLK, &tm_kv, k * 64, row, bz, bar(B_FULL + k));
+                    if (k == 2) TRACE(0, it, 2);
+                    if (k == 4) TRACE(0, it, 3);
+                    if (k == 6) TRACE(0, it, 4);
+                    if (k == RP) {
+                        mbar_expect_tx(bar(B_FULL + k), KV_BLK);
+                        tma_load_4d(base + OFF_KV + k * KV_BLK, &tm_kr, 0, row, k, bz, bar(B_FULL + k));
+                    } else {
+                        mbar_expect_tx(bar(B_FULL + k), 2 * KV_BLK);
+                        tma_load_4d(base + OFF_KV + k * KV_BLK, &tm_kv, 0, row, k, bz, bar(B_FULL + k));
+                    }
                     issued_it[k] = it;
                 }
             }
             if (!ok) {      // drain: do not leave the block with bulk copies in flight
                 mbar_wait(bar(B_QFULL), 0, p.err, 103);
-                for (int k = 0; k < NBLK; k++)
+                for (int k = 0; k < NBLK; k += 2)
                     if (issued_it[k] >= 0) mbar_wait(bar(B_FULL + k), (uint32_t)(issued_it[k] & 1), p.err, 104);
             }
         }
@@ -177,21 +191,26 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t ID_QK = idesc_bf16(128, 64, 0, 0);
             constexpr uint32_t ID_PV = idesc_bf16(128, 64, 1, 1);
+            // Descriptors are built once; every MMA adds a compile-time constant to the address field
+            // (the issue loop is one thread, and its instruction count bounds the MMA rate at N = 64).
+            const uint64_t dK = smem_desc(base + OFF_KV, 16, 1024), dQ = smem_desc(base + OFF_Q, 16, 1024);
+            const uint64_t dV = smem_desc(base + OFF_KV, KV_BLK, 1024), dP = smem_desc(base + OFF_KV + RP * KV_BLK, KV_BLK, 1024);
             bool ok = mbar_wait(bar(B_QFULL), 0, p.err, 201);
             for (int it = 0; it < n && ok; it++) {
                 const uint32_t par = (uint32_t)(it & 1);
                 // S^T = K Q^T over the nine column blocks (4 k-steps of 16 each)
-                for (int k = 0; k < NBLK && ok; k++) {
-                    ok = mbar_wait(bar(B_FULL + k), par, p.err, 202);
-                    if (!ok) break;
-                    if (k == 0) TRACE(1, it, 0);
-                    if (k == RP) TRACE(1, it, 1);
-                    tc_fence_after();
-                    const uint32_t a0 = base + OFF_KV + k * KV_BLK, b0 = base + OFF_Q + k * Q_BLK;
 #pragma unroll
-                    for (int ks = 0; ks < 4; ks++)
-                        umma_bf16(tmem + COL_S, smem_desc(a0 + ks * 32, 16, 1024), smem_desc(b0 + ks * 32, 16, 1024),
-                                  ID_QK, (k | ks) != 0);
+                for (int k = 0; k < NBLK; k++) {
+                    if (ok && (k & 1) == 0) ok = mbar_wait(bar(B_FULL + k), par, p.err, 202);     // blocks arrive in pairs (the rope block alone)
+                    if (ok) {
+                        if (k == 0) TRACE(1, it, 0);
+                        if (k == RP) TRACE(1, it, 1);
+                        tc_fence_after();
+#pragma unroll
+                        for (int ks = 0; ks < 4; ks++)
+                            umma_bf16(tmem + COL_S, dK + (uint64_t)((k * KV_BLK + ks * 32) >> 4), dQ + (uint64_t)((k * Q_BLK + ks * 32) >> 4),
+                                      ID_QK, (k | ks) != 0);
+                    }
                 }
                 if (!ok) break;
                 umma_commit(bar(B_SFULL));
@@ -201,13 +220,13 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 if (!ok) break;
                 TRACE(1, it, 3);
                 tc_fence_after();
-                const uint32_t pb = base + OFF_KV + RP * KV_BLK;
+                const uint32_t acc0 = it != 0;
+#pragma unroll
                 for (int mb = 0; mb < 4; mb++) {
-                    const uint32_t va = base + OFF_KV + (2 * mb) * KV_BLK;
 #pragma unroll
                     for (int ks = 0; ks < 8; ks++)
-                        umma_bf16(tmem + COL_O + mb * 64, smem_desc(va + ks * 2048, KV_BLK, 1024),
-                                  smem_desc(pb + ks * 2048, KV_BLK, 1024), ID_PV, (it | ks) != 0);
+                        umma_bf16(tmem + COL_O + mb * 64, dV + (uint64_t)((2 * mb * KV_BLK + ks * 2048) >> 4), dP + (uint64_t)((ks * 2048) >> 4),
+                                  ID_PV, ks != 0 ? 1u : acc0);
                     umma_commit(bar(B_EMPTY_L + mb));
                 }
                 umma_commit(bar(B_EMPTY_RP));
@@ -395,26 +414,29 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
         int es = cwk_ensure_err_word(ctx);
         if (es != CWK_OK) return es;
     }
-    CUtensorMap tm_q, tm_kv;
+    CUtensorMap tm_q, tm_kv, tm_kr;
+    const cuuint64_t nblk = (cuuint64_t)(width / 64);     // 9, or 8 for a rope-free latent: block 8 is then out of range and reads as zeros
     {
-        cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)B * NH};
-        cuuint64_t strides[1] = {(cuuint64_t)width * 2};
-        cuuint32_t box[2] = {64, NH};
-        cuuint32_t es[2] = {1, 1};
-        CUresult r = enc(&tm_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(q), dims, strides, box, es,
+        // q as [64][B*NH rows][blocks]: one box brings all nine column blocks of a sequence's 64 heads
+        cuuint64_t dims[3] = {64, (cuuint64_t)B * NH, nblk};
+        cuuint64_t strides[2] = {(cuuint64_t)width * 2, 128};
+        cuuint32_t box[3] = {64, NH, NBLK};
+        cuuint32_t es[3] = {1, 1, 1};
+        CUresult r = enc(&tm_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(q), dims, strides, box, es,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(q) failed: %d", (int)r);
     }
     const bool shared_cache = (seq_stride == 0);
-    {
+    for (int pass = 0; pass < 2; pass++) {
+        // the cache as [64][rows][blocks][sequences]; boxes of two column blocks (latent) or one (rope)
         const cuuint64_t nb = shared_cache ? 1 : (cuuint64_t)B;
-        cuuint64_t dims[3] = {(cuuint64_t)width, (cuuint64_t)max_kv_len, nb};
-        cuuint64_t strides[2] = {(cuuint64_t)ld * 2,
+        cuuint64_t dims[4] = {64, (cuuint64_t)max_kv_len, nblk, nb};
+        cuuint64_t strides[3] = {(cuuint64_t)ld * 2, 128,
                                  shared_cache ? (cuuint64_t)ld * 2 * (cuuint64_t)max_kv_len : (cuuint64_t)seq_stride * 2};
-        cuuint32_t box[3] = {64, TILE, 1};
-        cuuint32_t es[3] = {1, 1, 1};
-        CUresult r = enc(&tm_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(cache), dims, strides, box, es,
+        cuuint32_t box[4] = {64, TILE, pass == 0 ? 2u : 1u, 1};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        CUresult r = enc(pass == 0 ? &tm_kv : &tm_kr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(cache), dims, strides, box, es,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(cache) failed: %d", (int)r);
@@ -430,7 +452,7 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     p.trace = (long long *)ctx->tc_trace;
     p.out = (uint16_t *)out_direct;
     p.reverse_b = shared_cache ? 1 : 0;
-    mla_decode_tc_kernel<<<dim3(nsplit, B), NTHREADS, SMEM_TOTAL, ctx->stream>>>(tm_q, tm_kv, p);
+    mla_decode_tc_kernel<<<dim3(nsplit, B), NTHREADS, SMEM_TOTAL, ctx->stream>>>(tm_q, tm_kv, tm_kr, p);
     CWK_LAUNCH_CHECK(ctx, "mla_decode_tc_kernel");
     return CWK_OK;
 }

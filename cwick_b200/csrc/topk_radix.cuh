@@ -69,8 +69,8 @@ __device__ __forceinline__ void tk_load(const float *s, int c0, int end, uint32_
 // Exact want-th largest value of the row: 4 passes of 8 bits over the order-preserving integer
 // image. On return `prefix` is that image and `remaining` how many rows equal to it are wanted.
 // Every thread of every block of the cluster calls it; nb > want >= 1. Scores of one row usually
-// share their leading digits, so the lanes of a warp that hit the same bin are counted with one
-// atomic (match_any), not 32. kc holds the slice's keys when sl.cached (loaded by the caller).
+// share their leading digits, so the lanes of a warp that hit the first active lane's bin are
+// counted with one atomic, not 32. kc holds the slice's keys when sl.cached (loaded by the caller).
 __device__ __forceinline__ void tk_radix_select(const float *s, const TkSlice sl, uint32_t (&kc)[TK_PT], int want, TkShared &sh,
                                                 uint32_t &prefix, int &remaining) {
     cg::cluster_group cl = cg::this_cluster();
@@ -90,10 +90,14 @@ __device__ __forceinline__ void tk_radix_select(const float *s, const TkSlice sl
             for (int j = 0; j < TK_PT; j++) {
                 const bool act = (i0 + j < sl.end) && ((kc[j] & mask) == prefix);
                 const uint32_t d = (kc[j] >> shift) & 255u;
+                // the first active lane's digit is counted once for every lane that shares it; the others add singly
                 const uint32_t am = __ballot_sync(0xffffffffu, act);
-                if (act) {
-                    const uint32_t peers = __match_any_sync(am, d);
-                    if (lane == __ffs(peers) - 1) atomicAdd(&h[d], (uint32_t)__popc(peers));
+                if (am) {
+                    const int leader = __ffs(am) - 1;
+                    const uint32_t d0 = __shfl_sync(0xffffffffu, d, leader);
+                    const uint32_t same = __ballot_sync(0xffffffffu, act && d == d0);
+                    if (lane == leader) atomicAdd(&h[d0], (uint32_t)__popc(same));
+                    else if (act && d != d0) atomicAdd(&h[d], 1u);
                 }
             }
         }

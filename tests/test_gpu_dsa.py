@@ -146,6 +146,7 @@ def test_fused_selection_equals_oracle_selection(attn, B, T, want, keep_self, ex
     codes, ks, q, wt = make_index_inputs(300 + T, B, T)
     if not exact_q:
         q = (q + synth.normal(5 + T, 9, q.size).reshape(q.shape) * np.float32(1e-3)).astype(np.float32)
+        wt[:, ::5] *= np.float32(-0.5)         # negative head weights: the fused path carries their sign apart
     # duplicate keys: a run of identical rows gives exactly equal scores
     codes[0, 10:40] = codes[0, 7]
     ks[0, 10:40] = ks[0, 7]
