@@ -79,6 +79,27 @@ __global__ void __launch_bounds__(256) norm_rope_rows_kernel(const float *in, in
     if (kv_len_out && threadIdx.x == 0) kv_len_out[r] = (int)(pos0 + r + 1);
 }
 
+// Rope tail of the absorbed query: Qfull[t][h][L : L+rope] = RoPE(q[t][h][nope : nope+rope], pos0 + t).
+// The angle depends on (t, pair) only: one thread forms it once and rotates that pair of all heads.
+__global__ void __launch_bounds__(256) rope_tail_kernel(const uint16_t *q, uint16_t *qfull, int n, int nh, int nope, int n_rope, int L,
+                                                        int64_t pos0, float base) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * (n_rope / 2)) return;
+    const int t = i / (n_rope / 2), j = i % (n_rope / 2);
+    float cs, sn;
+    rope_cos_sin(pos0 + t, j, n_rope, base, cs, sn);
+    const uint16_t *src = q + (int64_t)t * nh * (nope + n_rope) + nope + 2 * j;
+    uint16_t *dst = qfull + (int64_t)t * nh * (L + n_rope) + L + 2 * j;
+#pragma unroll 8
+    for (int h = 0; h < nh; h++) {
+        const uint32_t v = *reinterpret_cast<const uint32_t *>(src + (int64_t)h * (nope + n_rope));
+        const float a = __uint_as_float(v << 16), b = __uint_as_float(v & 0xffff0000u);
+        *reinterpret_cast<uint32_t *>(dst + (int64_t)h * (L + n_rope)) = pack_bf16x2(a * cs - b * sn, b * cs + a * sn);
+    }
+}
+
+int cwk_absorb_tc_launch(cwk_ctx *ctx, const void *Q, int n, int nh, const void *Wuk, void *Qfull);
+
 // Absorb: Qfull[t][h][0:L] = q[t][h][0:nope] . W_uk[h] ([nope][L] row-major bf16), and
 // Qfull[t][h][L:L+rope] = RoPE(q[t][h][nope:nope+rope], pos0+t). The identity is
 // q_abs = W_k^T q of src/attention.c:741-744 (gemv_bf16_t), batched over tokens.
@@ -190,12 +211,25 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(KVA, row, kv_lora, rope, (const uint16_t *)kva_norm, eps, rope_base,
                                                       pos0, (uint16_t *)cache + pos0 * row, row, len, 1);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(kv_a)");
-    static bool attr_set[16] = {false};
-    if (!attr_set[ctx->device & 15]) {
-        CWK_CUDA(ctx, cudaFuncSetAttribute(absorb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AB_SMEM));
-        attr_set[ctx->device & 15] = true;
+    // absorb on the tensor path (tcgen05); the mma.sync kernel covers a context without the
+    // tensor-map encoder or a caller that forced the general kernels
+    s = CWK_ERR_UNSUPPORTED;
+    if (ctx->force_mla_path != 0 && ctx->force_mla_path != 1) {
+        s = cwk_absorb_tc_launch(ctx, Q, n, nh, Wuk, Qf);
+        if (s != CWK_OK && s != CWK_ERR_UNSUPPORTED) return s;
+        if (s == CWK_OK) {
+            rope_tail_kernel<<<(n * (rope / 2) + 255) / 256, 256, 0, ctx->stream>>>(Q, Qf, n, nh, nope, rope, kv_lora, pos0, rope_base);
+            CWK_LAUNCH_CHECK(ctx, "rope_tail_kernel");
+        }
     }
-    absorb_kernel<<<dim3((n + 63) / 64, nh), 256, AB_SMEM, ctx->stream>>>(Q, n, nh, (const uint16_t *)Wuk, rope_base, pos0, Qf);
-    CWK_LAUNCH_CHECK(ctx, "absorb_kernel");
+    if (s == CWK_ERR_UNSUPPORTED) {
+        static bool attr_set[16] = {false};
+        if (!attr_set[ctx->device & 15]) {
+            CWK_CUDA(ctx, cudaFuncSetAttribute(absorb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AB_SMEM));
+            attr_set[ctx->device & 15] = true;
+        }
+        absorb_kernel<<<dim3((n + 63) / 64, nh), 256, AB_SMEM, ctx->stream>>>(Q, n, nh, (const uint16_t *)Wuk, rope_base, pos0, Qf);
+        CWK_LAUNCH_CHECK(ctx, "absorb_kernel");
+    }
     return cwk_mla_decode(ctx, Qf, cache, 0, row, len, (int)(pos0 + n), nullptr, 0, n, nh, kv_lora, rope, scale, out, 0);
 }
