@@ -11,19 +11,24 @@
 // order of src/tensor.c:511-520). Two TMEM accumulators alternate so the MMA of
 // block kb+1 runs while block kb is being promoted.
 //
-// Block tile 128 (rows of X) x 128 (cols = one scale column block), K step 64
-// (one 128-byte swizzle atom of bf16). Warp 0 = TMA producer, warp 1 = MMA
-// issuer + TMEM owner, warps 4..7 = promotion / epilogue.
+// Block tile 128 (rows of X) x 256 (two scale column blocks), K step 128 = one scale block per
+// pipeline stage, two stages. An operand tile arrives as ONE TMA box of two 64-wide column blocks
+// (a TMA operation costs some 400 cycles whatever its size, and a 128 x 128 tile with 64-wide steps
+// is bound by that, not by the MMAs). The MMA is M 128 x N 256: at N = 256 the operand reads leave
+// shared-memory bandwidth for the incoming tiles. Warp 0 = TMA producer, warp 1 = MMA issuer + TMEM
+// owner, warps 4..11 = promotion / epilogue (TMEM lane quarter = warp % 4; warps 4-7 own output
+// columns 0-127 of the tile, warps 8-11 columns 128-255).
 #include "tc_common.cuh"
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int STAGES = 6;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;      // 16 KB each
+constexpr int BM = 128, BN = 256, BK = 128;
+constexpr int STAGES = 2;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;      // 32 KB + 64 KB
 constexpr int G_OFF_BAR = STAGES * (A_BYTES + B_BYTES);          // 196608
 constexpr int G_SMEM = G_OFF_BAR + 256 + 1024;
-constexpr uint32_t G_TMEM_COLS = 256;                             // two 128-column partial accumulators
+constexpr uint32_t G_TMEM_COLS = 512;                             // two 256-column partial accumulators
+constexpr int G_THREADS = 384;
 enum { GB_FULL = 0, GB_EMPTY = STAGES, GB_PFULL = 2 * STAGES, GB_PEMPTY = 2 * STAGES + 2, GB_COUNT = 2 * STAGES + 4 };
 
 // E4M3 -> bf16, exact. 16 codes per thread.
@@ -68,7 +73,7 @@ struct GemmParams {
     int *err;
 };
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(G_THREADS, 1)
 fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                      const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -81,13 +86,12 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int col0 = blockIdx.x * BN, row0 = blockIdx.y * BM;
-    const int nkb = (int)(p.k / 128);              // scale blocks along K
-    const int nst = nkb * 2;                       // K steps of 64
+    const int nkb = (int)(p.k / 128);              // scale blocks along K = pipeline steps
 
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
-        for (int i = 0; i < GB_COUNT; i++) mbar_init(bar(i), (i >= GB_PEMPTY) ? 128u : 1u);
+        for (int i = 0; i < GB_COUNT; i++) mbar_init(bar(i), (i >= GB_PEMPTY) ? 256u : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -102,18 +106,18 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     if (warp == 0) {
         if (lane == 0) {
             bool ok = true;
-            int last_issued = -1;
-            for (int s = 0; s < nst && ok; s++) {
+            int issued = 0;
+            for (int s = 0; s < nkb && ok; s++) {
                 const int slot = s % STAGES, use = s / STAGES;
                 ok = mbar_wait(bar(GB_EMPTY + slot), (uint32_t)((use & 1) ^ 1), p.err, 401);
                 if (!ok) break;
                 mbar_expect_tx(bar(GB_FULL + slot), A_BYTES + B_BYTES);
-                tma_load_2d(base + slot * (A_BYTES + B_BYTES), &tm_x, s * BK, row0, bar(GB_FULL + slot));
-                tma_load_2d(base + slot * (A_BYTES + B_BYTES) + A_BYTES, &tm_w, s * BK, col0, bar(GB_FULL + slot));
-                last_issued = s;
+                tma_load_3d(base + slot * (A_BYTES + B_BYTES), &tm_x, 0, row0, s * 2, bar(GB_FULL + slot));
+                tma_load_3d(base + slot * (A_BYTES + B_BYTES) + A_BYTES, &tm_w, 0, col0, s * 2, bar(GB_FULL + slot));
+                issued = s + 1;
             }
             if (!ok)      // drain the copies still in flight before leaving
-                for (int s = last_issued; s >= 0 && s > last_issued - STAGES; s--)
+                for (int s = (issued > STAGES ? issued - STAGES : 0); s < issued; s++)
                     mbar_wait(bar(GB_FULL + s % STAGES), (uint32_t)((s / STAGES) & 1), p.err, 402);
         }
     } else if (warp == 1) {
@@ -121,80 +125,78 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
             constexpr uint32_t ID = idesc_bf16(BM, BN, 0, 0);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; kb++) {
-                const int pb = kb & 1, puse = kb >> 1;
+                const int pb = kb & 1, puse = kb >> 1, slot = kb % STAGES, use = kb / STAGES;
                 ok = mbar_wait(bar(GB_PEMPTY + pb), (uint32_t)((puse & 1) ^ 1), p.err, 403);
+                if (ok) ok = mbar_wait(bar(GB_FULL + slot), (uint32_t)(use & 1), p.err, 404);
                 if (!ok) break;
                 tc_fence_after();
-                for (int h2 = 0; h2 < 2 && ok; h2++) {
-                    const int s = kb * 2 + h2, slot = s % STAGES, use = s / STAGES;
-                    ok = mbar_wait(bar(GB_FULL + slot), (uint32_t)(use & 1), p.err, 404);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t a0 = base + slot * (A_BYTES + B_BYTES), b0 = a0 + A_BYTES;
-                    const uint64_t da = smem_desc(a0, 16, 1024), db = smem_desc(b0, 16, 1024);   // one build per stage, constant adds per MMA
+                const uint32_t a0 = base + slot * (A_BYTES + B_BYTES), b0 = a0 + A_BYTES;
+                const uint64_t da = smem_desc(a0, 16, 1024), db = smem_desc(b0, 16, 1024);   // one build per stage, constant adds per MMA
 #pragma unroll
-                    for (int ks = 0; ks < 4; ks++)
-                        umma_bf16(tmem + pb * 128, da + (uint64_t)((ks * 32) >> 4), db + (uint64_t)((ks * 32) >> 4), ID, (h2 | ks) != 0);
-                    umma_commit(bar(GB_EMPTY + slot));        // stage may be refilled once these MMAs are done
-                }
-                if (ok) umma_commit(bar(GB_PFULL + pb));
+                for (int ks = 0; ks < 8; ks++)          // 64-wide column block ks >> 2 of each operand, 32 bytes per 16-wide step
+                    umma_bf16(tmem + pb * 256, da + (uint64_t)(((ks >> 2) * (BM * 128) + (ks & 3) * 32) >> 4),
+                              db + (uint64_t)(((ks >> 2) * (BN * 128) + (ks & 3) * 32) >> 4), ID, ks != 0);
+                umma_commit(bar(GB_EMPTY + slot));        // stage may be refilled once these MMAs are done
+                umma_commit(bar(GB_PFULL + pb));
             }
         }
     } else if (warp >= 4) {
-        const int q = warp & 3;
+        const int q = warp & 3, ch = (warp - 4) >> 2;
         const int row = q * 32 + lane;
+        const int cbase = col0 + ch * 128;             // first output column of this warp's 128
+        const bool live = cbase < p.cols;              // a tile past the last column block: only keep the barriers moving
         const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
         const int64_t ncb = (p.k + 127) / 128;
-        const float *srow = p.scale_inv + (int64_t)(col0 / 128) * ncb;
-        float acc[BN];
+        const float *srow = p.scale_inv + (int64_t)(live ? cbase / 128 : 0) * ncb;
+        float acc[128];
 #pragma unroll
-        for (int j = 0; j < BN; j++) acc[j] = 0.f;
+        for (int j = 0; j < 128; j++) acc[j] = 0.f;
         bool ok = true;
         for (int kb = 0; kb < nkb; kb++) {
             const int pb = kb & 1, puse = kb >> 1;
             ok = mbar_wait(bar(GB_PFULL + pb), (uint32_t)(puse & 1), p.err, 405);
             if (!ok) break;
             tc_fence_after();
-            const float sc = __ldg(srow + kb);
+            if (live) {
+                const float sc = __ldg(srow + kb);
 #pragma unroll
-            for (int c = 0; c < BN / 64; c++) {
-                uint32_t v[64];                              // four loads in flight per wait
-                TMEM_LD16(v, 0, tlane + pb * 128 + c * 64);
-                TMEM_LD16(v, 16, tlane + pb * 128 + c * 64 + 16);
-                TMEM_LD16(v, 32, tlane + pb * 128 + c * 64 + 32);
-                TMEM_LD16(v, 48, tlane + pb * 128 + c * 64 + 48);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (int c = 0; c < 4; c++) {
+                    uint32_t v[32];                              // two loads in flight per wait
+                    TMEM_LD16(v, 0, tlane + pb * 256 + ch * 128 + c * 32);
+                    TMEM_LD16(v, 16, tlane + pb * 256 + ch * 128 + c * 32 + 16);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < 64; j++) acc[c * 64 + j] = fmaf(__uint_as_float(v[j]), sc, acc[c * 64 + j]);
+                    for (int j = 0; j < 32; j++) acc[c * 32 + j] = fmaf(__uint_as_float(v[j]), sc, acc[c * 32 + j]);
+                }
             }
             tc_fence_before();
             mbar_arrive(bar(GB_PEMPTY + pb));
         }
-        if (ok && row0 + row < p.n) {
+        if (ok && live && row0 + row < p.n) {
             const int64_t r = row0 + row;
             if (p.out_bf16) {
-                uint16_t *y = (uint16_t *)p.Y + r * p.cols + col0;
+                uint16_t *y = (uint16_t *)p.Y + r * p.cols + cbase;
 #pragma unroll
-                for (int j = 0; j < BN; j += 8) {
-                    if (col0 + j + 8 <= p.cols) {
+                for (int j = 0; j < 128; j += 8) {
+                    if (cbase + j + 8 <= p.cols) {
                         uint4 w;
                         w.x = pack_bf16x2(acc[j], acc[j + 1]); w.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
                         w.z = pack_bf16x2(acc[j + 4], acc[j + 5]); w.w = pack_bf16x2(acc[j + 6], acc[j + 7]);
                         *reinterpret_cast<uint4 *>(y + j) = w;
                     } else {
                         for (int e = 0; e < 8; e++)
-                            if (col0 + j + e < p.cols) y[j + e] = (uint16_t)(pack_bf16x2(acc[j + e], 0.f) & 0xffffu);
+                            if (cbase + j + e < p.cols) y[j + e] = (uint16_t)(pack_bf16x2(acc[j + e], 0.f) & 0xffffu);
                     }
                 }
             } else {
-                float *y = (float *)p.Y + r * p.cols + col0;
+                float *y = (float *)p.Y + r * p.cols + cbase;
 #pragma unroll
-                for (int j = 0; j < BN; j += 4) {
-                    if (col0 + j + 4 <= p.cols) {
+                for (int j = 0; j < 128; j += 4) {
+                    if (cbase + j + 4 <= p.cols) {
                         *reinterpret_cast<float4 *>(y + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                     } else {
                         for (int e = 0; e < 4; e++)
-                            if (col0 + j + e < p.cols) y[j + e] = acc[j + e];
+                            if (cbase + j + e < p.cols) y[j + e] = acc[j + e];
                     }
                 }
             }
@@ -215,7 +217,7 @@ bool cwk_fp8_linear_tc_available() { return true; }
 int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv, int64_t n, int64_t k,
                              int64_t cols, void *Y, int out_bf16) {
     // vector stores in the epilogue want 16-byte aligned rows
-    if ((cols % 8) != 0 || (k % 128) != 0 || ((uintptr_t)Y % 16) != 0)
+    if ((cols % 8) != 0 || (k % 128) != 0 || ((uintptr_t)Y % 16) != 0 || ((uintptr_t)X % 16) != 0)
         return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 FP8 GEMM needs cols %% 8 == 0 and k %% 128 == 0");
     if (!cwk_encode_tiled_fn()) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
     {
@@ -238,9 +240,19 @@ int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const f
     e4m3_to_bf16_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, ctx->stream>>>((const uint8_t *)W, (uint16_t *)ctx->wbf16, n16);
     CWK_LAUNCH_CHECK(ctx, "e4m3_to_bf16_kernel");
     CUtensorMap tm_x, tm_w;
-    if (!cwk_make_tmap_bf16_2d(&tm_x, X, (uint64_t)n, (uint64_t)k, (uint64_t)k, BM) ||
-        !cwk_make_tmap_bf16_2d(&tm_w, ctx->wbf16, (uint64_t)cols, (uint64_t)k, (uint64_t)k, BN))
-        return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the projection operands");
+    {
+        // operands as [64][rows][k / 64 column blocks]: one box = all rows of a tile x two column blocks (one 128-wide scale block)
+        CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
+        cuuint32_t es[3] = {1, 1, 1};
+        cuuint64_t xd[3] = {64, (cuuint64_t)n, (cuuint64_t)(k / 64)}, wd[3] = {64, (cuuint64_t)cols, (cuuint64_t)(k / 64)};
+        cuuint64_t st[2] = {(cuuint64_t)k * 2, 128};
+        cuuint32_t xb[3] = {64, BM, 2}, wb[3] = {64, BN, 2};
+        if (enc(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(X), xd, st, xb, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+            enc(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ctx->wbf16, wd, st, wb, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the projection operands");
+    }
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
         CWK_CUDA(ctx, cudaFuncSetAttribute(fp8_linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM));
@@ -250,7 +262,7 @@ int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const f
     p.scale_inv = scale_inv; p.n = n; p.k = k; p.cols = cols; p.Y = Y; p.out_bf16 = out_bf16; p.err = ctx->dev_err;
     dim3 grid((unsigned)((cols + BN - 1) / BN), (unsigned)((n + BM - 1) / BM));
     CwkKernelTimer timer(ctx);
-    fp8_linear_tc_kernel<<<grid, 256, G_SMEM, ctx->stream>>>(tm_x, tm_w, p);
+    fp8_linear_tc_kernel<<<grid, G_THREADS, G_SMEM, ctx->stream>>>(tm_x, tm_w, p);
     CWK_LAUNCH_CHECK(ctx, "fp8_linear_tc_kernel");
     return CWK_OK;
 }

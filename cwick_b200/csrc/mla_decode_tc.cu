@@ -19,7 +19,8 @@
 // next tile streams in behind the MMAs of this one. A TMA operation costs some
 // 400 cycles however small its box, and operations of one block queue behind one
 // another, so the cache is described as [64][rows][9 blocks] and a tile arrives
-// as four boxes of two column blocks (32 KB) plus the rope block; Q is one box.
+// as three boxes of two column blocks (32 KB) and one of three (the last latent pair with the
+// rope block, which come free together); Q is one box.
 //
 // Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps
 // 4..11 = softmax / correction / epilogue: two groups of four warps, 32 heads
@@ -132,12 +133,12 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // single item of a short call.
         mbar_expect_tx(bar(B_QFULL), NBLK * Q_BLK);
         tma_load_3d(base + OFF_Q, &tm_q, 0, b * NH, 0, bar(B_QFULL));
-        for (int k = 0; k < RP; k += 2) {
+        for (int k = 0; k < 6; k += 2) {
             mbar_expect_tx(bar(B_FULL + k), 2 * KV_BLK);
             tma_load_4d(base + OFF_KV + k * KV_BLK, &tm_kv, 0, t0 * TILE, k, bz, bar(B_FULL + k));
         }
-        mbar_expect_tx(bar(B_FULL + RP), KV_BLK);
-        tma_load_4d(base + OFF_KV + RP * KV_BLK, &tm_kr, 0, t0 * TILE, RP, bz, bar(B_FULL + RP));
+        mbar_expect_tx(bar(B_FULL + 6), 3 * KV_BLK);
+        tma_load_4d(base + OFF_KV + 6 * KV_BLK, &tm_kr, 0, t0 * TILE, 6, bz, bar(B_FULL + 6));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TMEM_COLS) : "memory");
@@ -161,17 +162,18 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             for (int it = 1; it < n && ok; it++) {
                 const uint32_t par_free = (uint32_t)((it & 1) ^ 1);
                 const int row = (t0 + it) * TILE;
-                for (int k = 0; k < NBLK && ok; k += 2) {
-                    if (k == RP) ok = mbar_wait(bar(B_EMPTY_RP), par_free, p.err, 101);
-                    else ok = mbar_wait(bar(B_EMPTY_L + (k >> 1)), par_free, p.err, 102);
+                for (int k = 0; k < 8 && ok; k += 2) {
+                    ok = mbar_wait(bar(B_EMPTY_L + (k >> 1)), par_free, p.err, 102);
+                    // the last latent pair and the rope block (= the P^T slot) come free together, at the end of
+                    // the second product, and return as one box of three blocks
+                    if (ok && k == 6) ok = mbar_wait(bar(B_EMPTY_RP), par_free, p.err, 101);
                     if (!ok) break;
                     if (k == 0) TRACE(0, it, 0);
-                    if (k == RP) TRACE(0, it, 1);
                     if (k == 2) TRACE(0, it, 2);
                     if (k == 4) TRACE(0, it, 3);
-                    if (k == 6) TRACE(0, it, 4);
-                    if (k == RP) {
-                        mbar_expect_tx(bar(B_FULL + k), KV_BLK);
+                    if (k == 6) TRACE(0, it, 1);
+                    if (k == 6) {
+                        mbar_expect_tx(bar(B_FULL + k), 3 * KV_BLK);
                         tma_load_4d(base + OFF_KV + k * KV_BLK, &tm_kr, 0, row, k, bz, bar(B_FULL + k));
                     } else {
                         mbar_expect_tx(bar(B_FULL + k), 2 * KV_BLK);
@@ -182,7 +184,7 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             if (!ok) {      // drain: do not leave the block with bulk copies in flight
                 mbar_wait(bar(B_QFULL), 0, p.err, 103);
-                for (int k = 0; k < NBLK; k += 2)
+                for (int k = 0; k < 8; k += 2)
                     if (issued_it[k] >= 0) mbar_wait(bar(B_FULL + k), (uint32_t)(issued_it[k] & 1), p.err, 104);
             }
         }
@@ -201,7 +203,7 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 // S^T = K Q^T over the nine column blocks (4 k-steps of 16 each)
 #pragma unroll
                 for (int k = 0; k < NBLK; k++) {
-                    if (ok && (k & 1) == 0) ok = mbar_wait(bar(B_FULL + k), par, p.err, 202);     // blocks arrive in pairs (the rope block alone)
+                    if (ok && (k & 1) == 0 && k < 8) ok = mbar_wait(bar(B_FULL + k), par, p.err, 202);     // blocks arrive in pairs, the rope block with the last pair
                     if (ok) {
                         if (k == 0) TRACE(1, it, 0);
                         if (k == RP) TRACE(1, it, 1);
@@ -429,12 +431,12 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     }
     const bool shared_cache = (seq_stride == 0);
     for (int pass = 0; pass < 2; pass++) {
-        // the cache as [64][rows][blocks][sequences]; boxes of two column blocks (latent) or one (rope)
+        // the cache as [64][rows][blocks][sequences]; boxes of two column blocks, or three (blocks 6, 7 and the rope block)
         const cuuint64_t nb = shared_cache ? 1 : (cuuint64_t)B;
         cuuint64_t dims[4] = {64, (cuuint64_t)max_kv_len, nblk, nb};
         cuuint64_t strides[3] = {(cuuint64_t)ld * 2, 128,
                                  shared_cache ? (cuuint64_t)ld * 2 * (cuuint64_t)max_kv_len : (cuuint64_t)seq_stride * 2};
-        cuuint32_t box[4] = {64, TILE, pass == 0 ? 2u : 1u, 1};
+        cuuint32_t box[4] = {64, TILE, pass == 0 ? 2u : 3u, 1};
         cuuint32_t es[4] = {1, 1, 1, 1};
         CUresult r = enc(pass == 0 ? &tm_kv : &tm_kr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(cache), dims, strides, box, es,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
