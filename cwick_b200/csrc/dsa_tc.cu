@@ -28,22 +28,18 @@ __host__ __device__ constexpr uint32_t idesc_f16(int M, int N) {
     return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// Four E4M3 codes -> four f16 holding code * 2^-8, exactly: an E4M3 magnitude shifted into an f16's
-// exponent and mantissa fields (s eeee mmm -> s 0eeee mmm0000000) keeps its subnormals subnormal
-// and its normals normal, with the exponent bias differing by 8. Integer ALU only.
+// Four E4M3 codes -> four f16, exactly (every E4M3 value is an f16 value): the hardware's paired
+// conversion, two codes per instruction.
 __device__ __forceinline__ uint2 e4m3x4_f16x4(uint32_t w) {
-    const uint32_t t0 = __byte_perm(w, 0, 0x1404);                  // code 0 -> byte 1, code 1 -> byte 3
-    const uint32_t t1 = __byte_perm(w, 0, 0x3424);                  // codes 2, 3
     uint2 r;
-    r.x = (t0 & 0x80008000u) | ((t0 >> 1) & 0x3F803F80u);
-    r.y = (t1 & 0x80008000u) | ((t1 >> 1) & 0x3F803F80u);
+    asm("{\n.reg .b16 lo, hi;\nmov.b32 {lo, hi}, %2;\ncvt.rn.f16x2.e4m3x2 %0, lo;\ncvt.rn.f16x2.e4m3x2 %1, hi;\n}\n" : "=r"(r.x), "=r"(r.y) : "r"(w));
     return r;
 }
 
 struct IdxParams {
     const float *kscale;      // [B][key_stride]
     const uint16_t *q;        // f16 [B][128][128]: rows 0-63 the high parts of q * |head weight| * scale, 64-127 the low parts
-    const uint32_t *meta;     // [B][4]: f32 2^8 / scale, sign mask of head weights 0-31, of 32-63, unused
+    const uint32_t *meta;     // [B][4]: f32 1 / scale, sign mask of head weights 0-31, of 32-63, unused
     const int32_t *n;         // [B]
     float *sc;                // [B][key_stride]
     int64_t key_stride;
@@ -223,7 +219,8 @@ __device__ __forceinline__ float e4m3_to_f32_i(uint32_t b) {
 // One cluster per sequence: the row's largest approximate score, the exact want-th largest
 // approximate score tau, then the classification of every key: certainly selected (refined =
 // +inf), certainly not (refined = -inf), or in the band |a - tau| <= eps, whose indices are appended
-// to band_list (band_count zeroed by the caller).
+// to band_list. band_count[2b] counts the band's entries, band_count[2b + 1] the keys above the band
+// (both zeroed by the caller).
 __global__ void __cluster_dims__(TK_CL, 1, 1) __launch_bounds__(TK_THREADS, 1)
 band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int want, float *refined, int32_t *band_list,
                      int32_t *band_count) {
@@ -290,6 +287,13 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
             for (int j = 0; j < TK_PT; j++)
                 if (i0 + j < sl.end) f[i0 + j] = v[j];
         }
+        {
+            int nab = 0;
+#pragma unroll
+            for (int j = 0; j < TK_PT; j++) nab += (i0 + j < sl.end && v[j] > 0.f) ? 1 : 0;
+            nab = __reduce_add_sync(0xffffffffu, nab);
+            if (lane == 0 && nab) atomicAdd(band_count + 2 * b + 1, nab);
+        }
         // band entries: one global atomic per warp (the list's order does not matter; the rescoring
         // kernel overwrites refined[] at these indices)
         const int mine = __popc(inb);
@@ -301,7 +305,7 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
         }
         const int wtot = __shfl_sync(0xffffffffu, incl, 31);
         int at = 0;
-        if (lane == 31 && wtot) at = atomicAdd(band_count + b, wtot);
+        if (lane == 31 && wtot) at = atomicAdd(band_count + 2 * b, wtot);
         at = __shfl_sync(0xffffffffu, at, 31) + incl - mine;
 #pragma unroll
         for (int j = 0; j < TK_PT; j++)
@@ -321,7 +325,7 @@ __global__ void __launch_bounds__(256) band_rescore_kernel(const uint8_t *keys, 
     extern __shared__ __align__(16) float rs_sm[];
     float *sq = rs_sm, *sw = rs_sm + IT_IH * RS_QLD, *sp = sw + IT_IH;
     const int b = blockIdx.y, tid = threadIdx.x;
-    const int cnt = band_count[b];
+    const int cnt = band_count[2 * b];
     if ((int)blockIdx.x * 32 >= cnt) return;
     for (int i = tid; i < IT_IH * (IT_HD / 4); i += 256) {
         const int h = i / (IT_HD / 4), c = i % (IT_HD / 4);
@@ -372,11 +376,67 @@ __global__ void __launch_bounds__(256) band_rescore_kernel(const uint8_t *keys, 
     }
 }
 
+// One block per sequence: the exact (want - keys above the band)-th largest score among the band's
+// re-scored keys is the exact want-th largest score of the sequence. given[2b] = its order-preserving
+// integer image, given[2b + 1] = how many keys equal to it are wanted; the compaction kernel takes it
+// from there and skips its own radix passes over the whole row.
+__global__ void __launch_bounds__(1024) band_select_kernel(const float *refined, int64_t stride, const int32_t *n, int want,
+                                                           const int32_t *band_list, const int32_t *band_count, uint32_t *given) {
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+    if (n[b] <= want) return;                 // the compaction kernel takes the whole prefix
+    const int cnt = band_count[2 * b];
+    int remaining = want - band_count[2 * b + 1];
+    remaining = max(1, min(remaining, cnt));   // holds by construction; clamped so that a violated error bound cannot index out of range
+    const float *f = refined + (int64_t)b * stride;
+    const int32_t *list = band_list + (int64_t)b * stride;
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t s_sel[2];
+    uint32_t prefix = 0, mask = 0;
+    for (int pass = 0; pass < 4; pass++) {
+        const int shift = 24 - 8 * pass;
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        for (int i = tid; i < cnt; i += 1024) {
+            const uint32_t k = order_key(f[list[i]]);
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid < 32) {
+            uint32_t c[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { c[j] = hist[lane * 8 + j]; tot += c[j]; }
+            uint32_t incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_down_sync(0xffffffffu, incl, o);
+                if (lane + o < 32) incl += t;
+            }
+            uint32_t above = incl - tot;
+            const uint32_t r = (uint32_t)remaining;
+            if (above < r && r <= above + tot) {
+#pragma unroll
+                for (int j = 7; j >= 0; j--) {
+                    if (r <= above + c[j]) {
+                        s_sel[0] = prefix | ((uint32_t)(lane * 8 + j) << shift);
+                        s_sel[1] = r - above;
+                        break;
+                    }
+                    above += c[j];
+                }
+            }
+        }
+        __syncthreads();
+        prefix = s_sel[0];
+        remaining = (int)s_sel[1];
+        mask |= 255u << shift;
+    }
+    if (tid == 0) { given[2 * b] = prefix; given[2 * b + 1] = (uint32_t)remaining; }
+}
+
 // q f32 [B][64][128] -> f16 [B][128][128]: one block per sequence. Every element is multiplied by
 // the magnitude of its head's weight (w ReLU(x) = sign(w) ReLU(|w| x)) and by a power of two that
 // brings the sequence's largest product into [2^13, 2^14); rows 0-63 hold the f16 roundings, rows
-// 64-127 the f16 roundings of the remainders. meta = {2^8 / scale (the 2^8 undoes the keys' 2^-8),
-// sign masks of the 64 head weights}.
+// 64-127 the f16 roundings of the remainders. meta = {1 / scale, sign masks of the 64 head weights}.
 __global__ void __launch_bounds__(256) split_q_kernel(const float *q, const float *wt, uint16_t *y, uint32_t *meta) {
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
     __shared__ float red[8];
@@ -406,7 +466,7 @@ __global__ void __launch_bounds__(256) split_q_kernel(const float *q, const floa
             inv = __uint_as_float((uint32_t)(127 - sh) << 23);
         }
         s_scale = scale;
-        meta[b * 4] = __float_as_uint(256.f * inv);
+        meta[b * 4] = __float_as_uint(inv);
     }
     if (tid < 64) {
         const uint32_t neg = __ballot_sync(0xffffffffu, wt[(int64_t)b * IT_IH + tid] < 0.f);
@@ -428,6 +488,9 @@ __global__ void __launch_bounds__(256) split_q_kernel(const float *q, const floa
 
 }  // namespace
 
+// the ordered compaction of cwk_topk_select with the threshold already known: given[2b] = its integer image, given[2b+1] = ties wanted
+int cwk_topk_compact(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int want, int keep_self, int32_t *sel,
+                     int64_t sel_ld, int32_t *nsel, const uint32_t *given);
 extern "C" int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int max_n, int B, int want,
                                int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel);
 extern "C" int cwk_indexer_scores_fp8(cwk_ctx *ctx, const void *keys, const float *kscale, int64_t key_stride, const float *q,
@@ -449,14 +512,15 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     // workspace: approx f32 [B][stride], refined f32 [B][stride], band list int32 [B][stride], q f16 hi|lo,
     // per-sequence scale and weight signs, band counts
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-    const size_t b_sc = up((size_t)B * key_stride * 4), b_q = up((size_t)B * 2 * ih * hd * 2), b_w = up((size_t)B * 16);
-    int s = cwk_reserve_work(ctx, 3 * b_sc + b_q + b_w + up((size_t)B * 4));
+    const size_t b_sc = up((size_t)B * key_stride * 4), b_q = up((size_t)B * 2 * ih * hd * 2), b_w = up((size_t)B * 16) + up((size_t)B * 8);
+    int s = cwk_reserve_work(ctx, 3 * b_sc + b_q + b_w + up((size_t)B * 8));
     if (s != CWK_OK) return s;
     uint8_t *w = (uint8_t *)ctx->work;
     float *approx = (float *)w, *refined = (float *)(w + b_sc);
     int32_t *band_list = (int32_t *)(w + 2 * b_sc);
     uint16_t *qb = (uint16_t *)(w + 3 * b_sc);
     uint32_t *meta = (uint32_t *)(w + 3 * b_sc + b_q);
+    uint32_t *given = meta + (up((size_t)B * 16) / 4);
     int32_t *band = (int32_t *)(w + 3 * b_sc + b_q + b_w);
     if (!tc_ok) {
         // shapes the tensor-core path is not built for: exact scores for every key
@@ -495,12 +559,14 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
         indexer_scores_tc_kernel<<<dim3(bps, B), IT_THREADS, I_SMEM, ctx->stream>>>(tm_keys, p);
         CWK_LAUNCH_CHECK(ctx, "indexer_scores_tc_kernel");
     }
-    CWK_CUDA(ctx, cudaMemsetAsync(band, 0, (size_t)B * sizeof(int32_t), ctx->stream));
+    CWK_CUDA(ctx, cudaMemsetAsync(band, 0, (size_t)B * 2 * sizeof(int32_t), ctx->stream));
     band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band);
     CWK_LAUNCH_CHECK(ctx, "band_classify_kernel");
     band_rescore_kernel<<<dim3(std::max(8, std::min(128, 2 * ctx->sm_count / B)), B), 256, RS_SMEM, ctx->stream>>>((const uint8_t *)keys, kscale, key_stride, q, wt, band_list, band,
                                                                    refined);
     CWK_LAUNCH_CHECK(ctx, "band_rescore_kernel");
+    band_select_kernel<<<B, 1024, 0, ctx->stream>>>(refined, key_stride, n, want, band_list, band, given);
+    CWK_LAUNCH_CHECK(ctx, "band_select_kernel");
     if (scores_out) CWK_CUDA(ctx, cudaMemcpyAsync(scores_out, refined, (size_t)B * key_stride * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-    return cwk_topk_select(ctx, refined, key_stride, n, max_n, B, want, keep_self, sel, sel_ld, nsel);
+    return cwk_topk_compact(ctx, refined, key_stride, n, B, want, keep_self, sel, sel_ld, nsel, given);
 }
