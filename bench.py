@@ -44,7 +44,7 @@ WORKLOADS = {
     # name: (sequences per call, cached tokens, calls per step)
     "c2": dict(B=1, T=8192, calls=ROT, desc="config 2: MLA absorbed decode, batch 1, 64 heads, 512+64 bf16, 8192 cached tokens"),
     "c5a": dict(B=64, T=32768, calls=1, desc="config 5a on one GPU: 64 sequences x 32768 cached tokens, one batched call"),
-    "c5b": dict(B=1, T=131072, calls=1, desc="config 5b: one sequence, 131072 cached tokens, KV rows split across the GPUs, partial records all-gathered (NCCL) and merged"),
+    "c5b": dict(B=1, T=131072, calls=1, desc="config 5b: one sequence, 131072 cached tokens, KV rows split across the GPUs, partial records exchanged and merged with a log-sum-exp combine"),
     "c5a8": dict(B=8, T=32768, calls=1, desc="config 5a, one GPU's share at 8 GPUs: 8 sequences x 32768 cached tokens, one batched call"),
 }
 
