@@ -49,21 +49,28 @@ constexpr int SMEM_USED = OFF_MISC + 2048;
 constexpr int SMEM_TOTAL = SMEM_USED + 1024;    // slack to align the base to 1024 B
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_O = 0, COL_S = 256;
-constexpr int HG = 32;                          // heads per softmax warp group
+constexpr int HG = 16;                          // heads per softmax warp group
+constexpr int NG = NH / HG;                     // 4 groups of four warps
 constexpr float LAZY_LOG2 = 16.f;               // a score may outrun the reference exponent by 2^16 before a rescale
-constexpr int NTHREADS = 384;
+constexpr int NSOFT = NG * 128;                 // 512 softmax threads
+constexpr int NTHREADS = 128 + NSOFT;           // 640
 
 // barrier slots (8 bytes each) inside OFF_BAR
 enum { B_FULL = 0, B_EMPTY_L = 9, B_EMPTY_RP = 13, B_QFULL = 14, B_SFULL = 15, B_PFULL = 16, B_COUNT = 17 };
 
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
-// v[0..31] per lane -> lane L returns the reduction over the 32 lanes of v[L] (31 shuffles,
-// halving the live values each stage instead of reducing every value on its own).
+// v[0..15] per lane -> lane L returns the reduction over the 32 lanes of v[L & 15]: the two half-warps
+// are folded first, then the live values halve at every stage (31 shuffles in all).
 template <bool IS_MAX>
-__device__ __forceinline__ float warp_transpose_reduce(float (&v)[32], int lane) {
+__device__ __forceinline__ float warp_transpose_reduce16(float (&v)[16], int lane) {
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
+    for (int i = 0; i < 16; i++) {
+        const float r = __shfl_xor_sync(0xffffffffu, v[i], 16);
+        v[i] = IS_MAX ? fmaxf(v[i], r) : v[i] + r;
+    }
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) {
         const bool hi = (lane & off) != 0;
 #pragma unroll
         for (int i = 0; i < off; i++) {
@@ -98,10 +105,9 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t bar0 = base + OFF_BAR;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + OFF_MISC);
-    int *s_flag = reinterpret_cast<int *>(sm + OFF_MISC + 16);        // [2][8]
     float *s_mref = reinterpret_cast<float *>(sm + OFF_MISC + 128);   // [64]
     float *s_alpha = s_mref + 64;                                     // [64]
-    float *s_w = s_alpha + 64;                                        // [8 warps][32] per-warp max / sum
+    float *s_w = s_alpha + 64;                                        // [16 warps][16] per-warp max / sum
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = p.reverse_b ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
@@ -126,7 +132,7 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kv) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kr) : "memory");
-        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), i == B_PFULL ? 256u : 1u);
+        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), i == B_PFULL ? (uint32_t)NSOFT : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // The first tile's loads go out before the block-wide set-up (TMEM allocation, the
         // barrier below): nothing they touch depends on it, and their latency is the longest
@@ -237,13 +243,13 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ softmax / correction / epilogue
-        // Two groups of four warps: group g owns heads [32g, 32g+32) (S^T / O^T columns); inside a
+        // Four groups of four warps: group g owns heads [16g, 16g+16) (S^T / O^T columns); inside a
         // group, warp w owns TMEM lanes 32*(w%4).. = token rows (S^T) or dv rows (O^T).
         const int q = warp & 3;                       // TMEM lane quarter
         const int g = (warp - 4) >> 2;                // head group
         const int hb = g * HG;                        // first head of the group
         const int row = q * 32 + lane;                // token row inside the tile == TMEM lane
-        const int st = tid - 128;                     // 0..255
+        const int st = tid - 128;                     // 0..511
         const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
         float lpart[HG];
 #pragma unroll
@@ -256,8 +262,8 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             tc_fence_after();
             uint32_t sr[HG];
             TMEM_LD16(sr, 0, tlane + COL_S + hb);
-            TMEM_LD16(sr, 16, tlane + COL_S + hb + 16);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (st == 0) TRACE(2, it, 5);
             const bool valid = (t0 + it) * TILE + row < kv;
             float s[HG];
 #pragma unroll
@@ -272,29 +278,32 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
                 softmax_bar();
             }
+            // Probabilities against the current reference exponent, computed BEFORE the block agrees on
+            // whether a rescale is needed: the exponentials fill the time the barrier spends waiting for
+            // the slowest warp, and in the common case (no rescale) they are the final values.
+            float pv[HG];
             bool ex = false;
 #pragma unroll
             for (int h = 0; h < HG; h += 4) {
                 const float4 mr = *reinterpret_cast<const float4 *>(s_mref + hb + h);
-                ex |= (s[h] > mr.x + LAZY_LOG2) | (s[h + 1] > mr.y + LAZY_LOG2) | (s[h + 2] > mr.z + LAZY_LOG2) |
-                      (s[h + 3] > mr.w + LAZY_LOG2);
+                const float d0 = s[h] - mr.x, d1 = s[h + 1] - mr.y, d2 = s[h + 2] - mr.z, d3 = s[h + 3] - mr.w;
+                ex |= (d0 > LAZY_LOG2) | (d1 > LAZY_LOG2) | (d2 > LAZY_LOG2) | (d3 > LAZY_LOG2);
+                pv[h] = exp2f(d0); pv[h + 1] = exp2f(d1); pv[h + 2] = exp2f(d2); pv[h + 3] = exp2f(d3);
             }
-            const int any = __any_sync(0xffffffffu, ex);
-            if (lane == 0) s_flag[(it & 1) * 8 + (warp - 4)] = any;
-            softmax_bar();
-            int need = 0;
-#pragma unroll
-            for (int w = 0; w < 8; w++) need |= s_flag[(it & 1) * 8 + w];
+            uint32_t need;
+            asm volatile("{\n.reg .pred pi, po;\nsetp.ne.b32 pi, %1, 0;\nbar.red.or.pred po, 1, 512, pi;\nselp.u32 %0, 1, 0, po;\n}\n"
+                         : "=r"(need) : "r"((uint32_t)ex) : "memory");
+            if (st == 0) TRACE(2, it, 6);
             if (need) {
                 // exact column maxima over the 128 tokens, new reference, rescale what exists
                 float v[HG];
 #pragma unroll
                 for (int h = 0; h < HG; h++) v[h] = s[h];
-                const float mine = warp_transpose_reduce<true>(v, lane);     // lane L: max of head hb+L over this warp's rows
-                s_w[(warp - 4) * HG + lane] = mine;
+                const float mine = warp_transpose_reduce16<true>(v, lane);   // lane L: max of head hb+(L&15) over this warp's rows
+                if (lane < HG) s_w[(warp - 4) * HG + lane] = mine;
                 softmax_bar();
                 if (st < NH) {
-                    const int gg = st >> 5, hh = st & 31;
+                    const int gg = st / HG, hh = st % HG;
                     const float *w4 = s_w + gg * 4 * HG + hh;
                     const float M = fmaxf(fmaxf(w4[0], w4[HG]), fmaxf(w4[2 * HG], w4[3 * HG]));
                     const float mo = s_mref[st];
@@ -307,45 +316,43 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 for (int h = 0; h < HG; h++) lpart[h] *= s_alpha[hb + h];
                 if (it > 0) {
                     // O^T columns are heads: scale column h of every dv block by alpha[h]
-                    for (int cb = 0; cb < 8; cb++) {
+                    for (int mb = 0; mb < 4; mb++) {
                         uint32_t o[16];
-                        const uint32_t ta = tlane + COL_O + (cb >> 1) * 64 + hb + (cb & 1) * 16;
+                        const uint32_t ta = tlane + COL_O + mb * 64 + hb;
                         TMEM_LD16(o, 0, ta);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int j = 0; j < 16; j++)
-                            o[j] = __float_as_uint(__uint_as_float(o[j]) * s_alpha[hb + (cb & 1) * 16 + j]);
+                            o[j] = __float_as_uint(__uint_as_float(o[j]) * s_alpha[hb + j]);
                         TMEM_ST16(o, 0, ta);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
             }
+            if (need) {         // the reference moved: probabilities against the new one
+#pragma unroll
+                for (int h = 0; h < HG; h++) pv[h] = exp2f(s[h] - s_mref[hb + h]);
+            }
             // P^T row of this token -> the rope block's slot, MN-major, 128-byte swizzle
             uint8_t *prow = sm + OFF_KV + RP * KV_BLK + row * 128;
 #pragma unroll
             for (int c = 0; c < HG / 8; c++) {
-                float pv[8];
-                const float4 m0 = *reinterpret_cast<const float4 *>(s_mref + hb + c * 8);
-                const float4 m1 = *reinterpret_cast<const float4 *>(s_mref + hb + c * 8 + 4);
-                pv[0] = exp2f(s[c * 8 + 0] - m0.x); pv[1] = exp2f(s[c * 8 + 1] - m0.y);
-                pv[2] = exp2f(s[c * 8 + 2] - m0.z); pv[3] = exp2f(s[c * 8 + 3] - m0.w);
-                pv[4] = exp2f(s[c * 8 + 4] - m1.x); pv[5] = exp2f(s[c * 8 + 5] - m1.y);
-                pv[6] = exp2f(s[c * 8 + 6] - m1.z); pv[7] = exp2f(s[c * 8 + 7] - m1.w);
 #pragma unroll
-                for (int j = 0; j < 8; j++) lpart[c * 8 + j] += pv[j];
+                for (int j = 0; j < 8; j++) lpart[c * 8 + j] += pv[c * 8 + j];
                 uint4 w;
-                w.x = pack_bf16x2(pv[0], pv[1]); w.y = pack_bf16x2(pv[2], pv[3]);
-                w.z = pack_bf16x2(pv[4], pv[5]); w.w = pack_bf16x2(pv[6], pv[7]);
+                w.x = pack_bf16x2(pv[c * 8 + 0], pv[c * 8 + 1]); w.y = pack_bf16x2(pv[c * 8 + 2], pv[c * 8 + 3]);
+                w.z = pack_bf16x2(pv[c * 8 + 4], pv[c * 8 + 5]); w.w = pack_bf16x2(pv[c * 8 + 6], pv[c * 8 + 7]);
                 *reinterpret_cast<uint4 *>(prow + (((g * (HG / 8) + c) ^ (row & 7)) << 4)) = w;
             }
             if (!valid) {       // rows past the sequence end hold whatever the cache holds: 0 x NaN would poison O
                 const uint4 z = make_uint4(0, 0, 0, 0);
-                for (int k = g * 4; k < g * 4 + 4; k++) {
+                for (int k = g * 2; k < g * 2 + 2; k++) {
                     uint8_t *vrow = sm + OFF_KV + k * KV_BLK + row * 128;
 #pragma unroll
                     for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(vrow + (c << 4)) = z;
                 }
             }
+            if (st == 0) TRACE(2, it, 7);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             mbar_arrive(bar(B_PFULL));
@@ -356,12 +363,12 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (ok) {
             if (st == 0) TRACE(2, 15, 2);
             tc_fence_after();
-            const float mine = warp_transpose_reduce<false>(lpart, lane);    // lane L: sum of head hb+L over this warp's rows
-            s_w[(warp - 4) * HG + lane] = mine;
+            const float mine = warp_transpose_reduce16<false>(lpart, lane);  // lane L: sum of head hb+(L&15) over this warp's rows
+            if (lane < HG) s_w[(warp - 4) * HG + lane] = mine;
             if (st == 0) TRACE(2, 15, 3);
             softmax_bar();
             if (st < NH) {
-                const int gg = st >> 5, hh = st & 31;
+                const int gg = st / HG, hh = st % HG;
                 const float *w4 = s_w + gg * 4 * HG + hh;
                 const float lsum = (w4[0] + w4[HG]) + (w4[2 * HG] + w4[3 * HG]);
                 if (p.out) {
@@ -373,9 +380,9 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             if (p.out) softmax_bar();
             if (st == 0) TRACE(2, 15, 4);
-            for (int cb = 0; cb < 8; cb++) {
+            for (int mb = 0; mb < 4; mb++) {
                 uint32_t o[16];
-                const int mb = cb >> 1, h0 = hb + (cb & 1) * 16;
+                const int h0 = hb;
                 TMEM_LD16(o, 0, tlane + COL_O + mb * 64 + h0);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (p.out) {
