@@ -26,7 +26,8 @@ constexpr int AT_W_BYTES = AT_NOPE * AT_L * 2;      // 131072: eight [128 k][64 
 constexpr int AT_A_BYTES = AT_TOK * AT_NOPE * 2;    // 32768: two [128 tok][64 k] blocks
 constexpr int AT_OFF_W = 0;
 constexpr int AT_OFF_A = AT_W_BYTES;                // two stages
-constexpr int AT_OFF_BAR = AT_OFF_A + 2 * AT_A_BYTES;
+constexpr int AT_OFF_STG = AT_OFF_A + 2 * AT_A_BYTES;   // 8 epilogue warps x [32 rows][128 B] staging for full-line stores
+constexpr int AT_OFF_BAR = AT_OFF_STG + 8 * 4096;
 constexpr int AT_SMEM = AT_OFF_BAR + 256 + 1024;
 constexpr int AT_THREADS = 384;
 enum { AB_WFULL = 0, AB_AFULL = 1, AB_AEMPTY = 3, AB_DFULL = 5, AB_DEMPTY = 7, AB_COUNT = 9 };
@@ -129,7 +130,11 @@ absorb_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (ok) ok = mbar_wait(bar(AB_DFULL + half), (uint32_t)(i & 1), p.err, 907);
                 if (!ok) break;
                 tc_fence_after();
-                uint16_t *dst = p.qfull + ((int64_t)t * p.nh + h) * AT_ROW + half * 256 + g2 * 128;
+                // A thread holds one token row of the accumulator, and rows of Qfull lie 73 KB apart: storing from
+                // the registers would touch 32 lines per instruction, 16 bytes each. The 64 columns of a pass go
+                // through a per-warp staging tile instead, and leave as whole 128-byte lines, four rows per instruction.
+                uint8_t *stg = sm + AT_OFF_STG + (warp - 4) * 4096;
+                const int t0w = t - lane;                   // first token row of this warp
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
                     uint32_t v[64];
@@ -139,17 +144,24 @@ absorb_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     TMEM_LD16(v, 32, tlane + col + 32);
                     TMEM_LD16(v, 48, tlane + col + 48);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (t < p.n) {
 #pragma unroll
-                        for (int j = 0; j < 64; j += 8) {
-                            uint4 w;
-                            w.x = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                            w.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                            w.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-                            w.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                            *reinterpret_cast<uint4 *>(dst + c * 64 + j) = w;
-                        }
+                    for (int j = 0; j < 8; j++) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
+                        w.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                        w.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                        w.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                        *reinterpret_cast<uint4 *>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
                     }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int rr = i * 4 + (lane >> 3), jj = lane & 7;
+                        const uint4 w = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
+                        if (t0w + rr < p.n)
+                            *reinterpret_cast<uint4 *>(p.qfull + ((int64_t)(t0w + rr) * p.nh + h) * AT_ROW + col + jj * 8) = w;
+                    }
+                    __syncwarp();
                 }
                 tc_fence_before();
                 mbar_arrive(bar(AB_DEMPTY + half));

@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(128) indexer_scores_fp8_kernel(
 // it in index order, `want` in all (ascending: one list in index order).
 __global__ void __cluster_dims__(TK_CL, 1, 1) __launch_bounds__(TK_THREADS, 1)
 topk_select_kernel(const float *sc, int64_t sc_stride, const int32_t *n, int want, int keep_self, int32_t *sel, int64_t sel_ld,
-                   int32_t *nsel, int ascending, const uint32_t *given) {
+                   int32_t *nsel, int ascending, const int32_t *band_list, const int32_t *band_count) {
     cg::cluster_group cl = cg::this_cluster();
     const unsigned rank = cl.block_rank();
     const int b = blockIdx.y, tid = threadIdx.x;
@@ -92,10 +92,13 @@ topk_select_kernel(const float *sc, int64_t sc_stride, const int32_t *n, int wan
     if (tid == 0) sh.pub = 0;
     uint32_t thr;
     int need_eq;
-    if (given) {                            // the caller already knows the threshold
-        thr = given[2 * b];
-        need_eq = (int)given[2 * b + 1];
-        __syncthreads();                    // sh.pub = 0 before the atomics below
+    if (band_list) {
+        // The row holds +inf / -inf outside a short list of re-scored positions (cwk_dsa_select): the exact
+        // threshold is the (want - certainly selected)-th largest score of that list. Every block of the
+        // cluster finds it for itself; the list is a few hundred entries.
+        const int cnt = band_count[2 * b];
+        const int kth = max(1, min(want - band_count[2 * b + 1], cnt));   // holds by construction; clamped against a violated error bound
+        tk_list_select(s, band_list + (int64_t)b * sc_stride, cnt, kth, sh, thr, need_eq);
     } else {
         tk_radix_select(s, sl, kc, want, sh, thr, need_eq);
     }
@@ -217,7 +220,7 @@ int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int3
     (void)max_n;
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     CwkKernelTimer timer(ctx);
-    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel, 0, nullptr);
+    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel, 0, nullptr, nullptr);
     CWK_LAUNCH_CHECK(ctx, "topk_select_kernel");
     return CWK_OK;
 }
@@ -225,9 +228,9 @@ int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int3
 }  // extern "C"
 
 int cwk_topk_compact(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int want, int keep_self, int32_t *sel,
-                     int64_t sel_ld, int32_t *nsel, const uint32_t *given) {
+                     int64_t sel_ld, int32_t *nsel, const int32_t *band_list, const int32_t *band_count) {
     CwkKernelTimer timer(ctx);
-    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel, 0, given);
+    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel, 0, band_list, band_count);
     CWK_LAUNCH_CHECK(ctx, "topk_select_kernel(compaction)");
     return CWK_OK;
 }
@@ -240,7 +243,7 @@ int cwk_ds_topk(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t 
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_topk: bad argument");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     CwkKernelTimer timer(ctx);
-    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, k, 0, out, out_ld, count, 1, nullptr);
+    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, k, 0, out, out_ld, count, 1, nullptr, nullptr);
     CWK_LAUNCH_CHECK(ctx, "topk_select_kernel<ascending>");
     return CWK_OK;
 }

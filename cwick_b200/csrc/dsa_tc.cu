@@ -1,3 +1,30 @@
+// dsa_tc.cu -- the DSA lightning indexer on tensor cores, with exact selection (cwk_dsa_select).
+//
+// The reference's score is an f32 sum in a fixed order (src/attention.c:573-582); a tensor-core
+// contraction accumulates in another order, so its scores can differ in the last bits and flip
+// candidates that sit on the selection threshold. The selection here is still exact:
+//
+//   1. indexer_scores_tc_kernel: approximate scores a[c] for every key with tcgen05 MMAs.
+//      Keys are E4M3 codes with a positive per-key scale, so
+//        sum_h w_h ReLU(q_h . (code_c * s_c)) = s_c * sum_h sign(w_h) ReLU(|w_h| q_h . code_c):
+//      the codes are widened to f16 (exact) on their way through shared memory; the f32 query,
+//      times |w_h| and a power of two, is split into an f16 high part and an f16 low part (128 MMA
+//      columns), so the MMA D[128 keys][hi|lo] = codes . q^T has exact products and f32
+//      accumulation, and the epilogue adds the two halves, applies ReLU, the signs and the key's scale.
+//   2. band_classify_kernel: a radix select on a[] gives the approximate want-th largest score tau.
+//      The want-th largest value moves by at most delta when every score moves by at most delta, so
+//      keys with a > tau + 2*delta are certainly selected (refined = +inf), keys with
+//      a < tau - 2*delta certainly are not (-inf), and the band in between is listed. (delta is
+//      taken as 2^-9 of the row's largest score, far above the contraction's and the query
+//      split's worst case.)
+//   3. band_rescore_kernel: the listed keys are re-scored in the reference's exact order on CUDA cores.
+//   4. the selection kernel (csrc/dsa.cu) takes the exact threshold from the re-scored keys and
+//      writes the reference's list in the reference's order.
+//
+// Pipeline of step 1 per 128-key tile: TMA (raw E4M3 tile, 16 KB) -> 8 converter warps
+// (cvt.rn.f16x2.e4m3x2 into two 128-byte-swizzled K-major blocks) -> MMA issuer (8 MMAs, M 128,
+// N 128) -> 4 epilogue warps (TMEM -> a[c]). Blocks are persistent over the tiles of one sequence.
+// Every mbarrier wait is bounded and records a code in the context's error word when it gives up.
 #include <algorithm>
 
 #include <cuda_fp16.h>
@@ -17,7 +44,7 @@ constexpr int I_OFF_Q = 0;
 constexpr int I_OFF_A = Q_BYTES_I;                      // 2 buffers
 constexpr int I_OFF_RAW = I_OFF_A + 2 * A_BYTES_I;      // 4 stages
 constexpr int I_OFF_BAR = I_OFF_RAW + RAW_STAGES * RAW_BYTES;
-constexpr int I_OFF_W = I_OFF_BAR + 256;                // head weights f32 [64]
+constexpr int I_OFF_W = I_OFF_BAR + 256;                // 19 words: warp maxima of the query split, 1 / scale, sign masks of the head weights
 constexpr int I_SMEM = I_OFF_W + 256 + 1024;
 constexpr int IT_THREADS = 512;                          // TMA, MMA, 2 idle | 8 converter warps | 4 epilogue warps
 constexpr int IT_CONV = 256;
@@ -38,8 +65,8 @@ __device__ __forceinline__ uint2 e4m3x4_f16x4(uint32_t w) {
 
 struct IdxParams {
     const float *kscale;      // [B][key_stride]
-    const uint16_t *q;        // f16 [B][128][128]: rows 0-63 the high parts of q * |head weight| * scale, 64-127 the low parts
-    const uint32_t *meta;     // [B][4]: f32 1 / scale, sign mask of head weights 0-31, of 32-63, unused
+    const float *q;           // f32 [B][64][128]
+    const float *wt;          // f32 [B][64] head weights
     const int32_t *n;         // [B]
     float *sc;                // [B][key_stride]
     int64_t key_stride;
@@ -81,11 +108,59 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(256u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // q of this sequence: [128][128] f16 -> two swizzled [128][64] blocks (plain loads, once per block)
-    for (int i = tid; i < IT_QROWS * 16; i += IT_THREADS) {
-        const int r = i >> 4, c = i & 15;                      // 16-byte chunk c of row r
-        const uint4 v = *reinterpret_cast<const uint4 *>(p.q + ((int64_t)b * IT_QROWS + r) * IT_HD + c * 8);
-        *reinterpret_cast<uint4 *>(sm + I_OFF_Q + (c >> 3) * (IT_QROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+    // The B operand, built once per block from the f32 query of this sequence: every element is multiplied by
+    // the magnitude of its head's weight (w ReLU(x) = sign(w) ReLU(|w| x)) and by a power of two that brings the
+    // sequence's largest product into [2^13, 2^14); rows 0-63 of the operand hold the f16 roundings, rows 64-127
+    // the f16 roundings of the remainders (22 bits of every product survive). Two swizzled [128][64] blocks.
+    float *s_red = reinterpret_cast<float *>(sm + I_OFF_W);           // [16] warp maxima, then [16] = 1 / scale, [17..18] sign masks
+    {
+        const int h = tid >> 3, d0 = (tid & 7) * 16;
+        const float w = fabsf(p.wt[(int64_t)b * IT_IH + h]);
+        float x[16];
+        float m = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(p.q + ((int64_t)b * IT_IH + h) * IT_HD + d0 + j);
+            x[j] = v.x * w; x[j + 1] = v.y * w; x[j + 2] = v.z * w; x[j + 3] = v.w * w;
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(x[j]), fabsf(x[j + 1])), fmaxf(fabsf(x[j + 2]), fabsf(x[j + 3]))));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) s_red[warp] = m;
+        if (tid < IT_IH) {
+            const uint32_t neg = __ballot_sync(0xffffffffu, p.wt[(int64_t)b * IT_IH + tid] < 0.f);
+            if (lane == 0) reinterpret_cast<uint32_t *>(s_red)[17 + warp] = neg;
+        }
+        __syncthreads();
+        m = 0.f;
+#pragma unroll
+        for (int i = 0; i < IT_THREADS / 32; i++) m = fmaxf(m, s_red[i]);
+        float scale = 1.f, inv = 1.f;
+        if (m > 0.f && m < INFINITY) {
+            const int e = (int)((__float_as_uint(m) >> 23) & 255u) - 127;     // floor(log2 m) for normal m
+            const int sh = max(-100, min(100, 13 - e));
+            scale = __uint_as_float((uint32_t)(127 + sh) << 23);
+            inv = __uint_as_float((uint32_t)(127 - sh) << 23);
+        }
+        if (tid == 0) s_red[16] = inv;
+        uint32_t hi[8], lo[8];
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+            const float a0 = x[j] * scale, a1 = x[j + 1] * scale;
+            const __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
+            const __half l0 = __float2half_rn(a0 - __half2float(h0)), l1 = __float2half_rn(a1 - __half2float(h1));
+            hi[j >> 1] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+            lo[j >> 1] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+        }
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const int c16 = (tid & 7) * 2 + c;                                 // 16-byte chunk of the 256-byte row
+            uint8_t *blk = sm + I_OFF_Q + (c16 >> 3) * (IT_QROWS * 128);
+            const int cc = c16 & 7;
+            *reinterpret_cast<uint4 *>(blk + h * 128 + ((cc ^ (h & 7)) << 4)) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+            *reinterpret_cast<uint4 *>(blk + (IT_IH + h) * 128 + ((cc ^ ((IT_IH + h) & 7)) << 4)) =
+                make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+        }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
@@ -158,8 +233,8 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
         const int q4 = warp & 3;
         const int row = q4 * 32 + lane;
         const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
-        const float unscale = __uint_as_float(p.meta[b * 4]);
-        const uint32_t neg[2] = {p.meta[b * 4 + 1], p.meta[b * 4 + 2]};
+        const float unscale = s_red[16];
+        const uint32_t neg[2] = {reinterpret_cast<const uint32_t *>(s_red)[17], reinterpret_cast<const uint32_t *>(s_red)[18]};
         const bool any_neg = (neg[0] | neg[1]) != 0;
         bool ok = true;
         for (int i = 0; i < nt; i++) {
@@ -376,121 +451,11 @@ __global__ void __launch_bounds__(256) band_rescore_kernel(const uint8_t *keys, 
     }
 }
 
-// One block per sequence: the exact (want - keys above the band)-th largest score among the band's
-// re-scored keys is the exact want-th largest score of the sequence. given[2b] = its order-preserving
-// integer image, given[2b + 1] = how many keys equal to it are wanted; the compaction kernel takes it
-// from there and skips its own radix passes over the whole row.
-__global__ void __launch_bounds__(1024) band_select_kernel(const float *refined, int64_t stride, const int32_t *n, int want,
-                                                           const int32_t *band_list, const int32_t *band_count, uint32_t *given) {
-    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
-    if (n[b] <= want) return;                 // the compaction kernel takes the whole prefix
-    const int cnt = band_count[2 * b];
-    int remaining = want - band_count[2 * b + 1];
-    remaining = max(1, min(remaining, cnt));   // holds by construction; clamped so that a violated error bound cannot index out of range
-    const float *f = refined + (int64_t)b * stride;
-    const int32_t *list = band_list + (int64_t)b * stride;
-    __shared__ uint32_t hist[256];
-    __shared__ uint32_t s_sel[2];
-    uint32_t prefix = 0, mask = 0;
-    for (int pass = 0; pass < 4; pass++) {
-        const int shift = 24 - 8 * pass;
-        if (tid < 256) hist[tid] = 0;
-        __syncthreads();
-        for (int i = tid; i < cnt; i += 1024) {
-            const uint32_t k = order_key(f[list[i]]);
-            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        if (tid < 32) {
-            uint32_t c[8], tot = 0;
-#pragma unroll
-            for (int j = 0; j < 8; j++) { c[j] = hist[lane * 8 + j]; tot += c[j]; }
-            uint32_t incl = tot;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_down_sync(0xffffffffu, incl, o);
-                if (lane + o < 32) incl += t;
-            }
-            uint32_t above = incl - tot;
-            const uint32_t r = (uint32_t)remaining;
-            if (above < r && r <= above + tot) {
-#pragma unroll
-                for (int j = 7; j >= 0; j--) {
-                    if (r <= above + c[j]) {
-                        s_sel[0] = prefix | ((uint32_t)(lane * 8 + j) << shift);
-                        s_sel[1] = r - above;
-                        break;
-                    }
-                    above += c[j];
-                }
-            }
-        }
-        __syncthreads();
-        prefix = s_sel[0];
-        remaining = (int)s_sel[1];
-        mask |= 255u << shift;
-    }
-    if (tid == 0) { given[2 * b] = prefix; given[2 * b + 1] = (uint32_t)remaining; }
-}
-
-// q f32 [B][64][128] -> f16 [B][128][128]: one block per sequence. Every element is multiplied by
-// the magnitude of its head's weight (w ReLU(x) = sign(w) ReLU(|w| x)) and by a power of two that
-// brings the sequence's largest product into [2^13, 2^14); rows 0-63 hold the f16 roundings, rows
-// 64-127 the f16 roundings of the remainders. meta = {1 / scale, sign masks of the 64 head weights}.
-__global__ void __launch_bounds__(256) split_q_kernel(const float *q, const float *wt, uint16_t *y, uint32_t *meta) {
-    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
-    __shared__ float red[8];
-    __shared__ float s_scale;
-    float x[32];
-    float m = 0.f;
-    const int h = tid >> 2, d0 = (tid & 3) * 32;
-    const float w = fabsf(wt[(int64_t)b * IT_IH + h]);
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-        const float4 v = *reinterpret_cast<const float4 *>(q + ((int64_t)b * IT_IH + h) * IT_HD + d0 + j);
-        x[j] = v.x * w; x[j + 1] = v.y * w; x[j + 2] = v.z * w; x[j + 3] = v.w * w;
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(x[j]), fabsf(x[j + 1])), fmaxf(fabsf(x[j + 2]), fabsf(x[j + 3]))));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) red[tid >> 5] = m;
-    __syncthreads();
-    if (tid == 0) {
-        m = 0.f;
-        for (int i = 0; i < 8; i++) m = fmaxf(m, red[i]);
-        float scale = 1.f, inv = 1.f;
-        if (m > 0.f && m < INFINITY) {
-            const int e = (int)((__float_as_uint(m) >> 23) & 255u) - 127;     // floor(log2 m) for normal m
-            const int sh = max(-100, min(100, 13 - e));
-            scale = __uint_as_float((uint32_t)(127 + sh) << 23);
-            inv = __uint_as_float((uint32_t)(127 - sh) << 23);
-        }
-        s_scale = scale;
-        meta[b * 4] = __float_as_uint(inv);
-    }
-    if (tid < 64) {
-        const uint32_t neg = __ballot_sync(0xffffffffu, wt[(int64_t)b * IT_IH + tid] < 0.f);
-        if (lane == 0) meta[b * 4 + 1 + (tid >> 5)] = neg;
-    }
-    __syncthreads();
-    const float scale = s_scale;
-    uint16_t *yh = y + ((int64_t)b * IT_QROWS + h) * IT_HD + d0;
-    uint16_t *yl = y + ((int64_t)b * IT_QROWS + IT_IH + h) * IT_HD + d0;
-#pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-        const float a0 = x[j] * scale, a1 = x[j + 1] * scale;
-        const __half h0 = __float2half_rn(a0), h1 = __float2half_rn(a1);
-        const __half l0 = __float2half_rn(a0 - __half2float(h0)), l1 = __float2half_rn(a1 - __half2float(h1));
-        *reinterpret_cast<uint32_t *>(yh + j) = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
-        *reinterpret_cast<uint32_t *>(yl + j) = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
-    }
-}
-
 }  // namespace
 
-// the ordered compaction of cwk_topk_select with the threshold already known: given[2b] = its integer image, given[2b+1] = ties wanted
+// cwk_topk_select over a refined row: the threshold comes from the band's re-scored keys only, then the ordered compaction
 int cwk_topk_compact(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int want, int keep_self, int32_t *sel,
-                     int64_t sel_ld, int32_t *nsel, const uint32_t *given);
+                     int64_t sel_ld, int32_t *nsel, const int32_t *band_list, const int32_t *band_count);
 extern "C" int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int max_n, int B, int want,
                                int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel);
 extern "C" int cwk_indexer_scores_fp8(cwk_ctx *ctx, const void *keys, const float *kscale, int64_t key_stride, const float *q,
@@ -509,19 +474,15 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     }
     const bool tc_ok = ih == IT_IH && hd == IT_HD && ((uintptr_t)keys % 16) == 0 && cwk_encode_tiled_fn() != nullptr &&
                        ctx->force_mla_path != 0 && ctx->force_mla_path != 1;
-    // workspace: approx f32 [B][stride], refined f32 [B][stride], band list int32 [B][stride], q f16 hi|lo,
-    // per-sequence scale and weight signs, band counts
+    // workspace: approx f32 [B][stride], refined f32 [B][stride], band list int32 [B][stride], band counts [B][2]
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-    const size_t b_sc = up((size_t)B * key_stride * 4), b_q = up((size_t)B * 2 * ih * hd * 2), b_w = up((size_t)B * 16) + up((size_t)B * 8);
-    int s = cwk_reserve_work(ctx, 3 * b_sc + b_q + b_w + up((size_t)B * 8));
+    const size_t b_sc = up((size_t)B * key_stride * 4);
+    int s = cwk_reserve_work(ctx, 3 * b_sc + up((size_t)B * 8));
     if (s != CWK_OK) return s;
     uint8_t *w = (uint8_t *)ctx->work;
     float *approx = (float *)w, *refined = (float *)(w + b_sc);
     int32_t *band_list = (int32_t *)(w + 2 * b_sc);
-    uint16_t *qb = (uint16_t *)(w + 3 * b_sc);
-    uint32_t *meta = (uint32_t *)(w + 3 * b_sc + b_q);
-    uint32_t *given = meta + (up((size_t)B * 16) / 4);
-    int32_t *band = (int32_t *)(w + 3 * b_sc + b_q + b_w);
+    int32_t *band = (int32_t *)(w + 3 * b_sc);
     if (!tc_ok) {
         // shapes the tensor-core path is not built for: exact scores for every key
         s = cwk_indexer_scores_fp8(ctx, keys, kscale, key_stride, q, wt, n, max_n, B, ih, hd, scores_out ? scores_out : approx);
@@ -530,8 +491,6 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     }
     s = cwk_ensure_err_word(ctx);
     if (s != CWK_OK) return s;
-    split_q_kernel<<<B, 256, 0, ctx->stream>>>(q, wt, qb, meta);
-    CWK_LAUNCH_CHECK(ctx, "split_q_kernel");
     CUtensorMap tm_keys;
     {
         CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
@@ -551,7 +510,7 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
         attr_set[ctx->device & 15] = true;
     }
     IdxParams p;
-    p.kscale = kscale; p.q = qb; p.meta = meta; p.n = n; p.sc = approx; p.key_stride = key_stride; p.err = ctx->dev_err;
+    p.kscale = kscale; p.q = q; p.wt = wt; p.n = n; p.sc = approx; p.key_stride = key_stride; p.err = ctx->dev_err;
     const int tiles = (max_n + IT_KEYS - 1) / IT_KEYS;
     const int bps = std::max(1, std::min(tiles, ctx->sm_count / B));
     {
@@ -562,11 +521,9 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     CWK_CUDA(ctx, cudaMemsetAsync(band, 0, (size_t)B * 2 * sizeof(int32_t), ctx->stream));
     band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band);
     CWK_LAUNCH_CHECK(ctx, "band_classify_kernel");
-    band_rescore_kernel<<<dim3(std::max(8, std::min(128, 2 * ctx->sm_count / B)), B), 256, RS_SMEM, ctx->stream>>>((const uint8_t *)keys, kscale, key_stride, q, wt, band_list, band,
+    band_rescore_kernel<<<dim3(std::max(1, ctx->sm_count / B), B), 256, RS_SMEM, ctx->stream>>>((const uint8_t *)keys, kscale, key_stride, q, wt, band_list, band,
                                                                    refined);
     CWK_LAUNCH_CHECK(ctx, "band_rescore_kernel");
-    band_select_kernel<<<B, 1024, 0, ctx->stream>>>(refined, key_stride, n, want, band_list, band, given);
-    CWK_LAUNCH_CHECK(ctx, "band_select_kernel");
     if (scores_out) CWK_CUDA(ctx, cudaMemcpyAsync(scores_out, refined, (size_t)B * key_stride * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-    return cwk_topk_compact(ctx, refined, key_stride, n, B, want, keep_self, sel, sel_ld, nsel, given);
+    return cwk_topk_compact(ctx, refined, key_stride, n, B, want, keep_self, sel, sel_ld, nsel, band_list, band);
 }

@@ -65,17 +65,25 @@ __global__ void __launch_bounds__(256) e4m3_to_bf16_kernel(const uint8_t *src, u
     reinterpret_cast<uint4 *>(dst)[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-struct GemmParams {
+// One launch serves one projection, or two that share the activations X (q_a and kv_a of the MLA
+// prefill: alone they fill 1.3 and 0.65 waves of the SMs): column tiles [0, tiles_a) belong to the
+// first weight matrix, the rest to the second.
+struct GemmProblem {
     const float *scale_inv;
-    int64_t n, k, cols;
+    int64_t cols;
     void *Y;
     int out_bf16;
+};
+struct GemmParams {
+    GemmProblem pr[2];
+    int tiles_a;               // column tiles of the first problem
+    int64_t n, k;
     int *err;
 };
 
 __global__ void __launch_bounds__(G_THREADS, 1)
 fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                     const GemmParams p) {
+                     const __grid_constant__ CUtensorMap tm_w2, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -85,12 +93,19 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + G_OFF_BAR + 8 * GB_COUNT + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int col0 = blockIdx.x * BN, row0 = blockIdx.y * BM;
+    const int second = (int)blockIdx.x >= p.tiles_a;
+    GemmProblem pp;            // field-wise select: indexing the parameter struct with a run-time index would copy it to local memory
+    pp.scale_inv = second ? p.pr[1].scale_inv : p.pr[0].scale_inv;
+    pp.cols = second ? p.pr[1].cols : p.pr[0].cols;
+    pp.Y = second ? p.pr[1].Y : p.pr[0].Y;
+    pp.out_bf16 = second ? p.pr[1].out_bf16 : p.pr[0].out_bf16;
+    const int col0 = ((int)blockIdx.x - (second ? p.tiles_a : 0)) * BN, row0 = blockIdx.y * BM;
     const int nkb = (int)(p.k / 128);              // scale blocks along K = pipeline steps
 
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_x) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+        if (second) asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w2) : "memory");
+        else asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
         for (int i = 0; i < GB_COUNT; i++) mbar_init(bar(i), (i >= GB_PEMPTY) ? 256u : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -113,7 +128,9 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
                 if (!ok) break;
                 mbar_expect_tx(bar(GB_FULL + slot), A_BYTES + B_BYTES);
                 tma_load_3d(base + slot * (A_BYTES + B_BYTES), &tm_x, 0, row0, s * 2, bar(GB_FULL + slot));
-                tma_load_3d(base + slot * (A_BYTES + B_BYTES) + A_BYTES, &tm_w, 0, col0, s * 2, bar(GB_FULL + slot));
+                // (the maps are kernel parameters: their addresses must stay in parameter space, so no pointer select)
+                if (second) tma_load_3d(base + slot * (A_BYTES + B_BYTES) + A_BYTES, &tm_w2, 0, col0, s * 2, bar(GB_FULL + slot));
+                else tma_load_3d(base + slot * (A_BYTES + B_BYTES) + A_BYTES, &tm_w, 0, col0, s * 2, bar(GB_FULL + slot));
                 issued = s + 1;
             }
             if (!ok)      // drain the copies still in flight before leaving
@@ -144,10 +161,10 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
         const int q = warp & 3, ch = (warp - 4) >> 2;
         const int row = q * 32 + lane;
         const int cbase = col0 + ch * 128;             // first output column of this warp's 128
-        const bool live = cbase < p.cols;              // a tile past the last column block: only keep the barriers moving
+        const bool live = cbase < pp.cols;              // a tile past the last column block: only keep the barriers moving
         const uint32_t tlane = tmem + ((uint32_t)(q * 32) << 16);
         const int64_t ncb = (p.k + 127) / 128;
-        const float *srow = p.scale_inv + (int64_t)(live ? cbase / 128 : 0) * ncb;
+        const float *srow = pp.scale_inv + (int64_t)(live ? cbase / 128 : 0) * ncb;
         float acc[128];
 #pragma unroll
         for (int j = 0; j < 128; j++) acc[j] = 0.f;
@@ -174,29 +191,29 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
         }
         if (ok && live && row0 + row < p.n) {
             const int64_t r = row0 + row;
-            if (p.out_bf16) {
-                uint16_t *y = (uint16_t *)p.Y + r * p.cols + cbase;
+            if (pp.out_bf16) {
+                uint16_t *y = (uint16_t *)pp.Y + r * pp.cols + cbase;
 #pragma unroll
                 for (int j = 0; j < 128; j += 8) {
-                    if (cbase + j + 8 <= p.cols) {
+                    if (cbase + j + 8 <= pp.cols) {
                         uint4 w;
                         w.x = pack_bf16x2(acc[j], acc[j + 1]); w.y = pack_bf16x2(acc[j + 2], acc[j + 3]);
                         w.z = pack_bf16x2(acc[j + 4], acc[j + 5]); w.w = pack_bf16x2(acc[j + 6], acc[j + 7]);
                         *reinterpret_cast<uint4 *>(y + j) = w;
                     } else {
                         for (int e = 0; e < 8; e++)
-                            if (cbase + j + e < p.cols) y[j + e] = (uint16_t)(pack_bf16x2(acc[j + e], 0.f) & 0xffffu);
+                            if (cbase + j + e < pp.cols) y[j + e] = (uint16_t)(pack_bf16x2(acc[j + e], 0.f) & 0xffffu);
                     }
                 }
             } else {
-                float *y = (float *)p.Y + r * p.cols + cbase;
+                float *y = (float *)pp.Y + r * pp.cols + cbase;
 #pragma unroll
                 for (int j = 0; j < 128; j += 4) {
-                    if (cbase + j + 4 <= p.cols) {
+                    if (cbase + j + 4 <= pp.cols) {
                         *reinterpret_cast<float4 *>(y + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                     } else {
                         for (int e = 0; e < 4; e++)
-                            if (cbase + j + e < p.cols) y[j + e] = acc[j + e];
+                            if (cbase + j + e < pp.cols) y[j + e] = acc[j + e];
                     }
                 }
             }
@@ -214,10 +231,29 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
 
 bool cwk_fp8_linear_tc_available() { return true; }
 
-int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv, int64_t n, int64_t k,
-                             int64_t cols, void *Y, int out_bf16) {
+// Widens W (E4M3 [cols][k]) into the context's bf16 buffer at element offset `at` and encodes its tensor map.
+static int prepare_weights(cwk_ctx *ctx, const void *W, int64_t cols, int64_t k, size_t at, CUtensorMap *tm) {
+    const int64_t n16 = cols * k / 16;
+    uint16_t *dst = (uint16_t *)ctx->wbf16 + at;
+    e4m3_to_bf16_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, ctx->stream>>>((const uint8_t *)W, dst, n16);
+    CWK_LAUNCH_CHECK(ctx, "e4m3_to_bf16_kernel");
+    CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
+    cuuint32_t es[3] = {1, 1, 1};
+    cuuint64_t wd[3] = {64, (cuuint64_t)cols, (cuuint64_t)(k / 64)};
+    cuuint64_t st[2] = {(cuuint64_t)k * 2, 128};
+    cuuint32_t wb[3] = {64, BN, 2};
+    if (enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dst, wd, st, wb, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the projection weights");
+    return CWK_OK;
+}
+
+// Y1 = X . W1^T (block-scaled), and, when W2 is given, Y2 = X . W2^T in the same launch.
+int cwk_fp8_linear_tc_launch2(cwk_ctx *ctx, const void *X, int64_t n, int64_t k, const void *W1, const float *scale1, int64_t cols1,
+                              void *Y1, int out_bf16_1, const void *W2, const float *scale2, int64_t cols2, void *Y2, int out_bf16_2) {
     // vector stores in the epilogue want 16-byte aligned rows
-    if ((cols % 8) != 0 || (k % 128) != 0 || ((uintptr_t)Y % 16) != 0 || ((uintptr_t)X % 16) != 0)
+    if ((cols1 % 8) != 0 || (k % 128) != 0 || ((uintptr_t)Y1 % 16) != 0 || ((uintptr_t)X % 16) != 0 ||
+        (W2 && ((cols2 % 8) != 0 || ((uintptr_t)Y2 % 16) != 0)))
         return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 FP8 GEMM needs cols %% 8 == 0 and k %% 128 == 0");
     if (!cwk_encode_tiled_fn()) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
     {
@@ -225,7 +261,8 @@ int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const f
         if (es != CWK_OK) return es;
     }
     // widened weights live in their own buffer (the split scratch and the prefill workspace are in use around this call)
-    const size_t wbytes = (size_t)cols * k * 2;
+    const size_t e1 = (size_t)cols1 * k, e2 = W2 ? (size_t)cols2 * k : 0;
+    const size_t wbytes = (e1 + e2) * 2;
     if (wbytes > ctx->wbf16_bytes) {
         if (ctx->wbf16) {
             CWK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -236,22 +273,24 @@ int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const f
         CWK_CUDA(ctx, cudaMalloc(&ctx->wbf16, wbytes));
         ctx->wbf16_bytes = wbytes;
     }
-    const int64_t n16 = cols * k / 16;
-    e4m3_to_bf16_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, ctx->stream>>>((const uint8_t *)W, (uint16_t *)ctx->wbf16, n16);
-    CWK_LAUNCH_CHECK(ctx, "e4m3_to_bf16_kernel");
-    CUtensorMap tm_x, tm_w;
+    CUtensorMap tm_x, tm_w, tm_w2;
+    int s = prepare_weights(ctx, W1, cols1, k, 0, &tm_w);
+    if (s != CWK_OK) return s;
+    tm_w2 = tm_w;
+    if (W2) {
+        s = prepare_weights(ctx, W2, cols2, k, e1, &tm_w2);
+        if (s != CWK_OK) return s;
+    }
     {
-        // operands as [64][rows][k / 64 column blocks]: one box = all rows of a tile x two column blocks (one 128-wide scale block)
+        // activations as [64][rows][k / 64 column blocks]: one box = all rows of a tile x two column blocks (one 128-wide scale block)
         CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
         cuuint32_t es[3] = {1, 1, 1};
-        cuuint64_t xd[3] = {64, (cuuint64_t)n, (cuuint64_t)(k / 64)}, wd[3] = {64, (cuuint64_t)cols, (cuuint64_t)(k / 64)};
+        cuuint64_t xd[3] = {64, (cuuint64_t)n, (cuuint64_t)(k / 64)};
         cuuint64_t st[2] = {(cuuint64_t)k * 2, 128};
-        cuuint32_t xb[3] = {64, BM, 2}, wb[3] = {64, BN, 2};
+        cuuint32_t xb[3] = {64, BM, 2};
         if (enc(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(X), xd, st, xb, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
-            enc(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ctx->wbf16, wd, st, wb, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the projection operands");
+            return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the projection activations");
     }
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
@@ -259,10 +298,20 @@ int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const f
         attr_set[ctx->device & 15] = true;
     }
     GemmParams p;
-    p.scale_inv = scale_inv; p.n = n; p.k = k; p.cols = cols; p.Y = Y; p.out_bf16 = out_bf16; p.err = ctx->dev_err;
-    dim3 grid((unsigned)((cols + BN - 1) / BN), (unsigned)((n + BM - 1) / BM));
+    p.pr[0].scale_inv = scale1; p.pr[0].cols = cols1; p.pr[0].Y = Y1; p.pr[0].out_bf16 = out_bf16_1;
+    p.pr[1] = p.pr[0];
+    if (W2) { p.pr[1].scale_inv = scale2; p.pr[1].cols = cols2; p.pr[1].Y = Y2; p.pr[1].out_bf16 = out_bf16_2; }
+    p.tiles_a = (int)((cols1 + BN - 1) / BN);
+    p.n = n; p.k = k; p.err = ctx->dev_err;
+    const int tiles_b = W2 ? (int)((cols2 + BN - 1) / BN) : 0;
+    dim3 grid((unsigned)(p.tiles_a + tiles_b), (unsigned)((n + BM - 1) / BM));
     CwkKernelTimer timer(ctx);
-    fp8_linear_tc_kernel<<<grid, G_THREADS, G_SMEM, ctx->stream>>>(tm_x, tm_w, p);
+    fp8_linear_tc_kernel<<<grid, G_THREADS, G_SMEM, ctx->stream>>>(tm_x, tm_w, tm_w2, p);
     CWK_LAUNCH_CHECK(ctx, "fp8_linear_tc_kernel");
     return CWK_OK;
+}
+
+int cwk_fp8_linear_tc_launch(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv, int64_t n, int64_t k,
+                             int64_t cols, void *Y, int out_bf16) {
+    return cwk_fp8_linear_tc_launch2(ctx, X, n, k, W, scale_inv, cols, Y, out_bf16, nullptr, nullptr, 0, nullptr, 0);
 }

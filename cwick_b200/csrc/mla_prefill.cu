@@ -33,6 +33,9 @@ __device__ __forceinline__ uint16_t narrow_bf16_like_reference(float f) {
 
 extern "C" int cwk_fp8_linear(cwk_ctx *ctx, const void *X, const void *W, const float *scale_inv, int64_t n,
                               int64_t k, int64_t cols, void *Y, int out_bf16);
+bool cwk_fp8_linear_tc_available();
+int cwk_fp8_linear_tc_launch2(cwk_ctx *ctx, const void *X, int64_t n, int64_t k, const void *W1, const float *scale1, int64_t cols1,
+                              void *Y1, int out_bf16_1, const void *W2, const float *scale2, int64_t cols2, void *Y2, int out_bf16_2);
 extern "C" int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
                               const int32_t *kv_len, int max_kv_len, const int32_t *sel, int64_t sel_ld, int B,
                               int nh, int L, int R, float scale, void *out, int n_splits);
@@ -199,15 +202,26 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     uint16_t *Qf = (uint16_t *)(w + b_qa + b_qan + b_kva + b_q);
     int32_t *len = (int32_t *)(w + b_qa + b_qan + b_kva + b_q + b_qf);
 
-    s = cwk_fp8_linear(ctx, X, Wqa, Sqa, n, H, q_lora, QA, 0);
+    // q_a and kv_a share the activations: one launch of the tensor-core GEMM when it takes the shapes
+    bool kva_done = false;
+    s = CWK_ERR_UNSUPPORTED;
+    if (cwk_fp8_linear_tc_available() && ctx->force_mla_path != 0 && ctx->force_mla_path != 1 && H % 128 == 0 && q_lora % 8 == 0 &&
+        row % 8 == 0 && ((uintptr_t)X % 16) == 0) {
+        s = cwk_fp8_linear_tc_launch2(ctx, X, n, H, Wqa, Sqa, q_lora, QA, 0, Wkva, Skva, row, KVA, 0);
+        if (s == CWK_OK) kva_done = true;
+        else if (s != CWK_ERR_UNSUPPORTED) return s;
+    }
+    if (!kva_done) s = cwk_fp8_linear(ctx, X, Wqa, Sqa, n, H, q_lora, QA, 0);
     if (s != CWK_OK) return s;
     norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(QA, q_lora, q_lora, 0, (const uint16_t *)qa_norm, eps, rope_base,
                                                       pos0, QAn, q_lora, nullptr, 0);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(q_a)");
     s = cwk_fp8_linear(ctx, QAn, Wqb, Sqb, n, q_lora, (int64_t)nh * qd, Q, 1);
     if (s != CWK_OK) return s;
-    s = cwk_fp8_linear(ctx, X, Wkva, Skva, n, H, row, KVA, 0);
-    if (s != CWK_OK) return s;
+    if (!kva_done) {
+        s = cwk_fp8_linear(ctx, X, Wkva, Skva, n, H, row, KVA, 0);
+        if (s != CWK_OK) return s;
+    }
     norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(KVA, row, kv_lora, rope, (const uint16_t *)kva_norm, eps, rope_base,
                                                       pos0, (uint16_t *)cache + pos0 * row, row, len, 1);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(kv_a)");

@@ -66,6 +66,58 @@ __device__ __forceinline__ void tk_load(const float *s, int c0, int end, uint32_
     }
 }
 
+// Warp 0 of a block: the bin of a 256-bin digit histogram where the count from the top reaches
+// `remaining`. sel[0] = prefix extended by that digit, sel[1] = the rank still wanted inside the bin.
+__device__ __forceinline__ void tk_pick_bin(const uint32_t *hist, int lane, uint32_t prefix, int shift, int remaining, uint32_t *sel) {
+    uint32_t c[8], tot = 0;                    // 8 bins per lane, suffix sums across the lanes
+#pragma unroll
+    for (int j = 0; j < 8; j++) { c[j] = hist[lane * 8 + j]; tot += c[j]; }
+    uint32_t incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_down_sync(0xffffffffu, incl, o);
+        if (lane + o < 32) incl += t;
+    }
+    uint32_t above = incl - tot;               // elements in the bins of higher lanes
+    const uint32_t r = (uint32_t)remaining;
+    if (above < r && r <= above + tot) {
+#pragma unroll
+        for (int j = 7; j >= 0; j--) {
+            if (r <= above + c[j]) {
+                sel[0] = prefix | ((uint32_t)(lane * 8 + j) << shift);
+                sel[1] = r - above;
+                break;
+            }
+            above += c[j];
+        }
+    }
+}
+
+// The same selection over a short list of row positions (one block's worth of work, no cluster
+// traffic): the rank-th largest of s[list[0..cnt)]. Every thread of the block calls it.
+__device__ __forceinline__ void tk_list_select(const float *s, const int32_t *list, int cnt, int rank, TkShared &sh, uint32_t &prefix,
+                                               int &remaining) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    prefix = 0;
+    uint32_t mask = 0;
+    remaining = rank;
+    for (int pass = 0; pass < 4; pass++) {
+        const int shift = 24 - 8 * pass;
+        if (tid < 256) sh.tot[tid] = 0;
+        __syncthreads();
+        for (int i = tid; i < cnt; i += TK_THREADS) {
+            const uint32_t k = order_key(s[list[i]]);
+            if ((k & mask) == prefix) atomicAdd(&sh.tot[(k >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid < 32) tk_pick_bin(sh.tot, lane, prefix, shift, remaining, sh.sel);
+        __syncthreads();
+        prefix = sh.sel[0];
+        remaining = (int)sh.sel[1];
+        mask |= 255u << shift;
+    }
+}
+
 // Exact want-th largest value of the row: 4 passes of 8 bits over the order-preserving integer
 // image. On return `prefix` is that image and `remaining` how many rows equal to it are wanted.
 // Every thread of every block of the cluster calls it; nb > want >= 1. Scores of one row usually
@@ -109,31 +161,7 @@ __device__ __forceinline__ void tk_radix_select(const float *s, const TkSlice sl
             sh.tot[tid] = t;
         }
         __syncthreads();
-        if (tid < 32) {
-            // suffix sums over the 256 bins, 8 bins per lane: the bin where the count from the top reaches `remaining`
-            uint32_t c[8], tot = 0;
-#pragma unroll
-            for (int j = 0; j < 8; j++) { c[j] = sh.tot[lane * 8 + j]; tot += c[j]; }
-            uint32_t incl = tot;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_down_sync(0xffffffffu, incl, o);
-                if (lane + o < 32) incl += t;
-            }
-            uint32_t above = incl - tot;                       // elements in the bins of higher lanes
-            const uint32_t r = (uint32_t)remaining;
-            if (above < r && r <= above + tot) {
-#pragma unroll
-                for (int j = 7; j >= 0; j--) {
-                    if (r <= above + c[j]) {
-                        sh.sel[0] = prefix | ((uint32_t)(lane * 8 + j) << shift);
-                        sh.sel[1] = r - above;
-                        break;
-                    }
-                    above += c[j];
-                }
-            }
-        }
+        if (tid < 32) tk_pick_bin(sh.tot, lane, prefix, shift, remaining, sh.sel);
         __syncthreads();
         prefix = sh.sel[0];
         remaining = (int)sh.sel[1];
