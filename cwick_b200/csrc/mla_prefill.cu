@@ -7,6 +7,8 @@
 // writes, then mla_latent_decode per token). Here every stage is one batched
 // kernel over the chunk, and the attention is one launch in which query i sees
 // cache rows 0..pos0+i.
+#include <algorithm>
+
 #include "cwk_common.cuh"
 
 // cos/sin of the reference's rope angle, pos / powf(base, 2i/n) (src/attention.c:62), formed the
@@ -101,7 +103,27 @@ __global__ void __launch_bounds__(256) rope_tail_kernel(const uint16_t *q, uint1
     }
 }
 
+// RoPE of the rope part of q, in place: q[t][h][nope : nope+rope] at position pos0 + t. One thread per (t, pair).
+__global__ void __launch_bounds__(256) rope_q_inplace_kernel(uint16_t *q, int n, int nh, int nope, int n_rope, int64_t pos0, float base) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * (n_rope / 2)) return;
+    const int t = i / (n_rope / 2), j = i % (n_rope / 2);
+    float cs, sn;
+    rope_cos_sin(pos0 + t, j, n_rope, base, cs, sn);
+    uint16_t *src = q + (int64_t)t * nh * (nope + n_rope) + nope + 2 * j;
+#pragma unroll 8
+    for (int h = 0; h < nh; h++) {
+        uint32_t *w = reinterpret_cast<uint32_t *>(src + (int64_t)h * (nope + n_rope));
+        const uint32_t v = *w;
+        const float a = __uint_as_float(v << 16), b = __uint_as_float(v & 0xffff0000u);
+        *w = pack_bf16x2(a * cs - b * sn, b * cs + a * sn);
+    }
+}
+
 int cwk_absorb_tc_launch(cwk_ctx *ctx, const void *Q, int n, int nh, const void *Wuk, void *Qfull);
+bool cwk_mla_prefill_attn_tc_ok(const void *Q, const void *cache, const void *Wuk, const void *kx, const void *out);
+int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int64_t pos0, int n, int nh,
+                            float scale, void *out);
 
 // Absorb: Qfull[t][h][0:L] = q[t][h][0:nope] . W_uk[h] ([nope][L] row-major bf16), and
 // Qfull[t][h][L:L+rope] = RoPE(q[t][h][nope:nope+rope], pos0+t). The identity is
@@ -191,7 +213,13 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     // Qfull bf16 [n][nh][row], kv_len int32 [n]
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
     const size_t b_qa = up((size_t)n * q_lora * 4), b_qan = up((size_t)n * q_lora * 2), b_kva = up((size_t)n * row * 4);
-    const size_t b_q = up((size_t)n * nh * qd * 2), b_qf = up((size_t)n * nh * row * 2), b_len = up((size_t)n * 4);
+    // The attention takes one of two routes. Queries as MMA rows against per-head expanded keys (mla_prefill_attn.cu)
+    // needs Kx bf16 [pos0+n][nh][qd] and no Qfull; the absorbed route (the decode kernel once per query row) needs
+    // Qfull bf16 [n][nh][row]. The same workspace region serves whichever runs.
+    const bool expanded_keys = ctx->force_mla_path != 0 && ctx->force_mla_path != 1 && ctx->force_mla_path != 2 && pos0 + n <= 32768;
+    const size_t b_kx = up((size_t)(pos0 + n) * nh * qd * 2);
+    const size_t b_q = up((size_t)n * nh * qd * 2), b_qf = expanded_keys ? std::max(b_kx, up((size_t)n * nh * row * 2)) : up((size_t)n * nh * row * 2),
+                 b_len = up((size_t)n * 4);
     int s = cwk_reserve_work(ctx, b_qa + b_qan + b_kva + b_q + b_qf + b_len);
     if (s != CWK_OK) return s;
     uint8_t *w = (uint8_t *)ctx->work;
@@ -225,6 +253,11 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(KVA, row, kv_lora, rope, (const uint16_t *)kva_norm, eps, rope_base,
                                                       pos0, (uint16_t *)cache + pos0 * row, row, len, 1);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(kv_a)");
+    if (expanded_keys && cwk_mla_prefill_attn_tc_ok(Q, cache, Wuk, Qf, out)) {
+        rope_q_inplace_kernel<<<(n * (rope / 2) + 255) / 256, 256, 0, ctx->stream>>>(Q, n, nh, nope, rope, pos0, rope_base);
+        CWK_LAUNCH_CHECK(ctx, "rope_q_inplace_kernel");
+        return cwk_mla_prefill_attn_tc(ctx, Q, cache, Wuk, Qf, pos0, n, nh, scale, out);
+    }
     // absorb on the tensor path (tcgen05); the mma.sync kernel covers a context without the
     // tensor-map encoder or a caller that forced the general kernels
     s = CWK_ERR_UNSUPPORTED;

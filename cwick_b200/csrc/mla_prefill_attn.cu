@@ -1,0 +1,496 @@
+// mla_prefill_attn.cu -- causal MLA prefill attention with the queries as the MMA's rows.
+//
+// The decode kernel (mla_decode_tc.cu) treats a query token as 64 rows (its heads) of a 576-wide
+// product against the latent cache; run once per token of a prompt, its MMAs are 64 columns wide,
+// bound by shared-memory bandwidth, and every 128-key tile is a serial chain. A prompt has a better
+// shape: per HEAD, 128 consecutive tokens are the 128 rows of an MMA. Scores are taken against the
+// head's expanded key, not against the latent:
+//
+//   s[t][h][c] = q_nope[t][h] . (W_uk[h] lat[c])  +  q_rope[t][h] . k_rope[c]        (192-wide)
+//   out[t][h]  = sum_c softmax_c(s) lat[c]                                            (512-wide)
+//
+// which is the absorbed attention of src/attention.c:741-782 with the product W_uk^T q_nope . lat
+// re-associated: the same scores, 192 instead of 576 multiply-adds each, and the values are still the
+// shared latent, so the output is the absorbed [tokens][heads][512] result. Two kernels:
+//
+//   kexp_tc_kernel: Kx[c][h][0:128] = W_uk[h] lat[c] (tcgen05, W_uk[h] resident per block as the
+//     K-major B operand, latent tiles streamed), Kx[c][h][128:192] = k_rope[c].
+//   prefill_attn_kernel: one block = 128 queries x one head x one half of the 512 value columns
+//     (the accumulator of a half, 128 x 256 f32, is half of tensor memory; both halves recompute
+//     the 192-wide scores, which is cheaper than any exchange). Keys stream in tiles of 64 through a
+//     3-deep ring (24 KB each), latent halves through a 2-deep ring (32 KB each), one TMA box each.
+//     Per tile: S = Q Kx^T (12 MMAs, M 128 x N 64) into one of two TMEM score buffers; the softmax
+//     warps own one query row per thread (TMEM lane = row, so row maxima and sums need no shuffles),
+//     write P (bf16) to shared memory; O += P lat (4 MMAs, M 128 x N 256). The MMA thread issues
+//     the scores of tile i+1 before the values of tile i, so the tensor pipe works under the softmax.
+//     The running maximum is lazy: a row rescales its accumulator only when a score outruns its
+//     reference exponent by 2^8, and it owns its TMEM lane, so no other thread is involved.
+//
+// Every mbarrier wait is bounded and records a code in the context's error word when it gives up.
+#include <algorithm>
+
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int PA_QT = 128, PA_KT = 64, PA_DQK = 192, PA_DV = 256, PA_L = 512, PA_ROW = 576;
+constexpr int PA_Q_BYTES = PA_QT * PA_DQK * 2;        // 49152: three [128][64] blocks
+constexpr int PA_K_BYTES = PA_KT * PA_DQK * 2;        // 24576: three [64][64] blocks
+constexpr int PA_C_BYTES = PA_KT * PA_DV * 2;         // 32768: four [64][64] blocks
+constexpr int PA_P_BYTES = PA_QT * PA_KT * 2;         // 16384: one [128][64] block
+constexpr int PA_KST = 3, PA_CST = 2;
+constexpr int PA_OFF_Q = 0;
+constexpr int PA_OFF_K = PA_Q_BYTES;
+constexpr int PA_OFF_C = PA_OFF_K + PA_KST * PA_K_BYTES;
+constexpr int PA_OFF_P = PA_OFF_C + PA_CST * PA_C_BYTES;
+constexpr int PA_OFF_BAR = PA_OFF_P + 2 * PA_P_BYTES;  // 221184
+constexpr int PA_SMEM = PA_OFF_BAR + 256 + 1024;
+constexpr uint32_t PA_COL_O = 0, PA_COL_S = 256;       // S buffers at 256 and 320
+constexpr float PA_LAZY = 8.f;
+enum { PB_QFULL = 0, PB_KFULL = 1, PB_KEMPTY = 4, PB_CFULL = 7, PB_CEMPTY = 9, PB_SFULL = 11, PB_SEMPTY = 13, PB_PFULL = 15, PB_ODONE = 17,
+       PB_COUNT = 18 };
+
+struct AttnParams {
+    uint16_t *out;      // bf16 [n][nh][512]
+    int n, nh;
+    int64_t pos0;
+    float scale_log2;
+    int *err;
+};
+
+__global__ void __launch_bounds__(256, 1)
+prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_c,
+                    const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - raw);
+    const uint32_t bar0 = base + PA_OFF_BAR;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + PA_OFF_BAR + 8 * PB_COUNT + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qtile = (int)gridDim.x - 1 - (int)blockIdx.x;      // longest blocks first
+    const int h = blockIdx.y, half = blockIdx.z;
+    const int q0 = qtile * PA_QT;
+    // keys 0 .. pos0 + (last query of the block): tiles of 64
+    const int64_t last_q = p.pos0 + min(q0 + PA_QT - 1, p.n - 1);
+    const int nt = (int)(last_q / PA_KT) + 1;
+
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_c) : "memory");
+        for (int i = 0; i < PB_COUNT; i++) {
+            const bool by128 = (i >= PB_SEMPTY && i < PB_ODONE);         // s_empty, p_full: every softmax thread
+            mbar_init(bar(i), by128 ? 128u : 1u);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(bar(PB_QFULL), PA_Q_BYTES);
+            tma_load_3d(base + PA_OFF_Q, &tm_q, 0, q0, h * 3, bar(PB_QFULL));
+            bool ok = true;
+            int k_issued = 0, c_issued = 0;
+            for (int i = 0; i < nt && ok; i++) {
+                const int ks = i % PA_KST, ku = i / PA_KST, cs = i & 1, cu = i >> 1;
+                ok = mbar_wait(bar(PB_KEMPTY + ks), (uint32_t)((ku & 1) ^ 1), p.err, 1001);
+                if (!ok) break;
+                mbar_expect_tx(bar(PB_KFULL + ks), PA_K_BYTES);
+                tma_load_3d(base + PA_OFF_K + ks * PA_K_BYTES, &tm_k, 0, i * PA_KT, h * 3, bar(PB_KFULL + ks));
+                k_issued = i + 1;
+                ok = mbar_wait(bar(PB_CEMPTY + cs), (uint32_t)((cu & 1) ^ 1), p.err, 1002);
+                if (!ok) break;
+                mbar_expect_tx(bar(PB_CFULL + cs), PA_C_BYTES);
+                tma_load_3d(base + PA_OFF_C + cs * PA_C_BYTES, &tm_c, 0, i * PA_KT, half * 4, bar(PB_CFULL + cs));
+                c_issued = i + 1;
+            }
+            if (!ok) {      // drain the copies still in flight before leaving
+                mbar_wait(bar(PB_QFULL), 0, p.err, 1003);
+                for (int i = (k_issued > PA_KST ? k_issued - PA_KST : 0); i < k_issued; i++)
+                    mbar_wait(bar(PB_KFULL + i % PA_KST), (uint32_t)((i / PA_KST) & 1), p.err, 1004);
+                for (int i = (c_issued > PA_CST ? c_issued - PA_CST : 0); i < c_issued; i++)
+                    mbar_wait(bar(PB_CFULL + (i & 1)), (uint32_t)((i >> 1) & 1), p.err, 1005);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t ID_QK = idesc_bf16(128, PA_KT, 0, 0);
+            constexpr uint32_t ID_PV = idesc_bf16(128, PA_DV, 0, 1);
+            const uint64_t dQ = smem_desc(base + PA_OFF_Q, 16, 1024);
+            bool ok = mbar_wait(bar(PB_QFULL), 0, p.err, 1011);
+            // scores of tile j: S[j & 1] = Q Kx^T, three 64-wide blocks of the 192 dims, four 16-wide steps each
+            auto issue_qk = [&](int j) -> bool {
+                const int ks = j % PA_KST, ku = j / PA_KST, sb = j & 1, su = j >> 1;
+                if (!mbar_wait(bar(PB_KFULL + ks), (uint32_t)(ku & 1), p.err, 1012)) return false;
+                if (!mbar_wait(bar(PB_SEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1013)) return false;
+                tc_fence_after();
+                const uint64_t dK = smem_desc(base + PA_OFF_K + ks * PA_K_BYTES, 16, 1024);
+#pragma unroll
+                for (int s = 0; s < 12; s++)
+                    umma_bf16(tmem + PA_COL_S + sb * PA_KT, dQ + (uint64_t)(((s >> 2) * (PA_QT * 128) + (s & 3) * 32) >> 4),
+                              dK + (uint64_t)(((s >> 2) * (PA_KT * 128) + (s & 3) * 32) >> 4), ID_QK, s != 0);
+                umma_commit(bar(PB_KEMPTY + ks));
+                umma_commit(bar(PB_SFULL + sb));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int i = 0; i < nt && ok; i++) {
+                if (i + 1 < nt) ok = issue_qk(i + 1);
+                if (!ok) break;
+                const int cs = i & 1, cu = i >> 1;
+                ok = mbar_wait(bar(PB_CFULL + cs), (uint32_t)(cu & 1), p.err, 1014);
+                if (ok) ok = mbar_wait(bar(PB_PFULL + cs), (uint32_t)(cu & 1), p.err, 1015);
+                if (!ok) break;
+                tc_fence_after();
+                // values: O += P lat, P [128 q][64 keys] K-major, lat half [64 keys][256] with the 256 contiguous (MN-major, four 64-wide blocks)
+                const uint64_t dP = smem_desc(base + PA_OFF_P + cs * PA_P_BYTES, 16, 1024);
+                const uint64_t dC = smem_desc(base + PA_OFF_C + cs * PA_C_BYTES, PA_KT * 128, 1024);
+#pragma unroll
+                for (int s = 0; s < 4; s++)
+                    umma_bf16(tmem + PA_COL_O, dP + (uint64_t)((s * 32) >> 4), dC + (uint64_t)((s * 2048) >> 4), ID_PV, (s != 0) ? 1u : (uint32_t)(i != 0));
+                umma_commit(bar(PB_CEMPTY + cs));
+            }
+            if (ok) umma_commit(bar(PB_ODONE));
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------ softmax, correction, epilogue: one query row per thread
+        const int q4 = warp & 3;
+        const int row = q4 * 32 + lane;
+        const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
+        const int64_t tq = p.pos0 + q0 + row;                    // this row's position: keys 0..tq are visible
+        float m = 0.f, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < nt; i++) {
+            const int sb = i & 1, su = i >> 1;
+            ok = mbar_wait(bar(PB_SFULL + sb), (uint32_t)(su & 1), p.err, 1021);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t v[PA_KT];
+            TMEM_LD16(v, 0, tlane + PA_COL_S + sb * PA_KT);
+            TMEM_LD16(v, 16, tlane + PA_COL_S + sb * PA_KT + 16);
+            TMEM_LD16(v, 32, tlane + PA_COL_S + sb * PA_KT + 32);
+            TMEM_LD16(v, 48, tlane + PA_COL_S + sb * PA_KT + 48);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar(PB_SEMPTY + sb));
+            float s[PA_KT];
+            float mt = -INFINITY;
+            const int64_t k0 = (int64_t)i * PA_KT;
+            if (k0 + PA_KT - 1 <= p.pos0 + q0) {                 // every key of the tile is visible to every row of the block
+#pragma unroll
+                for (int j = 0; j < PA_KT; j++) { s[j] = __uint_as_float(v[j]) * p.scale_log2; mt = fmaxf(mt, s[j]); }
+            } else {
+#pragma unroll
+                for (int j = 0; j < PA_KT; j++) {
+                    s[j] = (k0 + j <= tq) ? __uint_as_float(v[j]) * p.scale_log2 : -INFINITY;
+                    mt = fmaxf(mt, s[j]);
+                }
+            }
+            if (i == 0) {
+                m = mt;                                          // key 0 is visible to every row: finite
+            } else if (mt > m + PA_LAZY) {
+                // this row's scores outran its reference exponent: rescale what it has accumulated. The row is this
+                // thread's TMEM lane; the value MMAs of the previous tile must have finished writing it.
+                ok = mbar_wait(bar(PB_CEMPTY + ((i - 1) & 1)), (uint32_t)(((i - 1) >> 1) & 1), p.err, 1022);
+                if (!ok) break;
+                tc_fence_after();
+                const float alpha = exp2f(m - mt);
+                l *= alpha;
+                m = mt;
+                for (int c = 0; c < PA_DV / 16; c++) {
+                    uint32_t o[16];
+                    TMEM_LD16(o, 0, tlane + PA_COL_O + c * 16);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                    TMEM_ST16(o, 0, tlane + PA_COL_O + c * 16);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            uint32_t pk[PA_KT / 2];
+            float lsum = 0.f;
+#pragma unroll
+            for (int j = 0; j < PA_KT; j += 2) {
+                const float p0 = exp2f(s[j] - m), p1 = exp2f(s[j + 1] - m);
+                lsum += p0 + p1;
+                pk[j >> 1] = pack_bf16x2(p0, p1);
+            }
+            l += lsum;
+            // the P buffer of this parity was read by the value MMAs of tile i - 2
+            ok = mbar_wait(bar(PB_CEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1023);
+            if (!ok) break;
+            uint8_t *prow = sm + PA_OFF_P + sb * PA_P_BYTES + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar(PB_PFULL + sb));
+        }
+        // ---- epilogue: O / l -> bf16 -> out[t][h][half * 256 ..], through the (now idle) P buffers for full-line stores
+        if (ok) ok = mbar_wait(bar(PB_ODONE), 0, p.err, 1024);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            uint8_t *stg = sm + PA_OFF_P + q4 * 4096;                // 4 KB per warp: [32 rows][128 B]
+            const int t0w = q0 + q4 * 32;
+#pragma unroll 1
+            for (int c = 0; c < PA_DV / 64; c++) {
+                uint32_t o[64];
+                TMEM_LD16(o, 0, tlane + PA_COL_O + c * 64);
+                TMEM_LD16(o, 16, tlane + PA_COL_O + c * 64 + 16);
+                TMEM_LD16(o, 32, tlane + PA_COL_O + c * 64 + 32);
+                TMEM_LD16(o, 48, tlane + PA_COL_O + c * 64 + 48);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    uint4 w;
+                    w.x = pack_bf16x2(__uint_as_float(o[8 * j]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
+                    w.y = pack_bf16x2(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
+                    w.z = pack_bf16x2(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
+                    w.w = pack_bf16x2(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int r8 = 0; r8 < 8; r8++) {
+                    const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
+                    const uint4 w = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
+                    if (t0w + rr < p.n)
+                        *reinterpret_cast<uint4 *>(p.out + ((int64_t)(t0w + rr) * p.nh + h) * PA_L + half * PA_DV + c * 64 + jj * 8) = w;
+                }
+                __syncwarp();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Key expansion: Kx[c][h][0:128] = W_uk[h] lat[c], Kx[c][h][128:192] = k_rope[c].
+constexpr int KX_TOK = 128, KX_NOPE = 128;
+constexpr int KX_W_BYTES = KX_NOPE * PA_L * 2;        // 131072: eight [128 d][64 l] blocks
+constexpr int KX_A_BYTES = KX_TOK * 128 * 2;          // 32768: two [128 tok][64 l] blocks = one 128-wide chunk of the latent
+constexpr int KX_OFF_W = 0, KX_OFF_A = KX_W_BYTES, KX_OFF_STG = KX_OFF_A + 2 * KX_A_BYTES, KX_OFF_BAR = KX_OFF_STG + 4 * 4096;
+constexpr int KX_SMEM = KX_OFF_BAR + 256 + 1024;
+enum { KB_WFULL = 0, KB_AFULL = 1, KB_AEMPTY = 3, KB_DFULL = 5, KB_DEMPTY = 7, KB_COUNT = 9 };
+
+struct KexpParams {
+    const uint16_t *cache;    // bf16 [T][576]
+    uint16_t *kx;             // bf16 [T][nh][192]
+    int T, nh;
+    int *err;
+};
+
+__global__ void __launch_bounds__(256, 1)
+kexp_tc_kernel(const __grid_constant__ CUtensorMap tm_lat, const __grid_constant__ CUtensorMap tm_w, const KexpParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - raw);
+    const uint32_t bar0 = base + KX_OFF_BAR;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + KX_OFF_BAR + 8 * KB_COUNT + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y;
+    const int ntiles = (p.T + KX_TOK - 1) / KX_TOK;
+    const int nt = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;     // tiles g, g + G, ...
+    if (nt <= 0) return;
+    const int nch = nt * 4;                                                              // 128-wide chunks of the 512 latent dims
+
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_lat) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+        for (int i = 0; i < KB_COUNT; i++) mbar_init(bar(i), i >= KB_DEMPTY ? 128u : 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(bar(KB_WFULL), KX_W_BYTES);
+            tma_load_3d(base + KX_OFF_W, &tm_w, 0, h * KX_NOPE, 0, bar(KB_WFULL));
+            bool ok = true;
+            int issued = 0;
+            for (int c = 0; c < nch && ok; c++) {
+                const int slot = c & 1, use = c >> 1;
+                ok = mbar_wait(bar(KB_AEMPTY + slot), (uint32_t)((use & 1) ^ 1), p.err, 1101);
+                if (!ok) break;
+                const int tile = (int)blockIdx.x + (c >> 2) * (int)gridDim.x;
+                mbar_expect_tx(bar(KB_AFULL + slot), KX_A_BYTES);
+                tma_load_3d(base + KX_OFF_A + slot * KX_A_BYTES, &tm_lat, 0, tile * KX_TOK, (c & 3) * 2, bar(KB_AFULL + slot));
+                issued = c + 1;
+            }
+            if (!ok) {
+                mbar_wait(bar(KB_WFULL), 0, p.err, 1102);
+                for (int c = (issued > 2 ? issued - 2 : 0); c < issued; c++) mbar_wait(bar(KB_AFULL + (c & 1)), (uint32_t)((c >> 1) & 1), p.err, 1103);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t ID = idesc_bf16(128, KX_NOPE, 0, 0);
+            const uint64_t dW = smem_desc(base + KX_OFF_W, 16, 1024);
+            bool ok = mbar_wait(bar(KB_WFULL), 0, p.err, 1104);
+            for (int c = 0; c < nch && ok; c++) {
+                const int slot = c & 1, use = c >> 1, ti = c >> 2, kc = c & 3, db = ti & 1;
+                if (kc == 0) ok = mbar_wait(bar(KB_DEMPTY + db), (uint32_t)(((ti >> 1) & 1) ^ 1), p.err, 1105);
+                if (ok) ok = mbar_wait(bar(KB_AFULL + slot), (uint32_t)(use & 1), p.err, 1106);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t dA = smem_desc(base + KX_OFF_A + slot * KX_A_BYTES, 16, 1024);
+#pragma unroll
+                for (int s = 0; s < 8; s++)       // chunk kc covers W blocks 2 kc and 2 kc + 1
+                    umma_bf16(tmem + db * KX_NOPE, dA + (uint64_t)(((s >> 2) * (KX_TOK * 128) + (s & 3) * 32) >> 4),
+                              dW + (uint64_t)((((kc * 2 + (s >> 2)) * (KX_NOPE * 128)) + (s & 3) * 32) >> 4), ID, (kc | s) != 0);
+                umma_commit(bar(KB_AEMPTY + slot));
+                if (kc == 3) umma_commit(bar(KB_DFULL + db));
+            }
+        }
+    } else if (warp >= 4) {
+        const int q4 = warp & 3;
+        const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
+        uint8_t *stg = sm + KX_OFF_STG + q4 * 4096;
+        bool ok = true;
+        for (int ti = 0; ti < nt && ok; ti++) {
+            const int db = ti & 1;
+            const int t0w = ((int)blockIdx.x + ti * (int)gridDim.x) * KX_TOK + q4 * 32;
+            // rope tail first (independent of the MMAs): 128 bytes per token, eight lanes per row
+#pragma unroll
+            for (int r8 = 0; r8 < 8; r8++) {
+                const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
+                if (t0w + rr < p.T) {
+                    const uint4 w = *reinterpret_cast<const uint4 *>(p.cache + (int64_t)(t0w + rr) * PA_ROW + PA_L + jj * 8);
+                    *reinterpret_cast<uint4 *>(p.kx + ((int64_t)(t0w + rr) * p.nh + h) * PA_DQK + KX_NOPE + jj * 8) = w;
+                }
+            }
+            ok = mbar_wait(bar(KB_DFULL + db), (uint32_t)((ti >> 1) & 1), p.err, 1107);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 2; c++) {
+                uint32_t v[64];
+                TMEM_LD16(v, 0, tlane + db * KX_NOPE + c * 64);
+                TMEM_LD16(v, 16, tlane + db * KX_NOPE + c * 64 + 16);
+                TMEM_LD16(v, 32, tlane + db * KX_NOPE + c * 64 + 32);
+                TMEM_LD16(v, 48, tlane + db * KX_NOPE + c * 64 + 48);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    uint4 w;
+                    w.x = pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
+                    w.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                    w.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                    w.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                    *reinterpret_cast<uint4 *>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int r8 = 0; r8 < 8; r8++) {
+                    const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
+                    const uint4 w = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
+                    if (t0w + rr < p.T)
+                        *reinterpret_cast<uint4 *>(p.kx + ((int64_t)(t0w + rr) * p.nh + h) * PA_DQK + c * 64 + jj * 8) = w;
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            mbar_arrive(bar(KB_DEMPTY + db));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    }
+}
+
+bool encode3(CUtensorMap *tm, const void *ptr, uint64_t rows, uint64_t blocks, uint64_t row_bytes, uint32_t box_rows, uint32_t box_blocks) {
+    CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {64, rows, blocks};
+    cuuint64_t strides[2] = {row_bytes, 128};
+    cuuint32_t box[3] = {64, box_rows, box_blocks};
+    cuuint32_t es[3] = {1, 1, 1};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// Whether cwk_mla_prefill_attn_tc can take these operands (asked before the caller rotates Q in place).
+bool cwk_mla_prefill_attn_tc_ok(const void *Q, const void *cache, const void *Wuk, const void *kx, const void *out) {
+    if (!cwk_encode_tiled_fn()) return false;
+    return ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(Wuk) | reinterpret_cast<uintptr_t>(kx) |
+             reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+}
+
+// Q bf16 [n][nh][192] with the rope part already rotated; cache bf16 [pos0 + n][576] (latent | rope key);
+// Wuk bf16 [nh][128][512]; kx = workspace bf16 [pos0 + n][nh][192]; out bf16 [n][nh][512].
+// Returns CWK_ERR_UNSUPPORTED (no error text) when the tensor path cannot run.
+int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int64_t pos0, int n, int nh,
+                            float scale, void *out) {
+    if (!cwk_encode_tiled_fn()) return CWK_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(Wuk) | reinterpret_cast<uintptr_t>(kx) |
+         reinterpret_cast<uintptr_t>(out)) & 15)
+        return CWK_ERR_UNSUPPORTED;
+    int s = cwk_ensure_err_word(ctx);
+    if (s != CWK_OK) return s;
+    const int T = (int)(pos0 + n);
+    CUtensorMap tm_lat, tm_w, tm_q, tm_k, tm_c;
+    if (!encode3(&tm_lat, cache, (uint64_t)T, PA_L / 64, PA_ROW * 2, KX_TOK, 2) ||                 // latent dims only: block index 8 (rope) stays out
+        !encode3(&tm_w, Wuk, (uint64_t)nh * KX_NOPE, PA_L / 64, PA_L * 2, KX_NOPE, PA_L / 64) ||
+        !encode3(&tm_q, Q, (uint64_t)n, (uint64_t)nh * 3, (uint64_t)nh * PA_DQK * 2, PA_QT, 3) ||
+        !encode3(&tm_k, kx, (uint64_t)T, (uint64_t)nh * 3, (uint64_t)nh * PA_DQK * 2, PA_KT, 3) ||
+        !encode3(&tm_c, cache, (uint64_t)T, PA_L / 64, PA_ROW * 2, PA_KT, 4))
+        return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the prefill attention operands");
+    static bool attr_set[16] = {false};
+    if (!attr_set[ctx->device & 15]) {
+        CWK_CUDA(ctx, cudaFuncSetAttribute(kexp_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KX_SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PA_SMEM));
+        attr_set[ctx->device & 15] = true;
+    }
+    {
+        KexpParams kp;
+        kp.cache = (const uint16_t *)cache; kp.kx = (uint16_t *)kx; kp.T = T; kp.nh = nh; kp.err = ctx->dev_err;
+        const int ntiles = (T + KX_TOK - 1) / KX_TOK;
+        const int G = std::max(1, std::min(ntiles, ctx->sm_count / std::max(1, nh)));
+        CwkKernelTimer timer(ctx);
+        kexp_tc_kernel<<<dim3(G, nh), 256, KX_SMEM, ctx->stream>>>(tm_lat, tm_w, kp);
+        CWK_LAUNCH_CHECK(ctx, "kexp_tc_kernel");
+    }
+    {
+        AttnParams ap;
+        ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.pos0 = pos0; ap.scale_log2 = scale * 1.4426950408889634f; ap.err = ctx->dev_err;
+        CwkKernelTimer timer(ctx);
+        prefill_attn_kernel<<<dim3((n + PA_QT - 1) / PA_QT, nh, 2), 256, PA_SMEM, ctx->stream>>>(tm_q, tm_k, tm_c, ap);
+        CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel");
+    }
+    return CWK_OK;
+}
