@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(256) rope_q_inplace_kernel(uint16_t *q, int n,
 
 int cwk_absorb_tc_launch(cwk_ctx *ctx, const void *Q, int n, int nh, const void *Wuk, void *Qfull);
 bool cwk_mla_prefill_attn_tc_ok(const void *Q, const void *cache, const void *Wuk, const void *kx, const void *out);
-int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int64_t pos0, int n, int nh,
+int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int *flags, int64_t pos0, int n, int nh,
                             float scale, void *out);
 
 // Absorb: Qfull[t][h][0:L] = q[t][h][0:nope] . W_uk[h] ([nope][L] row-major bf16), and
@@ -219,7 +219,7 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     const bool expanded_keys = ctx->force_mla_path != 0 && ctx->force_mla_path != 1 && ctx->force_mla_path != 2 && pos0 + n <= 32768;
     const size_t b_kx = up((size_t)(pos0 + n) * nh * qd * 2);
     const size_t b_q = up((size_t)n * nh * qd * 2), b_qf = expanded_keys ? std::max(b_kx, up((size_t)n * nh * row * 2)) : up((size_t)n * nh * row * 2),
-                 b_len = up((size_t)n * 4);
+                 b_len = up((size_t)n * 4) + up((size_t)((n + 127) / 128) * nh * 2 * 4);
     int s = cwk_reserve_work(ctx, b_qa + b_qan + b_kva + b_q + b_qf + b_len);
     if (s != CWK_OK) return s;
     uint8_t *w = (uint8_t *)ctx->work;
@@ -256,7 +256,7 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     if (expanded_keys && cwk_mla_prefill_attn_tc_ok(Q, cache, Wuk, Qf, out)) {
         rope_q_inplace_kernel<<<(n * (rope / 2) + 255) / 256, 256, 0, ctx->stream>>>(Q, n, nh, nope, rope, pos0, rope_base);
         CWK_LAUNCH_CHECK(ctx, "rope_q_inplace_kernel");
-        return cwk_mla_prefill_attn_tc(ctx, Q, cache, Wuk, Qf, pos0, n, nh, scale, out);
+        return cwk_mla_prefill_attn_tc(ctx, Q, cache, Wuk, Qf, (int *)((uint8_t *)len + up((size_t)n * 4)), pos0, n, nh, scale, out);
     }
     // absorb on the tensor path (tcgen05); the mma.sync kernel covers a context without the
     // tensor-map encoder or a caller that forced the general kernels

@@ -13,18 +13,23 @@
 // re-associated: the same scores, 192 instead of 576 multiply-adds each, and the values are still the
 // shared latent, so the output is the absorbed [tokens][heads][512] result. Two kernels:
 //
-//   kexp_tc_kernel: Kx[c][h][0:128] = W_uk[h] lat[c] (tcgen05, W_uk[h] resident per block as the
-//     K-major B operand, latent tiles streamed), Kx[c][h][128:192] = k_rope[c].
+//   kexp_tc_kernel: Kx[h][c][0:128] = W_uk[h] lat[c] (tcgen05, W_uk[h] resident per block as the
+//     K-major B operand, latent tiles streamed), Kx[h][c][128:192] = k_rope[c]. Head-major: a head's 64-key tile is
+//     24 KB of consecutive memory (token-major rows would lie 24 KB apart and crowd a few L2 slices).
 //   prefill_attn_kernel: one block = 128 queries x one head x one half of the 512 value columns
 //     (the accumulator of a half, 128 x 256 f32, is half of tensor memory; both halves recompute
 //     the 192-wide scores, which is cheaper than any exchange). Keys stream in tiles of 64 through a
-//     3-deep ring (24 KB each), latent halves through a 2-deep ring (32 KB each), one TMA box each.
+//     2-deep ring (24 KB each), latent halves through a 3-deep ring (32 KB each), one TMA box each.
 //     Per tile: S = Q Kx^T (12 MMAs, M 128 x N 64) into one of two TMEM score buffers; the softmax
 //     warps own one query row per thread (TMEM lane = row, so row maxima and sums need no shuffles),
-//     write P (bf16) to shared memory; O += P lat (4 MMAs, M 128 x N 256). The MMA thread issues
-//     the scores of tile i+1 before the values of tile i, so the tensor pipe works under the softmax.
-//     The running maximum is lazy: a row rescales its accumulator only when a score outruns its
-//     reference exponent by 2^8, and it owns its TMEM lane, so no other thread is involved.
+//     write P (bf16) to shared memory; O += P lat (4 MMAs, M 128 x N 256). The two products have
+//     issuer threads of their own and three score buffers, so the scores run up to two tiles ahead of the values and
+//     the tensor pipe works under the softmax.
+//     The kernel has two forms. The fast one splits the 64 keys of a row between two softmax warp groups
+//     (two threads per row) and never rescales: a row's reference exponent is its largest score of the first
+//     tile, later scores may outrun it by up to 2^64 (bf16 P and the f32 accumulators have the range), and a
+//     block that sees more raises a flag. The exact one (one thread per row, lazy rescale of its own TMEM lane
+//     when a score outruns the reference by 2^8) runs right after it and recomputes the flagged blocks only.
 //
 // Every mbarrier wait is bounded and records a code in the context's error word when it gives up.
 #include <algorithm>
@@ -38,27 +43,34 @@ constexpr int PA_Q_BYTES = PA_QT * PA_DQK * 2;        // 49152: three [128][64] 
 constexpr int PA_K_BYTES = PA_KT * PA_DQK * 2;        // 24576: three [64][64] blocks
 constexpr int PA_C_BYTES = PA_KT * PA_DV * 2;         // 32768: four [64][64] blocks
 constexpr int PA_P_BYTES = PA_QT * PA_KT * 2;         // 16384: one [128][64] block
-constexpr int PA_KST = 3, PA_CST = 2;
+constexpr int PA_KST = 2, PA_CST = 3;                  // the latent is needed last and its slot comes free last: the deeper ring
 constexpr int PA_OFF_Q = 0;
 constexpr int PA_OFF_K = PA_Q_BYTES;
 constexpr int PA_OFF_C = PA_OFF_K + PA_KST * PA_K_BYTES;
 constexpr int PA_OFF_P = PA_OFF_C + PA_CST * PA_C_BYTES;
-constexpr int PA_OFF_BAR = PA_OFF_P + 2 * PA_P_BYTES;  // 221184
-constexpr int PA_SMEM = PA_OFF_BAR + 256 + 1024;
-constexpr uint32_t PA_COL_O = 0, PA_COL_S = 256;       // S buffers at 256 and 320
-constexpr float PA_LAZY = 8.f;
-enum { PB_QFULL = 0, PB_KFULL = 1, PB_KEMPTY = 4, PB_CFULL = 7, PB_CEMPTY = 9, PB_SFULL = 11, PB_SEMPTY = 13, PB_PFULL = 15, PB_ODONE = 17,
-       PB_COUNT = 18 };
+constexpr int PA_OFF_BAR = PA_OFF_P + 2 * PA_P_BYTES;  // 229376
+constexpr int PA_OFF_X = PA_OFF_BAR + 256;             // [2][128] f32 exchanged between the two softmax groups
+static_assert(PA_OFF_BAR == 229376, "shared-memory budget");
+constexpr int PA_SMEM = PA_OFF_X + 1024 + 1024;
+constexpr uint32_t PA_COL_O = 0, PA_COL_S = 256;       // S buffers at 256, 320 and 384
+constexpr float PA_LAZY = 8.f;                         // exact form: rescale when a score outruns the reference by 2^8
+constexpr float PA_RANGE = 64.f;                       // fast form: flag the block when a score outruns it by 2^64
+constexpr int PA_SBUF = 3;                             // score buffers in tensor memory: the scores run two tiles ahead of the values
+enum { PB_QFULL = 0, PB_KFULL = 1, PB_KEMPTY = 3, PB_CFULL = 5, PB_CEMPTY = 8, PB_SFULL = 11, PB_SEMPTY = 14, PB_PFULL = 17, PB_PEMPTY = 19,
+       PB_ODONE = 21, PB_COUNT = 22 };
 
 struct AttnParams {
     uint16_t *out;      // bf16 [n][nh][512]
-    int n, nh;
+    int n, nh, T;       // T = pos0 + n cached rows
     int64_t pos0;
     float scale_log2;
+    int *flags;         // one word per block: fast form sets it, exact form runs only where it is set
     int *err;
+    long long *trace;   // optional clock64 stamps of block (0, 0, 0): [role][tile][event]; NULL = off
 };
 
-__global__ void __launch_bounds__(256, 1)
+template <int NWG>      // softmax warp groups: 2 = fast form, 1 = exact form
+__global__ void __launch_bounds__(128 + 128 * NWG, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_c,
                     const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -70,6 +82,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + PA_OFF_BAR + 8 * PB_COUNT + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int *flag = p.flags + ((int)blockIdx.z * (int)gridDim.y + (int)blockIdx.y) * (int)gridDim.x + (int)blockIdx.x;
+    if (NWG == 1 && *flag == 0) return;                           // the repair pass: nothing to repair here
     const int qtile = (int)gridDim.x - 1 - (int)blockIdx.x;      // longest blocks first
     const int h = blockIdx.y, half = blockIdx.z;
     const int q0 = qtile * PA_QT;
@@ -82,8 +96,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_c) : "memory");
         for (int i = 0; i < PB_COUNT; i++) {
-            const bool by128 = (i >= PB_SEMPTY && i < PB_ODONE);         // s_empty, p_full: every softmax thread
-            mbar_init(bar(i), by128 ? 128u : 1u);
+            const bool by_soft = (i >= PB_SEMPTY && i < PB_PEMPTY);      // s_empty, p_full: every softmax thread
+            mbar_init(bar(i), by_soft ? (uint32_t)(128 * NWG) : 1u);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -95,47 +109,68 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
+    long long *tr = (p.trace && NWG == 2 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+#define PTRACE(role, it, ev) do { if (tr && (it) < 16) tr[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
+    if (tr && tid == 0) tr[3 * 16 * 8] = clock64();
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer of Q and the key ring
         if (lane == 0) {
             mbar_expect_tx(bar(PB_QFULL), PA_Q_BYTES);
             tma_load_3d(base + PA_OFF_Q, &tm_q, 0, q0, h * 3, bar(PB_QFULL));
             bool ok = true;
-            int k_issued = 0, c_issued = 0;
+            int issued = 0;
             for (int i = 0; i < nt && ok; i++) {
-                const int ks = i % PA_KST, ku = i / PA_KST, cs = i & 1, cu = i >> 1;
+                const int ks = i % PA_KST, ku = i / PA_KST;
                 ok = mbar_wait(bar(PB_KEMPTY + ks), (uint32_t)((ku & 1) ^ 1), p.err, 1001);
                 if (!ok) break;
+                PTRACE(0, i, 0);
                 mbar_expect_tx(bar(PB_KFULL + ks), PA_K_BYTES);
-                tma_load_3d(base + PA_OFF_K + ks * PA_K_BYTES, &tm_k, 0, i * PA_KT, h * 3, bar(PB_KFULL + ks));
-                k_issued = i + 1;
-                ok = mbar_wait(bar(PB_CEMPTY + cs), (uint32_t)((cu & 1) ^ 1), p.err, 1002);
-                if (!ok) break;
-                mbar_expect_tx(bar(PB_CFULL + cs), PA_C_BYTES);
-                tma_load_3d(base + PA_OFF_C + cs * PA_C_BYTES, &tm_c, 0, i * PA_KT, half * 4, bar(PB_CFULL + cs));
-                c_issued = i + 1;
+                tma_load_3d(base + PA_OFF_K + ks * PA_K_BYTES, &tm_k, 0, h * p.T + i * PA_KT, 0, bar(PB_KFULL + ks));
+                issued = i + 1;
             }
             if (!ok) {      // drain the copies still in flight before leaving
                 mbar_wait(bar(PB_QFULL), 0, p.err, 1003);
-                for (int i = (k_issued > PA_KST ? k_issued - PA_KST : 0); i < k_issued; i++)
+                for (int i = (issued > PA_KST ? issued - PA_KST : 0); i < issued; i++)
                     mbar_wait(bar(PB_KFULL + i % PA_KST), (uint32_t)((i / PA_KST) & 1), p.err, 1004);
-                for (int i = (c_issued > PA_CST ? c_issued - PA_CST : 0); i < c_issued; i++)
-                    mbar_wait(bar(PB_CFULL + (i & 1)), (uint32_t)((i >> 1) & 1), p.err, 1005);
             }
         }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ TMA producer of the latent ring (its slots come free much
+        // later than the key slots: a thread of its own, so that the keys run ahead)
+        if (lane == 0) {
+            bool ok = true;
+            int issued = 0;
+            for (int i = 0; i < nt && ok; i++) {
+                const int cs = i % PA_CST, cu = i / PA_CST;
+                ok = mbar_wait(bar(PB_CEMPTY + cs), (uint32_t)((cu & 1) ^ 1), p.err, 1002);
+                if (!ok) break;
+                PTRACE(0, i, 1);
+                mbar_expect_tx(bar(PB_CFULL + cs), PA_C_BYTES);
+                tma_load_3d(base + PA_OFF_C + cs * PA_C_BYTES, &tm_c, 0, i * PA_KT, half * 4, bar(PB_CFULL + cs));
+                issued = i + 1;
+            }
+            if (!ok)
+                for (int i = (issued > PA_CST ? issued - PA_CST : 0); i < issued; i++)
+                    mbar_wait(bar(PB_CFULL + i % PA_CST), (uint32_t)((i / PA_CST) & 1), p.err, 1005);
+        }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------ MMA issuer of the scores
+        // The two products have issuers of their own (this warp and warp 3): a wait on an mbarrier costs a
+        // lone thread some 300 cycles even when the phase is long complete, and one thread doing all four
+        // waits of a tile in turn was the longest chain of the kernel.
         if (lane == 0) {
             constexpr uint32_t ID_QK = idesc_bf16(128, PA_KT, 0, 0);
-            constexpr uint32_t ID_PV = idesc_bf16(128, PA_DV, 0, 1);
             const uint64_t dQ = smem_desc(base + PA_OFF_Q, 16, 1024);
             bool ok = mbar_wait(bar(PB_QFULL), 0, p.err, 1011);
-            // scores of tile j: S[j & 1] = Q Kx^T, three 64-wide blocks of the 192 dims, four 16-wide steps each
-            auto issue_qk = [&](int j) -> bool {
-                const int ks = j % PA_KST, ku = j / PA_KST, sb = j & 1, su = j >> 1;
-                if (!mbar_wait(bar(PB_KFULL + ks), (uint32_t)(ku & 1), p.err, 1012)) return false;
-                if (!mbar_wait(bar(PB_SEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1013)) return false;
+            // scores of tile j: S[j % 3] = Q Kx^T, three 64-wide blocks of the 192 dims, four 16-wide steps each
+            for (int j = 0; j < nt && ok; j++) {
+                const int ks = j % PA_KST, ku = j / PA_KST, sb = j % PA_SBUF, su = j / PA_SBUF;
+                ok = mbar_wait(bar(PB_KFULL + ks), (uint32_t)(ku & 1), p.err, 1012);
+                PTRACE(1, j, 0);
+                if (ok) ok = mbar_wait(bar(PB_SEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1013);
+                if (!ok) break;
+                PTRACE(1, j, 1);
                 tc_fence_after();
                 const uint64_t dK = smem_desc(base + PA_OFF_K + ks * PA_K_BYTES, 16, 1024);
 #pragma unroll
@@ -144,116 +179,153 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                               dK + (uint64_t)(((s >> 2) * (PA_KT * 128) + (s & 3) * 32) >> 4), ID_QK, s != 0);
                 umma_commit(bar(PB_KEMPTY + ks));
                 umma_commit(bar(PB_SFULL + sb));
-                return true;
-            };
-            if (ok) ok = issue_qk(0);
+                PTRACE(1, j, 2);
+            }
+        }
+    } else if (warp == 3) {
+        // ------------------------------------------------------------ MMA issuer of the values
+        if (lane == 0) {
+            constexpr uint32_t ID_PV = idesc_bf16(128, PA_DV, 0, 1);
+            bool ok = true;
             for (int i = 0; i < nt && ok; i++) {
-                if (i + 1 < nt) ok = issue_qk(i + 1);
-                if (!ok) break;
-                const int cs = i & 1, cu = i >> 1;
+                const int cs = i % PA_CST, cu = i / PA_CST, pb = i & 1, pu = i >> 1;
                 ok = mbar_wait(bar(PB_CFULL + cs), (uint32_t)(cu & 1), p.err, 1014);
-                if (ok) ok = mbar_wait(bar(PB_PFULL + cs), (uint32_t)(cu & 1), p.err, 1015);
+                PTRACE(1, i, 3);
+                if (ok) ok = mbar_wait(bar(PB_PFULL + pb), (uint32_t)(pu & 1), p.err, 1015);
                 if (!ok) break;
+                PTRACE(1, i, 4);
                 tc_fence_after();
                 // values: O += P lat, P [128 q][64 keys] K-major, lat half [64 keys][256] with the 256 contiguous (MN-major, four 64-wide blocks)
-                const uint64_t dP = smem_desc(base + PA_OFF_P + cs * PA_P_BYTES, 16, 1024);
+                const uint64_t dP = smem_desc(base + PA_OFF_P + pb * PA_P_BYTES, 16, 1024);
                 const uint64_t dC = smem_desc(base + PA_OFF_C + cs * PA_C_BYTES, PA_KT * 128, 1024);
 #pragma unroll
                 for (int s = 0; s < 4; s++)
                     umma_bf16(tmem + PA_COL_O, dP + (uint64_t)((s * 32) >> 4), dC + (uint64_t)((s * 2048) >> 4), ID_PV, (s != 0) ? 1u : (uint32_t)(i != 0));
                 umma_commit(bar(PB_CEMPTY + cs));
+                umma_commit(bar(PB_PEMPTY + pb));
+                PTRACE(1, i, 5);
             }
             if (ok) umma_commit(bar(PB_ODONE));
         }
     } else if (warp >= 4) {
-        // ------------------------------------------------------------ softmax, correction, epilogue: one query row per thread
-        const int q4 = warp & 3;
+        // ------------------------------------------------------------ softmax, (correction,) epilogue
+        // A thread owns query row `row` (= its TMEM lane) and NC of the tile's 64 key columns.
+        constexpr int NC = PA_KT / NWG;
+        const int q4 = warp & 3, wg = (warp - 4) >> 2;
         const int row = q4 * 32 + lane;
         const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
         const int64_t tq = p.pos0 + q0 + row;                    // this row's position: keys 0..tq are visible
+        float *s_x = reinterpret_cast<float *>(sm + PA_OFF_X);
         float m = 0.f, l = 0.f;
-        bool ok = true;
+        bool ok = true, met = false;       // met: this thread has been to the first tile's barrier (every thread goes exactly once)
         for (int i = 0; i < nt; i++) {
-            const int sb = i & 1, su = i >> 1;
-            ok = mbar_wait(bar(PB_SFULL + sb), (uint32_t)(su & 1), p.err, 1021);
+            const int sb = i & 1, su = i >> 1;             // P buffer / latent slot of this tile
+            const int s3 = i % PA_SBUF;                       // its score buffer
+            ok = mbar_wait(bar(PB_SFULL + s3), (uint32_t)((i / PA_SBUF) & 1), p.err, 1021);
             if (!ok) break;
+            if (tid == 128) PTRACE(2, i, 0);
             tc_fence_after();
-            uint32_t v[PA_KT];
-            TMEM_LD16(v, 0, tlane + PA_COL_S + sb * PA_KT);
-            TMEM_LD16(v, 16, tlane + PA_COL_S + sb * PA_KT + 16);
-            TMEM_LD16(v, 32, tlane + PA_COL_S + sb * PA_KT + 32);
-            TMEM_LD16(v, 48, tlane + PA_COL_S + sb * PA_KT + 48);
+            uint32_t v[NC];
+#pragma unroll
+            for (int c = 0; c < NC / 16; c++) TMEM_LD16(v, c * 16, tlane + PA_COL_S + s3 * PA_KT + wg * NC + c * 16);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             tc_fence_before();
-            mbar_arrive(bar(PB_SEMPTY + sb));
-            float s[PA_KT];
+            mbar_arrive(bar(PB_SEMPTY + s3));
+            if (tid == 128) PTRACE(2, i, 1);
+            float s[NC];
             float mt = -INFINITY;
-            const int64_t k0 = (int64_t)i * PA_KT;
-            if (k0 + PA_KT - 1 <= p.pos0 + q0) {                 // every key of the tile is visible to every row of the block
+            const int64_t k0 = (int64_t)i * PA_KT + wg * NC;
+            if ((int64_t)i * PA_KT + PA_KT - 1 <= p.pos0 + q0) {   // every key of the tile is visible to every row of the block
 #pragma unroll
-                for (int j = 0; j < PA_KT; j++) { s[j] = __uint_as_float(v[j]) * p.scale_log2; mt = fmaxf(mt, s[j]); }
+                for (int j = 0; j < NC; j++) { s[j] = __uint_as_float(v[j]) * p.scale_log2; mt = fmaxf(mt, s[j]); }
             } else {
 #pragma unroll
-                for (int j = 0; j < PA_KT; j++) {
+                for (int j = 0; j < NC; j++) {
                     s[j] = (k0 + j <= tq) ? __uint_as_float(v[j]) * p.scale_log2 : -INFINITY;
                     mt = fmaxf(mt, s[j]);
                 }
             }
-            if (i == 0) {
-                m = mt;                                          // key 0 is visible to every row: finite
-            } else if (mt > m + PA_LAZY) {
-                // this row's scores outran its reference exponent: rescale what it has accumulated. The row is this
-                // thread's TMEM lane; the value MMAs of the previous tile must have finished writing it.
-                ok = mbar_wait(bar(PB_CEMPTY + ((i - 1) & 1)), (uint32_t)(((i - 1) >> 1) & 1), p.err, 1022);
-                if (!ok) break;
-                tc_fence_after();
-                const float alpha = exp2f(m - mt);
-                l *= alpha;
-                m = mt;
-                for (int c = 0; c < PA_DV / 16; c++) {
-                    uint32_t o[16];
-                    TMEM_LD16(o, 0, tlane + PA_COL_O + c * 16);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-                    TMEM_ST16(o, 0, tlane + PA_COL_O + c * 16);
+            if (NWG == 2) {
+                if (i == 0) {                                    // reference exponent of the row: its largest score of the first tile
+                    s_x[wg * 128 + row] = mt;
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    met = true;
+                    m = fmaxf(s_x[row], s_x[128 + row]);         // key 0 is visible to every row: finite
+                    asm volatile("bar.sync 1, 256;" ::: "memory");   // s_x is reused for the sums at the end
+                } else if (mt > m + PA_RANGE) {
+                    *flag = 1;                                   // out of the range this form covers: the exact form redoes the block
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            } else {
+                if (i == 0) {
+                    m = mt;
+                } else if (mt > m + PA_LAZY) {
+                    // this row's scores outran its reference exponent: rescale what it has accumulated. The row is this
+                    // thread's TMEM lane; the value MMAs of the previous tile must have finished writing it.
+                    ok = mbar_wait(bar(PB_PEMPTY + ((i - 1) & 1)), (uint32_t)(((i - 1) >> 1) & 1), p.err, 1022);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const float alpha = exp2f(m - mt);
+                    l *= alpha;
+                    m = mt;
+                    for (int c = 0; c < PA_DV / 16; c++) {
+                        uint32_t o[16];
+                        TMEM_LD16(o, 0, tlane + PA_COL_O + c * 16);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                        TMEM_ST16(o, 0, tlane + PA_COL_O + c * 16);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
             }
-            uint32_t pk[PA_KT / 2];
+            uint32_t pk[NC / 2];
             float lsum = 0.f;
 #pragma unroll
-            for (int j = 0; j < PA_KT; j += 2) {
+            for (int j = 0; j < NC; j += 2) {
                 const float p0 = exp2f(s[j] - m), p1 = exp2f(s[j + 1] - m);
                 lsum += p0 + p1;
                 pk[j >> 1] = pack_bf16x2(p0, p1);
             }
             l += lsum;
             // the P buffer of this parity was read by the value MMAs of tile i - 2
-            ok = mbar_wait(bar(PB_CEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1023);
+            if (tid == 128) PTRACE(2, i, 2);
+            ok = mbar_wait(bar(PB_PEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1023);
             if (!ok) break;
+            if (tid == 128) PTRACE(2, i, 3);
             uint8_t *prow = sm + PA_OFF_P + sb * PA_P_BYTES + row * 128;
 #pragma unroll
-            for (int c = 0; c < 8; c++)
-                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            for (int c = 0; c < NC / 8; c++)
+                *reinterpret_cast<uint4 *>(prow + (((wg * (NC / 8) + c) ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             mbar_arrive(bar(PB_PFULL + sb));
+            if (tid == 128) PTRACE(2, i, 4);
         }
         // ---- epilogue: O / l -> bf16 -> out[t][h][half * 256 ..], through the (now idle) P buffers for full-line stores
         if (ok) ok = mbar_wait(bar(PB_ODONE), 0, p.err, 1024);
+        if (NWG == 2) {                                          // the row's sum is the two groups' sums (every thread takes part in the barriers)
+            if (!met) {                                          // a wait gave up before the first tile: keep the barrier counts in step
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+            }
+            s_x[wg * 128 + row] = l;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            l = s_x[row] + s_x[128 + row];
+        }
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint8_t *stg = sm + PA_OFF_P + q4 * 4096;                // 4 KB per warp: [32 rows][128 B]
+            uint8_t *stg = sm + PA_OFF_P + (warp - 4) * 4096;        // 4 KB per warp: [32 rows][128 B]
             const int t0w = q0 + q4 * 32;
+            constexpr int NCH = PA_DV / 64 / NWG;                     // 64-column chunks per thread
 #pragma unroll 1
-            for (int c = 0; c < PA_DV / 64; c++) {
+            for (int c = 0; c < NCH; c++) {
+                const int col = (wg * NCH + c) * 64;
                 uint32_t o[64];
-                TMEM_LD16(o, 0, tlane + PA_COL_O + c * 64);
-                TMEM_LD16(o, 16, tlane + PA_COL_O + c * 64 + 16);
-                TMEM_LD16(o, 32, tlane + PA_COL_O + c * 64 + 32);
-                TMEM_LD16(o, 48, tlane + PA_COL_O + c * 64 + 48);
+                TMEM_LD16(o, 0, tlane + PA_COL_O + col);
+                TMEM_LD16(o, 16, tlane + PA_COL_O + col + 16);
+                TMEM_LD16(o, 32, tlane + PA_COL_O + col + 32);
+                TMEM_LD16(o, 48, tlane + PA_COL_O + col + 48);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
@@ -270,7 +342,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
                     const uint4 w = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
                     if (t0w + rr < p.n)
-                        *reinterpret_cast<uint4 *>(p.out + ((int64_t)(t0w + rr) * p.nh + h) * PA_L + half * PA_DV + c * 64 + jj * 8) = w;
+                        *reinterpret_cast<uint4 *>(p.out + ((int64_t)(t0w + rr) * p.nh + h) * PA_L + half * PA_DV + col + jj * 8) = w;
                 }
                 __syncwarp();
             }
@@ -285,7 +357,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Key expansion: Kx[c][h][0:128] = W_uk[h] lat[c], Kx[c][h][128:192] = k_rope[c].
+// Key expansion: Kx[h][c][0:128] = W_uk[h] lat[c], Kx[h][c][128:192] = k_rope[c].
 constexpr int KX_TOK = 128, KX_NOPE = 128;
 constexpr int KX_W_BYTES = KX_NOPE * PA_L * 2;        // 131072: eight [128 d][64 l] blocks
 constexpr int KX_A_BYTES = KX_TOK * 128 * 2;          // 32768: two [128 tok][64 l] blocks = one 128-wide chunk of the latent
@@ -295,7 +367,7 @@ enum { KB_WFULL = 0, KB_AFULL = 1, KB_AEMPTY = 3, KB_DFULL = 5, KB_DEMPTY = 7, K
 
 struct KexpParams {
     const uint16_t *cache;    // bf16 [T][576]
-    uint16_t *kx;             // bf16 [T][nh][192]
+    uint16_t *kx;             // bf16 [nh][T][192]: head-major, so that a head's key tile is one contiguous 24 KB
     int T, nh;
     int *err;
 };
@@ -386,7 +458,7 @@ kexp_tc_kernel(const __grid_constant__ CUtensorMap tm_lat, const __grid_constant
                 const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
                 if (t0w + rr < p.T) {
                     const uint4 w = *reinterpret_cast<const uint4 *>(p.cache + (int64_t)(t0w + rr) * PA_ROW + PA_L + jj * 8);
-                    *reinterpret_cast<uint4 *>(p.kx + ((int64_t)(t0w + rr) * p.nh + h) * PA_DQK + KX_NOPE + jj * 8) = w;
+                    *reinterpret_cast<uint4 *>(p.kx + ((int64_t)h * p.T + t0w + rr) * PA_DQK + KX_NOPE + jj * 8) = w;
                 }
             }
             ok = mbar_wait(bar(KB_DFULL + db), (uint32_t)((ti >> 1) & 1), p.err, 1107);
@@ -415,7 +487,7 @@ kexp_tc_kernel(const __grid_constant__ CUtensorMap tm_lat, const __grid_constant
                     const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
                     const uint4 w = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
                     if (t0w + rr < p.T)
-                        *reinterpret_cast<uint4 *>(p.kx + ((int64_t)(t0w + rr) * p.nh + h) * PA_DQK + c * 64 + jj * 8) = w;
+                        *reinterpret_cast<uint4 *>(p.kx + ((int64_t)h * p.T + t0w + rr) * PA_DQK + c * 64 + jj * 8) = w;
                 }
                 __syncwarp();
             }
@@ -452,9 +524,10 @@ bool cwk_mla_prefill_attn_tc_ok(const void *Q, const void *cache, const void *Wu
 }
 
 // Q bf16 [n][nh][192] with the rope part already rotated; cache bf16 [pos0 + n][576] (latent | rope key);
-// Wuk bf16 [nh][128][512]; kx = workspace bf16 [pos0 + n][nh][192]; out bf16 [n][nh][512].
+// Wuk bf16 [nh][128][512]; kx = workspace bf16 [nh][pos0 + n][192]; flags = workspace int32, one per block of the
+// attention grid (ceil(n / 128) x nh x 2); out bf16 [n][nh][512].
 // Returns CWK_ERR_UNSUPPORTED (no error text) when the tensor path cannot run.
-int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int64_t pos0, int n, int nh,
+int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int *flags, int64_t pos0, int n, int nh,
                             float scale, void *out) {
     if (!cwk_encode_tiled_fn()) return CWK_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(Wuk) | reinterpret_cast<uintptr_t>(kx) |
@@ -467,13 +540,15 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
     if (!encode3(&tm_lat, cache, (uint64_t)T, PA_L / 64, PA_ROW * 2, KX_TOK, 2) ||                 // latent dims only: block index 8 (rope) stays out
         !encode3(&tm_w, Wuk, (uint64_t)nh * KX_NOPE, PA_L / 64, PA_L * 2, KX_NOPE, PA_L / 64) ||
         !encode3(&tm_q, Q, (uint64_t)n, (uint64_t)nh * 3, (uint64_t)nh * PA_DQK * 2, PA_QT, 3) ||
-        !encode3(&tm_k, kx, (uint64_t)T, (uint64_t)nh * 3, (uint64_t)nh * PA_DQK * 2, PA_KT, 3) ||
+        !encode3(&tm_k, kx, (uint64_t)nh * T, 3, PA_DQK * 2, PA_KT, 3) ||            // rows past a head's last key belong to the next head: every such key is masked
+
         !encode3(&tm_c, cache, (uint64_t)T, PA_L / 64, PA_ROW * 2, PA_KT, 4))
         return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the prefill attention operands");
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
         CWK_CUDA(ctx, cudaFuncSetAttribute(kexp_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KX_SMEM));
-        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PA_SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PA_SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PA_SMEM));
         attr_set[ctx->device & 15] = true;
     }
     {
@@ -487,10 +562,19 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
     }
     {
         AttnParams ap;
-        ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.pos0 = pos0; ap.scale_log2 = scale * 1.4426950408889634f; ap.err = ctx->dev_err;
-        CwkKernelTimer timer(ctx);
-        prefill_attn_kernel<<<dim3((n + PA_QT - 1) / PA_QT, nh, 2), 256, PA_SMEM, ctx->stream>>>(tm_q, tm_k, tm_c, ap);
-        CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel");
+        ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.T = T; ap.pos0 = pos0; ap.scale_log2 = scale * 1.4426950408889634f; ap.flags = flags;
+        ap.err = ctx->dev_err;
+        ap.trace = (long long *)ctx->tc_trace;
+        const dim3 grid((n + PA_QT - 1) / PA_QT, nh, 2);
+        CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)grid.x * grid.y * grid.z * sizeof(int), ctx->stream));
+        {
+            CwkKernelTimer timer(ctx);
+            prefill_attn_kernel<2><<<grid, 384, PA_SMEM, ctx->stream>>>(tm_q, tm_k, tm_c, ap);
+            CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<2>");
+        }
+        // the repair pass: blocks whose flag is clear return at once
+        prefill_attn_kernel<1><<<grid, 256, PA_SMEM, ctx->stream>>>(tm_q, tm_k, tm_c, ap);
+        CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<1>");
     }
     return CWK_OK;
 }
