@@ -19,7 +19,9 @@
 //   prefill_attn_kernel: one block = 128 queries x one head x one half of the 512 value columns
 //     (the accumulator of a half, 128 x 256 f32, is half of tensor memory; both halves recompute
 //     the 192-wide scores, which is cheaper than any exchange). Keys stream in tiles of 64 through a
-//     2-deep ring (24 KB each), latent halves through a 3-deep ring (32 KB each), one TMA box each.
+//     3-deep ring (24 KB each), latent halves through a 3-deep ring (32 KB each), one TMA box each. The query tile
+//     itself sits in tensor memory (96 columns of bf16 pairs) as the A operand of the score MMAs: shared-memory
+//     bandwidth is what bounds this kernel, and this way the score MMAs read only the keys from it.
 //     Per tile: S = Q Kx^T (12 MMAs, M 128 x N 64) into one of two TMEM score buffers; the softmax
 //     warps own one query row per thread (TMEM lane = row, so row maxima and sums need no shuffles),
 //     write P (bf16) to shared memory; O += P lat (4 MMAs, M 128 x N 256). The two products have
@@ -39,27 +41,26 @@
 namespace {
 
 constexpr int PA_QT = 128, PA_KT = 64, PA_DQK = 192, PA_DV = 256, PA_L = 512, PA_ROW = 576;
-constexpr int PA_Q_BYTES = PA_QT * PA_DQK * 2;        // 49152: three [128][64] blocks
 constexpr int PA_K_BYTES = PA_KT * PA_DQK * 2;        // 24576: three [64][64] blocks
 constexpr int PA_C_BYTES = PA_KT * PA_DV * 2;         // 32768: four [64][64] blocks
 constexpr int PA_P_BYTES = PA_QT * PA_KT * 2;         // 16384: one [128][64] block
-constexpr int PA_KST = 2, PA_CST = 3;                  // the latent is needed last and its slot comes free last: the deeper ring
-constexpr int PA_OFF_Q = 0;
-constexpr int PA_OFF_K = PA_Q_BYTES;
+constexpr int PA_KST = 3, PA_CST = 3;
+constexpr int PA_OFF_K = 0;                            // (the query tile lives in tensor memory, not here)
 constexpr int PA_OFF_C = PA_OFF_K + PA_KST * PA_K_BYTES;
 constexpr int PA_OFF_P = PA_OFF_C + PA_CST * PA_C_BYTES;
-constexpr int PA_OFF_BAR = PA_OFF_P + 2 * PA_P_BYTES;  // 229376
+constexpr int PA_OFF_BAR = PA_OFF_P + 2 * PA_P_BYTES;  // 204800
 constexpr int PA_OFF_X = PA_OFF_BAR + 256;             // [2][128] f32 exchanged between the two softmax groups
-static_assert(PA_OFF_BAR == 229376, "shared-memory budget");
+static_assert(PA_OFF_BAR == 204800, "shared-memory budget");
 constexpr int PA_SMEM = PA_OFF_X + 1024 + 1024;
-constexpr uint32_t PA_COL_O = 0, PA_COL_S = 256;       // S buffers at 256, 320 and 384
+constexpr uint32_t PA_COL_O = 0, PA_COL_S = 256, PA_COL_Q = 384;   // S buffers at 256 and 320; Q: 96 columns of bf16 pairs
 constexpr float PA_LAZY = 8.f;                         // exact form: rescale when a score outruns the reference by 2^8
 constexpr float PA_RANGE = 64.f;                       // fast form: flag the block when a score outruns it by 2^64
-constexpr int PA_SBUF = 3;                             // score buffers in tensor memory: the scores run two tiles ahead of the values
-enum { PB_QFULL = 0, PB_KFULL = 1, PB_KEMPTY = 3, PB_CFULL = 5, PB_CEMPTY = 8, PB_SFULL = 11, PB_SEMPTY = 14, PB_PFULL = 17, PB_PEMPTY = 19,
+constexpr int PA_SBUF = 2;                             // score buffers in tensor memory
+enum { PB_QFULL = 0, PB_KFULL = 1, PB_KEMPTY = 4, PB_CFULL = 7, PB_CEMPTY = 10, PB_SFULL = 13, PB_SEMPTY = 15, PB_PFULL = 17, PB_PEMPTY = 19,
        PB_ODONE = 21, PB_COUNT = 22 };
 
 struct AttnParams {
+    const uint16_t *q;  // bf16 [n][nh][192], rope part rotated
     uint16_t *out;      // bf16 [n][nh][512]
     int n, nh, T;       // T = pos0 + n cached rows
     int64_t pos0;
@@ -71,8 +72,7 @@ struct AttnParams {
 
 template <int NWG>      // softmax warp groups: 2 = fast form, 1 = exact form
 __global__ void __launch_bounds__(128 + 128 * NWG, 1)
-prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_c,
-                    const AttnParams p) {
+prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_c, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -92,11 +92,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int nt = (int)(last_q / PA_KT) + 1;
 
     if (tid == 0) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_c) : "memory");
         for (int i = 0; i < PB_COUNT; i++) {
-            const bool by_soft = (i >= PB_SEMPTY && i < PB_PEMPTY);      // s_empty, p_full: every softmax thread
+            const bool by_soft = (i >= PB_SEMPTY && i < PB_PEMPTY) || i == PB_QFULL;   // s_empty, p_full, q_full: every softmax thread
             mbar_init(bar(i), by_soft ? (uint32_t)(128 * NWG) : 1u);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -114,10 +113,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (tr && tid == 0) tr[3 * 16 * 8] = clock64();
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer of Q and the key ring
+        // ------------------------------------------------------------ TMA producer of the key ring
         if (lane == 0) {
-            mbar_expect_tx(bar(PB_QFULL), PA_Q_BYTES);
-            tma_load_3d(base + PA_OFF_Q, &tm_q, 0, q0, h * 3, bar(PB_QFULL));
             bool ok = true;
             int issued = 0;
             for (int i = 0; i < nt && ok; i++) {
@@ -130,7 +127,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 issued = i + 1;
             }
             if (!ok) {      // drain the copies still in flight before leaving
-                mbar_wait(bar(PB_QFULL), 0, p.err, 1003);
                 for (int i = (issued > PA_KST ? issued - PA_KST : 0); i < issued; i++)
                     mbar_wait(bar(PB_KFULL + i % PA_KST), (uint32_t)((i / PA_KST) & 1), p.err, 1004);
             }
@@ -161,8 +157,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         // waits of a tile in turn was the longest chain of the kernel.
         if (lane == 0) {
             constexpr uint32_t ID_QK = idesc_bf16(128, PA_KT, 0, 0);
-            const uint64_t dQ = smem_desc(base + PA_OFF_Q, 16, 1024);
-            bool ok = mbar_wait(bar(PB_QFULL), 0, p.err, 1011);
+            bool ok = mbar_wait(bar(PB_QFULL), 0, p.err, 1011);     // the softmax threads have written the query tile into tensor memory
+            tc_fence_after();
             // scores of tile j: S[j % 3] = Q Kx^T, three 64-wide blocks of the 192 dims, four 16-wide steps each
             for (int j = 0; j < nt && ok; j++) {
                 const int ks = j % PA_KST, ku = j / PA_KST, sb = j % PA_SBUF, su = j / PA_SBUF;
@@ -175,8 +171,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 const uint64_t dK = smem_desc(base + PA_OFF_K + ks * PA_K_BYTES, 16, 1024);
 #pragma unroll
                 for (int s = 0; s < 12; s++)
-                    umma_bf16(tmem + PA_COL_S + sb * PA_KT, dQ + (uint64_t)(((s >> 2) * (PA_QT * 128) + (s & 3) * 32) >> 4),
-                              dK + (uint64_t)(((s >> 2) * (PA_KT * 128) + (s & 3) * 32) >> 4), ID_QK, s != 0);
+                    umma_bf16_ts(tmem + PA_COL_S + sb * PA_KT, tmem + PA_COL_Q + s * 8,       // A: 16 bf16 of every row = 8 TMEM columns per step
+                                 dK + (uint64_t)(((s >> 2) * (PA_KT * 128) + (s & 3) * 32) >> 4), ID_QK, s != 0);
                 umma_commit(bar(PB_KEMPTY + ks));
                 umma_commit(bar(PB_SFULL + sb));
                 PTRACE(1, j, 2);
@@ -216,6 +212,27 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
         const int64_t tq = p.pos0 + q0 + row;                    // this row's position: keys 0..tq are visible
         float *s_x = reinterpret_cast<float *>(sm + PA_OFF_X);
+        {
+            // The query tile is the A operand of every score MMA of this block; it is kept in tensor memory (row =
+            // lane, two consecutive bf16 per 32-bit column), so that those MMAs read only the keys from shared
+            // memory. A thread copies its row's share: 96 columns split between the groups.
+            constexpr int QW = (PA_DQK / 2) / NWG;               // 32-bit words per thread
+            const int t = q0 + row;
+            const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((int64_t)t * p.nh + h) * PA_DQK) + wg * (QW / 4);
+#pragma unroll
+            for (int c = 0; c < QW / 16; c++) {
+                uint32_t w[16];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint4 v = (t < p.n) ? src[c * 4 + j] : make_uint4(0, 0, 0, 0);
+                    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+                }
+                TMEM_ST16(w, 0, tlane + PA_COL_Q + wg * QW + c * 16);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar(PB_QFULL));
+        }
         float m = 0.f, l = 0.f;
         bool ok = true, met = false;       // met: this thread has been to the first tile's barrier (every thread goes exactly once)
         for (int i = 0; i < nt; i++) {
@@ -536,10 +553,9 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
     int s = cwk_ensure_err_word(ctx);
     if (s != CWK_OK) return s;
     const int T = (int)(pos0 + n);
-    CUtensorMap tm_lat, tm_w, tm_q, tm_k, tm_c;
+    CUtensorMap tm_lat, tm_w, tm_k, tm_c;
     if (!encode3(&tm_lat, cache, (uint64_t)T, PA_L / 64, PA_ROW * 2, KX_TOK, 2) ||                 // latent dims only: block index 8 (rope) stays out
         !encode3(&tm_w, Wuk, (uint64_t)nh * KX_NOPE, PA_L / 64, PA_L * 2, KX_NOPE, PA_L / 64) ||
-        !encode3(&tm_q, Q, (uint64_t)n, (uint64_t)nh * 3, (uint64_t)nh * PA_DQK * 2, PA_QT, 3) ||
         !encode3(&tm_k, kx, (uint64_t)nh * T, 3, PA_DQK * 2, PA_KT, 3) ||            // rows past a head's last key belong to the next head: every such key is masked
 
         !encode3(&tm_c, cache, (uint64_t)T, PA_L / 64, PA_ROW * 2, PA_KT, 4))
@@ -562,18 +578,18 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
     }
     {
         AttnParams ap;
-        ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.T = T; ap.pos0 = pos0; ap.scale_log2 = scale * 1.4426950408889634f; ap.flags = flags;
+        ap.q = (const uint16_t *)Q; ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.T = T; ap.pos0 = pos0; ap.scale_log2 = scale * 1.4426950408889634f; ap.flags = flags;
         ap.err = ctx->dev_err;
         ap.trace = (long long *)ctx->tc_trace;
         const dim3 grid((n + PA_QT - 1) / PA_QT, nh, 2);
         CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)grid.x * grid.y * grid.z * sizeof(int), ctx->stream));
         {
             CwkKernelTimer timer(ctx);
-            prefill_attn_kernel<2><<<grid, 384, PA_SMEM, ctx->stream>>>(tm_q, tm_k, tm_c, ap);
+            prefill_attn_kernel<2><<<grid, 384, PA_SMEM, ctx->stream>>>(tm_k, tm_c, ap);
             CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<2>");
         }
         // the repair pass: blocks whose flag is clear return at once
-        prefill_attn_kernel<1><<<grid, 256, PA_SMEM, ctx->stream>>>(tm_q, tm_k, tm_c, ap);
+        prefill_attn_kernel<1><<<grid, 256, PA_SMEM, ctx->stream>>>(tm_k, tm_c, ap);
         CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<1>");
     }
     return CWK_OK;
