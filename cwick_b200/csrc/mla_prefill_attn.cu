@@ -49,15 +49,15 @@ constexpr int PA_OFF_K = 0;                            // (the query tile lives 
 constexpr int PA_OFF_C = PA_OFF_K + PA_KST * PA_K_BYTES;
 constexpr int PA_OFF_P = PA_OFF_C + PA_CST * PA_C_BYTES;
 constexpr int PA_OFF_BAR = PA_OFF_P + 2 * PA_P_BYTES;  // 204800
-constexpr int PA_OFF_X = PA_OFF_BAR + 256;             // [2][128] f32 exchanged between the two softmax groups
+constexpr int PA_OFF_X = PA_OFF_BAR + 512;             // [2][128] f32 maxima, [2][128] f32 sums exchanged between the two softmax groups; 8 item numbers
 static_assert(PA_OFF_BAR == 204800, "shared-memory budget");
-constexpr int PA_SMEM = PA_OFF_X + 1024 + 1024;
+constexpr int PA_SMEM = PA_OFF_X + 2048 + 64 + 1024;
 constexpr uint32_t PA_COL_O = 0, PA_COL_S = 256, PA_COL_Q = 384;   // S buffers at 256 and 320; Q: 96 columns of bf16 pairs
 constexpr float PA_LAZY = 8.f;                         // exact form: rescale when a score outruns the reference by 2^8
 constexpr float PA_RANGE = 64.f;                       // fast form: flag the block when a score outruns it by 2^64
 constexpr int PA_SBUF = 2;                             // score buffers in tensor memory
 enum { PB_QFULL = 0, PB_KFULL = 1, PB_KEMPTY = 4, PB_CFULL = 7, PB_CEMPTY = 10, PB_SFULL = 13, PB_SEMPTY = 15, PB_PFULL = 17, PB_PEMPTY = 19,
-       PB_ODONE = 21, PB_COUNT = 22 };
+       PB_ODONE = 21, PB_QEMPTY = 22, PB_OFREE = 23, PB_XM = 24, PB_XL = 25, PB_ITEM = 26, PB_COUNT = 34 };
 
 struct AttnParams {
     const uint16_t *q;  // bf16 [n][nh][192], rope part rotated
@@ -65,11 +65,32 @@ struct AttnParams {
     int n, nh, T;       // T = pos0 + n cached rows
     int64_t pos0;
     float scale_log2;
-    int *flags;         // one word per block: fast form sets it, exact form runs only where it is set
+    int *flags;         // one word per item: fast form sets it, exact form runs only where it is set
+    int *counter;       // [2] item counters (fast form, exact form), zero at launch
     int *err;
     long long *trace;   // optional clock64 stamps of block (0, 0, 0): [role][tile][event]; NULL = off
 };
 
+struct AttnItem {
+    int q0, h, half, nt;
+};
+
+// Work item w of the attention grid: query tiles from the longest to the shortest inside one (head, half), then the next
+// (head, half): blocks that run at the same time work on the same few heads, whose keys stay in L2.
+__device__ __forceinline__ AttnItem attn_item(int w, const AttnParams &p, int nq) {
+    AttnItem it;
+    const int qtile = nq - 1 - (w % nq), hh = w / nq;
+    it.q0 = qtile * PA_QT;
+    it.h = hh % p.nh;
+    it.half = hh / p.nh;
+    const int64_t last_q = p.pos0 + min(it.q0 + PA_QT - 1, p.n - 1);     // keys 0 .. pos0 + (last query of the item): tiles of 64
+    it.nt = (int)(last_q / PA_KT) + 1;
+    return it;
+}
+
+// Persistent: one block per SM takes items from a global counter until none is left. The first TMA operation of a
+// block waits several thousand cycles for its tensor map, tensor memory is allocated once, and the loads of the next
+// item run under the epilogue of this one.
 template <int NWG>      // softmax warp groups: 2 = fast form, 1 = exact form
 __global__ void __launch_bounds__(128 + 128 * NWG, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_c, const AttnParams p) {
@@ -80,22 +101,18 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const uint32_t bar0 = base + PA_OFF_BAR;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + PA_OFF_BAR + 8 * PB_COUNT + 8);
+    volatile int *s_item = reinterpret_cast<volatile int *>(sm + PA_OFF_X + 2048);      // ring of 8 item numbers
+    float *s_m = reinterpret_cast<float *>(sm + PA_OFF_X), *s_l = s_m + 256;              // [2][128] each
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    int *flag = p.flags + ((int)blockIdx.z * (int)gridDim.y + (int)blockIdx.y) * (int)gridDim.x + (int)blockIdx.x;
-    if (NWG == 1 && *flag == 0) return;                           // the repair pass: nothing to repair here
-    const int qtile = (int)gridDim.x - 1 - (int)blockIdx.x;      // longest blocks first
-    const int h = blockIdx.y, half = blockIdx.z;
-    const int q0 = qtile * PA_QT;
-    // keys 0 .. pos0 + (last query of the block): tiles of 64
-    const int64_t last_q = p.pos0 + min(q0 + PA_QT - 1, p.n - 1);
-    const int nt = (int)(last_q / PA_KT) + 1;
+    const int nq = (p.n + PA_QT - 1) / PA_QT;
+    const int total = nq * p.nh * 2;
 
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_c) : "memory");
         for (int i = 0; i < PB_COUNT; i++) {
-            const bool by_soft = (i >= PB_SEMPTY && i < PB_PEMPTY) || i == PB_QFULL;   // s_empty, p_full, q_full: every softmax thread
+            const bool by_soft = (i >= PB_SEMPTY && i < PB_PEMPTY) || i == PB_QFULL || i == PB_OFREE || i == PB_XM || i == PB_XL;
             mbar_init(bar(i), by_soft ? (uint32_t)(128 * NWG) : 1u);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -108,47 +125,62 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    long long *tr = (p.trace && NWG == 2 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
-#define PTRACE(role, it, ev) do { if (tr && (it) < 16) tr[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
-    if (tr && tid == 0) tr[3 * 16 * 8] = clock64();
+
+    // item k of this block, as published by the key producer (-1: no more)
+    auto next_item = [&](int k, int &w) -> bool {
+        if (!mbar_wait(bar(PB_ITEM + (k & 7)), (uint32_t)((k >> 3) & 1), p.err, 1031)) return false;
+        w = s_item[k & 7];
+        return true;
+    };
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer of the key ring
+        // ------------------------------------------------------------ item fetcher and TMA producer of the key ring
         if (lane == 0) {
             bool ok = true;
-            int issued = 0;
-            for (int i = 0; i < nt && ok; i++) {
-                const int ks = i % PA_KST, ku = i / PA_KST;
-                ok = mbar_wait(bar(PB_KEMPTY + ks), (uint32_t)((ku & 1) ^ 1), p.err, 1001);
-                if (!ok) break;
-                PTRACE(0, i, 0);
-                mbar_expect_tx(bar(PB_KFULL + ks), PA_K_BYTES);
-                tma_load_3d(base + PA_OFF_K + ks * PA_K_BYTES, &tm_k, 0, h * p.T + i * PA_KT, 0, bar(PB_KFULL + ks));
-                issued = i + 1;
+            int kc = 0;                              // key tiles issued so far (ring position and phase run across items)
+            for (int k = 0; ok; k++) {
+                int w = atomicAdd(p.counter + (NWG == 1 ? 1 : 0), 1);
+                if (NWG == 1)                         // the repair pass takes flagged items only
+                    while (w < total && p.flags[w] == 0) w = atomicAdd(p.counter + 1, 1);
+                if (w >= total) w = -1;
+                s_item[k & 7] = w;                    // the roles of a block stay within a few tiles of each other: 8 slots cannot wrap
+                mbar_arrive(bar(PB_ITEM + (k & 7)));
+                if (w < 0) break;
+                const AttnItem it = attn_item(w, p, nq);
+                for (int i = 0; i < it.nt && ok; i++, kc++) {
+                    const int ks = kc % PA_KST, ku = kc / PA_KST;
+                    ok = mbar_wait(bar(PB_KEMPTY + ks), (uint32_t)((ku & 1) ^ 1), p.err, 1001);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(PB_KFULL + ks), PA_K_BYTES);
+                    tma_load_3d(base + PA_OFF_K + ks * PA_K_BYTES, &tm_k, 0, it.h * p.T + i * PA_KT, 0, bar(PB_KFULL + ks));
+                }
             }
-            if (!ok) {      // drain the copies still in flight before leaving
-                for (int i = (issued > PA_KST ? issued - PA_KST : 0); i < issued; i++)
-                    mbar_wait(bar(PB_KFULL + i % PA_KST), (uint32_t)((i / PA_KST) & 1), p.err, 1004);
-            }
+            if (!ok)        // drain the copies still in flight before leaving
+                for (int j = (kc > PA_KST ? kc - PA_KST : 0); j < kc; j++)
+                    mbar_wait(bar(PB_KFULL + j % PA_KST), (uint32_t)((j / PA_KST) & 1), p.err, 1004);
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------ TMA producer of the latent ring (its slots come free much
         // later than the key slots: a thread of its own, so that the keys run ahead)
         if (lane == 0) {
             bool ok = true;
-            int issued = 0;
-            for (int i = 0; i < nt && ok; i++) {
-                const int cs = i % PA_CST, cu = i / PA_CST;
-                ok = mbar_wait(bar(PB_CEMPTY + cs), (uint32_t)((cu & 1) ^ 1), p.err, 1002);
-                if (!ok) break;
-                PTRACE(0, i, 1);
-                mbar_expect_tx(bar(PB_CFULL + cs), PA_C_BYTES);
-                tma_load_3d(base + PA_OFF_C + cs * PA_C_BYTES, &tm_c, 0, i * PA_KT, half * 4, bar(PB_CFULL + cs));
-                issued = i + 1;
+            int cc = 0;
+            for (int k = 0; ok; k++) {
+                int w;
+                ok = next_item(k, w);
+                if (!ok || w < 0) break;
+                const AttnItem it = attn_item(w, p, nq);
+                for (int i = 0; i < it.nt && ok; i++, cc++) {
+                    const int cs = cc % PA_CST, cu = cc / PA_CST;
+                    ok = mbar_wait(bar(PB_CEMPTY + cs), (uint32_t)((cu & 1) ^ 1), p.err, 1002);
+                    if (!ok) break;
+                    mbar_expect_tx(bar(PB_CFULL + cs), PA_C_BYTES);
+                    tma_load_3d(base + PA_OFF_C + cs * PA_C_BYTES, &tm_c, 0, i * PA_KT, it.half * 4, bar(PB_CFULL + cs));
+                }
             }
             if (!ok)
-                for (int i = (issued > PA_CST ? issued - PA_CST : 0); i < issued; i++)
-                    mbar_wait(bar(PB_CFULL + i % PA_CST), (uint32_t)((i / PA_CST) & 1), p.err, 1005);
+                for (int j = (cc > PA_CST ? cc - PA_CST : 0); j < cc; j++)
+                    mbar_wait(bar(PB_CFULL + j % PA_CST), (uint32_t)((j / PA_CST) & 1), p.err, 1005);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer of the scores
@@ -157,25 +189,32 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         // waits of a tile in turn was the longest chain of the kernel.
         if (lane == 0) {
             constexpr uint32_t ID_QK = idesc_bf16(128, PA_KT, 0, 0);
-            bool ok = mbar_wait(bar(PB_QFULL), 0, p.err, 1011);     // the softmax threads have written the query tile into tensor memory
-            tc_fence_after();
-            // scores of tile j: S[j % 3] = Q Kx^T, three 64-wide blocks of the 192 dims, four 16-wide steps each
-            for (int j = 0; j < nt && ok; j++) {
-                const int ks = j % PA_KST, ku = j / PA_KST, sb = j % PA_SBUF, su = j / PA_SBUF;
-                ok = mbar_wait(bar(PB_KFULL + ks), (uint32_t)(ku & 1), p.err, 1012);
-                PTRACE(1, j, 0);
-                if (ok) ok = mbar_wait(bar(PB_SEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1013);
+            bool ok = true;
+            int kc = 0;                              // score tiles issued so far
+            for (int k = 0; ok; k++) {
+                int w;
+                ok = next_item(k, w);
+                if (!ok || w < 0) break;
+                const AttnItem it = attn_item(w, p, nq);
+                ok = mbar_wait(bar(PB_QFULL), (uint32_t)(k & 1), p.err, 1011);     // the softmax threads have written the item's query tile into tensor memory
                 if (!ok) break;
-                PTRACE(1, j, 1);
                 tc_fence_after();
-                const uint64_t dK = smem_desc(base + PA_OFF_K + ks * PA_K_BYTES, 16, 1024);
+                // scores of a tile: S[kc % 2] = Q Kx^T, three 64-wide blocks of the 192 dims, four 16-wide steps each
+                for (int i = 0; i < it.nt && ok; i++, kc++) {
+                    const int ks = kc % PA_KST, ku = kc / PA_KST, sb = kc % PA_SBUF, su = kc / PA_SBUF;
+                    ok = mbar_wait(bar(PB_KFULL + ks), (uint32_t)(ku & 1), p.err, 1012);
+                    if (ok) ok = mbar_wait(bar(PB_SEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1013);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t dK = smem_desc(base + PA_OFF_K + ks * PA_K_BYTES, 16, 1024);
 #pragma unroll
-                for (int s = 0; s < 12; s++)
-                    umma_bf16_ts(tmem + PA_COL_S + sb * PA_KT, tmem + PA_COL_Q + s * 8,       // A: 16 bf16 of every row = 8 TMEM columns per step
-                                 dK + (uint64_t)(((s >> 2) * (PA_KT * 128) + (s & 3) * 32) >> 4), ID_QK, s != 0);
-                umma_commit(bar(PB_KEMPTY + ks));
-                umma_commit(bar(PB_SFULL + sb));
-                PTRACE(1, j, 2);
+                    for (int s = 0; s < 12; s++)
+                        umma_bf16_ts(tmem + PA_COL_S + sb * PA_KT, tmem + PA_COL_Q + s * 8,       // A: 16 bf16 of every row = 8 TMEM columns per step
+                                     dK + (uint64_t)(((s >> 2) * (PA_KT * 128) + (s & 3) * 32) >> 4), ID_QK, s != 0);
+                    umma_commit(bar(PB_KEMPTY + ks));
+                    umma_commit(bar(PB_SFULL + sb));
+                }
+                if (ok) umma_commit(bar(PB_QEMPTY));       // the query tile may be replaced once these MMAs are done
             }
         }
     } else if (warp == 3) {
@@ -183,156 +222,169 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (lane == 0) {
             constexpr uint32_t ID_PV = idesc_bf16(128, PA_DV, 0, 1);
             bool ok = true;
-            for (int i = 0; i < nt && ok; i++) {
-                const int cs = i % PA_CST, cu = i / PA_CST, pb = i & 1, pu = i >> 1;
-                ok = mbar_wait(bar(PB_CFULL + cs), (uint32_t)(cu & 1), p.err, 1014);
-                PTRACE(1, i, 3);
-                if (ok) ok = mbar_wait(bar(PB_PFULL + pb), (uint32_t)(pu & 1), p.err, 1015);
-                if (!ok) break;
-                PTRACE(1, i, 4);
-                tc_fence_after();
-                // values: O += P lat, P [128 q][64 keys] K-major, lat half [64 keys][256] with the 256 contiguous (MN-major, four 64-wide blocks)
-                const uint64_t dP = smem_desc(base + PA_OFF_P + pb * PA_P_BYTES, 16, 1024);
-                const uint64_t dC = smem_desc(base + PA_OFF_C + cs * PA_C_BYTES, PA_KT * 128, 1024);
+            int cc = 0;                              // value tiles issued so far
+            for (int k = 0; ok; k++) {
+                int w;
+                ok = next_item(k, w);
+                if (!ok || w < 0) break;
+                const AttnItem it = attn_item(w, p, nq);
+                if (k > 0) {                         // the accumulator of the previous item has been read out
+                    ok = mbar_wait(bar(PB_OFREE), (uint32_t)((k - 1) & 1), p.err, 1016);
+                    if (!ok) break;
+                }
+                for (int i = 0; i < it.nt && ok; i++, cc++) {
+                    const int cs = cc % PA_CST, cu = cc / PA_CST, pb = cc & 1, pu = cc >> 1;
+                    ok = mbar_wait(bar(PB_CFULL + cs), (uint32_t)(cu & 1), p.err, 1014);
+                    if (ok) ok = mbar_wait(bar(PB_PFULL + pb), (uint32_t)(pu & 1), p.err, 1015);
+                    if (!ok) break;
+                    tc_fence_after();
+                    // values: O += P lat, P [128 q][64 keys] K-major, lat half [64 keys][256] with the 256 contiguous (MN-major, four 64-wide blocks)
+                    const uint64_t dP = smem_desc(base + PA_OFF_P + pb * PA_P_BYTES, 16, 1024);
+                    const uint64_t dC = smem_desc(base + PA_OFF_C + cs * PA_C_BYTES, PA_KT * 128, 1024);
 #pragma unroll
-                for (int s = 0; s < 4; s++)
-                    umma_bf16(tmem + PA_COL_O, dP + (uint64_t)((s * 32) >> 4), dC + (uint64_t)((s * 2048) >> 4), ID_PV, (s != 0) ? 1u : (uint32_t)(i != 0));
-                umma_commit(bar(PB_CEMPTY + cs));
-                umma_commit(bar(PB_PEMPTY + pb));
-                PTRACE(1, i, 5);
+                    for (int s = 0; s < 4; s++)
+                        umma_bf16(tmem + PA_COL_O, dP + (uint64_t)((s * 32) >> 4), dC + (uint64_t)((s * 2048) >> 4), ID_PV, (s != 0) ? 1u : (uint32_t)(i != 0));
+                    umma_commit(bar(PB_CEMPTY + cs));
+                    umma_commit(bar(PB_PEMPTY + pb));
+                }
+                if (ok) umma_commit(bar(PB_ODONE));
             }
-            if (ok) umma_commit(bar(PB_ODONE));
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ softmax, (correction,) epilogue
-        // A thread owns query row `row` (= its TMEM lane) and NC of the tile's 64 key columns.
+        // A thread owns query row `row` (= its TMEM lane) and NC of a tile's 64 key columns.
         constexpr int NC = PA_KT / NWG;
         const int q4 = warp & 3, wg = (warp - 4) >> 2;
         const int row = q4 * 32 + lane;
         const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
-        const int64_t tq = p.pos0 + q0 + row;                    // this row's position: keys 0..tq are visible
-        float *s_x = reinterpret_cast<float *>(sm + PA_OFF_X);
-        {
-            // The query tile is the A operand of every score MMA of this block; it is kept in tensor memory (row =
-            // lane, two consecutive bf16 per 32-bit column), so that those MMAs read only the keys from shared
-            // memory. A thread copies its row's share: 96 columns split between the groups.
-            constexpr int QW = (PA_DQK / 2) / NWG;               // 32-bit words per thread
-            const int t = q0 + row;
-            const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((int64_t)t * p.nh + h) * PA_DQK) + wg * (QW / 4);
-#pragma unroll
-            for (int c = 0; c < QW / 16; c++) {
-                uint32_t w[16];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint4 v = (t < p.n) ? src[c * 4 + j] : make_uint4(0, 0, 0, 0);
-                    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
-                }
-                TMEM_ST16(w, 0, tlane + PA_COL_Q + wg * QW + c * 16);
+        bool ok = true;
+        int tc = 0;                                  // tiles done so far (score buffer, P buffer and their phases run across items)
+        for (int k = 0; ok; k++) {
+            int w;
+            ok = next_item(k, w);
+            if (!ok || w < 0) break;
+            const AttnItem it = attn_item(w, p, nq);
+            const int q0 = it.q0, h = it.h, half = it.half, nt = it.nt;
+            const int64_t tq = p.pos0 + q0 + row;                    // this row's position: keys 0..tq are visible
+            if (k > 0) {                                             // the score MMAs of the previous item are done with its query tile
+                ok = mbar_wait(bar(PB_QEMPTY), (uint32_t)((k - 1) & 1), p.err, 1025);
+                if (!ok) break;
+                tc_fence_after();
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            tc_fence_before();
-            mbar_arrive(bar(PB_QFULL));
-        }
-        float m = 0.f, l = 0.f;
-        bool ok = true, met = false;       // met: this thread has been to the first tile's barrier (every thread goes exactly once)
-        for (int i = 0; i < nt; i++) {
-            const int sb = i & 1, su = i >> 1;             // P buffer / latent slot of this tile
-            const int s3 = i % PA_SBUF;                       // its score buffer
-            ok = mbar_wait(bar(PB_SFULL + s3), (uint32_t)((i / PA_SBUF) & 1), p.err, 1021);
-            if (!ok) break;
-            if (tid == 128) PTRACE(2, i, 0);
-            tc_fence_after();
-            uint32_t v[NC];
+            {
+                // The query tile is the A operand of every score MMA of the item; it is kept in tensor memory (row =
+                // lane, two consecutive bf16 per 32-bit column), so that those MMAs read only the keys from shared
+                // memory. A thread copies its row's share: 96 columns split between the groups.
+                constexpr int QW = (PA_DQK / 2) / NWG;               // 32-bit words per thread
+                const int t = q0 + row;
+                const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((int64_t)t * p.nh + h) * PA_DQK) + wg * (QW / 4);
 #pragma unroll
-            for (int c = 0; c < NC / 16; c++) TMEM_LD16(v, c * 16, tlane + PA_COL_S + s3 * PA_KT + wg * NC + c * 16);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            tc_fence_before();
-            mbar_arrive(bar(PB_SEMPTY + s3));
-            if (tid == 128) PTRACE(2, i, 1);
-            float s[NC];
-            float mt = -INFINITY;
-            const int64_t k0 = (int64_t)i * PA_KT + wg * NC;
-            if ((int64_t)i * PA_KT + PA_KT - 1 <= p.pos0 + q0) {   // every key of the tile is visible to every row of the block
+                for (int c = 0; c < QW / 16; c++) {
+                    uint32_t wv[16];
 #pragma unroll
-                for (int j = 0; j < NC; j++) { s[j] = __uint_as_float(v[j]) * p.scale_log2; mt = fmaxf(mt, s[j]); }
-            } else {
-#pragma unroll
-                for (int j = 0; j < NC; j++) {
-                    s[j] = (k0 + j <= tq) ? __uint_as_float(v[j]) * p.scale_log2 : -INFINITY;
-                    mt = fmaxf(mt, s[j]);
-                }
-            }
-            if (NWG == 2) {
-                if (i == 0) {                                    // reference exponent of the row: its largest score of the first tile
-                    s_x[wg * 128 + row] = mt;
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
-                    met = true;
-                    m = fmaxf(s_x[row], s_x[128 + row]);         // key 0 is visible to every row: finite
-                    asm volatile("bar.sync 1, 256;" ::: "memory");   // s_x is reused for the sums at the end
-                } else if (mt > m + PA_RANGE) {
-                    *flag = 1;                                   // out of the range this form covers: the exact form redoes the block
-                }
-            } else {
-                if (i == 0) {
-                    m = mt;
-                } else if (mt > m + PA_LAZY) {
-                    // this row's scores outran its reference exponent: rescale what it has accumulated. The row is this
-                    // thread's TMEM lane; the value MMAs of the previous tile must have finished writing it.
-                    ok = mbar_wait(bar(PB_PEMPTY + ((i - 1) & 1)), (uint32_t)(((i - 1) >> 1) & 1), p.err, 1022);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const float alpha = exp2f(m - mt);
-                    l *= alpha;
-                    m = mt;
-                    for (int c = 0; c < PA_DV / 16; c++) {
-                        uint32_t o[16];
-                        TMEM_LD16(o, 0, tlane + PA_COL_O + c * 16);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                        for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-                        TMEM_ST16(o, 0, tlane + PA_COL_O + c * 16);
+                    for (int j = 0; j < 4; j++) {
+                        const uint4 v = (t < p.n) ? src[c * 4 + j] : make_uint4(0, 0, 0, 0);
+                        wv[4 * j] = v.x; wv[4 * j + 1] = v.y; wv[4 * j + 2] = v.z; wv[4 * j + 3] = v.w;
                     }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    TMEM_ST16(wv, 0, tlane + PA_COL_Q + wg * QW + c * 16);
                 }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(bar(PB_QFULL));
             }
-            uint32_t pk[NC / 2];
-            float lsum = 0.f;
+            float m = 0.f, l = 0.f;
+            for (int i = 0; i < nt && ok; i++, tc++) {
+                const int sb = tc & 1, su = tc >> 1;             // P buffer of this tile
+                const int s3 = tc % PA_SBUF;                      // its score buffer
+                ok = mbar_wait(bar(PB_SFULL + s3), (uint32_t)((tc / PA_SBUF) & 1), p.err, 1021);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t v[NC];
 #pragma unroll
-            for (int j = 0; j < NC; j += 2) {
-                const float p0 = exp2f(s[j] - m), p1 = exp2f(s[j + 1] - m);
-                lsum += p0 + p1;
-                pk[j >> 1] = pack_bf16x2(p0, p1);
+                for (int c = 0; c < NC / 16; c++) TMEM_LD16(v, c * 16, tlane + PA_COL_S + s3 * PA_KT + wg * NC + c * 16);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(bar(PB_SEMPTY + s3));
+                float s[NC];
+                float mt = -INFINITY;
+                const int64_t k0 = (int64_t)i * PA_KT + wg * NC;
+                if ((int64_t)i * PA_KT + PA_KT - 1 <= p.pos0 + q0) {   // every key of the tile is visible to every row of the item
+#pragma unroll
+                    for (int j = 0; j < NC; j++) { s[j] = __uint_as_float(v[j]) * p.scale_log2; mt = fmaxf(mt, s[j]); }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NC; j++) {
+                        s[j] = (k0 + j <= tq) ? __uint_as_float(v[j]) * p.scale_log2 : -INFINITY;
+                        mt = fmaxf(mt, s[j]);
+                    }
+                }
+                if (NWG == 2) {
+                    if (i == 0) {                                    // reference exponent of the row: its largest score of the first tile
+                        s_m[wg * 128 + row] = mt;
+                        mbar_arrive(bar(PB_XM));
+                        ok = mbar_wait(bar(PB_XM), (uint32_t)(k & 1), p.err, 1026);
+                        if (!ok) break;
+                        m = fmaxf(s_m[row], s_m[128 + row]);         // key 0 is visible to every row: finite
+                    } else if (mt > m + PA_RANGE) {
+                        p.flags[w] = 1;                              // out of the range this form covers: the exact form redoes the item
+                    }
+                } else {
+                    if (i == 0) {
+                        m = mt;
+                    } else if (mt > m + PA_LAZY) {
+                        // this row's scores outran its reference exponent: rescale what it has accumulated. The row is this
+                        // thread's TMEM lane; the value MMAs of the previous tile must have finished writing it.
+                        ok = mbar_wait(bar(PB_PEMPTY + ((tc - 1) & 1)), (uint32_t)(((tc - 1) >> 1) & 1), p.err, 1022);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const float alpha = exp2f(m - mt);
+                        l *= alpha;
+                        m = mt;
+                        for (int c = 0; c < PA_DV / 16; c++) {
+                            uint32_t o[16];
+                            TMEM_LD16(o, 0, tlane + PA_COL_O + c * 16);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int j = 0; j < 16; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                            TMEM_ST16(o, 0, tlane + PA_COL_O + c * 16);
+                        }
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    }
+                }
+                uint32_t pk[NC / 2];
+                float lsum = 0.f;
+#pragma unroll
+                for (int j = 0; j < NC; j += 2) {
+                    const float p0 = exp2f(s[j] - m), p1 = exp2f(s[j + 1] - m);
+                    lsum += p0 + p1;
+                    pk[j >> 1] = pack_bf16x2(p0, p1);
+                }
+                l += lsum;
+                // the P buffer of this parity was read by the value MMAs two tiles ago
+                ok = mbar_wait(bar(PB_PEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1023);
+                if (!ok) break;
+                uint8_t *prow = sm + PA_OFF_P + sb * PA_P_BYTES + row * 128;
+#pragma unroll
+                for (int c = 0; c < NC / 8; c++)
+                    *reinterpret_cast<uint4 *>(prow + (((wg * (NC / 8) + c) ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(bar(PB_PFULL + sb));
             }
-            l += lsum;
-            // the P buffer of this parity was read by the value MMAs of tile i - 2
-            if (tid == 128) PTRACE(2, i, 2);
-            ok = mbar_wait(bar(PB_PEMPTY + sb), (uint32_t)((su & 1) ^ 1), p.err, 1023);
             if (!ok) break;
-            if (tid == 128) PTRACE(2, i, 3);
-            uint8_t *prow = sm + PA_OFF_P + sb * PA_P_BYTES + row * 128;
-#pragma unroll
-            for (int c = 0; c < NC / 8; c++)
-                *reinterpret_cast<uint4 *>(prow + (((wg * (NC / 8) + c) ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_before();
-            mbar_arrive(bar(PB_PFULL + sb));
-            if (tid == 128) PTRACE(2, i, 4);
-        }
-        // ---- epilogue: O / l -> bf16 -> out[t][h][half * 256 ..], through the (now idle) P buffers for full-line stores
-        if (ok) ok = mbar_wait(bar(PB_ODONE), 0, p.err, 1024);
-        if (NWG == 2) {                                          // the row's sum is the two groups' sums (every thread takes part in the barriers)
-            if (!met) {                                          // a wait gave up before the first tile: keep the barrier counts in step
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-            }
-            s_x[wg * 128 + row] = l;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            l = s_x[row] + s_x[128 + row];
-        }
-        if (ok) {
+            // ---- epilogue of the item: O / l -> bf16 -> out[t][h][half * 256 ..], full lines through a staging tile
+            ok = mbar_wait(bar(PB_ODONE), (uint32_t)(k & 1), p.err, 1024);
+            if (!ok) break;
             tc_fence_after();
+            if (NWG == 2) {                                          // the row's sum is the two groups' sums
+                s_l[wg * 128 + row] = l;
+                mbar_arrive(bar(PB_XL));
+                ok = mbar_wait(bar(PB_XL), (uint32_t)(k & 1), p.err, 1027);
+                if (!ok) break;
+                l = s_l[row] + s_l[128 + row];
+            }
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint8_t *stg = sm + PA_OFF_P + (warp - 4) * 4096;        // 4 KB per warp: [32 rows][128 B]
+            uint8_t *stg = sm + PA_OFF_P + (warp - 4) * 4096;         // 4 KB per warp: [32 rows][128 B], in the P buffers (idle: the item's value MMAs are done, and the next item's P comes from these threads)
             const int t0w = q0 + q4 * 32;
             constexpr int NCH = PA_DV / 64 / NWG;                     // 64-column chunks per thread
 #pragma unroll 1
@@ -346,23 +398,25 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                    uint4 w;
-                    w.x = pack_bf16x2(__uint_as_float(o[8 * j]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
-                    w.y = pack_bf16x2(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
-                    w.z = pack_bf16x2(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
-                    w.w = pack_bf16x2(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
-                    *reinterpret_cast<uint4 *>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = w;
+                    uint4 wv;
+                    wv.x = pack_bf16x2(__uint_as_float(o[8 * j]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
+                    wv.y = pack_bf16x2(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
+                    wv.z = pack_bf16x2(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
+                    wv.w = pack_bf16x2(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = wv;
                 }
                 __syncwarp();
 #pragma unroll
                 for (int r8 = 0; r8 < 8; r8++) {
                     const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
-                    const uint4 w = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
+                    const uint4 wv = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
                     if (t0w + rr < p.n)
-                        *reinterpret_cast<uint4 *>(p.out + ((int64_t)(t0w + rr) * p.nh + h) * PA_L + half * PA_DV + col + jj * 8) = w;
+                        *reinterpret_cast<uint4 *>(p.out + ((int64_t)(t0w + rr) * p.nh + h) * PA_L + half * PA_DV + col + jj * 8) = wv;
                 }
                 __syncwarp();
             }
+            tc_fence_before();
+            mbar_arrive(bar(PB_OFREE));                              // the value MMAs of the next item may overwrite the accumulator
         }
     }
     tc_fence_before();
@@ -541,8 +595,8 @@ bool cwk_mla_prefill_attn_tc_ok(const void *Q, const void *cache, const void *Wu
 }
 
 // Q bf16 [n][nh][192] with the rope part already rotated; cache bf16 [pos0 + n][576] (latent | rope key);
-// Wuk bf16 [nh][128][512]; kx = workspace bf16 [nh][pos0 + n][192]; flags = workspace int32, one per block of the
-// attention grid (ceil(n / 128) x nh x 2); out bf16 [n][nh][512].
+// Wuk bf16 [nh][128][512]; kx = workspace bf16 [nh][pos0 + n][192]; flags = workspace int32, one per item of the
+// attention (ceil(n / 128) x nh x 2) plus two counters; out bf16 [n][nh][512].
 // Returns CWK_ERR_UNSUPPORTED (no error text) when the tensor path cannot run.
 int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int *flags, int64_t pos0, int n, int nh,
                             float scale, void *out) {
@@ -581,14 +635,16 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
         ap.q = (const uint16_t *)Q; ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.T = T; ap.pos0 = pos0; ap.scale_log2 = scale * 1.4426950408889634f; ap.flags = flags;
         ap.err = ctx->dev_err;
         ap.trace = (long long *)ctx->tc_trace;
-        const dim3 grid((n + PA_QT - 1) / PA_QT, nh, 2);
-        CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)grid.x * grid.y * grid.z * sizeof(int), ctx->stream));
+        const int total = ((n + PA_QT - 1) / PA_QT) * nh * 2;
+        ap.counter = flags + total;
+        CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)(total + 2) * sizeof(int), ctx->stream));
+        const int grid = std::min(total, ctx->sm_count);
         {
             CwkKernelTimer timer(ctx);
             prefill_attn_kernel<2><<<grid, 384, PA_SMEM, ctx->stream>>>(tm_k, tm_c, ap);
             CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<2>");
         }
-        // the repair pass: blocks whose flag is clear return at once
+        // the repair pass: items whose flag is clear are skipped
         prefill_attn_kernel<1><<<grid, 256, PA_SMEM, ctx->stream>>>(tm_k, tm_c, ap);
         CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<1>");
     }
