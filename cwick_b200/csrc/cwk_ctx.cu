@@ -174,7 +174,7 @@ int cwk_ctx_debug_trace(cwk_ctx *ctx, void *device_buffer) {
 }
 
 int cwk_ctx_force_mla_path(cwk_ctx *ctx, int path) {
-    if (!ctx || path < -1 || path > 2) return CWK_ERR_ARGUMENT;
+    if (!ctx || path < -1 || path > 3) return CWK_ERR_ARGUMENT;     // 3: exact form of the prefill attention (cwk_mla_prefill only)
     ctx->force_mla_path = path;
     return CWK_OK;
 }

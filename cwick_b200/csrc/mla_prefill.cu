@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(256) rope_q_inplace_kernel(uint16_t *q, int n,
 int cwk_absorb_tc_launch(cwk_ctx *ctx, const void *Q, int n, int nh, const void *Wuk, void *Qfull);
 bool cwk_mla_prefill_attn_tc_ok(const void *Q, const void *cache, const void *Wuk, const void *kx, const void *out);
 int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int *flags, int64_t pos0, int n, int nh,
-                            float scale, void *out);
+                            float scale, void *out, int exact_only);
 
 // Absorb: Qfull[t][h][0:L] = q[t][h][0:nope] . W_uk[h] ([nope][L] row-major bf16), and
 // Qfull[t][h][L:L+rope] = RoPE(q[t][h][nope:nope+rope], pos0+t). The identity is
@@ -216,7 +216,10 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     // The attention takes one of two routes. Queries as MMA rows against per-head expanded keys (mla_prefill_attn.cu)
     // needs Kx bf16 [pos0+n][nh][qd] and no Qfull; the absorbed route (the decode kernel once per query row) needs
     // Qfull bf16 [n][nh][row]. The same workspace region serves whichever runs.
-    const bool expanded_keys = ctx->force_mla_path != 0 && ctx->force_mla_path != 1 && ctx->force_mla_path != 2 && pos0 + n <= 32768;
+    // The expansion covers every cached row, so it pays when the chunk is a fair share of the context (always for a
+    // prompt from position 0); a short chunk after a long history takes the absorbed route.
+    const bool expanded_keys = ctx->force_mla_path != 0 && ctx->force_mla_path != 1 && ctx->force_mla_path != 2 && pos0 + n <= 32768 &&
+                               (int64_t)n * 4 >= pos0 + n;
     const size_t b_kx = up((size_t)(pos0 + n) * nh * qd * 2);
     const size_t b_q = up((size_t)n * nh * qd * 2), b_qf = expanded_keys ? std::max(b_kx, up((size_t)n * nh * row * 2)) : up((size_t)n * nh * row * 2),
                  b_len = up((size_t)n * 4) + up(((size_t)((n + 127) / 128) * nh * 2 + 2) * 4);
@@ -256,7 +259,7 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     if (expanded_keys && cwk_mla_prefill_attn_tc_ok(Q, cache, Wuk, Qf, out)) {
         rope_q_inplace_kernel<<<(n * (rope / 2) + 255) / 256, 256, 0, ctx->stream>>>(Q, n, nh, nope, rope, pos0, rope_base);
         CWK_LAUNCH_CHECK(ctx, "rope_q_inplace_kernel");
-        return cwk_mla_prefill_attn_tc(ctx, Q, cache, Wuk, Qf, (int *)((uint8_t *)len + up((size_t)n * 4)), pos0, n, nh, scale, out);
+        return cwk_mla_prefill_attn_tc(ctx, Q, cache, Wuk, Qf, (int *)((uint8_t *)len + up((size_t)n * 4)), pos0, n, nh, scale, out, ctx->force_mla_path == 3);
     }
     // absorb on the tensor path (tcgen05); the mma.sync kernel covers a context without the
     // tensor-map encoder or a caller that forced the general kernels

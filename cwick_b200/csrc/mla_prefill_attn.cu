@@ -296,7 +296,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             for (int i = 0; i < nt && ok; i++, tc++) {
                 const int sb = tc & 1, su = tc >> 1;             // P buffer of this tile
                 const int s3 = tc % PA_SBUF;                      // its score buffer
-                ok = mbar_wait(bar(PB_SFULL + s3), (uint32_t)((tc / PA_SBUF) & 1), p.err, 1021);
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(PB_SFULL + s3), (uint32_t)((tc / PA_SBUF) & 1), p.err, 1021));   // warp-uniform: the TMEM loads below are warp-wide
                 if (!ok) break;
                 tc_fence_after();
                 uint32_t v[NC];
@@ -329,17 +329,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                         p.flags[w] = 1;                              // out of the range this form covers: the exact form redoes the item
                     }
                 } else {
-                    if (i == 0) {
-                        m = mt;
-                    } else if (mt > m + PA_LAZY) {
-                        // this row's scores outran its reference exponent: rescale what it has accumulated. The row is this
+                    // tcgen05.ld / st are warp-wide instructions: the warp decides together, and a lane that has no
+                    // need of it rescales by 1
+                    const bool mine = (i != 0) && (mt > m + PA_LAZY);
+                    if (i == 0) m = mt;
+                    if (__any_sync(0xffffffffu, mine)) {
+                        // some row's scores outran its reference exponent: rescale what it has accumulated. A row is its
                         // thread's TMEM lane; the value MMAs of the previous tile must have finished writing it.
                         ok = mbar_wait(bar(PB_PEMPTY + ((tc - 1) & 1)), (uint32_t)(((tc - 1) >> 1) & 1), p.err, 1022);
+                        ok = __all_sync(0xffffffffu, ok);
                         if (!ok) break;
                         tc_fence_after();
-                        const float alpha = exp2f(m - mt);
+                        const float alpha = mine ? exp2f(m - mt) : 1.f;
                         l *= alpha;
-                        m = mt;
+                        if (mine) m = mt;
                         for (int c = 0; c < PA_DV / 16; c++) {
                             uint32_t o[16];
                             TMEM_LD16(o, 0, tlane + PA_COL_O + c * 16);
@@ -596,10 +599,11 @@ bool cwk_mla_prefill_attn_tc_ok(const void *Q, const void *cache, const void *Wu
 
 // Q bf16 [n][nh][192] with the rope part already rotated; cache bf16 [pos0 + n][576] (latent | rope key);
 // Wuk bf16 [nh][128][512]; kx = workspace bf16 [nh][pos0 + n][192]; flags = workspace int32, one per item of the
-// attention (ceil(n / 128) x nh x 2) plus two counters; out bf16 [n][nh][512].
+// attention (ceil(n / 128) x nh x 2) plus two counters; out bf16 [n][nh][512]. exact_only: skip the fast form and run
+// the exact form on every item (for tests).
 // Returns CWK_ERR_UNSUPPORTED (no error text) when the tensor path cannot run.
 int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int *flags, int64_t pos0, int n, int nh,
-                            float scale, void *out) {
+                            float scale, void *out, int exact_only) {
     if (!cwk_encode_tiled_fn()) return CWK_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(Wuk) | reinterpret_cast<uintptr_t>(kx) |
          reinterpret_cast<uintptr_t>(out)) & 15)
@@ -638,8 +642,9 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
         const int total = ((n + PA_QT - 1) / PA_QT) * nh * 2;
         ap.counter = flags + total;
         CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)(total + 2) * sizeof(int), ctx->stream));
+        if (exact_only) CWK_CUDA(ctx, cudaMemsetAsync(flags, 1, (size_t)total * sizeof(int), ctx->stream));     // every item flagged (any non-zero word)
         const int grid = std::min(total, ctx->sm_count);
-        {
+        if (!exact_only) {
             CwkKernelTimer timer(ctx);
             prefill_attn_kernel<2><<<grid, 384, PA_SMEM, ctx->stream>>>(tm_k, tm_c, ap);
             CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<2>");

@@ -77,7 +77,11 @@ CWK_API int cwk_ctx_debug_trace(cwk_ctx *ctx, void *device_buffer);
 /* Which implementation the next cwk_mla_decode call would take for these
  * dimensions: 2 = tcgen05/TMA kernel, 1 = mma.sync kernel, 0 = generic. */
 CWK_API int cwk_mla_decode_path(const cwk_ctx *ctx, int nh, int L, int R);
-/* Force a path (same codes; -1 = automatic). For A/B measurement and tests. */
+/* Force a path (same codes; -1 = automatic). For A/B measurement and tests.
+ * In cwk_mla_prefill: 0..2 also select the absorbed attention route (the decode
+ * kernel once per query row) instead of the expanded-key route, and 3 keeps the
+ * expanded-key route but runs the exact form of its attention kernel on every
+ * block. */
 CWK_API int cwk_ctx_force_mla_path(cwk_ctx *ctx, int path);
 
 /* ---- MLA absorbed decode ---------------------------------------------------

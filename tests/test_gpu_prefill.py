@@ -95,3 +95,65 @@ def test_config3_full_size_sampled_rows(attn):
     g = bf16_to_np(got)
     assert np.isfinite(g).all()
     close(g[rows], want)
+
+
+def _forced(attn, path, fn):
+    assert attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, path) == 0
+    try:
+        return fn()
+    finally:
+        assert attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1) == 0
+
+
+def test_exact_attention_form(attn):
+    """The exact form of the prefill attention (one thread per query row, running maximum with a lazy
+    rescale of the row's accumulator), forced onto every block: against the oracle on ordinary inputs,
+    and against the fast form on sharper scores (q_b weights x4: the running maximum then moves by more
+    than the rescale threshold many times per row). The two forms take the same scores from the same
+    MMAs, so they must agree even where a sharp softmax amplifies rounding differences against the CPU."""
+    n, pos0, nh, H, q_lora = 300, 20, 64, 512, 256
+    m = make_model(41, H, q_lora, nh)
+    X = synth.normal_bf16(41, 9, (n, H))
+    cache0 = np.zeros((pos0 + n, LAT + ROPE), np.uint16)
+    cache0[:pos0] = synth.normal_bf16(41, 10, (pos0, LAT + ROPE))
+    exact, _ = _forced(attn, 3, lambda: run_gpu(attn, m, X, cache0, pos0, nh))
+    want, _ = run_oracle(m, X, cache0, pos0, nh, np.arange(n))
+    close(bf16_to_np(exact), want)
+    m["Sqb"] = (m["Sqb"] * np.float32(4.0)).astype(np.float32)
+    fast, _ = run_gpu(attn, m, X, cache0, pos0, nh)
+    exact, _ = _forced(attn, 3, lambda: run_gpu(attn, m, X, cache0, pos0, nh))
+    close(bf16_to_np(fast), bf16_to_np(exact))
+
+
+def test_scores_out_of_the_fast_forms_range_are_repaired(attn):
+    """Scores spread over hundreds of log2 units (q_b weights x400) overflow the range the fast form
+    covers; the blocks that see it raise their flags and the exact form recomputes them (the others
+    keep the fast form's result): finite everywhere, and equal to the exact form run on every block
+    within the tolerance (both forms take the same scores from the same MMAs)."""
+    n, pos0, nh, H, q_lora = 300, 0, 64, 512, 256
+    m = make_model(43, H, q_lora, nh)
+    m["Sqb"] = (m["Sqb"] * np.float32(400.0)).astype(np.float32)
+    X = synth.normal_bf16(43, 9, (n, H))
+    cache0 = np.zeros((n, LAT + ROPE), np.uint16)
+    got, _ = run_gpu(attn, m, X, cache0, pos0, nh)
+    exact, _ = _forced(attn, 3, lambda: run_gpu(attn, m, X, cache0, pos0, nh))
+    g, e = bf16_to_np(got), bf16_to_np(exact)
+    assert np.isfinite(g).all()
+    close(g, e)
+
+
+def test_absorbed_route_agrees_with_the_expanded_key_route(attn):
+    """The two attention routes of the prefill (queries as MMA rows against expanded keys; the decode
+    kernel once per query row against the latent) give the same output within the tolerance, on a chunk
+    that continues an existing cache and spans several 64-key tiles."""
+    n, pos0, nh, H, q_lora = 333, 200, 64, 512, 256
+    m = make_model(52, H, q_lora, nh)
+    X = synth.normal_bf16(52, 9, (n, H))
+    cache0 = np.zeros((pos0 + n, LAT + ROPE), np.uint16)
+    cache0[:pos0] = synth.normal_bf16(52, 10, (pos0, LAT + ROPE))
+    a, _ = run_gpu(attn, m, X, cache0, pos0, nh)
+    b, _ = _forced(attn, 2, lambda: run_gpu(attn, m, X, cache0, pos0, nh))
+    want, _ = run_oracle(m, X, cache0, pos0, nh, np.array([0, 1, 63, 64, 200, 332], np.int32))
+    close(bf16_to_np(a)[[0, 1, 63, 64, 200, 332]], want)
+    close(bf16_to_np(b)[[0, 1, 63, 64, 200, 332]], want)
+    close(bf16_to_np(a), bf16_to_np(b))
