@@ -68,7 +68,6 @@ struct AttnParams {
     int *flags;         // one word per item: fast form sets it, exact form runs only where it is set
     int *counter;       // [2] item counters (fast form, exact form), zero at launch
     int *err;
-    long long *trace;   // optional clock64 stamps of block (0, 0, 0): [role][tile][event]; NULL = off
 };
 
 struct AttnItem {
@@ -638,7 +637,6 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
         AttnParams ap;
         ap.q = (const uint16_t *)Q; ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.T = T; ap.pos0 = pos0; ap.scale_log2 = scale * 1.4426950408889634f; ap.flags = flags;
         ap.err = ctx->dev_err;
-        ap.trace = (long long *)ctx->tc_trace;
         const int total = ((n + PA_QT - 1) / PA_QT) * nh * 2;
         ap.counter = flags + total;
         CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)(total + 2) * sizeof(int), ctx->stream));
