@@ -222,7 +222,7 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
                                (int64_t)n * 4 >= pos0 + n;
     const size_t b_kx = up((size_t)(pos0 + n) * nh * qd * 2);
     const size_t b_q = up((size_t)n * nh * qd * 2), b_qf = expanded_keys ? std::max(b_kx, up((size_t)n * nh * row * 2)) : up((size_t)n * nh * row * 2),
-                 b_len = up((size_t)n * 4) + up(((size_t)((n + 127) / 128) * nh * 2 + 2) * 4);
+                 b_len = up((size_t)n * 4) + up(((size_t)((n + 127) / 128) * nh * 2 + 3) * 4);
     int s = cwk_reserve_work(ctx, b_qa + b_qan + b_kva + b_q + b_qf + b_len);
     if (s != CWK_OK) return s;
     uint8_t *w = (uint8_t *)ctx->work;

@@ -66,7 +66,7 @@ struct AttnParams {
     int64_t pos0;
     float scale_log2;
     int *flags;         // one word per item: fast form sets it, exact form runs only where it is set
-    int *counter;       // [2] item counters (fast form, exact form), zero at launch
+    int *counter;       // [3]: item counters of the fast and the exact form, number of flags raised; zero at launch
     int *err;
 };
 
@@ -104,6 +104,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     float *s_m = reinterpret_cast<float *>(sm + PA_OFF_X), *s_l = s_m + 256;              // [2][128] each
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (NWG == 1 && p.counter[2] == 0) return;                   // the repair pass: the fast form raised no flag
     const int nq = (p.n + PA_QT - 1) / PA_QT;
     const int total = nq * p.nh * 2;
 
@@ -326,6 +327,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                         m = fmaxf(s_m[row], s_m[128 + row]);         // key 0 is visible to every row: finite
                     } else if (mt > m + PA_RANGE) {
                         p.flags[w] = 1;                              // out of the range this form covers: the exact form redoes the item
+                        atomicAdd(p.counter + 2, 1);
                     }
                 } else {
                     // tcgen05.ld / st are warp-wide instructions: the warp decides together, and a lane that has no
@@ -598,7 +600,7 @@ bool cwk_mla_prefill_attn_tc_ok(const void *Q, const void *cache, const void *Wu
 
 // Q bf16 [n][nh][192] with the rope part already rotated; cache bf16 [pos0 + n][576] (latent | rope key);
 // Wuk bf16 [nh][128][512]; kx = workspace bf16 [nh][pos0 + n][192]; flags = workspace int32, one per item of the
-// attention (ceil(n / 128) x nh x 2) plus two counters; out bf16 [n][nh][512]. exact_only: skip the fast form and run
+// attention (ceil(n / 128) x nh x 2) plus three counters; out bf16 [n][nh][512]. exact_only: skip the fast form and run
 // the exact form on every item (for tests).
 // Returns CWK_ERR_UNSUPPORTED (no error text) when the tensor path cannot run.
 int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, const void *Wuk, void *kx, int *flags, int64_t pos0, int n, int nh,
@@ -639,8 +641,11 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
         ap.err = ctx->dev_err;
         const int total = ((n + PA_QT - 1) / PA_QT) * nh * 2;
         ap.counter = flags + total;
-        CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)(total + 2) * sizeof(int), ctx->stream));
-        if (exact_only) CWK_CUDA(ctx, cudaMemsetAsync(flags, 1, (size_t)total * sizeof(int), ctx->stream));     // every item flagged (any non-zero word)
+        CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)(total + 3) * sizeof(int), ctx->stream));
+        if (exact_only) {       // every item flagged (any non-zero word), the flag count non-zero, the two item counters back to zero
+            CWK_CUDA(ctx, cudaMemsetAsync(flags, 1, (size_t)(total + 3) * sizeof(int), ctx->stream));
+            CWK_CUDA(ctx, cudaMemsetAsync(flags + total, 0, 2 * sizeof(int), ctx->stream));
+        }
         const int grid = std::min(total, ctx->sm_count);
         if (!exact_only) {
             CwkKernelTimer timer(ctx);
