@@ -103,16 +103,18 @@ __global__ void __launch_bounds__(256) rope_tail_kernel(const uint16_t *q, uint1
     }
 }
 
-// RoPE of the rope part of q, in place: q[t][h][nope : nope+rope] at position pos0 + t. One thread per (t, pair).
+// RoPE of the rope part of q, in place: q[t][h][nope : nope+rope] at position pos0 + t. One thread per (t, pair) and
+// group of heads (blockIdx.y): the angle is formed once per thread and applied to the group's heads.
 __global__ void __launch_bounds__(256) rope_q_inplace_kernel(uint16_t *q, int n, int nh, int nope, int n_rope, int64_t pos0, float base) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n * (n_rope / 2)) return;
     const int t = i / (n_rope / 2), j = i % (n_rope / 2);
+    const int hpg = (nh + (int)gridDim.y - 1) / (int)gridDim.y, h0 = (int)blockIdx.y * hpg, h1 = min(nh, h0 + hpg);
     float cs, sn;
     rope_cos_sin(pos0 + t, j, n_rope, base, cs, sn);
     uint16_t *src = q + (int64_t)t * nh * (nope + n_rope) + nope + 2 * j;
 #pragma unroll 8
-    for (int h = 0; h < nh; h++) {
+    for (int h = h0; h < h1; h++) {
         uint32_t *w = reinterpret_cast<uint32_t *>(src + (int64_t)h * (nope + n_rope));
         const uint32_t v = *w;
         const float a = __uint_as_float(v << 16), b = __uint_as_float(v & 0xffff0000u);
@@ -257,7 +259,7 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
                                                       pos0, (uint16_t *)cache + pos0 * row, row, len, 1);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(kv_a)");
     if (expanded_keys && cwk_mla_prefill_attn_tc_ok(Q, cache, Wuk, Qf, out)) {
-        rope_q_inplace_kernel<<<(n * (rope / 2) + 255) / 256, 256, 0, ctx->stream>>>(Q, n, nh, nope, rope, pos0, rope_base);
+        rope_q_inplace_kernel<<<dim3((n * (rope / 2) + 255) / 256, nh >= 8 ? 8 : 1), 256, 0, ctx->stream>>>(Q, n, nh, nope, rope, pos0, rope_base);
         CWK_LAUNCH_CHECK(ctx, "rope_q_inplace_kernel");
         return cwk_mla_prefill_attn_tc(ctx, Q, cache, Wuk, Qf, (int *)((uint8_t *)len + up((size_t)n * 4)), pos0, n, nh, scale, out, ctx->force_mla_path == 3);
     }
