@@ -246,11 +246,19 @@ int cwk_mla_decode_host(cwk_ctx *ctx, const void *q_host, const void *cache_dev,
         if (sb) memcpy(pin + o_s, sel_host, sb);
         CWK_CUDA(ctx, cudaMemcpyAsync(dev + o_l, pin + o_l, o_o - o_l, cudaMemcpyHostToDevice, ctx->stream));
     }
+    // A page-locked output buffer that the device can address (mapped pinned memory) is written by the last kernel
+    // itself: one copy operation less between the kernels and the caller.
+    void *out_alias = nullptr;
+    if (o_pinned && cudaHostGetDevicePointer(&out_alias, out_host, 0) != cudaSuccess) {
+        (void)cudaGetLastError();
+        out_alias = nullptr;
+    }
     s = mla_launch(ctx, dev + o_q, cache_dev, seq_stride, ld, lens_imm ? nullptr : (const int32_t *)(dev + o_l), max_len,
-                   sb ? (const int32_t *)(dev + o_s) : nullptr, sel_ld, B, nh, L, R, scale, dev + o_o,
+                   sb ? (const int32_t *)(dev + o_s) : nullptr, sel_ld, B, nh, L, R, scale, out_alias ? out_alias : (void *)(dev + o_o),
                    nullptr, n_splits);
     if (s != CWK_OK) return s;
-    CWK_CUDA(ctx, cudaMemcpyAsync(o_pinned ? out_host : (void *)(pin + o_o), dev + o_o, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!out_alias)
+        CWK_CUDA(ctx, cudaMemcpyAsync(o_pinned ? out_host : (void *)(pin + o_o), dev + o_o, ob, cudaMemcpyDeviceToHost, ctx->stream));
     CWK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     s = cwk_check_device_error(ctx);
     if (s != CWK_OK) return s;

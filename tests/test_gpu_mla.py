@@ -142,6 +142,20 @@ def test_host_entry_point_matches_device_entry_point(attn):
     assert torch.equal(outh, dev.cpu())
 
 
+@pytest.mark.parametrize("B,T", [(1, 8192), (3, 500)])
+def test_host_entry_point_with_page_locked_buffers(attn, B, T):
+    """Page-locked caller buffers: q is copied from in place and the output is written by the last
+    kernel straight into the caller's (device-mapped) buffer. One sequence goes through the split +
+    merge kernels, several short ones through the direct-output kernel."""
+    q, cache = make_case(13, B, 64, T)
+    lens = np.array([T - 3 * b for b in range(B)], np.int32)
+    dev = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+    qh = torch.from_numpy(q.view(np.int16)).view(torch.bfloat16).pin_memory()
+    outh = torch.zeros(B, 64, L, dtype=torch.bfloat16).pin_memory()
+    attn.mla_decode_host(qh, to_bf16_cuda(cache), torch.from_numpy(lens), L, R, SCALE, outh)
+    assert torch.equal(outh, dev.cpu())
+
+
 def test_kv_range_partials_and_merge(attn):
     """Split one sequence into G ranges, as the multi-GPU KV-range split does, and merge."""
     T, G = 3000, 4
