@@ -17,7 +17,8 @@
 //      a < tau - 2*delta certainly are not (-inf), and the band in between is listed. (delta is
 //      taken as 2^-9 of the row's largest score, far above the contraction's and the query
 //      split's worst case.)
-//   3. band_rescore_kernel: the listed keys are re-scored in the reference's exact order on CUDA cores.
+//   3. the same kernel then re-scores the listed keys in the reference's exact order on CUDA cores (the
+//      cluster's blocks share the list).
 //   4. the selection kernel (csrc/dsa.cu) takes the exact threshold from the re-scored keys and
 //      writes the reference's list in the reference's order.
 //
@@ -291,6 +292,10 @@ __device__ __forceinline__ float e4m3_to_f32_i(uint32_t b) {
     return (b & 0x80u) ? -mag : mag;
 }
 
+constexpr int BC_KEYS = 64;                                   // band keys re-scored per pass and block
+constexpr int BC_QLD = IT_HD + 4;                             // padded q rows in shared memory
+constexpr int BC_SMEM = (IT_IH * BC_QLD + IT_IH + BC_KEYS * IT_HD + BC_KEYS * (IT_IH + 1)) * 4;
+
 // One cluster per sequence: the row's largest approximate score, the exact want-th largest
 // approximate score tau, then the classification of every key: certainly selected (refined =
 // +inf), certainly not (refined = -inf), or in the band |a - tau| <= eps, whose indices are appended
@@ -298,7 +303,9 @@ __device__ __forceinline__ float e4m3_to_f32_i(uint32_t b) {
 // (both zeroed by the caller).
 __global__ void __cluster_dims__(TK_CL, 1, 1) __launch_bounds__(TK_THREADS, 1)
 band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int want, float *refined, int32_t *band_list,
-                     int32_t *band_count) {
+                     int32_t *band_count, const uint8_t *keys, const float *kscale, const float *q, const float *wt) {
+    extern __shared__ __align__(16) float bc_sm[];
+    float *sq = bc_sm, *sw = sq + IT_IH * BC_QLD, *skey = sw + IT_IH, *sprod = skey + BC_KEYS * IT_HD;
     cg::cluster_group cl = cg::this_cluster();
     const unsigned rank = cl.block_rank();
     const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
@@ -314,6 +321,13 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
     __shared__ float red[32];
     uint32_t kc[TK_PT];
     if (sl.cached) tk_load(s, sl.begin, sl.end, kc);
+    // the query and the head weights of this sequence, for the exact re-scoring at the end (padded rows: the heads of a
+    // key's 16 threads then read different banks)
+    for (int i = tid; i < IT_IH * (IT_HD / 4); i += TK_THREADS) {
+        const int h = i / (IT_HD / 4), c = i % (IT_HD / 4);
+        *reinterpret_cast<float4 *>(sq + h * BC_QLD + c * 4) = __ldg(reinterpret_cast<const float4 *>(q + ((int64_t)b * IT_IH + h) * IT_HD) + c);
+    }
+    if (tid < IT_IH) sw[tid] = wt[(int64_t)b * IT_IH + tid];
     // largest score of this block's slice (scores are sums of non-negative terms)
     float m = 0.f;
     for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
@@ -386,68 +400,58 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
         for (int j = 0; j < TK_PT; j++)
             if (inb & (1u << j)) list[at++] = i0 + j;
     }
-    cl.sync();                              // keep this block's shared memory alive until every neighbour has read fmax
-}
-
-// Exact scores (the reference's order: src/attention.c:573-582 with dot_f32's grouping, :249-258)
-// of the keys in the band. Eight lanes share a key: each computes the dots of eight heads in the
-// reference's order, and one lane then adds the 64 weighted terms in head order.
-constexpr int RS_QLD = IT_HD + 4;                            // padded q rows: the eight heads of a key group hit different banks
-constexpr int RS_SMEM = (IT_IH * RS_QLD + IT_IH + 32 * IT_IH) * 4;
-__global__ void __launch_bounds__(256) band_rescore_kernel(const uint8_t *keys, const float *kscale, int64_t key_stride,
-                                                           const float *q, const float *wt, const int32_t *band_list,
-                                                           const int32_t *band_count, float *refined) {
-    extern __shared__ __align__(16) float rs_sm[];
-    float *sq = rs_sm, *sw = rs_sm + IT_IH * RS_QLD, *sp = sw + IT_IH;
-    const int b = blockIdx.y, tid = threadIdx.x;
-    const int cnt = band_count[2 * b];
-    if ((int)blockIdx.x * 32 >= cnt) return;
-    for (int i = tid; i < IT_IH * (IT_HD / 4); i += 256) {
-        const int h = i / (IT_HD / 4), c = i % (IT_HD / 4);
-        *reinterpret_cast<float4 *>(sq + h * RS_QLD + c * 4) = __ldg(reinterpret_cast<const float4 *>(q + ((int64_t)b * IT_IH + h) * IT_HD) + c);
-    }
-    if (tid < IT_IH) sw[tid] = wt[(int64_t)b * IT_IH + tid];
-    __syncthreads();
-    const int g = tid >> 3, l8 = tid & 7;
-    float *pg = sp + g * IT_IH;
-    for (int k = blockIdx.x * 32 + g; k < cnt; k += gridDim.x * 32) {
-        const int c = band_list[(int64_t)b * key_stride + k];
-        const uint8_t *kr = keys + ((int64_t)b * key_stride + c) * IT_HD;
-        const float s = kscale[(int64_t)b * key_stride + c];
-        float kf[IT_HD];
+    cl.sync();                              // every block's part of the band list is written (and fmax has been read everywhere)
+    // ---- exact scores of the band (the reference's order: src/attention.c:573-582 with dot_f32's grouping, :249-258).
+    // The cluster's blocks share the list evenly; 64 keys per pass: dequantise into shared memory (16 threads per key),
+    // one (key, head) dot per thread and four heads in turn, then one thread per key adds the 64 weighted terms in head order.
+    const int total = *reinterpret_cast<volatile int32_t *>(band_count + 2 * b);
+    const int per = (total + TK_CL - 1) / TK_CL;
+    const int k_begin = min(total, (int)rank * per), k_end = min(total, k_begin + per);
+    for (int k0 = k_begin; k0 < k_end; k0 += BC_KEYS) {
+        {
+            const int kk = tid >> 4, part = tid & 15;
+            if (k0 + kk < k_end) {
+                const int c = list[k0 + kk];
+                const float sc = kscale[(int64_t)b * stride + c];
+                const uint2 v = *reinterpret_cast<const uint2 *>(keys + ((int64_t)b * stride + c) * IT_HD + part * 8);
+                float *dst = skey + kk * IT_HD + part * 8;
 #pragma unroll
-        for (int ch = 0; ch < IT_HD / 16; ch++) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(kr) + ch);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) kf[ch * 16 + kk * 4 + j] = __fmul_rn(e4m3_to_f32_i((w[kk] >> (8 * j)) & 0xffu), s);
-        }
-        for (int j = 0; j < 8; j++) {
-            const int h = j * 8 + l8;
-            const float4 *qh = reinterpret_cast<const float4 *>(sq + h * RS_QLD);
-            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < IT_HD / 4; i++) {
-                const float4 qv = qh[i];
-                s0 = __fadd_rn(s0, __fmul_rn(kf[4 * i + 0], qv.x));
-                s1 = __fadd_rn(s1, __fmul_rn(kf[4 * i + 1], qv.y));
-                s2 = __fadd_rn(s2, __fmul_rn(kf[4 * i + 2], qv.z));
-                s3 = __fadd_rn(s3, __fmul_rn(kf[4 * i + 3], qv.w));
+                for (int j = 0; j < 4; j++) {
+                    dst[j] = __fmul_rn(e4m3_to_f32_i((v.x >> (8 * j)) & 0xffu), sc);
+                    dst[4 + j] = __fmul_rn(e4m3_to_f32_i((v.y >> (8 * j)) & 0xffu), sc);
+                }
             }
-            float d = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
-            if (d < 0.f) d = 0.f;
-            pg[h] = __fmul_rn(d, sw[h]);
         }
-        __syncwarp();
-        if (l8 == 0) {
-            float total = 0.f;
+        __syncthreads();
+        {
+            const int kk = tid >> 4;
+            const float4 *kp = reinterpret_cast<const float4 *>(skey + kk * IT_HD);
+#pragma unroll 1
+            for (int j = 0; j < 4; j++) {
+                const int h = (tid & 15) + 16 * j;
+                const float4 *qp = reinterpret_cast<const float4 *>(sq + h * BC_QLD);
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll 8
-            for (int h = 0; h < IT_IH; h++) total = __fadd_rn(total, pg[h]);
-            refined[(int64_t)b * key_stride + c] = total;
+                for (int i = 0; i < IT_HD / 4; i++) {
+                    const float4 kv = kp[i], qv = qp[i];
+                    s0 = __fadd_rn(s0, __fmul_rn(kv.x, qv.x));
+                    s1 = __fadd_rn(s1, __fmul_rn(kv.y, qv.y));
+                    s2 = __fadd_rn(s2, __fmul_rn(kv.z, qv.z));
+                    s3 = __fadd_rn(s3, __fmul_rn(kv.w, qv.w));
+                }
+                float d = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
+                if (d < 0.f) d = 0.f;
+                sprod[kk * (IT_IH + 1) + h] = __fmul_rn(d, sw[h]);
+            }
         }
-        __syncwarp();
+        __syncthreads();
+        if (tid < BC_KEYS && k0 + tid < k_end) {
+            float tot = 0.f;
+#pragma unroll 8
+            for (int h = 0; h < IT_IH; h++) tot = __fadd_rn(tot, sprod[tid * (IT_IH + 1) + h]);
+            f[list[k0 + tid]] = tot;
+        }
+        __syncthreads();
     }
 }
 
@@ -506,7 +510,7 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
         CWK_CUDA(ctx, cudaFuncSetAttribute(indexer_scores_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, I_SMEM));
-        CWK_CUDA(ctx, cudaFuncSetAttribute(band_rescore_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(band_classify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BC_SMEM));
         attr_set[ctx->device & 15] = true;
     }
     IdxParams p;
@@ -519,11 +523,9 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
         CWK_LAUNCH_CHECK(ctx, "indexer_scores_tc_kernel");
     }
     CWK_CUDA(ctx, cudaMemsetAsync(band, 0, (size_t)B * 2 * sizeof(int32_t), ctx->stream));
-    band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band);
+    band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, BC_SMEM, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band,
+                                                                              (const uint8_t *)keys, kscale, q, wt);
     CWK_LAUNCH_CHECK(ctx, "band_classify_kernel");
-    band_rescore_kernel<<<dim3(std::max(1, ctx->sm_count / B), B), 256, RS_SMEM, ctx->stream>>>((const uint8_t *)keys, kscale, key_stride, q, wt, band_list, band,
-                                                                   refined);
-    CWK_LAUNCH_CHECK(ctx, "band_rescore_kernel");
     if (scores_out) CWK_CUDA(ctx, cudaMemcpyAsync(scores_out, refined, (size_t)B * key_stride * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     return cwk_topk_compact(ctx, refined, key_stride, n, B, want, keep_self, sel, sel_ld, nsel, band_list, band);
 }
