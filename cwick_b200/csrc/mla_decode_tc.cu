@@ -23,8 +23,11 @@
 // rope block, which come free together); Q is one box.
 //
 // Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps
-// 4..11 = softmax / correction / epilogue: two groups of four warps, 32 heads
-// each (TMEM lane quarter = warp % 4).
+// 4..19 = softmax / correction / epilogue: four groups of four warps, 16 heads
+// each (TMEM lane quarter = warp % 4). The exponentials of a tile are computed
+// against the current reference exponents before the block agrees (one barrier
+// with an OR reduction) on whether any score outran them; only then are they
+// redone.
 // Every mbarrier wait is bounded; a wait that gives up records a code in a
 // device word and the block tears down (TMEM freed, copies drained).
 #include <cuda.h>
