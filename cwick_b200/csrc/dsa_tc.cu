@@ -22,9 +22,11 @@
 //   4. the selection kernel (csrc/dsa.cu) takes the exact threshold from the re-scored keys and
 //      writes the reference's list in the reference's order.
 //
-// Pipeline of step 1 per 128-key tile: TMA (raw E4M3 tile, 16 KB) -> 8 converter warps
-// (cvt.rn.f16x2.e4m3x2 into two 128-byte-swizzled K-major blocks) -> MMA issuer (8 MMAs, M 128,
-// N 128) -> 4 epilogue warps (TMEM -> a[c]). Blocks are persistent over the tiles of one sequence.
+// Pipeline of step 1 per 128-key tile: TMA (raw E4M3 tile, 16 KB, 8 stages) -> 8 converter warps
+// (cvt.rn.f16x2.e4m3x2; a thread owns a key row and stores its f16 pairs into tensor memory, where
+// they are the MMA's A operand: shared-memory bandwidth bounds this kernel, and so the MMAs read only
+// the query from it) -> MMA issuer (8 MMAs, M 128, N 128) -> 4 epilogue warps (TMEM -> a[c]).
+// Blocks are persistent over the tiles of one sequence.
 // Every mbarrier wait is bounded and records a code in the context's error word when it gives up.
 #include <algorithm>
 
@@ -36,20 +38,19 @@
 namespace {
 
 constexpr int IT_KEYS = 128, IT_HD = 128, IT_IH = 64;
-constexpr int RAW_STAGES = 4;
+constexpr int RAW_STAGES = 8;
 constexpr int RAW_BYTES = IT_KEYS * IT_HD;              // 16384
-constexpr int A_BYTES_I = IT_KEYS * IT_HD * 2;          // 32768: two [128][64] f16 blocks
 constexpr int IT_QROWS = 2 * IT_IH;                      // q split into f16 hi and lo parts: 128 MMA columns
 constexpr int Q_BYTES_I = IT_QROWS * IT_HD * 2;         // 32768: two [128][64] f16 blocks
 constexpr int I_OFF_Q = 0;
-constexpr int I_OFF_A = Q_BYTES_I;                      // 2 buffers
-constexpr int I_OFF_RAW = I_OFF_A + 2 * A_BYTES_I;      // 4 stages
+constexpr int I_OFF_RAW = Q_BYTES_I;                    // 8 stages of raw E4M3 tiles (128-byte swizzle)
+constexpr uint32_t I_COL_D = 0, I_COL_A = 256;          // TMEM: two 128-column accumulators, two 64-column A operands (f16 pairs)
 constexpr int I_OFF_BAR = I_OFF_RAW + RAW_STAGES * RAW_BYTES;
 constexpr int I_OFF_W = I_OFF_BAR + 256;                // 19 words: warp maxima of the query split, 1 / scale, sign masks of the head weights
 constexpr int I_SMEM = I_OFF_W + 256 + 1024;
 constexpr int IT_THREADS = 512;                          // TMA, MMA, 2 idle | 8 converter warps | 4 epilogue warps
 constexpr int IT_CONV = 256;
-enum { IB_RAW_FULL = 0, IB_RAW_EMPTY = 4, IB_A_FULL = 8, IB_A_EMPTY = 10, IB_D_FULL = 12, IB_D_EMPTY = 14, IB_COUNT = 16 };
+enum { IB_RAW_FULL = 0, IB_RAW_EMPTY = 8, IB_A_FULL = 16, IB_A_EMPTY = 18, IB_D_FULL = 20, IB_D_EMPTY = 22, IB_COUNT = 24 };
 
 // M x N f16 x f16 -> f32, both operands K-major
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N) {
@@ -106,7 +107,7 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(256u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // The B operand, built once per block from the f32 query of this sequence: every element is multiplied by
@@ -191,41 +192,46 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
                 if (ok) ok = mbar_wait(bar(IB_D_EMPTY + ab), (uint32_t)((use & 1) ^ 1), p.err, 804);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t da = smem_desc(base + I_OFF_A + ab * A_BYTES_I, 16, 1024), db = smem_desc(base + I_OFF_Q, 16, 1024);
+                const uint64_t db = smem_desc(base + I_OFF_Q, 16, 1024);
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++)
-                    umma_bf16(tmem + ab * 128, da + (uint64_t)(((ks >> 2) * (IT_KEYS * 128) + (ks & 3) * 32) >> 4),
-                              db + (uint64_t)(((ks >> 2) * (IT_QROWS * 128) + (ks & 3) * 32) >> 4), ID, ks != 0);
+                for (int ks = 0; ks < 8; ks++)          // A: the converted keys in tensor memory, 16 f16 of every row = 8 columns per step
+                    umma_bf16_ts(tmem + I_COL_D + ab * 128, tmem + I_COL_A + ab * 64 + ks * 8,
+                                 db + (uint64_t)(((ks >> 2) * (IT_QROWS * 128) + (ks & 3) * 32) >> 4), ID, ks != 0);
                 umma_commit(bar(IB_A_EMPTY + ab));
                 umma_commit(bar(IB_D_FULL + ab));
             }
         }
     } else if (warp >= 4 && warp < 12) {
-        // ---------------- converters: raw E4M3 tile -> f16 K-major blocks
-        const int ct = tid - 128;
+        // ---------------- converters: raw E4M3 tile -> f16 pairs in tensor memory, the MMA's A operand
+        // A thread owns one key row (= its TMEM lane) and half of its 128 codes; the MMAs then read only the query
+        // from shared memory.
+        const int q4 = warp & 3, hv = (warp - 4) >> 2;
+        const int row = q4 * 32 + lane;
+        const uint32_t tl = tmem + ((uint32_t)(q4 * 32) << 16);
         bool ok = true;
         for (int i = 0; i < nt; i++) {
             const int r = i % RAW_STAGES, ruse = i / RAW_STAGES, ab = i & 1, ause = i >> 1;
             ok = mbar_wait(bar(IB_RAW_FULL + r), (uint32_t)(ruse & 1), p.err, 805);
             if (ok) ok = mbar_wait(bar(IB_A_EMPTY + ab), (uint32_t)((ause & 1) ^ 1), p.err, 806);
+            ok = __all_sync(0xffffffffu, ok);            // the TMEM stores below are warp-wide
             if (!ok) break;
-            const uint8_t *src = sm + I_OFF_RAW + r * RAW_BYTES;
-            uint8_t *dst = sm + I_OFF_A + ab * A_BYTES_I;
+            tc_fence_after();
+            const uint8_t *src = sm + I_OFF_RAW + r * RAW_BYTES + row * 128;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int row = j * 32 + (ct >> 3), ch = ct & 7;          // 16 codes = dims ch*16 .. +15
-                const uint4 v = *reinterpret_cast<const uint4 *>(src + row * 128 + ch * 16);
-                const uint2 c0 = e4m3x4_f16x4(v.x), c1 = e4m3x4_f16x4(v.y), c2 = e4m3x4_f16x4(v.z), c3 = e4m3x4_f16x4(v.w);
-                const uint4 lo = make_uint4(c0.x, c0.y, c1.x, c1.y), hi = make_uint4(c2.x, c2.y, c3.x, c3.y);
-                uint8_t *blk = dst + (ch >> 2) * (IT_KEYS * 128) + row * 128;       // dims 0-63 | 64-127
-                const int k0 = (ch & 3) * 2;
-                // the threads of the second block store their halves in the other order, so that the eight
-                // threads of a row hit eight different 16-byte bank groups in each store
-                const int sw = ch >> 2;
-                *reinterpret_cast<uint4 *>(blk + (((k0 + sw) ^ (row & 7)) << 4)) = sw ? hi : lo;
-                *reinterpret_cast<uint4 *>(blk + (((k0 + 1 - sw) ^ (row & 7)) << 4)) = sw ? lo : hi;
+            for (int half = 0; half < 2; half++) {
+                uint32_t w[16];
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int ch = hv * 4 + half * 2 + j;                    // 16 codes = dims ch*16 .. +15
+                    const uint4 v = *reinterpret_cast<const uint4 *>(src + ((ch ^ (row & 7)) << 4));
+                    const uint2 c0 = e4m3x4_f16x4(v.x), c1 = e4m3x4_f16x4(v.y), c2 = e4m3x4_f16x4(v.z), c3 = e4m3x4_f16x4(v.w);
+                    w[8 * j] = c0.x; w[8 * j + 1] = c0.y; w[8 * j + 2] = c1.x; w[8 * j + 3] = c1.y;
+                    w[8 * j + 4] = c2.x; w[8 * j + 5] = c2.y; w[8 * j + 6] = c3.x; w[8 * j + 7] = c3.y;
+                }
+                TMEM_ST16(w, 0, tl + I_COL_A + ab * 64 + hv * 32 + half * 16);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
             mbar_arrive(bar(IB_A_FULL + ab));
             mbar_arrive(bar(IB_RAW_EMPTY + r));
         }
@@ -279,7 +285,7 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
@@ -503,7 +509,7 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
         cuuint32_t box[2] = {(cuuint32_t)hd, IT_KEYS};
         cuuint32_t es[2] = {1, 1};
         if (enc(&tm_keys, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(keys), dims, strides, box, es,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(keys) failed");
     }

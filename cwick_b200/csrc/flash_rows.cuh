@@ -330,21 +330,30 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
 }
 
 // ---------------------------------------------------------------------------
-// Split merge. grid (nh, B, ceil(D/128)), 128 threads. Weights e^(m_s-M) are computed once
-// into shared memory; the value pass then streams each record's row once with
-// float2 loads. FOLD = false: normalised bf16 rows out[b][h][D].
+// Split merge. grid (nh, B, ceil(D/128)), 128 threads, one output column per thread. A short call
+// is a chain of latencies, so the loads of the first 32 records' values go out before anything
+// else: the weights e^(m_s-M) (two warp-shuffle reductions, one block barrier each) are computed
+// while they are in flight. FOLD = false: normalised bf16 rows out[b][h][D].
 // FOLD = true: one un-normalised record (same layout as the inputs) at rec_out.
 // ---------------------------------------------------------------------------
 constexpr int CWK_MAX_SPLITS = 512;
+constexpr int CWK_MERGE_AHEAD = 32;
 
 template <bool FOLD>
 static __global__ void __launch_bounds__(128) lse_merge_kernel(const float *partial, int nsplit, int nh, int D,
                                                                uint16_t *out, float *rec_out) {
-    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t rec_sz = (int64_t)nh * (D + 2);
     const float *base = partial + (int64_t)b * nsplit * rec_sz;
     __shared__ float sw[CWK_MAX_SPLITS];
-    __shared__ float red[128];
+    __shared__ float red[8];
+    // value pass, part one: blockIdx.z picks a 128-column chunk of the row
+    const float *orow = base + 2 * nh + (int64_t)h * D;
+    const int i = blockIdx.z * 128 + tid;
+    float v[CWK_MERGE_AHEAD];
+#pragma unroll
+    for (int s = 0; s < CWK_MERGE_AHEAD; s++) v[s] = (i < D && s < nsplit) ? orow[(int64_t)s * rec_sz + i] : 0.f;
+
     float mloc = -INFINITY;
     for (int s = tid; s < nsplit; s += 128) {
         const float l = base[s * rec_sz + nh + h];
@@ -352,14 +361,11 @@ static __global__ void __launch_bounds__(128) lse_merge_kernel(const float *part
         sw[s] = (l > 0.f) ? m : -INFINITY;
         if (l > 0.f) mloc = fmaxf(mloc, m);
     }
-    red[tid] = mloc;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+    if (lane == 0) red[warp] = mloc;
     __syncthreads();
-    for (int o = 64; o > 0; o >>= 1) {
-        if (tid < o) red[tid] = fmaxf(red[tid], red[tid + o]);
-        __syncthreads();
-    }
-    const float M = red[0];
-    __syncthreads();
+    const float M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     float dloc = 0.f;
     for (int s = tid; s < nsplit; s += 128) {
         const float m = sw[s];
@@ -367,34 +373,32 @@ static __global__ void __launch_bounds__(128) lse_merge_kernel(const float *part
         sw[s] = w;
         dloc += w * base[s * rec_sz + nh + h];
     }
-    red[tid] = dloc;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dloc += __shfl_xor_sync(0xffffffffu, dloc, o);
+    if (lane == 0) red[4 + warp] = dloc;
     __syncthreads();
-    for (int o = 64; o > 0; o >>= 1) {
-        if (tid < o) red[tid] += red[tid + o];
-        __syncthreads();
-    }
-    const float den = red[0];
+    const float den = (red[4] + red[5]) + (red[6] + red[7]);
     const float inv = FOLD ? 1.f : (den > 0.f ? 1.f / den : 0.f);
     if (FOLD && tid == 0 && blockIdx.z == 0) {
         rec_out[h] = M;
         rec_out[nh + h] = den;
     }
-    // value pass: blockIdx.z picks a 128-column chunk of the row, one column per thread
-    const float *orow = base + 2 * nh + (int64_t)h * D;
-    const int i = blockIdx.z * 128 + tid;
     if (i < D) {
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        int s = 0;
-        for (; s + 4 <= nsplit; s += 4) {
-            a0 += sw[s] * orow[(int64_t)s * rec_sz + i];
-            a1 += sw[s + 1] * orow[(int64_t)(s + 1) * rec_sz + i];
-            a2 += sw[s + 2] * orow[(int64_t)(s + 2) * rec_sz + i];
-            a3 += sw[s + 3] * orow[(int64_t)(s + 3) * rec_sz + i];
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < CWK_MERGE_AHEAD; s++)
+            if (s < nsplit) a[s & 3] += sw[s] * v[s];
+        for (int s0 = CWK_MERGE_AHEAD; s0 < nsplit; s0 += 16) {
+            float u[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) u[j] = (s0 + j < nsplit) ? orow[(int64_t)(s0 + j) * rec_sz + i] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (s0 + j < nsplit) a[j & 3] += sw[s0 + j] * u[j];
         }
-        for (; s < nsplit; s++) a0 += sw[s] * orow[(int64_t)s * rec_sz + i];
-        const float a = (a0 + a1) + (a2 + a3);
-        if (FOLD) rec_out[2 * nh + (int64_t)h * D + i] = a;
-        else out[((int64_t)b * nh + h) * D + i] = (uint16_t)(pack_bf16x2(a * inv, 0.f) & 0xffffu);
+        const float r = (a[0] + a[1]) + (a[2] + a[3]);
+        if (FOLD) rec_out[2 * nh + (int64_t)h * D + i] = r;
+        else out[((int64_t)b * nh + h) * D + i] = (uint16_t)(pack_bf16x2(r * inv, 0.f) & 0xffffu);
     }
 }
 

@@ -361,11 +361,10 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_arrive(bar(B_PFULL));
             if (st == 0) TRACE(2, it, 1);
         }
-        // ---- epilogue: wait for the last P.V, then write the un-normalised record
-        if (ok) ok = mbar_wait(bar(B_EMPTY_RP), (uint32_t)((n - 1) & 1), p.err, 302);
+        // ---- epilogue: the row sums need only the last softmax; each 128-row block of O^T is written as soon
+        // as its own MMAs have completed (their commit is the barrier that frees the block's latent slot), so
+        // the write-out of block 0 runs under the MMAs of blocks 1-3
         if (ok) {
-            if (st == 0) TRACE(2, 15, 2);
-            tc_fence_after();
             const float mine = warp_transpose_reduce16<false>(lpart, lane);  // lane L: sum of head hb+(L&15) over this warp's rows
             if (lane < HG) s_w[(warp - 4) * HG + lane] = mine;
             if (st == 0) TRACE(2, 15, 3);
@@ -383,7 +382,12 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             if (p.out) softmax_bar();
             if (st == 0) TRACE(2, 15, 4);
-            for (int mb = 0; mb < 4; mb++) {
+            for (int mb = 0; mb < 4 && ok; mb++) {
+                ok = mbar_wait(bar(mb == 3 ? B_EMPTY_RP : B_EMPTY_L + mb), (uint32_t)((n - 1) & 1), p.err, 302);
+                ok = __all_sync(0xffffffffu, ok);                  // the TMEM load below is warp-wide
+                if (!ok) break;
+                if (st == 0 && mb == 0) TRACE(2, 15, 2);
+                tc_fence_after();
                 uint32_t o[16];
                 const int h0 = hb;
                 TMEM_LD16(o, 0, tlane + COL_O + mb * 64 + h0);
