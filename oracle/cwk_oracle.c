@@ -1007,3 +1007,156 @@ ORC_API void orc_ds_lin_q(const float *x, const uint8_t *w, const uint8_t *w_sca
     }
     free(asf); free(af);
 }
+
+/* ------------------------------------------------------------------ */
+/* DeepSeek compressor and candidate blocks                            */
+/* ------------------------------------------------------------------ */
+
+/* The reference's e2m1 rounding as written: thresholds .25 .75 1.25 1.75 2.5 3.5 5
+ * with results 0 1 1 2 2 4 4 6 (so 0.5, 1.5 and 3 are never produced). Kept as
+ * it is: parity is with the reference's behaviour. src/ds_ops.c:212-226. */
+ORC_API float orc_ds_fp4_round(float v) {
+    static const float thr[7] = {0.25f, 0.75f, 1.25f, 1.75f, 2.5f, 3.5f, 5.0f};
+    static const float res[8] = {0.0f, 1.0f, 1.0f, 2.0f, 2.0f, 4.0f, 4.0f, 6.0f};
+    float a = v < 0 ? -v : v;
+    int i = 0;
+    while (i < 7 && a > thr[i]) i++;
+    return v < 0 ? -res[i] : res[i];
+}
+
+/* ceil(log2 x) of a positive normal float from its bits. src/ds_ops.c:228-233. */
+static int log2_ceil_of(float x) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    return (int)((u >> 23) & 0xFFu) - 127 + ((u & 0x7FFFFFu) ? 1 : 0);
+}
+
+/* Quantise-dequantise to e2m1 with a power-of-two scale per 32 values.
+ * src/ds_ops.c:254-272 (ds_qdq_fp4_e8m0). */
+ORC_API void orc_ds_qdq_fp4_e8m0(float *x, int n) {
+    const float floor_amax = 6.0f * ldexpf(1.0f, -126);
+    for (int b = 0; b < n; b += 32) {
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) {
+            float a = fabsf(x[b + i]);
+            if (a > amax) amax = a;
+        }
+        if (amax < floor_amax) amax = floor_amax;
+        float s = ldexpf(1.0f, log2_ceil_of(amax * (1.0f / 6.0f)));
+        for (int i = 0; i < 32; i++) {
+            float q = x[b + i] / s;
+            if (q > 6.0f) q = 6.0f;
+            if (q < -6.0f) q = -6.0f;
+            x[b + i] = orc_ds_fp4_round(q) * s;
+        }
+    }
+}
+
+/* The same with an E4M3-rounded scale per `block` values (the compressed KV).
+ * src/ds_ops.c:274-293 (ds_qdq_fp4_e4m3). */
+ORC_API void orc_ds_qdq_fp4_e4m3(float *x, int n, int block) {
+    const float floor_amax = 6.0f * ldexpf(1.0f, -9);
+    for (int b = 0; b < n; b += block) {
+        float amax = 0.0f;
+        for (int i = 0; i < block; i++) {
+            float a = fabsf(x[b + i]);
+            if (a > amax) amax = a;
+        }
+        if (amax < floor_amax) amax = floor_amax;
+        float s = orc_e4m3_to_f32(orc_f32_to_e4m3_ref(amax * (1.0f / 6.0f)));
+        for (int i = 0; i < block; i++) {
+            float q = x[b + i] / s;
+            if (q > 6.0f) q = 6.0f;
+            if (q < -6.0f) q = -6.0f;
+            x[b + i] = orc_ds_fp4_round(q) * s;
+        }
+    }
+}
+
+/* Rotate adjacent pairs of x[0 .. 2*npairs) by freq[i]*pos, angle in double,
+ * cos/sin rounded to f32. src/ds_ops.c:49-58 (ds_rope, forward). */
+ORC_API void orc_ds_rope(float *x, const float *freq, int npairs, int64_t pos) {
+    for (int i = 0; i < npairs; i++) {
+        double ang = (double)freq[i] * (double)pos;
+        float c = (float)cos(ang), s = (float)sin(ang);
+        float a = x[2 * i], b = x[2 * i + 1];
+        x[2 * i] = a * c - b * s;
+        x[2 * i + 1] = a * s + b * c;
+    }
+}
+
+/* RMS norm with a bf16 weight, mean square in double, result rounded to bf16.
+ * src/ds_ops.c:75-87 (ds_rmsnorm_bf16w). */
+ORC_API void orc_ds_rmsnorm_bf16w(float *y, const float *x, const uint16_t *w, int n, float eps) {
+    double acc = 0.0;
+    for (int i = 0; i < n; i++) acc += (double)x[i] * (double)x[i];
+    float r = (float)(1.0 / sqrt(acc / n + eps));
+    for (int i = 0; i < n; i++) {
+        float t = x[i] * r;
+        y[i] = orc_bf16_round(w ? bf16f(w[i]) * t : t);
+    }
+}
+
+/* Pooling of `ratio` cached projections into one latent row: per element a
+ * softmax over the ratio axis of the gate scores (expf, f32 sum in slot
+ * order), then the weighted sum of the states with weights w[r]/s.
+ * src/ds_model.c:1029-1041. state, score: [ratio][hd]. */
+ORC_API void orc_ds_pool(const float *state, const float *score, int ratio, int hd, float *out) {
+    float w[64];
+    for (int i = 0; i < hd; i++) {
+        float mx = -INFINITY, s = 0.0f, acc = 0.0f;
+        for (int r = 0; r < ratio; r++)
+            if (score[(size_t)r * hd + i] > mx) mx = score[(size_t)r * hd + i];
+        for (int r = 0; r < ratio; r++) {
+            w[r] = expf(score[(size_t)r * hd + i] - mx);
+            s += w[r];
+        }
+        for (int r = 0; r < ratio; r++) acc += state[(size_t)r * hd + i] * (w[r] / s);
+        out[i] = acc;
+    }
+}
+
+/* What the compressor and the indexer do to a finished row before it is
+ * stored: rotate the last 2*npairs elements, round those to bf16, then
+ * quantise-dequantise the whole row (mode 0: e2m1 with power-of-two scales per
+ * 32; mode 1: e2m1 with E4M3 scales per `block`). rows x n, in place.
+ * src/ds_model.c:1059-1068 (index key, mode 0), :1071-1073 (compressed KV,
+ * mode 1, block 16), :1091-1096 (index query heads, mode 0). */
+ORC_API void orc_ds_rope_round_qdq(float *x, int rows, int n, const float *freq, int npairs,
+                                   int64_t pos, int mode, int block) {
+    for (int r = 0; r < rows; r++) {
+        float *t = x + (size_t)r * n + (n - 2 * npairs);
+        orc_ds_rope(t, freq, npairs, pos);
+        for (int i = 0; i < 2 * npairs; i++) t[i] = orc_bf16_round(t[i]);
+    }
+    if (mode == 0) orc_ds_qdq_fp4_e8m0(x, rows * n);
+    else orc_ds_qdq_fp4_e4m3(x, rows * n, block);
+}
+
+/* Candidate blocks: the maximum score of every block of `bs` positions, the last
+ * block forced in, the best `kblocks` blocks by ds_topk's rule, and a byte per
+ * position saying whether its block was kept. Returns the number of blocks kept.
+ * src/ds_model.c:1126-1145. */
+ORC_API int orc_ds_candidates(const float *sc, int n, int bs, int kblocks, uint8_t *cand) {
+    int nblk = (n + bs - 1) / bs;
+    float *bsc = malloc(sizeof(float) * (size_t)(nblk > 0 ? nblk : 1));
+    int *blk = malloc(sizeof(int) * (size_t)(kblocks > 0 ? kblocks : 1));
+    for (int b = 0; b < nblk; b++) {
+        int hi = (b + 1) * bs;
+        if (hi > n) hi = n;
+        float mx = -INFINITY;
+        for (int t = b * bs; t < hi; t++)
+            if (sc[t] > mx) mx = sc[t];
+        bsc[b] = mx;
+    }
+    if (n > 0) bsc[(n - 1) / bs] = INFINITY;
+    int k = orc_ds_topk(bsc, nblk, kblocks, blk);
+    memset(cand, 0, (size_t)n);
+    for (int i = 0; i < k; i++) {
+        int hi = (blk[i] + 1) * bs;
+        if (hi > n) hi = n;
+        for (int t = blk[i] * bs; t < hi; t++) cand[t] = 1;
+    }
+    free(bsc); free(blk);
+    return k;
+}

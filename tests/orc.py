@@ -91,6 +91,16 @@ def oracle():
                                            C.c_int, C.c_int, C.c_float, f32p, C.c_int]
         L.orc_mla_decode_ranges.argtypes = [f32p, u16p, C.c_int64, C.c_int64, C.c_int, C.c_int,
                                             C.c_int, C.c_float, f32p, C.c_int]
+        L.orc_ds_fp4_round.restype = C.c_float
+        L.orc_ds_fp4_round.argtypes = [C.c_float]
+        L.orc_ds_qdq_fp4_e8m0.argtypes = [f32p, C.c_int]
+        L.orc_ds_qdq_fp4_e4m3.argtypes = [f32p, C.c_int, C.c_int]
+        L.orc_ds_rope.argtypes = [f32p, f32p, C.c_int, C.c_int64]
+        L.orc_ds_rmsnorm_bf16w.argtypes = [f32p, f32p, u16p, C.c_int, C.c_float]
+        L.orc_ds_pool.argtypes = [f32p, f32p, C.c_int, C.c_int, f32p]
+        L.orc_ds_rope_round_qdq.argtypes = [f32p, C.c_int, C.c_int, f32p, C.c_int, C.c_int64, C.c_int, C.c_int]
+        L.orc_ds_candidates.restype = C.c_int
+        L.orc_ds_candidates.argtypes = [f32p, C.c_int, C.c_int, C.c_int, u8p]
         _oracle = L
     return _oracle
 
@@ -119,6 +129,14 @@ def ref():
         if hasattr(L, "ds_f32_to_e4m3"):
             L.ds_f32_to_e4m3.restype = C.c_uint8
             L.ds_f32_to_e4m3.argtypes = [C.c_float]
+        if hasattr(L, "ds_fp4_round"):
+            L.ds_fp4_round.restype = C.c_float
+            L.ds_fp4_round.argtypes = [C.c_float]
+            L.ds_qdq_fp4_e8m0.argtypes = [f32p, C.c_int]
+            L.ds_qdq_fp4_e4m3.argtypes = [f32p, C.c_int, C.c_int]
+            L.ds_freqs_init.argtypes = [C.c_void_p, C.c_int, C.c_double, C.c_double, C.c_int, C.c_int, C.c_int]
+            L.ds_rope.argtypes = [f32p, C.c_void_p, C.c_int64, C.c_int]
+            L.ds_rmsnorm_bf16w.argtypes = [f32p, f32p, u16p, C.c_int, C.c_float]
         L.refdrv_mla_latent_layer.argtypes = [C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int,
                                               C.c_float] + [C.c_void_p] * 7 + [C.c_void_p, C.c_int64,
                                                                               C.c_int64, f32p, f32p]
