@@ -4,22 +4,10 @@
 // indexer scores (bf16-rounded head dots) and its block-scaled FP8 projection with quantised
 // activations.
 #include "cwk_common.cuh"
+#include "ds_codec.cuh"
 
 namespace {
 
-__device__ __forceinline__ float e4m3f(uint32_t b) {
-    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
-    float mag;
-    if (e == 0) mag = (float)m * 0.001953125f;
-    else if (e == 15 && m == 7) mag = __int_as_float(0x7fc00000);
-    else mag = __uint_as_float(((e + 120u) << 23) | (m << 20));
-    return (b & 0x80u) ? -mag : mag;
-}
-__device__ __forceinline__ float bf16_round_rne(float v) {       // ds_bf16_round, src/ds_ops.c:89-96
-    uint32_t u = __float_as_uint(v);
-    u += 0x7FFFu + ((u >> 16) & 1u);
-    return __uint_as_float(u & 0xFFFF0000u);
-}
 __device__ __forceinline__ uint16_t to_bf16(float v) { return (uint16_t)(pack_bf16x2(v, 0.f) & 0xffffu); }
 
 // One block of `hd` threads per (token, head). Heads 0..nh-1 are query heads (input stride 2*hd, the
@@ -198,25 +186,6 @@ __global__ void __launch_bounds__(128) ds_indexer_scores_kernel(const float *key
 // power-of-two scale (src/ds_quant.c:143-159). Step 2: one warp per output row, lanes over the
 // 32-wide blocks: (sum_32 e4m3(w) * a) * a_scale * 2^(w_scale-127), summed, rounded to bf16
 // (src/ds_quant.c:653-666, src/ds_model.c:880-885).
-__device__ __forceinline__ float e4m3_quantise_dequantise_ref(float v) {
-    if (v == 0.f) return 0.f;
-    const float a = fabsf(v);
-    int ex;
-    (void)frexpf(a, &ex);
-    int e = ex - 1;
-    float r;
-    if (e < -6) {
-        if (e < -10) return copysignf(0.f, v);
-        const float qv = rintf(a * 512.f);
-        r = (qv >= 8.f) ? 0.f : qv * 0.001953125f;      // the reference masks a carried mantissa to zero
-    } else {
-        float qv = rintf(ldexpf(a, 3 - e));
-        if (qv == 16.f) { qv = 8.f; e++; }
-        if (e > 8) { e = 8; qv = 14.f; }
-        r = ldexpf(qv, e - 3);
-    }
-    return copysignf(r, v);
-}
 __global__ void __launch_bounds__(256) ds_act_quant_kernel(const float *x, int64_t K, float *af, float *asf) {
     for (int64_t b = threadIdx.x; b < K / 32; b += 256) {
         float amax = 0.f;

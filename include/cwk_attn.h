@@ -283,6 +283,35 @@ CWK_API int cwk_ds_topk(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const 
 CWK_API int cwk_ds_lin_q(cwk_ctx *ctx, const float *x, const void *w, const void *w_scale, int64_t N, int64_t K,
                          float *out);
 
+/* ---- DeepSeek-V4 compressor and candidate blocks -----------------------------------
+ * The pieces of ds_compress (src/ds_model.c:1002-1077) and of the two-level selection of ds_indexer
+ * (:1091-1096, :1126-1149) around its projections, which are plain GEMVs (cwk_ds_lin_q and bf16 ones).
+ * All results are the reference's bit for bit, except cwk_ds_pool_norm's, where the reference's expf comes
+ * from the C library (values may differ in the last place before the norm's bf16 rounding).
+ *
+ * Pooling + norm (:1029-1042): state, score f32 [B][ratio][hd] (the kv and gate projections of the ratio
+ * positions of a group, slot order) -> per element softmax over the ratio axis, weighted sum, RMS norm
+ * with the bf16 weight norm_w [hd] (NULL = ones), result rounded to bf16: latent f32 [B][hd]. ratio = 1
+ * gives the plain norm of `state` (:1012-1017). */
+CWK_API int cwk_ds_pool_norm(cwk_ctx *ctx, const float *state, const float *score, int B, int ratio, int hd,
+                             const void *norm_w, float eps, float *latent);
+/* ds_rmsnorm_bf16w (src/ds_ops.c:75-87) on rows x n values, w bf16 [n] or NULL. */
+CWK_API int cwk_ds_rmsnorm_bf16w(cwk_ctx *ctx, const float *x, const void *w, int rows, int n, float eps, float *y);
+/* What a finished row goes through before it is stored (:1062-1066 index key, :1071-1073 compressed KV,
+ * :1091-1096 index query heads), in place on x f32 [rows][n] (device): ds_rope on the last 2*npairs values
+ * of every row at position pos (freq: HOST array [npairs] of ds_freqs.freq; the angles' cos/sin are formed
+ * on the host in double as src/ds_ops.c:51-52 does), bf16 rounding of those values, then
+ * mode 0: ds_qdq_fp4_e8m0 (src/ds_ops.c:254-272, scale per 32), mode 1: ds_qdq_fp4_e4m3 (:274-293, scale per
+ * `block`). n must be a multiple of the scale block. The e2m1 rounding is the reference's as written
+ * (src/ds_ops.c:212-226: magnitudes 0, 1, 2, 4, 6). Subnormal inputs (below 2^-126) count as zero. */
+CWK_API int cwk_ds_rope_round_qdq(cwk_ctx *ctx, float *x, int rows, int n, const float *freq, int npairs, int64_t pos,
+                                  int mode, int block);
+/* Candidate blocks of the source layer (:1126-1145): maxima of the blocks of bs scores, the last block
+ * forced in, the best kblocks blocks (cwk_ds_topk's rule), cand uint8 [n] = 1 inside kept blocks. */
+CWK_API int cwk_ds_candidates(cwk_ctx *ctx, const float *sc, int n, int bs, int kblocks, uint8_t *cand);
+/* What the layers using the candidates do first (:1146-1149): sc[t] = -inf where cand[t] == 0. */
+CWK_API int cwk_ds_mask_candidates(cwk_ctx *ctx, float *sc, const uint8_t *cand, int n);
+
 /* ---- MLA causal prefill of a chunk ---------------------------------------
  * Replaces cwick_attention_mla_prefill_chunk up to the attention output
  * (src/attention.c:943-1019) for FP8-E4M3 block-scaled q_a / q_b / kv_a
