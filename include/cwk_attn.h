@@ -283,6 +283,16 @@ CWK_API int cwk_ds_topk(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const 
 CWK_API int cwk_ds_lin_q(cwk_ctx *ctx, const float *x, const void *w, const void *w_scale, int64_t N, int64_t K,
                          float *out);
 
+/* ---- The output side of the absorbed attention -------------------------------------
+ * Un-absorb of a chunk's attention output through W_v (src/attention.c:812-815, gemv_bf16_n, batched over
+ * tokens; the step between the absorbed attention and o_proj, :1020-1023) on tcgen05:
+ *   out[t][h][0:128] = attn[t][h][0:512] . W_v[h]^T
+ * attn bf16 [n][nh][512] (what cwk_mla_prefill and cwk_mla_decode write), Wv bf16: head h's [128][512] rows start
+ * at row h * w_head_rows of a 512-wide row-major matrix (128 for a packed [nh][128][512]; nope + vdim with Wv
+ * pointing at row `nope` of the reference's kv_b_proj, :737-740), out bf16 [n][nh * 128]: the input rows of
+ * o_proj (cwk_fp8_linear for an FP8 o_proj). 16-byte aligned buffers; latent 512 and vdim 128 only. */
+CWK_API int cwk_mla_unabsorb(cwk_ctx *ctx, const void *attn, const void *Wv, int64_t w_head_rows, int n, int nh, void *out);
+
 /* ---- DeepSeek-V4 compressor and candidate blocks -----------------------------------
  * The pieces of ds_compress (src/ds_model.c:1002-1077) and of the two-level selection of ds_indexer
  * (:1091-1096, :1126-1149) around its projections, which are plain GEMVs (cwk_ds_lin_q and bf16 ones).
