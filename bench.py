@@ -532,6 +532,25 @@ def side_prefill(attn, dev, stream, peak):
     def call():
         attn.mla_prefill(X, Wqa, Sqa, Wqb, Sqb, Wkva, Skva, ones_q, ones_k, Wuk, cache, 0, nh)
     ms, k_ms, k_n = _time_calls(attn, stream, call, n=5, warm=2)
+    # the output side of the same layer (not part of config 3's FLOP count or time): un-absorb through W_v, then an
+    # FP8 block-scaled o_proj (nh * 128 -> H)
+    vdim = 128
+    Wuv = (0.02 * torch.randn(nh, vdim, lat, device=dev, generator=g)).to(torch.bfloat16)
+    Wo, So = fp8w(H, nh * vdim)
+    res = {}
+
+    def out_a():
+        res["att"] = attn.mla_prefill(X, Wqa, Sqa, Wqb, Sqb, Wkva, Skva, ones_q, ones_k, Wuk, cache, 0, nh)
+    out_a()
+
+    def out_u():
+        res["v"] = attn.mla_unabsorb(res["att"], Wuv)
+    ms_u, _, _ = _time_calls(attn, stream, out_u, n=5, warm=2)
+
+    def out_o():
+        res["o"] = attn.fp8_linear(res["v"], Wo, So, out_bf16=True)
+    ms_o, _, _ = _time_calls(attn, stream, out_o, n=5, warm=2)
+    unabsorb_bytes = n * nh * (lat + vdim) * 2
     proj = 2.0 * n * (H * q_lora + q_lora * nh * (nope + rope) + H * (lat + rope))
     absorb = 2.0 * n * nh * nope * lat
     pairs = n * (n + 1) / 2.0
@@ -546,7 +565,11 @@ def side_prefill(attn, dev, stream, peak):
             "tflops_executed": executed / (ms / 1e3) / 1e12,
             "flops": {"fp8_projections": proj, "absorb": absorb, "causal_attention": attn_fl,
                       "causal_attention_executed": attn_exec},
-            "main_kernel_ms": k_ms, "main_kernels_per_call": k_n}
+            "main_kernel_ms": k_ms, "main_kernels_per_call": k_n,
+            "output_side": {"unabsorb_ms": ms_u, "unabsorb_gbs": unabsorb_bytes / (ms_u / 1e3) / 1e9,
+                            "unabsorb_frac_of_measured_peak": unabsorb_bytes / (ms_u / 1e3) / 1e9 / peak,
+                            "o_proj_fp8_ms": ms_o, "o_proj_tflops": 2.0 * n * H * nh * vdim / (ms_o / 1e3) / 1e12,
+                            "note": "after the attention: cwk_mla_unabsorb then cwk_fp8_linear (8192 -> 4096); not in ms_per_prefill"}}
 
 
 def side_dsa(attn, dev, stream, peak):

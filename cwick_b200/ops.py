@@ -170,6 +170,15 @@ class Attn:
                                                1 if out_bf16 else 0))
         return Y
 
+    def mla_unabsorb(self, attn_out, Wv, head_rows=128):
+        """attn_out bf16 [n][nh][512]; Wv bf16, head h's [128][512] at row h * head_rows. Returns bf16 [n][nh*128]
+        (src/attention.c:812-815 batched over tokens: the input rows of o_proj)."""
+        _bf16(attn_out), _bf16(Wv)
+        n, nh, _ = attn_out.shape
+        out = torch.empty(n, nh * 128, dtype=torch.bfloat16, device=attn_out.device)
+        self.ctx.check(self.lib.cwk_mla_unabsorb(self.ctx.h, _p(attn_out), _p(Wv), head_rows, n, nh, _p(out)))
+        return out
+
     # ---- MLA prefill -----------------------------------------------------------------
     def mla_prefill(self, X, Wqa, Sqa, Wqb, Sqb, Wkva, Skva, qa_norm, kva_norm, Wuk, cache, pos0, nh,
                     nope=128, rope=64, kv_lora=512, eps=1e-6, rope_base=10000.0, scale=None):
