@@ -82,11 +82,12 @@ struct RopeTable {
 
 // One block per row: rotary + bf16 rounding of the last 2*npairs values, then the row's quantise/dequantise.
 // mode 0: scale 2^ceil(log2(amax/6)) per 32 values (src/ds_ops.c:254-272); mode 1: scale = E4M3(amax/6) per
-// `block` values (:274-293).
+// `block` values (:274-293); mode 2: the attention output before its projections (src/ds_model.c:1258-1272):
+// the whole row is rounded to bf16 first, the table holds the inverse rotation, nothing is quantised.
 __global__ void __launch_bounds__(DC_THREADS) ds_rope_round_qdq_kernel(float *x, int n, int npairs, const RopeTable tab, int mode, int block) {
     extern __shared__ float xs[];
     float *row = x + (int64_t)blockIdx.x * n;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) xs[i] = row[i];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) xs[i] = mode == 2 ? bf16_round_rne(row[i]) : row[i];
     __syncthreads();
     float *t = xs + n - 2 * npairs;
     for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(DC_THREADS) ds_rope_round_qdq_kernel(float *x,
     }
     __syncthreads();
     const int bl = mode == 0 ? 32 : block;
-    for (int g = threadIdx.x; g < n / bl; g += blockDim.x) {
+    for (int g = threadIdx.x; mode != 2 && g < n / bl; g += blockDim.x) {
         float *v = xs + g * bl;
         float amax = 0.f;
         for (int i = 0; i < bl; i++) amax = fmaxf(amax, fabsf(v[i]));
@@ -179,24 +180,35 @@ int cwk_ds_rmsnorm_bf16w(cwk_ctx *ctx, const float *x, const void *w, int rows, 
     return CWK_OK;
 }
 
-int cwk_ds_rope_round_qdq(cwk_ctx *ctx, float *x, int rows, int n, const float *freq, int npairs, int64_t pos, int mode,
-                          int block) {
+static int rope_rows_launch(cwk_ctx *ctx, const char *what, float *x, int rows, int n, const float *freq, int npairs, int64_t pos,
+                            int mode, int block) {
     if (!ctx || !x || rows <= 0 || n <= 0 || n > 8192 || npairs < 0 || npairs > 64 || 2 * npairs > n || (npairs && !freq))
-        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_rope_round_qdq: bad argument");
+        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "%s: bad argument", what);
     const int bl = mode == 0 ? 32 : block;
-    if ((mode != 0 && mode != 1) || bl <= 0 || bl > 128 || n % bl)
-        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_rope_round_qdq: the row length must be a multiple of the scale block (<= 128)");
+    if (mode != 2 && ((mode != 0 && mode != 1) || bl <= 0 || bl > 128 || n % bl))
+        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "%s: the row length must be a multiple of the scale block (<= 128)", what);
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     RopeTable tab;
-    for (int i = 0; i < npairs; i++) {          // the reference's own expressions (src/ds_ops.c:51-52), on the host's C library
+    for (int i = 0; i < npairs; i++) {          // the reference's own expressions (src/ds_ops.c:51-53), on the host's C library
         const double ang = (double)freq[i] * (double)pos;
         tab.c[i] = (float)cos(ang);
         tab.s[i] = (float)sin(ang);
+        if (mode == 2) tab.s[i] = -tab.s[i];
     }
     for (int i = npairs; i < 64; i++) tab.c[i] = tab.s[i] = 0.f;
     ds_rope_round_qdq_kernel<<<rows, DC_THREADS, n * sizeof(float), ctx->stream>>>(x, n, npairs, tab, mode, block);
     CWK_LAUNCH_CHECK(ctx, "ds_rope_round_qdq_kernel");
     return CWK_OK;
+}
+
+int cwk_ds_rope_round_qdq(cwk_ctx *ctx, float *x, int rows, int n, const float *freq, int npairs, int64_t pos, int mode,
+                          int block) {
+    if (mode != 0 && mode != 1) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_rope_round_qdq: mode is 0 or 1");
+    return rope_rows_launch(ctx, "ds_rope_round_qdq", x, rows, n, freq, npairs, pos, mode, block);
+}
+
+int cwk_ds_out_unrope(cwk_ctx *ctx, float *o, int rows, int n, const float *freq, int npairs, int64_t pos) {
+    return rope_rows_launch(ctx, "ds_out_unrope", o, rows, n, freq, npairs, pos, 2, 0);
 }
 
 int cwk_ds_topk(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int k, int32_t *out, int64_t out_ld,

@@ -316,6 +316,12 @@ CWK_API int cwk_ds_rmsnorm_bf16w(cwk_ctx *ctx, const float *x, const void *w, in
  * (src/ds_ops.c:212-226: magnitudes 0, 1, 2, 4, 6). Subnormal inputs (below 2^-126) count as zero. */
 CWK_API int cwk_ds_rope_round_qdq(cwk_ctx *ctx, float *x, int rows, int n, const float *freq, int npairs, int64_t pos,
                                   int mode, int block);
+/* The attention output before its projections (src/ds_model.c:1258-1272), in place on o f32 [rows = heads][n]:
+ * every value rounded to bf16, the query rotation undone on each row's last 2*npairs values (ds_rope with
+ * inverse = 1), those rounded again. The grouped wo_a and wo_b that follow (:1279-1303) are cwk_ds_lin_q calls:
+ * per group g, cwk_ds_lin_q(o + g*per, wo_a.w + g*OR*per, wo_a.scale + (g*OR/32)*(per/32), OR, per, o_g + g*OR),
+ * then cwk_ds_lin_q(o_g, wo_b.w, wo_b.scale, D, G*OR, attn_out). */
+CWK_API int cwk_ds_out_unrope(cwk_ctx *ctx, float *o, int rows, int n, const float *freq, int npairs, int64_t pos);
 /* Candidate blocks of the source layer (:1126-1145): maxima of the blocks of bs scores, the last block
  * forced in, the best kblocks blocks (cwk_ds_topk's rule), cand uint8 [n] = 1 inside kept blocks. */
 CWK_API int cwk_ds_candidates(cwk_ctx *ctx, const float *sc, int n, int bs, int kblocks, uint8_t *cand);

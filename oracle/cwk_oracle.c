@@ -1160,3 +1160,22 @@ ORC_API int orc_ds_candidates(const float *sc, int n, int bs, int kblocks, uint8
     free(bsc); free(blk);
     return k;
 }
+
+/* The attention output before its projections: every value rounded to bf16, then
+ * the query rotation undone on each row's last 2*npairs values (ds_rope with
+ * inverse = 1: the sine negated) and those rounded again. rows x n, in place.
+ * src/ds_model.c:1258-1272, src/ds_ops.c:49-58. */
+ORC_API void orc_ds_out_unrope(float *o, int rows, int n, const float *freq, int npairs, int64_t pos) {
+    for (int i = 0; i < rows * n; i++) o[i] = orc_bf16_round(o[i]);
+    for (int r = 0; r < rows; r++) {
+        float *t = o + (size_t)r * n + (n - 2 * npairs);
+        for (int i = 0; i < npairs; i++) {
+            double ang = (double)freq[i] * (double)pos;
+            float c = (float)cos(ang), s = -(float)sin(ang);
+            float a = t[2 * i], b = t[2 * i + 1];
+            t[2 * i] = a * c - b * s;
+            t[2 * i + 1] = a * s + b * c;
+        }
+        for (int i = 0; i < 2 * npairs; i++) t[i] = orc_bf16_round(t[i]);
+    }
+}

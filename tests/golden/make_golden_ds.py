@@ -60,6 +60,14 @@ def main():
             t[i] = row
         G["rope_pos"] = pos
         G["rope_out_" + name] = t
+        # the attention output's un-rotation: bf16-valued rows, ds_rope with inverse = 1, bf16 rounding
+        u = np.array([r.ds_bf16_round(float(v)) for v in G["rope_in_" + name].reshape(-1)], np.float32).reshape(pos.size, 64)
+        G["unrope_in_" + name] = u.copy()
+        for i, p in enumerate(pos):
+            row = u[i].copy()
+            r.ds_rope(orc.P(row, orc.f32p), C.byref(f), int(p), 1)
+            u[i] = [r.ds_bf16_round(float(v)) for v in row]
+        G["unrope_out_" + name] = u
     # norm with a bf16 weight
     for n in (128, 512):
         xin = (synth.normal(SEED, 704 + n, 4 * n) * 3).astype(np.float32).reshape(4, n)

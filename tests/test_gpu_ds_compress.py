@@ -158,3 +158,19 @@ def test_candidate_blocks(attn, G):
         attn.ctx.check(attn.lib.cwk_ds_mask_candidates(attn.ctx.h, dp(d), dp(c2), n))
         m = d.cpu().numpy()
         assert np.array_equal(m[want == 1], s2[want == 1]) and np.all(np.isneginf(m[want == 0]))
+
+
+@pytest.mark.parametrize("name", ["plain", "yarn"])
+def test_output_unrotation_equals_the_oracle(attn, G, name):
+    """64 heads x 512 values, rope on the last 64: bf16 rounding, inverse rotation, rounding (bit-exact)."""
+    o = orc.oracle()
+    freq = np.ascontiguousarray(G["freq_" + name])
+    for rows, n in ((64, 512), (5, 128)):
+        for pos in (0, 9, 4095, 1048575):
+            x = (synth.normal(SEED, 830 + pos % 89, rows * n) * 2).astype(np.float32)
+            want = x.copy()
+            o.orc_ds_out_unrope(P(want, f32p), rows, n, P(freq, f32p), freq.size, pos)
+            t = cu(x.reshape(rows, n))
+            attn.ctx.check(attn.lib.cwk_ds_out_unrope(attn.ctx.h, dp(t), rows, n, hostf(freq), freq.size, pos))
+            attn.ctx.sync()
+            assert np.array_equal(t.cpu().numpy().reshape(-1), want), (rows, n, pos)

@@ -117,3 +117,16 @@ def test_row_finishing_is_the_composition(G):
         else:
             o.orc_ds_qdq_fp4_e4m3(P(flat, f32p), flat.size, blk)
         assert same_bits(a.reshape(-1), flat)
+
+
+@pytest.mark.parametrize("name", ["plain", "yarn"])
+def test_output_unrotation_identical(G, name):
+    """orc_ds_out_unrope = bf16 rounding, the reference's ds_rope(inverse = 1), bf16 rounding."""
+    o = orc.oracle()
+    f = np.ascontiguousarray(G["freq_" + name])
+    t = G["unrope_in_" + name].copy()
+    for i, p in enumerate(G["rope_pos"]):
+        row = t[i].copy()
+        o.orc_ds_out_unrope(P(row, f32p), 1, 64, P(f, f32p), f.size, int(p))
+        t[i] = row
+    assert same_bits(t, G["unrope_out_" + name])
