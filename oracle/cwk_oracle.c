@@ -1179,3 +1179,92 @@ ORC_API void orc_ds_out_unrope(float *o, int rows, int n, const float *freq, int
         for (int i = 0; i < 2 * npairs; i++) t[i] = orc_bf16_round(t[i]);
     }
 }
+
+/* ------------------------------------------------------------------ */
+/* KDA (gated delta-rule linear attention) decode step                 */
+/* ------------------------------------------------------------------ */
+
+/* Everything of cwick_attention_kda_decode between its projections and o_proj
+ * (src/attention.c:1243-1417), for one token of one layer, given the projected
+ * inputs: q, k, v [nh*hd] (= q/k/v_proj x; overwritten with the conv + SiLU +
+ * normalised values), gate_raw (= fb_proj f_a), beta_raw (= b_proj x), gate
+ * (= gb_proj g_a). Short convolution over a 3-deep window of projected values
+ * with SiLU (:1253-1281), per-head L2 norm of q and k, q also / sqrt(hd)
+ * (:1285-1301), decay lower * sigmoid(exp(a_log[h]) * (gate_raw + dt_bias))
+ * (:1314-1320), beta = sigmoid (:1339-1342), per head: state rows scaled by
+ * exp(decay), delta = v - k.state, state += outer(beta k, delta),
+ * core = q.state (:1352-1396), then RMS norm of core per head times o_norm
+ * times sigmoid(gate) (:1406-1417). conv: [3][nh*hd][3], rec: [nh][hd][hd],
+ * both updated in place. */
+ORC_API void orc_kda_step(int nh, int hd, float lower, float rms_eps, float *q, float *k, float *v,
+                          const uint16_t *q_conv, const uint16_t *k_conv, const uint16_t *v_conv,
+                          float *conv, const float *gate_raw, const float *dt_bias, const float *a_log,
+                          const float *beta_raw, const float *gate, const uint16_t *o_norm, float *rec,
+                          float *core) {
+    const int64_t proj = (int64_t)nh * hd;
+    const float eps = 1.0e-5f;
+    float *ins[3] = {q, k, v};
+    const uint16_t *cw[3] = {q_conv, k_conv, v_conv};
+    for (int w = 0; w < 3; w++) {
+        for (int64_t i = 0; i < proj; i++) {
+            float *s = conv + (size_t)w * proj * 3 + i * 3;
+            const uint16_t *c = cw[w] + i * 4;
+            float acc = s[0] * bf16f(c[0]) + s[1] * bf16f(c[1]) + s[2] * bf16f(c[2]) + ins[w][i] * bf16f(c[3]);
+            float p = ins[w][i];
+            ins[w][i] = acc * (1.0f / (1.0f + expf(-acc)));
+            s[0] = s[1]; s[1] = s[2]; s[2] = p;
+        }
+    }
+    for (int h = 0; h < nh; h++) {
+        float *qr = q + (size_t)h * hd, *kr = k + (size_t)h * hd;
+        double qn = 0.0, kn = 0.0;
+        for (int j = 0; j < hd; j++) {
+            qn += (double)qr[j] * qr[j];
+            kn += (double)kr[j] * kr[j];
+        }
+        float qinv = 1.0f / (float)(sqrt(qn) < eps ? eps : sqrt(qn));
+        float kinv = 1.0f / (float)(sqrt(kn) < eps ? eps : sqrt(kn));
+        for (int j = 0; j < hd; j++) {
+            qr[j] = qr[j] * qinv / sqrtf((float)hd);
+            kr[j] = kr[j] * kinv;
+        }
+    }
+    float *gd = malloc(sizeof(float) * (size_t)proj);
+    float *delta = malloc(sizeof(float) * (size_t)hd);
+    for (int64_t i = 0; i < proj; i++) {
+        float raw = gate_raw[i] + dt_bias[i];
+        float sg = 1.0f / (1.0f + expf(-expf(a_log[i / hd]) * raw));
+        gd[i] = lower * sg;
+    }
+    for (int h = 0; h < nh; h++) {
+        const float *qr = q + (size_t)h * hd, *kr = k + (size_t)h * hd, *vr = v + (size_t)h * hd;
+        const float *g = gd + (size_t)h * hd;
+        const float b = 1.0f / (1.0f + expf(-beta_raw[h]));
+        float *r = rec + (size_t)h * hd * hd, *o = core + (size_t)h * hd;
+        for (int kk = 0; kk < hd; kk++) {
+            float e = expf(g[kk]);
+            for (int vv = 0; vv < hd; vv++) r[(size_t)kk * hd + vv] *= e;
+        }
+        memcpy(delta, vr, sizeof(float) * (size_t)hd);
+        for (int kk = 0; kk < hd; kk++)
+            for (int vv = 0; vv < hd; vv++) delta[vv] -= kr[kk] * r[(size_t)kk * hd + vv];
+        for (int kk = 0; kk < hd; kk++) {
+            float c = b * kr[kk];
+            for (int vv = 0; vv < hd; vv++) r[(size_t)kk * hd + vv] += c * delta[vv];
+        }
+        memset(o, 0, sizeof(float) * (size_t)hd);
+        for (int kk = 0; kk < hd; kk++)
+            for (int vv = 0; vv < hd; vv++) o[vv] += qr[kk] * r[(size_t)kk * hd + vv];
+    }
+    for (int h = 0; h < nh; h++) {
+        float *o = core + (size_t)h * hd;
+        double ss = 0.0;
+        for (int j = 0; j < hd; j++) ss += (double)o[j] * o[j];
+        float inv = 1.0f / (float)sqrt(ss / (double)hd + (double)rms_eps);
+        for (int j = 0; j < hd; j++) {
+            float sg = 1.0f / (1.0f + expf(-gate[(size_t)h * hd + j]));
+            o[j] = o[j] * inv * bf16f(o_norm[j]) * sg;
+        }
+    }
+    free(gd); free(delta);
+}

@@ -133,3 +133,43 @@ int refdrv_mla_latent_indexed(int64_t H, int nh, int nope, int vdim, int64_t q_l
     free(st.q); free(st.wt); free(st.sc); free(st.sc2);
     return np;
 }
+
+/* One KDA (linear attention) decode step through cwick_attention_kda_decode.
+ * All weights bf16 except a_log [nh] and dt_bias [nh*hd] (f32). rec is the
+ * layer's [nh][hd][hd] state, conv its [3][nh*hd][3] window; both are updated
+ * in place (layer index 0). With selection matrices as projections a test can
+ * feed the reference arbitrary projected inputs and read the gated, normed core
+ * back through an identity o_proj. */
+void refdrv_kda_layer(int64_t H, int nh, int hd, float lower, float rms_eps,
+                      const void *q_proj, const void *k_proj, const void *v_proj,
+                      const void *q_conv, const void *k_conv, const void *v_conv,
+                      const float *a_log, const float *dt_bias, const void *o_norm,
+                      const void *fa_proj, const void *fb_proj, const void *b_proj,
+                      const void *ga_proj, const void *gb_proj, const void *o_proj,
+                      float *rec, float *conv, const float *x, float *out) {
+    cwick_model_spec s;
+    cwick_tensor tq, tk, tv, tqc, tkc, tvc, tal, tdt, ton, tfa, tfb, tb, tga, tgb, to;
+    const int64_t proj = (int64_t)nh * hd;
+    memset(&s, 0, sizeof(s));
+    s.hidden_size = H; s.linear_num_heads = nh; s.linear_head_dim = hd;
+    s.short_conv_kernel_size = 4; s.gate_lower_bound = lower; s.rms_norm_eps_f = rms_eps;
+    tensor_bf16(&tq, proj, H, q_proj);
+    tensor_bf16(&tk, proj, H, k_proj);
+    tensor_bf16(&tv, proj, H, v_proj);
+    tensor_bf16(&tqc, proj, 4, q_conv);
+    tensor_bf16(&tkc, proj, 4, k_conv);
+    tensor_bf16(&tvc, proj, 4, v_conv);
+    memset(&tal, 0, sizeof(tal));
+    tal.rows = 1; tal.cols = nh; tal.kind = CWICK_WEIGHT_F32; tal.data = a_log; tal.data_bytes = (size_t)nh * 4;
+    memset(&tdt, 0, sizeof(tdt));
+    tdt.rows = 1; tdt.cols = proj; tdt.kind = CWICK_WEIGHT_F32; tdt.data = dt_bias; tdt.data_bytes = (size_t)proj * 4;
+    tensor_bf16(&ton, 1, hd, o_norm);
+    tensor_bf16(&tfa, hd, H, fa_proj);
+    tensor_bf16(&tfb, proj, hd, fb_proj);
+    tensor_bf16(&tb, nh, H, b_proj);
+    tensor_bf16(&tga, hd, H, ga_proj);
+    tensor_bf16(&tgb, proj, hd, gb_proj);
+    tensor_bf16(&to, H, proj, o_proj);
+    cwick_attention_kda_decode(&s, &tq, &tk, &tv, &tqc, &tkc, &tvc, &tal, &tdt, &ton, &tfa, &tfb, &tb,
+                               &tga, &tgb, &to, rec, conv, 0, x, out, NULL);
+}
