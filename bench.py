@@ -356,7 +356,8 @@ def run_ours(args):
             except Exception as e:  # noqa: BLE001
                 extra["c5a_64x32768"] = {"error": str(e)[:200]}
             for name, fn in (("c1_gqa_decode_4096", side_gqa_decode), ("c3_mla_prefill_4096", side_prefill),
-                             ("c4_dsa_8x65536_top2048", side_dsa)):
+                             ("c4_dsa_8x65536_top2048", side_dsa),
+                             ("kda_decode_step_64x128", side_kda)):
                 try:
                     torch.cuda.empty_cache()
                     extra[name] = fn(attn, dev, stream, peak)
@@ -572,6 +573,41 @@ def side_prefill(attn, dev, stream, peak):
                             "note": "after the attention: cwk_mla_unabsorb then cwk_fp8_linear (8192 -> 4096); not in ms_per_prefill"}}
 
 
+def side_kda(attn, dev, stream, peak):
+    """KDA linear-attention decode step (not a BASELINE config; the layers next to the MLA ones): 64 heads of
+    128, 1 and 64 slots; the traffic is the [hd][hd] state of every head, read and written once."""
+    import torch
+    from cwick_b200 import lib as cl
+    g = torch.Generator(device=dev).manual_seed(14)
+    nh, hd = 64, 128
+    proj = nh * hd
+    out = {}
+    for B, rot in ((1, 40), (64, 2)):                   # rot distinct state sets: > L2 between revisits
+        w = [(0.5 * torch.randn(proj, 4, device=dev, generator=g)).to(torch.bfloat16) for _ in range(3)]
+        a_log = 0.5 * torch.randn(nh, device=dev, generator=g)
+        dt = 0.5 * torch.randn(proj, device=dev, generator=g)
+        on = torch.ones(hd, device=dev, dtype=torch.bfloat16)
+        ins = [torch.randn(B, nh if i == 4 else proj, device=dev, generator=g) for i in range(6)]
+        recs = [0.1 * torch.randn(B, nh, hd, hd, device=dev, generator=g) for _ in range(rot)]
+        convs = [torch.zeros(B, 3, proj, 3, device=dev) for _ in range(rot)]
+        core = torch.empty(B, proj, device=dev)
+        it = [0]
+        p = lambda t: cl.vp(t.data_ptr())  # noqa: E731
+
+        def call():
+            r = it[0] % rot
+            it[0] += 1
+            attn.ctx.check(attn.lib.cwk_kda_step(attn.ctx.h, B, nh, hd, -5.0, 1e-6, p(ins[0]), p(ins[1]), p(ins[2]), p(w[0]), p(w[1]), p(w[2]),
+                                                 p(convs[r]), p(ins[3]), p(dt), p(a_log), p(ins[4]), p(ins[5]), p(on), p(recs[r]), p(core)))
+        ms, k_ms, _ = _time_calls(attn, stream, call, n=40, warm=3)
+        by = B * nh * hd * hd * 4 * 2
+        out["slots_%d" % B] = {"us_per_step": ms * 1e3, "kernel_us": k_ms * 1e3, "state_bytes": by,
+                               "kernel_gbs": by / (k_ms / 1e3) / 1e9, "kernel_frac_of_measured_peak": by / (k_ms / 1e3) / 1e9 / peak}
+        del recs, convs
+        torch.cuda.empty_cache()
+    return out
+
+
 def side_dsa(attn, dev, stream, peak):
     """Config 4: DSA sparse decode, 8 sequences x 65536 cached tokens, 64x128 indexer heads over FP8
     keys, top 2048, gathered MLA attention."""
@@ -626,7 +662,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="c5b: how partial records travel")
-    ap.add_argument("--extra-only", default=None, choices=["c1", "c3", "c4", "c5a"],
+    ap.add_argument("--extra-only", default=None, choices=["c1", "c3", "c4", "c5a", "kda"],
                     help="run one side measurement alone and print its JSON (for profiling that kernel)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline")
     args = ap.parse_args()
@@ -640,7 +676,7 @@ def main():
         torch.cuda.set_stream(stream)
         attn = Attn(0)
         peak, _ = peaks()
-        fn = {"c1": side_gqa_decode, "c3": side_prefill, "c4": side_dsa,
+        fn = {"c1": side_gqa_decode, "c3": side_prefill, "c4": side_dsa, "kda": side_kda,
               "c5a": lambda a, d, s_, p_: side_measure(a, d, s_, 64, 32768, p_)}[args.extra_only]
         print(json.dumps({args.extra_only: fn(attn, dev, stream, peak)}))
     elif args.impl == "reference":

@@ -293,6 +293,28 @@ CWK_API int cwk_ds_lin_q(cwk_ctx *ctx, const float *x, const void *w, const void
  * o_proj (cwk_fp8_linear for an FP8 o_proj). 16-byte aligned buffers; latent 512 and vdim 128 only. */
 CWK_API int cwk_mla_unabsorb(cwk_ctx *ctx, const void *attn, const void *Wv, int64_t w_head_rows, int n, int nh, void *out);
 
+/* ---- KDA (gated delta-rule linear attention) decode step ---------------------------
+ * Everything of cwick_attention_kda_decode between its projections and o_proj (src/attention.c:1243-1417), for
+ * B engine slots in one launch: short convolution + SiLU over the 3-deep window of projected values, per-head
+ * L2 norm of q and k, the gated decay, the delta-rule update of the [hd][hd] state of every head and the gated
+ * RMS norm of the result. All device pointers:
+ *   q, k, v        f32 [B][nh*hd]   q_proj x, k_proj x, v_proj x        (:1230-1232)
+ *   q/k/v_conv     bf16 [nh*hd][4]
+ *   conv           f32 [B][3][nh*hd][3]   the layer's window, updated   (:1249-1252)
+ *   gate_raw       f32 [B][nh*hd]   fb_proj (fa_proj x)                 (:1313)
+ *   dt_bias f32 [nh*hd], a_log f32 [nh]  (cwick_tensor_value of the checkpoint's tensors)
+ *   beta_raw       f32 [B][nh]      b_proj x                            (:1339)
+ *   gate           f32 [B][nh*hd]   gb_proj (ga_proj x)                 (:1408)
+ *   o_norm         bf16 [hd]
+ *   rec            f32 [B][nh][hd][hd]   the layer's state, updated     (:1351)
+ *   core           f32 [B][nh*hd]   the input of o_proj                 (:1420)
+ * lower = spec->gate_lower_bound, rms_eps = spec->rms_norm_eps_f. hd 32, 64 or 128. Operation order is the
+ * reference's; results differ from it only where the C library's expf and a rounded double exp differ. */
+CWK_API int cwk_kda_step(cwk_ctx *ctx, int B, int nh, int hd, float lower, float rms_eps, const float *q, const float *k,
+                         const float *v, const void *q_conv, const void *k_conv, const void *v_conv, float *conv,
+                         const float *gate_raw, const float *dt_bias, const float *a_log, const float *beta_raw,
+                         const float *gate, const void *o_norm, float *rec, float *core);
+
 /* ---- DeepSeek-V4 compressor and candidate blocks -----------------------------------
  * The pieces of ds_compress (src/ds_model.c:1002-1077) and of the two-level selection of ds_indexer
  * (:1091-1096, :1126-1149) around its projections, which are plain GEMVs (cwk_ds_lin_q and bf16 ones).
