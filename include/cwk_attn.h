@@ -293,6 +293,19 @@ CWK_API int cwk_ds_lin_q(cwk_ctx *ctx, const float *x, const void *w, const void
  * o_proj (cwk_fp8_linear for an FP8 o_proj). 16-byte aligned buffers; latent 512 and vdim 128 only. */
 CWK_API int cwk_mla_unabsorb(cwk_ctx *ctx, const void *attn, const void *Wv, int64_t w_head_rows, int n, int nh, void *out);
 
+/* ---- Device caches in the reference's prefix-state layouts -------------------------
+ * cwick_prefix_state.keys holds a prefix as f32 rows [nslots][pos][lat_stride] (src/pfx.h:40-60; src/pfx.c:561,
+ * :681); the Qwen3.5 snapshot holds bf16 K and V rows per layer (q35_prefix_pack / _apply,
+ * src/q35_model.c:591-665). cache: device bf16 rows of `width` values, `ld` apart; host buffers may be pageable.
+ * export_f32: out_host[r][c] = f32(cache[r][c]) (exact). import_f32: cache[r][c] = bf16(in_host[r][c]) with
+ * rounding 1 = the reference's cache-row write (cwick_f32_to_bf16, src/util.c:202-210, as used at
+ * src/attention.c:703-705), 0 = round to nearest even (q35_narrow_rows, src/q35_model.c:1558-1575).
+ * copy_bf16: packed bf16 host rows <-> the cache's strided rows (to_device != 0: host -> cache). */
+CWK_API int cwk_cache_export_f32(cwk_ctx *ctx, const void *cache, int64_t ld, int64_t rows, int width, float *out_host);
+CWK_API int cwk_cache_import_f32(cwk_ctx *ctx, const float *in_host, int64_t rows, int width, void *cache, int64_t ld,
+                                 int rounding);
+CWK_API int cwk_cache_copy_bf16(cwk_ctx *ctx, int to_device, void *host, void *cache, int64_t ld, int64_t rows, int width);
+
 /* ---- KDA (gated delta-rule linear attention) decode step ---------------------------
  * Everything of cwick_attention_kda_decode between its projections and o_proj (src/attention.c:1243-1417), for
  * B engine slots in one launch: short convolution + SiLU over the 3-deep window of projected values, per-head
