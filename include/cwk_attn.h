@@ -328,6 +328,21 @@ CWK_API int cwk_kda_step(cwk_ctx *ctx, int B, int nh, int hd, float lower, float
                          const float *gate_raw, const float *dt_bias, const float *a_log, const float *beta_raw,
                          const float *gate, const void *o_norm, float *rec, float *core);
 
+/* ---- Gated DeltaNet scan (Qwen3.5 linear-attention layers) ------------------------
+ * lin_rec_heads (src/q35_model.c:1177-1264) for n positions of B slots: per value head the decayed delta-rule
+ * update of its [head_v][head_k] state and the gated RMS norm of its output. All device pointers:
+ *   up    f32 [B][n][2*key_dim + val_dim]  q heads | k heads | v heads after the convolution, SiLU and the q/k
+ *                                          normalisation (:1286-1372); key_dim = nh/kv_group*head_k, val_dim = nh*head_v
+ *   gdec, beta  f32 [B][n][nh]   the raw decay and write inputs (w_a x, w_b x, :1281-1284)
+ *   gate  f32 [B][n][val_dim]    w_z x
+ *   a_log, dt_bias f32 [nh], norm f32 [head_v]
+ *   S     f32 [B][nh][head_v][head_k]  the layer's state, updated
+ *   out   f32 [B][n][val_dim]    the input of out_proj
+ * head_k 64 or 128, head_v a multiple of 32 up to 128. Positions are processed in order (a scan). */
+CWK_API int cwk_gdn_scan(cwk_ctx *ctx, int B, int n, int nh, int head_k, int head_v, int kv_group, const float *up,
+                         const float *gdec, const float *beta, const float *gate, const float *a_log, const float *dt_bias,
+                         const float *norm, float rms_eps, float *S, float *out);
+
 /* ---- DeepSeek-V4 compressor and candidate blocks -----------------------------------
  * The pieces of ds_compress (src/ds_model.c:1002-1077) and of the two-level selection of ds_indexer
  * (:1091-1096, :1126-1149) around its projections, which are plain GEMVs (cwk_ds_lin_q and bf16 ones).

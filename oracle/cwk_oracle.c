@@ -1268,3 +1268,60 @@ ORC_API void orc_kda_step(int nh, int hd, float lower, float rms_eps, float *q, 
     }
     free(gd); free(delta);
 }
+
+/* ------------------------------------------------------------------ */
+/* Gated DeltaNet scan (Qwen3.5 linear-attention layers)               */
+/* ------------------------------------------------------------------ */
+
+/* The per-head delta-rule scan of lin_rec_heads (src/q35_model.c:1177-1264) over
+ * n positions: per value head vh (key head vh / kv_group), per position:
+ * g = -exp(a_log) softplus(araw + dt_bias), decay = exp(g), beta = sigmoid;
+ * per value row j of S [head_v][head_k]: the row is decayed and dotted with k in
+ * one pass, delta = beta (v_j - dot), then the row takes k delta and is dotted
+ * with q; the head's outputs go through the gated RMS norm (plain weight,
+ * silu of the gate). `up` rows are [q heads | k heads | v heads] after the
+ * convolution, SiLU and the q/k normalisation (:1286-1372). The reference's model
+ * file does not build off its own platform, so this restatement follows its text
+ * and is not checked against its execution: parity unpinned. */
+static float q35_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+static float q35_silu(float x) { return x / (1.0f + expf(-x)); }
+ORC_API void orc_gdn_scan(int n, int nh, int head_k, int head_v, int kv_group, const float *up,
+                          const float *gdec, const float *beta, const float *gate, const float *a_log,
+                          const float *dt_bias, const float *norm, float rms_eps, float *S, float *out) {
+    const int key_dim = (nh / kv_group) * head_k, val_dim = nh * head_v, qkv_dim = 2 * key_dim + val_dim;
+    float *tmp = malloc(sizeof(float) * (size_t)head_v);
+    for (int vh = 0; vh < nh; vh++) {
+        const int kh = vh / kv_group;
+        float *Sh = S + (size_t)vh * head_v * head_k;
+        for (int t = 0; t < n; t++) {
+            const float *row = up + (size_t)t * qkv_dim;
+            const float *qh = row + (size_t)kh * head_k, *kk = row + key_dim + (size_t)kh * head_k;
+            const float *vrow = row + 2 * key_dim + (size_t)vh * head_v;
+            const float g = -expf(a_log[vh]) * q35_softplus(gdec[(size_t)t * nh + vh] + dt_bias[vh]);
+            const float decay = expf(g);
+            const float bet = 1.0f / (1.0f + expf(-beta[(size_t)t * nh + vh]));
+            for (int j = 0; j < head_v; j++) {
+                float *sj = Sh + (size_t)j * head_k;
+                float dot = 0.0f;
+                for (int i = 0; i < head_k; i++) {
+                    sj[i] *= decay;
+                    dot += sj[i] * kk[i];
+                }
+                float delta = bet * (vrow[j] - dot);
+                float acc = 0.0f;
+                for (int i = 0; i < head_k; i++) {
+                    sj[i] += kk[i] * delta;
+                    acc += sj[i] * qh[i];
+                }
+                tmp[j] = acc;
+            }
+            float ss = 0.0f;
+            for (int j = 0; j < head_v; j++) ss += tmp[j] * tmp[j];
+            float rstd = 1.0f / sqrtf(ss / (float)head_v + rms_eps);
+            const float *z = gate + (size_t)t * val_dim + (size_t)vh * head_v;
+            float *o = out + (size_t)t * val_dim + (size_t)vh * head_v;
+            for (int j = 0; j < head_v; j++) o[j] = tmp[j] * rstd * norm[j] * q35_silu(z[j]);
+        }
+    }
+    free(tmp);
+}

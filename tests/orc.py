@@ -102,6 +102,7 @@ def oracle():
         L.orc_ds_out_unrope.argtypes = [f32p, C.c_int, C.c_int, f32p, C.c_int, C.c_int64]
         L.orc_kda_step.argtypes = [C.c_int, C.c_int, C.c_float, C.c_float, f32p, f32p, f32p, u16p, u16p, u16p, f32p, f32p, f32p,
                                    f32p, f32p, f32p, u16p, f32p, f32p]
+        L.orc_gdn_scan.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, f32p, f32p, f32p, f32p, C.c_float, f32p, f32p]
         L.orc_ds_candidates.restype = C.c_int
         L.orc_ds_candidates.argtypes = [f32p, C.c_int, C.c_int, C.c_int, u8p]
         _oracle = L
