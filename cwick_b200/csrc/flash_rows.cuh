@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
         const int j = t * TK + r;                   // position in the key list
         const bool valid = j < kmax_block;
         int64_t row = j;
-        if (MODE == MODE_MLA && p.sel != nullptr && valid) row = p.sel[(int64_t)b * p.sel_ld + j];
+        if ((MODE == MODE_MLA || MODE == MODE_GQA_DEC) && p.sel != nullptr && valid) row = p.sel[(int64_t)b * p.sel_ld + j];
         const uint16_t *ksrc = kbase + row * p.ld + head_off;
         for (int c = c0; c < KC; c += TPR)
             cp_async16(smem_u32(dK + r * (DK * 2) + ((c ^ (r & 7)) << 4)),

@@ -36,9 +36,10 @@ static int gqa_prefill_launch(cwk_ctx *ctx, const FlashRowsParams &p, int nblock
 
 extern "C" {
 
-int cwk_gqa_decode(cwk_ctx *ctx, const void *q, const void *K, const void *V, int64_t seq_stride,
-                   const int32_t *kv_len, int max_kv_len, int B, int nh, int nkv, int hd, float scale,
-                   void *out, int n_splits) {
+// sel != NULL: the keys of sequence b are rows sel[b*sel_ld + 0 .. kv_len[b]) of its cache, in that order.
+static int gqa_decode_impl(cwk_ctx *ctx, const void *q, const void *K, const void *V, int64_t seq_stride,
+                           const int32_t *kv_len, int max_kv_len, const int32_t *sel, int64_t sel_ld, int B, int nh, int nkv, int hd,
+                           float scale, void *out, int n_splits) {
     if (!ctx || !q || !K || !V || !kv_len || !out) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "gqa_decode: null argument");
     if (B <= 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || max_kv_len < 0)
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "gqa_decode: bad dimensions");
@@ -62,7 +63,7 @@ int cwk_gqa_decode(cwk_ctx *ctx, const void *q, const void *K, const void *V, in
     if (s != CWK_OK) return s;
     FlashRowsParams p{};
     p.q = (const uint16_t *)q; p.k = (const uint16_t *)K; p.v = (const uint16_t *)V;
-    p.seq_stride = seq_stride; p.ld = (int64_t)nkv * hd; p.kv_len = kv_len; p.sel = nullptr;
+    p.seq_stride = seq_stride; p.ld = (int64_t)nkv * hd; p.kv_len = kv_len; p.sel = sel; p.sel_ld = sel_ld;
     p.nh = nh; p.nkv = nkv; p.group = group; p.scale_log2 = scale * 1.4426950408889634f;
     p.partial = ctx->scratch; p.nsplit = ns; p.direct = 0;
     {
@@ -73,6 +74,19 @@ int cwk_gqa_decode(cwk_ctx *ctx, const void *q, const void *K, const void *V, in
     lse_combine_launch(ctx->stream, ctx->scratch, ns, nh, hd, B, (uint16_t *)out);
     CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel");
     return CWK_OK;
+}
+
+int cwk_gqa_decode(cwk_ctx *ctx, const void *q, const void *K, const void *V, int64_t seq_stride,
+                   const int32_t *kv_len, int max_kv_len, int B, int nh, int nkv, int hd, float scale,
+                   void *out, int n_splits) {
+    return gqa_decode_impl(ctx, q, K, V, seq_stride, kv_len, max_kv_len, nullptr, 0, B, nh, nkv, hd, scale, out, n_splits);
+}
+
+int cwk_gqa_decode_sel(cwk_ctx *ctx, const void *q, const void *K, const void *V, int64_t seq_stride,
+                       const int32_t *nsel, int max_nsel, const int32_t *sel, int64_t sel_ld, int B, int nh, int nkv, int hd,
+                       float scale, void *out, int n_splits) {
+    if (!sel || sel_ld < max_nsel) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "gqa_decode_sel: bad selection list");
+    return gqa_decode_impl(ctx, q, K, V, seq_stride, nsel, max_nsel, sel, sel_ld, B, nh, nkv, hd, scale, out, n_splits);
 }
 
 int cwk_gqa_prefill(cwk_ctx *ctx, const void *Q, const void *K, const void *V, int64_t pos, int n, int nh,

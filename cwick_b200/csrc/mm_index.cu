@@ -1,0 +1,133 @@
+// mm_index.cu -- the MiniMax block indexer: per-position index scores over bf16 keys and the selection of
+// blocks a query may attend to (src/mm_model.c:1733-1781). The attention over the selected positions is the
+// gathered GQA decode of csrc/gqa.cu (cwk_gqa_decode_sel).
+//   mm_index_scores_kernel   sc[s] = sum_h ReLU(q_h . k_s): one thread per key, heads in order, sequential f32
+//                            dots (the reference's order, so block maxima and ties are the reference's)
+//   mm_block_max_kernel      maximum of every block of `bs` scores (fmaxf from -1e30, partial last block included)
+//   mm_expand_blocks_kernel  the top blocks (exact top-k of csrc/dsa.cu, ascending) plus the block holding the next
+//                            position when it is missing, expanded to the list of positions (at most `cap`)
+#include "cwk_common.cuh"
+
+namespace {
+
+template <int ID>
+__global__ void __launch_bounds__(128) mm_index_scores_kernel(const uint16_t *keys, int64_t n, const float *q, int ih, float *sc) {
+    extern __shared__ float s_q[];                 // [ih][ID]
+    for (int i = threadIdx.x; i < ih * ID; i += blockDim.x) s_q[i] = q[i];
+    __syncthreads();
+    const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n) return;
+    float kf[ID];
+    const uint4 *kp = reinterpret_cast<const uint4 *>(keys + s * ID);
+#pragma unroll
+    for (int c = 0; c < ID / 8; c++) {
+        const uint4 v = kp[c];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            kf[c * 8 + 2 * t] = __uint_as_float(w[t] << 16);
+            kf[c * 8 + 2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
+        }
+    }
+    float tot = 0.f;
+    for (int h = 0; h < ih; h++) {
+        const float *qh = s_q + h * ID;
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < ID; i++) d = __fadd_rn(d, __fmul_rn(qh[i], kf[i]));
+        if (d > 0.f) tot = __fadd_rn(tot, d);
+    }
+    sc[s] = tot;
+}
+
+__global__ void mm_block_max_kernel(const float *sc, int64_t limit, int bs, float *bsc, int32_t *nblk_out) {
+    const int nblk = (int)((limit + bs - 1) / bs);
+    const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *nblk_out = nblk;
+    if (b >= nblk) return;
+    const int64_t s0 = (int64_t)b * bs, s1 = min((int64_t)limit, s0 + bs);
+    float mx = -1e30f;
+    for (int64_t t = s0 + lane; t < s1; t += 32) mx = fmaxf(mx, sc[t]);
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) bsc[b] = mx;
+}
+
+// One block. blk: the ascending top blocks (count in *cnt). Appends block limit / bs when it is not among them and
+// the list is shorter than topk + 4, then writes the positions of the blocks in list order, clipped to `limit` and
+// to `cap` entries; *nsel = number of positions, *nblk_sel = number of blocks.
+__global__ void __launch_bounds__(256) mm_expand_blocks_kernel(int32_t *blk, const int32_t *cnt, int64_t limit, int bs, int topk, int cap,
+                                                               int32_t *sel, int32_t *nsel, int32_t *nblk_sel) {
+    __shared__ int s_off[1024 + 8];
+    __shared__ int s_nb;
+    if (threadIdx.x == 0) {
+        int nb = *cnt;
+        const int last = (int)(limit / bs);
+        bool have = false;
+        for (int i = 0; i < nb; i++) have |= (blk[i] == last);
+        if (!have && nb < topk + 4) blk[nb++] = last;
+        int off = 0;
+        for (int i = 0; i < nb; i++) {
+            s_off[i] = off;
+            const int64_t s0 = (int64_t)blk[i] * bs;
+            const int64_t s1 = min(limit, s0 + bs);
+            off += (int)max((int64_t)0, s1 - s0);
+        }
+        s_off[nb] = off;
+        s_nb = nb;
+        *nsel = min(off, cap);
+        *nblk_sel = nb;
+    }
+    __syncthreads();
+    const int nb = s_nb;
+    for (int i = 0; i < nb; i++) {
+        const int64_t s0 = (int64_t)blk[i] * bs;
+        const int len = s_off[i + 1] - s_off[i];
+        for (int t = threadIdx.x; t < len; t += blockDim.x)
+            if (s_off[i] + t < cap) sel[s_off[i] + t] = (int32_t)(s0 + t);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int cwk_ds_topk(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int k, int32_t *out, int64_t out_ld,
+                int32_t *count);
+
+int cwk_mm_index_scores(cwk_ctx *ctx, const void *keys, int64_t n, int id, const float *q, int ih, float *sc) {
+    if (!ctx || !keys || !q || !sc || n < 0 || ih <= 0) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mm_index_scores: bad argument");
+    if (id != 64 && id != 128) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mm_index_scores is built for index dims 64 and 128 (got %d)", id);
+    if (reinterpret_cast<uintptr_t>(keys) & 15) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mm_index_scores: keys must be 16-byte aligned");
+    if ((size_t)ih * id * 4 > 48 * 1024) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mm_index_scores: too many index heads");
+    CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (n == 0) return CWK_OK;
+    CwkKernelTimer timer(ctx);
+    const unsigned grid = (unsigned)((n + 127) / 128);
+    if (id == 128) mm_index_scores_kernel<128><<<grid, 128, (size_t)ih * id * 4, ctx->stream>>>((const uint16_t *)keys, n, q, ih, sc);
+    else mm_index_scores_kernel<64><<<grid, 128, (size_t)ih * id * 4, ctx->stream>>>((const uint16_t *)keys, n, q, ih, sc);
+    CWK_LAUNCH_CHECK(ctx, "mm_index_scores_kernel");
+    return CWK_OK;
+}
+
+int cwk_mm_select_blocks(cwk_ctx *ctx, const float *sc, int64_t limit, int bs, int topk, int cap, int32_t *sel, int32_t *nsel,
+                         int32_t *blk_out, int32_t *nblk_out) {
+    if (!ctx || !sc || !sel || !nsel || limit <= 0 || bs <= 0 || topk <= 0 || topk + 4 > 1024 || cap <= 0)
+        return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mm_select_blocks: bad argument (topk <= 1020)");
+    CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int nblk = (int)((limit + bs - 1) / bs);
+    // work: block maxima [nblk + 1] | kept blocks [topk + 4] | block count | kept count | blocks selected
+    int s = cwk_reserve_work(ctx, ((size_t)nblk + 1 + topk + 4 + 3) * sizeof(float));
+    if (s != CWK_OK) return s;
+    float *bsc = (float *)ctx->work;
+    int32_t *blk = blk_out ? blk_out : (int32_t *)(bsc + nblk + 1);
+    int32_t *nb = (int32_t *)(bsc + nblk + 1) + topk + 4, *cnt = nb + 1, *nbs = nblk_out ? nblk_out : nb + 2;
+    mm_block_max_kernel<<<(nblk + 7) / 8, 256, 0, ctx->stream>>>(sc, limit, bs, bsc, nb);
+    CWK_LAUNCH_CHECK(ctx, "mm_block_max_kernel");
+    s = cwk_ds_topk(ctx, bsc, nblk, nb, 1, topk, blk, topk, cnt);
+    if (s != CWK_OK) return s;
+    mm_expand_blocks_kernel<<<1, 256, 0, ctx->stream>>>(blk, cnt, limit, bs, topk, cap, sel, nsel, nbs);
+    CWK_LAUNCH_CHECK(ctx, "mm_expand_blocks_kernel");
+    return CWK_OK;
+}
+
+}  // extern "C"

@@ -55,6 +55,9 @@ SIGNATURES = {
     "cwk_cache_import_f32": (i32, [vp, vp, i64, i32, vp, i64, i32]),
     "cwk_cache_copy_bf16": (i32, [vp, i32, vp, vp, i64, i64, i32]),
     "cwk_gdn_scan": (i32, [vp, i32, i32, i32, i32, i32, i32] + [vp] * 7 + [f32, vp, vp]),
+    "cwk_mm_index_scores": (i32, [vp, vp, i64, i32, vp, i32, vp]),
+    "cwk_mm_select_blocks": (i32, [vp, vp, i64, i32, i32, i32, vp, vp, vp, vp]),
+    "cwk_gqa_decode_sel": (i32, [vp, vp, vp, vp, i64, vp, i32, vp, i64, i32, i32, i32, i32, f32, vp, i32]),
     "cwk_kda_step": (i32, [vp, i32, i32, i32, f32, f32] + [vp] * 15),
     "cwk_ds_pool_norm": (i32, [vp, vp, vp, i32, i32, i32, vp, f32, vp]),
     "cwk_ds_rmsnorm_bf16w": (i32, [vp, vp, vp, i32, i32, f32, vp]),

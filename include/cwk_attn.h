@@ -229,6 +229,12 @@ CWK_API int cwk_gqa_decode(cwk_ctx *ctx, const void *q, const void *K, const voi
                    int64_t seq_stride, const int32_t *kv_len, int max_kv_len, int B, int nh,
                    int nkv, int hd, float scale, void *out, int n_splits);
 
+/* The same over a list of rows: the keys of sequence b are rows sel[b*sel_ld + 0 .. nsel[b]) of its cache, in that
+ * order (the attention over the positions of the selected blocks, src/mm_model.c:1978-2040). */
+CWK_API int cwk_gqa_decode_sel(cwk_ctx *ctx, const void *q, const void *K, const void *V, int64_t seq_stride,
+                   const int32_t *nsel, int max_nsel, const int32_t *sel, int64_t sel_ld, int B, int nh,
+                   int nkv, int hd, float scale, void *out, int n_splits);
+
 /* Causal prefill of n queries at positions pos..pos+n-1 against pos+n cached
  * rows. Replaces the per-(head, 128-query tile) QK^T / masked softmax / SV of
  * mixer_attn (src/q35_model.c:1713-1746).
@@ -342,6 +348,18 @@ CWK_API int cwk_kda_step(cwk_ctx *ctx, int B, int nh, int hd, float lower, float
 CWK_API int cwk_gdn_scan(cwk_ctx *ctx, int B, int n, int nh, int head_k, int head_v, int kv_group, const float *up,
                          const float *gdec, const float *beta, const float *gate, const float *a_log, const float *dt_bias,
                          const float *norm, float rms_eps, float *S, float *out);
+
+/* ---- MiniMax block indexer ----------------------------------------------------------
+ * Index scores of one query over bf16 index keys (mm_index_scores, src/mm_model.c:1765-1781):
+ * sc[s] = sum_h ReLU(q_h . k_s), keys bf16 [n][id] (16-byte aligned), q f32 [ih][id], id 64 or 128. */
+CWK_API int cwk_mm_index_scores(cwk_ctx *ctx, const void *keys, int64_t n, int id, const float *q, int ih, float *sc);
+/* Blocks and positions a query at position limit-1 attends to (mm_select_blocks, :1733-1762, and the expansion at
+ * :1968-1976): maxima of the blocks of bs scores, the best topk blocks (cwk_ds_topk's rule = mm_topk's heap up to
+ * exact ties), the block holding position `limit` appended when missing, positions of the blocks in that order
+ * clipped to limit and to cap entries (4096 in the reference). sel int32 [cap], nsel int32 [1]; blk_out (optional,
+ * int32 [topk + 4]) and nblk_out (optional) receive the block list. All device pointers. */
+CWK_API int cwk_mm_select_blocks(cwk_ctx *ctx, const float *sc, int64_t limit, int bs, int topk, int cap, int32_t *sel,
+                                 int32_t *nsel, int32_t *blk_out, int32_t *nblk_out);
 
 /* ---- DeepSeek-V4 compressor and candidate blocks -----------------------------------
  * The pieces of ds_compress (src/ds_model.c:1002-1077) and of the two-level selection of ds_indexer

@@ -1325,3 +1325,86 @@ ORC_API void orc_gdn_scan(int n, int nh, int head_k, int head_v, int kv_group, c
     }
     free(tmp);
 }
+
+/* ------------------------------------------------------------------ */
+/* MiniMax block indexer and attention over the selected blocks        */
+/* ------------------------------------------------------------------ */
+/* The reference's model file (src/mm_model.c) does not build off its own platform
+ * (unguarded NEON inside its forward function); these follow its text, scalar
+ * branches: parity unpinned. */
+
+/* Per-position index score: sum over heads of ReLU(q_h . k), bf16 keys,
+ * sequential f32 dots. src/mm_model.c:1765-1781 (mm_index_scores). */
+ORC_API void orc_mm_index_scores(const uint16_t *keys, int64_t n, int id, const float *q, int ih, float *sc) {
+    for (int64_t s = 0; s < n; s++) {
+        const uint16_t *k = keys + (size_t)s * id;
+        float tot = 0.0f;
+        for (int h = 0; h < ih; h++) {
+            const float *qh = q + (size_t)h * id;
+            float d = 0.0f;
+            for (int i = 0; i < id; i++) d += qh[i] * bf16f(k[i]);
+            if (d > 0.0f) tot += d;
+        }
+        sc[s] = tot;
+    }
+}
+
+/* Blocks a query at position limit-1 may attend to: block maxima (fmaxf from
+ * -1e30), the best `topk` by the heap rule of mm_topk (the same as ds_topk_scores,
+ * ascending), and the block holding position `limit` appended when it is missing.
+ * Returns the number of blocks. src/mm_model.c:1733-1762 (mm_select_blocks). */
+ORC_API int orc_mm_select_blocks(const float *sc, int64_t limit, int bs, int topk, int *blk_out) {
+    int64_t nblk = (limit + bs - 1) / bs;
+    float *bscore = calloc((size_t)nblk + 1, sizeof(float));
+    for (int64_t b = 0; b < nblk; b++) {
+        int64_t s0 = b * bs, s1 = s0 + bs;
+        if (s1 > limit) s1 = limit;
+        if (s0 >= s1) continue;
+        float best = -1e30f;
+        for (int64_t s = s0; s < s1; s++) best = fmaxf(best, sc[s]);
+        bscore[b] = best;
+    }
+    int nb = orc_ds_topk(bscore, (int)nblk, topk, blk_out);
+    int have_last = 0;
+    for (int i = 0; i < nb; i++)
+        if (blk_out[i] == (int)(limit / bs)) have_last = 1;
+    if (!have_last && nb < topk + 4) blk_out[nb++] = (int)(limit / bs);
+    free(bscore);
+    return nb;
+}
+
+/* Attention of one position over the selected positions, GQA layout, bf16 K/V rows
+ * of nkv*hd: score = (q_h . k) * qscale, max, expf, f32 sum in list order, weights
+ * divided by the sum, output = sum of weight * v in list order.
+ * src/mm_model.c:1983-2003 and the scalar branch :2034-2040. */
+ORC_API void orc_mm_sparse_attn(const float *q, const uint16_t *K, const uint16_t *V, const int64_t *selpos, int ns,
+                                int nh, int nkv, int hd, float qscale, float *out) {
+    const int kvd = nkv * hd;
+    float *sc = malloc(sizeof(float) * (size_t)(ns > 0 ? ns : 1));
+    for (int hh = 0; hh < nh; hh++) {
+        const float *qh = q + (size_t)hh * hd;
+        const size_t kvh = (size_t)(hh / (nh / nkv)) * hd;
+        float best = -1e30f;
+        for (int i = 0; i < ns; i++) {
+            const uint16_t *k = K + (size_t)selpos[i] * kvd + kvh;
+            float d = 0.0f;
+            for (int j = 0; j < hd; j++) d += qh[j] * bf16f(k[j]);
+            d *= qscale;
+            sc[i] = d;
+            if (d > best) best = d;
+        }
+        float sum = 0.0f;
+        for (int i = 0; i < ns; i++) {
+            sc[i] = expf(sc[i] - best);
+            sum += sc[i];
+        }
+        float *oh = out + (size_t)hh * hd;
+        for (int j = 0; j < hd; j++) oh[j] = 0.0f;
+        for (int i = 0; i < ns; i++) {
+            sc[i] /= sum;
+            const uint16_t *v = V + (size_t)selpos[i] * kvd + kvh;
+            for (int j = 0; j < hd; j++) oh[j] += sc[i] * bf16f(v[j]);
+        }
+    }
+    free(sc);
+}

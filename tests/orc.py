@@ -103,6 +103,10 @@ def oracle():
         L.orc_kda_step.argtypes = [C.c_int, C.c_int, C.c_float, C.c_float, f32p, f32p, f32p, u16p, u16p, u16p, f32p, f32p, f32p,
                                    f32p, f32p, f32p, u16p, f32p, f32p]
         L.orc_gdn_scan.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, f32p, f32p, f32p, f32p, C.c_float, f32p, f32p]
+        L.orc_mm_index_scores.argtypes = [u16p, C.c_int64, C.c_int, f32p, C.c_int, f32p]
+        L.orc_mm_select_blocks.restype = C.c_int
+        L.orc_mm_select_blocks.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, i32p]
+        L.orc_mm_sparse_attn.argtypes = [f32p, u16p, u16p, i64p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, f32p]
         L.orc_ds_candidates.restype = C.c_int
         L.orc_ds_candidates.argtypes = [f32p, C.c_int, C.c_int, C.c_int, u8p]
         _oracle = L
