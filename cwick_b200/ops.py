@@ -193,3 +193,50 @@ class Attn:
             self.ctx.h, _p(X), _p(Wqa), _p(Sqa), _p(Wqb), _p(Sqb), _p(Wkva), _p(Skva), _p(qa_norm), _p(kva_norm),
             _p(Wuk), _p(cache), pos0, n, H, q_lora, nh, nope, rope, kv_lora, eps, rope_base, scale, _p(out)))
         return out
+
+    # ---- linear-attention layers and the sparse variants next to the MLA path ------------
+    def kda_step(self, q, k, v, q_conv, k_conv, v_conv, conv, gate_raw, dt_bias, a_log, beta_raw, gate, o_norm, rec,
+                 lower, rms_eps):
+        """One KDA decode step for B slots (cwk_kda_step): q, k, v, gate_raw, gate f32 [B][nh*hd]; beta_raw f32 [B][nh];
+        conv f32 [B][3][nh*hd][3] and rec f32 [B][nh][hd][hd] are updated in place. Returns core f32 [B][nh*hd]."""
+        B, nh, hd, _ = rec.shape
+        core = torch.empty(B, nh * hd, dtype=torch.float32, device=q.device)
+        self.ctx.check(self.lib.cwk_kda_step(self.ctx.h, B, nh, hd, lower, rms_eps, _p(q), _p(k), _p(v), _p(q_conv), _p(k_conv),
+                                             _p(v_conv), _p(conv), _p(gate_raw), _p(dt_bias), _p(a_log), _p(beta_raw), _p(gate),
+                                             _p(o_norm), _p(rec), _p(core)))
+        return core
+
+    def gdn_scan(self, up, gdec, beta, gate, a_log, dt_bias, norm, S, kv_group, rms_eps):
+        """Gated DeltaNet scan (cwk_gdn_scan): up f32 [B][n][2*key_dim + val_dim]; gdec, beta f32 [B][n][nh]; gate f32
+        [B][n][val_dim]; S f32 [B][nh][head_v][head_k] updated in place. Returns f32 [B][n][val_dim]."""
+        B, n, _ = up.shape
+        _, nh, hv, hk = S.shape
+        out = torch.empty(B, n, nh * hv, dtype=torch.float32, device=up.device)
+        self.ctx.check(self.lib.cwk_gdn_scan(self.ctx.h, B, n, nh, hk, hv, kv_group, _p(up), _p(gdec), _p(beta), _p(gate), _p(a_log),
+                                             _p(dt_bias), _p(norm), rms_eps, _p(S), _p(out)))
+        return out
+
+    def mm_select(self, index_keys, iq, limit, block_size, topk_blocks, cap=4096):
+        """MiniMax indexer for one query: index scores over bf16 keys [rows][id] (the first `limit` rows), then the
+        positions of the selected blocks. Returns (sel int32 [cap], nsel int32 [1])."""
+        _bf16(index_keys)
+        ih, idim = iq.shape
+        sc = torch.empty(limit, dtype=torch.float32, device=iq.device)
+        self.ctx.check(self.lib.cwk_mm_index_scores(self.ctx.h, _p(index_keys), limit, idim, _p(iq), ih, _p(sc)))
+        sel = torch.full((cap,), -1, dtype=torch.int32, device=iq.device)
+        nsel = torch.zeros(1, dtype=torch.int32, device=iq.device)
+        self.ctx.check(self.lib.cwk_mm_select_blocks(self.ctx.h, _p(sc), limit, block_size, topk_blocks, cap, _p(sel), _p(nsel), None, None))
+        return sel, nsel
+
+    def gqa_decode_sel(self, q, K, V, sel, nsel, max_nsel, scale=None, n_splits=0):
+        """GQA decode over the rows sel[b][0:nsel[b]] of each sequence's cache (cwk_gqa_decode_sel)."""
+        _bf16(q), _bf16(K), _bf16(V)
+        B, nh, hd = q.shape
+        T, nkv = K.shape[1], K.shape[2]
+        if scale is None:
+            scale = 1.0 / math.sqrt(hd)
+        out = torch.empty_like(q)
+        self.ctx.check(self.lib.cwk_gqa_decode_sel(self.ctx.h, _p(q), _p(K), _p(V), T * nkv * hd, _p(nsel), max_nsel, _p(sel),
+                                                   sel.shape[-1], B, nh, nkv, hd, scale, _p(out), n_splits))
+        return out
+
