@@ -8,6 +8,7 @@
 #include <cstdlib>
 #include <map>
 #include <mutex>
+#include <vector>
 #include <unordered_map>
 
 #include "../../include/cwick_compat.h"
@@ -247,6 +248,143 @@ void cwick_attention_mla_decode(const cwkc_model_spec *spec, const cwkc_tensor *
     memcpy(out, p_out, (size_t)H * 4);
     memcpy(host_layer + (size_t)pos * kv_lora, p_row, (size_t)kv_lora * 2);     // the caller's array stays the source of truth
     cm.next_pos = pos + 1;
+}
+
+
+// cwick_attention_kda_decode (src/attention.c:1176-1437) on the GPU: the six projections of x, the two second-stage
+// gates, cwk_kda_step, o_proj. The signature leaves the layer's recurrent state and convolution window with the caller
+// and says nothing about when the caller rewrites them (a new sequence zeroes them, a prefix restore replaces them),
+// so both travel to the device and back on every call: correct for any caller, and dominated by that traffic
+// (4 MB each way at 64 heads of 128). A caller that keeps the state on the device calls cwk_kda_step itself.
+extern "C" int cwk_kda_step(cwk_ctx *ctx, int B, int nh, int hd, float lower, float rms_eps, const float *q, const float *k,
+                            const float *v, const void *q_conv, const void *k_conv, const void *v_conv, float *conv,
+                            const float *gate_raw, const float *dt_bias, const float *a_log, const float *beta_raw,
+                            const float *gate, const void *o_norm, float *rec, float *core);
+
+static float tensor_value(const cwkc_tensor *t, int64_t i) {       // cwick_tensor_value, src/tensor.c:767-774
+    if (t->kind == CWKC_WEIGHT_BF16) {
+        const uint32_t u = (uint32_t)((const uint16_t *)t->data)[i] << 16;
+        float f;
+        memcpy(&f, &u, 4);
+        return f;
+    }
+    return t->kind == CWKC_WEIGHT_F32 ? ((const float *)t->data)[i] : 0.0f;
+}
+
+void cwick_attention_kda_decode(const cwkc_model_spec *spec, const cwkc_tensor *q_proj, const cwkc_tensor *k_proj,
+                                const cwkc_tensor *v_proj, const cwkc_tensor *q_conv, const cwkc_tensor *k_conv,
+                                const cwkc_tensor *v_conv, const cwkc_tensor *a_log, const cwkc_tensor *dt_bias,
+                                const cwkc_tensor *o_norm, const cwkc_tensor *fa_proj, const cwkc_tensor *fb_proj,
+                                const cwkc_tensor *b_proj, const cwkc_tensor *ga_proj, const cwkc_tensor *gb_proj,
+                                const cwkc_tensor *o_proj, float *rec, float *conv, int64_t layer, const float *x, float *out,
+                                cwkc_error *err) {
+    const cwkc_tensor *ws[] = {q_proj, k_proj, v_proj, fa_proj, b_proj, ga_proj, fb_proj, gb_proj, o_proj, q_conv, k_conv, v_conv, o_norm};
+    if (!spec || !a_log || !dt_bias || !rec || !conv || !x || !out || layer < 0)
+        return set_err(err, CWK_ERR_ARGUMENT, "cwick_attention_kda_decode: bad argument");
+    for (const cwkc_tensor *t : ws) {
+        if (!t || !t->data) return set_err(err, CWK_ERR_ARGUMENT, "cwick_attention_kda_decode: missing tensor");
+        if (t->kind != CWKC_WEIGHT_BF16) return set_err(err, CWK_ERR_UNSUPPORTED, "only BF16 weights are handled here");
+    }
+    const int64_t H = spec->hidden_size;
+    const int nh = (int)spec->linear_num_heads, hd = (int)spec->linear_head_dim;
+    const int64_t proj = (int64_t)nh * hd;
+    if (spec->short_conv_kernel_size != 4) return set_err(err, CWK_ERR_UNSUPPORTED, "short convolution width %lld not built (4)", (long long)spec->short_conv_kernel_size);
+    if ((hd != 32 && hd != 64 && hd != 128) || (H & 7)) return set_err(err, CWK_ERR_UNSUPPORTED, "KDA head dim %d / hidden %lld not built", hd, (long long)H);
+
+    std::lock_guard<std::mutex> lock(g.mu);
+    if (!g.ctx) {
+        const char *d = getenv("CWK_DEVICE");
+        if (cwk_ctx_create(d ? atoi(d) : 0, &g.ctx) != CWK_OK) return set_err(err, CWK_ERR_STATE, "no usable sm_100 GPU");
+    }
+    cwk_ctx *ctx = g.ctx;
+    cudaStream_t st = ctx->stream;
+    const uint16_t *d_w[13];
+    for (int i = 0; i < 13; i++)
+        if (!(d_w[i] = mirror_weight(ws[i]))) return set_err(err, CWK_ERR_MEMORY, "device mirror of a weight failed");
+    // floats: x[H] q k v gate_raw gate core [proj each] f_a g_a [hd each] beta a_log [nh each] dt[proj] out[H] rec conv
+    const size_t n_rec = (size_t)nh * hd * hd, n_conv = (size_t)3 * proj * 3;
+    const size_t nf = (size_t)H * 2 + (size_t)proj * 7 + (size_t)hd * 2 + (size_t)nh * 2 + n_rec + n_conv + 64;
+    if (nf * 4 > g.d_buf_bytes) {
+        if (g.d_buf) cudaFree(g.d_buf);
+        if (cudaMalloc(&g.d_buf, nf * 4) != cudaSuccess) { g.d_buf = nullptr; g.d_buf_bytes = 0; return set_err(err, CWK_ERR_MEMORY, "device scratch"); }
+        g.d_buf_bytes = nf * 4;
+    }
+    float *d_x = g.d_buf, *d_q = d_x + H, *d_k = d_q + proj, *d_v = d_k + proj, *d_graw = d_v + proj, *d_gate = d_graw + proj;
+    float *d_core = d_gate + proj, *d_dt = d_core + proj, *d_fa = d_dt + proj, *d_ga = d_fa + hd, *d_beta = d_ga + hd, *d_alog = d_beta + nh;
+    float *d_out = d_alog + nh;
+    float *d_rec = g.d_buf + ((((size_t)(d_out - g.d_buf) + (size_t)H) + 3) & ~(size_t)3), *d_conv = d_rec + n_rec;     // 16-byte aligned state
+    std::vector<float> small((size_t)nh + proj);
+    for (int h = 0; h < nh; h++) small[h] = tensor_value(a_log, h);
+    for (int64_t i = 0; i < proj; i++) small[nh + i] = tensor_value(dt_bias, i);
+    float *h_rec = rec + (size_t)layer * n_rec, *h_conv = conv + (size_t)layer * n_conv;
+    cudaMemcpyAsync(d_x, x, (size_t)H * 4, cudaMemcpyHostToDevice, st);
+    cudaMemcpyAsync(d_alog, small.data(), (size_t)nh * 4, cudaMemcpyHostToDevice, st);
+    cudaMemcpyAsync(d_dt, small.data() + nh, (size_t)proj * 4, cudaMemcpyHostToDevice, st);
+    cudaMemcpyAsync(d_rec, h_rec, n_rec * 4, cudaMemcpyHostToDevice, st);
+    cudaMemcpyAsync(d_conv, h_conv, n_conv * 4, cudaMemcpyHostToDevice, st);
+    const int P = (int)proj;
+    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[0], d_x, d_q, P, (int)H);
+    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[1], d_x, d_k, P, (int)H);
+    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[2], d_x, d_v, P, (int)H);
+    gemv_bf16_kernel<<<(hd + 7) / 8, 256, 0, st>>>(d_w[3], d_x, d_fa, hd, (int)H);
+    gemv_bf16_kernel<<<(nh + 7) / 8, 256, 0, st>>>(d_w[4], d_x, d_beta, nh, (int)H);
+    gemv_bf16_kernel<<<(hd + 7) / 8, 256, 0, st>>>(d_w[5], d_x, d_ga, hd, (int)H);
+    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[6], d_fa, d_graw, P, hd);
+    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[7], d_ga, d_gate, P, hd);
+    ctx->launches += 8;
+    int s = cwk_kda_step(ctx, 1, nh, hd, spec->gate_lower_bound, spec->rms_norm_eps_f, d_q, d_k, d_v, d_w[9], d_w[10], d_w[11], d_conv,
+                         d_graw, d_dt, d_alog, d_beta, d_gate, d_w[12], d_rec, d_core);
+    if (s != CWK_OK) return set_err(err, s, "%s", cwk_last_error(ctx));
+    gemv_bf16_kernel<<<(int)((H + 7) / 8), 256, 0, st>>>(d_w[8], d_core, d_out, (int)H, P);
+    ctx->launches += 1;
+    cudaMemcpyAsync(out, d_out, (size_t)H * 4, cudaMemcpyDeviceToHost, st);
+    cudaMemcpyAsync(h_rec, d_rec, n_rec * 4, cudaMemcpyDeviceToHost, st);
+    cudaMemcpyAsync(h_conv, d_conv, n_conv * 4, cudaMemcpyDeviceToHost, st);
+    if (cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess)
+        return set_err(err, CWK_ERR_CUDA, "GPU KDA decode failed: %s", cudaGetErrorString(cudaGetLastError()));
+}
+
+// ---- the rest of attention.c's link surface (src/cwick.h:864-938, src/prof.c:78-85) -------------------------
+// The phase timers prof.c reads; the GPU entry points do not split their time into these phases.
+uint64_t g_attn_proj_ns = 0, g_attn_conv_ns = 0, g_attn_gate_ns = 0, g_attn_rec_ns = 0, g_attn_mla_ns = 0, g_attn_tail_ns = 0;
+
+// src/attention.c:446-458: floats the engine reserves per KV slot for the indexer's pool, tails, selection and scratch.
+uint64_t cwick_indexer_bytes(const cwkc_model_spec *spec, int64_t capacity) {
+    const int64_t hd = spec->index_head_dim;
+    const int64_t kp = spec->index_kpool > 0 ? spec->index_kpool : 1;
+    const int64_t topk = spec->index_topk > 0 ? spec->index_topk : 0;
+    if (hd <= 0 || spec->index_n_heads <= 0) return 0;
+    const int64_t pools = capacity / kp + 2, sel = topk + kp + 2;
+    return (uint64_t)((pools * hd) + (2 * kp * hd) + sel + (spec->index_n_heads * hd) + spec->index_n_heads + 2 * pools) * sizeof(float);
+}
+
+// src/attention.c:460-468
+void cwick_indexer_reset(const cwkc_model_spec *spec, cwkc_indexer_state *st) {
+    if (!st) return;
+    const int64_t hd = spec->index_head_dim;
+    const int64_t kp = spec->index_kpool > 0 ? spec->index_kpool : 1;
+    if (hd > 0 && st->pool) {
+        memset(st->pool, 0, (size_t)st->pool_cap * (size_t)hd * sizeof(float));
+        memset(st->tail_k, 0, (size_t)kp * (size_t)hd * sizeof(float));
+        memset(st->tail_g, 0, (size_t)kp * (size_t)hd * sizeof(float));
+    }
+    st->n_pools = 0;
+}
+
+// The chunk path with host pointers is not taken over: the engine asks first (src/engine.c:2387-2414) and runs its
+// per-token loop through cwick_attention_mla_decode above when the answer is no; a device-resident caller uses
+// cwk_mla_prefill. The entry point itself answers CWICK_ERR_UNSUPPORTED, on which the caller falls back too
+// (src/engine.c:2415-2431).
+bool cwick_mla_chunk_supported(const cwkc_model_spec *, const cwkc_tensor *, const cwkc_tensor *, const cwkc_tensor *,
+                               const cwkc_tensor *, const cwkc_tensor *, const float *) {
+    return false;
+}
+int cwick_attention_mla_prefill_chunk(const cwkc_model_spec *, const cwkc_tensor *, const cwkc_tensor *, const cwkc_tensor *,
+                                      const cwkc_tensor *, const cwkc_tensor *, const cwkc_tensor *, const cwkc_tensor *, float *, float *,
+                                      int64_t, int64_t, int64_t, int64_t, const cwkc_indexer_weights *, cwkc_indexer_state *,
+                                      const float *, float *, cwkc_error *err) {
+    set_err(err, CWK_ERR_UNSUPPORTED, "the host-pointer chunk path is not taken over: per-token decode, or cwk_mla_prefill on device buffers");
+    return CWK_ERR_UNSUPPORTED;
 }
 
 }  // extern "C"

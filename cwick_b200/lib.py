@@ -72,7 +72,9 @@ SIGNATURES = {
 # reference-named entry points (include/cwick_compat.h); bound separately because their
 # arguments are the reference's structs
 COMPAT_SYMBOLS = ["cwick_attention_mla_decode", "cwick_mla_latent_enabled", "cwick_indexer_active",
-                  "cwick_latent_bf16_enabled", "cwick_latent_elem_bytes", "cwk_dropin_reset"]
+                  "cwick_latent_bf16_enabled", "cwick_latent_elem_bytes", "cwk_dropin_reset",
+                  "cwick_indexer_bytes", "cwick_indexer_reset", "cwick_mla_chunk_supported",
+                  "cwick_attention_mla_prefill_chunk", "cwick_attention_kda_decode"]
 
 _lib = None
 

@@ -114,6 +114,29 @@ CWK_API bool cwick_indexer_active(const cwkc_model_spec *spec, int64_t npos);
 CWK_API bool cwick_latent_bf16_enabled(void);
 CWK_API size_t cwick_latent_elem_bytes(void);
 /* Drop every device mirror (weights and caches) this process holds. */
+/* The rest of attention.c's link surface (src/cwick.h:864-938; src/prof.c:78-85 reads the six counters).
+ * cwick_attention_kda_decode computes the layer on the GPU (BF16 weights, convolution width 4, head dim 32/64/128);
+ * the layer's state and window stay with the caller, so they cross to the device and back on every call.
+ * The chunk path with host pointers is not taken over: cwick_mla_chunk_supported answers false and the entry point
+ * CWICK_ERR_UNSUPPORTED, on either of which the engine runs its per-token loop (src/engine.c:2387-2431). */
+CWK_API uint64_t cwick_indexer_bytes(const cwkc_model_spec *spec, int64_t capacity);
+CWK_API void cwick_indexer_reset(const cwkc_model_spec *spec, cwkc_indexer_state *st);
+CWK_API bool cwick_mla_chunk_supported(const cwkc_model_spec *spec, const cwkc_tensor *qa, const cwkc_tensor *qb,
+                                       const cwkc_tensor *kva, const cwkc_tensor *kvb, const cwkc_tensor *o, const float *values);
+CWK_API int cwick_attention_mla_prefill_chunk(const cwkc_model_spec *spec, const cwkc_tensor *qa, const cwkc_tensor *qb,
+                                              const cwkc_tensor *kva, const cwkc_tensor *kvb, const cwkc_tensor *o,
+                                              const cwkc_tensor *qa_n, const cwkc_tensor *kva_n, float *keys, float *values,
+                                              int64_t capacity, int64_t pos0, int64_t n, int64_t layer,
+                                              const cwkc_indexer_weights *idx_w, cwkc_indexer_state *idx, const float *X,
+                                              float *Out, cwkc_error *err);
+CWK_API void cwick_attention_kda_decode(const cwkc_model_spec *spec, const cwkc_tensor *q_proj, const cwkc_tensor *k_proj,
+                                        const cwkc_tensor *v_proj, const cwkc_tensor *q_conv, const cwkc_tensor *k_conv,
+                                        const cwkc_tensor *v_conv, const cwkc_tensor *a_log, const cwkc_tensor *dt_bias,
+                                        const cwkc_tensor *o_norm, const cwkc_tensor *fa_proj, const cwkc_tensor *fb_proj,
+                                        const cwkc_tensor *b_proj, const cwkc_tensor *ga_proj, const cwkc_tensor *gb_proj,
+                                        const cwkc_tensor *o_proj, float *rec, float *conv, int64_t layer, const float *x,
+                                        float *out, cwkc_error *err);
+CWK_API extern uint64_t g_attn_proj_ns, g_attn_conv_ns, g_attn_gate_ns, g_attn_rec_ns, g_attn_mla_ns, g_attn_tail_ns;
 CWK_API void cwk_dropin_reset(void);
 #endif /* CWICK_COMPAT_TYPES_ONLY */
 

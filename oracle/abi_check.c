@@ -27,6 +27,10 @@ SAME_OFF(cwick_model_spec, cwkc_model_spec, qk_nope_head_dim);
 SAME_OFF(cwick_model_spec, cwkc_model_spec, qk_rope_head_dim);
 SAME_OFF(cwick_model_spec, cwkc_model_spec, value_head_dim);
 SAME_OFF(cwick_model_spec, cwkc_model_spec, rms_norm_eps_f);
+SAME_OFF(cwick_model_spec, cwkc_model_spec, linear_num_heads);
+SAME_OFF(cwick_model_spec, cwkc_model_spec, linear_head_dim);
+SAME_OFF(cwick_model_spec, cwkc_model_spec, short_conv_kernel_size);
+SAME_OFF(cwick_model_spec, cwkc_model_spec, gate_lower_bound);
 SAME_OFF(cwick_model_spec, cwkc_model_spec, layers);
 SAME_OFF(cwick_model_spec, cwkc_model_spec, quant);
 SAME_OFF(cwick_model_spec, cwkc_model_spec, index_head_dim);
