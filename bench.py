@@ -367,7 +367,8 @@ def run_ours(args):
                 extra["c5a_64x32768"] = {"error": str(e)[:200]}
             for name, fn in (("c1_gqa_decode_4096", side_gqa_decode), ("c3_mla_prefill_4096", side_prefill),
                              ("c4_dsa_8x65536_top2048", side_dsa),
-                             ("kda_decode_step_64x128", side_kda)):
+                             ("kda_decode_step_64x128", side_kda),
+                             ("gdn_step_and_mm_indexer", side_gdn_mm)):
                 try:
                     torch.cuda.empty_cache()
                     extra[name] = fn(attn, dev, stream, peak)
@@ -618,6 +619,58 @@ def side_kda(attn, dev, stream, peak):
     return out
 
 
+def side_gdn_mm(attn, dev, stream, peak):
+    """The other rows next to the path (not BASELINE configs): Gated DeltaNet decode step (32 value heads of 128 x 128,
+    1 and 64 slots) and the MiniMax indexer (index scores over 65536 bf16 keys of 128, 4 heads; block selection)."""
+    import torch
+    from cwick_b200 import lib as cl
+    g = torch.Generator(device=dev).manual_seed(15)
+    p = lambda t: cl.vp(t.data_ptr())  # noqa: E731
+    out = {}
+    nh, hk, hv, grp = 32, 128, 128, 2
+    key_dim, val_dim = (nh // grp) * hk, nh * hv
+    a_log, dtb, norm = (0.5 * torch.randn(nh, device=dev, generator=g), 0.5 * torch.randn(nh, device=dev, generator=g),
+                        torch.ones(hv, device=dev))
+    for B, rot in ((1, 80), (64, 3)):
+        up = torch.randn(B, 1, 2 * key_dim + val_dim, device=dev, generator=g) * 0.1
+        gdec, beta = torch.randn(B, 1, nh, device=dev, generator=g), torch.randn(B, 1, nh, device=dev, generator=g)
+        gate = torch.randn(B, 1, val_dim, device=dev, generator=g)
+        S = [0.05 * torch.randn(B, nh, hv, hk, device=dev, generator=g) for _ in range(rot)]
+        o = torch.empty(B, 1, val_dim, device=dev)
+        it = [0]
+
+        def call():
+            r = it[0] % rot
+            it[0] += 1
+            attn.ctx.check(attn.lib.cwk_gdn_scan(attn.ctx.h, B, 1, nh, hk, hv, grp, p(up), p(gdec), p(beta), p(gate), p(a_log), p(dtb),
+                                                 p(norm), 1e-6, p(S[r]), p(o)))
+        ms, k_ms, _ = _time_calls(attn, stream, call, n=40, warm=3)
+        by = B * nh * hv * hk * 4 * 2
+        out["gdn_slots_%d" % B] = {"us_per_step": ms * 1e3, "kernel_us": k_ms * 1e3, "state_bytes": by,
+                                   "kernel_gbs": by / (k_ms / 1e3) / 1e9, "kernel_frac_of_measured_peak": by / (k_ms / 1e3) / 1e9 / peak}
+        del S
+        torch.cuda.empty_cache()
+    n, idim, ih = 65536, 128, 4
+    keys = [torch.randn(n, idim, device=dev, generator=g).to(torch.bfloat16) for _ in range(12)]      # 201 MB in rotation
+    iq = torch.randn(ih, idim, device=dev, generator=g)
+    sc = torch.empty(n, device=dev)
+    sel = torch.empty(4096, dtype=torch.int32, device=dev)
+    nsel = torch.zeros(1, dtype=torch.int32, device=dev)
+    it = [0]
+
+    def scores():
+        it[0] += 1
+        attn.ctx.check(attn.lib.cwk_mm_index_scores(attn.ctx.h, p(keys[it[0] % 12]), n, idim, p(iq), ih, p(sc)))
+    ms_s, k_s, _ = _time_calls(attn, stream, scores, n=24, warm=3)
+
+    def select():
+        attn.ctx.check(attn.lib.cwk_mm_select_blocks(attn.ctx.h, p(sc), n, 64, 16, 4096, p(sel), p(nsel), None, None))
+    ms_b, _, _ = _time_calls(attn, stream, select, n=24, warm=3)
+    out["mm_index_65536"] = {"scores_us": ms_s * 1e3, "scores_kernel_us": k_s * 1e3, "scores_gbs": n * idim * 2 / (k_s / 1e3) / 1e9,
+                             "scores_frac_of_measured_peak": n * idim * 2 / (k_s / 1e3) / 1e9 / peak, "select_blocks_us": ms_b * 1e3}
+    return out
+
+
 def side_dsa(attn, dev, stream, peak):
     """Config 4: DSA sparse decode, 8 sequences x 65536 cached tokens, 64x128 indexer heads over FP8
     keys, top 2048, gathered MLA attention."""
@@ -672,7 +725,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="c5b: how partial records travel")
-    ap.add_argument("--extra-only", default=None, choices=["c1", "c3", "c4", "c5a", "kda"],
+    ap.add_argument("--extra-only", default=None, choices=["c1", "c3", "c4", "c5a", "kda", "gdn_mm"],
                     help="run one side measurement alone and print its JSON (for profiling that kernel)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline")
     args = ap.parse_args()
@@ -686,7 +739,7 @@ def main():
         torch.cuda.set_stream(stream)
         attn = Attn(0)
         peak, _ = peaks()
-        fn = {"c1": side_gqa_decode, "c3": side_prefill, "c4": side_dsa, "kda": side_kda,
+        fn = {"c1": side_gqa_decode, "c3": side_prefill, "c4": side_dsa, "kda": side_kda, "gdn_mm": side_gdn_mm,
               "c5a": lambda a, d, s_, p_: side_measure(a, d, s_, 64, 32768, p_)}[args.extra_only]
         print(json.dumps({args.extra_only: fn(attn, dev, stream, peak)}))
     elif args.impl == "reference":
