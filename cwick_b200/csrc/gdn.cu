@@ -2,7 +2,9 @@
 // (src/q35_model.c:1177-1264) for n positions of B slots, after the projections, the convolution and the q/k
 // normalisation (which are GEMMs and elementwise passes on the caller's side, :1277-1372).
 //
-// One block per (value head, slot), one thread per VALUE row of the head's [head_v][head_k] state. A thread keeps
+// One work item per (value head, slot), one thread per VALUE row of the head's [head_v][head_k] state; blocks are
+// persistent, and the next item's state tile streams into shared memory (16-byte asynchronous copies, padded rows)
+// while the current item is scanned. A thread keeps
 // its row (head_k floats) in registers over all n positions, so the state is read once and written once per call;
 // per position the block shares q and k of the head's key head through shared memory. A row's two passes -- decay
 // and dot with k; update with k delta and dot with q -- are sequential over the key dimension, in the
@@ -10,6 +12,8 @@
 // reference forms it). Positions are a scan: they run one after the other (a decode step is n = 1).
 // Products and sums that the reference rounds separately use the _rn intrinsics (fast-math build); exp and log1p go
 // through double.
+#include <algorithm>
+
 #include "cwk_common.cuh"
 
 namespace {
@@ -29,62 +33,100 @@ struct GdnParams {
     float rms_eps;
 };
 
+// Row stride of the staged state tile in shared memory: 4 floats of padding make a thread's 16-byte reads of its own
+// row conflict-free (eight lanes of a quarter warp then cover all 32 banks).
+template <int HK> __host__ __device__ constexpr int gdn_ld() { return HK + 4; }
+
 template <int HK>
-__global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnParams p) {
+__device__ __forceinline__ void gdn_prefetch(const GdnParams &p, int item, int hv, float *s_tile, int j, int nthreads) {
+    const int vh = item % p.nh, b = item / p.nh;
+    const float *src = p.S + (((int64_t)b * p.nh + vh) * hv) * HK;
+    const uint32_t tb = (uint32_t)__cvta_generic_to_shared(s_tile);
+    for (int ch = j; ch < hv * (HK / 4); ch += nthreads) {            // 16-byte chunks, coalesced
+        const int row = ch / (HK / 4), c4 = ch % (HK / 4);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tb + (uint32_t)(row * gdn_ld<HK>() + c4 * 4) * 4u), "l"(src + (int64_t)ch * 4) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// Persistent blocks: block g works on items g, g + G, ... (item = slot * nh + value head). While an item's positions
+// are scanned with the state in registers, the next item's state tile streams into shared memory.
+template <int HK>
+__global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnParams p, int nitems) {
+    extern __shared__ float4 s_dyn4[];
+    float *s_tile = reinterpret_cast<float *>(s_dyn4);                // [hv][HK + 4], the NEXT item's state
     __shared__ float s_q[HK], s_k[HK], s_tmp[128];
     __shared__ float s_rstd;
-    const int vh = blockIdx.x, b = blockIdx.y, j = threadIdx.x, hv = blockDim.x;
-    const int kh = vh / p.kv_group;
+    const int j = threadIdx.x, hv = blockDim.x;
     const int key_dim = (p.nh / p.kv_group) * HK, val_dim = p.nh * hv, qkv_dim = 2 * key_dim + val_dim;
-    float *Srow = p.S + ((((int64_t)b * p.nh + vh) * hv) + j) * HK;
-    float sj[HK];
+    const bool single = nitems <= (int)gridDim.x;                     // one item per block: nothing to overlap with
+    const float nw = p.norm[j];
+    if (!single) gdn_prefetch<HK>(p, blockIdx.x, hv, s_tile, j, hv);
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+        const int vh = item % p.nh, b = item / p.nh;
+        const int kh = vh / p.kv_group;
+        float *Srow = p.S + ((((int64_t)b * p.nh + vh) * hv) + j) * HK;
+        float sj[HK];
+        if (single) {
 #pragma unroll
-    for (int i = 0; i < HK; i += 4) {
-        const float4 v = *reinterpret_cast<const float4 *>(Srow + i);
-        sj[i] = v.x; sj[i + 1] = v.y; sj[i + 2] = v.z; sj[i + 3] = v.w;
+            for (int i = 0; i < HK; i += 4) {
+                const float4 v = *reinterpret_cast<const float4 *>(Srow + i);
+                sj[i] = v.x; sj[i + 1] = v.y; sj[i + 2] = v.z; sj[i + 3] = v.w;
+            }
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < HK; i += 4) {
+                const float4 v = *reinterpret_cast<const float4 *>(s_tile + j * gdn_ld<HK>() + i);
+                sj[i] = v.x; sj[i + 1] = v.y; sj[i + 2] = v.z; sj[i + 3] = v.w;
+            }
+            __syncthreads();
+            if (item + (int)gridDim.x < nitems) gdn_prefetch<HK>(p, item + gridDim.x, hv, s_tile, j, hv);
+        }
+        const float ea = g_exp(p.a_log[vh]), dtb = p.dt_bias[vh];
+        for (int t = 0; t < p.n; t++) {
+            const float *row = p.up + ((int64_t)b * p.n + t) * qkv_dim;
+            for (int i = j; i < HK; i += hv) {
+                s_q[i] = row[(int64_t)kh * HK + i];
+                s_k[i] = row[key_dim + (int64_t)kh * HK + i];
+            }
+            const float vj = row[2 * key_dim + (int64_t)vh * hv + j];
+            const float zj = p.gate[((int64_t)b * p.n + t) * val_dim + (int64_t)vh * hv + j];
+            const float x = __fadd_rn(p.gdec[((int64_t)b * p.n + t) * p.nh + vh], dtb);
+            const float sp = x > 20.0f ? x : (float)log1p((double)g_exp(x));
+            const float decay = g_exp(__fmul_rn(-ea, sp));
+            const float bet = __fdiv_rn(1.0f, __fadd_rn(1.0f, g_exp(-p.beta[((int64_t)b * p.n + t) * p.nh + vh])));
+            __syncthreads();
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < HK; i++) {
+                sj[i] = __fmul_rn(sj[i], decay);
+                dot = __fadd_rn(dot, __fmul_rn(sj[i], s_k[i]));
+            }
+            const float delta = __fmul_rn(bet, __fsub_rn(vj, dot));
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < HK; i++) {
+                sj[i] = __fadd_rn(sj[i], __fmul_rn(s_k[i], delta));
+                acc = __fadd_rn(acc, __fmul_rn(sj[i], s_q[i]));
+            }
+            s_tmp[j] = acc;
+            __syncthreads();
+            if (j == 0) {
+                float ss = 0.f;
+                for (int r = 0; r < hv; r++) ss = __fadd_rn(ss, __fmul_rn(s_tmp[r], s_tmp[r]));
+                s_rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hv), p.rms_eps)));
+            }
+            __syncthreads();
+            float o = __fmul_rn(acc, s_rstd);
+            o = __fmul_rn(o, nw);
+            o = __fmul_rn(o, __fdiv_rn(zj, __fadd_rn(1.0f, g_exp(-zj))));
+            p.out[((int64_t)b * p.n + t) * val_dim + (int64_t)vh * hv + j] = o;
+        }
+#pragma unroll
+        for (int i = 0; i < HK; i += 4) *reinterpret_cast<float4 *>(Srow + i) = make_float4(sj[i], sj[i + 1], sj[i + 2], sj[i + 3]);
     }
-    const float ea = g_exp(p.a_log[vh]), dtb = p.dt_bias[vh], nw = p.norm[j];
-    for (int t = 0; t < p.n; t++) {
-        const float *row = p.up + ((int64_t)b * p.n + t) * qkv_dim;
-        for (int i = j; i < HK; i += hv) {
-            s_q[i] = row[(int64_t)kh * HK + i];
-            s_k[i] = row[key_dim + (int64_t)kh * HK + i];
-        }
-        const float vj = row[2 * key_dim + (int64_t)vh * hv + j];
-        const float zj = p.gate[((int64_t)b * p.n + t) * val_dim + (int64_t)vh * hv + j];
-        const float x = __fadd_rn(p.gdec[((int64_t)b * p.n + t) * p.nh + vh], dtb);
-        const float sp = x > 20.0f ? x : (float)log1p((double)g_exp(x));
-        const float decay = g_exp(__fmul_rn(-ea, sp));
-        const float bet = __fdiv_rn(1.0f, __fadd_rn(1.0f, g_exp(-p.beta[((int64_t)b * p.n + t) * p.nh + vh])));
-        __syncthreads();
-        float dot = 0.f;
-#pragma unroll
-        for (int i = 0; i < HK; i++) {
-            sj[i] = __fmul_rn(sj[i], decay);
-            dot = __fadd_rn(dot, __fmul_rn(sj[i], s_k[i]));
-        }
-        const float delta = __fmul_rn(bet, __fsub_rn(vj, dot));
-        float acc = 0.f;
-#pragma unroll
-        for (int i = 0; i < HK; i++) {
-            sj[i] = __fadd_rn(sj[i], __fmul_rn(s_k[i], delta));
-            acc = __fadd_rn(acc, __fmul_rn(sj[i], s_q[i]));
-        }
-        s_tmp[j] = acc;
-        __syncthreads();
-        if (j == 0) {
-            float ss = 0.f;
-            for (int r = 0; r < hv; r++) ss = __fadd_rn(ss, __fmul_rn(s_tmp[r], s_tmp[r]));
-            s_rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hv), p.rms_eps)));
-        }
-        __syncthreads();
-        float o = __fmul_rn(acc, s_rstd);
-        o = __fmul_rn(o, nw);
-        o = __fmul_rn(o, __fdiv_rn(zj, __fadd_rn(1.0f, g_exp(-zj))));
-        p.out[((int64_t)b * p.n + t) * val_dim + (int64_t)vh * hv + j] = o;
-    }
-#pragma unroll
-    for (int i = 0; i < HK; i += 4) *reinterpret_cast<float4 *>(Srow + i) = make_float4(sj[i], sj[i + 1], sj[i + 2], sj[i + 3]);
 }
 
 }  // namespace
@@ -102,9 +144,18 @@ extern "C" int cwk_gdn_scan(cwk_ctx *ctx, int B, int n, int nh, int head_k, int 
     GdnParams p;
     p.up = up; p.gdec = gdec; p.beta = beta; p.gate = gate; p.a_log = a_log; p.dt_bias = dt_bias; p.norm = norm; p.S = S; p.out = out;
     p.n = n; p.nh = nh; p.kv_group = kv_group; p.rms_eps = rms_eps;
+    const int nitems = B * nh;
+    const int grid = std::min(nitems, 2 * ctx->sm_count);
+    const size_t smem = (size_t)head_v * (head_k + 4) * sizeof(float);
+    static bool attr_set[16] = {false};
+    if (!attr_set[ctx->device & 15]) {
+        CWK_CUDA(ctx, cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 132 * 4));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(gdn_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 68 * 4));
+        attr_set[ctx->device & 15] = true;
+    }
     CwkKernelTimer timer(ctx);
-    if (head_k == 128) gdn_scan_kernel<128><<<dim3(nh, B), head_v, 0, ctx->stream>>>(p);
-    else gdn_scan_kernel<64><<<dim3(nh, B), head_v, 0, ctx->stream>>>(p);
+    if (head_k == 128) gdn_scan_kernel<128><<<grid, head_v, smem, ctx->stream>>>(p, nitems);
+    else gdn_scan_kernel<64><<<grid, head_v, smem, ctx->stream>>>(p, nitems);
     CWK_LAUNCH_CHECK(ctx, "gdn_scan_kernel");
     return CWK_OK;
 }

@@ -65,9 +65,10 @@ def test_kda_step_follows_the_reference_over_tokens(attn, case):
 
 
 def test_kda_step_batch_of_slots(attn):
-    """4 slots x 64 heads x 128, three tokens; every slot against the oracle run on it alone."""
+    """6 slots x 64 heads x 128 (more work items than resident blocks, so the persistent loop with its prefetch of the
+    next item's state runs), three tokens; every slot against the oracle run on it alone."""
     o = orc.oracle()
-    B, nh, hd, steps = 4, 64, 128, 3
+    B, nh, hd, steps = 6, 64, 128, 3
     proj = nh * hd
     lower, rms_eps = -5.0, 1e-6
     qc, kc, vc = (synth.normal_bf16(SEED, 981 + i, (proj, 4), 0.5) for i in range(3))
