@@ -68,3 +68,28 @@ def test_product_code_never_touches_the_oracle():
                 if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                     t = open(os.path.join(dp, f)).read()
                     assert "oracle" not in t.lower() or f == "synth.py", os.path.join(dp, f)
+
+
+def test_link_surface_answers_without_a_gpu():
+    """The reference-named symbols that compute nothing answer as documented on any machine: the chunk path is not
+    taken over (false / CWICK_ERR_UNSUPPORTED, on which the engine falls back per token), the counters exist."""
+    import ctypes as C
+    L = lib.load()
+
+    class Err(C.Structure):
+        _fields_ = [("status", C.c_int), ("message", C.c_char * 512)]
+    spec = (C.c_uint8 * 1024)()
+    L.cwick_mla_chunk_supported.restype = C.c_bool
+    L.cwick_mla_chunk_supported.argtypes = [C.c_void_p] * 7
+    assert L.cwick_mla_chunk_supported(C.addressof(spec), None, None, None, None, None, None) is False
+    err = Err()
+    L.cwick_attention_mla_prefill_chunk.restype = C.c_int
+    L.cwick_attention_mla_prefill_chunk.argtypes = [C.c_void_p] * 10 + [C.c_int64] * 4 + [C.c_void_p] * 5
+    st = L.cwick_attention_mla_prefill_chunk(C.addressof(spec), *([None] * 9), 0, 0, 0, 0, None, None, None, None, C.byref(err))
+    assert st == lib.ERR_UNSUPPORTED and err.status == lib.ERR_UNSUPPORTED and err.message
+    for name in ("proj", "conv", "gate", "rec", "mla", "tail"):
+        assert C.c_uint64.in_dll(L, "g_attn_%s_ns" % name).value == 0
+    L.cwick_indexer_bytes.restype = C.c_uint64
+    L.cwick_indexer_bytes.argtypes = [C.c_void_p, C.c_int64]
+    assert L.cwick_indexer_bytes(C.addressof(spec), 4096) == 0          # no indexer configured in a zeroed spec
+
