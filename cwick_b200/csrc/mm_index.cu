@@ -1,8 +1,9 @@
 // mm_index.cu -- the MiniMax block indexer: per-position index scores over bf16 keys and the selection of
 // blocks a query may attend to (src/mm_model.c:1733-1781). The attention over the selected positions is the
 // gathered GQA decode of csrc/gqa.cu (cwk_gqa_decode_sel).
-//   mm_index_scores_kernel   sc[s] = sum_h ReLU(q_h . k_s): one thread per key, heads in order, sequential f32
-//                            dots (the reference's order, so block maxima and ties are the reference's)
+//   mm_index_scores_kernel   sc[s] = sum_h ReLU(q_h . k_s): one thread per key (rows staged through shared memory),
+//                            heads in order, sequential f32 dots (the reference's order, so block maxima and ties
+//                            are the reference's)
 //   mm_block_max_kernel      maximum of every block of `bs` scores (fmaxf from -1e30, partial last block included)
 //   mm_expand_blocks_kernel  the top blocks (exact top-k of csrc/dsa.cu, ascending) plus the block holding the next
 //                            position when it is missing, expanded to the list of positions (at most `cap`)
@@ -10,18 +11,33 @@
 
 namespace {
 
+// 128 keys per block: their rows (ID bf16 each) come into shared memory by 16-byte asynchronous copies, coalesced, into
+// rows padded by 4 words, so that a thread's 16-byte reads of its own row are conflict-free.
 template <int ID>
 __global__ void __launch_bounds__(128) mm_index_scores_kernel(const uint16_t *keys, int64_t n, const float *q, int ih, float *sc) {
-    extern __shared__ float s_q[];                 // [ih][ID]
+    constexpr int WPR = ID / 2, LD = WPR + 4;      // words per key row, padded row stride
+    extern __shared__ float s_dyn[];
+    float *s_q = s_dyn;                            // [ih][ID]
+    uint32_t *s_k = reinterpret_cast<uint32_t *>(s_dyn + ih * ID);       // [128][LD]
+    const int64_t s0 = (int64_t)blockIdx.x * 128;
+    const int nk = (int)min((int64_t)128, n - s0);
+    {
+        const uint32_t kb = (uint32_t)__cvta_generic_to_shared(s_k);
+        const uint16_t *src = keys + s0 * ID;
+        for (int ch = threadIdx.x; ch < nk * (WPR / 4); ch += 128) {
+            const int row = ch / (WPR / 4), c4 = ch % (WPR / 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kb + (uint32_t)(row * LD + c4 * 4) * 4u), "l"(src + (int64_t)ch * 8) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     for (int i = threadIdx.x; i < ih * ID; i += blockDim.x) s_q[i] = q[i];
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= n) return;
+    if ((int)threadIdx.x >= nk) return;
     float kf[ID];
-    const uint4 *kp = reinterpret_cast<const uint4 *>(keys + s * ID);
 #pragma unroll
-    for (int c = 0; c < ID / 8; c++) {
-        const uint4 v = kp[c];
+    for (int c = 0; c < WPR / 4; c++) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(s_k + threadIdx.x * LD + c * 4);
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int t = 0; t < 4; t++) {
@@ -37,7 +53,7 @@ __global__ void __launch_bounds__(128) mm_index_scores_kernel(const uint16_t *ke
         for (int i = 0; i < ID; i++) d = __fadd_rn(d, __fmul_rn(qh[i], kf[i]));
         if (d > 0.f) tot = __fadd_rn(tot, d);
     }
-    sc[s] = tot;
+    sc[s0 + threadIdx.x] = tot;
 }
 
 __global__ void mm_block_max_kernel(const float *sc, int64_t limit, int bs, float *bsc, int32_t *nblk_out) {
@@ -98,13 +114,14 @@ int cwk_mm_index_scores(cwk_ctx *ctx, const void *keys, int64_t n, int id, const
     if (!ctx || !keys || !q || !sc || n < 0 || ih <= 0) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mm_index_scores: bad argument");
     if (id != 64 && id != 128) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mm_index_scores is built for index dims 64 and 128 (got %d)", id);
     if (reinterpret_cast<uintptr_t>(keys) & 15) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mm_index_scores: keys must be 16-byte aligned");
-    if ((size_t)ih * id * 4 > 48 * 1024) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mm_index_scores: too many index heads");
+    const size_t smem = (size_t)ih * id * 4 + (size_t)128 * (id / 2 + 4) * 4;
+    if (smem > 48 * 1024) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mm_index_scores: too many index heads");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     if (n == 0) return CWK_OK;
     CwkKernelTimer timer(ctx);
     const unsigned grid = (unsigned)((n + 127) / 128);
-    if (id == 128) mm_index_scores_kernel<128><<<grid, 128, (size_t)ih * id * 4, ctx->stream>>>((const uint16_t *)keys, n, q, ih, sc);
-    else mm_index_scores_kernel<64><<<grid, 128, (size_t)ih * id * 4, ctx->stream>>>((const uint16_t *)keys, n, q, ih, sc);
+    if (id == 128) mm_index_scores_kernel<128><<<grid, 128, smem, ctx->stream>>>((const uint16_t *)keys, n, q, ih, sc);
+    else mm_index_scores_kernel<64><<<grid, 128, smem, ctx->stream>>>((const uint16_t *)keys, n, q, ih, sc);
     CWK_LAUNCH_CHECK(ctx, "mm_index_scores_kernel");
     return CWK_OK;
 }
