@@ -41,8 +41,15 @@ struct cwk_ctx {
     int *dev_err = nullptr;
     // block ticket of the KV-split push kernel
     void *ticket = nullptr;
-    // optional device buffer for the tcgen05 kernel's phase stamps (developer aid, see cwk_ctx_debug_trace)
+    // optional device buffer for the tcgen05 kernel's phase stamps (only in a -DCWK_TRACE build)
     void *tc_trace = nullptr;
+    // persistent MLA decode kernel: accumulators + parked records + control words (one allocation, fixed size),
+    // and its cache of encoded tensor maps
+    void *sk_acc = nullptr;
+    size_t sk_bytes = 0;
+    void *sk_tmaps = nullptr;
+    // iteration limit of the bounded device-side waits on a peer's flag (cwk_ctx_set_wait_limit)
+    unsigned int wait_limit = 1u << 22;
     char err[512] = {0};
 };
 
@@ -55,6 +62,9 @@ int cwk_reserve_work(cwk_ctx *ctx, size_t bytes);
 int cwk_check_device_error(cwk_ctx *ctx);
 // Allocate the error word on first use: pinned, mapped host memory, so the host reads it without a copy.
 int cwk_ensure_err_word(cwk_ctx *ctx);
+// persistent MLA decode kernel (mla_decode_sk.cu): release its buffers; zero them after a failed step
+void cwk_sk_free(cwk_ctx *ctx);
+void cwk_sk_reset(cwk_ctx *ctx);
 
 // Brackets a main-kernel launch with events when profiling is on.
 struct CwkKernelTimer {

@@ -82,6 +82,8 @@ int cwk_check_device_error(cwk_ctx *ctx) {
     const int code = *(volatile int *)ctx->dev_err;      // call after a stream synchronise
     if (code == 0) return CWK_OK;
     *(volatile int *)ctx->dev_err = 0;
+    cwk_sk_reset(ctx);          // accumulators and tickets of the persistent decode kernel may hold a half-finished step
+    cudaStreamSynchronize(ctx->stream);
     return cwk_fail(ctx, CWK_ERR_STATE, "a kernel gave up a bounded wait (code %d); its results are invalid", code);
 }
 
@@ -120,6 +122,7 @@ void cwk_ctx_destroy(cwk_ctx *ctx) {
     if (ctx->stage_pin) cudaFreeHost(ctx->stage_pin);
     if (ctx->dev_err) cudaFreeHost(ctx->dev_err);
     if (ctx->ticket) cudaFree(ctx->ticket);
+    cwk_sk_free(ctx);
     for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -167,14 +170,26 @@ int cwk_ctx_profile_read(cwk_ctx *ctx, double *total_ms, int *launches) {
     return CWK_OK;
 }
 
+#ifdef CWK_TRACE
+// Developer builds only (-DCWK_TRACE; not declared in the public header): a device buffer of at least 4096 bytes that
+// block (0,0) of the split-record tcgen05 MLA decode kernel fills with clock64() stamps of its pipeline phases
+// ([role 0..2][tile 0..15][event 0..7] as int64). NULL turns it off.
+CWK_API int cwk_ctx_debug_trace(cwk_ctx *ctx, void *device_buffer);
 int cwk_ctx_debug_trace(cwk_ctx *ctx, void *device_buffer) {
     if (!ctx) return CWK_ERR_ARGUMENT;
     ctx->tc_trace = device_buffer;
     return CWK_OK;
 }
+#endif
+
+int cwk_ctx_set_wait_limit(cwk_ctx *ctx, unsigned int polls) {
+    if (!ctx || polls == 0) return CWK_ERR_ARGUMENT;
+    ctx->wait_limit = polls;
+    return CWK_OK;
+}
 
 int cwk_ctx_force_mla_path(cwk_ctx *ctx, int path) {
-    if (!ctx || path < -1 || path > 3) return CWK_ERR_ARGUMENT;     // 3: exact form of the prefill attention (cwk_mla_prefill only)
+    if (!ctx || path < -1 || path > 4) return CWK_ERR_ARGUMENT;     // 3: exact form of the prefill attention (cwk_mla_prefill only)
     ctx->force_mla_path = path;
     return CWK_OK;
 }

@@ -14,6 +14,11 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
                              int64_t ld, const int32_t *kv_len, int max_kv_len, int B, int nh,
                              int R, float scale, float *partial, int nsplit, void *out_direct);
 bool cwk_mla_decode_tc_available();
+// persistent tcgen05/TMA kernel with the cross-block reduction inside (mla_decode_sk.cu): bf16 rows to `out`, or one
+// folded record per sequence to `rec_out`
+int cwk_mla_decode_sk_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
+                             const int32_t *kv_len, int max_kv_len, int B, int nh, int R, float scale, void *out,
+                             float *rec_out, int blocks);
 
 // ---------------------------------------------------------------------------
 // General kernel: any nh, L <= 512 (multiple of 2), any R. One block per
@@ -112,18 +117,36 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     // the tcgen05 kernel also takes the rope-free 512-wide latent: its ninth column block is then
     // out of the tensor's bounds and arrives as zeros
     if (L == 512 && (R == 64 || R == 0) && aligned && !sel && nh == 64 && max_kv_len > 0 && cwk_mla_decode_tc_available())
-        path = 2;
-    if (ctx->force_mla_path >= 0) {
+        path = 4;
+    if (ctx->force_mla_path >= 0 && ctx->force_mla_path != 3) {
         if (ctx->force_mla_path > path) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mla_decode: forced path %d not applicable (best %d)", ctx->force_mla_path, path);
         path = ctx->force_mla_path;
+    }
+    if (path == 4) {
+        // one persistent launch: no split records, no merge
+        const size_t recb = (size_t)nh * (L + 2) * sizeof(float);
+        float *rec_dst = partial_out;
+        if (!out && !partial_out) {           // keep_splits: one folded record in the context's scratch
+            int s = cwk_reserve_scratch(ctx, recb);
+            if (s != CWK_OK) return s;
+            rec_dst = ctx->scratch;
+        }
+        {
+            CwkKernelTimer timer(ctx);
+            int s = cwk_mla_decode_sk_launch(ctx, q, cache, seq_stride, ld, kv_len, max_kv_len, B, nh, R, scale, out, rec_dst,
+                                             n_splits > 0 ? n_splits * B : -n_splits);
+            if (s != CWK_OK) return s;
+        }
+        ctx->last_nsplit = 1;
+        return CWK_OK;
     }
     if (path == 0 && (L > 512 || (L & 1)))
         return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mla_decode: general kernel needs even L <= 512 (got %d)", L);
 
-    const int tile = (path == 2) ? 128 : (path == 1 ? 64 : 32);
+    const int tile = (path >= 2) ? 128 : (path == 1 ? 64 : 32);
     const int max_tiles = (max_kv_len + tile - 1) / tile;
     const int hblocks = (path == 0) ? nh : (nh + 63) / 64;
-    int ns = plan_splits(ctx->sm_count, B * hblocks, max_tiles, n_splits);
+    int ns = plan_splits(ctx->sm_count, B * hblocks, max_tiles, n_splits > 0 ? n_splits : 0);
     // One split per sequence needs no records at all: the kernel normalises and writes bf16.
     const bool direct = (ns == 1 && out && !partial_out && path != 0);
     const size_t rec = (size_t)nh * (L + 2) * sizeof(float);
@@ -196,8 +219,8 @@ extern "C" {
 int cwk_mla_decode_path(const cwk_ctx *ctx, int nh, int L, int R) {
     if (!ctx) return -1;
     int path = (L == 512 && R == 64) ? 1 : 0;
-    if (L == 512 && (R == 64 || R == 0) && nh == 64 && cwk_mla_decode_tc_available()) path = 2;
-    if (ctx->force_mla_path >= 0 && ctx->force_mla_path <= path) path = ctx->force_mla_path;
+    if (L == 512 && (R == 64 || R == 0) && nh == 64 && cwk_mla_decode_tc_available()) path = 4;
+    if (ctx->force_mla_path >= 0 && ctx->force_mla_path != 3 && ctx->force_mla_path <= path) path = ctx->force_mla_path;
     return path;
 }
 

@@ -95,7 +95,9 @@ struct TcParams {
     int batch_coord_zero;  // all sequences read cache slice 0 (shared cache)
     uint16_t *out;         // direct mode (nsplit == 1): normalised bf16 [B][NH][L]; NULL = write partial records
     int reverse_b;         // schedule sequences last-to-first (causal prefill: longest first)
-    long long *trace;      // optional: per-phase clock64 stamps of block (0,0); NULL = off
+#ifdef CWK_TRACE
+    long long *trace;      // developer build only: per-phase clock64 stamps of block (0,0); NULL = off
+#endif
 };
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -157,10 +159,14 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
+#ifdef CWK_TRACE
     // trace slots: [role][tile][event]; only block (0,0) writes
     long long *tr = (p.trace && split == 0 && blockIdx.y == 0) ? p.trace : nullptr;
 #define TRACE(role, it, ev) do { if (tr && (it) < 16) tr[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
     if (tr && tid == 0) tr[3 * 16 * 8] = clock64();
+#else
+#define TRACE(role, it, ev) do { } while (0)
+#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -405,7 +411,9 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
         }
     }
+#ifdef CWK_TRACE
     if (tr && tid == 128) tr[3 * 16 * 8 + 1] = clock64();
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -465,7 +473,9 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     TcParams p;
     p.kv_len = kv_len; p.kv_len_imm = max_kv_len; p.partial = partial; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f;
     p.err = ctx->dev_err; p.batch_coord_zero = shared_cache ? 1 : 0;
+#ifdef CWK_TRACE
     p.trace = (long long *)ctx->tc_trace;
+#endif
     p.out = (uint16_t *)out_direct;
     p.reverse_b = shared_cache ? 1 : 0;
     mla_decode_tc_kernel<<<dim3(nsplit, B), NTHREADS, SMEM_TOTAL, ctx->stream>>>(tm_q, tm_kv, tm_kr, p);

@@ -220,7 +220,7 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     // Qfull bf16 [n][nh][row]. The same workspace region serves whichever runs.
     // The expansion covers every cached row, so it pays when the chunk is a fair share of the context (always for a
     // prompt from position 0); a short chunk after a long history takes the absorbed route.
-    const bool expanded_keys = ctx->force_mla_path != 0 && ctx->force_mla_path != 1 && ctx->force_mla_path != 2 && pos0 + n <= 32768 &&
+    const bool expanded_keys = ctx->force_mla_path != 0 && ctx->force_mla_path != 1 && ctx->force_mla_path != 2 && ctx->force_mla_path != 4 && pos0 + n <= 32768 &&
                                (int64_t)n * 4 >= pos0 + n;
     const size_t b_kx = up((size_t)(pos0 + n) * nh * qd * 2);
     const size_t b_q = up((size_t)n * nh * qd * 2), b_qf = expanded_keys ? std::max(b_kx, up((size_t)n * nh * row * 2)) : up((size_t)n * nh * row * 2),

@@ -24,7 +24,7 @@ SIGNATURES = {
     "cwk_ctx_sm_count": (i32, [vp]),
     "cwk_ctx_profile": (i32, [vp, i32]),
     "cwk_ctx_profile_read": (i32, [vp, C.POINTER(C.c_double), C.POINTER(i32)]),
-    "cwk_ctx_debug_trace": (i32, [vp, vp]),
+    "cwk_ctx_set_wait_limit": (i32, [vp, C.c_uint32]),
     "cwk_mla_decode_path": (i32, [vp, i32, i32, i32]),
     "cwk_ctx_force_mla_path": (i32, [vp, i32]),
     "cwk_mla_decode": (i32, [vp, vp, vp, i64, i64, vp, i32, vp, i64, i32, i32, i32, i32, f32, vp, i32]),

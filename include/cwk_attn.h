@@ -70,18 +70,22 @@ CWK_API int cwk_ctx_sm_count(const cwk_ctx *ctx);
  * turn it on inside a stream capture. */
 CWK_API int cwk_ctx_profile(cwk_ctx *ctx, int on);
 CWK_API int cwk_ctx_profile_read(cwk_ctx *ctx, double *total_ms, int *launches);
-/* Developer aid: a device buffer of at least 4096 bytes that block (0,0) of the
- * tcgen05 MLA decode kernel fills with clock64() stamps of its pipeline phases
- * ([role 0..2][tile 0..15][event 0..7] as int64). NULL turns it off. */
-CWK_API int cwk_ctx_debug_trace(cwk_ctx *ctx, void *device_buffer);
+/* Iteration limit of the device-side waits on another rank's flag
+ * (cwk_mla_decode_kv_split). Default 2^22 polls of ~200 ns (about a second);
+ * a test of the give-up path sets a few thousand. */
+CWK_API int cwk_ctx_set_wait_limit(cwk_ctx *ctx, unsigned int polls);
 /* Which implementation the next cwk_mla_decode call would take for these
- * dimensions: 2 = tcgen05/TMA kernel, 1 = mma.sync kernel, 0 = generic. */
+ * dimensions: 4 = persistent tcgen05/TMA kernel (one launch, blocks share
+ * sequences tile by tile and reduce through f32 atomics: results can differ
+ * in the last bits between runs), 2 = tcgen05/TMA kernel with split records
+ * and a merge launch (reproducible bit for bit), 1 = mma.sync kernel,
+ * 0 = generic. */
 CWK_API int cwk_mla_decode_path(const cwk_ctx *ctx, int nh, int L, int R);
-/* Force a path (same codes; -1 = automatic). For A/B measurement and tests.
- * In cwk_mla_prefill: 0..2 also select the absorbed attention route (the decode
- * kernel once per query row) instead of the expanded-key route, and 3 keeps the
- * expanded-key route but runs the exact form of its attention kernel on every
- * block. */
+/* Force a path (same codes; -1 = automatic). For A/B measurement, tests, and
+ * callers that need run-to-run identical bits (2). In cwk_mla_prefill: 0..2 and
+ * 4 also select the absorbed attention route (the decode kernel once per query
+ * row) instead of the expanded-key route, and 3 keeps the expanded-key route
+ * but runs the exact form of its attention kernel on every block. */
 CWK_API int cwk_ctx_force_mla_path(cwk_ctx *ctx, int path);
 
 /* ---- MLA absorbed decode ---------------------------------------------------
@@ -100,7 +104,9 @@ CWK_API int cwk_ctx_force_mla_path(cwk_ctx *ctx, int path);
  *            src/attention.c:757 `sel ? sel[i] : i`); then kv_len[b] counts
  *            selected rows. NULL = rows 0..kv_len[b]-1.
  *   out      bf16 [B][nh][L].  kv_len[b] == 0 writes zeros.
- * n_splits: 0 = choose from the SM count. */
+ * n_splits: 0 = choose from the SM count. The persistent kernel (path 4) has no
+ * splits: n_splits > 0 caps its grid at n_splits * B blocks, n_splits < 0 at
+ * -n_splits blocks (for tests of its partitioning). */
 CWK_API int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride,
                    int64_t ld, const int32_t *kv_len, int max_kv_len, const int32_t *sel,
                    int64_t sel_ld, int B, int nh, int L, int R, float scale, void *out,

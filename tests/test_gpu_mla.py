@@ -43,7 +43,7 @@ def oracle_out(q, cache, lens, l=L, r=R, scale=SCALE, sel=None):
 
 
 @pytest.mark.parametrize("T", [1, 63, 64, 65, 200, 1000])
-@pytest.mark.parametrize("path", [2, 1, 0])
+@pytest.mark.parametrize("path", [4, 2, 1, 0])
 def test_single_sequence_sizes(attn, T, path):
     q, cache = make_case(10 + T, 1, 64, T)
     lens = np.array([T], np.int32)
@@ -97,7 +97,7 @@ def test_sparse_gather(attn):
     close(bf16_to_np(got), oracle_out(q, cache, lens, sel=sel.astype(np.int64)))
 
 
-@pytest.mark.parametrize("path", [2, 1])
+@pytest.mark.parametrize("path", [4, 2, 1])
 def test_config2_full_size(attn, path):
     """BASELINE config 2: batch 1, 64 heads, 8192 cached tokens, on both tensor-core kernels."""
     q, cache = make_case(synth.DEFAULT_SEED, 1, 64, 8192)
@@ -122,7 +122,7 @@ def test_scores_that_outgrow_the_running_maximum(attn):
     cf[:, :, :L] = np.abs(cf[:, :, :L]) * ramp * np.sign(qf[:, :1, :L] + 1e-6)   # align keys with head 0's query
     cache = synth.f32_to_bf16(cf).reshape(cache.shape)
     lens = np.array([T], np.int32)
-    for path in (2, 1):
+    for path in (4, 2, 1):
         attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, path)
         try:
             got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
@@ -132,28 +132,47 @@ def test_scores_that_outgrow_the_running_maximum(attn):
         close(bf16_to_np(got), oracle_out(q, cache, lens))
 
 
-def test_host_entry_point_matches_device_entry_point(attn):
+def same(a, b, exact):
+    """Bit for bit on the reproducible kernels; within one bf16 step of O(1) values on the persistent
+    kernel, whose cross-block sums go through f32 atomics in no fixed order."""
+    if exact:
+        assert torch.equal(a, b)
+    else:
+        close(bf16_to_np(a), bf16_to_np(b), max_abs=4e-3)
+
+
+@pytest.mark.parametrize("path", [4, 2])
+def test_host_entry_point_matches_device_entry_point(attn, path):
     q, cache = make_case(12, 3, 64, 500)
     lens = np.array([500, 77, 256], np.int32)
-    dev = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
-    qh = torch.from_numpy(q.view(np.int16)).view(torch.bfloat16)
-    outh = torch.empty(3, 64, L, dtype=torch.bfloat16)
-    attn.mla_decode_host(qh, to_bf16_cuda(cache), torch.from_numpy(lens), L, R, SCALE, outh)
-    assert torch.equal(outh, dev.cpu())
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, path)
+    try:
+        dev = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+        qh = torch.from_numpy(q.view(np.int16)).view(torch.bfloat16)
+        outh = torch.empty(3, 64, L, dtype=torch.bfloat16)
+        attn.mla_decode_host(qh, to_bf16_cuda(cache), torch.from_numpy(lens), L, R, SCALE, outh)
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
+    same(outh, dev.cpu(), exact=(path == 2))
 
 
+@pytest.mark.parametrize("path", [4, 2])
 @pytest.mark.parametrize("B,T", [(1, 8192), (3, 500)])
-def test_host_entry_point_with_page_locked_buffers(attn, B, T):
+def test_host_entry_point_with_page_locked_buffers(attn, B, T, path):
     """Page-locked caller buffers: q is copied from in place and the output is written by the last
     kernel straight into the caller's (device-mapped) buffer. One sequence goes through the split +
     merge kernels, several short ones through the direct-output kernel."""
     q, cache = make_case(13, B, 64, T)
     lens = np.array([T - 3 * b for b in range(B)], np.int32)
-    dev = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
-    qh = torch.from_numpy(q.view(np.int16)).view(torch.bfloat16).pin_memory()
-    outh = torch.zeros(B, 64, L, dtype=torch.bfloat16).pin_memory()
-    attn.mla_decode_host(qh, to_bf16_cuda(cache), torch.from_numpy(lens), L, R, SCALE, outh)
-    assert torch.equal(outh, dev.cpu())
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, path)
+    try:
+        dev = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+        qh = torch.from_numpy(q.view(np.int16)).view(torch.bfloat16).pin_memory()
+        outh = torch.zeros(B, 64, L, dtype=torch.bfloat16).pin_memory()
+        attn.mla_decode_host(qh, to_bf16_cuda(cache), torch.from_numpy(lens), L, R, SCALE, outh)
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
+    same(outh, dev.cpu(), exact=(path == 2))
 
 
 def test_kv_range_partials_and_merge(attn):
@@ -205,6 +224,82 @@ def test_batch_and_split_invariance_at_config5_shape(attn):
     cn = cache[3].view(torch.int16).cpu().numpy().view(np.uint16)
     want = orc.mla_decode(synth.bf16_to_f32(qn), cn, T, L, R, SCALE)
     close(bf16_to_np(full[3]), want)
+
+
+def test_persistent_kernel_shares_sequences_between_blocks(attn):
+    """Ragged lengths and block counts that cut sequences at odd places: every sequence is shared by
+    several blocks (accumulator + ticket), some blocks hold the end of one sequence and the start of the
+    next, one sequence is empty. Run twice on one context: the second run finds the accumulators,
+    tickets and counters as the first left them."""
+    B, T = 5, 2100
+    q, cache = make_case(41, B, 64, T)
+    lens = np.array([2100, 129, 0, 1500, 777], np.int32)
+    want = oracle_out(q, cache, lens)
+    assert cwk_path(attn) == 4
+    for n_splits in (0, 1, 2, 3, 7):
+        for _ in range(2):
+            got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE,
+                                  n_splits=n_splits)
+            attn.ctx.sync()
+            g = bf16_to_np(got)
+            assert np.all(g[2] == 0)
+            close(g, want)
+
+
+def test_persistent_kernel_many_short_sequences(attn):
+    """More segments in one block's range than its segment table holds (several table fills), most of
+    them whole sequences written straight from tensor memory."""
+    B, T = 300, 140
+    q, cache = make_case(43, B, 64, T)
+    # sequences of one or two rows return those rows themselves: halve the cached values so that the
+    # bf16 rounding of the outputs (values up to ~2 instead of ~4.5) stays inside the absolute bar
+    cache = synth.f32_to_bf16(0.5 * synth.bf16_to_f32(cache)).reshape(cache.shape)
+    rng = np.random.default_rng(7)
+    lens = rng.integers(0, T + 1, B).astype(np.int32)
+    lens[:3] = [T, 0, 1]
+    want = oracle_out(q, cache, lens)
+    for n_splits in (0, 1):            # 0: one block per SM; 1: capped at B blocks
+        got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE,
+                              n_splits=n_splits, max_kv_len=T)
+        attn.ctx.sync()
+        close(bf16_to_np(got), want)
+    # two blocks for all 300 sequences: about 150 segments each, four table fills
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, 4)
+    try:
+        got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE,
+                              n_splits=-2, max_kv_len=T)
+        attn.ctx.sync()
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
+    close(bf16_to_np(got), want)
+
+
+def test_persistent_kernel_parks_records_that_outran_the_common_reference(attn):
+    """The first cached row scores far below the rest (by more than 2^64 after scaling), so every block
+    that shares the sequence has to move its own reference beyond what may be added into the common
+    accumulator: the records are parked and the finishing block folds them in."""
+    T = 1500
+    q, cache = make_case(47, 1, 64, T)
+    qf = synth.bf16_to_f32(q)
+    cf = synth.bf16_to_f32(cache)
+    cf[0, 0, :L] = -0.25 * np.sign(qf[0, 0, :L] + 1e-6)          # row 0 against head 0's query: a large negative score
+    cf[0, 1:, :L] = 0.5 * np.abs(cf[0, 1:, :L]) * np.sign(qf[0, :1, :L] + 1e-6)   # the others with it
+    cache = synth.f32_to_bf16(cf).reshape(cache.shape)
+    lens = np.array([T], np.int32)
+    want = oracle_out(q, cache, lens)
+    for _ in range(2):
+        got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+        attn.ctx.sync()
+        close(bf16_to_np(got), want)
+    # and an ordinary call afterwards finds pool, tags and counters clean
+    q2, cache2 = make_case(48, 1, 64, 900)
+    got = attn.mla_decode(to_bf16_cuda(q2), to_bf16_cuda(cache2), torch.from_numpy(np.array([900], np.int32)).cuda(), scale=SCALE)
+    attn.ctx.sync()
+    close(bf16_to_np(got), oracle_out(q2, cache2, np.array([900], np.int32)))
+
+
+def cwk_path(attn):
+    return attn.lib.cwk_mla_decode_path(attn.ctx.h, 64, L, R)
 
 
 def test_bad_arguments_are_reported_not_run(attn):
