@@ -222,6 +222,8 @@ def run_ours(args):
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
     attn = Attn(local)                       # binds the context to `stream`
+    if args.mla_path >= 0:                   # A/B: 4 persistent kernel, 2 split records + merge, 1 mma.sync
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, args.mla_path)
 
     g = torch.Generator(device=dev).manual_seed(20261125 + rank)
     caches, qs, outs = [], [], []
@@ -304,7 +306,8 @@ def run_ours(args):
     per_launch_bytes = algorithmic_bytes(B, T)
     achieved = per_launch_bytes / (k_ms / k_n / 1e3) / 1e9 if k_n else 0.0
     path = int(attn.lib.cwk_mla_decode_path(attn.ctx.h, NH, L, R))
-    kernel_name = {2: "mla_decode_tc_kernel (tcgen05+TMA)", 1: "flash_rows_kernel<MLA> (mma.sync)", 0: "mla_decode_general_kernel"}[path]
+    kernel_name = {4: "mla_decode_sk_kernel (tcgen05+TMA, persistent, in-kernel reduction)", 2: "mla_decode_tc_kernel (tcgen05+TMA)",
+                   1: "flash_rows_kernel<MLA> (mma.sync)", 0: "mla_decode_general_kernel"}[path]
     roofline = {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBps_spec": achieved / 8000.0,
                 "algorithmic_bytes_per_launch": per_launch_bytes, "avg_launch_us": 1e3 * k_ms / max(1, k_n),
@@ -341,7 +344,8 @@ def run_ours(args):
     h2d = calls * (B * NH * DK * 2 + (B * 4 if B > 1 else 0))      # one sequence: its length is a call argument
     d2h = calls * B * NH * L * 2
     # sanity: both paths computed the same thing
-    assert torch.equal(oh[0], outs[0].cpu()), "host and device entry points disagree"
+    # (cross-block sums go through f32 atomics in no fixed order: equal up to a bf16 step, not bit for bit)
+    assert float((oh[0].float() - outs[0].cpu().float()).abs().max()) <= 4e-3, "host and device entry points disagree"
 
     line = {"metric": "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -727,6 +731,7 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="c5b: how partial records travel")
     ap.add_argument("--extra-only", default=None, choices=["c1", "c3", "c4", "c5a", "kda", "gdn_mm"],
                     help="run one side measurement alone and print its JSON (for profiling that kernel)")
+    ap.add_argument("--mla-path", type=int, default=-1, help="force an MLA decode kernel (cwk_ctx_force_mla_path codes)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline")
     args = ap.parse_args()
     if args.extra_only:

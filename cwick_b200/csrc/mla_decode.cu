@@ -116,10 +116,14 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     int path = (L == 512 && R == 64 && aligned) ? 1 : 0;
     // the tcgen05 kernel also takes the rope-free 512-wide latent: its ninth column block is then
     // out of the tensor's bounds and arrives as zeros
-    if (L == 512 && (R == 64 || R == 0) && aligned && !sel && nh == 64 && max_kv_len > 0 && cwk_mla_decode_tc_available())
-        path = 4;
+    const bool tc_ok = L == 512 && (R == 64 || R == 0) && aligned && !sel && nh == 64 && max_kv_len > 0 && cwk_mla_decode_tc_available();
+    if (tc_ok) path = 2;
     if (ctx->force_mla_path >= 0 && ctx->force_mla_path != 3) {
-        if (ctx->force_mla_path > path) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mla_decode: forced path %d not applicable (best %d)", ctx->force_mla_path, path);
+        // 4 = the persistent kernel: same conditions as 2, taken only on request (its cross-block sums go through f32
+        // atomics, which the split records + merge launch of 2 beat at every shape measured so far)
+        const int best = tc_ok ? 4 : path;
+        if (ctx->force_mla_path > best || (ctx->force_mla_path == 3))
+            return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mla_decode: forced path %d not applicable (best %d)", ctx->force_mla_path, path);
         path = ctx->force_mla_path;
     }
     if (path == 4) {
@@ -219,8 +223,9 @@ extern "C" {
 int cwk_mla_decode_path(const cwk_ctx *ctx, int nh, int L, int R) {
     if (!ctx) return -1;
     int path = (L == 512 && R == 64) ? 1 : 0;
-    if (L == 512 && (R == 64 || R == 0) && nh == 64 && cwk_mla_decode_tc_available()) path = 4;
-    if (ctx->force_mla_path >= 0 && ctx->force_mla_path != 3 && ctx->force_mla_path <= path) path = ctx->force_mla_path;
+    const bool tc_ok = L == 512 && (R == 64 || R == 0) && nh == 64 && cwk_mla_decode_tc_available();
+    if (tc_ok) path = 2;
+    if (ctx->force_mla_path >= 0 && ctx->force_mla_path != 3 && ctx->force_mla_path <= (tc_ok ? 4 : path)) path = ctx->force_mla_path;
     return path;
 }
 

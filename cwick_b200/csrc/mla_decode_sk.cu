@@ -89,6 +89,7 @@ struct SkParams {
     float *acc;              // [G][REC] {unused[NH], l[NH], o[NH][L]}; zero between launches
     unsigned int *ctl;       // [0] exit ticket, [1] pool counter, [2, 2+slots) sequence tickets; zero between launches
     unsigned int *tags;      // [exc_cap] which sequence slot (+1) a parked record belongs to, 0 = free; zero between launches
+                             // tags[exc_cap] counts the records parked since the buffers were created (never reset)
     float *exc;              // [exc_cap][REC] parked records, m in log2 units
     int exc_cap;
     uint16_t *out;           // bf16 [B][NH][L], or NULL
@@ -258,6 +259,7 @@ __device__ __noinline__ bool segment_epilogue(const SkParams &p, const Seg &s, u
         if (park) {
             if (st == 0) {
                 const unsigned int e = atomicAdd(&p.ctl[1], 1u);
+                atomicAdd(&p.tags[p.exc_cap], 1u);
                 s_flags[2] = (e < (unsigned int)p.exc_cap) ? (int)e : -1;
                 if (e >= (unsigned int)p.exc_cap) atomicCAS(p.err, 0, 401);   // more parked records than the pool holds
             }
@@ -744,23 +746,6 @@ mla_decode_sk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
 }
 
-struct TmapKey {
-    const void *ptr;
-    int64_t a, b, c;
-    int d;
-    bool operator==(const TmapKey &o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c && d == o.d; }
-};
-struct TmapEntry {
-    TmapKey key;
-    CUtensorMap m[2];
-    bool used;
-};
-constexpr int TMAP_SLOTS = 64;
-struct TmapCache {
-    TmapEntry q[TMAP_SLOTS], kv[TMAP_SLOTS];
-    int next_q = 0, next_kv = 0;
-};
-
 }  // namespace
 
 constexpr int CWK_SK_EXC_CAP = 16;
@@ -768,8 +753,22 @@ constexpr int CWK_SK_EXC_CAP = 16;
 void cwk_sk_free(cwk_ctx *ctx) {
     if (ctx->sk_acc) cudaFree(ctx->sk_acc);
     ctx->sk_acc = nullptr;
-    delete (TmapCache *)ctx->sk_tmaps;
+    delete (CwkMlaTmapCache *)ctx->sk_tmaps;
     ctx->sk_tmaps = nullptr;
+}
+
+// How many records blocks have parked so far on this context (see the file comment); synchronises the stream.
+extern "C" CWK_API int cwk_mla_decode_parked_records(cwk_ctx *ctx, uint64_t *count) {
+    if (!ctx || !count) return CWK_ERR_ARGUMENT;
+    *count = 0;
+    if (!ctx->sk_acc) return CWK_OK;
+    const int slots = ctx->sm_count;
+    const unsigned int *tags = (const unsigned int *)((const float *)ctx->sk_acc + (size_t)(slots + CWK_SK_EXC_CAP) * REC) + 2 + slots;
+    unsigned int v = 0;
+    CWK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    CWK_CUDA(ctx, cudaMemcpy(&v, tags + CWK_SK_EXC_CAP, sizeof(v), cudaMemcpyDeviceToHost));
+    *count = v;
+    return CWK_OK;
 }
 
 // After a kernel gave up a wait: accumulators and tickets may hold a half-finished step.
@@ -784,8 +783,6 @@ int cwk_mla_decode_sk_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     if (nh != NH) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode is built for 64 heads");
     if (max_kv_len <= 0) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode needs a non-empty cache");
     if (!out && !rec_out) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mla_decode: no output");
-    CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
-    if (!enc) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
     {
         int es = cwk_ensure_err_word(ctx);
         if (es != CWK_OK) return es;
@@ -795,67 +792,15 @@ int cwk_mla_decode_sk_launch(cwk_ctx *ctx, const void *q, const void *cache, int
         // accumulators [slots][REC] | parked records [EXC_CAP][REC] | control words: one allocation, zeroed once;
         // the kernel leaves everything it touched zeroed again
         const size_t acc_b = (size_t)slots * REC * 4, exc_b = (size_t)CWK_SK_EXC_CAP * REC * 4;
-        const size_t ctl_b = ((size_t)(2 + slots + CWK_SK_EXC_CAP) * 4 + 255) & ~(size_t)255;
+        const size_t ctl_b = ((size_t)(2 + slots + CWK_SK_EXC_CAP + 1) * 4 + 255) & ~(size_t)255;
         CWK_CUDA(ctx, cudaMalloc(&ctx->sk_acc, acc_b + exc_b + ctl_b));
         ctx->sk_bytes = acc_b + exc_b + ctl_b;
         CWK_CUDA(ctx, cudaMemsetAsync(ctx->sk_acc, 0, ctx->sk_bytes, ctx->stream));
     }
-    if (!ctx->sk_tmaps) ctx->sk_tmaps = new TmapCache();
-    TmapCache *tc = (TmapCache *)ctx->sk_tmaps;
-
-    const cuuint64_t nblk = (cuuint64_t)(width / 64);     // 9, or 8 for a rope-free latent: block 8 is then out of range and reads as zeros
     const CUtensorMap *tm_q = nullptr, *tm_kv = nullptr, *tm_kr = nullptr;
     {
-        const TmapKey key{q, B, width, 0, 0};
-        TmapEntry *e = nullptr;
-        for (int i = 0; i < TMAP_SLOTS; i++)
-            if (tc->q[i].used && tc->q[i].key == key) { e = &tc->q[i]; break; }
-        if (!e) {
-            e = &tc->q[tc->next_q];
-            tc->next_q = (tc->next_q + 1) % TMAP_SLOTS;
-            e->used = false;
-            // q as [64][B*NH rows][blocks]: one box brings all nine column blocks of a sequence's 64 heads
-            cuuint64_t dims[3] = {64, (cuuint64_t)B * NH, nblk};
-            cuuint64_t strides[2] = {(cuuint64_t)width * 2, 128};
-            cuuint32_t box[3] = {64, NH, NBLK};
-            cuuint32_t es[3] = {1, 1, 1};
-            CUresult r = enc(&e->m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(q), dims, strides, box, es,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(q) failed: %d", (int)r);
-            e->key = key;
-            e->used = true;
-        }
-        tm_q = &e->m[0];
-    }
-    const bool shared_cache = (seq_stride == 0);
-    {
-        const TmapKey key{cache, seq_stride, ld, max_kv_len, shared_cache ? -width : B * 1024 + width};
-        TmapEntry *e = nullptr;
-        for (int i = 0; i < TMAP_SLOTS; i++)
-            if (tc->kv[i].used && tc->kv[i].key == key) { e = &tc->kv[i]; break; }
-        if (!e) {
-            e = &tc->kv[tc->next_kv];
-            tc->next_kv = (tc->next_kv + 1) % TMAP_SLOTS;
-            e->used = false;
-            for (int pass = 0; pass < 2; pass++) {
-                // the cache as [64][rows][blocks][sequences]; boxes of two column blocks, or three (blocks 6, 7 and the rope block)
-                const cuuint64_t nb = shared_cache ? 1 : (cuuint64_t)B;
-                cuuint64_t dims[4] = {64, (cuuint64_t)max_kv_len, nblk, nb};
-                cuuint64_t strides[3] = {(cuuint64_t)ld * 2, 128,
-                                         shared_cache ? (cuuint64_t)ld * 2 * (cuuint64_t)max_kv_len : (cuuint64_t)seq_stride * 2};
-                cuuint32_t box[4] = {64, TILE, pass == 0 ? 2u : 3u, 1};
-                cuuint32_t es[4] = {1, 1, 1, 1};
-                CUresult r = enc(&e->m[pass], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(cache), dims, strides, box, es,
-                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-                if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(cache) failed: %d", (int)r);
-            }
-            e->key = key;
-            e->used = true;
-        }
-        tm_kv = &e->m[0];
-        tm_kr = &e->m[1];
+        int ts = cwk_mla_tensor_maps(ctx, q, cache, seq_stride, ld, max_kv_len, B, width, &tm_q, &tm_kv, &tm_kr);
+        if (ts != CWK_OK) return ts;
     }
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {

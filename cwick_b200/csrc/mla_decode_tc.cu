@@ -95,6 +95,7 @@ struct TcParams {
     int batch_coord_zero;  // all sequences read cache slice 0 (shared cache)
     uint16_t *out;         // direct mode (nsplit == 1): normalised bf16 [B][NH][L]; NULL = write partial records
     int reverse_b;         // schedule sequences last-to-first (causal prefill: longest first)
+    int halves;            // 2: blockIdx.z picks one half of the 512 value columns (two blocks share a tile's scores)
 #ifdef CWK_TRACE
     long long *trace;      // developer build only: per-phase clock64 stamps of block (0,0); NULL = off
 #endif
@@ -116,6 +117,10 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = p.reverse_b ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
+    // With few blocks in the launch (one short sequence), two blocks take each tile: both compute the tile's scores
+    // and probabilities, each accumulates and writes one half of the value columns. Half the value MMAs per block,
+    // and the records leave through twice as many SMs.
+    const int mb0 = p.halves == 2 ? 2 * (int)blockIdx.z : 0, mb1 = p.halves == 2 ? mb0 + 2 : 4;
     const int kv = p.kv_len ? p.kv_len[b] : p.kv_len_imm;
     const int ntiles = (kv + TILE - 1) / TILE;
     const int t0 = (int)((int64_t)ntiles * split / p.nsplit);
@@ -240,11 +245,13 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const uint32_t acc0 = it != 0;
 #pragma unroll
                 for (int mb = 0; mb < 4; mb++) {
+                    if (mb >= mb0 && mb < mb1) {
 #pragma unroll
-                    for (int ks = 0; ks < 8; ks++)
-                        umma_bf16(tmem + COL_O + mb * 64, dV + (uint64_t)((2 * mb * KV_BLK + ks * 2048) >> 4), dP + (uint64_t)((ks * 2048) >> 4),
-                                  ID_PV, ks != 0 ? 1u : acc0);
-                    umma_commit(bar(B_EMPTY_L + mb));
+                        for (int ks = 0; ks < 8; ks++)
+                            umma_bf16(tmem + COL_O + mb * 64, dV + (uint64_t)((2 * mb * KV_BLK + ks * 2048) >> 4), dP + (uint64_t)((ks * 2048) >> 4),
+                                      ID_PV, ks != 0 ? 1u : acc0);
+                    }
+                    umma_commit(bar(B_EMPTY_L + mb));      // also for the other half's blocks: their slots are free once the scores are done
                 }
                 umma_commit(bar(B_EMPTY_RP));
                 TRACE(1, it, 4);
@@ -381,14 +388,14 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 const float lsum = (w4[0] + w4[HG]) + (w4[2 * HG] + w4[3 * HG]);
                 if (p.out) {
                     s_alpha[st] = lsum > 0.f ? 1.f / lsum : 0.f;
-                } else {
+                } else if (mb0 == 0) {         // both halves hold the same (m, l): one writes them
                     rec[st] = s_mref[st] * 0.6931471805599453f;
                     rec[NH + st] = lsum;
                 }
             }
             if (p.out) softmax_bar();
             if (st == 0) TRACE(2, 15, 4);
-            for (int mb = 0; mb < 4 && ok; mb++) {
+            for (int mb = mb0; mb < mb1 && ok; mb++) {
                 ok = mbar_wait(bar(mb == 3 ? B_EMPTY_RP : B_EMPTY_L + mb), (uint32_t)((n - 1) & 1), p.err, 302);
                 ok = __all_sync(0xffffffffu, ok);                  // the TMEM load below is warp-wide
                 if (!ok) break;
@@ -432,39 +439,16 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     const int width = L + R;          // 576, or 512 for a rope-free latent (the rope block then reads as zeros)
     if (nh != NH) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode is built for 64 heads");
     if (max_kv_len <= 0) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode needs a non-empty cache");
-    CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
-    if (!enc) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
     {
         int es = cwk_ensure_err_word(ctx);
         if (es != CWK_OK) return es;
     }
-    CUtensorMap tm_q, tm_kv, tm_kr;
-    const cuuint64_t nblk = (cuuint64_t)(width / 64);     // 9, or 8 for a rope-free latent: block 8 is then out of range and reads as zeros
+    const CUtensorMap *tm_q = nullptr, *tm_kv = nullptr, *tm_kr = nullptr;
     {
-        // q as [64][B*NH rows][blocks]: one box brings all nine column blocks of a sequence's 64 heads
-        cuuint64_t dims[3] = {64, (cuuint64_t)B * NH, nblk};
-        cuuint64_t strides[2] = {(cuuint64_t)width * 2, 128};
-        cuuint32_t box[3] = {64, NH, NBLK};
-        cuuint32_t es[3] = {1, 1, 1};
-        CUresult r = enc(&tm_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(q), dims, strides, box, es,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(q) failed: %d", (int)r);
+        int ts = cwk_mla_tensor_maps(ctx, q, cache, seq_stride, ld, max_kv_len, B, width, &tm_q, &tm_kv, &tm_kr);
+        if (ts != CWK_OK) return ts;
     }
     const bool shared_cache = (seq_stride == 0);
-    for (int pass = 0; pass < 2; pass++) {
-        // the cache as [64][rows][blocks][sequences]; boxes of two column blocks, or three (blocks 6, 7 and the rope block)
-        const cuuint64_t nb = shared_cache ? 1 : (cuuint64_t)B;
-        cuuint64_t dims[4] = {64, (cuuint64_t)max_kv_len, nblk, nb};
-        cuuint64_t strides[3] = {(cuuint64_t)ld * 2, 128,
-                                 shared_cache ? (cuuint64_t)ld * 2 * (cuuint64_t)max_kv_len : (cuuint64_t)seq_stride * 2};
-        cuuint32_t box[4] = {64, TILE, pass == 0 ? 2u : 3u, 1};
-        cuuint32_t es[4] = {1, 1, 1, 1};
-        CUresult r = enc(pass == 0 ? &tm_kv : &tm_kr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(cache), dims, strides, box, es,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(cache) failed: %d", (int)r);
-    }
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
         CWK_CUDA(ctx, cudaFuncSetAttribute(mla_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
@@ -478,7 +462,8 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
 #endif
     p.out = (uint16_t *)out_direct;
     p.reverse_b = shared_cache ? 1 : 0;
-    mla_decode_tc_kernel<<<dim3(nsplit, B), NTHREADS, SMEM_TOTAL, ctx->stream>>>(tm_q, tm_kv, tm_kr, p);
+    p.halves = ((int64_t)nsplit * B * 2 <= ctx->sm_count) ? 2 : 1;
+    mla_decode_tc_kernel<<<dim3(nsplit, B, p.halves), NTHREADS, SMEM_TOTAL, ctx->stream>>>(*tm_q, *tm_kv, *tm_kr, p);
     CWK_LAUNCH_CHECK(ctx, "mla_decode_tc_kernel");
     return CWK_OK;
 }

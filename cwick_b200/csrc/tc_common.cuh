@@ -136,3 +136,90 @@ inline bool cwk_make_tmap_bf16_2d(CUtensorMap *tm, const void *ptr, uint64_t row
 }
 
 }  // namespace
+
+// ---- tensor maps of the MLA decode kernels, cached per context ------------------------------------------------
+// Encoding a tensor map costs about a microsecond of host time and a decode call needs three; a serving loop calls
+// with the same few (pointer, shape) combinations over and over, so each context keeps the last 64 of each kind.
+struct CwkMlaTmapKey {
+    const void *ptr;
+    int64_t a, b, c;
+    int d;
+    bool operator==(const CwkMlaTmapKey &o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c && d == o.d; }
+};
+struct CwkMlaTmapEntry {
+    CwkMlaTmapKey key;
+    CUtensorMap m[2];
+    bool used;
+};
+struct CwkMlaTmapCache {
+    static constexpr int SLOTS = 64;
+    CwkMlaTmapEntry q[SLOTS], kv[SLOTS];
+    int next_q = 0, next_kv = 0;
+    CwkMlaTmapCache() {
+        for (int i = 0; i < SLOTS; i++) q[i].used = kv[i].used = false;
+    }
+};
+
+// q as [64][B*64 heads][blocks] (one box = all column blocks of a sequence's 64 heads); the cache as
+// [64][rows][blocks][sequences] with boxes of two column blocks (tm_kv) or three (tm_kr: blocks 6, 7 and the rope block).
+// width = 576, or 512 for a rope-free latent (its ninth block is then out of range and reads as zeros).
+inline int cwk_mla_tensor_maps(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld, int max_kv_len,
+                               int B, int width, const CUtensorMap **tm_q, const CUtensorMap **tm_kv, const CUtensorMap **tm_kr) {
+    constexpr int NH_ = 64, NBLK_ = 9, TILE_ = 128;
+    CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
+    if (!enc) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
+    if (!ctx->sk_tmaps) ctx->sk_tmaps = new CwkMlaTmapCache();
+    CwkMlaTmapCache *tc = (CwkMlaTmapCache *)ctx->sk_tmaps;
+    const cuuint64_t nblk = (cuuint64_t)(width / 64);
+    {
+        const CwkMlaTmapKey key{q, B, width, 0, 0};
+        CwkMlaTmapEntry *e = nullptr;
+        for (int i = 0; i < CwkMlaTmapCache::SLOTS; i++)
+            if (tc->q[i].used && tc->q[i].key == key) { e = &tc->q[i]; break; }
+        if (!e) {
+            e = &tc->q[tc->next_q];
+            tc->next_q = (tc->next_q + 1) % CwkMlaTmapCache::SLOTS;
+            e->used = false;
+            cuuint64_t dims[3] = {64, (cuuint64_t)B * NH_, nblk};
+            cuuint64_t strides[2] = {(cuuint64_t)width * 2, 128};
+            cuuint32_t box[3] = {64, NH_, NBLK_};
+            cuuint32_t es[3] = {1, 1, 1};
+            CUresult r = enc(&e->m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(q), dims, strides, box, es,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(q) failed: %d", (int)r);
+            e->key = key;
+            e->used = true;
+        }
+        *tm_q = &e->m[0];
+    }
+    const bool shared_cache = (seq_stride == 0);
+    {
+        const CwkMlaTmapKey key{cache, seq_stride, ld, max_kv_len, shared_cache ? -width : B * 1024 + width};
+        CwkMlaTmapEntry *e = nullptr;
+        for (int i = 0; i < CwkMlaTmapCache::SLOTS; i++)
+            if (tc->kv[i].used && tc->kv[i].key == key) { e = &tc->kv[i]; break; }
+        if (!e) {
+            e = &tc->kv[tc->next_kv];
+            tc->next_kv = (tc->next_kv + 1) % CwkMlaTmapCache::SLOTS;
+            e->used = false;
+            for (int pass = 0; pass < 2; pass++) {
+                const cuuint64_t nb = shared_cache ? 1 : (cuuint64_t)B;
+                cuuint64_t dims[4] = {64, (cuuint64_t)max_kv_len, nblk, nb};
+                cuuint64_t strides[3] = {(cuuint64_t)ld * 2, 128,
+                                         shared_cache ? (cuuint64_t)ld * 2 * (cuuint64_t)max_kv_len : (cuuint64_t)seq_stride * 2};
+                cuuint32_t box[4] = {64, TILE_, pass == 0 ? 2u : 3u, 1};
+                cuuint32_t es[4] = {1, 1, 1, 1};
+                CUresult r = enc(&e->m[pass], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(cache), dims, strides, box, es,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(cache) failed: %d", (int)r);
+            }
+            e->key = key;
+            e->used = true;
+        }
+        *tm_kv = &e->m[0];
+        *tm_kr = &e->m[1];
+    }
+    return CWK_OK;
+}

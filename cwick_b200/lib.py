@@ -27,6 +27,7 @@ SIGNATURES = {
     "cwk_ctx_set_wait_limit": (i32, [vp, C.c_uint32]),
     "cwk_mla_decode_path": (i32, [vp, i32, i32, i32]),
     "cwk_ctx_force_mla_path": (i32, [vp, i32]),
+    "cwk_mla_decode_parked_records": (i32, [vp, C.POINTER(C.c_uint64)]),
     "cwk_mla_decode": (i32, [vp, vp, vp, i64, i64, vp, i32, vp, i64, i32, i32, i32, i32, f32, vp, i32]),
     "cwk_mla_decode_host": (i32, [vp, vp, vp, i64, i64, vp, vp, i64, i32, i32, i32, i32, f32, vp, i32]),
     "cwk_mla_decode_noalloc": (i32, [vp, vp, vp, i64, i64, vp, i32, i32, i32, f32, vp, C.c_char_p, C.c_size_t]),

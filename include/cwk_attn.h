@@ -75,18 +75,25 @@ CWK_API int cwk_ctx_profile_read(cwk_ctx *ctx, double *total_ms, int *launches);
  * a test of the give-up path sets a few thousand. */
 CWK_API int cwk_ctx_set_wait_limit(cwk_ctx *ctx, unsigned int polls);
 /* Which implementation the next cwk_mla_decode call would take for these
- * dimensions: 4 = persistent tcgen05/TMA kernel (one launch, blocks share
- * sequences tile by tile and reduce through f32 atomics: results can differ
- * in the last bits between runs), 2 = tcgen05/TMA kernel with split records
- * and a merge launch (reproducible bit for bit), 1 = mma.sync kernel,
- * 0 = generic. */
+ * dimensions: 2 = tcgen05/TMA kernel with split records and a merge launch
+ * (the default where it applies; reproducible bit for bit), 1 = mma.sync
+ * kernel, 0 = generic. 4 is only ever taken on request
+ * (cwk_ctx_force_mla_path): the persistent tcgen05/TMA kernel, one launch,
+ * blocks share sequences tile by tile and reduce through f32 atomics, so
+ * results can differ in the last bits between runs. */
 CWK_API int cwk_mla_decode_path(const cwk_ctx *ctx, int nh, int L, int R);
-/* Force a path (same codes; -1 = automatic). For A/B measurement, tests, and
- * callers that need run-to-run identical bits (2). In cwk_mla_prefill: 0..2 and
+/* Force a path (same codes; -1 = automatic). For A/B measurement and tests.
+ * In cwk_mla_prefill: 0..2 and
  * 4 also select the absorbed attention route (the decode kernel once per query
  * row) instead of the expanded-key route, and 3 keeps the expanded-key route
  * but runs the exact form of its attention kernel on every block. */
 CWK_API int cwk_ctx_force_mla_path(cwk_ctx *ctx, int path);
+/* The persistent kernel (path 4) adds a block's partial sums into a shared
+ * accumulator only while the block's own reference exponent stays within 2^64
+ * of the sequence's common one; beyond that the block parks a full record that
+ * the finishing block merges properly. This counts the records parked on the
+ * context so far (a statistic; tests use it to know that path was taken). */
+CWK_API int cwk_mla_decode_parked_records(cwk_ctx *ctx, uint64_t *count);
 
 /* ---- MLA absorbed decode ---------------------------------------------------
  * Replaces the attention reduction inside mla_latent_decode

@@ -12,7 +12,8 @@
  * sources produced (tests/golden).
  *
  * Plain C11, no SIMD, built with -O2 -ffp-contract=off so no FMA contraction
- * changes a last bit between hosts.
+ * changes a last bit between hosts; the few places where the reference's only
+ * code path is NEON with fused multiply-adds say fmaf explicitly.
  */
 #include <math.h>
 #include <pthread.h>
@@ -639,20 +640,31 @@ ORC_API void orc_ds_sparse_attn(const float *q, const float *kv, const int *idx,
 /* ------------------------------------------------------------------ */
 
 /* The reference's dot is NEON-only (src/q35_model.c:1425-1437): four 4-lane
- * accumulators over 16-element steps, then (s0+s1)+(s2+s3) lane-wise and a
- * horizontal add. The scalar image of that: 16 strided accumulators, lane j of
- * vector v is element 4v+j; vaddvq adds lanes pairwise ((l0+l1)+(l2+l3)). */
+ * accumulators over 16-element steps, each step a fused multiply-add
+ * (vfmaq_f32: one rounding), then (s0+s1)+(s2+s3) lane-wise and a horizontal
+ * add. The scalar image of that: 16 strided accumulators updated with fmaf,
+ * lane j of vector v is element 4v+j; vaddvq adds lanes pairwise
+ * ((l0+l1)+(l2+l3)); the tail is plain multiply then add. */
 static float dot_q35(const float *a, const float *b, int n) {
     float acc[16] = {0};
     int i = 0;
     for (; i + 16 <= n; i += 16)
-        for (int u = 0; u < 16; u++) acc[u] += a[i + u] * b[i + u];
+        for (int u = 0; u < 16; u++) acc[u] = fmaf(a[i + u], b[i + u], acc[u]);
     float lane[4];
     for (int j = 0; j < 4; j++)
         lane[j] = (acc[j] + acc[4 + j]) + (acc[8 + j] + acc[12 + j]);
     float s = (lane[0] + lane[1]) + (lane[2] + lane[3]);
     for (; i < n; i++) s += a[i] * b[i];
     return s;
+}
+
+/* o += w * v as q35_axpy_f32 does it (src/q35_model.c:1439-1448): fused
+ * multiply-adds over whole groups of 8, plain multiply then add on the tail. */
+static void axpy_q35(float *o, const float *v, float w, int n) {
+    int i = 0;
+    for (; i + 8 <= n; i += 8)
+        for (int u = 0; u < 8; u++) o[i + u] = fmaf(w, v[i + u], o[i + u]);
+    for (; i < n; i++) o[i] += w * v[i];
 }
 
 /* Single-query GQA decode. q f32 [nh][hd]; K,V bf16 [keys][nkv][hd] (the
@@ -684,8 +696,7 @@ ORC_API void orc_gqa_decode(const float *q, const uint16_t *K, const uint16_t *V
             for (int h = 0; h < nh; h++) {
                 float w = scores[(size_t)h * keys + t];
                 if (w == 0.0f) continue;
-                const float *v = row + (size_t)(h / group) * hd;
-                for (int i = 0; i < hd; i++) o[(size_t)h * hd + i] += w * v[i];
+                axpy_q35(o + (size_t)h * hd, row + (size_t)(h / group) * hd, w, hd);
             }
         }
     }
@@ -1180,6 +1191,186 @@ ORC_API void orc_ds_out_unrope(float *o, int rows, int n, const float *freq, int
     }
 }
 
+/* Quantise-dequantise to E4M3 with a power-of-two scale per 32 values: what the
+ * window KV row goes through before it is stored. src/ds_ops.c:235-252
+ * (ds_qdq_fp8_e8m0): amax floor 1e-4, scale 2^ceil(log2(amax/448)), clamp to
+ * +-448, the reference's own E4M3 encoder. */
+ORC_API void orc_ds_qdq_fp8_e8m0(float *x, int n) {
+    for (int b = 0; b < n; b += 32) {
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) {
+            float a = x[b + i] < 0 ? -x[b + i] : x[b + i];
+            if (a > amax) amax = a;
+        }
+        if (amax < 1e-4f) amax = 1e-4f;
+        float s = ldexpf(1.0f, log2_ceil_of(amax * (1.0f / 448.0f)));
+        for (int i = 0; i < 32; i++) {
+            float q = x[b + i] / s;
+            if (q > 448.0f) q = 448.0f;
+            if (q < -448.0f) q = -448.0f;
+            x[b + i] = orc_e4m3_to_f32(orc_f32_to_e4m3_ref(q)) * s;
+        }
+    }
+}
+
+/* Plain bf16 projection, one accumulator per row, K additions in order: the form
+ * of ds_bf16_gemv the reference runs off Apple silicon (src/ds_quant.c:896-908;
+ * its NEON form, :924-950, keeps four partial sums). round != 0 rounds the
+ * result to bf16 (ds_lin_bf16, src/ds_model.c:889-893). */
+ORC_API void orc_ds_lin_bf16(const uint16_t *w, const float *x, int N, int K, float *out, int round) {
+    for (int n = 0; n < N; n++) {
+        float acc = 0.0f;
+        for (int k = 0; k < K; k++) acc += bf16f(w[(size_t)n * K + k]) * x[k];
+        out[n] = round ? orc_bf16_round(acc) : acc;
+    }
+}
+
+/* One DeepSeek attention layer over positions 0..n-1 of one sequence: ds_attention
+ * (src/ds_model.c:1168-1305) with ds_compress (:1002-1077) and ds_indexer (:1081-1164)
+ * inside, composed from the pieces above in the reference's order. Arguments and
+ * outputs as refdrv_ds_attention of oracle/ref_driver_ds.c (dims[17], one output row
+ * per position). The layer is a KV source and an index source when its ratio > 0. */
+ORC_API int orc_ds_attention(const int *dims, float rms_eps,
+                             const uint8_t *wq_a, const uint8_t *wq_a_s, const uint8_t *wq_b, const uint8_t *wq_b_s,
+                             const uint8_t *wkv, const uint8_t *wkv_s, const uint8_t *wo_a, const uint8_t *wo_a_s,
+                             const uint8_t *wo_b, const uint8_t *wo_b_s, const uint16_t *q_norm,
+                             const uint16_t *kv_norm, const float *sink, const uint16_t *cmp_wkv,
+                             const uint16_t *cmp_wgate, const uint16_t *cmp_norm, const uint8_t *idx_wq_b,
+                             const uint8_t *idx_wq_b_s, const uint16_t *idx_wk, const uint16_t *idx_k_norm,
+                             const uint16_t *idx_weights_proj, const float *freq, const float *subs, int n,
+                             float *qr_out, float *q_out, float *kvrow_out, float *o_out, float *og_out,
+                             float *attn_out, int *topk_out, float *scores_out, float *cmp_kv, float *idx_k,
+                             int *n_cmp) {
+    const int D = dims[0], H = dims[1], HD = dims[2], rd = dims[3], R = dims[4], OR = dims[5], G = dims[6],
+              W = dims[7], NH = dims[8], IH = dims[9], topk = dims[10], ratio = dims[11], is_cand = dims[12],
+              uses_cand = dims[13], bs = dims[14], kblocks = dims[15], maxseq = dims[16];
+    const int np = rd / 2, rr = ratio > 0 ? ratio : 1;
+    float *win = calloc((size_t)W * HD, sizeof(float));
+    float *kv_all = calloc((size_t)(W + maxseq) * HD, sizeof(float));    /* window rows then compressed rows */
+    float *cstate = calloc((size_t)rr * HD, sizeof(float)), *cscore = calloc((size_t)rr * HD, sizeof(float));
+    float *qr = malloc(sizeof(float) * R), *q = malloc(sizeof(float) * H * HD), *kv = malloc(sizeof(float) * HD);
+    float *latent = malloc(sizeof(float) * HD), *ik = malloc(sizeof(float) * (IH + 1));
+    float *q_idx = malloc(sizeof(float) * ((size_t)NH * IH + 1)), *iw = malloc(sizeof(float) * (NH + 1));
+    float *sc = malloc(sizeof(float) * (maxseq + 1)), *o = malloc(sizeof(float) * H * HD);
+    float *o_g = malloc(sizeof(float) * G * OR);
+    int *idxs = malloc(sizeof(int) * (W + topk + 1)), *top = malloc(sizeof(int) * (topk + 1));
+    uint8_t *cand = calloc((size_t)maxseq + 1, 1);
+    memset(cmp_kv, 0, sizeof(float) * (size_t)maxseq * HD);
+    memset(idx_k, 0, sizeof(float) * (size_t)maxseq * IH);
+    for (int i = 0; i < topk; i++) top[i] = 0;
+
+    for (int64_t pos = 0; pos < n; pos++) {
+        const float *sub = subs + (size_t)pos * D;
+        /* :1179-1193 query */
+        orc_ds_lin_q(sub, wq_a, wq_a_s, R, D, qr);
+        orc_ds_rmsnorm_bf16w(qr, qr, q_norm, R, rms_eps);
+        orc_ds_lin_q(qr, wq_b, wq_b_s, (int64_t)H * HD, R, q);
+        for (int h = 0; h < H; h++) {
+            float *t = q + (size_t)h * HD + (HD - rd);
+            orc_ds_rope(t, freq, np, pos);
+            for (int i = 0; i < rd; i++) t[i] = orc_bf16_round(t[i]);
+        }
+        /* :1201-1212 window KV row */
+        orc_ds_lin_q(sub, wkv, wkv_s, HD, D, kv);
+        orc_ds_rmsnorm_bf16w(kv, kv, kv_norm, HD, rms_eps);
+        orc_ds_rope(kv + HD - rd, freq, np, pos);
+        for (int i = 0; i < rd; i++) kv[HD - rd + i] = orc_bf16_round(kv[HD - rd + i]);
+        orc_ds_qdq_fp8_e8m0(kv, HD);
+        memcpy(win + (size_t)(pos % W) * HD, kv, sizeof(float) * HD);
+        /* :1216-1222 window slots, oldest first */
+        int nwin = 0;
+        {
+            int64_t lo = pos - W + 1;
+            if (lo < 0) lo = 0;
+            for (int64_t pp = lo; pp <= pos; pp++) idxs[nwin++] = (int)(pp % W);
+            while (nwin < W) idxs[nwin++] = -1;
+        }
+        int ncmp = 0;
+        for (int i = 0; i < maxseq; i++) sc[i] = 0.0f;
+        if (ratio > 0) {
+            const int nvis = (int)((pos + 1) / ratio);
+            /* ---- ds_compress :1002-1077 ---- */
+            int produced = 0, j = 0;
+            int64_t lp = 0;
+            if (ratio == 1) {
+                orc_ds_lin_bf16(cmp_wkv, sub, HD, D, latent, 1);
+                orc_ds_rmsnorm_bf16w(latent, latent, cmp_norm, HD, rms_eps);
+                j = (int)pos; lp = pos; produced = 1;
+            } else {
+                const int slot = (int)(pos % ratio);
+                orc_ds_lin_bf16(cmp_wkv, sub, HD, D, cstate + (size_t)slot * HD, 0);
+                orc_ds_lin_bf16(cmp_wgate, sub, HD, D, cscore + (size_t)slot * HD, 0);
+                if ((pos + 1) % ratio == 0) {
+                    j = (int)((pos + 1) / ratio - 1);
+                    lp = (int64_t)j * ratio;
+                    orc_ds_pool(cstate, cscore, ratio, HD, latent);
+                    orc_ds_rmsnorm_bf16w(latent, latent, cmp_norm, HD, rms_eps);
+                    produced = 1;
+                }
+            }
+            if (produced) {
+                if (topk > 0) {                         /* index key from the un-rotated latent, :1058-1068 */
+                    orc_ds_lin_bf16(idx_wk, latent, IH, HD, ik, 1);
+                    orc_ds_rmsnorm_bf16w(ik, ik, idx_k_norm, IH, rms_eps);
+                    orc_ds_rope_round_qdq(ik, 1, IH, freq, np, lp, 0, 32);
+                    memcpy(idx_k + (size_t)j * IH, ik, sizeof(float) * IH);
+                }
+                orc_ds_rope_round_qdq(latent, 1, HD, freq, np, lp, 1, 16);       /* :1071-1075 */
+                memcpy(cmp_kv + (size_t)j * HD, latent, sizeof(float) * HD);
+            }
+            /* ---- ds_indexer :1081-1164 ---- */
+            if (topk > 0) {
+                orc_ds_lin_q(qr, idx_wq_b, idx_wq_b_s, (int64_t)NH * IH, R, q_idx);
+                for (int h = 0; h < NH; h++) {
+                    float *t = q_idx + (size_t)h * IH + (IH - rd);
+                    orc_ds_rope(t, freq, np, pos);
+                    for (int i = 0; i < rd; i++) t[i] = orc_bf16_round(t[i]);
+                }
+                orc_ds_qdq_fp4_e8m0(q_idx, NH * IH);
+                orc_ds_lin_bf16(idx_weights_proj, sub, NH, D, iw, 1);
+                const float fscale = powf((float)IH, -0.5f) * powf((float)NH, -0.5f);
+                for (int h = 0; h < NH; h++) iw[h] = orc_bf16_round(iw[h] * fscale);
+                if (nvis <= 0) {
+                    top[0] = -1;
+                } else {
+                    orc_ds_indexer_scores(idx_k, nvis, IH, q_idx, iw, NH, sc);
+                    if (is_cand) orc_ds_candidates(sc, nvis, bs, kblocks, cand);
+                    else if (uses_cand)
+                        for (int t = 0; t < nvis; t++) if (!cand[t]) sc[t] = -INFINITY;
+                    const int cnt = nvis < topk ? nvis : topk;
+                    const int got = orc_ds_topk(sc, nvis, cnt, top);
+                    for (int i = 0; i < got; i++) top[i] += W;
+                    for (int i = got; i < cnt; i++) top[i] = -1;
+                }
+            }
+            ncmp = nvis < topk ? nvis : topk;
+            for (int jj = 0; jj < ncmp; jj++) idxs[W + jj] = top[jj];
+        }
+        /* ---- ds_sparse_attn :917-966 over window rows then compressed rows ---- */
+        memcpy(kv_all, win, sizeof(float) * (size_t)W * HD);
+        memcpy(kv_all + (size_t)W * HD, cmp_kv, sizeof(float) * (size_t)maxseq * HD);
+        orc_ds_sparse_attn(q, kv_all, idxs, W + ncmp, H, HD, sink, powf((float)HD, -0.5f), o);
+        orc_ds_out_unrope(o, H, HD, freq, np, pos);                  /* :1256-1272 */
+        /* :1279-1303 grouped wo_a, then wo_b */
+        const int per = H * HD / G;
+        for (int g = 0; g < G; g++)
+            orc_ds_lin_q(o + (size_t)g * per, wo_a + (size_t)g * OR * per, wo_a_s + (size_t)(g * OR / 32) * (per / 32), OR, per,
+                         o_g + (size_t)g * OR);
+        memcpy(qr_out + (size_t)pos * R, qr, sizeof(float) * R);
+        memcpy(q_out + (size_t)pos * H * HD, q, sizeof(float) * H * HD);
+        memcpy(kvrow_out + (size_t)pos * HD, kv, sizeof(float) * HD);
+        memcpy(o_out + (size_t)pos * H * HD, o, sizeof(float) * H * HD);
+        memcpy(og_out + (size_t)pos * G * OR, o_g, sizeof(float) * G * OR);
+        orc_ds_lin_q(o_g, wo_b, wo_b_s, D, (int64_t)G * OR, attn_out + (size_t)pos * D);
+        if (topk > 0) memcpy(topk_out + (size_t)pos * topk, top, sizeof(int) * topk);
+        memcpy(scores_out + (size_t)pos * maxseq, sc, sizeof(float) * maxseq);
+    }
+    *n_cmp = ratio > 0 ? n / ratio : 0;
+    free(win); free(kv_all); free(cstate); free(cscore); free(qr); free(q); free(kv); free(latent); free(ik);
+    free(q_idx); free(iw); free(sc); free(o); free(o_g); free(idxs); free(top); free(cand);
+    return 0;
+}
+
 /* ------------------------------------------------------------------ */
 /* KDA (gated delta-rule linear attention) decode step                 */
 /* ------------------------------------------------------------------ */
@@ -1280,9 +1471,9 @@ ORC_API void orc_kda_step(int nh, int hd, float lower, float rms_eps, float *q, 
  * one pass, delta = beta (v_j - dot), then the row takes k delta and is dotted
  * with q; the head's outputs go through the gated RMS norm (plain weight,
  * silu of the gate). `up` rows are [q heads | k heads | v heads] after the
- * convolution, SiLU and the q/k normalisation (:1286-1372). The reference's model
- * file does not build off its own platform, so this restatement follows its text
- * and is not checked against its execution: parity unpinned. */
+ * convolution, SiLU and the q/k normalisation (:1286-1372). Pinned bit for bit
+ * against lin_rec_heads itself, reached through oracle/ref_driver_q35.c
+ * (tests/test_oracle_pin_statics.py). */
 static float q35_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 static float q35_silu(float x) { return x / (1.0f + expf(-x)); }
 ORC_API void orc_gdn_scan(int n, int nh, int head_k, int head_v, int kv_group, const float *up,
@@ -1329,9 +1520,10 @@ ORC_API void orc_gdn_scan(int n, int nh, int head_k, int head_v, int kv_group, c
 /* ------------------------------------------------------------------ */
 /* MiniMax block indexer and attention over the selected blocks        */
 /* ------------------------------------------------------------------ */
-/* The reference's model file (src/mm_model.c) does not build off its own platform
- * (unguarded NEON inside its forward function); these follow its text, scalar
- * branches: parity unpinned. */
+/* mm_index_scores and mm_select_blocks are pinned bit for bit against the reference's
+ * own static functions, reached through oracle/ref_driver_mm.c (the model file builds
+ * against oracle/shim/arm_neon.h); the attention over the selected positions is inline in
+ * its forward function and follows its text (scalar branch): that one piece is unpinned. */
 
 /* Per-position index score: sum over heads of ReLU(q_h . k), bf16 keys,
  * sequential f32 dots. src/mm_model.c:1765-1781 (mm_index_scores). */

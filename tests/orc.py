@@ -29,6 +29,12 @@ def P(a, t):
 _oracle = None
 _ref = None
 
+# the weight, input and output pointers of one DeepSeek attention layer, shared by orc_ds_attention and
+# refdrv_ds_attention: 10 quantised weight/scale pointers, q_norm, kv_norm, sink, cmp_wkv, cmp_wgate, cmp_norm,
+# idx_wq_b + scale, idx_wk, idx_k_norm, idx_weights_proj, freq, subs, n, then the outputs
+DS_LAYER_ARGS = [u8p] * 10 + [u16p, u16p, f32p, u16p, u16p, u16p, u8p, u8p, u16p, u16p, u16p, f32p, f32p, C.c_int,
+                             f32p, f32p, f32p, f32p, f32p, f32p, i32p, f32p, f32p, f32p, i32p]
+
 
 def oracle():
     global _oracle
@@ -109,6 +115,10 @@ def oracle():
         L.orc_mm_sparse_attn.argtypes = [f32p, u16p, u16p, i64p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, f32p]
         L.orc_ds_candidates.restype = C.c_int
         L.orc_ds_candidates.argtypes = [f32p, C.c_int, C.c_int, C.c_int, u8p]
+        L.orc_ds_qdq_fp8_e8m0.argtypes = [f32p, C.c_int]
+        L.orc_ds_lin_bf16.argtypes = [u16p, f32p, C.c_int, C.c_int, f32p, C.c_int]
+        L.orc_ds_attention.restype = C.c_int
+        L.orc_ds_attention.argtypes = [i32p, C.c_float] + DS_LAYER_ARGS
         _oracle = L
     return _oracle
 
@@ -156,6 +166,26 @@ def ref():
                                                 C.c_float, C.c_int, C.c_int, C.c_int] + \
             [C.c_void_p] * 7 + [C.c_void_p] * 4 + [f32p, f32p, C.c_void_p] + \
             [C.c_void_p, C.c_int64, C.c_int64, f32p, f32p, i64p, i64p, f32p, f32p, f32p, f32p]
+        if hasattr(L, "refdrv_ds_attention"):
+            L.refdrv_ds_sparse_attn.argtypes = [f32p, f32p, f32p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, f32p,
+                                                C.c_float, f32p, f32p]
+            L.refdrv_ds_attention.restype = C.c_int
+            L.refdrv_ds_attention.argtypes = [i32p, f32p] + DS_LAYER_ARGS
+            L.refdrv_ds_freqs.argtypes = [C.c_int, C.c_double, C.c_double, C.c_int, C.c_int, C.c_int, f32p]
+        if hasattr(L, "ds_qdq_fp8_e8m0"):
+            L.ds_qdq_fp8_e8m0.argtypes = [f32p, C.c_int]
+        if hasattr(L, "refdrv_q35_decode_attn"):
+            L.refdrv_q35_qk_prep.argtypes = [f32p, f32p, f32p, f32p, C.c_float, C.c_int, C.c_double, C.c_int64, C.c_int,
+                                             C.c_int, C.c_int, C.c_int, f32p, f32p]
+            L.refdrv_q35_decode_attn.argtypes = [f32p, f32p, f32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, f32p]
+            L.refdrv_q35_prefill_attn.argtypes = [f32p, f32p, f32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                  C.c_float, f32p]
+            L.refdrv_q35_gate.argtypes = [f32p, f32p, C.c_int, C.c_int, C.c_int]
+            L.refdrv_q35_gdn.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int] + [f32p] * 7 + [C.c_float, f32p, f32p]
+        if hasattr(L, "refdrv_mm_index_scores"):
+            L.refdrv_mm_index_scores.argtypes = [u16p, C.c_int64, C.c_int, f32p, C.c_int, f32p]
+            L.refdrv_mm_select_blocks.restype = C.c_int
+            L.refdrv_mm_select_blocks.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, i32p]
         _ref = L
     return _ref
 

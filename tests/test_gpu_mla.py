@@ -235,15 +235,20 @@ def test_persistent_kernel_shares_sequences_between_blocks(attn):
     q, cache = make_case(41, B, 64, T)
     lens = np.array([2100, 129, 0, 1500, 777], np.int32)
     want = oracle_out(q, cache, lens)
-    assert cwk_path(attn) == 4
-    for n_splits in (0, 1, 2, 3, 7):
-        for _ in range(2):
-            got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE,
-                                  n_splits=n_splits)
-            attn.ctx.sync()
-            g = bf16_to_np(got)
-            assert np.all(g[2] == 0)
-            close(g, want)
+    assert cwk_path(attn) == 2
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, 4)
+    try:
+        assert cwk_path(attn) == 4
+        for n_splits in (0, 1, 2, 3, 7):
+            for _ in range(2):
+                got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE,
+                                      n_splits=n_splits)
+                attn.ctx.sync()
+                g = bf16_to_np(got)
+                assert np.all(g[2] == 0)
+                close(g, want)
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
 
 
 def test_persistent_kernel_many_short_sequences(attn):
@@ -258,14 +263,14 @@ def test_persistent_kernel_many_short_sequences(attn):
     lens = rng.integers(0, T + 1, B).astype(np.int32)
     lens[:3] = [T, 0, 1]
     want = oracle_out(q, cache, lens)
-    for n_splits in (0, 1):            # 0: one block per SM; 1: capped at B blocks
-        got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE,
-                              n_splits=n_splits, max_kv_len=T)
-        attn.ctx.sync()
-        close(bf16_to_np(got), want)
-    # two blocks for all 300 sequences: about 150 segments each, four table fills
     attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, 4)
     try:
+        for n_splits in (0, 1):            # 0: one block per SM; 1: capped at B blocks
+            got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE,
+                                  n_splits=n_splits, max_kv_len=T)
+            attn.ctx.sync()
+            close(bf16_to_np(got), want)
+        # two blocks for all 300 sequences: about 150 segments each, four table fills
         got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE,
                               n_splits=-2, max_kv_len=T)
         attn.ctx.sync()
@@ -282,20 +287,29 @@ def test_persistent_kernel_parks_records_that_outran_the_common_reference(attn):
     q, cache = make_case(47, 1, 64, T)
     qf = synth.bf16_to_f32(q)
     cf = synth.bf16_to_f32(cache)
-    cf[0, 0, :L] = -0.25 * np.sign(qf[0, 0, :L] + 1e-6)          # row 0 against head 0's query: a large negative score
-    cf[0, 1:, :L] = 0.5 * np.abs(cf[0, 1:, :L]) * np.sign(qf[0, :1, :L] + 1e-6)   # the others with it
+    cf[0, 0, :L] = -1.5 * np.sign(qf[0, 0, :L] + 1e-6)          # row 0 against head 0's query: about -44 after scaling
+    cf[0, 1:, :L] = np.abs(cf[0, 1:, :L]) * np.sign(qf[0, :1, :L] + 1e-6)     # the others with it: about +24
     cache = synth.f32_to_bf16(cf).reshape(cache.shape)
     lens = np.array([T], np.int32)
     want = oracle_out(q, cache, lens)
-    for _ in range(2):
-        got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+    import ctypes as C
+    parked0, parked1 = C.c_uint64(0), C.c_uint64(0)
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, 4)
+    try:
+        attn.ctx.check(attn.lib.cwk_mla_decode_parked_records(attn.ctx.h, C.byref(parked0)))
+        for _ in range(2):
+            got = attn.mla_decode(to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda(), scale=SCALE)
+            attn.ctx.sync()
+            close(bf16_to_np(got), want)
+        attn.ctx.check(attn.lib.cwk_mla_decode_parked_records(attn.ctx.h, C.byref(parked1)))
+        assert parked1.value > parked0.value, "the inputs were meant to make blocks park their records"
+        # and an ordinary call afterwards finds pool, tags and counters clean
+        q2, cache2 = make_case(48, 1, 64, 900)
+        got = attn.mla_decode(to_bf16_cuda(q2), to_bf16_cuda(cache2), torch.from_numpy(np.array([900], np.int32)).cuda(), scale=SCALE)
         attn.ctx.sync()
-        close(bf16_to_np(got), want)
-    # and an ordinary call afterwards finds pool, tags and counters clean
-    q2, cache2 = make_case(48, 1, 64, 900)
-    got = attn.mla_decode(to_bf16_cuda(q2), to_bf16_cuda(cache2), torch.from_numpy(np.array([900], np.int32)).cuda(), scale=SCALE)
-    attn.ctx.sync()
-    close(bf16_to_np(got), oracle_out(q2, cache2, np.array([900], np.int32)))
+        close(bf16_to_np(got), oracle_out(q2, cache2, np.array([900], np.int32)))
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
 
 
 def cwk_path(attn):
