@@ -83,8 +83,13 @@ struct RopeTable {
 // One block per row: rotary + bf16 rounding of the last 2*npairs values, then the row's quantise/dequantise.
 // mode 0: scale 2^ceil(log2(amax/6)) per 32 values (src/ds_ops.c:254-272); mode 1: scale = E4M3(amax/6) per
 // `block` values (:274-293); mode 2: the attention output before its projections (src/ds_model.c:1258-1272):
-// the whole row is rounded to bf16 first, the table holds the inverse rotation, nothing is quantised.
-__global__ void __launch_bounds__(DC_THREADS) ds_rope_round_qdq_kernel(float *x, int n, int npairs, const RopeTable tab, int mode, int block) {
+// the whole row is rounded to bf16 first, the table holds the inverse rotation, nothing is quantised;
+// mode 3: rotation and rounding only (the query heads, src/ds_model.c:1188-1193); mode 4: E4M3 with a
+// power-of-two scale per 32 values (ds_qdq_fp8_e8m0, src/ds_ops.c:235-252: amax floor 1e-4, scale
+// 2^ceil(log2(amax / 448)), clamp to +-448, the reference's own encoder), the window KV row (:1201-1205).
+// copy_to (optional): row r is also written to copy_to + r*n (the window ring slot, :1211-1212).
+__global__ void __launch_bounds__(DC_THREADS) ds_rope_round_qdq_kernel(float *x, int n, int npairs, const RopeTable tab, int mode, int block,
+                                                                       float *copy_to) {
     extern __shared__ float xs[];
     float *row = x + (int64_t)blockIdx.x * n;
     for (int i = threadIdx.x; i < n; i += blockDim.x) xs[i] = mode == 2 ? bf16_round_rne(row[i]) : row[i];
@@ -96,12 +101,24 @@ __global__ void __launch_bounds__(DC_THREADS) ds_rope_round_qdq_kernel(float *x,
         t[2 * i + 1] = bf16_round_rne(__fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c)));
     }
     __syncthreads();
-    const int bl = mode == 0 ? 32 : block;
-    for (int g = threadIdx.x; mode != 2 && g < n / bl; g += blockDim.x) {
+    const int bl = (mode == 0 || mode == 4) ? 32 : block;
+    for (int g = threadIdx.x; mode != 2 && mode != 3 && g < n / bl; g += blockDim.x) {
         float *v = xs + g * bl;
         float amax = 0.f;
         for (int i = 0; i < bl; i++) amax = fmaxf(amax, fabsf(v[i]));
         float sc;
+        if (mode == 4) {
+            if (amax < 1e-4f) amax = 1e-4f;
+            const uint32_t u = __float_as_uint(__fmul_rn(amax, 1.0f / 448.0f));
+            const int e = (int)((u >> 23) & 0xFFu) - 127 + ((u & 0x7FFFFFu) ? 1 : 0);
+            sc = __uint_as_float((uint32_t)(e + 127) << 23);
+            for (int i = 0; i < bl; i++) {
+                float q = __fdiv_rn(v[i], sc);
+                q = fminf(fmaxf(q, -448.f), 448.f);
+                v[i] = __fmul_rn(e4m3_quantise_dequantise_ref(q), sc);
+            }
+            continue;
+        }
         if (mode == 0) {
             const float fl = 6.0f * 1.1754943508222875e-38f;              // 6 * 2^-126
             if (amax <= fl) {
@@ -123,7 +140,10 @@ __global__ void __launch_bounds__(DC_THREADS) ds_rope_round_qdq_kernel(float *x,
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) row[i] = xs[i];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        row[i] = xs[i];
+        if (copy_to) copy_to[(int64_t)blockIdx.x * n + i] = xs[i];
+    }
 }
 
 // Maximum of every block of bs scores; the last block is forced in with +inf; word [nblk_out] gets the count.
@@ -181,11 +201,11 @@ int cwk_ds_rmsnorm_bf16w(cwk_ctx *ctx, const float *x, const void *w, int rows, 
 }
 
 static int rope_rows_launch(cwk_ctx *ctx, const char *what, float *x, int rows, int n, const float *freq, int npairs, int64_t pos,
-                            int mode, int block) {
+                            int mode, int block, float *copy_to = nullptr) {
     if (!ctx || !x || rows <= 0 || n <= 0 || n > 8192 || npairs < 0 || npairs > 64 || 2 * npairs > n || (npairs && !freq))
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "%s: bad argument", what);
-    const int bl = mode == 0 ? 32 : block;
-    if (mode != 2 && ((mode != 0 && mode != 1) || bl <= 0 || bl > 128 || n % bl))
+    const int bl = (mode == 0 || mode == 4) ? 32 : block;
+    if (mode != 2 && mode != 3 && ((mode != 0 && mode != 1 && mode != 4) || bl <= 0 || bl > 128 || n % bl))
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "%s: the row length must be a multiple of the scale block (<= 128)", what);
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     RopeTable tab;
@@ -196,15 +216,21 @@ static int rope_rows_launch(cwk_ctx *ctx, const char *what, float *x, int rows, 
         if (mode == 2) tab.s[i] = -tab.s[i];
     }
     for (int i = npairs; i < 64; i++) tab.c[i] = tab.s[i] = 0.f;
-    ds_rope_round_qdq_kernel<<<rows, DC_THREADS, n * sizeof(float), ctx->stream>>>(x, n, npairs, tab, mode, block);
+    ds_rope_round_qdq_kernel<<<rows, DC_THREADS, n * sizeof(float), ctx->stream>>>(x, n, npairs, tab, mode, block, copy_to);
     CWK_LAUNCH_CHECK(ctx, "ds_rope_round_qdq_kernel");
     return CWK_OK;
 }
 
 int cwk_ds_rope_round_qdq(cwk_ctx *ctx, float *x, int rows, int n, const float *freq, int npairs, int64_t pos, int mode,
                           int block) {
-    if (mode != 0 && mode != 1) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_rope_round_qdq: mode is 0 or 1");
-    return rope_rows_launch(ctx, "ds_rope_round_qdq", x, rows, n, freq, npairs, pos, mode, block);
+    if (mode < 0 || mode > 3) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_rope_round_qdq: mode is 0..3");
+    // public 2 = rotation and rounding only, 3 = E4M3 with power-of-two scales (kernel modes 3 and 4; 2 is the un-rotation)
+    return rope_rows_launch(ctx, "ds_rope_round_qdq", x, rows, n, freq, npairs, pos, mode >= 2 ? mode + 1 : mode, block);
+}
+
+int cwk_ds_kv_row_store(cwk_ctx *ctx, float *kv, int n, const float *freq, int npairs, int64_t pos, float *win_kv, int window) {
+    if (!win_kv || window <= 0 || pos < 0) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "ds_kv_row_store: bad argument");
+    return rope_rows_launch(ctx, "ds_kv_row_store", kv, 1, n, freq, npairs, pos, 4, 32, win_kv + (pos % window) * (int64_t)n);
 }
 
 int cwk_ds_out_unrope(cwk_ctx *ctx, float *o, int rows, int n, const float *freq, int npairs, int64_t pos) {

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(128) fold_push_kernel(const float *partial, in
 
 // grid (nh), 128 threads. Waits on the OWN window only.
 __global__ void __launch_bounds__(128) wait_merge_kernel(float *own, int nh, int D, int world, uint32_t epoch, uint16_t *out,
-                                                         int *err) {
+                                                         int *err, unsigned int wait_limit) {
     const int h = blockIdx.x, tid = threadIdx.x;
     const int parity = (int)(epoch & 1u);
     __shared__ int s_ok;
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(128) wait_merge_kernel(float *own, int nh, int
             for (;;) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f + g) : "memory");
                 if (v == epoch) break;
-                if (++spins > (1u << 22)) { ok = 0; break; }      // ~1 s: a peer never published
+                if (++spins > wait_limit) { ok = 0; break; }      // default ~1 s: a peer never published
                 __nanosleep(200);
             }
         }
@@ -214,7 +214,8 @@ int cwk_mla_decode_kv_split(cwk_ctx *ctx, const void *q, const void *cache, int6
     for (int g = 0; g < MAX_WORLD; g++) pw.win[g] = (g < world) ? (float *)windows[g] : nullptr;
     fold_push_kernel<<<nh, 128, 0, ctx->stream>>>(partial, ns, nh, L, pw, rank, world, epoch, (unsigned int *)ctx->ticket);
     CWK_LAUNCH_CHECK(ctx, "fold_push_kernel");
-    wait_merge_kernel<<<nh, 128, 0, ctx->stream>>>((float *)windows[rank], nh, L, world, epoch, (uint16_t *)out, ctx->dev_err);
+    wait_merge_kernel<<<nh, 128, 0, ctx->stream>>>((float *)windows[rank], nh, L, world, epoch, (uint16_t *)out, ctx->dev_err,
+                                                 ctx->wait_limit);
     CWK_LAUNCH_CHECK(ctx, "wait_merge_kernel");
     return CWK_OK;
 }

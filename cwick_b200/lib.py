@@ -63,6 +63,7 @@ SIGNATURES = {
     "cwk_ds_pool_norm": (i32, [vp, vp, vp, i32, i32, i32, vp, f32, vp]),
     "cwk_ds_rmsnorm_bf16w": (i32, [vp, vp, vp, i32, i32, f32, vp]),
     "cwk_ds_rope_round_qdq": (i32, [vp, vp, i32, i32, vp, i32, i64, i32, i32]),
+    "cwk_ds_kv_row_store": (i32, [vp, vp, i32, vp, i32, i64, vp, i32]),
     "cwk_ds_out_unrope": (i32, [vp, vp, i32, i32, vp, i32, i64]),
     "cwk_ds_candidates": (i32, [vp, vp, i32, i32, i32, vp]),
     "cwk_ds_mask_candidates": (i32, [vp, vp, vp, i32]),

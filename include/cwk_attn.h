@@ -393,10 +393,18 @@ CWK_API int cwk_ds_rmsnorm_bf16w(cwk_ctx *ctx, const float *x, const void *w, in
  * of every row at position pos (freq: HOST array [npairs] of ds_freqs.freq; the angles' cos/sin are formed
  * on the host in double as src/ds_ops.c:51-52 does), bf16 rounding of those values, then
  * mode 0: ds_qdq_fp4_e8m0 (src/ds_ops.c:254-272, scale per 32), mode 1: ds_qdq_fp4_e4m3 (:274-293, scale per
- * `block`). n must be a multiple of the scale block. The e2m1 rounding is the reference's as written
+ * `block`), mode 2: nothing more (the query heads of ds_attention, src/ds_model.c:1188-1193), mode 3:
+ * ds_qdq_fp8_e8m0 (src/ds_ops.c:235-252: E4M3 with a power-of-two scale per 32, the window KV row). n must be a
+ * multiple of the scale block. The e2m1 rounding is the reference's as written
  * (src/ds_ops.c:212-226: magnitudes 0, 1, 2, 4, 6). Subnormal inputs (below 2^-126) count as zero. */
 CWK_API int cwk_ds_rope_round_qdq(cwk_ctx *ctx, float *x, int rows, int n, const float *freq, int npairs, int64_t pos,
                                   int mode, int block);
+/* The window KV row of ds_attention (src/ds_model.c:1201-1212) after its projection and norm (cwk_ds_lin_q,
+ * cwk_ds_rmsnorm_bf16w): ds_rope on the last 2*npairs values at `pos`, bf16 rounding of those, ds_qdq_fp8_e8m0 of
+ * the row, in place on kv f32 [n] (device), and the finished row stored into the layer's ring,
+ * win_kv f32 [window][n] (device), at slot pos % window. */
+CWK_API int cwk_ds_kv_row_store(cwk_ctx *ctx, float *kv, int n, const float *freq, int npairs, int64_t pos, float *win_kv,
+                                int window);
 /* The attention output before its projections (src/ds_model.c:1258-1272), in place on o f32 [rows = heads][n]:
  * every value rounded to bf16, the query rotation undone on each row's last 2*npairs values (ds_rope with
  * inverse = 1), those rounded again. The grouped wo_a and wo_b that follow (:1279-1303) are cwk_ds_lin_q calls:

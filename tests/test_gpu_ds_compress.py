@@ -89,6 +89,45 @@ def test_row_finishing_equals_the_oracle(attn, G, name, mode, block):
             assert np.array_equal(got, want), (rows, n, pos)
 
 
+def test_query_heads_and_window_kv_row(attn, G):
+    """The two row forms of ds_attention that were missing: query heads (rotation + bf16 rounding, nothing quantised,
+    src/ds_model.c:1188-1193) and the window KV row (rotation, rounding, ds_qdq_fp8_e8m0, ring store at pos % W,
+    :1201-1212). Bit for bit against the oracle, whose fp8 round trip is pinned to the reference's function."""
+    o = orc.oracle()
+    freq = np.ascontiguousarray(G["freq_plain"])
+    npairs = freq.size
+    for pos in (0, 7, 4095):
+        x = (synth.normal(SEED, 821 + pos % 97, 64 * 512) * 2).astype(np.float32)
+        want = x.copy().reshape(64, 512)
+        for h in range(64):
+            t = np.ascontiguousarray(want[h, 512 - 2 * npairs:])
+            o.orc_ds_rope(P(t, f32p), P(freq, f32p), npairs, pos)
+            want[h, 512 - 2 * npairs:] = [o.orc_bf16_round(float(v)) for v in t]
+        got = qdq(attn, x, 64, 512, freq, pos, 2, 0)
+        assert np.array_equal(got, want.reshape(-1)), pos
+    W, n = 8, 512
+    win = torch.zeros(W, n, dtype=torch.float32, device="cuda")
+    rows = {}
+    for pos in (0, 3, 9, 17):
+        x = (synth.normal(SEED, 830 + pos, n) * np.repeat(np.exp2(synth.normal(SEED, 831 + pos, n // 32) * 6), 32)).astype(np.float32)
+        want = x.copy()
+        t = np.ascontiguousarray(want[n - 2 * npairs:])
+        o.orc_ds_rope(P(t, f32p), P(freq, f32p), npairs, pos)
+        want[n - 2 * npairs:] = [o.orc_bf16_round(float(v)) for v in t]
+        o.orc_ds_qdq_fp8_e8m0(P(want, f32p), n)
+        kv = cu(x)
+        attn.ctx.check(attn.lib.cwk_ds_kv_row_store(attn.ctx.h, dp(kv), n, hostf(freq), npairs, pos, dp(win), W))
+        attn.ctx.sync()
+        assert np.array_equal(kv.cpu().numpy(), want), pos
+        rows[pos % W] = want
+        # mode 3 of the row finisher is the same quantiser without the ring
+        assert np.array_equal(qdq(attn, x, 1, n, freq, pos, 3, 32), want)
+    w = win.cpu().numpy()
+    for slot, want in rows.items():
+        assert np.array_equal(w[slot], want), slot
+    assert not w[2].any() and not w[4].any()            # untouched slots stay as they were
+
+
 @pytest.mark.parametrize("n", [128, 512])
 def test_norm_equals_the_reference(attn, G, n):
     x, w = G["rms_in_%d" % n], G["rms_w_%d" % n]

@@ -109,3 +109,50 @@ def test_peer_exchange_entry_point_on_one_gpu():
         attn.ctx.sync()
         assert float((got.float() - want.float()).abs().max()) <= 4e-3
     x.close()
+
+
+def test_a_peer_that_never_publishes_is_reported_and_the_context_stays_usable():
+    """Failure detection without a fault: rank 0 of a pretended world of 2 runs its step against a second local
+    window standing in for the peer's. Nothing ever publishes the peer's slot of the own window, so the merge
+    kernel's bounded wait runs out (the limit is a context setting, a few thousand polls here), the kernel records
+    that and returns, cwk_ctx_sync answers CWK_ERR_STATE, and the next ordinary call on the same context is right."""
+    import ctypes as C
+    from cwick_b200 import lib as cl
+    from cwick_b200.ops import Attn
+    attn = Attn(0)
+    lib, ctx = attn.lib, attn.ctx
+    g = torch.Generator(device="cuda").manual_seed(9)
+    T = 1000
+    q = torch.randn(NH, L + R, device="cuda", generator=g).to(torch.bfloat16)
+    cache = torch.randn(T, L + R, device="cuda", generator=g).to(torch.bfloat16)
+    own, peer = C.c_void_p(), C.c_void_p()
+    ctx.check(lib.cwk_xchg_create(ctx.h, NH, L, 2, C.byref(own), None))
+    ctx.check(lib.cwk_xchg_create(ctx.h, NH, L, 2, C.byref(peer), None))
+    windows = (C.c_void_p * 2)(own.value, peer.value)
+    out = torch.zeros(NH, L, dtype=torch.bfloat16, device="cuda")
+    ctx.check(lib.cwk_ctx_set_wait_limit(ctx.h, 4000))
+    try:
+        ctx.check(lib.cwk_mla_decode_kv_split(ctx.h, C.c_void_p(q.data_ptr()), C.c_void_p(cache.data_ptr()), L + R, T, NH, L, R,
+                                              SCALE, windows, 0, 2, 1, C.c_void_p(out.data_ptr())))
+        with pytest.raises(cl.CwkError) as e:
+            ctx.sync()
+        assert e.value.status == cl.ERR_STATE
+        assert "bounded wait" in str(e.value)
+    finally:
+        ctx.check(lib.cwk_ctx_set_wait_limit(ctx.h, 1 << 22))
+    # the context is still usable and the error does not stick
+    lens = torch.tensor([T], dtype=torch.int32, device="cuda")
+    got = attn.mla_decode(q[None], cache[None], lens, scale=SCALE, max_kv_len=T)[0]
+    ctx.sync()
+    one = (C.c_void_p * 1)(own.value)
+    # a real world of 1 on the same window (epoch 2: the parity not used by the failed step)
+    ctx.check(lib.cwk_xchg_destroy(ctx.h, peer))
+    ctx.check(lib.cwk_xchg_destroy(ctx.h, own))
+    own1 = C.c_void_p()
+    ctx.check(lib.cwk_xchg_create(ctx.h, NH, L, 1, C.byref(own1), None))
+    one = (C.c_void_p * 1)(own1.value)
+    ctx.check(lib.cwk_mla_decode_kv_split(ctx.h, C.c_void_p(q.data_ptr()), C.c_void_p(cache.data_ptr()), L + R, T, NH, L, R,
+                                          SCALE, one, 0, 1, 1, C.c_void_p(out.data_ptr())))
+    ctx.sync()
+    assert float((out.float() - got.float()).abs().max()) <= 4e-3
+    ctx.check(lib.cwk_xchg_destroy(ctx.h, own1))
