@@ -17,35 +17,100 @@
 int cwk_mla_decode_rows(cwk_ctx *ctx, const void *q, const void *cache, int64_t ld, int rows, int nh, int L, int R,
                         float scale, void *out);
 
+int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld, const int32_t *kv_len,
+                   int max_kv_len, const int32_t *sel, int64_t sel_ld, int B, int nh, int L, int R, float scale, void *out,
+                   int n_splits);
+
 namespace {
 
-// y[r] = W[r] . x, W bf16 [rows][k] row-major, x f32. One warp per row, f32 accumulate.
+// ---- projections ------------------------------------------------------------------------------------------------
+// y[t][r] = W[r] . x[t], W bf16 [rows][k] row-major, x f32. One warp per (row, token), f32 accumulate; blockIdx.y = t.
 // (cwick_linear on a BF16 tensor with rows == 1: src/tensor.c:745-765 -> gemv_bf16_range :143-176.)
-__global__ void __launch_bounds__(256) gemv_bf16_kernel(const uint16_t *W, const float *x, float *y, int rows, int k) {
+__global__ void __launch_bounds__(256) gemv_bf16_kernel(const uint16_t *W, const float *x, float *y, int rows, int k, int64_t ldx,
+                                                        int64_t ldy) {
     const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= rows) return;
+    x += (int64_t)blockIdx.y * ldx;
+    y += (int64_t)blockIdx.y * ldy;
     const uint16_t *w = W + (int64_t)r * k;
     float acc = 0.f;
-    for (int j = lane * 8; j + 8 <= k; j += 256) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(w + j);
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    if ((k & 7) == 0) {
+        for (int j = lane * 8; j + 8 <= k; j += 256) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(w + j);
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-            acc += bf16_bits_to_f32((uint16_t)(u[e] & 0xffffu)) * x[j + 2 * e];
-            acc += bf16_bits_to_f32((uint16_t)(u[e] >> 16)) * x[j + 2 * e + 1];
+            for (int e = 0; e < 4; e++) {
+                acc += bf16_bits_to_f32((uint16_t)(u[e] & 0xffffu)) * x[j + 2 * e];
+                acc += bf16_bits_to_f32((uint16_t)(u[e] >> 16)) * x[j + 2 * e + 1];
+            }
         }
+    } else {
+        for (int j = lane; j < k; j += 32) acc += bf16_bits_to_f32(w[j]) * x[j];
     }
-    for (int j = (k & ~7) + lane; j < k; j += 32) acc += bf16_bits_to_f32(w[j]) * x[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[r] = acc;
+}
+
+__global__ void __launch_bounds__(256) gemv_f32_kernel(const float *W, const float *x, float *y, int rows, int k, int64_t ldx, int64_t ldy) {
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    x += (int64_t)blockIdx.y * ldx;
+    y += (int64_t)blockIdx.y * ldy;
+    float acc = 0.f;
+    for (int j = lane; j < k; j += 32) acc += W[(int64_t)r * k + j] * x[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[r] = acc;
+}
+
+__device__ __forceinline__ float e4m3_val(uint32_t b) {
+    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    float mag;
+    if (e == 0) mag = (float)m * 0.001953125f;
+    else if (e == 15 && m == 7) mag = __int_as_float(0x7fc00000);
+    else mag = __uint_as_float(((e + 120u) << 23) | (m << 20));
+    return (b & 0x80u) ? -mag : mag;
+}
+
+// FP8-E4M3 weights with one F32 multiplier per 128x128 block (cwick_linear's FP8 branch with rows == 1,
+// src/tensor.c:745-765 -> cwick_gemv_fp8 :674-691 -> gemv_fp8_range :495-532): per output row, the 128-wide
+// block sums in f32, each times its block's scale. One warp per (row, token); a lane takes 4 weights of each block.
+__global__ void __launch_bounds__(256) gemv_fp8_kernel(const uint8_t *W, const float *scales, const float *x, float *y, int rows, int k,
+                                                       int64_t ldx, int64_t ldy) {
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    x += (int64_t)blockIdx.y * ldx;
+    y += (int64_t)blockIdx.y * ldy;
+    const int nkb = (k + 127) / 128;
+    const uint8_t *w = W + (int64_t)r * k;
+    const float *sc = scales + (int64_t)(r / 128) * nkb;
+    float acc = 0.f;
+    for (int kb = 0; kb < nkb; kb++) {
+        const int j = kb * 128 + lane * 4;
+        float part = 0.f;
+        if (j + 4 <= k && (k & 3) == 0) {
+            const uint32_t v = *reinterpret_cast<const uint32_t *>(w + j);
+#pragma unroll
+            for (int e = 0; e < 4; e++) part += e4m3_val((v >> (8 * e)) & 0xffu) * x[j + e];
+        } else {
+            for (int e = 0; e < 4 && j + e < k; e++) part += e4m3_val(w[j + e]) * x[j + e];
+        }
+        acc += part * sc[kb];
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0) y[r] = acc;
 }
 
 // In place: x <- x / sqrt(mean(x^2) + eps) * w (cwick_rms_norm + apply_bf16_vec, src/tensor.c:780-791,
-// src/attention.c:70-73). Optionally also narrows the result to bf16 the way the reference narrows a
-// latent-cache row (src/util.c:202-210) into `row_out`. One block.
-__global__ void __launch_bounds__(256) rms_scale_kernel(float *x, int n, const uint16_t *w, float eps, uint16_t *row_out) {
+// src/attention.c:70-73), one block per row (blockIdx.x). Optionally also narrows the result to bf16 the way the
+// reference narrows a latent-cache row (src/util.c:202-210) into row_out + row * row_ld.
+__global__ void __launch_bounds__(256) rms_scale_kernel(float *x, int n, int64_t ldx, const uint16_t *w, float eps, uint16_t *row_out,
+                                                        int64_t row_ld) {
     __shared__ double red[256];
+    x += (int64_t)blockIdx.x * ldx;
+    if (row_out) row_out += (int64_t)blockIdx.x * row_ld;
     double ss = 0.0;
     for (int i = threadIdx.x; i < n; i += 256) ss += (double)x[i] * (double)x[i];
     red[threadIdx.x] = ss;
@@ -65,10 +130,12 @@ __global__ void __launch_bounds__(256) rms_scale_kernel(float *x, int n, const u
     }
 }
 
-// q_abs[h][c] = sum_r q[h][r] * W_k[h][r][c] (src/attention.c:741-744), W_k = rows [h*kv_dim, +nope) of
-// kv_b_proj [nh*kv_dim][kv_lora]. grid (nh), thread per column, bf16 out.
-__global__ void absorb_q_kernel(const float *q, const uint16_t *kvb, int nope, int kv_dim, int kv_lora, uint16_t *qabs) {
+// q_abs[t][h][c] = sum_r q[t][h][r] * W_k[h][r][c] (src/attention.c:741-744), W_k = rows [h*kv_dim, +nope) of
+// kv_b_proj [nh*kv_dim][kv_lora]. grid (nh, tokens), thread per column, bf16 out.
+__global__ void absorb_q_kernel(const float *q, const uint16_t *kvb, int nh, int nope, int kv_dim, int kv_lora, uint16_t *qabs) {
     const int h = blockIdx.x;
+    q += (int64_t)blockIdx.y * nh * nope;
+    qabs += (int64_t)blockIdx.y * nh * kv_lora;
     const uint16_t *wk = kvb + (int64_t)h * kv_dim * kv_lora;
     for (int c = threadIdx.x; c < kv_lora; c += blockDim.x) {
         float acc = 0.f;
@@ -77,11 +144,13 @@ __global__ void absorb_q_kernel(const float *q, const uint16_t *kvb, int nope, i
     }
 }
 
-// attn_out[h][r] = W_v[h][r] . c_acc[h] (src/attention.c:812-815). One warp per (h, r).
+// attn_out[t][h][r] = W_v[h][r] . c_acc[t][h] (src/attention.c:812-815). One warp per (h, r); blockIdx.y = token.
 __global__ void __launch_bounds__(256) unabsorb_kernel(const uint16_t *cacc, const uint16_t *kvb, int nh, int nope, int vdim,
                                                        int kv_lora, float *attn) {
     const int idx = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (idx >= nh * vdim) return;
+    cacc += (int64_t)blockIdx.y * nh * kv_lora;
+    attn += (int64_t)blockIdx.y * nh * vdim;
     const int h = idx / vdim, r = idx % vdim;
     const uint16_t *w = kvb + ((int64_t)h * (nope + vdim) + nope + r) * kv_lora;
     const uint16_t *c = cacc + (int64_t)h * kv_lora;
@@ -92,16 +161,73 @@ __global__ void __launch_bounds__(256) unabsorb_kernel(const uint16_t *cacc, con
     if (lane == 0) attn[idx] = acc;
 }
 
+// Indexer scores over the f32 pool rows, the reference's order (src/attention.c:573-582 with dot_f32's scalar
+// grouping :249-258): per head four strided accumulators with separate multiply and add, (s0+s1)+(s2+s3), then any
+// remainder in order; ReLU; times the head weight; heads summed in order. One thread per pool row.
+__global__ void __launch_bounds__(128) pool_scores_kernel(const float *pool, int n, int hd, const float *q, const float *wt, int ih,
+                                                          float *sc) {
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    if (c >= n) return;
+    const float *kv = pool + (int64_t)c * hd;
+    float total = 0.f;
+    for (int h = 0; h < ih; h++) {
+        const float *qh = q + (int64_t)h * hd;
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        int i = 0;
+        for (; i + 4 <= hd; i += 4) {
+            s0 = __fadd_rn(s0, __fmul_rn(kv[i], qh[i]));
+            s1 = __fadd_rn(s1, __fmul_rn(kv[i + 1], qh[i + 1]));
+            s2 = __fadd_rn(s2, __fmul_rn(kv[i + 2], qh[i + 2]));
+            s3 = __fadd_rn(s3, __fmul_rn(kv[i + 3], qh[i + 3]));
+        }
+        float d = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
+        for (; i < hd; i++) d = __fadd_rn(d, __fmul_rn(kv[i], qh[i]));
+        if (d < 0.f) d = 0.f;
+        total = __fadd_rn(total, __fmul_rn(d, wt[h]));
+    }
+    sc[c] = total;
+}
+
+__global__ void scale_vec_kernel(float *x, int n, float s) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = __fmul_rn(x[i], s);
+}
+
+// ---- device mirrors ---------------------------------------------------------------------------------------------
+struct WeightMirror {
+    void *data = nullptr;
+    float *scales = nullptr;
+    int kind = 0;
+    int64_t rows = 0, cols = 0;
+};
+struct WeightKey {
+    const void *ptr;
+    int64_t rows, cols;
+    int kind;
+    bool operator<(const WeightKey &o) const {
+        if (ptr != o.ptr) return ptr < o.ptr;
+        if (rows != o.rows) return rows < o.rows;
+        if (cols != o.cols) return cols < o.cols;
+        return kind < o.kind;
+    }
+};
 struct CacheMirror {
     uint16_t *dev = nullptr;
     int64_t capacity = 0, width = 0, next_pos = 0;
+    std::vector<uint8_t> last_row;          // the caller's row next_pos-1 as it was when the mirror last agreed with it
+};
+struct IndexMirror {
+    float *pool = nullptr, *tails = nullptr;      // [pool_cap][hd]; tail_k [kp][hd] then tail_g [kp][hd]
+    int64_t pool_cap = 0, hd = 0, kp = 0, n_pools = 0;
+    std::vector<float> last_row;
 };
 
 struct Registry {
     std::mutex mu;
     cwk_ctx *ctx = nullptr;
-    std::unordered_map<const void *, void *> weights;
+    std::map<WeightKey, WeightMirror> weights;
     std::map<std::pair<const void *, int64_t>, CacheMirror> caches;
+    std::map<const void *, IndexMirror> indexers;
     float *d_buf = nullptr;       // activations
     size_t d_buf_bytes = 0;
     void *pin = nullptr;
@@ -125,15 +251,410 @@ bool latent_ok(const cwkc_model_spec *s, const cwkc_tensor *kvb) {
     return kvb->rows == s->num_attention_heads * kv_dim && kvb->cols >= s->kv_lora_rank;
 }
 
-const uint16_t *mirror_weight(const cwkc_tensor *t) {
-    auto it = g.weights.find(t->data);
-    if (it != g.weights.end()) return (const uint16_t *)it->second;
-    void *d = nullptr;
-    const size_t bytes = (size_t)t->rows * (size_t)t->cols * 2;
-    if (cudaMalloc(&d, bytes) != cudaSuccess) return nullptr;
-    if (cudaMemcpy(d, t->data, bytes, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(d); return nullptr; }
-    g.weights[t->data] = d;
-    return (const uint16_t *)d;
+bool kind_ok(int kind) { return kind == CWKC_WEIGHT_BF16 || kind == CWKC_WEIGHT_F32 || kind == CWKC_WEIGHT_FP8_E4M3; }
+
+// The device copy of a weight tensor, made on first sight. Keyed by data pointer, shape and kind.
+const WeightMirror *mirror_weight(const cwkc_tensor *t) {
+    if (!t || !t->data || !kind_ok(t->kind)) return nullptr;
+    const WeightKey key{t->data, t->rows, t->cols, t->kind};
+    auto it = g.weights.find(key);
+    if (it != g.weights.end()) return &it->second;
+    WeightMirror m;
+    m.kind = t->kind; m.rows = t->rows; m.cols = t->cols;
+    const size_t el = t->kind == CWKC_WEIGHT_BF16 ? 2 : (t->kind == CWKC_WEIGHT_F32 ? 4 : 1);
+    const size_t bytes = (size_t)t->rows * (size_t)t->cols * el;
+    if (cudaMalloc(&m.data, bytes) != cudaSuccess) return nullptr;
+    if (cudaMemcpy(m.data, t->data, bytes, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(m.data); return nullptr; }
+    if (t->kind == CWKC_WEIGHT_FP8_E4M3) {
+        const size_t ns = (size_t)((t->rows + 127) / 128) * (size_t)((t->cols + 127) / 128);
+        if (!t->scales || cudaMalloc((void **)&m.scales, ns * 4) != cudaSuccess) { cudaFree(m.data); return nullptr; }
+        if (cudaMemcpy(m.scales, t->scales, ns * 4, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(m.data); cudaFree(m.scales); return nullptr; }
+    }
+    return &(g.weights[key] = m);
+}
+
+// y[t][0..rows) = W . x[t] for n tokens (cwick_linear, src/tensor.c:745-765), whatever the weight's kind.
+void dev_linear(cwk_ctx *ctx, const WeightMirror *w, const float *x, float *y, int n, int64_t ldx, int64_t ldy) {
+    const dim3 grid((unsigned)((w->rows + 7) / 8), (unsigned)n);
+    if (w->kind == CWKC_WEIGHT_BF16)
+        gemv_bf16_kernel<<<grid, 256, 0, ctx->stream>>>((const uint16_t *)w->data, x, y, (int)w->rows, (int)w->cols, ldx, ldy);
+    else if (w->kind == CWKC_WEIGHT_F32)
+        gemv_f32_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)w->data, x, y, (int)w->rows, (int)w->cols, ldx, ldy);
+    else
+        gemv_fp8_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)w->data, w->scales, x, y, (int)w->rows, (int)w->cols, ldx, ldy);
+    ctx->launches++;
+}
+
+// Values of a small vector tensor as f32 on the device (cwick_tensor_value, src/tensor.c:767-774).
+float *mirror_vector_f32(const cwkc_tensor *t, int64_t n) {
+    if (!t || !t->data) return nullptr;
+    const WeightKey key{t->data, -n, 1, t->kind};       // negative rows: the widened-vector form of the tensor
+    auto it = g.weights.find(key);
+    if (it != g.weights.end()) return (float *)it->second.data;
+    std::vector<float> v((size_t)n);
+    for (int64_t i = 0; i < n; i++) {
+        if (t->kind == CWKC_WEIGHT_BF16) {
+            const uint32_t u = (uint32_t)((const uint16_t *)t->data)[i] << 16;
+            memcpy(&v[(size_t)i], &u, 4);
+        } else if (t->kind == CWKC_WEIGHT_F32) v[(size_t)i] = ((const float *)t->data)[i];
+        else v[(size_t)i] = 0.0f;
+    }
+    WeightMirror m;
+    m.kind = t->kind; m.rows = -n; m.cols = 1;
+    if (cudaMalloc(&m.data, (size_t)n * 4) != cudaSuccess) return nullptr;
+    if (cudaMemcpy(m.data, v.data(), (size_t)n * 4, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(m.data); return nullptr; }
+    g.weights[key] = m;
+    return (float *)m.data;
+}
+
+bool ensure_ctx(cwkc_error *err) {
+    if (g.ctx) return true;
+    const char *d = getenv("CWK_DEVICE");
+    if (cwk_ctx_create(d ? atoi(d) : 0, &g.ctx) != CWK_OK) { set_err(err, CWK_ERR_STATE, "no usable sm_100 GPU"); return false; }
+    return true;
+}
+bool ensure_bufs(size_t dev_bytes, size_t pin_bytes, cwkc_error *err) {
+    if (dev_bytes > g.d_buf_bytes) {
+        if (g.d_buf) { cudaStreamSynchronize(g.ctx->stream); cudaFree(g.d_buf); }
+        if (cudaMalloc(&g.d_buf, dev_bytes) != cudaSuccess) { g.d_buf = nullptr; g.d_buf_bytes = 0; set_err(err, CWK_ERR_MEMORY, "device scratch"); return false; }
+        g.d_buf_bytes = dev_bytes;
+    }
+    if (pin_bytes > g.pin_bytes) {
+        if (g.pin) { cudaStreamSynchronize(g.ctx->stream); cudaFreeHost(g.pin); }
+        if (cudaMallocHost(&g.pin, pin_bytes) != cudaSuccess) { g.pin = nullptr; g.pin_bytes = 0; set_err(err, CWK_ERR_MEMORY, "pinned staging"); return false; }
+        g.pin_bytes = pin_bytes;
+    }
+    return true;
+}
+
+// Moves the k largest values to the front by Hoare partitions around the middle element, exactly as the reference's
+// score_select does (src/attention.c:528-543): the value left at v[k-1] is what the reference takes as its
+// threshold, which is one of the k largest but not always the smallest of them. Reproducing the procedure, not just
+// "the k-th largest", is what makes the selection below the reference's own, entry for entry.
+void select_front(float *v, int64_t n, int64_t k) {
+    int64_t lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const float pivot = v[(size_t)((lo + hi) >> 1)];
+        int64_t i = lo, j = hi;
+        while (i <= j) {
+            while (v[i] > pivot) i++;
+            while (v[j] < pivot) j--;
+            if (i <= j) { std::swap(v[i], v[j]); i++; j--; }
+        }
+        if (k <= j) hi = j;
+        else if (k >= i) lo = i;
+        else break;
+    }
+}
+
+// Everything one layer call needs, resolved once.
+struct Layer {
+    const cwkc_model_spec *spec;
+    const WeightMirror *qa, *qb, *kva, *kvb, *o;
+    const uint16_t *qa_n, *kva_n;
+    int64_t H;
+    int nh, nope, vdim, q_lora, kv_lora, kv_dim;
+    bool lbf;                       // the caller's cache array holds bf16 (CWICK_LATENT_BF16) or f32
+    CacheMirror *cm;
+    uint8_t *host_layer;            // the caller's rows of this layer
+    size_t host_row_bytes;
+    // indexer (all null when the layer has none)
+    const cwkc_indexer_weights *idx_w = nullptr;
+    cwkc_indexer_state *idx = nullptr;
+    IndexMirror *im = nullptr;
+    const WeightMirror *wq_b = nullptr, *wk = nullptr, *gate = nullptr, *weights_proj = nullptr;
+    const uint16_t *ape = nullptr;
+    float *k_norm = nullptr, *k_norm_b = nullptr;
+    int ih = 0, ihd = 0, kp = 1;
+};
+
+// Bring the device mirror of the latent cache in step with the caller's rows 0..pos-1.
+int sync_cache(cwk_ctx *ctx, Layer &ly, int64_t capacity, int64_t pos) {
+    CacheMirror &cm = *ly.cm;
+    const int kv_lora = ly.kv_lora;
+    if (!cm.dev || cm.capacity != capacity || cm.width != kv_lora) {
+        if (cm.dev) { cudaStreamSynchronize(ctx->stream); cudaFree(cm.dev); }
+        if (cudaMalloc(&cm.dev, (size_t)capacity * kv_lora * 2) != cudaSuccess) { cm.dev = nullptr; return CWK_ERR_MEMORY; }
+        cm.capacity = capacity; cm.width = kv_lora; cm.next_pos = -1;
+    }
+    bool stale = pos != cm.next_pos;
+    if (!stale && pos > 0)      // same length: trust the mirror only while the caller's last row is the one written through it
+        stale = cm.last_row.size() != ly.host_row_bytes || memcmp(cm.last_row.data(), ly.host_layer + (size_t)(pos - 1) * ly.host_row_bytes, ly.host_row_bytes) != 0;
+    if (stale && pos > 0) {
+        if (ly.lbf) {
+            if (cudaMemcpyAsync(cm.dev, ly.host_layer, (size_t)pos * kv_lora * 2, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) return CWK_ERR_CUDA;
+            if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return CWK_ERR_CUDA;      // the source is pageable caller memory
+        } else {
+            int s = cwk_cache_import_f32(ctx, (const float *)ly.host_layer, pos, kv_lora, cm.dev, kv_lora, 1);
+            if (s != CWK_OK) return s;
+        }
+    }
+    return CWK_OK;
+}
+
+void note_row_written(Layer &ly, int64_t pos) {
+    CacheMirror &cm = *ly.cm;
+    cm.last_row.assign(ly.host_layer + (size_t)pos * ly.host_row_bytes, ly.host_layer + (size_t)(pos + 1) * ly.host_row_bytes);
+    cm.next_pos = pos + 1;
+}
+
+// The indexer's device state in step with the caller's (pool rows 0..n_pools-1, both tails).
+int sync_indexer(cwk_ctx *ctx, Layer &ly) {
+    IndexMirror &im = *ly.im;
+    cwkc_indexer_state *st = ly.idx;
+    const int64_t hd = ly.ihd, kp = ly.kp;
+    if (!im.pool || im.pool_cap != st->pool_cap || im.hd != hd || im.kp != kp) {
+        if (im.pool) { cudaStreamSynchronize(ctx->stream); cudaFree(im.pool); cudaFree(im.tails); }
+        im.pool = im.tails = nullptr;
+        if (cudaMalloc((void **)&im.pool, (size_t)std::max<int64_t>(1, st->pool_cap) * hd * 4) != cudaSuccess) return CWK_ERR_MEMORY;
+        if (cudaMalloc((void **)&im.tails, (size_t)2 * kp * hd * 4) != cudaSuccess) return CWK_ERR_MEMORY;
+        im.pool_cap = st->pool_cap; im.hd = hd; im.kp = kp; im.n_pools = -1;
+    }
+    bool stale = im.n_pools != st->n_pools;
+    if (!stale && st->n_pools > 0)
+        stale = im.last_row.size() != (size_t)hd || memcmp(im.last_row.data(), st->pool + (size_t)(st->n_pools - 1) * hd, (size_t)hd * 4) != 0;
+    if (stale && st->n_pools > 0)
+        if (cudaMemcpyAsync(im.pool, st->pool, (size_t)st->n_pools * hd * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) return CWK_ERR_CUDA;
+    // the tails are small and the caller may have rewritten them (reset, prefix restore): they travel every call
+    if (cudaMemcpyAsync(im.tails, st->tail_k, (size_t)kp * hd * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) return CWK_ERR_CUDA;
+    if (cudaMemcpyAsync(im.tails + kp * hd, st->tail_g, (size_t)kp * hd * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) return CWK_ERR_CUDA;
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return CWK_ERR_CUDA;
+    im.n_pools = st->n_pools;
+    if (st->n_pools > 0) im.last_row.assign(st->pool + (size_t)(st->n_pools - 1) * hd, st->pool + (size_t)st->n_pools * hd);
+    return CWK_OK;
+}
+
+// One token of one layer, the reference's mla_latent_decode (src/attention.c:642-902) stage by stage on the device.
+// x_host/out_host: H floats each. Returns a cwk status; the message goes to err.
+int token_step(cwk_ctx *ctx, Layer &ly, int64_t capacity, int64_t pos, const float *x_host, float *out_host, cwkc_error *err) {
+    cudaStream_t st = ctx->stream;
+    const int64_t H = ly.H;
+    const int nh = ly.nh, nope = ly.nope, vdim = ly.vdim, q_lora = ly.q_lora, kv_lora = ly.kv_lora, kv_dim = ly.kv_dim;
+    const int ih = ly.ih, ihd = ly.ihd, kp = ly.kp;
+    // floats: x[H] qa[q_lora] q[nh*nope] kva[kv_lora] attn[nh*vdim] out[H] iq[ih*ihd] iwt[ih] isc[pool_cap] | bf16: qabs, cacc | int32: sel
+    const int64_t pool_cap = ly.idx ? ly.idx->pool_cap : 0;
+    const int64_t topk = ly.idx ? ly.spec->index_topk : 0;
+    const size_t nf = (size_t)H * 2 + q_lora + (size_t)nh * nope + kv_lora + (size_t)nh * vdim + (size_t)ih * ihd + ih + pool_cap + 64;
+    const size_t nsel = (size_t)topk + kp + 4;
+    const size_t need = nf * 4 + (size_t)nh * kv_lora * 2 * 2 + nsel * 4 + 512;
+    const size_t pin_need = (size_t)H * 4 * 2 + (size_t)kv_lora * 4 + (size_t)(2 * ihd + ih * ihd + ih + pool_cap) * 4 + nsel * 4 + 256;
+    if (!ensure_bufs(need, pin_need, err)) return CWK_ERR_MEMORY;
+    float *d_x = g.d_buf, *d_qa = d_x + H, *d_q = d_qa + q_lora, *d_kva = d_q + (size_t)nh * nope;
+    float *d_attn = d_kva + kv_lora, *d_out = d_attn + (size_t)nh * vdim, *d_iq = d_out + H, *d_iwt = d_iq + (size_t)ih * ihd;
+    float *d_isc = d_iwt + ih;
+    uint16_t *d_qabs = (uint16_t *)(((uintptr_t)(d_isc + pool_cap) + 63) & ~(uintptr_t)63), *d_cacc = d_qabs + (size_t)nh * kv_lora;
+    int32_t *d_sel = (int32_t *)(d_cacc + (size_t)nh * kv_lora);
+    float *p_x = (float *)g.pin, *p_out = p_x + H, *p_row = p_out + H;          // p_row: kv_lora f32, or kv_lora bf16
+    float *p_tail = p_row + kv_lora, *p_iq = p_tail + 2 * ihd, *p_iwt = p_iq + (size_t)ih * ihd, *p_sc = p_iwt + ih;
+    int32_t *p_sel = (int32_t *)(p_sc + pool_cap);
+
+    int s = sync_cache(ctx, ly, capacity, pos);
+    if (s != CWK_OK) { set_err(err, s, "latent cache mirror failed"); return s; }
+    CacheMirror &cm = *ly.cm;
+
+    memcpy(p_x, x_host, (size_t)H * 4);
+    cudaMemcpyAsync(d_x, p_x, (size_t)H * 4, cudaMemcpyHostToDevice, st);
+    dev_linear(ctx, ly.qa, d_x, d_qa, 1, 0, 0);
+    dev_linear(ctx, ly.kva, d_x, d_kva, 1, 0, 0);
+    rms_scale_kernel<<<1, 256, 0, st>>>(d_qa, q_lora, 0, ly.qa_n, ly.spec->rms_norm_eps_f, nullptr, 0);
+    dev_linear(ctx, ly.qb, d_qa, d_q, 1, 0, 0);
+    rms_scale_kernel<<<1, 256, 0, st>>>(d_kva, kv_lora, 0, ly.kva_n, ly.spec->rms_norm_eps_f, cm.dev + (size_t)pos * kv_lora, 0);
+    // the caller's array stays the source of truth: the row goes back in the caller's element width
+    if (ly.lbf) cudaMemcpyAsync(p_row, cm.dev + (size_t)pos * kv_lora, (size_t)kv_lora * 2, cudaMemcpyDeviceToHost, st);
+    else cudaMemcpyAsync(p_row, d_kva, (size_t)kv_lora * 4, cudaMemcpyDeviceToHost, st);
+    absorb_q_kernel<<<dim3(nh, 1), 256, 0, st>>>(d_q, (const uint16_t *)ly.kvb->data, nh, nope, kv_dim, kv_lora, d_qabs);
+    ctx->launches += 3;
+
+    // ---- DSA indexer (src/attention.c:716-735): absorb this position, then pick the rows to attend to ----
+    int64_t nlist = pos + 1;
+    bool use_sel = false;
+    if (ly.idx) {
+        cwkc_indexer_state *ist = ly.idx;
+        IndexMirror &im = *ly.im;
+        s = sync_indexer(ctx, ly);
+        if (s != CWK_OK) { set_err(err, s, "indexer state mirror failed"); return s; }
+        const int64_t r = pos % kp;
+        // indexer_absorb (:472-526): this position's raw key and gate rows
+        dev_linear(ctx, ly.wk, d_x, im.tails + r * ihd, 1, 0, 0);
+        dev_linear(ctx, ly.gate, d_x, im.tails + (kp + r) * ihd, 1, 0, 0);
+        cudaMemcpyAsync(p_tail, im.tails + r * ihd, (size_t)ihd * 4, cudaMemcpyDeviceToHost, st);
+        cudaMemcpyAsync(p_tail + ihd, im.tails + (kp + r) * ihd, (size_t)ihd * 4, cudaMemcpyDeviceToHost, st);
+        bool closed = false;
+        if (r == kp - 1 && ist->n_pools < ist->pool_cap && kp <= 8) {
+            s = cwk_indexer_pool_compress(ctx, im.tails, im.tails + kp * ihd, ly.ape, ly.k_norm, ly.k_norm_b, 1, kp, ihd,
+                                          ly.spec->rms_norm_eps_f, im.pool + ist->n_pools * ihd);
+            if (s != CWK_OK) { set_err(err, s, "%s", cwk_last_error(ctx)); return s; }
+            closed = true;
+        }
+        if (cudaStreamSynchronize(st) != cudaSuccess) { set_err(err, CWK_ERR_CUDA, "indexer absorb failed"); return CWK_ERR_CUDA; }
+        memcpy(ist->tail_k + r * ihd, p_tail, (size_t)ihd * 4);
+        memcpy(ist->tail_g + r * ihd, p_tail + ihd, (size_t)ihd * 4);
+        if (closed) {
+            if (cudaMemcpy(ist->pool + (size_t)ist->n_pools * ihd, im.pool + ist->n_pools * ihd, (size_t)ihd * 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+                set_err(err, CWK_ERR_CUDA, "pool row read-back failed");
+                return CWK_ERR_CUDA;
+            }
+            im.last_row.assign(ist->pool + (size_t)ist->n_pools * ihd, ist->pool + (size_t)(ist->n_pools + 1) * ihd);
+            ist->n_pools++;
+            im.n_pools = ist->n_pools;
+        }
+        // indexer_select (:548-622)
+        const int64_t n_comp = ist->n_pools, want = (topk + kp - 1) / kp, npos = pos + 1;
+        if (want > 0 && n_comp > want) {
+            dev_linear(ctx, ly.wq_b, d_qa, d_iq, 1, 0, 0);
+            dev_linear(ctx, ly.weights_proj, d_x, d_iwt, 1, 0, 0);
+            const float wscale = 1.0f / sqrtf((float)((double)ihd * (double)ih));
+            scale_vec_kernel<<<(ih + 127) / 128, 128, 0, st>>>(d_iwt, ih, wscale);
+            pool_scores_kernel<<<(unsigned)((n_comp + 127) / 128), 128, 0, st>>>(im.pool, (int)n_comp, ihd, d_iq, d_iwt, ih, d_isc);
+            ctx->launches += 2;
+            cudaMemcpyAsync(p_iq, d_iq, (size_t)ih * ihd * 4, cudaMemcpyDeviceToHost, st);
+            cudaMemcpyAsync(p_iwt, d_iwt, (size_t)ih * 4, cudaMemcpyDeviceToHost, st);
+            cudaMemcpyAsync(p_sc, d_isc, (size_t)n_comp * 4, cudaMemcpyDeviceToHost, st);
+            if (cudaStreamSynchronize(st) != cudaSuccess) { set_err(err, CWK_ERR_CUDA, "indexer scores failed"); return CWK_ERR_CUDA; }
+            // the reference leaves q, wt and the scores in the state's scratch: so does this
+            memcpy(ist->q, p_iq, (size_t)ih * ihd * 4);
+            memcpy(ist->wt, p_iwt, (size_t)ih * 4);
+            memcpy(ist->sc, p_sc, (size_t)n_comp * 4);
+            memcpy(ist->sc2, p_sc, (size_t)n_comp * 4);
+            select_front(ist->sc2, n_comp, want);
+            const float thr = ist->sc2[want - 1];
+            const int64_t cap = want * kp;
+            int64_t n = 0;
+            int64_t *sel = ist->sel;
+            for (int pass = 0; pass < 2 && n < cap; pass++)
+                for (int64_t c = 0; c < n_comp && n < cap; c++) {
+                    const bool take = pass == 0 ? (ist->sc[c] > thr) : (ist->sc[c] == thr);
+                    if (take) for (int64_t rr = 0; rr < kp; rr++) sel[n++] = c * kp + rr;      // the pool's positions
+                }
+            const int64_t tail = npos % kp;              // positions in no closed pool yet: always kept (:600-604)
+            for (int64_t rr = 0; rr < tail; rr++) sel[n++] = npos - tail + rr;
+            if (getenv("CWICK_INDEXER_STRICT") == nullptr && (n == 0 || sel[n - 1] != npos - 1)) sel[n++] = npos - 1;   // :618-621
+            if (n > 0) {
+                for (int64_t i = 0; i < n; i++) p_sel[i] = (int32_t)sel[i];
+                cudaMemcpyAsync(d_sel, p_sel, (size_t)n * 4, cudaMemcpyHostToDevice, st);
+                nlist = n;
+                use_sel = true;
+            }
+        }
+    }
+
+    s = cwk_mla_decode(ctx, d_qabs, cm.dev, 0, kv_lora, nullptr, (int)nlist, use_sel ? d_sel : nullptr, use_sel ? (int64_t)nlist : 0, 1, nh,
+                       kv_lora, 0, 1.0f / sqrtf((float)nope), d_cacc, 0);
+    if (s != CWK_OK) { set_err(err, s, "%s", cwk_last_error(ctx)); return s; }
+    unabsorb_kernel<<<dim3((nh * vdim + 7) / 8, 1), 256, 0, st>>>(d_cacc, (const uint16_t *)ly.kvb->data, nh, nope, vdim, kv_lora, d_attn);
+    ctx->launches += 1;
+    dev_linear(ctx, ly.o, d_attn, d_out, 1, 0, 0);
+    cudaMemcpyAsync(p_out, d_out, (size_t)H * 4, cudaMemcpyDeviceToHost, st);
+    if (cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess) {
+        set_err(err, CWK_ERR_CUDA, "GPU decode failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return CWK_ERR_CUDA;
+    }
+    if (cwk_check_device_error(ctx) != CWK_OK) { set_err(err, CWK_ERR_STATE, "%s", cwk_last_error(ctx)); return CWK_ERR_STATE; }
+    memcpy(out_host, p_out, (size_t)H * 4);
+    memcpy(ly.host_layer + (size_t)pos * ly.host_row_bytes, p_row, ly.host_row_bytes);
+    note_row_written(ly, pos);
+    return CWK_OK;
+}
+
+// A chunk of n tokens of a layer without an indexer: every stage batched over the tokens, the attention as n
+// decode-shaped problems over one shared cache (row t sees rows 0..pos0+t), src/attention.c:943-1024.
+int chunk_steps(cwk_ctx *ctx, Layer &ly, int64_t capacity, int64_t pos0, int64_t n, const float *X_host, float *Out_host, cwkc_error *err) {
+    cudaStream_t st = ctx->stream;
+    const int64_t H = ly.H;
+    const int nh = ly.nh, nope = ly.nope, vdim = ly.vdim, q_lora = ly.q_lora, kv_lora = ly.kv_lora, kv_dim = ly.kv_dim;
+    const size_t per_f = (size_t)H * 2 + q_lora + (size_t)nh * nope + kv_lora + (size_t)nh * vdim;
+    const size_t need = (size_t)n * (per_f * 4 + (size_t)nh * kv_lora * 2 * 2 + 4) + 1024;
+    if (!ensure_bufs(need, 64, err)) return CWK_ERR_MEMORY;
+    float *d_x = g.d_buf, *d_qa = d_x + n * H, *d_q = d_qa + n * q_lora, *d_kva = d_q + n * (size_t)nh * nope;
+    float *d_attn = d_kva + n * kv_lora, *d_out = d_attn + n * (size_t)nh * vdim;
+    uint16_t *d_qabs = (uint16_t *)(((uintptr_t)(d_out + n * H) + 63) & ~(uintptr_t)63), *d_cacc = d_qabs + n * (size_t)nh * kv_lora;
+    int32_t *d_len = (int32_t *)(d_cacc + n * (size_t)nh * kv_lora);
+    int s = sync_cache(ctx, ly, capacity, pos0);
+    if (s != CWK_OK) { set_err(err, s, "latent cache mirror failed"); return s; }
+    CacheMirror &cm = *ly.cm;
+    std::vector<int32_t> lens((size_t)n);
+    for (int64_t t = 0; t < n; t++) lens[(size_t)t] = (int32_t)(pos0 + t + 1);
+    if (cudaMemcpyAsync(d_x, X_host, (size_t)n * H * 4, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+        cudaMemcpyAsync(d_len, lens.data(), (size_t)n * 4, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess) {
+        set_err(err, CWK_ERR_CUDA, "chunk upload failed");
+        return CWK_ERR_CUDA;
+    }
+    dev_linear(ctx, ly.qa, d_x, d_qa, (int)n, H, q_lora);
+    dev_linear(ctx, ly.kva, d_x, d_kva, (int)n, H, kv_lora);
+    rms_scale_kernel<<<(unsigned)n, 256, 0, st>>>(d_qa, q_lora, q_lora, ly.qa_n, ly.spec->rms_norm_eps_f, nullptr, 0);
+    rms_scale_kernel<<<(unsigned)n, 256, 0, st>>>(d_kva, kv_lora, kv_lora, ly.kva_n, ly.spec->rms_norm_eps_f, cm.dev + (size_t)pos0 * kv_lora, kv_lora);
+    dev_linear(ctx, ly.qb, d_qa, d_q, (int)n, q_lora, (int64_t)nh * nope);
+    absorb_q_kernel<<<dim3(nh, (unsigned)n), 256, 0, st>>>(d_q, (const uint16_t *)ly.kvb->data, nh, nope, kv_dim, kv_lora, d_qabs);
+    ctx->launches += 3;
+    s = cwk_mla_decode(ctx, d_qabs, cm.dev, 0, kv_lora, d_len, (int)(pos0 + n), nullptr, 0, (int)n, nh, kv_lora, 0, 1.0f / sqrtf((float)nope),
+                       d_cacc, 0);
+    if (s != CWK_OK) { set_err(err, s, "%s", cwk_last_error(ctx)); return s; }
+    unabsorb_kernel<<<dim3((nh * vdim + 7) / 8, (unsigned)n), 256, 0, st>>>(d_cacc, (const uint16_t *)ly.kvb->data, nh, nope, vdim, kv_lora, d_attn);
+    ctx->launches += 1;
+    dev_linear(ctx, ly.o, d_attn, d_out, (int)n, (int64_t)nh * vdim, H);
+    // results and the chunk's cache rows back to the caller (pageable memory: synchronous copies)
+    bool ok = cudaMemcpyAsync(Out_host, d_out, (size_t)n * H * 4, cudaMemcpyDeviceToHost, st) == cudaSuccess;
+    if (ly.lbf) ok = ok && cudaMemcpyAsync(ly.host_layer + (size_t)pos0 * ly.host_row_bytes, cm.dev + (size_t)pos0 * kv_lora, (size_t)n * kv_lora * 2, cudaMemcpyDeviceToHost, st) == cudaSuccess;
+    else ok = ok && cudaMemcpyAsync(ly.host_layer + (size_t)pos0 * ly.host_row_bytes, d_kva, (size_t)n * kv_lora * 4, cudaMemcpyDeviceToHost, st) == cudaSuccess;
+    if (!ok || cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess) {
+        set_err(err, CWK_ERR_CUDA, "GPU chunk failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return CWK_ERR_CUDA;
+    }
+    if (cwk_check_device_error(ctx) != CWK_OK) { set_err(err, CWK_ERR_STATE, "%s", cwk_last_error(ctx)); return CWK_ERR_STATE; }
+    note_row_written(ly, pos0 + n - 1);
+    return CWK_OK;
+}
+
+// Resolve a layer call: checks, device context, mirrors. Returns a cwk status.
+int resolve_layer(Layer &ly, const cwkc_model_spec *spec, const cwkc_tensor *qa, const cwkc_tensor *qb, const cwkc_tensor *kva,
+                  const cwkc_tensor *kvb, const cwkc_tensor *o, const cwkc_tensor *qa_n, const cwkc_tensor *kva_n, float *keys,
+                  int64_t capacity, int64_t layer, const cwkc_indexer_weights *idx_w, cwkc_indexer_state *idx, cwkc_error *err) {
+    ly.spec = spec;
+    ly.H = spec->hidden_size;
+    ly.nh = (int)spec->num_attention_heads; ly.nope = (int)spec->qk_nope_head_dim; ly.vdim = (int)spec->value_head_dim;
+    ly.q_lora = (int)spec->q_lora_rank; ly.kv_lora = (int)spec->kv_lora_rank; ly.kv_dim = ly.nope + ly.vdim;
+    if (ly.kv_lora > 512 || (ly.kv_lora & 7)) { set_err(err, CWK_ERR_UNSUPPORTED, "kv_lora_rank %d not built (multiple of 8, <= 512)", ly.kv_lora); return CWK_ERR_UNSUPPORTED; }
+    if (kvb->kind != CWKC_WEIGHT_BF16 || qa_n->kind != CWKC_WEIGHT_BF16 || kva_n->kind != CWKC_WEIGHT_BF16) {
+        set_err(err, CWK_ERR_UNSUPPORTED, "kv_b_proj and the two layer norms are handled as BF16 tensors only");
+        return CWK_ERR_UNSUPPORTED;
+    }
+    for (const cwkc_tensor *t : {qa, qb, kva, o})
+        if (!kind_ok(t->kind)) { set_err(err, CWK_ERR_UNSUPPORTED, "projection weight kind %d is not handled (BF16, F32, FP8-E4M3)", t->kind); return CWK_ERR_UNSUPPORTED; }
+    if (!ensure_ctx(err)) return CWK_ERR_STATE;
+    ly.qa = mirror_weight(qa); ly.qb = mirror_weight(qb); ly.kva = mirror_weight(kva); ly.kvb = mirror_weight(kvb); ly.o = mirror_weight(o);
+    const WeightMirror *n1 = mirror_weight(qa_n), *n2 = mirror_weight(kva_n);
+    if (!ly.qa || !ly.qb || !ly.kva || !ly.kvb || !ly.o || !n1 || !n2) { set_err(err, CWK_ERR_MEMORY, "device mirror of a weight failed"); return CWK_ERR_MEMORY; }
+    ly.qa_n = (const uint16_t *)n1->data; ly.kva_n = (const uint16_t *)n2->data;
+    ly.lbf = cwick_latent_bf16_enabled();
+    ly.host_row_bytes = (size_t)ly.kv_lora * (ly.lbf ? 2 : 4);
+    ly.host_layer = (uint8_t *)keys + (size_t)layer * (size_t)capacity * ly.host_row_bytes;
+    ly.cm = &g.caches[{(const void *)keys, layer}];
+    if (idx_w && idx && spec->index_head_dim > 0 && spec->index_n_heads > 0) {
+        ly.idx_w = idx_w; ly.idx = idx;
+        ly.ih = (int)spec->index_n_heads; ly.ihd = (int)spec->index_head_dim; ly.kp = spec->index_kpool > 0 ? (int)spec->index_kpool : 1;
+        if (!idx_w->wq_b || !idx_w->wk || !idx_w->gate || !idx_w->ape || !idx_w->k_norm || !idx_w->k_norm_b || !idx_w->weights_proj ||
+            !idx->pool || !idx->tail_k || !idx->tail_g || !idx->sel || !idx->q || !idx->wt || !idx->sc || !idx->sc2) {
+            set_err(err, CWK_ERR_ARGUMENT, "indexer weights or state incomplete");
+            return CWK_ERR_ARGUMENT;
+        }
+        if (idx_w->ape->kind != CWKC_WEIGHT_BF16 || ly.ihd > 1024 || ly.kp > 8) {
+            set_err(err, CWK_ERR_UNSUPPORTED, "indexer shape not built (ape BF16, head dim <= 1024, kpool <= 8)");
+            return CWK_ERR_UNSUPPORTED;
+        }
+        ly.wq_b = mirror_weight(idx_w->wq_b); ly.wk = mirror_weight(idx_w->wk); ly.gate = mirror_weight(idx_w->gate);
+        ly.weights_proj = mirror_weight(idx_w->weights_proj);
+        const WeightMirror *ap = mirror_weight(idx_w->ape);
+        ly.k_norm = mirror_vector_f32(idx_w->k_norm, ly.ihd);
+        ly.k_norm_b = mirror_vector_f32(idx_w->k_norm_b, ly.ihd);
+        if (!ly.wq_b || !ly.wk || !ly.gate || !ly.weights_proj || !ap || !ly.k_norm || !ly.k_norm_b) {
+            set_err(err, CWK_ERR_MEMORY, "device mirror of an indexer weight failed");
+            return CWK_ERR_MEMORY;
+        }
+        ly.ape = (const uint16_t *)ap->data;
+        ly.im = &g.indexers[(const void *)idx];
+    }
+    return CWK_OK;
 }
 
 }  // namespace
@@ -141,7 +662,7 @@ const uint16_t *mirror_weight(const cwkc_tensor *t) {
 extern "C" {
 
 bool cwick_latent_bf16_enabled(void) {
-    // src/attention.c:288-296: CWICK_LATENT_BF16=1|on. This build keeps the latent in bf16 only.
+    // src/attention.c:288-296: CWICK_LATENT_BF16=1|on
     const char *e = getenv("CWICK_LATENT_BF16");
     return e && (e[0] == '1' || strcmp(e, "on") == 0);
 }
@@ -156,10 +677,12 @@ bool cwick_indexer_active(const cwkc_model_spec *spec, int64_t npos) {
 void cwk_dropin_reset(void) {
     std::lock_guard<std::mutex> lock(g.mu);
     if (g.ctx) cwk_ctx_sync(g.ctx);
-    for (auto &kv : g.weights) cudaFree(kv.second);
+    for (auto &kv : g.weights) { cudaFree(kv.second.data); if (kv.second.scales) cudaFree(kv.second.scales); }
     g.weights.clear();
     for (auto &kv : g.caches) cudaFree(kv.second.dev);
     g.caches.clear();
+    for (auto &kv : g.indexers) { cudaFree(kv.second.pool); cudaFree(kv.second.tails); }
+    g.indexers.clear();
 }
 
 void cwick_attention_mla_decode(const cwkc_model_spec *spec, const cwkc_tensor *qa, const cwkc_tensor *qb,
@@ -173,83 +696,11 @@ void cwick_attention_mla_decode(const cwkc_model_spec *spec, const cwkc_tensor *
         return set_err(err, CWK_ERR_ARGUMENT, "cwick_attention_mla_decode: bad argument");
     if (values != nullptr || !latent_ok(spec, kvb))
         return set_err(err, CWK_ERR_UNSUPPORTED, "expanded-cache MLA decode is not built into the GPU attention library");
-    if (idx_w || idx) return set_err(err, CWK_ERR_UNSUPPORTED, "pooled DSA indexer state is not handled by the GPU decode entry point");
-    if (!cwick_latent_bf16_enabled()) return set_err(err, CWK_ERR_UNSUPPORTED, "the GPU latent cache is bf16: set CWICK_LATENT_BF16=1");
-    const cwkc_tensor *ws[] = {qa, qb, kva, kvb, o, qa_n, kva_n};
-    for (const cwkc_tensor *t : ws)
-        if (t->kind != CWKC_WEIGHT_BF16) return set_err(err, CWK_ERR_UNSUPPORTED, "only BF16 projection weights are handled here");
-    const int64_t H = spec->hidden_size;
-    const int nh = (int)spec->num_attention_heads, nope = (int)spec->qk_nope_head_dim, vdim = (int)spec->value_head_dim;
-    const int q_lora = (int)spec->q_lora_rank, kv_lora = (int)spec->kv_lora_rank, kv_dim = nope + vdim;
-    if (kv_lora > 512 || (kv_lora & 7)) return set_err(err, CWK_ERR_UNSUPPORTED, "kv_lora_rank %d not built (multiple of 8, <= 512)", kv_lora);
-
     std::lock_guard<std::mutex> lock(g.mu);
-    if (!g.ctx) {
-        const char *d = getenv("CWK_DEVICE");
-        if (cwk_ctx_create(d ? atoi(d) : 0, &g.ctx) != CWK_OK) return set_err(err, CWK_ERR_STATE, "no usable sm_100 GPU");
-    }
-    cwk_ctx *ctx = g.ctx;
-    cudaStream_t st = ctx->stream;
-    const uint16_t *d_w[7];
-    for (int i = 0; i < 7; i++)
-        if (!(d_w[i] = mirror_weight(ws[i]))) return set_err(err, CWK_ERR_MEMORY, "device mirror of a weight failed");
-    // activations: x[H] qa[q_lora] q[nh*nope] kva[kv_lora] attn[nh*vdim] out[H] | bf16: qabs, cacc [nh*kv_lora]
-    const size_t nf = (size_t)H + q_lora + (size_t)nh * nope + kv_lora + (size_t)nh * vdim + H;
-    const size_t need = nf * 4 + (size_t)nh * kv_lora * 2 * 2 + 256;
-    if (need > g.d_buf_bytes) {
-        if (g.d_buf) cudaFree(g.d_buf);
-        if (cudaMalloc(&g.d_buf, need) != cudaSuccess) { g.d_buf = nullptr; g.d_buf_bytes = 0; return set_err(err, CWK_ERR_MEMORY, "device scratch"); }
-        g.d_buf_bytes = need;
-    }
-    const size_t pin_need = (size_t)H * 4 * 2 + (size_t)kv_lora * 2;
-    if (pin_need > g.pin_bytes) {
-        if (g.pin) cudaFreeHost(g.pin);
-        if (cudaMallocHost(&g.pin, pin_need) != cudaSuccess) { g.pin = nullptr; g.pin_bytes = 0; return set_err(err, CWK_ERR_MEMORY, "pinned staging"); }
-        g.pin_bytes = pin_need;
-    }
-    float *d_x = g.d_buf, *d_qa = d_x + H, *d_q = d_qa + q_lora, *d_kva = d_q + (size_t)nh * nope;
-    float *d_attn = d_kva + kv_lora, *d_out = d_attn + (size_t)nh * vdim;
-    uint16_t *d_qabs = (uint16_t *)(d_out + H), *d_cacc = d_qabs + (size_t)nh * kv_lora;
-    float *p_x = (float *)g.pin, *p_out = p_x + H;
-    uint16_t *p_row = (uint16_t *)(p_out + H);
-
-    // the latent cache mirror of this (array, layer)
-    CacheMirror &cm = g.caches[{(const void *)keys, layer}];
-    uint16_t *host_layer = (uint16_t *)keys + (size_t)layer * (size_t)capacity * (size_t)kv_lora;
-    if (!cm.dev || cm.capacity != capacity || cm.width != kv_lora) {
-        if (cm.dev) cudaFree(cm.dev);
-        if (cudaMalloc(&cm.dev, (size_t)capacity * kv_lora * 2) != cudaSuccess) { cm.dev = nullptr; return set_err(err, CWK_ERR_MEMORY, "device latent cache"); }
-        cm.capacity = capacity; cm.width = kv_lora; cm.next_pos = 0;
-    }
-    if (pos != cm.next_pos && pos > 0) {     // the caller rewound or restored a prefix: take rows 0..pos-1 from its array
-        if (cudaMemcpyAsync(cm.dev, host_layer, (size_t)pos * kv_lora * 2, cudaMemcpyHostToDevice, st) != cudaSuccess)
-            return set_err(err, CWK_ERR_CUDA, "latent cache upload failed");
-    }
-
-    memcpy(p_x, x, (size_t)H * 4);
-    cudaMemcpyAsync(d_x, p_x, (size_t)H * 4, cudaMemcpyHostToDevice, st);
-    gemv_bf16_kernel<<<(q_lora + 7) / 8, 256, 0, st>>>(d_w[0], d_x, d_qa, q_lora, (int)H);
-    gemv_bf16_kernel<<<(kv_lora + 7) / 8, 256, 0, st>>>(d_w[2], d_x, d_kva, kv_lora, (int)H);
-    rms_scale_kernel<<<1, 256, 0, st>>>(d_qa, q_lora, d_w[5], spec->rms_norm_eps_f, nullptr);
-    gemv_bf16_kernel<<<(nh * nope + 7) / 8, 256, 0, st>>>(d_w[1], d_qa, d_q, nh * nope, q_lora);
-    rms_scale_kernel<<<1, 256, 0, st>>>(d_kva, kv_lora, d_w[6], spec->rms_norm_eps_f, cm.dev + (size_t)pos * kv_lora);
-    cudaMemcpyAsync(p_row, cm.dev + (size_t)pos * kv_lora, (size_t)kv_lora * 2, cudaMemcpyDeviceToHost, st);
-    absorb_q_kernel<<<nh, 256, 0, st>>>(d_q, d_w[3], nope, kv_dim, kv_lora, d_qabs);
-    ctx->launches += 6;
-    int s = cwk_mla_decode_rows(ctx, d_qabs, cm.dev, kv_lora, (int)(pos + 1), nh, kv_lora, 0, 1.0f / sqrtf((float)nope), d_cacc);
-    if (s != CWK_OK) return set_err(err, s, "%s", cwk_last_error(ctx));
-    unabsorb_kernel<<<(nh * vdim + 7) / 8, 256, 0, st>>>(d_cacc, d_w[3], nh, nope, vdim, kv_lora, d_attn);
-    gemv_bf16_kernel<<<(int)((H + 7) / 8), 256, 0, st>>>(d_w[4], d_attn, d_out, (int)H, nh * vdim);
-    ctx->launches += 2;
-    cudaMemcpyAsync(p_out, d_out, (size_t)H * 4, cudaMemcpyDeviceToHost, st);
-    if (cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess)
-        return set_err(err, CWK_ERR_CUDA, "GPU decode failed: %s", cudaGetErrorString(cudaGetLastError()));
-    if (cwk_check_device_error(ctx) != CWK_OK) return set_err(err, CWK_ERR_STATE, "%s", cwk_last_error(ctx));
-    memcpy(out, p_out, (size_t)H * 4);
-    memcpy(host_layer + (size_t)pos * kv_lora, p_row, (size_t)kv_lora * 2);     // the caller's array stays the source of truth
-    cm.next_pos = pos + 1;
+    Layer ly;
+    if (resolve_layer(ly, spec, qa, qb, kva, kvb, o, qa_n, kva_n, keys, capacity, layer, idx_w, idx, err) != CWK_OK) return;
+    token_step(g.ctx, ly, capacity, pos, x, out, err);
 }
-
 
 // cwick_attention_kda_decode (src/attention.c:1176-1437) on the GPU: the six projections of x, the two second-stage
 // gates, cwk_kda_step, o_proj. The signature leaves the layer's recurrent state and convolution window with the caller
@@ -292,15 +743,16 @@ void cwick_attention_kda_decode(const cwkc_model_spec *spec, const cwkc_tensor *
     if ((hd != 32 && hd != 64 && hd != 128) || (H & 7)) return set_err(err, CWK_ERR_UNSUPPORTED, "KDA head dim %d / hidden %lld not built", hd, (long long)H);
 
     std::lock_guard<std::mutex> lock(g.mu);
-    if (!g.ctx) {
-        const char *d = getenv("CWK_DEVICE");
-        if (cwk_ctx_create(d ? atoi(d) : 0, &g.ctx) != CWK_OK) return set_err(err, CWK_ERR_STATE, "no usable sm_100 GPU");
-    }
+    if (!ensure_ctx(err)) return;
     cwk_ctx *ctx = g.ctx;
     cudaStream_t st = ctx->stream;
     const uint16_t *d_w[13];
     for (int i = 0; i < 13; i++)
-        if (!(d_w[i] = mirror_weight(ws[i]))) return set_err(err, CWK_ERR_MEMORY, "device mirror of a weight failed");
+        {
+            const WeightMirror *wm = mirror_weight(ws[i]);
+            if (!wm) return set_err(err, CWK_ERR_MEMORY, "device mirror of a weight failed");
+            d_w[i] = (const uint16_t *)wm->data;
+        }
     // floats: x[H] q k v gate_raw gate core [proj each] f_a g_a [hd each] beta a_log [nh each] dt[proj] out[H] rec conv
     const size_t n_rec = (size_t)nh * hd * hd, n_conv = (size_t)3 * proj * 3;
     const size_t nf = (size_t)H * 2 + (size_t)proj * 7 + (size_t)hd * 2 + (size_t)nh * 2 + n_rec + n_conv + 64;
@@ -323,19 +775,19 @@ void cwick_attention_kda_decode(const cwkc_model_spec *spec, const cwkc_tensor *
     cudaMemcpyAsync(d_rec, h_rec, n_rec * 4, cudaMemcpyHostToDevice, st);
     cudaMemcpyAsync(d_conv, h_conv, n_conv * 4, cudaMemcpyHostToDevice, st);
     const int P = (int)proj;
-    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[0], d_x, d_q, P, (int)H);
-    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[1], d_x, d_k, P, (int)H);
-    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[2], d_x, d_v, P, (int)H);
-    gemv_bf16_kernel<<<(hd + 7) / 8, 256, 0, st>>>(d_w[3], d_x, d_fa, hd, (int)H);
-    gemv_bf16_kernel<<<(nh + 7) / 8, 256, 0, st>>>(d_w[4], d_x, d_beta, nh, (int)H);
-    gemv_bf16_kernel<<<(hd + 7) / 8, 256, 0, st>>>(d_w[5], d_x, d_ga, hd, (int)H);
-    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[6], d_fa, d_graw, P, hd);
-    gemv_bf16_kernel<<<(P + 7) / 8, 256, 0, st>>>(d_w[7], d_ga, d_gate, P, hd);
+    gemv_bf16_kernel<<<dim3((P + 7) / 8, 1), 256, 0, st>>>(d_w[0], d_x, d_q, P, (int)H, 0, 0);
+    gemv_bf16_kernel<<<dim3((P + 7) / 8, 1), 256, 0, st>>>(d_w[1], d_x, d_k, P, (int)H, 0, 0);
+    gemv_bf16_kernel<<<dim3((P + 7) / 8, 1), 256, 0, st>>>(d_w[2], d_x, d_v, P, (int)H, 0, 0);
+    gemv_bf16_kernel<<<dim3((hd + 7) / 8, 1), 256, 0, st>>>(d_w[3], d_x, d_fa, hd, (int)H, 0, 0);
+    gemv_bf16_kernel<<<dim3((nh + 7) / 8, 1), 256, 0, st>>>(d_w[4], d_x, d_beta, nh, (int)H, 0, 0);
+    gemv_bf16_kernel<<<dim3((hd + 7) / 8, 1), 256, 0, st>>>(d_w[5], d_x, d_ga, hd, (int)H, 0, 0);
+    gemv_bf16_kernel<<<dim3((P + 7) / 8, 1), 256, 0, st>>>(d_w[6], d_fa, d_graw, P, hd, 0, 0);
+    gemv_bf16_kernel<<<dim3((P + 7) / 8, 1), 256, 0, st>>>(d_w[7], d_ga, d_gate, P, hd, 0, 0);
     ctx->launches += 8;
     int s = cwk_kda_step(ctx, 1, nh, hd, spec->gate_lower_bound, spec->rms_norm_eps_f, d_q, d_k, d_v, d_w[9], d_w[10], d_w[11], d_conv,
                          d_graw, d_dt, d_alog, d_beta, d_gate, d_w[12], d_rec, d_core);
     if (s != CWK_OK) return set_err(err, s, "%s", cwk_last_error(ctx));
-    gemv_bf16_kernel<<<(int)((H + 7) / 8), 256, 0, st>>>(d_w[8], d_core, d_out, (int)H, P);
+    gemv_bf16_kernel<<<dim3((unsigned)((H + 7) / 8), 1), 256, 0, st>>>(d_w[8], d_core, d_out, (int)H, P, 0, 0);
     ctx->launches += 1;
     cudaMemcpyAsync(out, d_out, (size_t)H * 4, cudaMemcpyDeviceToHost, st);
     cudaMemcpyAsync(h_rec, d_rec, n_rec * 4, cudaMemcpyDeviceToHost, st);
@@ -371,20 +823,38 @@ void cwick_indexer_reset(const cwkc_model_spec *spec, cwkc_indexer_state *st) {
     st->n_pools = 0;
 }
 
-// The chunk path with host pointers is not taken over: the engine asks first (src/engine.c:2387-2414) and runs its
-// per-token loop through cwick_attention_mla_decode above when the answer is no; a device-resident caller uses
-// cwk_mla_prefill. The entry point itself answers CWICK_ERR_UNSUPPORTED, on which the caller falls back too
-// (src/engine.c:2415-2431).
-bool cwick_mla_chunk_supported(const cwkc_model_spec *, const cwkc_tensor *, const cwkc_tensor *, const cwkc_tensor *,
-                               const cwkc_tensor *, const cwkc_tensor *, const float *) {
-    return false;
+// src/attention.c:932-941: the chunk path runs for the latent layout with BF16 projections (the reference's own
+// condition, kept as it is: the engine asks before it commits to the chunk's pre-mix).
+bool cwick_mla_chunk_supported(const cwkc_model_spec *spec, const cwkc_tensor *qa, const cwkc_tensor *qb, const cwkc_tensor *kva,
+                               const cwkc_tensor *kvb, const cwkc_tensor *o, const float *values) {
+    if (!spec || !qa || !qb || !kva || !kvb || !o) return false;
+    const char *e = getenv("CWICK_NO_CHUNK_ATTN");
+    if (e && *e && *e != '0') return false;
+    if (values != nullptr || !latent_ok(spec, kvb)) return false;
+    return qa->kind == CWKC_WEIGHT_BF16 && kva->kind == CWKC_WEIGHT_BF16 && qb->kind == CWKC_WEIGHT_BF16 && o->kind == CWKC_WEIGHT_BF16;
 }
-int cwick_attention_mla_prefill_chunk(const cwkc_model_spec *, const cwkc_tensor *, const cwkc_tensor *, const cwkc_tensor *,
-                                      const cwkc_tensor *, const cwkc_tensor *, const cwkc_tensor *, const cwkc_tensor *, float *, float *,
-                                      int64_t, int64_t, int64_t, int64_t, const cwkc_indexer_weights *, cwkc_indexer_state *,
-                                      const float *, float *, cwkc_error *err) {
-    set_err(err, CWK_ERR_UNSUPPORTED, "the host-pointer chunk path is not taken over: per-token decode, or cwk_mla_prefill on device buffers");
-    return CWK_ERR_UNSUPPORTED;
+
+// src/attention.c:943-1024. Without an indexer every stage is batched over the chunk's tokens; with one, the
+// selection depends on token order (each token absorbs into the pools before it selects), so the tokens run one
+// after another through the same stages as the decode entry point.
+int cwick_attention_mla_prefill_chunk(const cwkc_model_spec *spec, const cwkc_tensor *qa, const cwkc_tensor *qb, const cwkc_tensor *kva,
+                                      const cwkc_tensor *kvb, const cwkc_tensor *o, const cwkc_tensor *qa_n, const cwkc_tensor *kva_n,
+                                      float *keys, float *values, int64_t capacity, int64_t pos0, int64_t n, int64_t layer,
+                                      const cwkc_indexer_weights *idx_w, cwkc_indexer_state *idx, const float *X, float *Out,
+                                      cwkc_error *err) {
+    if (!spec || n <= 0 || !keys || !qa || !qb || !kva || !kvb || !o || !qa_n || !kva_n || !X || !Out || pos0 < 0 || pos0 + n > capacity)
+        return CWK_ERR_ARGUMENT;
+    if (!cwick_mla_chunk_supported(spec, qa, qb, kva, kvb, o, values)) return CWK_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g.mu);
+    Layer ly;
+    int s = resolve_layer(ly, spec, qa, qb, kva, kvb, o, qa_n, kva_n, keys, capacity, layer, idx_w, idx, err);
+    if (s != CWK_OK) return s;
+    if (!ly.idx) return chunk_steps(g.ctx, ly, capacity, pos0, n, X, Out, err);
+    for (int64_t t = 0; t < n; t++) {
+        s = token_step(g.ctx, ly, capacity, pos0 + t, X + t * ly.H, Out + t * ly.H, err);
+        if (s != CWK_OK) return s;
+    }
+    return CWK_OK;
 }
 
 }  // extern "C"

@@ -91,18 +91,31 @@ typedef struct cwkc_indexer_state {
 #ifndef CWICK_COMPAT_TYPES_ONLY   /* (the ABI check includes the reference's own prototypes instead) */
 /* ---- reference-named entry points (src/cwick.h:864-893) --------------------
  * cwick_attention_mla_decode: one token of one sparse-attention layer, latent
- * (absorbed) path: q_a/kv_a/q_b projections, norms, latent row write, absorb,
- * attention over rows 0..pos, un-absorb, o_proj -- src/attention.c:642-902 --
- * computed on the GPU. Host pointers in and out, as the reference passes them.
- * Handled: values == NULL, qk_rope_head_dim == 0, BF16 weights, bf16 latent
- * cache (CWICK_LATENT_BF16=1), no indexer. Anything else is not computed:
- * `out` is left untouched and err (when given) carries CWICK_ERR_UNSUPPORTED --
- * there is no CPU fallback in this library.
- * The weights are mirrored to the device on first sight (keyed by their host
- * data pointer); the latent cache is mirrored per (keys, layer) and kept in
- * step: row `pos` is written to BOTH the device mirror and the caller's host
- * array (so prefix snapshots keep working); a call whose pos is not the
- * mirror's next row re-uploads rows 0..pos-1 from the host array first. */
+ * (absorbed) path: q_a/kv_a/q_b projections, norms, latent row write, DSA
+ * indexer (pool absorb + selection), absorb, attention over the selected rows
+ * (or rows 0..pos), un-absorb, o_proj -- src/attention.c:642-902 -- computed on
+ * the GPU. Host pointers in and out, as the reference passes them.
+ * Handled: values == NULL and qk_rope_head_dim == 0 (the latent layout);
+ * q_a / q_b / kv_a / o_proj as BF16, F32 or FP8-E4M3 with 128x128 F32 scales
+ * (src/tensor.c:745-765); kv_b_proj and the two norms as BF16; the latent cache
+ * in the caller's width, bf16 (CWICK_LATENT_BF16=1) or f32 (the device copy is
+ * bf16 either way: f32 rows are narrowed on upload); idx_w / idx with
+ * index_kpool <= 8: the pool rows, both tails, n_pools, q, wt, sc and sel of
+ * the caller's cwick_indexer_state are kept exactly as the reference keeps
+ * them (the selection repeats the reference's own threshold search on the
+ * device-computed scores, so sel[] is the reference's entry for entry).
+ * Anything else (the expanded cache, values != NULL) is not computed: `out` is
+ * left untouched and err (when given) carries CWICK_ERR_UNSUPPORTED -- there is
+ * no CPU fallback in this library.
+ * Mirrors: weights are copied to the device on first sight (keyed by data
+ * pointer, shape and kind); the latent cache per (keys, layer) and the indexer
+ * pool per state pointer. Row `pos` is written to BOTH the device mirror and
+ * the caller's array (so prefix snapshots keep working). A call re-uploads
+ * rows 0..pos-1 from the caller's array when pos is not the mirror's next row
+ * or when the caller's row pos-1 is no longer the one written through the
+ * mirror (a restored prefix of the same length); the same two checks guard the
+ * pool. A caller that rewrites OLDER rows in place without touching the last
+ * one must call cwk_dropin_reset(). */
 CWK_API void cwick_attention_mla_decode(const cwkc_model_spec *spec, const cwkc_tensor *qa, const cwkc_tensor *qb,
                                         const cwkc_tensor *kva, const cwkc_tensor *kvb, const cwkc_tensor *g,
                                         const cwkc_tensor *o, const cwkc_tensor *qa_n, const cwkc_tensor *kva_n,
@@ -117,8 +130,11 @@ CWK_API size_t cwick_latent_elem_bytes(void);
 /* The rest of attention.c's link surface (src/cwick.h:864-938; src/prof.c:78-85 reads the six counters).
  * cwick_attention_kda_decode computes the layer on the GPU (BF16 weights, convolution width 4, head dim 32/64/128);
  * the layer's state and window stay with the caller, so they cross to the device and back on every call.
- * The chunk path with host pointers is not taken over: cwick_mla_chunk_supported answers false and the entry point
- * CWICK_ERR_UNSUPPORTED, on either of which the engine runs its per-token loop (src/engine.c:2387-2431). */
+ * cwick_mla_chunk_supported answers as the reference does (latent layout, BF16 projections, src/attention.c:932-941)
+ * and cwick_attention_mla_prefill_chunk (src/attention.c:943-1024) runs the chunk on the GPU: every stage batched
+ * over the chunk's tokens when the layer has no indexer, token after token when it has (the selection depends on
+ * token order). Same statuses as the reference: CWICK_ERR_ARGUMENT, CWICK_ERR_UNSUPPORTED (the engine then runs its
+ * per-token loop, src/engine.c:2415-2431), CWICK_ERR_MEMORY. */
 CWK_API uint64_t cwick_indexer_bytes(const cwkc_model_spec *spec, int64_t capacity);
 CWK_API void cwick_indexer_reset(const cwkc_model_spec *spec, cwkc_indexer_state *st);
 CWK_API bool cwick_mla_chunk_supported(const cwkc_model_spec *spec, const cwkc_tensor *qa, const cwkc_tensor *qb,

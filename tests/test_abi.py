@@ -71,8 +71,10 @@ def test_product_code_never_touches_the_oracle():
 
 
 def test_link_surface_answers_without_a_gpu():
-    """The reference-named symbols that compute nothing answer as documented on any machine: the chunk path is not
-    taken over (false / CWICK_ERR_UNSUPPORTED, on which the engine falls back per token), the counters exist."""
+    """The reference-named symbols answer as the reference's do on any machine, before any GPU is touched: a missing
+    argument is CWICK_ERR_ARGUMENT (src/attention.c:958), a layer that is not in the latent layout is not taken by the
+    chunk path (false / CWICK_ERR_UNSUPPORTED, on which the engine falls back per token, src/engine.c:2415-2431), the
+    counters exist."""
     import ctypes as C
     L = lib.load()
 
@@ -86,7 +88,19 @@ def test_link_surface_answers_without_a_gpu():
     L.cwick_attention_mla_prefill_chunk.restype = C.c_int
     L.cwick_attention_mla_prefill_chunk.argtypes = [C.c_void_p] * 10 + [C.c_int64] * 4 + [C.c_void_p] * 5
     st = L.cwick_attention_mla_prefill_chunk(C.addressof(spec), *([None] * 9), 0, 0, 0, 0, None, None, None, None, C.byref(err))
-    assert st == lib.ERR_UNSUPPORTED and err.status == lib.ERR_UNSUPPORTED and err.message
+    assert st == lib.ERR_ARGUMENT
+    # a zeroed spec is not a latent-MLA layer: with every pointer in place the chunk path declines it
+    class Tensor(C.Structure):
+        _fields_ = [("rows", C.c_int64), ("cols", C.c_int64), ("kind", C.c_int), ("data", C.c_void_p),
+                    ("scales", C.c_void_p), ("data_bytes", C.c_size_t), ("scale_bytes", C.c_size_t), ("name", C.c_char * 128)]
+    t = Tensor()
+    t.kind = 1
+    buf = (C.c_float * 16)()
+    tp, bp = C.addressof(t), C.addressof(buf)
+    assert L.cwick_mla_chunk_supported(C.addressof(spec), tp, tp, tp, tp, tp, None) is False
+    st = L.cwick_attention_mla_prefill_chunk(C.addressof(spec), tp, tp, tp, tp, tp, tp, tp, bp, None, 4, 0, 1, 0, None, None, bp, bp,
+                                             C.byref(err))
+    assert st == lib.ERR_UNSUPPORTED
     for name in ("proj", "conv", "gate", "rec", "mla", "tail"):
         assert C.c_uint64.in_dll(L, "g_attn_%s_ns" % name).value == 0
     L.cwick_indexer_bytes.restype = C.c_uint64

@@ -94,6 +94,6 @@ def test_link_surface_symbols():
     L.cwick_attention_mla_prefill_chunk.restype = C.c_int
     L.cwick_attention_mla_prefill_chunk.argtypes = [C.c_void_p] * 10 + [C.c_int64] * 4 + [C.c_void_p] * 5
     st = L.cwick_attention_mla_prefill_chunk(C.addressof(spec), *([None] * 9), 0, 0, 0, 0, None, None, None, None, C.byref(err))
-    assert st == cl.ERR_UNSUPPORTED and err.status == cl.ERR_UNSUPPORTED
+    assert st == cl.ERR_ARGUMENT          # nothing to run on: the reference answers the same (src/attention.c:958)
     for name in ("proj", "conv", "gate", "rec", "mla", "tail"):
         assert C.c_uint64.in_dll(L, "g_attn_%s_ns" % name).value == 0
