@@ -6,13 +6,16 @@
 
 Default workload `c2` is BASELINE.json's config 2: MLA absorbed decode, batch 1,
 64 heads, 512-d latent + 64-d rope key, 8192 cached tokens, BF16. One *step* is
-one decode call on each of ROT distinct sequences (each call batch 1, its own
-cache), so consecutive calls never find their cache in L2 (ROT x 9.4 MB > 126 MB).
-`value` is tokens/s with everything resident in HBM (the ROT calls replayed as one
-CUDA graph); `e2e` is the same work through the host-buffer entry point
-(cwk_mla_decode_host: pinned staging, H2D of q, D2H of the output, one sync per
-call). With N > 1 every rank runs the same step on its own sequences (weak
-scaling, no collective: sequences are independent).
+ROUNDS passes over ROT distinct sequences, one batch-1 decode call per sequence
+and pass (512 calls); consecutive calls never find their cache in L2
+(ROT x 9.4 MB > 126 MB). `value` is tokens/s with everything resident in HBM (the
+calls of a step replayed as one CUDA graph); `e2e` is the same work through the
+host-buffer entry point (cwk_mla_decode_host: pinned staging, H2D of q, D2H of
+the output, one sync per call). With N > 1 every rank runs the same step on its
+own sequences (weak scaling, no collective: sequences are independent), and
+`extra` carries BASELINE config 5 at that N: the batch of 64 x 32768 dealt over
+the ranks by sequence (strong scaling, no collective) and one 131072-token
+sequence split by KV range with the peer-memory exchange of partial records.
 
 `--impl reference` times the reference's own CPU attention (oracle/_ref, the
 unmodified cwick_attention_mla_decode latent path over a bf16 cache) on the
@@ -37,12 +40,13 @@ sys.path.insert(0, ROOT)
 NH, L, R = 64, 512, 64
 DK = L + R
 SCALE = 1.0 / math.sqrt(192.0)
-ROT = 32                      # distinct sequences per step
+ROT = 32                      # distinct sequences (each its own 9.4 MB cache): 302 MB in rotation, no call finds its cache in L2
+ROUNDS = 16                   # passes over them per step, so that a step is milliseconds, not microseconds
 L2_BYTES = 126 * 1024 * 1024
 
 WORKLOADS = {
     # name: (sequences per call, cached tokens, calls per step)
-    "c2": dict(B=1, T=8192, calls=ROT, desc="config 2: MLA absorbed decode, batch 1, 64 heads, 512+64 bf16, 8192 cached tokens"),
+    "c2": dict(B=1, T=8192, calls=ROT, rounds=ROUNDS, desc="config 2: MLA absorbed decode, batch 1, 64 heads, 512+64 bf16, 8192 cached tokens"),
     "c5a": dict(B=64, T=32768, calls=1, desc="config 5a on one GPU: 64 sequences x 32768 cached tokens, one batched call"),
     "c5b": dict(B=1, T=131072, calls=1, desc="config 5b: one sequence, 131072 cached tokens, KV rows split across the GPUs, partial records exchanged and merged with a log-sum-exp combine"),
     "c5a8": dict(B=8, T=32768, calls=1, desc="config 5a, one GPU's share at 8 GPUs: 8 sequences x 32768 cached tokens, one batched call"),
@@ -217,6 +221,7 @@ def run_ours(args):
 
     wl = WORKLOADS[args.workload]
     B, T, calls = wl["B"], wl["T"], wl["calls"]
+    rounds = wl.get("rounds", 1)
     if args.workload == "c5b":
         return run_kv_split(args, torch, dist, world, rank, local, dev, wl)
     stream = torch.cuda.Stream(device=dev)
@@ -237,16 +242,17 @@ def run_ours(args):
     if total_cache_bytes <= 2 * L2_BYTES:    # inputs do not exceed L2 by themselves: flush between steps
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
 
-    def step_device():
-        for i in range(calls):
-            attn.mla_decode(qs[i], caches[i], lens, max_kv_len=T, scale=SCALE, out=outs[i])
+    def step_device(r=rounds):
+        for _ in range(r):
+            for i in range(calls):
+                attn.mla_decode(qs[i], caches[i], lens, max_kv_len=T, scale=SCALE, out=outs[i])
 
     # warm-up outside capture (scratch allocation, function attributes), then capture one step
     step_device()
     stream.synchronize()
     l0 = attn.ctx.launches
     step_device()
-    launches_per_step = attn.ctx.launches - l0
+    launches_per_step = attn.ctx.launches - l0          # kernels of this library per step (decode + split merge per call)
     stream.synchronize()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=stream):
@@ -292,14 +298,14 @@ def run_ours(args):
     steps, warmup = args.steps, max(3, args.warmup)
     ms_total, clocks = timed(graph.replay, steps, warmup)
     ms_step = ms_total / steps
-    tokens_per_step = calls * B * world
+    tokens_per_step = rounds * calls * B * world
     value = tokens_per_step / (ms_step / 1e3)
-    kv_gbs = world * calls * algorithmic_bytes(B, T) / (ms_step / 1e3) / 1e9
+    kv_gbs = world * rounds * calls * algorithmic_bytes(B, T) / (ms_step / 1e3) / 1e9
 
     # ---- roofline: main kernel's own duration, CUDA events on the launching stream ----
     attn.ctx.profile(True)
     for _ in range(max(1, min(steps, 20))):
-        step_device()
+        step_device(1)
     k_ms, k_n = attn.ctx.profile_read()
     attn.ctx.profile(False)
     peak, peak_kind = peaks()
@@ -333,16 +339,17 @@ def run_ours(args):
               _cl.vp(lens_h.data_ptr()), None, 0, B, NH, L, R, SCALE, _cl.vp(oh[i].data_ptr()), 0) for i in range(calls)]
 
     def step_host():
-        for a in bound:
-            st = host_fn(*a)
-            if st:
-                attn.ctx.check(st)
+        for _ in range(rounds):
+            for a in bound:
+                st = host_fn(*a)
+                if st:
+                    attn.ctx.check(st)
 
     e_steps = max(3, min(steps, 20))
     e_ms, _ = timed(step_host, e_steps, 3)
     e2e_value = tokens_per_step / (e_ms / e_steps / 1e3)
-    h2d = calls * (B * NH * DK * 2 + (B * 4 if B > 1 else 0))      # one sequence: its length is a call argument
-    d2h = calls * B * NH * L * 2
+    h2d = rounds * calls * (B * NH * DK * 2 + (B * 4 if B > 1 else 0))      # one sequence: its length is a call argument
+    d2h = rounds * calls * B * NH * L * 2
     # sanity: both paths computed the same thing
     # (cross-block sums go through f32 atomics in no fixed order: equal up to a bf16 step, not bit for bit)
     assert float((oh[0].float() - outs[0].cpu().float()).abs().max()) <= 4e-3, "host and device entry points disagree"
@@ -350,7 +357,7 @@ def run_ours(args):
     line = {"metric": "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl["desc"], "calls_per_step": calls, "sequences_per_call": B, "cached_tokens": T,
+            "config": {"workload": wl["desc"], "calls_per_step": rounds * calls, "distinct_sequences": calls, "sequences_per_call": B, "cached_tokens": T,
                        "heads": NH, "latent": L, "rope": R,
                        "l2": "flush between steps" if flush is not None else "inputs larger than L2 (%d MB per step)" % (total_cache_bytes >> 20),
                        "parallelism": f"{world} x independent sequences"},
@@ -359,17 +366,23 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "cwk_mla_decode_host"},
             "gpu_launches": int(launches_per_step * steps)}
+    del graph
 
-    if rank == 0 and world == 1 and not args.no_extra:
-        extra = {}
-        if args.workload == "c2":
+    extra = {}
+    if args.workload == "c2" and not args.no_extra:
+        # BASELINE config 5 at this N, on every rank (collective calls inside: all ranks take the same path)
+        del caches, qs, outs, flush
+        torch.cuda.empty_cache()
+        for name, fn in (("c5a_batch64x32768_by_sequence", side_c5a), ("c5b_one_sequence_131072_by_kv_range", side_c5b)):
             try:
-                del caches, qs, outs
-                torch.cuda.empty_cache()
-                extra["c5a_64x32768"] = side_measure(attn, dev, stream, 64, 32768, peak)
+                extra[name] = fn(attn, torch, dist, world, rank, local, dev, stream, peak)
             except Exception as e:  # noqa: BLE001
-                extra["c5a_64x32768"] = {"error": str(e)[:200]}
-            for name, fn in (("c1_gqa_decode_4096", side_gqa_decode), ("c3_mla_prefill_4096", side_prefill),
+                extra[name] = {"error": str(e)[:300]}
+            torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_extra:
+        if args.workload == "c2":
+            for name, fn in (("c1_gqa_decode_4096", side_gqa_decode), ("gqa_batched_decode_and_attnbench_tile", side_gqa_batched_and_prefill),
+                             ("c3_mla_prefill_4096", side_prefill),
                              ("c4_dsa_8x65536_top2048", side_dsa),
                              ("kda_decode_step_64x128", side_kda),
                              ("gdn_step_and_mm_indexer", side_gdn_mm)):
@@ -378,9 +391,10 @@ def run_ours(args):
                     extra[name] = fn(attn, dev, stream, peak)
                 except Exception as e:  # noqa: BLE001
                     extra[name] = {"error": str(e)[:200]}
-        line["extra"] = extra
         tps, info = cpu_reference(seconds_budget=12.0)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", **info}
+    if extra:
+        line["extra"] = extra
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -460,6 +474,113 @@ def run_kv_split(args, torch, dist, world, rank, local, dev, wl):
         dist.destroy_process_group()
 
 
+def _max_over_ranks(torch, dist, world, dev, x):
+    if world == 1:
+        return x
+    t = torch.tensor([x], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def side_c5a(attn, torch, dist, world, rank, local, dev, stream, peak):
+    """BASELINE config 5, first case: ONE batch of 64 sequences x 32768 cached tokens, dealt over the ranks by sequence
+    (cwick_b200.dist.shard_sequences; no collective, the sequences are independent). Strong scaling: the batch is
+    the same at every N. A step = one batched decode call per rank; time = max over ranks, CUDA events."""
+    from cwick_b200 import dist as cd
+    Bt, T = 64, 32768
+    mine = cd.shard_sequences(Bt, world, rank)
+    B = len(mine)
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    cache = torch.empty(B, T, DK, device=dev, dtype=torch.bfloat16)
+    for b in range(B):
+        cache[b] = torch.randn(T, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    q = torch.randn(B, NH, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    lens = torch.full((B,), T, dtype=torch.int32, device=dev)
+    out = torch.empty(B, NH, L, device=dev, dtype=torch.bfloat16)
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev) if B * T * DK * 2 <= 2 * L2_BYTES else None
+    for _ in range(3):
+        attn.mla_decode(q, cache, lens, max_kv_len=T, scale=SCALE, out=out)
+    n = 20
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+    for i in range(n):                          # the calls of a serving loop follow one another without a host sync
+        if flush is not None:
+            flush.fill_(i & 1)
+        ev[i][0].record(stream)
+        attn.mla_decode(q, cache, lens, max_kv_len=T, scale=SCALE, out=out)
+        ev[i][1].record(stream)
+    torch.cuda.synchronize(dev)
+    ms = sum(a.elapsed_time(b) for a, b in ev)
+    attn.ctx.profile(True)
+    for i in range(n):
+        attn.mla_decode(q, cache, lens, max_kv_len=T, scale=SCALE, out=out)
+    k_ms, k_n = attn.ctx.profile_read()
+    attn.ctx.profile(False)
+    ms = _max_over_ranks(torch, dist, world, dev, ms / n)
+    k_ms = _max_over_ranks(torch, dist, world, dev, k_ms / max(1, k_n))
+    by = algorithmic_bytes(B, T)
+    return {"n_gpus": world, "sequences": Bt, "sequences_per_gpu": B, "cached_tokens": T, "scaling": "strong",
+            "ms_per_step": ms, "tokens_per_s": Bt / (ms / 1e3), "kv_hbm_gbs_total": world * by / (ms / 1e3) / 1e9,
+            "per_gpu": {"main_kernel_ms": k_ms, "kernel_gbs": by / (k_ms / 1e3) / 1e9,
+                        "kernel_frac_of_measured_peak": by / (k_ms / 1e3) / 1e9 / peak,
+                        "call_frac_of_measured_peak": by / (ms / 1e3) / 1e9 / peak, "algorithmic_bytes": by},
+            "collective": "none (sequences are independent)"}
+
+
+def side_c5b(attn, torch, dist, world, rank, local, dev, stream, peak):
+    """BASELINE config 5, second case: ONE sequence of 131072 cached tokens whose rows are split by range over the
+    ranks; each rank decodes its rows, the 131,584-byte partial records are exchanged by the kernels themselves
+    (stores into the peers' windows over NVLink + epoch flags) and every rank merges. Strong scaling."""
+    from cwick_b200 import dist as cd
+    T = 131072
+    row0, rows = cd.kv_ranges(T, world)[rank]
+    g = torch.Generator(device=dev).manual_seed(20261125)            # q is the same on every rank
+    q = torch.randn(NH, DK, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    g2 = torch.Generator(device=dev).manual_seed(31 + rank)
+    rot = max(2, (2 * L2_BYTES) // max(1, rows * DK * 2) + 1)         # distinct local caches so a step never hits L2
+    caches = [torch.randn(rows, DK, device=dev, generator=g2, dtype=torch.float32).to(torch.bfloat16) for _ in range(rot)]
+    xchg = cd.KvSplitExchange(attn, NH, L)
+    out = torch.empty(NH, L, dtype=torch.bfloat16, device=dev)
+    i = 0
+    for _ in range(5):
+        xchg.decode(q, caches[i % rot], rows, R, SCALE, out=out)
+        i += 1
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    n = 200
+    l0 = attn.ctx.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(n):
+        xchg.decode(q, caches[i % rot], rows, R, SCALE, out=out)
+        i += 1
+    e1.record(stream)
+    e1.synchronize()
+    launches = (attn.ctx.launches - l0) // n
+    ms = _max_over_ranks(torch, dist, world, dev, e0.elapsed_time(e1) / n)
+    # the decode part alone, for the split of a step into streaming and exchange + merge
+    attn.ctx.profile(True)
+    for _ in range(20):
+        xchg.decode(q, caches[i % rot], rows, R, SCALE, out=out)
+        i += 1
+    k_ms, k_n = attn.ctx.profile_read()
+    attn.ctx.profile(False)
+    k_ms = _max_over_ranks(torch, dist, world, dev, k_ms / max(1, k_n))
+    xchg.close()
+    by = algorithmic_bytes(1, T)
+    rec = NH * (L + 2) * 4
+    return {"n_gpus": world, "cached_tokens": T, "rows_per_gpu": rows, "scaling": "strong", "us_per_step": ms * 1e3,
+            "tokens_per_s": 1e3 / ms, "kv_hbm_gbs_total": by / (ms / 1e3) / 1e9,
+            "per_gpu": {"decode_kernel_us": k_ms * 1e3, "exchange_and_merge_us": (ms - k_ms) * 1e3,
+                        "kernel_frac_of_measured_peak": (by / world) / (k_ms / 1e3) / 1e9 / peak,
+                        "streaming_floor_us": (by / world) / peak / 1e3, "launches_per_step": int(launches)},
+            "exchange": "peer-memory stores of %d-byte records + epoch flags, no collective call" % rec,
+            "l2": "rotation of %d local caches" % rot}
+
+
 def side_measure(attn, dev, stream, B, T, peak):
     """Config 5a on one GPU: the batched call whose cache (2.4 GB) dwarfs L2."""
     import torch
@@ -525,17 +646,59 @@ def side_gqa_decode(attn, dev, stream, peak):
             "algorithmic_bytes": by}
 
 
+def side_gqa_batched_and_prefill(attn, dev, stream, peak):
+    """Two measurements the single-query config 1 cannot give: (i) the decode kernel with work to do -- 64 sequences x
+    4096 cached tokens in one call (1.07 GB of K and V), HBM fraction of the kernel; (ii) the shape the reference's
+    attnbench tool times (tools/attnbench.c:38-42): a 512-query prefill tile, 16 heads, 4 KV heads, head dim 256,
+    against 11,000 cached keys, reported as multiply-accumulates per second of the QK^T and the AV products together
+    (the reference quotes 818 / 537 GMAC/s for the two passes on one M3 Max core complex, docs/DECISIONS.md:3115-3116)."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(16)
+    nh, nkv, hd = 16, 4, 256
+    out = {}
+    B, T = 64, 4096
+    K = torch.randn(B, T, nkv, hd, device=dev, generator=g).to(torch.bfloat16)
+    V = torch.randn(B, T, nkv, hd, device=dev, generator=g).to(torch.bfloat16)
+    q = torch.randn(B, nh, hd, device=dev, generator=g).to(torch.bfloat16)
+    lens = torch.full((B,), T, dtype=torch.int32, device=dev)
+
+    def dec():
+        attn.gqa_decode(q, K, V, lens, max_kv_len=T)
+    ms, k_ms, _ = _time_calls(attn, stream, dec, n=20)
+    by = B * (2 * T * nkv * hd * 2 + 2 * nh * hd * 2)
+    out["decode_64x4096"] = {"ms_per_call": ms, "kernel_ms": k_ms, "tokens_per_s": B / (ms / 1e3), "kernel_gbs": by / (k_ms / 1e3) / 1e9,
+                             "kernel_frac_of_measured_peak": by / (k_ms / 1e3) / 1e9 / peak,
+                             "call_frac_of_measured_peak": by / (ms / 1e3) / 1e9 / peak, "algorithmic_bytes": by}
+    del K, V
+    torch.cuda.empty_cache()
+    keys, nq = 11000, 512
+    pos = keys - nq
+    Kp = torch.randn(keys, nkv, hd, device=dev, generator=g).to(torch.bfloat16)
+    Vp = torch.randn(keys, nkv, hd, device=dev, generator=g).to(torch.bfloat16)
+    Q = torch.randn(nq, nh, hd, device=dev, generator=g).to(torch.bfloat16)
+
+    def pre():
+        attn.gqa_prefill(Q, Kp, Vp, pos)
+    ms, k_ms, _ = _time_calls(attn, stream, pre, n=10)
+    pairs = sum(pos + i + 1 for i in range(nq))                   # causal: query i sees pos + i + 1 keys
+    macs = 2.0 * pairs * nh * hd                                  # QK^T and AV, one multiply-accumulate per (pair, head, dim) each
+    out["attnbench_tile_512q_11000keys"] = {"ms_per_call": ms, "kernel_ms": k_ms, "gmac_per_s_qk_plus_av": macs / (k_ms / 1e3) / 1e9,
+                                            "tflops": 2.0 * macs / (k_ms / 1e3) / 1e12,
+                                            "reference_gmac_per_s": {"qk": 818, "av": 537, "hardware": "Apple M3 Max, cblas_sgemm",
+                                                                     "source": "docs/DECISIONS.md:3115-3116"}}
+    return out
+
+
 def side_prefill(attn, dev, stream, peak):
     """Config 3: MLA causal prefill of 4096 tokens, hidden 4096, FP8 block-scaled q_a/q_b/kv_a."""
     import torch
     g = torch.Generator(device=dev).manual_seed(12)
     n, H, q_lora, nh, nope, rope, lat = 4096, 4096, 1536, 64, 128, 64, 512
 
-    def fp8w(rows, cols):
-        w = torch.randint(0, 255, (rows, cols), device=dev, generator=g, dtype=torch.int32).to(torch.uint8)
-        w = torch.where((w & 0x7F) == 0x7F, torch.zeros_like(w), w)          # no NaN codes
-        sc = torch.full(((rows + 127) // 128, cols // 128), 1e-4, device=dev, dtype=torch.float32)
-        return w, sc
+    from cwick_b200 import synth
+
+    def fp8w(rows, cols):                     # the configuration's own weights: N(0, 0.02) quantised per 128 x 128 block
+        return synth.fp8_block128_weights(rows, cols, 0.02, g, dev)
     Wqa, Sqa = fp8w(q_lora, H)
     Wqb, Sqb = fp8w(nh * (nope + rope), q_lora)
     Wkva, Skva = fp8w(lat + rope, H)
@@ -681,10 +844,9 @@ def side_dsa(attn, dev, stream, peak):
     import torch
     g = torch.Generator(device=dev).manual_seed(13)
     B, T, ih, hd, want = 8, 65536, 64, 128, 2048
-    keys = torch.randint(0, 255, (B, T, hd), device=dev, generator=g, dtype=torch.int32).to(torch.uint8)
-    keys = torch.where((keys & 0x7F) == 0x7F, torch.zeros_like(keys), keys)
-    ks = torch.full((B, T), 0.01, device=dev, dtype=torch.float32)
-    q = torch.randn(B, ih, hd, device=dev, generator=g)
+    from cwick_b200 import synth
+    keys, ks = synth.fp8_token_keys(B, T, hd, g, dev)        # the configuration's own keys: N(0,1), one F32 scale per token
+    q = torch.randn(B, ih, hd, device=dev, generator=g).to(torch.bfloat16).float()
     wt = torch.rand(B, ih, device=dev, generator=g) / math.sqrt(hd * ih)
     n = torch.full((B,), T, dtype=torch.int32, device=dev)
     mq = torch.randn(B, NH, DK, device=dev, generator=g).to(torch.bfloat16)
@@ -729,7 +891,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="c5b: how partial records travel")
-    ap.add_argument("--extra-only", default=None, choices=["c1", "c3", "c4", "c5a", "kda", "gdn_mm"],
+    ap.add_argument("--extra-only", default=None, choices=["c1", "gqa", "c3", "c4", "c5a", "kda", "gdn_mm"],
                     help="run one side measurement alone and print its JSON (for profiling that kernel)")
     ap.add_argument("--mla-path", type=int, default=-1, help="force an MLA decode kernel (cwk_ctx_force_mla_path codes)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline")
@@ -744,7 +906,7 @@ def main():
         torch.cuda.set_stream(stream)
         attn = Attn(0)
         peak, _ = peaks()
-        fn = {"c1": side_gqa_decode, "c3": side_prefill, "c4": side_dsa, "kda": side_kda, "gdn_mm": side_gdn_mm,
+        fn = {"c1": side_gqa_decode, "gqa": side_gqa_batched_and_prefill, "c3": side_prefill, "c4": side_dsa, "kda": side_kda, "gdn_mm": side_gdn_mm,
               "c5a": lambda a, d, s_, p_: side_measure(a, d, s_, 64, 32768, p_)}[args.extra_only]
         print(json.dumps({args.extra_only: fn(attn, dev, stream, peak)}))
     elif args.impl == "reference":

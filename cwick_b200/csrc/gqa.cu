@@ -34,6 +34,9 @@ static int gqa_prefill_launch(cwk_ctx *ctx, const FlashRowsParams &p, int nblock
     return CWK_OK;
 }
 
+int cwk_gqa_prefill_tc(cwk_ctx *ctx, const void *Q, const void *K, const void *V, int64_t pos, int n, int nh, int nkv, int hd,
+                       float scale, void *out, int *flags);
+
 extern "C" {
 
 // sel != NULL: the keys of sequence b are rows sel[b*sel_ld + 0 .. kv_len[b]) of its cache, in that order.
@@ -100,6 +103,15 @@ int cwk_gqa_prefill(cwk_ctx *ctx, const void *Q, const void *K, const void *V, i
     if (((uintptr_t)K | (uintptr_t)V | (uintptr_t)Q) % 16 != 0)
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "gqa_prefill: pointers must be 16-byte aligned");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    // head dim 256 on the tcgen05/TMA prefill kernel (queries as MMA rows, K/V tiles by TMA from the caches); forcing a
+    // general path on the context (cwk_ctx_force_mla_path 0 or 1) keeps the mma.sync kernel for A/B runs
+    if (hd == 256 && ctx->force_mla_path != 0 && ctx->force_mla_path != 1) {
+        const size_t flags_bytes = ((size_t)((n + 127) / 128) * nh + 3) * sizeof(int);
+        int s = cwk_reserve_work(ctx, flags_bytes);
+        if (s != CWK_OK) return s;
+        s = cwk_gqa_prefill_tc(ctx, Q, K, V, pos, n, nh, nkv, hd, scale, out, (int *)ctx->work);
+        if (s != CWK_ERR_UNSUPPORTED) return s;
+    }
     const int QT = 64 / group;
     FlashRowsParams p{};
     p.q = (const uint16_t *)Q; p.k = (const uint16_t *)K; p.v = (const uint16_t *)V;

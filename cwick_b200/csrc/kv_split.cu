@@ -212,6 +212,16 @@ int cwk_mla_decode_kv_split(cwk_ctx *ctx, const void *q, const void *cache, int6
     if (s != CWK_OK) return s;
     PeerWindows pw;
     for (int g = 0; g < MAX_WORLD; g++) pw.win[g] = (g < world) ? (float *)windows[g] : nullptr;
+    if (ns > 4) {
+        // Many split records (a long local range): fold them with the wide merge kernel first (a block per head and
+        // 128-column chunk, loads in flight 32 deep), so that the push kernel below, whose blocks walk the splits one
+        // after another, has a single record left to send.
+        float *folded = partial + (size_t)ns * window_rec_floats(nh, L);        // room behind the splits (reserved by the launch below)
+        lse_fold_launch(ctx->stream, partial, ns, nh, L, folded);
+        CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel<fold>");
+        partial = folded;
+        ns = 1;
+    }
     fold_push_kernel<<<nh, 128, 0, ctx->stream>>>(partial, ns, nh, L, pw, rank, world, epoch, (unsigned int *)ctx->ticket);
     CWK_LAUNCH_CHECK(ctx, "fold_push_kernel");
     wait_merge_kernel<<<nh, 128, 0, ctx->stream>>>((float *)windows[rank], nh, L, world, epoch, (uint16_t *)out, ctx->dev_err,

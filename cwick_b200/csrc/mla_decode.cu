@@ -155,7 +155,7 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     const bool direct = (ns == 1 && out && !partial_out && path != 0);
     const size_t rec = (size_t)nh * (L + 2) * sizeof(float);
     if (!direct) {
-        int s = cwk_reserve_scratch(ctx, rec * ns * B);
+        int s = cwk_reserve_scratch(ctx, rec * ((size_t)ns * B + (ctx->keep_splits ? 1 : 0)));      // keep_splits: room for one folded record behind them
         if (s != CWK_OK) return s;
     }
     float *partial = ctx->scratch;

@@ -40,19 +40,30 @@
 
 namespace {
 
-constexpr int PA_QT = 128, PA_KT = 64, PA_DQK = 192, PA_DV = 256, PA_L = 512, PA_ROW = 576;
-constexpr int PA_K_BYTES = PA_KT * PA_DQK * 2;        // 24576: three [64][64] blocks
+constexpr int PA_QT = 128, PA_KT = 64, PA_DV = 256, PA_L = 512, PA_ROW = 576;
 constexpr int PA_C_BYTES = PA_KT * PA_DV * 2;         // 32768: four [64][64] blocks
 constexpr int PA_P_BYTES = PA_QT * PA_KT * 2;         // 16384: one [128][64] block
-constexpr int PA_KST = 3, PA_CST = 3;
+constexpr int PA_KST = 3;
 constexpr int PA_OFF_K = 0;                            // (the query tile lives in tensor memory, not here)
-constexpr int PA_OFF_C = PA_OFF_K + PA_KST * PA_K_BYTES;
-constexpr int PA_OFF_P = PA_OFF_C + PA_CST * PA_C_BYTES;
-constexpr int PA_OFF_BAR = PA_OFF_P + 2 * PA_P_BYTES;  // 204800
-constexpr int PA_OFF_X = PA_OFF_BAR + 512;             // [2][128] f32 maxima, [2][128] f32 sums exchanged between the two softmax groups; 8 item numbers
-static_assert(PA_OFF_BAR == 204800, "shared-memory budget");
-constexpr int PA_SMEM = PA_OFF_X + 2048 + 64 + 1024;
-constexpr uint32_t PA_COL_O = 0, PA_COL_S = 256, PA_COL_Q = 384;   // S buffers at 256 and 320; Q: 96 columns of bf16 pairs
+// The kernel serves two shapes. MLA prefill: 192-wide expanded keys, the 512 value columns in two halves, three value
+// stages. GQA prefill (Qwen3.5 layers): 256-wide keys and values of one KV head, two value stages (the key tiles are
+// 32 KB instead of 24 KB). Shared-memory layout and the query tile's width in tensor memory follow from DQK and CST.
+template <int DQK_, int CST_>
+struct PaCfg {
+    static constexpr int DQK = DQK_, CST = CST_;
+    static constexpr int K_BYTES = PA_KT * DQK * 2;    // 24576 / 32768: DQK / 64 blocks of [64][64]
+    static constexpr int OFF_C = PA_OFF_K + PA_KST * K_BYTES;
+    static constexpr int OFF_P = OFF_C + CST * PA_C_BYTES;
+    static constexpr int OFF_BAR = OFF_P + 2 * PA_P_BYTES;
+    static constexpr int OFF_X = OFF_BAR + 512;        // [2][128] f32 maxima, [2][128] f32 sums exchanged between the two softmax groups; 8 item numbers
+    static constexpr int SMEM = OFF_X + 2048 + 64 + 1024;
+    static_assert(SMEM <= 232448, "shared-memory budget");
+    static_assert(384 + DQK / 2 <= 512, "tensor-memory budget");
+};
+using PaMla = PaCfg<192, 3>;
+using PaGqa = PaCfg<256, 2>;
+static_assert(PaMla::OFF_BAR == 204800, "shared-memory budget");
+constexpr uint32_t PA_COL_O = 0, PA_COL_S = 256, PA_COL_Q = 384;   // S buffers at 256 and 320; Q: DQK / 2 columns of bf16 pairs
 constexpr float PA_LAZY = 8.f;                         // exact form: rescale when a score outruns the reference by 2^8
 constexpr float PA_RANGE = 64.f;                       // fast form: flag the block when a score outruns it by 2^64
 constexpr int PA_SBUF = 2;                             // score buffers in tensor memory
@@ -60,9 +71,10 @@ enum { PB_QFULL = 0, PB_KFULL = 1, PB_KEMPTY = 4, PB_CFULL = 7, PB_CEMPTY = 10, 
        PB_ODONE = 21, PB_QEMPTY = 22, PB_OFREE = 23, PB_XM = 24, PB_XL = 25, PB_ITEM = 26, PB_COUNT = 34 };
 
 struct AttnParams {
-    const uint16_t *q;  // bf16 [n][nh][192], rope part rotated
-    uint16_t *out;      // bf16 [n][nh][512]
+    const uint16_t *q;  // bf16 [n][nh][DQK] (MLA: rope part rotated)
+    uint16_t *out;      // bf16 [n][nh][512] (MLA) / [n][nh][256] (GQA)
     int n, nh, T;       // T = pos0 + n cached rows
+    int group;          // GQA: query heads per KV head (MLA: unused)
     int64_t pos0;
     float scale_log2;
     int *flags;         // one word per item: fast form sets it, exact form runs only where it is set
@@ -81,7 +93,7 @@ __device__ __forceinline__ AttnItem attn_item(int w, const AttnParams &p, int nq
     const int qtile = nq - 1 - (w % nq), hh = w / nq;
     it.q0 = qtile * PA_QT;
     it.h = hh % p.nh;
-    it.half = hh / p.nh;
+    it.half = hh / p.nh;                                                   // GQA: the grid has one "half", always 0
     const int64_t last_q = p.pos0 + min(it.q0 + PA_QT - 1, p.n - 1);     // keys 0 .. pos0 + (last query of the item): tiles of 64
     it.nt = (int)(last_q / PA_KT) + 1;
     return it;
@@ -90,9 +102,11 @@ __device__ __forceinline__ AttnItem attn_item(int w, const AttnParams &p, int nq
 // Persistent: one block per SM takes items from a global counter until none is left. The first TMA operation of a
 // block waits several thousand cycles for its tensor map, tensor memory is allocated once, and the loads of the next
 // item run under the epilogue of this one.
-template <int NWG>      // softmax warp groups: 2 = fast form, 1 = exact form
+template <int NWG, class CFG, bool GQA>      // NWG softmax warp groups: 2 = fast form, 1 = exact form
 __global__ void __launch_bounds__(128 + 128 * NWG, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_c, const AttnParams p) {
+    constexpr int PA_DQK = CFG::DQK, PA_K_BYTES = CFG::K_BYTES, PA_CST = CFG::CST, PA_OFF_C = CFG::OFF_C, PA_OFF_P = CFG::OFF_P,
+                  PA_OFF_BAR = CFG::OFF_BAR, PA_OFF_X = CFG::OFF_X;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -106,7 +120,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (NWG == 1 && p.counter[2] == 0) return;                   // the repair pass: the fast form raised no flag
     const int nq = (p.n + PA_QT - 1) / PA_QT;
-    const int total = nq * p.nh * 2;
+    const int total = nq * p.nh * (GQA ? 1 : 2);
 
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
@@ -152,7 +166,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                     ok = mbar_wait(bar(PB_KEMPTY + ks), (uint32_t)((ku & 1) ^ 1), p.err, 1001);
                     if (!ok) break;
                     mbar_expect_tx(bar(PB_KFULL + ks), PA_K_BYTES);
-                    tma_load_3d(base + PA_OFF_K + ks * PA_K_BYTES, &tm_k, 0, it.h * p.T + i * PA_KT, 0, bar(PB_KFULL + ks));
+                    if (GQA) tma_load_3d(base + PA_OFF_K + ks * PA_K_BYTES, &tm_k, 0, i * PA_KT, (it.h / p.group) * (PA_DQK / 64), bar(PB_KFULL + ks));
+                    else tma_load_3d(base + PA_OFF_K + ks * PA_K_BYTES, &tm_k, 0, it.h * p.T + i * PA_KT, 0, bar(PB_KFULL + ks));
                 }
             }
             if (!ok)        // drain the copies still in flight before leaving
@@ -175,7 +190,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                     ok = mbar_wait(bar(PB_CEMPTY + cs), (uint32_t)((cu & 1) ^ 1), p.err, 1002);
                     if (!ok) break;
                     mbar_expect_tx(bar(PB_CFULL + cs), PA_C_BYTES);
-                    tma_load_3d(base + PA_OFF_C + cs * PA_C_BYTES, &tm_c, 0, i * PA_KT, it.half * 4, bar(PB_CFULL + cs));
+                    tma_load_3d(base + PA_OFF_C + cs * PA_C_BYTES, &tm_c, 0, i * PA_KT, (GQA ? it.h / p.group : it.half) * 4, bar(PB_CFULL + cs));
                 }
             }
             if (!ok)
@@ -208,7 +223,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                     tc_fence_after();
                     const uint64_t dK = smem_desc(base + PA_OFF_K + ks * PA_K_BYTES, 16, 1024);
 #pragma unroll
-                    for (int s = 0; s < 12; s++)
+                    for (int s = 0; s < PA_DQK / 16; s++)
                         umma_bf16_ts(tmem + PA_COL_S + sb * PA_KT, tmem + PA_COL_Q + s * 8,       // A: 16 bf16 of every row = 8 TMEM columns per step
                                      dK + (uint64_t)(((s >> 2) * (PA_KT * 128) + (s & 3) * 32) >> 4), ID_QK, s != 0);
                     umma_commit(bar(PB_KEMPTY + ks));
@@ -415,7 +430,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                     const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
                     const uint4 wv = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
                     if (t0w + rr < p.n)
-                        *reinterpret_cast<uint4 *>(p.out + ((int64_t)(t0w + rr) * p.nh + h) * PA_L + half * PA_DV + col + jj * 8) = wv;
+                        *reinterpret_cast<uint4 *>(p.out + ((int64_t)(t0w + rr) * p.nh + h) * (GQA ? PA_DV : PA_L) + half * PA_DV + col + jj * 8) = wv;
                 }
                 __syncwarp();
             }
@@ -533,7 +548,7 @@ kexp_tc_kernel(const __grid_constant__ CUtensorMap tm_lat, const __grid_constant
                 const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
                 if (t0w + rr < p.T) {
                     const uint4 w = *reinterpret_cast<const uint4 *>(p.cache + (int64_t)(t0w + rr) * PA_ROW + PA_L + jj * 8);
-                    *reinterpret_cast<uint4 *>(p.kx + ((int64_t)h * p.T + t0w + rr) * PA_DQK + KX_NOPE + jj * 8) = w;
+                    *reinterpret_cast<uint4 *>(p.kx + ((int64_t)h * p.T + t0w + rr) * PaMla::DQK + KX_NOPE + jj * 8) = w;
                 }
             }
             ok = mbar_wait(bar(KB_DFULL + db), (uint32_t)((ti >> 1) & 1), p.err, 1107);
@@ -562,7 +577,7 @@ kexp_tc_kernel(const __grid_constant__ CUtensorMap tm_lat, const __grid_constant
                     const int rr = r8 * 4 + (lane >> 3), jj = lane & 7;
                     const uint4 w = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((jj ^ (rr & 7)) << 4));
                     if (t0w + rr < p.T)
-                        *reinterpret_cast<uint4 *>(p.kx + ((int64_t)h * p.T + t0w + rr) * PA_DQK + c * 64 + jj * 8) = w;
+                        *reinterpret_cast<uint4 *>(p.kx + ((int64_t)h * p.T + t0w + rr) * PaMla::DQK + c * 64 + jj * 8) = w;
                 }
                 __syncwarp();
             }
@@ -615,15 +630,15 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
     CUtensorMap tm_lat, tm_w, tm_k, tm_c;
     if (!encode3(&tm_lat, cache, (uint64_t)T, PA_L / 64, PA_ROW * 2, KX_TOK, 2) ||                 // latent dims only: block index 8 (rope) stays out
         !encode3(&tm_w, Wuk, (uint64_t)nh * KX_NOPE, PA_L / 64, PA_L * 2, KX_NOPE, PA_L / 64) ||
-        !encode3(&tm_k, kx, (uint64_t)nh * T, 3, PA_DQK * 2, PA_KT, 3) ||            // rows past a head's last key belong to the next head: every such key is masked
+        !encode3(&tm_k, kx, (uint64_t)nh * T, 3, PaMla::DQK * 2, PA_KT, 3) ||            // rows past a head's last key belong to the next head: every such key is masked
 
         !encode3(&tm_c, cache, (uint64_t)T, PA_L / 64, PA_ROW * 2, PA_KT, 4))
         return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the prefill attention operands");
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
         CWK_CUDA(ctx, cudaFuncSetAttribute(kexp_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KX_SMEM));
-        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PA_SMEM));
-        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PA_SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<1, PaMla, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PaMla::SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<2, PaMla, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PaMla::SMEM));
         attr_set[ctx->device & 15] = true;
     }
     {
@@ -637,7 +652,7 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
     }
     {
         AttnParams ap;
-        ap.q = (const uint16_t *)Q; ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.T = T; ap.pos0 = pos0; ap.scale_log2 = scale * 1.4426950408889634f; ap.flags = flags;
+        ap.q = (const uint16_t *)Q; ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.T = T; ap.pos0 = pos0; ap.group = 1; ap.scale_log2 = scale * 1.4426950408889634f; ap.flags = flags;
         ap.err = ctx->dev_err;
         const int total = ((n + PA_QT - 1) / PA_QT) * nh * 2;
         ap.counter = flags + total;
@@ -649,12 +664,53 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
         const int grid = std::min(total, ctx->sm_count);
         if (!exact_only) {
             CwkKernelTimer timer(ctx);
-            prefill_attn_kernel<2><<<grid, 384, PA_SMEM, ctx->stream>>>(tm_k, tm_c, ap);
+            prefill_attn_kernel<2, PaMla, false><<<grid, 384, PaMla::SMEM, ctx->stream>>>(tm_k, tm_c, ap);
             CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<2>");
         }
         // the repair pass: items whose flag is clear are skipped
-        prefill_attn_kernel<1><<<grid, 256, PA_SMEM, ctx->stream>>>(tm_k, tm_c, ap);
+        prefill_attn_kernel<1, PaMla, false><<<grid, 256, PaMla::SMEM, ctx->stream>>>(tm_k, tm_c, ap);
         CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<1>");
     }
+    return CWK_OK;
+}
+
+// Causal GQA prefill on the same kernel (Qwen3.5 full-attention layers, src/q35_model.c:1713-1746): per query head,
+// 128 consecutive queries are the MMA's rows; keys and values are the 256-wide rows of the head's KV head, streamed in
+// 64-key tiles by TMA straight from the caches. Q bf16 [n][nh][256]; K, V bf16 [pos + n][nkv][256]; out bf16
+// [n][nh][256]; flags = workspace int32 [ceil(n / 128) * nh + 3]. Returns CWK_ERR_UNSUPPORTED (no error text) when the
+// tensor path cannot take the operands.
+int cwk_gqa_prefill_tc(cwk_ctx *ctx, const void *Q, const void *K, const void *V, int64_t pos, int n, int nh, int nkv, int hd,
+                       float scale, void *out, int *flags) {
+    if (!cwk_encode_tiled_fn() || hd != 256 || nkv <= 0 || nh % nkv) return CWK_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return CWK_ERR_UNSUPPORTED;
+    int s = cwk_ensure_err_word(ctx);
+    if (s != CWK_OK) return s;
+    const int T = (int)(pos + n);
+    CUtensorMap tm_k, tm_v;
+    // the caches as [64][rows][nkv * 4 column blocks]: a tile is one box of 64 keys x the 4 blocks of one KV head
+    if (!encode3(&tm_k, K, (uint64_t)T, (uint64_t)nkv * 4, (uint64_t)nkv * hd * 2, PA_KT, 4) ||
+        !encode3(&tm_v, V, (uint64_t)T, (uint64_t)nkv * 4, (uint64_t)nkv * hd * 2, PA_KT, 4))
+        return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GQA prefill operands");
+    static bool attr_set[16] = {false};
+    if (!attr_set[ctx->device & 15]) {
+        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<1, PaGqa, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PaGqa::SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<2, PaGqa, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PaGqa::SMEM));
+        attr_set[ctx->device & 15] = true;
+    }
+    AttnParams ap;
+    ap.q = (const uint16_t *)Q; ap.out = (uint16_t *)out; ap.n = n; ap.nh = nh; ap.T = T; ap.pos0 = pos; ap.group = nh / nkv;
+    ap.scale_log2 = scale * 1.4426950408889634f; ap.flags = flags; ap.err = ctx->dev_err;
+    const int total = ((n + PA_QT - 1) / PA_QT) * nh;
+    ap.counter = flags + total;
+    CWK_CUDA(ctx, cudaMemsetAsync(flags, 0, (size_t)(total + 3) * sizeof(int), ctx->stream));
+    const int grid = std::min(total, ctx->sm_count);
+    {
+        CwkKernelTimer timer(ctx);
+        prefill_attn_kernel<2, PaGqa, true><<<grid, 384, PaGqa::SMEM, ctx->stream>>>(tm_k, tm_v, ap);
+        CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<2, gqa>");
+    }
+    prefill_attn_kernel<1, PaGqa, true><<<grid, 256, PaGqa::SMEM, ctx->stream>>>(tm_k, tm_v, ap);      // repairs flagged items only
+    CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<1, gqa>");
     return CWK_OK;
 }

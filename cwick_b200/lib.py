@@ -55,6 +55,12 @@ SIGNATURES = {
     "cwk_cache_export_f32": (i32, [vp, vp, i64, i64, i32, vp]),
     "cwk_cache_import_f32": (i32, [vp, vp, i64, i32, vp, i64, i32]),
     "cwk_cache_copy_bf16": (i32, [vp, i32, vp, vp, i64, i64, i32]),
+    "cwk_ds_state_bytes": (C.c_size_t, [vp, i64]),
+    "cwk_ds_state_pack": (i32, [vp, vp, i64, vp, C.c_size_t]),
+    "cwk_ds_state_apply": (i32, [vp, vp, vp, C.c_size_t, C.POINTER(i64)]),
+    "cwk_q35_prefix_bytes": (C.c_size_t, [vp, i64]),
+    "cwk_q35_prefix_pack": (i32, [vp, vp, i64, vp, C.c_size_t]),
+    "cwk_q35_prefix_apply": (i32, [vp, vp, vp, C.c_size_t, i64, C.POINTER(i64)]),
     "cwk_gdn_scan": (i32, [vp, i32, i32, i32, i32, i32, i32] + [vp] * 7 + [f32, vp, vp]),
     "cwk_mm_index_scores": (i32, [vp, vp, i64, i32, vp, i32, vp]),
     "cwk_mm_select_blocks": (i32, [vp, vp, i64, i32, i32, i32, vp, vp, vp, vp]),

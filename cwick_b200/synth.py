@@ -58,3 +58,34 @@ def bf16_to_f32(b: np.ndarray) -> np.ndarray:
 def normal_bf16(seed: int, tid: int, shape, std: float = 1.0) -> np.ndarray:
     n = int(np.prod(shape))
     return f32_to_bf16(normal(seed, tid, n, std)).reshape(shape)
+
+
+# ---- the same distributions generated on the device, for benchmark-sized tensors (torch) ----------------------
+
+def fp8_block128_weights(rows, cols, std, gen, dev):
+    """N(0, std^2) weights quantised to E4M3 with one F32 multiplier per 128 x 128 block (scale = amax / 448, the
+    layout of the reference's FP8 tensors, src/tensor.c:495-532): (uint8 codes [rows][cols], f32 scales
+    [ceil(rows/128)][cols/128])."""
+    import torch
+    w = torch.randn(rows, cols, device=dev, generator=gen, dtype=torch.float32) * std
+    rb, cb = (rows + 127) // 128, cols // 128
+    pad = torch.zeros(rb * 128, cols, device=dev)
+    pad[:rows] = w
+    blk = pad.view(rb, 128, cb, 128)
+    sc = (blk.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-30)
+    q = (blk / sc[:, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    codes = q.view(torch.uint8).view(rb * 128, cols)[:rows].contiguous()
+    return codes, sc.contiguous()
+
+
+def fp8_token_keys(B, T, hd, gen, dev):
+    """N(0,1) index keys quantised to E4M3 with one F32 scale per token (amax / 448): (uint8 [B][T][hd], f32 [B][T])."""
+    import torch
+    codes = torch.empty(B, T, hd, device=dev, dtype=torch.uint8)
+    scales = torch.empty(B, T, device=dev, dtype=torch.float32)
+    for b in range(B):
+        k = torch.randn(T, hd, device=dev, generator=gen, dtype=torch.float32)
+        sc = (k.abs().amax(dim=1) / 448.0).clamp_min(1e-30)
+        codes[b] = (k / sc[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+        scales[b] = sc
+    return codes, scales

@@ -325,6 +325,37 @@ CWK_API int cwk_cache_import_f32(cwk_ctx *ctx, const float *in_host, int64_t row
                                  int rounding);
 CWK_API int cwk_cache_copy_bf16(cwk_ctx *ctx, int to_device, void *host, void *cache, int64_t ld, int64_t rows, int width);
 
+/* ---- Prefix snapshots of device-resident state, in the reference's blob layouts -------
+ * The server's prefix cache stores a backend's cross-token state as one opaque blob (src/pfx.h:44-52). These
+ * write and read, for state that lives on the GPU, the same bytes as the reference's ds_state_pack / _apply
+ * (src/ds_model.c:2008-2105; header ds_snap_hdr :1974-1977) and q35_prefix_pack / _apply
+ * (src/q35_model.c:591-665), so a snapshot taken by one side restores on the other. All array members are DEVICE
+ * pointers except tok_cache; buf is host memory. apply answers CWK_ERR_NOT_FOUND for a snapshot of another
+ * geometry (a cache miss to the caller, src/ds_model.c:2061-2068). */
+typedef struct cwk_ds_state {
+    int n_layers, window, head_dim, n_src, idx_head_dim, max_ratio, max_seq_len;
+    float *win_kv;        /* [n_layers][window][head_dim] */
+    float *cmp_kv;        /* [n_src][max_seq_len][head_dim] */
+    float *cmp_state;     /* [n_src][max_ratio][head_dim] */
+    float *cmp_score;     /* [n_src][max_ratio][head_dim] */
+    float *idx_k;         /* [n_src][max_seq_len][idx_head_dim] */
+    int64_t *tok_cache;   /* HOST [max_seq_len] token ids of the engram hash; may be NULL (zeros are written) */
+} cwk_ds_state;
+CWK_API size_t cwk_ds_state_bytes(const cwk_ds_state *st, int64_t pos);
+CWK_API int cwk_ds_state_pack(cwk_ctx *ctx, const cwk_ds_state *st, int64_t pos, void *buf, size_t cap);
+CWK_API int cwk_ds_state_apply(cwk_ctx *ctx, cwk_ds_state *st, const void *buf, size_t len, int64_t *pos_out);
+typedef struct cwk_q35_state {
+    int n_layers, max_seq_len;
+    const uint8_t *is_linear;   /* HOST [n_layers]: 1 = Gated DeltaNet layer, 0 = full-attention layer */
+    size_t conv_bytes, ssm_bytes; /* per recurrent layer: (taps-1) x qkv floats; v_heads x k_dim x v_dim floats */
+    void **conv_state, **ssm_state; /* HOST arrays [n_layers] of device pointers (NULL for attention layers) */
+    int64_t kv_row, kv_ld;      /* values per cached row (n_kv_heads x head_dim) and the caches' row stride */
+    void **kcache, **vcache;    /* HOST arrays [n_layers] of device bf16 caches (NULL for recurrent layers) */
+} cwk_q35_state;
+CWK_API size_t cwk_q35_prefix_bytes(const cwk_q35_state *st, int64_t pos);
+CWK_API int cwk_q35_prefix_pack(cwk_ctx *ctx, const cwk_q35_state *st, int64_t pos, void *buf, size_t cap);
+CWK_API int cwk_q35_prefix_apply(cwk_ctx *ctx, cwk_q35_state *st, const void *buf, size_t len, int64_t want, int64_t *pos_out);
+
 /* ---- KDA (gated delta-rule linear attention) decode step ---------------------------
  * Everything of cwick_attention_kda_decode between its projections and o_proj (src/attention.c:1243-1417), for
  * B engine slots in one launch: short convolution + SiLU over the 3-deep window of projected values, per-head

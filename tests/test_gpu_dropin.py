@@ -161,3 +161,43 @@ def test_unsupported_requests_are_refused_not_computed(golden):
        C.byref(ts[5]), C.byref(ts[6]), cache.ctypes.data, None, 4, 0, 0, None, None, x.ctypes.data, out.ctypes.data,
        C.byref(err))
     assert err.status == cl.ERR_UNSUPPORTED and np.all(out == 7.0)
+
+
+def test_prefix_restored_into_the_same_array_at_the_same_length(golden):
+    """The caller swaps the rows of its array for another prefix of the SAME length and goes on at the position the
+    device copy expects next: the copy must be noticed as out of date (the caller's last row is no longer the one
+    written through it) and re-read, or the next token would attend to the old sequence."""
+    os.environ["CWICK_LATENT_BF16"] = "1"
+    L = cl.load()
+    dims = [int(v) for v in golden["lat_dims"][:6]]
+    H, nh, nope, vdim, q_lora, kv_lora = dims
+    W = {k: np.ascontiguousarray(golden["lat_" + k]) for k in ("qa", "qb", "kva", "kvb", "o", "qa_n", "kva_n")}
+    spec = make_spec(H, nh, nope, vdim, q_lora, kv_lora, 1e-6)
+    ts = [tensor(W["qa"], q_lora, H), tensor(W["qb"], nh * nope, q_lora), tensor(W["kva"], kv_lora, H),
+          tensor(W["kvb"], nh * (nope + vdim), kv_lora), tensor(W["o"], H, nh * vdim), tensor(W["qa_n"], 1, q_lora),
+          tensor(W["kva_n"], 1, kv_lora)]
+    fn = L.cwick_attention_mla_decode
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 9 + [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_void_p, C.c_void_p]
+    cap, n = 16, 10
+    xs_a = synth.normal(77, 1, (n + 1) * H).reshape(n + 1, H)
+    xs_b = synth.normal(77, 2, (n + 1) * H).reshape(n + 1, H)
+
+    def step(cache, p, x):
+        out, err = np.zeros(H, np.float32), Err()
+        x = np.ascontiguousarray(x)
+        fn(C.addressof(spec), C.byref(ts[0]), C.byref(ts[1]), C.byref(ts[2]), C.byref(ts[3]), None, C.byref(ts[4]), C.byref(ts[5]),
+           C.byref(ts[6]), cache.ctypes.data, None, cap, p, 0, None, None, x.ctypes.data, out.ctypes.data, C.byref(err))
+        assert err.status == 0, err.message
+        return out
+    cache_a, cache_b = np.zeros((cap, kv_lora), np.uint16), np.zeros((cap, kv_lora), np.uint16)
+    for p in range(n):
+        step(cache_a, p, xs_a[p])
+    for p in range(n):
+        step(cache_b, p, xs_b[p])
+    want = step(cache_b, n, xs_b[n])                  # sequence B continued in its own array
+    cache_a[:n] = cache_b[:n]                         # ... and restored over sequence A's rows, same length
+    got = step(cache_a, n, xs_b[n])
+    assert np.array_equal(got, want)
+    L.cwk_dropin_reset()

@@ -53,18 +53,51 @@ def test_decode_ragged_batch_and_splits(attn):
             close(got[b], oracle_decode(q[b], K[b], V[b], int(lens[b]), nh, nkv, hd))
 
 
-@pytest.mark.parametrize("n,pos", [(200, 37), (64, 0), (17, 300)])
-def test_prefill_causal(attn, n, pos):
-    nh, nkv, hd = 16, 4, 256
+def oracle_prefill(Q, K, V, pos, n, nh, nkv, hd):
     o = orc.oracle()
-    Q = synth.normal_bf16(40 + n, 1, (n, nh, hd))
-    K = np.ascontiguousarray(synth.normal_bf16(40 + n, 2, (pos + n, nkv, hd)))
-    V = np.ascontiguousarray(synth.normal_bf16(40 + n, 3, (pos + n, nkv, hd)))
-    got = attn.gqa_prefill(to_bf16_cuda(Q), to_bf16_cuda(K), to_bf16_cuda(V), pos)
     Qf = np.ascontiguousarray(synth.bf16_to_f32(Q))
     want = np.empty((n, nh, hd), np.float32)
     o.orc_gqa_prefill(P(Qf, f32p), P(K, u16p), P(V, u16p), pos, n, nh, nkv, hd, 1.0 / np.sqrt(hd), P(want, f32p))
-    close(bf16_to_np(got), want)
+    return want
+
+
+@pytest.mark.parametrize("path", [-1, 1])          # -1: the tcgen05/TMA kernel (head dim 256); 1: the mma.sync kernel
+@pytest.mark.parametrize("n,pos", [(200, 37), (64, 0), (17, 300), (300, 1)])
+def test_prefill_causal(attn, n, pos, path):
+    nh, nkv, hd = 16, 4, 256
+    Q = synth.normal_bf16(40 + n, 1, (n, nh, hd))
+    K = np.ascontiguousarray(synth.normal_bf16(40 + n, 2, (pos + n, nkv, hd)))
+    V = np.ascontiguousarray(synth.normal_bf16(40 + n, 3, (pos + n, nkv, hd)))
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, path)
+    try:
+        got = attn.gqa_prefill(to_bf16_cuda(Q), to_bf16_cuda(K), to_bf16_cuda(V), pos)
+        attn.ctx.sync()
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
+    close(bf16_to_np(got), oracle_prefill(Q, K, V, pos, n, nh, nkv, hd))
+
+
+def test_prefill_other_groupings_and_rising_scores(attn):
+    """8 query heads on 8 KV heads and 8 on 1; and keys whose scores climb along the prompt by far more than the
+    range the fast form of the tensor-core kernel covers, so that its exact form has to redo those blocks."""
+    hd, n, pos = 256, 150, 20
+    for nh, nkv in ((8, 8), (8, 1)):
+        Q = synth.normal_bf16(51, 1, (n, nh, hd))
+        K = np.ascontiguousarray(synth.normal_bf16(51, 2, (pos + n, nkv, hd)))
+        V = np.ascontiguousarray(synth.normal_bf16(51, 3, (pos + n, nkv, hd)))
+        got = attn.gqa_prefill(to_bf16_cuda(Q), to_bf16_cuda(K), to_bf16_cuda(V), pos)
+        attn.ctx.sync()
+        close(bf16_to_np(got), oracle_prefill(Q, K, V, pos, n, nh, nkv, hd))
+    nh, nkv, n, pos = 4, 1, 256, 0
+    Q = synth.normal_bf16(52, 1, (n, nh, hd))
+    Kf = synth.normal(52, 2, (pos + n) * nkv * hd).reshape(pos + n, nkv, hd)
+    qdir = np.sign(synth.bf16_to_f32(Q)[n - 1, 0] + 1e-6)                     # every key leans towards one query's direction,
+    ramp = np.linspace(0.0, 6.0, pos + n, dtype=np.float32)[:, None, None]    # later keys harder: scores rise by ~90 (log2) over the prompt
+    K = np.ascontiguousarray(synth.f32_to_bf16(Kf * 0.2 + ramp * qdir[None, None, :]).reshape(pos + n, nkv, hd))
+    V = np.ascontiguousarray(synth.normal_bf16(52, 3, (pos + n, nkv, hd)))
+    got = attn.gqa_prefill(to_bf16_cuda(Q), to_bf16_cuda(K), to_bf16_cuda(V), pos)
+    attn.ctx.sync()
+    close(bf16_to_np(got), oracle_prefill(Q, K, V, pos, n, nh, nkv, hd))
 
 
 def test_prefill_last_row_equals_decode(attn):
