@@ -127,3 +127,19 @@ void refdrv_ds_freqs(int rope_dim, double base, double factor, int original, int
     ds_freqs_init(&f, rope_dim, base, factor, original, beta_fast, beta_slow);
     memcpy(freq_out, f.freq, (size_t)f.npairs * sizeof(float));
 }
+
+/* ds_state_pack (src/ds_model.c:2008-2054) on a model assembled from caller arrays. Returns the blob size, or -1. */
+long refdrv_ds_state_pack(int n_layers, int window, int head_dim, int n_src, int idx_head_dim, int max_ratio, int max_seq,
+                          float *win_kv, float *cmp_kv, float *cmp_state, float *cmp_score, float *idx_k, int64_t *tok_cache,
+                          int64_t pos, void *buf, size_t cap) {
+    ds_model *m = calloc(1, sizeof(*m));
+    ds_config *c = &m->cfg;
+    c->n_layers = n_layers; c->window_size = window; c->head_dim = head_dim; c->n_kv_source = n_src;
+    c->index_head_dim = idx_head_dim; c->max_ratio = max_ratio; c->max_seq_len = max_seq;
+    m->win_kv = win_kv; m->cmp_kv = cmp_kv; m->cmp_state = cmp_state; m->cmp_score = cmp_score; m->idx_k = idx_k;
+    m->tok_cache = tok_cache;
+    long n = (long)ds_state_bytes(m, pos);
+    if ((size_t)n > cap || ds_state_pack(m, pos, buf, cap) != 0) n = -1;
+    free(m);
+    return n;
+}

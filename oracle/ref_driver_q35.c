@@ -115,3 +115,21 @@ void refdrv_q35_gdn(int n, int nh, int head_k, int head_v, const float *up, cons
     lin_rec_heads(&a, 0, nh);
     free(L); free(m);
 }
+
+/* q35_prefix_pack (src/q35_model.c:591-624) on a model assembled from caller arrays: layers alternate by is_linear;
+ * conv/ssm/k/v are HOST arrays [n_layers] of f32 buffers (NULL where a layer has none). Returns the blob size, or -1. */
+long refdrv_q35_prefix_pack(int n_layers, const uint8_t *is_linear, int max_seq, int n_kv_heads, int head_dim, int lin_k_heads,
+                            int lin_v_heads, int lin_k_dim, int lin_v_dim, int conv_kernel, float **conv, float **ssm, float **kc,
+                            float **vc, int64_t pos, void *buf, size_t cap) {
+    q35_model *m = calloc(1, sizeof(*m));
+    q35_config *c = &m->cfg;
+    c->n_layers = n_layers; c->max_seq_len = max_seq; c->n_kv_heads = n_kv_heads; c->head_dim = head_dim;
+    c->lin_k_heads = lin_k_heads; c->lin_v_heads = lin_v_heads; c->lin_k_dim = lin_k_dim; c->lin_v_dim = lin_v_dim;
+    c->conv_kernel = conv_kernel; c->is_linear = (uint8_t *)is_linear;
+    for (int l = 0; l < n_layers; l++) { if (is_linear[l]) c->n_lin_layers++; else c->n_full_layers++; }
+    m->conv_state = conv; m->ssm_state = ssm; m->kcache = kc; m->vcache = vc;
+    long n = (long)q35_prefix_bytes(m, pos);
+    if ((size_t)n > cap || q35_prefix_pack(m, pos, buf, cap) != 0) n = -1;
+    free(m);
+    return n;
+}

@@ -41,6 +41,8 @@ def main():
         for k2, v in out.items():
             G["ds_layer_%s_%s" % (name, k2)] = v
     G["qdq_fp8"] = sc.run_qdq_fp8(r, ref=True)
+    G["snap_ds"] = sc.run_ds_pack_ref(r)                # the blobs of ds_state_pack and q35_prefix_pack
+    G["snap_q35"] = sc.run_q35_pack_ref(r)
     path = os.path.join(HERE, "statics_vectors.npz")
     np.savez_compressed(path, **G)
     print("wrote", path, "%.1f KB" % (os.path.getsize(path) / 1024), "with", len(G), "arrays")

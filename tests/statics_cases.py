@@ -291,3 +291,63 @@ def run_ds_layer(lib, name, ref):
         out["topk"][p, min(nvis, topk):] = -7
     out["n_cmp"] = n_cmp
     return out
+
+
+# ---------------------------------------------------------------- prefix snapshots (ds_state_pack, q35_prefix_pack)
+DS_SNAP = dict(n_layers=3, window=4, head_dim=32, n_src=2, idx_head_dim=16, max_ratio=2, max_seq=16, pos=9)
+Q35_SNAP = dict(is_linear=[1, 0, 1, 1, 0], max_seq=12, n_kv_heads=2, head_dim=16, lin_k_heads=2, lin_v_heads=4, lin_k_dim=8,
+                lin_v_dim=8, conv_kernel=4, pos=7)
+
+
+def ds_snapshot_arrays():
+    c = DS_SNAP
+    a = dict(win_kv=synth.normal(SEED, 3301, c["n_layers"] * c["window"] * c["head_dim"]),
+             cmp_kv=synth.normal(SEED, 3302, c["n_src"] * c["max_seq"] * c["head_dim"]),
+             cmp_state=synth.normal(SEED, 3303, c["n_src"] * c["max_ratio"] * c["head_dim"]),
+             cmp_score=synth.normal(SEED, 3304, c["n_src"] * c["max_ratio"] * c["head_dim"]),
+             idx_k=synth.normal(SEED, 3305, c["n_src"] * c["max_seq"] * c["idx_head_dim"]),
+             tok=(np.arange(c["max_seq"], dtype=np.int64) * 7919 + 13))
+    return a
+
+
+def run_ds_pack_ref(r):
+    c, a = DS_SNAP, ds_snapshot_arrays()
+    buf = np.zeros(1 << 16, np.uint8)
+    r.refdrv_ds_state_pack.restype = C.c_long
+    r.refdrv_ds_state_pack.argtypes = [C.c_int] * 7 + [f32p] * 5 + [orc.i64p, C.c_int64, C.c_void_p, C.c_size_t]
+    n = r.refdrv_ds_state_pack(c["n_layers"], c["window"], c["head_dim"], c["n_src"], c["idx_head_dim"], c["max_ratio"], c["max_seq"],
+                               P(a["win_kv"], f32p), P(a["cmp_kv"], f32p), P(a["cmp_state"], f32p), P(a["cmp_score"], f32p),
+                               P(a["idx_k"], f32p), P(a["tok"], orc.i64p), c["pos"], buf.ctypes.data, buf.size)
+    assert n > 0
+    return buf[:n].copy()
+
+
+def q35_snapshot_arrays():
+    c = Q35_SNAP
+    qkv = 2 * c["lin_k_heads"] * c["lin_k_dim"] + c["lin_v_heads"] * c["lin_v_dim"]
+    conv_n, ssm_n = (c["conv_kernel"] - 1) * qkv, c["lin_v_heads"] * c["lin_k_dim"] * c["lin_v_dim"]
+    row = c["n_kv_heads"] * c["head_dim"]
+    L = []
+    for l, lin in enumerate(c["is_linear"]):
+        if lin:
+            L.append(dict(conv=synth.normal(SEED, 3310 + l, conv_n), ssm=synth.normal(SEED, 3320 + l, ssm_n)))
+        else:
+            L.append(dict(k=synth.normal(SEED, 3330 + l, c["max_seq"] * row), v=synth.normal(SEED, 3340 + l, c["max_seq"] * row)))
+    return L, conv_n, ssm_n, row
+
+
+def run_q35_pack_ref(r):
+    c = Q35_SNAP
+    L, conv_n, ssm_n, row = q35_snapshot_arrays()
+    n_layers = len(L)
+    fpp = C.POINTER(C.c_float)
+    arr = lambda key: (fpp * n_layers)(*[(P(d[key], f32p) if key in d else None) for d in L])       # noqa: E731
+    lin = np.array(c["is_linear"], np.uint8)
+    buf = np.zeros(1 << 16, np.uint8)
+    r.refdrv_q35_prefix_pack.restype = C.c_long
+    r.refdrv_q35_prefix_pack.argtypes = [C.c_int, u8p] + [C.c_int] * 8 + [C.POINTER(fpp)] * 4 + [C.c_int64, C.c_void_p, C.c_size_t]
+    n = r.refdrv_q35_prefix_pack(n_layers, P(lin, u8p), c["max_seq"], c["n_kv_heads"], c["head_dim"], c["lin_k_heads"], c["lin_v_heads"],
+                                 c["lin_k_dim"], c["lin_v_dim"], c["conv_kernel"], arr("conv"), arr("ssm"), arr("k"), arr("v"), c["pos"],
+                                 buf.ctypes.data, buf.size)
+    assert n > 0
+    return buf[:n].copy()
