@@ -52,7 +52,14 @@ typedef struct cwk_ctx cwk_ctx;
 /* ---- context -------------------------------------------------------------
  * One context per engine slot (the reference runs one request thread per slot,
  * src/engine.c:78-88): it owns a stream, the split-KV scratch and the last
- * error text. Not thread-safe; use one per thread. */
+ * error text. Not thread-safe; use one per thread.
+ * The context's buffers (split records, prefill workspace, staging) grow on
+ * demand: a call that needs more room synchronises the stream, frees the old
+ * buffer and allocates a larger one. Addresses captured into a CUDA graph are
+ * therefore only valid until a LARGER call runs on the same context: warm the
+ * context up with the largest shape before capturing, and do not grow it while
+ * a captured graph is still being replayed (nor during capture, which an
+ * allocation would break). */
 CWK_API int cwk_ctx_create(int device, cwk_ctx **out);
 CWK_API void cwk_ctx_destroy(cwk_ctx *ctx);
 /* Run on a caller-owned cudaStream_t instead of the context's own. */
@@ -144,7 +151,11 @@ CWK_API int cwk_mla_decode_host(cwk_ctx *ctx, const void *q_host, const void *ca
  *     (nothing is launched); fewer splits per sequence are used when B is large.
  *   - It calls no cudaMalloc, cudaFree or allocating library routine, on any call.
  *   - The FIRST call on each device also resolves the array's device address and
- *     sets one kernel attribute; make that first call before any stream capture.
+ *     sets one kernel attribute; make that first call before any stream capture,
+ *     and at start-up: loading the library's code on a device (which the first
+ *     call of any entry point triggers) is itself a driver allocation that
+ *     includes the 16 MiB array, so it must happen before the host's own arena
+ *     takes what is left of the device.
  *   - All calls on a device share the one array and it keeps the last call's
  *     contents: two calls that overlap on the GPU (different streams, no ordering)
  *     race on it. Calls on one stream are ordered and safe.
@@ -427,7 +438,7 @@ CWK_API int cwk_ds_rmsnorm_bf16w(cwk_ctx *ctx, const float *x, const void *w, in
  * `block`), mode 2: nothing more (the query heads of ds_attention, src/ds_model.c:1188-1193), mode 3:
  * ds_qdq_fp8_e8m0 (src/ds_ops.c:235-252: E4M3 with a power-of-two scale per 32, the window KV row). n must be a
  * multiple of the scale block. The e2m1 rounding is the reference's as written
- * (src/ds_ops.c:212-226: magnitudes 0, 1, 2, 4, 6). Subnormal inputs (below 2^-126) count as zero. */
+ * (src/ds_ops.c:212-226: magnitudes 0, 1, 2, 4, 6). */
 CWK_API int cwk_ds_rope_round_qdq(cwk_ctx *ctx, float *x, int rows, int n, const float *freq, int npairs, int64_t pos,
                                   int mode, int block);
 /* The window KV row of ds_attention (src/ds_model.c:1201-1212) after its projection and norm (cwk_ds_lin_q,

@@ -51,6 +51,17 @@ def test_two_calls_in_a_row_match_the_regular_entry_point():
         want = attn.mla_decode(q, cache, lens, max_kv_len=T, scale=SCALE)
         torch.cuda.synchronize()
         close(bf16_to_np(got), bf16_to_np(want))
+        # a call in steady state (not the first on the device) takes nothing from the driver's allocator
+        out2 = torch.empty_like(got)
+        torch.cuda.synchronize()
+        free0 = torch.cuda.mem_get_info()[0]
+        err = C.create_string_buffer(512)
+        st = attn.lib.cwk_mla_decode_noalloc(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.c_void_p(q.data_ptr()),
+                                             C.c_void_p(cache.data_ptr()), cache.shape[1] * cache.shape[2], cache.shape[2],
+                                             C.c_void_p(lens.data_ptr()), T, B, NH, SCALE, C.c_void_p(out2.data_ptr()), err, 512)
+        torch.cuda.synchronize()
+        assert st == 0 and torch.cuda.mem_get_info()[0] == free0
+        assert torch.equal(out2, got)
 
 
 def test_request_beyond_the_fixed_scratch_is_refused():
