@@ -24,6 +24,9 @@ struct cwk_ctx {
     // FP8 weights widened to bf16 for the tensor-core projection
     void *wbf16 = nullptr;
     size_t wbf16_bytes = 0;
+    // ... and the widened copies kept across calls (fp8_linear_tc.cu), with their byte budget
+    void *wide_cache = nullptr;
+    size_t wide_cache_budget = 0;             // off until the caller says its weights are immutable (cwk_ctx_weight_cache)
     // staging for the *_host entry points
     void *stage_dev = nullptr;
     size_t stage_dev_bytes = 0;
@@ -64,6 +67,7 @@ int cwk_check_device_error(cwk_ctx *ctx);
 int cwk_ensure_err_word(cwk_ctx *ctx);
 // persistent MLA decode kernel (mla_decode_sk.cu): release its buffers; zero them after a failed step
 void cwk_sk_free(cwk_ctx *ctx);
+void cwk_fp8_weight_cache_free(cwk_ctx *ctx);
 void cwk_sk_reset(cwk_ctx *ctx);
 
 // Brackets a main-kernel launch with events when profiling is on.

@@ -123,6 +123,7 @@ void cwk_ctx_destroy(cwk_ctx *ctx) {
     if (ctx->dev_err) cudaFreeHost(ctx->dev_err);
     if (ctx->ticket) cudaFree(ctx->ticket);
     cwk_sk_free(ctx);
+    cwk_fp8_weight_cache_free(ctx);
     for (cudaEvent_t e : ctx->ev) cudaEventDestroy(e);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -181,6 +182,14 @@ int cwk_ctx_debug_trace(cwk_ctx *ctx, void *device_buffer) {
     return CWK_OK;
 }
 #endif
+
+int cwk_ctx_weight_cache(cwk_ctx *ctx, size_t budget_bytes) {
+    if (!ctx) return CWK_ERR_ARGUMENT;
+    CWK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    cwk_fp8_weight_cache_free(ctx);
+    ctx->wide_cache_budget = budget_bytes;
+    return CWK_OK;
+}
 
 int cwk_ctx_set_wait_limit(cwk_ctx *ctx, unsigned int polls) {
     if (!ctx || polls == 0) return CWK_ERR_ARGUMENT;

@@ -18,6 +18,9 @@
 // shared-memory bandwidth for the incoming tiles. Warp 0 = TMA producer, warp 1 = MMA issuer + TMEM
 // owner, warps 4..11 = promotion / epilogue (TMEM lane quarter = warp % 4; warps 4-7 own output
 // columns 0-127 of the tile, warps 8-11 columns 128-255).
+#include <map>
+#include <tuple>
+
 #include "tc_common.cuh"
 
 namespace {
@@ -231,12 +234,59 @@ fp8_linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
 
 bool cwk_fp8_linear_tc_available() { return true; }
 
-// Widens W (E4M3 [cols][k]) into the context's bf16 buffer at element offset `at` and encodes its tensor map.
+// Widened copies of weight tensors, kept per context. A serving loop applies the same few projections to every
+// chunk, and checkpoints are immutable (the reference maps them read-only), so the exact E4M3 -> bf16 widening of a
+// weight is done once per (pointer, shape) and reused, up to a byte budget; beyond it, or after
+// cwk_ctx_drop_weight_cache, a call widens into the context's transient buffer as before.
+struct WideEntry {
+    void *dev;
+    CUtensorMap tm;
+};
+struct WideCache {
+    std::map<std::tuple<const void *, int64_t, int64_t>, WideEntry> m;
+    size_t bytes = 0;
+};
+
+void cwk_fp8_weight_cache_free(cwk_ctx *ctx) {
+    WideCache *wc = (WideCache *)ctx->wide_cache;
+    if (!wc) return;
+    for (auto &kv : wc->m) cudaFree(kv.second.dev);
+    delete wc;
+    ctx->wide_cache = nullptr;
+}
+
+static int encode_weight_map(cwk_ctx *ctx, const void *dst, int64_t cols, int64_t k, CUtensorMap *tm);
+
+// Widens W (E4M3 [cols][k]) to bf16 and encodes its tensor map: from the context's cache when the weight has been
+// seen, into the cache when it has room, else into the context's transient buffer at element offset `at`.
 static int prepare_weights(cwk_ctx *ctx, const void *W, int64_t cols, int64_t k, size_t at, CUtensorMap *tm) {
     const int64_t n16 = cols * k / 16;
+    const size_t bytes = (size_t)cols * k * 2;
+    if (!ctx->wide_cache) ctx->wide_cache = new WideCache();
+    WideCache *wc = (WideCache *)ctx->wide_cache;
+    const auto key = std::make_tuple(W, cols, k);
+    auto it = wc->m.find(key);
+    if (it != wc->m.end()) { *tm = it->second.tm; return CWK_OK; }
     uint16_t *dst = (uint16_t *)ctx->wbf16 + at;
+    bool cached = false;
+    if (wc->bytes + bytes <= ctx->wide_cache_budget) {
+        void *d = nullptr;
+        if (cudaMalloc(&d, bytes) == cudaSuccess) { dst = (uint16_t *)d; cached = true; }
+        else (void)cudaGetLastError();
+    }
     e4m3_to_bf16_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, ctx->stream>>>((const uint8_t *)W, dst, n16);
     CWK_LAUNCH_CHECK(ctx, "e4m3_to_bf16_kernel");
+    int s = encode_weight_map(ctx, dst, cols, k, tm);
+    if (s != CWK_OK) { if (cached) cudaFree(dst); return s; }
+    if (cached) {
+        wc->m[key] = WideEntry{dst, *tm};
+        wc->bytes += bytes;
+    }
+    return CWK_OK;
+}
+
+static int encode_weight_map(cwk_ctx *ctx, const void *dst_c, int64_t cols, int64_t k, CUtensorMap *tm) {
+    void *dst = const_cast<void *>(dst_c);
     CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
     cuuint32_t es[3] = {1, 1, 1};
     cuuint64_t wd[3] = {64, (cuuint64_t)cols, (cuuint64_t)(k / 64)};

@@ -25,6 +25,7 @@ SIGNATURES = {
     "cwk_ctx_profile": (i32, [vp, i32]),
     "cwk_ctx_profile_read": (i32, [vp, C.POINTER(C.c_double), C.POINTER(i32)]),
     "cwk_ctx_set_wait_limit": (i32, [vp, C.c_uint32]),
+    "cwk_ctx_weight_cache": (i32, [vp, C.c_size_t]),
     "cwk_mla_decode_path": (i32, [vp, i32, i32, i32]),
     "cwk_ctx_force_mla_path": (i32, [vp, i32]),
     "cwk_mla_decode_parked_records": (i32, [vp, C.POINTER(C.c_uint64)]),

@@ -77,6 +77,13 @@ CWK_API int cwk_ctx_sm_count(const cwk_ctx *ctx);
  * turn it on inside a stream capture. */
 CWK_API int cwk_ctx_profile(cwk_ctx *ctx, int on);
 CWK_API int cwk_ctx_profile_read(cwk_ctx *ctx, double *total_ms, int *launches);
+/* The tensor-core FP8 projection multiplies bf16 copies of the E4M3 weights (the widening is exact). A context
+ * can keep the copy of every weight it has seen, keyed by (pointer, shape), up to `budget_bytes`; the default is 0:
+ * keep none and widen on every call (16 us per projection of a 4096-wide layer). A caller whose weight buffers
+ * are immutable for the life of the context -- the reference maps its checkpoints read-only -- turns the cache
+ * on once. Calling this drops every copy held so far: do that before a weight buffer is rewritten in place or
+ * its memory is reused for another tensor. */
+CWK_API int cwk_ctx_weight_cache(cwk_ctx *ctx, size_t budget_bytes);
 /* Iteration limit of the device-side waits on another rank's flag
  * (cwk_mla_decode_kv_split). Default 2^22 polls of ~200 ns (about a second);
  * a test of the give-up path sets a few thousand. */

@@ -48,3 +48,30 @@ def test_against_per_row_gemv(attn, n, k, cols, out_bf16, kernel):
     scale = np.abs(want).max()
     tol = (8e-3 if out_bf16 else 2e-3) * scale
     assert np.max(np.abs(got - want)) <= tol
+
+
+def test_weight_cache_is_opt_in_and_dropped_on_request(attn):
+    """The bf16 copies of FP8 weights are kept only when the caller says its weights are immutable. With the cache on,
+    a weight buffer rewritten in place keeps giving the OLD product (that is the contract) until the cache is dropped;
+    with it off (the default) every call sees the current bytes."""
+    n, k, cols = 64, 512, 256
+    q1, sc = quantise(901, cols, k)
+    q2, _ = quantise(902, cols, k)
+    X = to_bf16_cuda(synth.normal_bf16(903, 2, (n, k)))
+    W, S = torch.from_numpy(q1).cuda(), torch.from_numpy(sc).cuda()
+    y1 = attn.fp8_linear(X, W, S, False).clone()
+    W.copy_(torch.from_numpy(q2).cuda())
+    y2 = attn.fp8_linear(X, W, S, False).clone()
+    assert not torch.equal(y1, y2)                        # default: no copy kept
+    attn.ctx.check(attn.lib.cwk_ctx_weight_cache(attn.ctx.h, 64 << 20))
+    try:
+        a = attn.fp8_linear(X, W, S, False).clone()       # widens q2 and keeps it
+        assert torch.equal(a, y2)
+        W.copy_(torch.from_numpy(q1).cuda())              # rewritten in place behind the cache's back
+        b = attn.fp8_linear(X, W, S, False).clone()
+        assert torch.equal(b, y2)                         # still the kept copy
+        attn.ctx.check(attn.lib.cwk_ctx_weight_cache(attn.ctx.h, 64 << 20))     # drop, keep caching
+        c = attn.fp8_linear(X, W, S, False).clone()
+        assert torch.equal(c, y1)
+    finally:
+        attn.ctx.check(attn.lib.cwk_ctx_weight_cache(attn.ctx.h, 0))
