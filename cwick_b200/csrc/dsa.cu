@@ -89,108 +89,9 @@ topk_select_kernel(const float *sc, int64_t sc_stride, const int32_t *n, int wan
     __shared__ TkShared sh;
     uint32_t kc[TK_PT];
     if (sl.cached) tk_load(s, sl.begin, sl.end, kc);
-    if (tid == 0) sh.pub = 0;
-    uint32_t thr;
-    int need_eq;
-    if (band_list) {
-        // The row holds +inf / -inf outside a short list of re-scored positions (cwk_dsa_select): the exact
-        // threshold is the (want - certainly selected)-th largest score of that list. Every block of the
-        // cluster finds it for itself; the list is a few hundred entries.
-        const int cnt = band_count[2 * b];
-        const int kth = max(1, min(want - band_count[2 * b + 1], cnt));   // holds by construction; clamped against a violated error bound
-        tk_list_select(s, band_list + (int64_t)b * sc_stride, cnt, kth, sh, thr, need_eq);
-    } else {
-        tk_radix_select(s, sl, kc, want, sh, thr, need_eq);
-    }
-    // thr is the integer image of the threshold; need_eq rows equal to it are wanted (the first
-    // ones in index order); want - need_eq rows lie above it.
-    const int n_gt = want - need_eq;
-    const int lane = tid & 31, warp = tid >> 5;
-    // this block's totals, for the offsets of the blocks after it
-    {
-        unsigned long long mine = 0;
-        for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
-            if (!sl.cached) tk_load(s, c0, sl.end, kc);
-            const int i0 = c0 + tid * TK_PT;
-#pragma unroll
-            for (int j = 0; j < TK_PT; j++)
-                if (i0 + j < sl.end) mine += (kc[j] > thr ? 1ull : 0ull) + (kc[j] == thr ? (1ull << 32) : 0ull);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
-        if (lane == 0 && mine) atomicAdd(&sh.pub, mine);
-    }
-    cl.sync();
-    if (tid == 0) {
-        unsigned long long base = 0;
-        int tbase = 0;
-        for (unsigned r = 0; r < rank; r++) {
-            const unsigned long long v = *cl.map_shared_rank(&sh.pub, r);
-            const int g = (int)(v & 0xffffffffull), e = (int)(v >> 32), eb = (int)(base >> 32);
-            tbase += g + max(0, min(e, need_eq - eb));
-            base += v;
-        }
-        sh.base = base;
-        sh.tbase = tbase;
-    }
-    __syncthreads();
-    unsigned long long running = sh.base;
-    const int eq_before_block = (int)(sh.base >> 32);
-    const int tbase = sh.tbase;
-    const int eq_quota = max(0, need_eq - eq_before_block);     // ties this block may still take
-    unsigned long long local = 0;                                // (above | equal) in this block's earlier chunks
-    for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
-        if (!sl.cached) tk_load(s, c0, sl.end, kc);
-        const int i0 = c0 + tid * TK_PT;
-        unsigned long long mine = 0;
-#pragma unroll
-        for (int j = 0; j < TK_PT; j++)
-            if (i0 + j < sl.end) mine += (kc[j] > thr ? 1ull : 0ull) + (kc[j] == thr ? (1ull << 32) : 0ull);
-        unsigned long long incl = mine;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += t;
-        }
-        if (lane == 31) sh.cnt[warp] = incl;
-        __syncthreads();
-        if (warp == 0) {
-            const unsigned long long v = sh.cnt[lane];
-            unsigned long long wi = v;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const unsigned long long t = __shfl_up_sync(0xffffffffu, wi, o);
-                if (lane >= o) wi += t;
-            }
-            sh.off[lane] = wi - v;
-            if (lane == 31) sh.total = wi;
-        }
-        __syncthreads();
-        const unsigned long long before = local + sh.off[warp] + incl - mine;   // within this block
-        int lg = (int)(before & 0xffffffffull), le = (int)(before >> 32);
-        const int og0 = (int)(running & 0xffffffffull), oe0 = (int)(running >> 32);
-#pragma unroll
-        for (int j = 0; j < TK_PT; j++) {
-            if (i0 + j < sl.end) {
-                const bool gt = kc[j] > thr, eq = kc[j] == thr;
-                const bool take = gt || (eq && le < eq_quota);
-                if (take) {
-                    if (ascending) out[tbase + lg + min(le, eq_quota)] = i0 + j;
-                    else if (gt) out[og0 + lg] = i0 + j;
-                    else out[n_gt + oe0 + le] = i0 + j;
-                }
-                lg += gt ? 1 : 0;
-                le += eq ? 1 : 0;
-            }
-        }
-        local += sh.total;
-    }
-    cl.sync();                              // every block's part of the list is written; nobody reads a neighbour's shared memory after this
-    if (rank == 0 && tid == 0) {
-        int cnt = want;
-        if (keep_self && out[cnt - 1] != nb - 1) out[cnt++] = nb - 1;
-        nsel[b] = cnt;
-    }
+    tk_threshold_and_compact(s, sl, kc, nb, want, keep_self, ascending, out, nsel + b,
+                             band_list ? band_list + (int64_t)b * sc_stride : nullptr, band_list ? band_count[2 * b] : 0,
+                             band_list ? band_count[2 * b + 1] : 0, sh);
 }
 
 extern "C" {
@@ -226,14 +127,6 @@ int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int3
 }
 
 }  // extern "C"
-
-int cwk_topk_compact(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int want, int keep_self, int32_t *sel,
-                     int64_t sel_ld, int32_t *nsel, const int32_t *band_list, const int32_t *band_count) {
-    CwkKernelTimer timer(ctx);
-    topk_select_kernel<<<dim3(TK_CL, B), TK_THREADS, 0, ctx->stream>>>(sc, sc_stride, n, want, keep_self, sel, sel_ld, nsel, 0, band_list, band_count);
-    CWK_LAUNCH_CHECK(ctx, "topk_select_kernel(compaction)");
-    return CWK_OK;
-}
 
 extern "C" {
 

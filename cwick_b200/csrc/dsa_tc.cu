@@ -71,6 +71,7 @@ struct IdxParams {
     const float *wt;          // f32 [B][64] head weights
     const int32_t *n;         // [B]
     float *sc;                // [B][key_stride]
+    int32_t *band;            // [B][2] counters of the classification that follows: zeroed here
     int64_t key_stride;
     int *err;
 };
@@ -94,6 +95,7 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tm_keys, const IdxP
     const int t_begin = (int)((int64_t)ntile * blockIdx.x / blocks_per_seq);
     const int t_end = (int)((int64_t)ntile * (blockIdx.x + 1) / blocks_per_seq);
     const int nt = t_end - t_begin;
+    if (blockIdx.x == 0 && tid < 2) p.band[2 * b + tid] = 0;
     if (nt <= 0) return;
 
     if (tid == 0) {
@@ -306,10 +308,12 @@ constexpr int BC_SMEM = (IT_IH * BC_QLD + IT_IH + BC_KEYS * IT_HD + BC_KEYS * (I
 // approximate score tau, then the classification of every key: certainly selected (refined =
 // +inf), certainly not (refined = -inf), or in the band |a - tau| <= eps, whose indices are appended
 // to band_list. band_count[2b] counts the band's entries, band_count[2b + 1] the keys above the band
-// (both zeroed by the caller).
+// (both zeroed by the scoring kernel before it). The same launch then re-scores the band exactly and
+// writes the selection.
 __global__ void __cluster_dims__(TK_CL, 1, 1) __launch_bounds__(TK_THREADS, 1)
 band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int want, float *refined, int32_t *band_list,
-                     int32_t *band_count, const uint8_t *keys, const float *kscale, const float *q, const float *wt) {
+                     int32_t *band_count, const uint8_t *keys, const float *kscale, const float *q, const float *wt,
+                     int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel) {
     extern __shared__ __align__(16) float bc_sm[];
     float *sq = bc_sm, *sw = sq + IT_IH * BC_QLD, *skey = sw + IT_IH, *sprod = skey + BC_KEYS * IT_HD;
     cg::cluster_group cl = cg::this_cluster();
@@ -319,8 +323,10 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
     const float *s = approx + (int64_t)b * stride;
     float *f = refined + (int64_t)b * stride;
     const TkSlice sl = tk_slice(nb, rank);
+    int32_t *out = sel + (int64_t)b * sel_ld;
     if (nb <= want) {                         // everything is selected: any finite value will do
-        for (int i = sl.begin + tid; i < sl.end; i += TK_THREADS) f[i] = s[i];
+        for (int i = sl.begin + tid; i < sl.end; i += TK_THREADS) { f[i] = s[i]; out[i] = i; }
+        if (rank == 0 && tid == 0) nsel[b] = nb;
         return;
     }
     __shared__ TkShared sh;
@@ -459,13 +465,16 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
         }
         __syncthreads();
     }
+    // ---- the selection itself, on the refined row: the exact threshold is the (want - certainly selected)-th largest of the
+    // re-scored keys; then the reference's list in the reference's order
+    cl.sync();                              // every block's re-scored keys are in refined[]
+    if (sl.cached) tk_load(f, sl.begin, sl.end, kc);
+    tk_threshold_and_compact(f, sl, kc, nb, want, keep_self, 0, out, nsel + b, list, total,
+                             *reinterpret_cast<volatile int32_t *>(band_count + 2 * b + 1), sh);
 }
 
 }  // namespace
 
-// cwk_topk_select over a refined row: the threshold comes from the band's re-scored keys only, then the ordered compaction
-int cwk_topk_compact(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int B, int want, int keep_self, int32_t *sel,
-                     int64_t sel_ld, int32_t *nsel, const int32_t *band_list, const int32_t *band_count);
 extern "C" int cwk_topk_select(cwk_ctx *ctx, const float *sc, int64_t sc_stride, const int32_t *n, int max_n, int B, int want,
                                int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel);
 extern "C" int cwk_indexer_scores_fp8(cwk_ctx *ctx, const void *keys, const float *kscale, int64_t key_stride, const float *q,
@@ -520,7 +529,7 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
         attr_set[ctx->device & 15] = true;
     }
     IdxParams p;
-    p.kscale = kscale; p.q = q; p.wt = wt; p.n = n; p.sc = approx; p.key_stride = key_stride; p.err = ctx->dev_err;
+    p.kscale = kscale; p.q = q; p.wt = wt; p.n = n; p.sc = approx; p.band = band; p.key_stride = key_stride; p.err = ctx->dev_err;
     const int tiles = (max_n + IT_KEYS - 1) / IT_KEYS;
     const int bps = std::max(1, std::min(tiles, ctx->sm_count / B));
     {
@@ -528,10 +537,12 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
         indexer_scores_tc_kernel<<<dim3(bps, B), IT_THREADS, I_SMEM, ctx->stream>>>(tm_keys, p);
         CWK_LAUNCH_CHECK(ctx, "indexer_scores_tc_kernel");
     }
-    CWK_CUDA(ctx, cudaMemsetAsync(band, 0, (size_t)B * 2 * sizeof(int32_t), ctx->stream));
-    band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, BC_SMEM, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band,
-                                                                              (const uint8_t *)keys, kscale, q, wt);
-    CWK_LAUNCH_CHECK(ctx, "band_classify_kernel");
+    {
+        CwkKernelTimer timer(ctx);
+        band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, BC_SMEM, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band,
+                                                                                  (const uint8_t *)keys, kscale, q, wt, keep_self, sel, sel_ld, nsel);
+        CWK_LAUNCH_CHECK(ctx, "band_classify_kernel");
+    }
     if (scores_out) CWK_CUDA(ctx, cudaMemcpyAsync(scores_out, refined, (size_t)B * key_stride * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-    return cwk_topk_compact(ctx, refined, key_stride, n, B, want, keep_self, sel, sel_ld, nsel, band_list, band);
+    return CWK_OK;
 }

@@ -331,15 +331,16 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
 
 // ---------------------------------------------------------------------------
 // Split merge. grid (nh, B, ceil(D/128)), 128 threads, one output column per thread. A short call
-// is a chain of latencies, so the loads of the first 32 records' values go out before anything
+// is a chain of latencies, so the loads of the first 64 records' values go out before anything
 // else: the weights e^(m_s-M) (two warp-shuffle reductions, one block barrier each) are computed
 // while they are in flight. FOLD = false: normalised bf16 rows out[b][h][D].
 // FOLD = true: one un-normalised record (same layout as the inputs) at rec_out.
 // ---------------------------------------------------------------------------
 constexpr int CWK_MAX_SPLITS = 512;
-constexpr int CWK_MERGE_AHEAD = 32;
 
-template <bool FOLD>
+// CWK_MERGE_AHEAD: records whose values a thread loads before it needs the weights (a load from L2 outlasts everything
+// else here): 64 for one sequence in many splits, 8 for many sequences in few (registers, hence blocks per SM).
+template <bool FOLD, int CWK_MERGE_AHEAD>
 static __global__ void __launch_bounds__(128) lse_merge_kernel(const float *partial, int nsplit, int nh, int D,
                                                                uint16_t *out, float *rec_out) {
     const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -404,8 +405,13 @@ static __global__ void __launch_bounds__(128) lse_merge_kernel(const float *part
 
 static inline void lse_combine_launch(cudaStream_t st, const float *partial, int nsplit, int nh, int D, int B,
                                       uint16_t *out) {
-    lse_merge_kernel<false><<<dim3(nh, B, (D + 127) / 128), 128, 0, st>>>(partial, nsplit, nh, D, out, nullptr);
+    const dim3 grid(nh, B, (D + 127) / 128);
+    if (nsplit > 32) lse_merge_kernel<false, 64><<<grid, 128, 0, st>>>(partial, nsplit, nh, D, out, nullptr);
+    else if (nsplit > 8) lse_merge_kernel<false, 32><<<grid, 128, 0, st>>>(partial, nsplit, nh, D, out, nullptr);
+    else lse_merge_kernel<false, 8><<<grid, 128, 0, st>>>(partial, nsplit, nh, D, out, nullptr);
 }
 static inline void lse_fold_launch(cudaStream_t st, const float *partial, int nsplit, int nh, int D, float *rec_out) {
-    lse_merge_kernel<true><<<dim3(nh, 1, (D + 127) / 128), 128, 0, st>>>(partial, nsplit, nh, D, nullptr, rec_out);
+    const dim3 grid(nh, 1, (D + 127) / 128);
+    if (nsplit > 32) lse_merge_kernel<true, 64><<<grid, 128, 0, st>>>(partial, nsplit, nh, D, nullptr, rec_out);
+    else lse_merge_kernel<true, 32><<<grid, 128, 0, st>>>(partial, nsplit, nh, D, nullptr, rec_out);
 }

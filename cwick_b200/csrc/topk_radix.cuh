@@ -57,12 +57,12 @@ __device__ __forceinline__ TkSlice tk_slice(int nb, unsigned rank) {
 __device__ __forceinline__ void tk_load(const float *s, int c0, int end, uint32_t (&k)[TK_PT]) {
     const int i0 = c0 + (int)threadIdx.x * TK_PT;
     if (i0 + TK_PT <= end && (reinterpret_cast<uintptr_t>(s + i0) & 15u) == 0) {
-        const float4 a = *reinterpret_cast<const float4 *>(s + i0), b = *reinterpret_cast<const float4 *>(s + i0 + 4);
+        const float4 a = __ldcg(reinterpret_cast<const float4 *>(s + i0)), b = __ldcg(reinterpret_cast<const float4 *>(s + i0 + 4));   // L2: the row may have been written by this launch
         k[0] = order_key(a.x); k[1] = order_key(a.y); k[2] = order_key(a.z); k[3] = order_key(a.w);
         k[4] = order_key(b.x); k[5] = order_key(b.y); k[6] = order_key(b.z); k[7] = order_key(b.w);
     } else {
 #pragma unroll
-        for (int j = 0; j < TK_PT; j++) k[j] = (i0 + j < end) ? order_key(s[i0 + j]) : 0u;
+        for (int j = 0; j < TK_PT; j++) k[j] = (i0 + j < end) ? order_key(__ldcg(s + i0 + j)) : 0u;
     }
 }
 
@@ -106,7 +106,7 @@ __device__ __forceinline__ void tk_list_select(const float *s, const int32_t *li
         if (tid < 256) sh.tot[tid] = 0;
         __syncthreads();
         for (int i = tid; i < cnt; i += TK_THREADS) {
-            const uint32_t k = order_key(s[list[i]]);
+            const uint32_t k = order_key(__ldcg(s + __ldcg(list + i)));
             if ((k & mask) == prefix) atomicAdd(&sh.tot[(k >> shift) & 255u], 1u);
         }
         __syncthreads();
@@ -166,5 +166,118 @@ __device__ __forceinline__ void tk_radix_select(const float *s, const TkSlice sl
         prefix = sh.sel[0];
         remaining = (int)sh.sel[1];
         mask |= 255u << shift;
+    }
+}
+
+// The second half of a selection, for every thread of every block of the row's cluster: the exact threshold (radix select
+// over the row, or, when the row holds +inf / -inf outside a short list of re-scored positions, over that list only), then
+// the ordered compaction into out[]: rows above the threshold in index order, then rows equal to it in index order, `want`
+// in all (ascending: one list in index order). kc holds the slice's keys when sl.cached.
+__device__ __forceinline__ void tk_threshold_and_compact(const float *s, const TkSlice sl, uint32_t (&kc)[TK_PT], int nb, int want,
+                                                         int keep_self, int ascending, int32_t *out, int32_t *nsel_b,
+                                                         const int32_t *band_list, int band_cnt, int band_above, TkShared &sh) {
+    cg::cluster_group cl = cg::this_cluster();
+    const unsigned rank = cl.block_rank();
+    const int tid = threadIdx.x;
+    if (tid == 0) sh.pub = 0;
+    uint32_t thr;
+    int need_eq;
+    if (band_list) {
+        // The row holds +inf / -inf outside a short list of re-scored positions (cwk_dsa_select): the exact
+        // threshold is the (want - certainly selected)-th largest score of that list. Every block of the
+        // cluster finds it for itself; the list is a few hundred entries.
+        const int kth = max(1, min(want - band_above, band_cnt));   // holds by construction; clamped against a violated error bound
+        tk_list_select(s, band_list, band_cnt, kth, sh, thr, need_eq);
+    } else {
+        tk_radix_select(s, sl, kc, want, sh, thr, need_eq);
+    }
+    // thr is the integer image of the threshold; need_eq rows equal to it are wanted (the first
+    // ones in index order); want - need_eq rows lie above it.
+    const int n_gt = want - need_eq;
+    const int lane = tid & 31, warp = tid >> 5;
+    // this block's totals, for the offsets of the blocks after it
+    {
+        unsigned long long mine = 0;
+        for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
+            if (!sl.cached) tk_load(s, c0, sl.end, kc);
+            const int i0 = c0 + tid * TK_PT;
+#pragma unroll
+            for (int j = 0; j < TK_PT; j++)
+                if (i0 + j < sl.end) mine += (kc[j] > thr ? 1ull : 0ull) + (kc[j] == thr ? (1ull << 32) : 0ull);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+        if (lane == 0 && mine) atomicAdd(&sh.pub, mine);
+    }
+    cl.sync();
+    if (tid == 0) {
+        unsigned long long base = 0;
+        int tbase = 0;
+        for (unsigned r = 0; r < rank; r++) {
+            const unsigned long long v = *cl.map_shared_rank(&sh.pub, r);
+            const int g = (int)(v & 0xffffffffull), e = (int)(v >> 32), eb = (int)(base >> 32);
+            tbase += g + max(0, min(e, need_eq - eb));
+            base += v;
+        }
+        sh.base = base;
+        sh.tbase = tbase;
+    }
+    __syncthreads();
+    unsigned long long running = sh.base;
+    const int eq_before_block = (int)(sh.base >> 32);
+    const int tbase = sh.tbase;
+    const int eq_quota = max(0, need_eq - eq_before_block);     // ties this block may still take
+    unsigned long long local = 0;                                // (above | equal) in this block's earlier chunks
+    for (int c0 = sl.begin; c0 < sl.end; c0 += TK_CHUNK) {
+        if (!sl.cached) tk_load(s, c0, sl.end, kc);
+        const int i0 = c0 + tid * TK_PT;
+        unsigned long long mine = 0;
+#pragma unroll
+        for (int j = 0; j < TK_PT; j++)
+            if (i0 + j < sl.end) mine += (kc[j] > thr ? 1ull : 0ull) + (kc[j] == thr ? (1ull << 32) : 0ull);
+        unsigned long long incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) sh.cnt[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            const unsigned long long v = sh.cnt[lane];
+            unsigned long long wi = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long t = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= o) wi += t;
+            }
+            sh.off[lane] = wi - v;
+            if (lane == 31) sh.total = wi;
+        }
+        __syncthreads();
+        const unsigned long long before = local + sh.off[warp] + incl - mine;   // within this block
+        int lg = (int)(before & 0xffffffffull), le = (int)(before >> 32);
+        const int og0 = (int)(running & 0xffffffffull), oe0 = (int)(running >> 32);
+#pragma unroll
+        for (int j = 0; j < TK_PT; j++) {
+            if (i0 + j < sl.end) {
+                const bool gt = kc[j] > thr, eq = kc[j] == thr;
+                const bool take = gt || (eq && le < eq_quota);
+                if (take) {
+                    if (ascending) out[tbase + lg + min(le, eq_quota)] = i0 + j;
+                    else if (gt) out[og0 + lg] = i0 + j;
+                    else out[n_gt + oe0 + le] = i0 + j;
+                }
+                lg += gt ? 1 : 0;
+                le += eq ? 1 : 0;
+            }
+        }
+        local += sh.total;
+    }
+    cl.sync();                              // every block's part of the list is written; nobody reads a neighbour's shared memory after this
+    if (rank == 0 && tid == 0) {
+        int cnt = want;
+        if (keep_self && out[cnt - 1] != nb - 1) out[cnt++] = nb - 1;
+        *nsel_b = cnt;
     }
 }

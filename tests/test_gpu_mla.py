@@ -226,6 +226,54 @@ def test_batch_and_split_invariance_at_config5_shape(attn):
     close(bf16_to_np(full[3]), want)
 
 
+@pytest.mark.parametrize("lens_list", [[129], [300], [1000], [5000], [8192], [9500], [2000, 1], [700, 0, 2500], [640, 640, 640, 100]])
+def test_short_launches_with_two_blocks_per_tile(attn, lens_list):
+    """One or a few sequences (at most half of the SMs would get a block): every tile is taken by two blocks, one per
+    half of the value columns. Against the oracle; twice, for reproducibility."""
+    B, T = len(lens_list), max(lens_list)
+    q, cache = make_case(500 + T + B, B, 64, T)
+    lens = np.array(lens_list, np.int32)
+    qd, cd, ld = to_bf16_cuda(q), to_bf16_cuda(cache), torch.from_numpy(lens).cuda()
+    got = attn.mla_decode(qd, cd, ld, scale=SCALE)
+    again = attn.mla_decode(qd, cd, ld, scale=SCALE)
+    attn.ctx.sync()
+    close(bf16_to_np(got), oracle_out(q, cache, lens))
+    assert torch.equal(got, again)
+
+
+def oracle_by_head_groups(q_u16, cache_u16, n, threads=16):
+    """orc.mla_decode over one long sequence, heads dealt over host threads (the C call releases the GIL)."""
+    from concurrent.futures import ThreadPoolExecutor
+    qf = synth.bf16_to_f32(q_u16)
+    nh = qf.shape[0]
+    groups = [list(range(i, nh, threads)) for i in range(threads) if i < nh]
+    out = np.empty((nh, L), np.float32)
+    def run(hs):
+        out[hs] = orc.mla_decode(qf[hs], cache_u16, n, L, R, SCALE)
+    with ThreadPoolExecutor(len(groups)) as ex:
+        list(ex.map(run, groups))
+    return out
+
+
+def test_config5b_one_131072_token_sequence_against_the_oracle(attn):
+    """BASELINE config 5b's sequence (1 x 131072 tokens, 64 heads) on one GPU, every head against the oracle;
+    then the same sequence as 8 KV ranges through the partial + merge entry points, as 8 ranks split it."""
+    T = 131072
+    g = torch.Generator(device="cuda").manual_seed(55)
+    q = torch.randn(1, 64, L + R, device="cuda", generator=g).to(torch.bfloat16)
+    cache = torch.randn(1, T, L + R, device="cuda", generator=g).to(torch.bfloat16)
+    lens = torch.full((1,), T, dtype=torch.int32, device="cuda")
+    got = attn.mla_decode(q, cache, lens, scale=SCALE, max_kv_len=T)
+    attn.ctx.sync()
+    qn = q[0].view(torch.int16).cpu().numpy().view(np.uint16)
+    cn = cache[0].view(torch.int16).cpu().numpy().view(np.uint16)
+    want = oracle_by_head_groups(qn, cn, T)
+    close(bf16_to_np(got[0]), want)
+    G = 8
+    parts = torch.stack([attn.mla_decode_partial(q[0], cache[0], r * (T // G), T // G, L, R, SCALE) for r in range(G)])
+    close(bf16_to_np(attn.lse_combine(parts, 64, L)), want)
+
+
 def test_persistent_kernel_shares_sequences_between_blocks(attn):
     """Ragged lengths and block counts that cut sequences at odd places: every sequence is shared by
     several blocks (accumulator + ticket), some blocks hold the end of one sequence and the start of the

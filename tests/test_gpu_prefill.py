@@ -65,6 +65,21 @@ def run_oracle(m, X, cache_init, pos0, nh, rows):
     return out, cache
 
 
+def run_oracle_rows(m, X, cache, nh, rows):
+    """Outputs of some query rows over a cache the oracle has already filled (n = 0: no row is rewritten)."""
+    o = orc.oracle()
+    H = X.shape[1]
+    q_lora = m["Wqa"].shape[0]
+    Xf = np.ascontiguousarray(synth.bf16_to_f32(X))
+    rows = np.ascontiguousarray(rows, np.int32)
+    out = np.empty((rows.size, nh, LAT), np.float32)
+    o.orc_mla_prefill(P(Xf, f32p), P(m["Wqa"], u8p), P(m["Sqa"], f32p), P(m["Wqb"], u8p), P(m["Sqb"], f32p),
+                      P(m["Wkva"], u8p), P(m["Skva"], f32p), P(m["qa_n"], u16p), P(m["kva_n"], u16p),
+                      P(m["Wuk"], u16p), P(cache, u16p), 0, 0, H, q_lora, nh, NOPE, ROPE, LAT, 1e-6, 10000.0,
+                      1.0 / math.sqrt(NOPE + ROPE), P(rows, i32p), rows.size, P(out, f32p))
+    return out
+
+
 @pytest.mark.parametrize("n,pos0,nh", [(96, 0, 64), (70, 45, 64), (40, 3, 16)])
 def test_small_chunks_every_row(attn, n, pos0, nh):
     H, q_lora = 512, 256
@@ -82,16 +97,26 @@ def test_small_chunks_every_row(attn, n, pos0, nh):
     close(bf16_to_np(got), want)
 
 
-def test_config3_full_size_sampled_rows(attn):
-    """BASELINE config 3: 4096-token prompt, hidden 4096, q_lora 1536, 64 heads. The oracle writes all
-    4096 latent rows but produces outputs for a handful of query rows only (first, last, middle)."""
+def test_config3_full_size_every_64th_row_and_the_last_128(attn):
+    """BASELINE config 3: 4096-token prompt, hidden 4096, q_lora 1536, 64 heads. The oracle writes all 4096
+    latent rows once, then produces the outputs of every 64th query row, the last 128 rows and a few rows at
+    tile edges (203 rows), dealt over host threads (the C call releases the GIL)."""
+    from concurrent.futures import ThreadPoolExecutor
     n, H, q_lora, nh = 4096, 4096, 1536, 64
     m = make_model(3, H, q_lora, nh)
     X = synth.normal_bf16(3, 9, (n, H))
     cache0 = np.zeros((n, LAT + ROPE), np.uint16)
     got, gcache = run_gpu(attn, m, X, cache0, 0, nh)
-    rows = np.array([0, 1, 127, 128, 2047, 4095], np.int32)
-    want, wcache = run_oracle(m, X, cache0, 0, nh, rows)
+    rows = np.array(sorted(set(range(0, n, 64)) | set(range(n - 128, n)) | {1, 63, 127, 128, 129, 2047}), np.int32)
+    _, wcache = run_oracle(m, X, cache0, 0, nh, rows[:0])               # the cache rows, no outputs
+    threads = 16
+    want = np.empty((rows.size, nh, LAT), np.float32)
+
+    def some_rows(i):                                                   # interleaved: long and short rows in every share
+        part = rows[i::threads]
+        want[i::threads] = run_oracle_rows(m, X, wcache, nh, part)
+    with ThreadPoolExecutor(threads) as ex:
+        list(ex.map(some_rows, range(threads)))
     g = bf16_to_np(got)
     assert np.isfinite(g).all()
     close(g[rows], want)

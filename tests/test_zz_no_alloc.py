@@ -4,8 +4,8 @@ It exists for hosts that cannot call cudaMalloc at the time they need attention 
 whose arena owns the device, a latency-bound request thread): its split records live in a
 fixed array inside the library instead of a buffer grown on demand. This test calls it
 through the C ABI twice in a row -- different shapes, so the second call runs over the first
-call's leftovers in the shared array -- and checks each result against the regular entry
-point, cwk_mla_decode, within the tolerance the other parity tests use. It also checks that a
+call's leftovers in the shared array -- and checks each result against the CPU oracle and
+against the regular entry point, cwk_mla_decode, within the tolerance the other parity tests use. It also checks that a
 request larger than the fixed array is refused with a message rather than run.
 
 Collected last (file name) so that a run stopping at the first failure has already run every
@@ -14,9 +14,12 @@ other test; it does not depend on them and passes alone in a fresh process.
 import ctypes as C
 import math
 
+import numpy as np
 import pytest
 import torch
 
+import orc
+from cwick_b200 import synth
 from gpu_util import bf16_to_np, close
 
 pytestmark = pytest.mark.gpu
@@ -51,6 +54,10 @@ def test_two_calls_in_a_row_match_the_regular_entry_point():
         want = attn.mla_decode(q, cache, lens, max_kv_len=T, scale=SCALE)
         torch.cuda.synchronize()
         close(bf16_to_np(got), bf16_to_np(want))
+        for b, n in enumerate(lens_list):                      # and every sequence against the oracle
+            qn = q[b].view(torch.int16).cpu().numpy().view(np.uint16)
+            cn = cache[b].view(torch.int16).cpu().numpy().view(np.uint16)
+            close(bf16_to_np(got[b]), orc.mla_decode(synth.bf16_to_f32(qn), cn, n, L, R, SCALE))
         # a call in steady state (not the first on the device) takes nothing from the driver's allocator
         out2 = torch.empty_like(got)
         torch.cuda.synchronize()
