@@ -624,6 +624,27 @@ def _time_calls(attn, stream, fn, n=20, warm=3):
     return e0.elapsed_time(e1) / n, k_ms / n, k_n // n
 
 
+def _time_graph(stream, fn, calls=16, reps=20):
+    """Mean milliseconds per fn() when `calls` of them are captured once as a CUDA graph and replayed: what a launch-bound
+    call costs on the device without the harness's per-call Python and launch overhead."""
+    import torch
+    fn()
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        for _ in range(calls):
+            fn()
+    for _ in range(3):
+        g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        g.replay()
+    e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / reps / calls
+
+
 def side_gqa_decode(attn, dev, stream, peak):
     """Config 1: GQA single-query decode, 16 q heads / 4 kv heads, hd 256, 4096 cached tokens; 16
     distinct caches in rotation (268 MB > L2)."""
@@ -640,9 +661,17 @@ def side_gqa_decode(attn, dev, stream, peak):
         attn.gqa_decode(q, K[i[0] % rot], V[i[0] % rot], lens, max_kv_len=T)
         i[0] += 1
     ms, k_ms, _ = _time_calls(attn, stream, call, n=64)
+    out = torch.empty(1, nh, hd, dtype=torch.bfloat16, device=dev)
+
+    def call_into():
+        attn.gqa_decode(q, K[i[0] % rot], V[i[0] % rot], lens, max_kv_len=T, out=out)
+        i[0] += 1
+    ms_g = _time_graph(stream, call_into, calls=rot)
     by = 2 * T * nkv * hd * 2 + 2 * nh * hd * 2
-    return {"us_per_call": 1e3 * ms, "kernel_us": 1e3 * k_ms, "tokens_per_s": 1e3 / ms,
-            "kernel_gbs": by / (k_ms / 1e3) / 1e9, "kernel_frac_of_measured_peak": by / (k_ms / 1e3) / 1e9 / peak,
+    return {"us_per_call": 1e3 * ms_g, "tokens_per_s": 1e3 / ms_g, "call_gbs": by / (ms_g / 1e3) / 1e9,
+            "call_frac_of_measured_peak": by / (ms_g / 1e3) / 1e9 / peak,
+            "how": "16 calls on 16 caches captured as one CUDA graph and replayed (decode kernel + merge per call)",
+            "us_per_call_eager_launches": 1e3 * ms, "kernel_us_between_events": 1e3 * k_ms,
             "algorithmic_bytes": by}
 
 
@@ -783,9 +812,12 @@ def side_kda(attn, dev, stream, peak):
             attn.ctx.check(attn.lib.cwk_kda_step(attn.ctx.h, B, nh, hd, -5.0, 1e-6, p(ins[0]), p(ins[1]), p(ins[2]), p(w[0]), p(w[1]), p(w[2]),
                                                  p(convs[r]), p(ins[3]), p(dt), p(a_log), p(ins[4]), p(ins[5]), p(on), p(recs[r]), p(core)))
         ms, k_ms, _ = _time_calls(attn, stream, call, n=40, warm=3)
+        ms_g = _time_graph(stream, call, calls=rot)
         by = B * nh * hd * hd * 4 * 2
-        out["slots_%d" % B] = {"us_per_step": ms * 1e3, "kernel_us": k_ms * 1e3, "state_bytes": by,
-                               "kernel_gbs": by / (k_ms / 1e3) / 1e9, "kernel_frac_of_measured_peak": by / (k_ms / 1e3) / 1e9 / peak}
+        out["slots_%d" % B] = {"us_per_step": ms_g * 1e3, "state_bytes": by, "step_gbs": by / (ms_g / 1e3) / 1e9,
+                               "step_frac_of_measured_peak": by / (ms_g / 1e3) / 1e9 / peak,
+                               "how": "steps over %d state sets captured as a CUDA graph and replayed" % rot,
+                               "us_per_step_eager_launches": ms * 1e3, "kernel_us_between_events": k_ms * 1e3}
         del recs, convs
         torch.cuda.empty_cache()
     return out
@@ -817,9 +849,12 @@ def side_gdn_mm(attn, dev, stream, peak):
             attn.ctx.check(attn.lib.cwk_gdn_scan(attn.ctx.h, B, 1, nh, hk, hv, grp, p(up), p(gdec), p(beta), p(gate), p(a_log), p(dtb),
                                                  p(norm), 1e-6, p(S[r]), p(o)))
         ms, k_ms, _ = _time_calls(attn, stream, call, n=40, warm=3)
+        ms_g = _time_graph(stream, call, calls=rot)
         by = B * nh * hv * hk * 4 * 2
-        out["gdn_slots_%d" % B] = {"us_per_step": ms * 1e3, "kernel_us": k_ms * 1e3, "state_bytes": by,
-                                   "kernel_gbs": by / (k_ms / 1e3) / 1e9, "kernel_frac_of_measured_peak": by / (k_ms / 1e3) / 1e9 / peak}
+        out["gdn_slots_%d" % B] = {"us_per_step": ms_g * 1e3, "state_bytes": by, "step_gbs": by / (ms_g / 1e3) / 1e9,
+                                   "step_frac_of_measured_peak": by / (ms_g / 1e3) / 1e9 / peak,
+                                   "how": "steps over %d state sets captured as a CUDA graph and replayed" % rot,
+                                   "us_per_step_eager_launches": ms * 1e3, "kernel_us_between_events": k_ms * 1e3}
         del S
         torch.cuda.empty_cache()
     n, idim, ih = 65536, 128, 4
@@ -834,12 +869,17 @@ def side_gdn_mm(attn, dev, stream, peak):
         it[0] += 1
         attn.ctx.check(attn.lib.cwk_mm_index_scores(attn.ctx.h, p(keys[it[0] % 12]), n, idim, p(iq), ih, p(sc)))
     ms_s, k_s, _ = _time_calls(attn, stream, scores, n=24, warm=3)
+    us_s = 1e3 * _time_graph(stream, scores, calls=12)
 
     def select():
         attn.ctx.check(attn.lib.cwk_mm_select_blocks(attn.ctx.h, p(sc), n, 64, 16, 4096, p(sel), p(nsel), None, None))
     ms_b, _, _ = _time_calls(attn, stream, select, n=24, warm=3)
-    out["mm_index_65536"] = {"scores_us": ms_s * 1e3, "scores_kernel_us": k_s * 1e3, "scores_gbs": n * idim * 2 / (k_s / 1e3) / 1e9,
-                             "scores_frac_of_measured_peak": n * idim * 2 / (k_s / 1e3) / 1e9 / peak, "select_blocks_us": ms_b * 1e3}
+    us_b = 1e3 * _time_graph(stream, select, calls=8)
+    out["mm_index_65536"] = {"scores_us": us_s, "scores_gbs": n * idim * 2 / (us_s / 1e6) / 1e9,
+                             "scores_frac_of_measured_peak": n * idim * 2 / (us_s / 1e6) / 1e9 / peak, "select_blocks_us": us_b,
+                             "how": "calls captured as a CUDA graph and replayed (12 key sets in rotation)",
+                             "scores_us_eager_launches": ms_s * 1e3, "scores_kernel_us_between_events": k_s * 1e3,
+                             "select_blocks_us_eager_launches": ms_b * 1e3}
     return out
 
 
@@ -876,16 +916,44 @@ def side_dsa(attn, dev, stream, peak):
     def gather():
         attn.mla_decode(mq, cache, out["fnsel"], sel=out["fsel"], scale=SCALE, max_kv_len=want + 1)
     ms_g, k_g, _ = _time_calls(attn, stream, gather, n=20, warm=3)
+
+    # The step as a device would replay it: selection + gathered attention captured as a CUDA graph, over two key sets in
+    # rotation (2 x 69 MB: a call does not find its keys in L2 from the call before).
+    from cwick_b200 import lib as cl
+    keys2, ks2 = synth.fp8_token_keys(B, T, hd, g, dev)
+    kk, sc2 = [keys, keys2], [ks, ks2]
+    gsel = torch.full((B, want + 1), -1, dtype=torch.int32, device=dev)
+    gnsel = torch.zeros(B, dtype=torch.int32, device=dev)
+    gout = torch.empty(B, NH, L, dtype=torch.bfloat16, device=dev)
+    p = lambda t: cl.vp(t.data_ptr())  # noqa: E731
+    it = [0]
+
+    def g_select():
+        r = it[0] & 1
+        it[0] += 1
+        attn.ctx.check(attn.lib.cwk_dsa_select(attn.ctx.h, p(kk[r]), p(sc2[r]), T, p(q), p(wt), p(n), T, B, ih, hd, want, 0,
+                                               p(gsel), want + 1, p(gnsel), None))
+
+    def g_gather():
+        attn.mla_decode(mq, cache, gnsel, sel=gsel, scale=SCALE, max_kv_len=want + 1, out=gout)
+
+    def g_step():
+        g_select()
+        g_gather()
+    us_sel = 1e3 * _time_graph(stream, g_select, calls=8)
+    us_gat = 1e3 * _time_graph(stream, g_gather, calls=8)
+    us_step = 1e3 * _time_graph(stream, g_step, calls=8)
     idx_bytes = B * T * (hd + 4)
     gat_bytes = B * want * DK * 2
-    total_ms = ms_f + ms_g
-    return {"ms_per_step": total_ms, "tokens_per_s": B / (total_ms / 1e3),
-            "select_ms": ms_f, "select_timed_kernels_ms": k_f, "select_gbs": idx_bytes / (ms_f / 1e3) / 1e9,
-            "select_frac_of_measured_peak": idx_bytes / (ms_f / 1e3) / 1e9 / peak,
-            "select_equals_exact_route": same,
-            "exact_route_indexer_ms": ms_s, "exact_route_topk_ms": ms_t,
-            "gather_attention_ms": ms_g, "gather_gbs": gat_bytes / (k_g / 1e3) / 1e9,
-            "gather_frac_of_measured_peak": gat_bytes / (k_g / 1e3) / 1e9 / peak}
+    return {"ms_per_step": us_step / 1e3, "tokens_per_s": B / (us_step / 1e6),
+            "how": "selection + gathered attention captured as a CUDA graph (8 steps, two key sets in rotation) and replayed",
+            "select_ms": us_sel / 1e3, "select_gbs": idx_bytes / (us_sel / 1e6) / 1e9,
+            "select_frac_of_measured_peak": idx_bytes / (us_sel / 1e6) / 1e9 / peak,
+            "select_launches": 2, "select_equals_exact_route": same,
+            "gather_attention_ms": us_gat / 1e3, "gather_gbs": gat_bytes / (us_gat / 1e6) / 1e9,
+            "gather_frac_of_measured_peak": gat_bytes / (us_gat / 1e6) / 1e9 / peak,
+            "eager_launches": {"ms_per_step": ms_f + ms_g, "select_ms": ms_f, "select_kernels_between_events_ms": k_f,
+                               "gather_attention_ms": ms_g, "exact_route_indexer_ms": ms_s, "exact_route_topk_ms": ms_t}}
 
 
 def main():

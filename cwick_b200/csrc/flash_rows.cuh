@@ -9,8 +9,10 @@
 //
 // Shared-memory tiles are rows of 16-byte chunks with chunk' = chunk ^ (row&7),
 // which makes every ldmatrix phase bank-conflict free. K/V tiles arrive by
-// cp.async, double buffered; a split of the key range ends in an un-normalised
-// partial {m, l, o} per row, or (direct mode) in normalised bf16 rows.
+// cp.async into a ring of NSTAGE tile buffers (2, or 3 where the kernel has nothing
+// but memory latency to hide: NSTAGE - 1 tiles are in flight while one is in use);
+// a split of the key range ends in an un-normalised partial {m, l, o} per row, or
+// (direct mode) in normalised bf16 rows.
 #pragma once
 #include "cwk_common.cuh"
 
@@ -36,7 +38,7 @@ struct FlashRowsParams {
     int nq;                   // GQA_PRE
 };
 
-template <int HB, int DK, int DV, int TK, int NWARPS, bool SEP_V>
+template <int HB, int DK, int DV, int TK, int NWARPS, bool SEP_V, int NSTAGE = 2>
 struct FlashRowsSmem {
     static constexpr int KC = DK / 8, VC = DV / 8, PC = TK / 8;
     static constexpr int Q_BYTES = HB * DK * 2;
@@ -45,24 +47,25 @@ struct FlashRowsSmem {
     static constexpr int P_BYTES = HB * TK * 2;
     static constexpr int WM = HB / 16, WN = NWARPS / WM;
     static constexpr int STAT_BYTES = 2 * 2 * WN * HB * 4;   // [parity][max|sum][WN][HB]
-    static constexpr int TOTAL = Q_BYTES + 2 * (K_BYTES + V_BYTES) + P_BYTES + STAT_BYTES;
+    static constexpr int TOTAL = Q_BYTES + NSTAGE * (K_BYTES + V_BYTES) + P_BYTES + STAT_BYTES;
 };
 
-template <int MODE, int HB, int DK, int DV, int TK, int NWARPS, bool SEP_V>
+template <int MODE, int HB, int DK, int DV, int TK, int NWARPS, bool SEP_V, int NSTAGE = 2>
 __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashRowsParams p) {
-    using SM = FlashRowsSmem<HB, DK, DV, TK, NWARPS, SEP_V>;
+    using SM = FlashRowsSmem<HB, DK, DV, TK, NWARPS, SEP_V, NSTAGE>;
+    static_assert(NSTAGE >= 2 && NSTAGE <= 4, "ring of 2 to 4 tile buffers");
     constexpr int KC = SM::KC, VC = SM::VC, PC = SM::PC;
     constexpr int WM = SM::WM, WN = SM::WN;
     constexpr int NT_S = TK / WN / 8;      // score n-tiles per warp
     constexpr int NT_O = DV / WN / 8;      // output n-tiles per warp
     constexpr int NTHREADS = NWARPS * 32;
-    static_assert(NT_S % 2 == 0 && NT_O % 2 == 0, "n-tiles are consumed in pairs");
+    static_assert((NT_S % 2 == 0 || NT_S == 1) && NT_O % 2 == 0, "n-tiles are consumed in pairs (a warp may own one score tile)");
     static_assert(KC % 8 == 0 && VC % 8 == 0 && PC % 8 == 0, "swizzle needs 8-chunk groups");
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *sQ = smem;
     uint8_t *sK0 = sQ + SM::Q_BYTES;
-    uint8_t *sP = sK0 + 2 * (SM::K_BYTES + SM::V_BYTES);
+    uint8_t *sP = sK0 + NSTAGE * (SM::K_BYTES + SM::V_BYTES);
     float *sStat = reinterpret_cast<float *>(sP + SM::P_BYTES);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -133,8 +136,11 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
         }
     };
 
-    if (tile_begin < tile_end) load_tile(tile_begin, 0);
-    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < NSTAGE - 1; i++) {          // one commit group per tile, empty ones included, so that the counts line up
+        if (tile_begin + i < tile_end) load_tile(tile_begin + i, i);
+        cp_async_commit();
+    }
 
     // ---- running state for this thread's two rows -----------------------------
     const int r0 = wm * 16 + (lane >> 2), r1 = r0 + 8;
@@ -149,10 +155,10 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
     for (int i = 0; i < NT_O; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
     for (int t = tile_begin; t < tile_end; t++) {
-        const int buf = (t - tile_begin) & 1;
-        cp_async_wait<0>();
-        __syncthreads();                 // tile t landed; everyone is done with tile t-1
-        if (t + 1 < tile_end) load_tile(t + 1, buf ^ 1);
+        const int buf = (t - tile_begin) % NSTAGE, par = (t - tile_begin) & 1;
+        cp_async_wait<NSTAGE - 2>();
+        __syncthreads();                 // tile t landed; everyone is done with tile t-1, whose buffer takes tile t+NSTAGE-1
+        if (t + NSTAGE - 1 < tile_end) load_tile(t + NSTAGE - 1, (buf + NSTAGE - 1) % NSTAGE);
         cp_async_commit();
 
         const uint8_t *tK = sK0 + buf * (SM::K_BYTES + SM::V_BYTES);
@@ -171,6 +177,12 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
             for (int ks = 0; ks < DK / 16; ks++) {
                 uint32_t a[4];
                 ldmatrix_x4(a[0], a[1], a[2], a[3], abase + (((ks * 2 + (lane >> 4)) ^ axor) << 4));
+                if constexpr (NT_S == 1) {          // eight keys per warp: one n-tile, two 8 x 8 matrices per k-step
+                    const int brow = wn * 8 + (lane & 7);
+                    uint32_t b0, b1;
+                    ldmatrix_x2(b0, b1, smem_u32(tK + brow * (DK * 2)) + (((ks * 2 + ((lane >> 3) & 1)) ^ (brow & 7)) << 4));
+                    mma_bf16_16816(s[0], a, b0, b1);
+                }
 #pragma unroll
                 for (int np = 0; np < NT_S / 2; np++) {
                     const int brow = wn * (TK / WN) + np * 16 + (lane & 7) + ((lane >> 4) << 3);
@@ -200,7 +212,7 @@ __global__ void __launch_bounds__(NWARPS * 32, 1) flash_rows_kernel(const FlashR
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        float *stMax = sStat + buf * (2 * WN * HB);
+        float *stMax = sStat + par * (2 * WN * HB);
         float *stSum = stMax + WN * HB;
         if ((lane & 3) == 0) {
             stMax[wn * HB + r0] = mx0;

@@ -8,14 +8,17 @@
 
 template <int HD>
 static int gqa_decode_launch(cwk_ctx *ctx, const FlashRowsParams &p, int B, int nkv, int ns) {
-    using SM = FlashRowsSmem<16, HD, HD, 64, 4, true>;
-    auto kern = flash_rows_kernel<MODE_GQA_DEC, 16, HD, HD, 64, 4, true>;
+    // A decode step is 4 FLOP per cached byte: nothing but latency to hide. A ring of three tiles (two in flight, 128 KB per
+    // SM at head dimension 256) and eight warps (two per scheduler; each owns eight keys of a tile's scores and 1/8 of the
+    // value columns), since the shared memory of a tile ring leaves room for one block per SM only.
+    using SM = FlashRowsSmem<16, HD, HD, 64, 8, true, 3>;
+    auto kern = flash_rows_kernel<MODE_GQA_DEC, 16, HD, HD, 64, 8, true, 3>;
     static bool attr_set[16] = {false};
     if (!attr_set[ctx->device & 15]) {
         CWK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL));
         attr_set[ctx->device & 15] = true;
     }
-    kern<<<dim3(ns, nkv, B), 128, SM::TOTAL, ctx->stream>>>(p);
+    kern<<<dim3(ns, nkv, B), 256, SM::TOTAL, ctx->stream>>>(p);
     CWK_LAUNCH_CHECK(ctx, "flash_rows_kernel<GQA_DEC>");
     return CWK_OK;
 }

@@ -134,7 +134,7 @@ class Attn:
         return (sel, nsel, sc) if return_scores else (sel, nsel)
 
     # ---- GQA -----------------------------------------------------------------
-    def gqa_decode(self, q, K, V, kv_len, scale=None, max_kv_len=None, n_splits=0):
+    def gqa_decode(self, q, K, V, kv_len, scale=None, max_kv_len=None, n_splits=0, out=None):
         """q [B][nh][hd]; K,V [B][T][nkv][hd] bf16; kv_len int32 [B]."""
         _bf16(q), _bf16(K), _bf16(V)
         B, nh, hd = q.shape
@@ -143,7 +143,8 @@ class Attn:
             scale = 1.0 / math.sqrt(hd)
         if max_kv_len is None:
             max_kv_len = int(kv_len.max().item())
-        out = torch.empty(B, nh, hd, dtype=torch.bfloat16, device=q.device)
+        if out is None:
+            out = torch.empty(B, nh, hd, dtype=torch.bfloat16, device=q.device)
         self.ctx.check(self.lib.cwk_gqa_decode(self.ctx.h, _p(q), _p(K), _p(V), T * nkv * hd, _p(kv_len),
                                                max_kv_len, B, nh, nkv, hd, scale, _p(out), n_splits))
         return out
