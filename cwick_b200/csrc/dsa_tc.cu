@@ -313,7 +313,14 @@ constexpr int BC_SMEM = (IT_IH * BC_QLD + IT_IH + BC_KEYS * IT_HD + BC_KEYS * (I
 __global__ void __cluster_dims__(TK_CL, 1, 1) __launch_bounds__(TK_THREADS, 1)
 band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int want, float *refined, int32_t *band_list,
                      int32_t *band_count, const uint8_t *keys, const float *kscale, const float *q, const float *wt,
-                     int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel) {
+                     int keep_self, int32_t *sel, int64_t sel_ld, int32_t *nsel, long long *trace) {
+#ifdef CWK_TRACE
+#define BTRACE(i) do { if (trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) trace[i] = clock64(); } while (0)
+#else
+#define BTRACE(i) do { } while (0)
+#endif
+    (void)trace;
+    BTRACE(0);
     extern __shared__ __align__(16) float bc_sm[];
     float *sq = bc_sm, *sw = sq + IT_IH * BC_QLD, *skey = sw + IT_IH, *sprod = skey + BC_KEYS * IT_HD;
     cg::cluster_group cl = cg::this_cluster();
@@ -361,7 +368,9 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
     }
     uint32_t prefix;
     int remaining;
+    BTRACE(1);
     tk_radix_select(s, sl, kc, want, sh, prefix, remaining);       // its cluster barriers also publish fmax
+    BTRACE(2);
     m = 0.f;
 #pragma unroll
     for (unsigned r = 0; r < TK_CL; r++) m = fmaxf(m, *cl.map_shared_rank(&sh.fmax, r));
@@ -412,10 +421,12 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
         for (int j = 0; j < TK_PT; j++)
             if (inb & (1u << j)) list[at++] = i0 + j;
     }
+    BTRACE(3);
     cl.sync();                              // every block's part of the band list is written (and fmax has been read everywhere)
+    BTRACE(4);
     // ---- exact scores of the band (the reference's order: src/attention.c:573-582 with dot_f32's grouping, :249-258).
     // The cluster's blocks share the list evenly; 64 keys per pass: dequantise into shared memory (16 threads per key),
-    // one (key, head) dot per thread and four heads in turn, then one thread per key adds the 64 weighted terms in head order.
+    // 2 x 2 (key, head) dots per thread, then one thread per key adds the 64 weighted terms in head order.
     const int total = *reinterpret_cast<volatile int32_t *>(band_count + 2 * b);
     const int per = (total + TK_CL - 1) / TK_CL;
     const int k_begin = min(total, (int)rank * per), k_end = min(total, k_begin + per);
@@ -436,25 +447,31 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
         }
         __syncthreads();
         {
-            const int kk = tid >> 4;
-            const float4 *kp = reinterpret_cast<const float4 *>(skey + kk * IT_HD);
-#pragma unroll 1
-            for (int j = 0; j < 4; j++) {
-                const int h = (tid & 15) + 16 * j;
-                const float4 *qp = reinterpret_cast<const float4 *>(sq + h * BC_QLD);
-                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll 8
-                for (int i = 0; i < IT_HD / 4; i++) {
-                    const float4 kv = kp[i], qv = qp[i];
-                    s0 = __fadd_rn(s0, __fmul_rn(kv.x, qv.x));
-                    s1 = __fadd_rn(s1, __fmul_rn(kv.y, qv.y));
-                    s2 = __fadd_rn(s2, __fmul_rn(kv.z, qv.z));
-                    s3 = __fadd_rn(s3, __fmul_rn(kv.w, qv.w));
-                }
-                float d = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
+            // a thread owns 2 keys x 2 heads (a warp: one key pair, broadcast, against all 64 heads): half the shared-memory
+            // reads of one (key, head) pair per thread. Every dot keeps the reference's order: four strided accumulators
+            // with separate multiply and add, then (s0 + s1) + (s2 + s3).
+            const int ka = (tid >> 5) * 2, ha = lane, hb2 = lane + 32;
+            const float4 *kp0 = reinterpret_cast<const float4 *>(skey + ka * IT_HD), *kp1 = kp0 + IT_HD / 4;
+            const float4 *qp0 = reinterpret_cast<const float4 *>(sq + ha * BC_QLD), *qp1 = reinterpret_cast<const float4 *>(sq + hb2 * BC_QLD);
+            float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f}, b0[4] = {0.f, 0.f, 0.f, 0.f}, b1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+            for (int i = 0; i < IT_HD / 4; i++) {
+                const float4 k0v = kp0[i], k1v = kp1[i], q0v = qp0[i], q1v = qp1[i];
+                a0[0] = __fadd_rn(a0[0], __fmul_rn(k0v.x, q0v.x)); a0[1] = __fadd_rn(a0[1], __fmul_rn(k0v.y, q0v.y));
+                a0[2] = __fadd_rn(a0[2], __fmul_rn(k0v.z, q0v.z)); a0[3] = __fadd_rn(a0[3], __fmul_rn(k0v.w, q0v.w));
+                a1[0] = __fadd_rn(a1[0], __fmul_rn(k0v.x, q1v.x)); a1[1] = __fadd_rn(a1[1], __fmul_rn(k0v.y, q1v.y));
+                a1[2] = __fadd_rn(a1[2], __fmul_rn(k0v.z, q1v.z)); a1[3] = __fadd_rn(a1[3], __fmul_rn(k0v.w, q1v.w));
+                b0[0] = __fadd_rn(b0[0], __fmul_rn(k1v.x, q0v.x)); b0[1] = __fadd_rn(b0[1], __fmul_rn(k1v.y, q0v.y));
+                b0[2] = __fadd_rn(b0[2], __fmul_rn(k1v.z, q0v.z)); b0[3] = __fadd_rn(b0[3], __fmul_rn(k1v.w, q0v.w));
+                b1[0] = __fadd_rn(b1[0], __fmul_rn(k1v.x, q1v.x)); b1[1] = __fadd_rn(b1[1], __fmul_rn(k1v.y, q1v.y));
+                b1[2] = __fadd_rn(b1[2], __fmul_rn(k1v.z, q1v.z)); b1[3] = __fadd_rn(b1[3], __fmul_rn(k1v.w, q1v.w));
+            }
+            auto fin = [&](const float (&s4)[4], int kk, int h) {
+                float d = __fadd_rn(__fadd_rn(s4[0], s4[1]), __fadd_rn(s4[2], s4[3]));
                 if (d < 0.f) d = 0.f;
                 sprod[kk * (IT_IH + 1) + h] = __fmul_rn(d, sw[h]);
-            }
+            };
+            fin(a0, ka, ha); fin(a1, ka, hb2); fin(b0, ka + 1, ha); fin(b1, ka + 1, hb2);
         }
         __syncthreads();
         if (tid < BC_KEYS && k0 + tid < k_end) {
@@ -467,10 +484,13 @@ band_classify_kernel(const float *approx, int64_t stride, const int32_t *n, int 
     }
     // ---- the selection itself, on the refined row: the exact threshold is the (want - certainly selected)-th largest of the
     // re-scored keys; then the reference's list in the reference's order
+    BTRACE(5);
     cl.sync();                              // every block's re-scored keys are in refined[]
+    BTRACE(6);
     if (sl.cached) tk_load(f, sl.begin, sl.end, kc);
     tk_threshold_and_compact(f, sl, kc, nb, want, keep_self, 0, out, nsel + b, list, total,
                              *reinterpret_cast<volatile int32_t *>(band_count + 2 * b + 1), sh);
+    BTRACE(7);
 }
 
 }  // namespace
@@ -540,7 +560,8 @@ extern "C" int cwk_dsa_select(cwk_ctx *ctx, const void *keys, const float *kscal
     {
         CwkKernelTimer timer(ctx);
         band_classify_kernel<<<dim3(TK_CL, B), TK_THREADS, BC_SMEM, ctx->stream>>>(approx, key_stride, n, want, refined, band_list, band,
-                                                                                  (const uint8_t *)keys, kscale, q, wt, keep_self, sel, sel_ld, nsel);
+                                                                                  (const uint8_t *)keys, kscale, q, wt, keep_self, sel, sel_ld, nsel,
+                                                                                  (long long *)ctx->tc_trace);
         CWK_LAUNCH_CHECK(ctx, "band_classify_kernel");
     }
     if (scores_out) CWK_CUDA(ctx, cudaMemcpyAsync(scores_out, refined, (size_t)B * key_stride * 4, cudaMemcpyDeviceToDevice, ctx->stream));

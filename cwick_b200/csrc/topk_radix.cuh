@@ -101,11 +101,14 @@ __device__ __forceinline__ void tk_list_select(const float *s, const int32_t *li
     prefix = 0;
     uint32_t mask = 0;
     remaining = rank;
+    // a thread's first entry stays in a register over the four passes (two dependent loads from L2 each time otherwise)
+    const uint32_t first = tid < cnt ? order_key(__ldcg(s + __ldcg(list + tid))) : 0u;
     for (int pass = 0; pass < 4; pass++) {
         const int shift = 24 - 8 * pass;
         if (tid < 256) sh.tot[tid] = 0;
         __syncthreads();
-        for (int i = tid; i < cnt; i += TK_THREADS) {
+        if (tid < cnt && (first & mask) == prefix) atomicAdd(&sh.tot[(first >> shift) & 255u], 1u);
+        for (int i = tid + TK_THREADS; i < cnt; i += TK_THREADS) {
             const uint32_t k = order_key(__ldcg(s + __ldcg(list + i)));
             if ((k & mask) == prefix) atomicAdd(&sh.tot[(k >> shift) & 255u], 1u);
         }
@@ -210,17 +213,25 @@ __device__ __forceinline__ void tk_threshold_and_compact(const float *s, const T
         if (lane == 0 && mine) atomicAdd(&sh.pub, mine);
     }
     cl.sync();
-    if (tid == 0) {
+    if (tid < 32) {
+        // totals of the blocks of lower rank: the lanes fetch them from the neighbours' shared memory together
+        // (one round trip instead of one per block), lane 0 adds them up in rank order
+        const unsigned long long mine = (unsigned)tid < rank ? *cl.map_shared_rank(&sh.pub, (unsigned)tid) : 0ull;
         unsigned long long base = 0;
         int tbase = 0;
-        for (unsigned r = 0; r < rank; r++) {
-            const unsigned long long v = *cl.map_shared_rank(&sh.pub, r);
-            const int g = (int)(v & 0xffffffffull), e = (int)(v >> 32), eb = (int)(base >> 32);
-            tbase += g + max(0, min(e, need_eq - eb));
-            base += v;
+#pragma unroll
+        for (unsigned r = 0; r < TK_CL; r++) {
+            const unsigned long long v = __shfl_sync(0xffffffffu, mine, (int)r);
+            if (r < rank) {
+                const int g = (int)(v & 0xffffffffull), e = (int)(v >> 32), eb = (int)(base >> 32);
+                tbase += g + max(0, min(e, need_eq - eb));
+                base += v;
+            }
         }
-        sh.base = base;
-        sh.tbase = tbase;
+        if (tid == 0) {
+            sh.base = base;
+            sh.tbase = tbase;
+        }
     }
     __syncthreads();
     unsigned long long running = sh.base;
