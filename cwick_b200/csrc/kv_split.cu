@@ -3,13 +3,15 @@
 // collective library call in the step.
 //
 // Every rank owns a "window": for each of two epoch parities, `world` record slots
-// {m[nh], l[nh], o[nh][L]} and `world` epoch words. A step on rank r is three launches:
+// {m[nh], l[nh], o[nh][L]} and `world` epoch words. A step on rank r is two launches:
 //   1. the split-KV decode over the local rows -> split records in local scratch;
-//   2. fold_push_kernel: folds the splits into ONE un-normalised record and stores it into
-//      slot r of EVERY rank's window (plain stores through peer pointers), then publishes the
-//      step's epoch number in word r of every window (release, system scope);
-//   3. wait_merge_kernel: waits (bounded) until all `world` words of the OWN window carry the
-//      epoch, then merges the `world` records -> bf16 output.
+//   2. xchg_step_kernel, one block per (head, 128-column chunk): folds the splits into ONE
+//      un-normalised record and stores its part of it into slot r of EVERY rank's window (plain
+//      stores through peer pointers); the last block to have done so publishes the step's epoch
+//      number in word r of every window (release, system scope); every block then waits
+//      (bounded) until all `world` words of the OWN window carry the epoch and merges its part of
+//      the `world` records -> bf16 output. All blocks of the launch are resident at once (256
+//      blocks of 128 threads), so the block that publishes never waits for a block that waits.
 // The records land in the consumer's own memory before it reads them; nothing reads remote
 // memory, nothing is multicast. Kernels of different GPUs wait on each other, kernels on one
 // GPU never do. A rank can be at most one step ahead of a peer (its next merge needs the peer's
@@ -39,59 +41,77 @@ __device__ __forceinline__ uint32_t *flag_ptr(float *win, int parity, int nh, in
     return reinterpret_cast<uint32_t *>(b + (((size_t)world * window_rec_floats(nh, L) * 4 + 255) & ~(size_t)255));
 }
 
-// grid (nh), 128 threads.
-__global__ void __launch_bounds__(128) fold_push_kernel(const float *partial, int nsplit, int nh, int D, PeerWindows pw,
-                                                        int rank, int world, uint32_t epoch, unsigned int *ticket) {
-    const int h = blockIdx.x, tid = threadIdx.x;
+// grid (nh, D / 128), 128 threads: thread = one column of one head. AHEAD: split records whose values a thread loads
+// before it needs their weights (a load from L2 outlasts everything else here).
+template <int AHEAD>
+__global__ void __launch_bounds__(128) xchg_step_kernel(const float *partial, int nsplit, int nh, int D, PeerWindows pw, int rank,
+                                                        int world, uint32_t epoch, unsigned int *ticket, uint16_t *out, int *err,
+                                                        unsigned int wait_limit) {
+    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int i = blockIdx.y * 128 + tid;
     const int64_t rec_sz = (int64_t)nh * (D + 2);
     __shared__ float sw[CWK_MAX_SPLITS];
-    __shared__ float red[128];
+    __shared__ float red[8];
+    __shared__ int s_ok;
+    // ---- fold the local splits: this thread's column of every record, the head's weights
+    const float *orow = partial + 2 * nh + (int64_t)h * D;
+    float v[AHEAD];
+#pragma unroll
+    for (int s = 0; s < AHEAD; s++) v[s] = (i < D && s < nsplit) ? orow[(int64_t)s * rec_sz + i] : 0.f;
     float mloc = -INFINITY;
     for (int s = tid; s < nsplit; s += 128) {
         const float l = partial[s * rec_sz + nh + h], m = partial[s * rec_sz + h];
         sw[s] = (l > 0.f) ? m : -INFINITY;
         if (l > 0.f) mloc = fmaxf(mloc, m);
     }
-    red[tid] = mloc;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+    if (lane == 0) red[warp] = mloc;
     __syncthreads();
-    for (int o = 64; o > 0; o >>= 1) { if (tid < o) red[tid] = fmaxf(red[tid], red[tid + o]); __syncthreads(); }
-    const float M = red[0];
-    __syncthreads();
+    const float M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     float dloc = 0.f;
     for (int s = tid; s < nsplit; s += 128) {
         const float w = (sw[s] == -INFINITY) ? 0.f : __expf(sw[s] - M);
         sw[s] = w;
         dloc += w * partial[s * rec_sz + nh + h];
     }
-    red[tid] = dloc;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dloc += __shfl_xor_sync(0xffffffffu, dloc, o);
+    if (lane == 0) red[4 + warp] = dloc;
     __syncthreads();
-    for (int o = 64; o > 0; o >>= 1) { if (tid < o) red[tid] += red[tid + o]; __syncthreads(); }
-    const float den = red[0];
+    const float den = (red[4] + red[5]) + (red[6] + red[7]);
+    float r = 0.f;
+    if (i < D) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < AHEAD; s++)
+            if (s < nsplit) a[s & 3] += sw[s] * v[s];
+        for (int s0 = AHEAD; s0 < nsplit; s0 += 16) {
+            float u[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) u[j] = (s0 + j < nsplit) ? orow[(int64_t)(s0 + j) * rec_sz + i] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (s0 + j < nsplit) a[j & 3] += sw[s0 + j] * u[j];
+        }
+        r = (a[0] + a[1]) + (a[2] + a[3]);
+    }
+    // ---- this block's part of the folded record into every rank's window
     const int parity = (int)(epoch & 1u);
-    if (tid == 0)
-        for (int g = 0; g < world; g++) {
-            float *dst = slot_ptr(pw.win[g], parity, nh, D, world, rank);
+    for (int g = 0; g < world; g++) {
+        float *dst = slot_ptr(pw.win[g], parity, nh, D, world, rank);
+        if (i < D) dst[2 * nh + (int64_t)h * D + i] = r;
+        if (blockIdx.y == 0 && tid == 0) {
             dst[h] = M;
             dst[nh + h] = den;
         }
-    const float *orow = partial + 2 * nh + (int64_t)h * D;
-    for (int i = tid * 2; i < D; i += 256) {
-        float a0 = 0.f, a1 = 0.f;
-        for (int s = 0; s < nsplit; s++) {
-            const float2 o = *reinterpret_cast<const float2 *>(orow + s * rec_sz + i);
-            a0 += sw[s] * o.x;
-            a1 += sw[s] * o.y;
-        }
-        for (int g = 0; g < world; g++)
-            *reinterpret_cast<float2 *>(slot_ptr(pw.win[g], parity, nh, D, world, rank) + 2 * nh + (int64_t)h * D + i) =
-                make_float2(a0, a1);
     }
-    // publish once every head's stores are out
+    // ---- publish once every block's stores are out
     __threadfence_system();
     __syncthreads();
     if (tid == 0) {
         const unsigned int t = atomicAdd(ticket, 1u);
-        if (t == (unsigned int)nh - 1) {
+        if (t == gridDim.x * gridDim.y - 1) {
             *ticket = 0;
             __threadfence_system();
             for (int g = 0; g < world; g++) {
@@ -99,26 +119,17 @@ __global__ void __launch_bounds__(128) fold_push_kernel(const float *partial, in
                 asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
             }
         }
-    }
-}
-
-// grid (nh), 128 threads. Waits on the OWN window only.
-__global__ void __launch_bounds__(128) wait_merge_kernel(float *own, int nh, int D, int world, uint32_t epoch, uint16_t *out,
-                                                         int *err, unsigned int wait_limit) {
-    const int h = blockIdx.x, tid = threadIdx.x;
-    const int parity = (int)(epoch & 1u);
-    __shared__ int s_ok;
-    if (tid == 0) {
-        const uint32_t *f = flag_ptr(own, parity, nh, D, world);
+        // ---- wait (bounded) for every rank's record in the OWN window
+        const uint32_t *f = flag_ptr(pw.win[rank], parity, nh, D, world);
         int ok = 1;
         for (int g = 0; g < world && ok; g++) {
-            uint32_t v = 0;
+            uint32_t fv = 0;
             unsigned int spins = 0;
             for (;;) {
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f + g) : "memory");
-                if (v == epoch) break;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(fv) : "l"(f + g) : "memory");
+                if (fv == epoch) break;
                 if (++spins > wait_limit) { ok = 0; break; }      // default ~1 s: a peer never published
-                __nanosleep(200);
+                __nanosleep(100);
             }
         }
         if (!ok) atomicCAS(err, 0, 701);
@@ -126,27 +137,31 @@ __global__ void __launch_bounds__(128) wait_merge_kernel(float *own, int nh, int
     }
     __syncthreads();
     if (!s_ok) return;
-    const float *base = slot_ptr(own, parity, nh, D, world, 0);
-    const int64_t rec_sz = (int64_t)nh * (D + 2);
-    float M = -INFINITY;
-    for (int g = 0; g < world; g++)
-        if (base[g * rec_sz + nh + h] > 0.f) M = fmaxf(M, base[g * rec_sz + h]);
-    float w[MAX_WORLD], den = 0.f;
-    for (int g = 0; g < world; g++) {
-        const float l = base[g * rec_sz + nh + h];
-        w[g] = l > 0.f ? __expf(base[g * rec_sz + h] - M) : 0.f;
-        den += w[g] * l;
+    // ---- merge the ranks' records: this thread's column
+    const float *base = slot_ptr(pw.win[rank], parity, nh, D, world, 0);
+    float ov[MAX_WORLD], mv[MAX_WORLD], lv[MAX_WORLD];
+#pragma unroll
+    for (int g = 0; g < MAX_WORLD; g++) {
+        const bool in = g < world && i < D;
+        ov[g] = in ? __ldcg(base + g * rec_sz + 2 * nh + (int64_t)h * D + i) : 0.f;
+        mv[g] = in ? __ldcg(base + g * rec_sz + h) : -INFINITY;
+        lv[g] = in ? __ldcg(base + g * rec_sz + nh + h) : 0.f;
     }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    for (int i = tid * 2; i < D; i += 256) {
-        float a0 = 0.f, a1 = 0.f;
-        for (int g = 0; g < world; g++) {
-            const float2 o = *reinterpret_cast<const float2 *>(base + g * rec_sz + 2 * nh + (int64_t)h * D + i);
-            a0 += w[g] * o.x;
-            a1 += w[g] * o.y;
-        }
-        *reinterpret_cast<uint32_t *>(out + (int64_t)h * D + i) = pack_bf16x2(a0 * inv, a1 * inv);
+    float M2 = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < MAX_WORLD; g++)
+        if (lv[g] > 0.f) M2 = fmaxf(M2, mv[g]);
+    float den2 = 0.f, acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < MAX_WORLD; g++) {
+        const float w = lv[g] > 0.f ? __expf(mv[g] - M2) : 0.f;
+        den2 += w * lv[g];
+        acc += w * ov[g];
     }
+    const float res = den2 > 0.f ? acc / den2 : 0.f;
+    // two columns per store
+    const float nb = __shfl_down_sync(0xffffffffu, res, 1);
+    if ((lane & 1) == 0 && i < D) *reinterpret_cast<uint32_t *>(out + (int64_t)h * D + i) = pack_bf16x2(res, nb);      // D is even
 }
 
 }  // namespace
@@ -212,21 +227,14 @@ int cwk_mla_decode_kv_split(cwk_ctx *ctx, const void *q, const void *cache, int6
     if (s != CWK_OK) return s;
     PeerWindows pw;
     for (int g = 0; g < MAX_WORLD; g++) pw.win[g] = (g < world) ? (float *)windows[g] : nullptr;
-    if (ns > 4) {
-        // Many split records (a long local range): fold them with the wide merge kernel first (a block per head and
-        // 128-column chunk, loads in flight 32 deep), so that the push kernel below, whose blocks walk the splits one
-        // after another, has a single record left to send.
-        float *folded = partial + (size_t)ns * window_rec_floats(nh, L);        // room behind the splits (reserved by the launch below)
-        lse_fold_launch(ctx->stream, partial, ns, nh, L, folded);
-        CWK_LAUNCH_CHECK(ctx, "lse_merge_kernel<fold>");
-        partial = folded;
-        ns = 1;
-    }
-    fold_push_kernel<<<nh, 128, 0, ctx->stream>>>(partial, ns, nh, L, pw, rank, world, epoch, (unsigned int *)ctx->ticket);
-    CWK_LAUNCH_CHECK(ctx, "fold_push_kernel");
-    wait_merge_kernel<<<nh, 128, 0, ctx->stream>>>((float *)windows[rank], nh, L, world, epoch, (uint16_t *)out, ctx->dev_err,
-                                                 ctx->wait_limit);
-    CWK_LAUNCH_CHECK(ctx, "wait_merge_kernel");
+    const dim3 grid(nh, (L + 127) / 128);
+    if (ns > 32)
+        xchg_step_kernel<64><<<grid, 128, 0, ctx->stream>>>(partial, ns, nh, L, pw, rank, world, epoch, (unsigned int *)ctx->ticket,
+                                                          (uint16_t *)out, ctx->dev_err, ctx->wait_limit);
+    else
+        xchg_step_kernel<32><<<grid, 128, 0, ctx->stream>>>(partial, ns, nh, L, pw, rank, world, epoch, (unsigned int *)ctx->ticket,
+                                                          (uint16_t *)out, ctx->dev_err, ctx->wait_limit);
+    CWK_LAUNCH_CHECK(ctx, "xchg_step_kernel");
     return CWK_OK;
 }
 

@@ -96,6 +96,7 @@ struct TcParams {
     uint16_t *out;         // direct mode (nsplit == 1): normalised bf16 [B][NH][L]; NULL = write partial records
     int reverse_b;         // schedule sequences last-to-first (causal prefill: longest first)
     int halves;            // 2: blockIdx.z picks one half of the 512 value columns (two blocks share a tile's scores)
+    int stagger;           // cycles between the start times of eight groups of blocks (0 = all at once)
 #ifdef CWK_TRACE
     long long *trace;      // developer build only: per-phase clock64 stamps of block (0,0); NULL = off
 #endif
@@ -144,6 +145,16 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kr) : "memory");
         for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), i == B_PFULL ? (uint32_t)NSOFT : 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // A full wave of blocks with many tiles each: blocks that start together stay in lockstep for their first tiles
+        // (every SM loads, then every SM computes, and HBM idles through the compute phases: 10 k cycles per tile against
+        // 7 k once they have drifted apart), so eight groups of blocks start a fraction of a tile period apart.
+        // Blocks that have one tile more than the others start first.
+        if (p.stagger) {
+            const bool longest = (ntiles % p.nsplit) != 0 && n == (ntiles + p.nsplit - 1) / p.nsplit;
+            const int group = longest ? 0 : ((ntiles % p.nsplit) != 0 ? 1 + (split + 3 * b) % 7 : (split + 3 * b) & 7);
+            const long long until = clock64() + (long long)group * p.stagger;
+            while (clock64() < until) { }
+        }
         // The first tile's loads go out before the block-wide set-up (TMEM allocation, the
         // barrier below): nothing they touch depends on it, and their latency is the longest
         // single item of a short call.
@@ -463,6 +474,10 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     p.out = (uint16_t *)out_direct;
     p.reverse_b = shared_cache ? 1 : 0;
     p.halves = ((int64_t)nsplit * B * 2 <= ctx->sm_count) ? 2 : 1;
+    {
+        const int tiles_per_block = ((max_kv_len + TILE - 1) / TILE + nsplit - 1) / nsplit;
+        p.stagger = ((int64_t)nsplit * B * 2 > ctx->sm_count && tiles_per_block >= 6) ? 700 : 0;
+    }
     mla_decode_tc_kernel<<<dim3(nsplit, B, p.halves), NTHREADS, SMEM_TOTAL, ctx->stream>>>(*tm_q, *tm_kv, *tm_kr, p);
     CWK_LAUNCH_CHECK(ctx, "mla_decode_tc_kernel");
     return CWK_OK;
