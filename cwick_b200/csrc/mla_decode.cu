@@ -12,7 +12,7 @@
 // not apply so the caller can take the mma.sync path.
 int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride,
                              int64_t ld, const int32_t *kv_len, int max_kv_len, int B, int nh,
-                             int R, float scale, float *partial, int nsplit, void *out_direct);
+                             int R, float scale, float *partial, int nsplit, void *out_direct, const int32_t *sel, int64_t sel_ld);
 bool cwk_mla_decode_tc_available();
 // persistent tcgen05/TMA kernel with the cross-block reduction inside (mla_decode_sk.cu): bf16 rows to `out`, or one
 // folded record per sequence to `rec_out`
@@ -116,12 +116,13 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     int path = (L == 512 && R == 64 && aligned) ? 1 : 0;
     // the tcgen05 kernel also takes the rope-free 512-wide latent: its ninth column block is then
     // out of the tensor's bounds and arrives as zeros
-    const bool tc_ok = L == 512 && (R == 64 || R == 0) && aligned && !sel && nh == 64 && max_kv_len > 0 && cwk_mla_decode_tc_available();
+    // (a row list goes to the same kernel: two of its warps fetch the listed rows with 16-byte copies instead of TMA boxes)
+    const bool tc_ok = L == 512 && (R == 64 || R == 0) && aligned && nh == 64 && max_kv_len > 0 && cwk_mla_decode_tc_available();
     if (tc_ok) path = 2;
     if (ctx->force_mla_path >= 0 && ctx->force_mla_path != 3) {
         // 4 = the persistent kernel: same conditions as 2, taken only on request (its cross-block sums go through f32
         // atomics, which the split records + merge launch of 2 beat at every shape measured so far)
-        const int best = tc_ok ? 4 : path;
+        const int best = tc_ok ? (sel ? 2 : 4) : path;
         if (ctx->force_mla_path > best || (ctx->force_mla_path == 3))
             return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "mla_decode: forced path %d not applicable (best %d)", ctx->force_mla_path, path);
         path = ctx->force_mla_path;
@@ -164,7 +165,7 @@ static int mla_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t se
     CwkKernelTimer timer(ctx);
     if (path == 2) {
         int s = cwk_mla_decode_tc_launch(ctx, q, cache, seq_stride, ld, kv_len, max_kv_len, B, nh, R, scale, partial, ns,
-                                         direct ? out : nullptr);
+                                         direct ? out : nullptr, sel, sel_ld);
         if (s != CWK_OK) return s;
     } else if (path == 1) {
         static bool attr_set[16] = {false};

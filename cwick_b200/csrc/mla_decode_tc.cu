@@ -97,6 +97,14 @@ struct TcParams {
     int reverse_b;         // schedule sequences last-to-first (causal prefill: longest first)
     int halves;            // 2: blockIdx.z picks one half of the 512 value columns (two blocks share a tile's scores)
     int stagger;           // cycles between the start times of eight groups of blocks (0 = all at once)
+    // gather mode (sel != NULL): the tile's rows are cache rows sel[b][j], fetched with 16-byte asynchronous copies into
+    // the same swizzled blocks the tiled loads fill (a TMA box cannot follow a row list): the first tile by the 16
+    // softmax warps, which have nothing else to do yet, the following ones by two otherwise idle warps
+    const int32_t *sel;    // [B][sel_ld] device
+    int64_t sel_ld;
+    const uint16_t *cache;
+    int64_t seq_stride, ld;
+    int rope_cols;         // 64, or 0: the ninth block is zeros
 #ifdef CWK_TRACE
     long long *trace;      // developer build only: per-phase clock64 stamps of block (0,0); NULL = off
 #endif
@@ -143,7 +151,8 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kv) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_kr) : "memory");
-        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), i == B_PFULL ? (uint32_t)NSOFT : 1u);
+        for (int i = 0; i < B_COUNT; i++)
+            mbar_init(bar(i), i == B_PFULL ? (uint32_t)NSOFT : (p.sel && i < B_EMPTY_L) ? (uint32_t)NSOFT : 1u);      // gather: 512 arrivals fill a block
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // A full wave of blocks with many tiles each: blocks that start together stay in lockstep for their first tiles
         // (every SM loads, then every SM computes, and HBM idles through the compute phases: 10 k cycles per tile against
@@ -160,12 +169,14 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // single item of a short call.
         mbar_expect_tx(bar(B_QFULL), NBLK * Q_BLK);
         tma_load_3d(base + OFF_Q, &tm_q, 0, b * NH, 0, bar(B_QFULL));
-        for (int k = 0; k < 6; k += 2) {
-            mbar_expect_tx(bar(B_FULL + k), 2 * KV_BLK);
-            tma_load_4d(base + OFF_KV + k * KV_BLK, &tm_kv, 0, t0 * TILE, k, bz, bar(B_FULL + k));
+        if (!p.sel) {
+            for (int k = 0; k < 6; k += 2) {
+                mbar_expect_tx(bar(B_FULL + k), 2 * KV_BLK);
+                tma_load_4d(base + OFF_KV + k * KV_BLK, &tm_kv, 0, t0 * TILE, k, bz, bar(B_FULL + k));
+            }
+            mbar_expect_tx(bar(B_FULL + 6), 3 * KV_BLK);
+            tma_load_4d(base + OFF_KV + 6 * KV_BLK, &tm_kr, 0, t0 * TILE, 6, bz, bar(B_FULL + 6));
         }
-        mbar_expect_tx(bar(B_FULL + 6), 3 * KV_BLK);
-        tma_load_4d(base + OFF_KV + 6 * KV_BLK, &tm_kr, 0, t0 * TILE, 6, bz, bar(B_FULL + 6));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TMEM_COLS) : "memory");
@@ -186,7 +197,7 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (lane == 0 && !p.sel) {
             bool ok = true;
             int issued_it[NBLK];
             for (int k = 0; k < NBLK; k++) issued_it[k] = 0;      // tile 0 went out during set-up
@@ -218,6 +229,59 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 for (int k = 0; k < 8; k += 2)
                     if (issued_it[k] >= 0) mbar_wait(bar(B_FULL + k), (uint32_t)(issued_it[k] & 1), p.err, 104);
             }
+        }
+    } else if ((warp == 2 || warp == 3) && p.sel) {
+        // ------------------------------------------------------------ gather producer (row lists)
+        // 64 threads, two rows of the tile each: a row's 1152 bytes go out as 72 copies of 16 bytes, each to its place
+        // in the 128-byte-swizzled block of its 64 columns. One commit group per pair of blocks (three for the last),
+        // so that the score MMAs start on the first pair while the others are still arriving.
+        const int pt = tid - 64;
+        const uint16_t *cbase = p.cache + (p.batch_coord_zero ? 0 : (int64_t)b * p.seq_stride);
+        const int32_t *selb = p.sel + (int64_t)b * p.sel_ld;
+        bool ok = true;
+        for (int it = 1; it < n && ok; it++) {          // (the first tile is fetched by the softmax warps, idle until its scores exist)
+            const uint32_t par_free = (uint32_t)((it & 1) ^ 1);
+            const uint16_t *src[2];
+            bool val[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) {
+                const int j = (t0 + it) * TILE + pt + 64 * rr;
+                val[rr] = j < kv;
+                src[rr] = cbase + (int64_t)(val[rr] ? selb[j] : 0) * p.ld;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) {
+                ok = mbar_wait(bar(B_EMPTY_L + (k >> 1)), par_free, p.err, 105);
+                if (ok && k == 6) ok = mbar_wait(bar(B_EMPTY_RP), par_free, p.err, 106);
+                if (ok) {
+#pragma unroll
+                    for (int kb = k; kb < (k == 6 ? 9 : k + 2); kb++) {
+#pragma unroll
+                        for (int rr = 0; rr < 2; rr++) {
+                            const int r = pt + 64 * rr;
+                            const bool v = val[rr] && (kb < 8 || p.rope_cols != 0);
+                            const uint32_t dst = base + OFF_KV + kb * KV_BLK + r * 128;
+#pragma unroll
+                            for (int c = 0; c < 8; c++)
+                                cp_async16(dst + (uint32_t)((c ^ (r & 7)) << 4), src[rr] + kb * 64 + c * 8, v);
+                        }
+                    }
+                }
+                cp_async_commit();        // (an empty group after a failed wait keeps the counts below in step)
+            }
+            // a group's bytes are in shared memory -> visible to the tensor-core (asynchronous) proxy -> the block pair is full
+            cp_async_wait<3>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive_n(bar(B_FULL + 0), NSOFT / 64);
+            cp_async_wait<2>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive_n(bar(B_FULL + 2), NSOFT / 64);
+            cp_async_wait<1>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive_n(bar(B_FULL + 4), NSOFT / 64);
+            cp_async_wait<0>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive_n(bar(B_FULL + 6), NSOFT / 64);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -281,6 +345,41 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         float lpart[HG];
 #pragma unroll
         for (int h = 0; h < HG; h++) lpart[h] = 0.f;
+        if (p.sel) {
+            // gather mode: these 512 threads have nothing to do until the first tile's scores exist, so they fetch the
+            // first tile (four threads per row; 16-byte copies into the swizzled blocks, one commit group per block pair)
+            const int r = st >> 2, part = st & 3;
+            const int j = t0 * TILE + r;
+            const bool val = j < kv;
+            const uint16_t *src = p.cache + (p.batch_coord_zero ? 0 : (int64_t)b * p.seq_stride) +
+                                  (int64_t)(val ? p.sel[(int64_t)b * p.sel_ld + j] : 0) * p.ld;
+            const uint32_t drow = base + OFF_KV + r * 128;
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) {
+                const int per = (k == 6) ? 6 : 4;                // 16-byte pieces of the pair (or triple) for this thread
+#pragma unroll
+                for (int x = 0; x < 6; x++) {
+                    if (x < per) {
+                        const int cc = part * per + x, kb = k + (cc >> 3), c = cc & 7;
+                        cp_async16(drow + (uint32_t)(kb * KV_BLK) + (uint32_t)((c ^ (r & 7)) << 4), src + kb * 64 + c * 8,
+                                   val && (kb < 8 || p.rope_cols != 0));
+                    }
+                }
+                cp_async_commit();
+            }
+            cp_async_wait<3>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar(B_FULL + 0));
+            cp_async_wait<2>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar(B_FULL + 2));
+            cp_async_wait<1>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar(B_FULL + 4));
+            cp_async_wait<0>();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar(B_FULL + 6));
+        }
         bool ok = true;
         for (int it = 0; it < n; it++) {
             ok = mbar_wait(bar(B_SFULL), (uint32_t)(it & 1), p.err, 301);
@@ -446,7 +545,7 @@ bool cwk_mla_decode_tc_available() { return true; }
 
 int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_stride, int64_t ld,
                              const int32_t *kv_len, int max_kv_len, int B, int nh, int R, float scale, float *partial,
-                             int nsplit, void *out_direct) {
+                             int nsplit, void *out_direct, const int32_t *sel, int64_t sel_ld) {
     const int width = L + R;          // 576, or 512 for a rope-free latent (the rope block then reads as zeros)
     if (nh != NH) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode is built for 64 heads");
     if (max_kv_len <= 0) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "tcgen05 MLA decode needs a non-empty cache");
@@ -472,6 +571,7 @@ int cwk_mla_decode_tc_launch(cwk_ctx *ctx, const void *q, const void *cache, int
     p.trace = (long long *)ctx->tc_trace;
 #endif
     p.out = (uint16_t *)out_direct;
+    p.sel = sel; p.sel_ld = sel_ld; p.cache = (const uint16_t *)cache; p.seq_stride = seq_stride; p.ld = ld; p.rope_cols = R;
     p.reverse_b = shared_cache ? 1 : 0;
     p.halves = ((int64_t)nsplit * B * 2 <= ctx->sm_count) ? 2 : 1;
     {

@@ -28,6 +28,10 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// one thread standing in for `count` arrivals
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
 // Bounded wait. Returns false (and records `code`) when it gives up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *err, int code) {
     for (uint32_t i = 0; i < WAIT_LIMIT; i++)
