@@ -82,12 +82,19 @@ struct CwkKernelTimer {
             ctx->ev.push_back(a);
             ctx->ev.push_back(b);
         }
-        cudaEventRecord(ctx->ev[ctx->ev_used], ctx->stream);
+        record(ctx->ev[ctx->ev_used]);
     }
     ~CwkKernelTimer() {
         if (!ctx->profiling) return;
-        cudaEventRecord(ctx->ev[ctx->ev_used + 1], ctx->stream);
+        record(ctx->ev[ctx->ev_used + 1]);
         ctx->ev_used += 2;
+    }
+    // Inside a stream capture the record becomes an event-record node of the graph (the "external" form, whose time can
+    // be read after a replay): a caller can time the kernels in the graph it actually replays.
+    void record(cudaEvent_t e) {
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(ctx->stream, &st);
+        cudaEventRecordWithFlags(e, ctx->stream, st == cudaStreamCaptureStatusActive ? cudaEventRecordExternal : cudaEventRecordDefault);
     }
 };
 
