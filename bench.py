@@ -870,6 +870,27 @@ def side_gdn_mm(attn, dev, stream, peak):
                                    "us_per_step_eager_launches": ms * 1e3, "kernel_us_between_events": k_ms * 1e3}
         del S
         torch.cuda.empty_cache()
+    # a 4096-token prompt through the scan: chunk-parallel (64 positions at a time) against position-serial
+    npr = 4096
+    up = torch.randn(1, npr, 2 * key_dim + val_dim, device=dev, generator=g) * 0.1
+    kq = up[:, :, :2 * key_dim].reshape(1, npr, 2 * (nh // grp), hk)
+    kq /= kq.norm(dim=-1, keepdim=True)
+    gdec, beta = torch.randn(1, npr, nh, device=dev, generator=g), torch.randn(1, npr, nh, device=dev, generator=g)
+    gate = torch.randn(1, npr, val_dim, device=dev, generator=g)
+    Sp = 0.05 * torch.randn(1, nh, hv, hk, device=dev, generator=g)
+    op = torch.empty(1, npr, val_dim, device=dev)
+
+    def prompt():
+        attn.ctx.check(attn.lib.cwk_gdn_scan(attn.ctx.h, 1, npr, nh, hk, hv, grp, p(up), p(gdec), p(beta), p(gate), p(a_log), p(dtb),
+                                             p(norm), 1e-6, p(Sp), p(op)))
+    ms_c, k_c, _ = _time_calls(attn, stream, prompt, n=5, warm=2)
+    attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, 0)
+    try:
+        ms_ser, _, _ = _time_calls(attn, stream, prompt, n=2, warm=1)
+    finally:
+        attn.lib.cwk_ctx_force_mla_path(attn.ctx.h, -1)
+    out["gdn_prompt_4096"] = {"ms_chunk_parallel": ms_c, "ms_position_serial": ms_ser, "ms_in_order_pass_between_events": k_c, "tokens_per_s": npr / (ms_c / 1e3),
+                              "heads": nh, "head_dims": [hk, hv]}
     n, idim, ih = 65536, 128, 4
     keys = [torch.randn(n, idim, device=dev, generator=g).to(torch.bfloat16) for _ in range(12)]      # 201 MB in rotation
     iq = torch.randn(ih, idim, device=dev, generator=g)

@@ -20,7 +20,7 @@ NVCC_FLAGS = [
 # recurrences) are compiled WITHOUT fast-math: IEEE division and square root, no flush-to-zero, no contraction of
 # a*b+c across statements that the source keeps apart. Everything else (the tensor-core attention kernels, whose
 # bar is a tolerance) takes --use_fast_math for its exp2/division forms.
-EXACT_SOURCES = {"dsa.cu", "ds_compress.cu", "prep_ds.cu", "mm_index.cu", "cache_io.cu", "kda.cu", "gdn.cu"}
+EXACT_SOURCES = {"dsa.cu", "ds_compress.cu", "prep_ds.cu", "mm_index.cu", "cache_io.cu", "kda.cu", "gdn.cu", "gdn_chunk.cu"}
 
 
 def sources():

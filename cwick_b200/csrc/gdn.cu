@@ -30,6 +30,7 @@ struct GdnParams {
     float *S;              // [B][nh][head_v][head_k]
     float *out;            // [B][n][val_dim]
     int n, nh, kv_group;
+    int n_stride;          // positions per slot in the arrays (>= n: a call's tail after the chunk-parallel part)
     float rms_eps;
 };
 
@@ -86,17 +87,17 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnParams p, int ni
         }
         const float ea = g_exp(p.a_log[vh]), dtb = p.dt_bias[vh];
         for (int t = 0; t < p.n; t++) {
-            const float *row = p.up + ((int64_t)b * p.n + t) * qkv_dim;
+            const float *row = p.up + ((int64_t)b * p.n_stride + t) * qkv_dim;
             for (int i = j; i < HK; i += hv) {
                 s_q[i] = row[(int64_t)kh * HK + i];
                 s_k[i] = row[key_dim + (int64_t)kh * HK + i];
             }
             const float vj = row[2 * key_dim + (int64_t)vh * hv + j];
-            const float zj = p.gate[((int64_t)b * p.n + t) * val_dim + (int64_t)vh * hv + j];
-            const float x = __fadd_rn(p.gdec[((int64_t)b * p.n + t) * p.nh + vh], dtb);
+            const float zj = p.gate[((int64_t)b * p.n_stride + t) * val_dim + (int64_t)vh * hv + j];
+            const float x = __fadd_rn(p.gdec[((int64_t)b * p.n_stride + t) * p.nh + vh], dtb);
             const float sp = x > 20.0f ? x : (float)log1p((double)g_exp(x));
             const float decay = g_exp(__fmul_rn(-ea, sp));
-            const float bet = __fdiv_rn(1.0f, __fadd_rn(1.0f, g_exp(-p.beta[((int64_t)b * p.n + t) * p.nh + vh])));
+            const float bet = __fdiv_rn(1.0f, __fadd_rn(1.0f, g_exp(-p.beta[((int64_t)b * p.n_stride + t) * p.nh + vh])));
             __syncthreads();
             float dot = 0.f;
 #pragma unroll
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnParams p, int ni
             float o = __fmul_rn(acc, s_rstd);
             o = __fmul_rn(o, nw);
             o = __fmul_rn(o, __fdiv_rn(zj, __fadd_rn(1.0f, g_exp(-zj))));
-            p.out[((int64_t)b * p.n + t) * val_dim + (int64_t)vh * hv + j] = o;
+            p.out[((int64_t)b * p.n_stride + t) * val_dim + (int64_t)vh * hv + j] = o;
         }
 #pragma unroll
         for (int i = 0; i < HK; i += 4) *reinterpret_cast<float4 *>(Srow + i) = make_float4(sj[i], sj[i + 1], sj[i + 2], sj[i + 3]);
@@ -130,6 +131,10 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnParams p, int ni
 }
 
 }  // namespace
+
+int cwk_gdn_scan_chunked(cwk_ctx *ctx, int B, int n_stride, int nchunks, int nh, int kv_group, const float *up, const float *gdec,
+                         const float *beta, const float *gate, const float *a_log, const float *dt_bias, const float *norm,
+                         float rms_eps, float *S, float *out);
 
 extern "C" int cwk_gdn_scan(cwk_ctx *ctx, int B, int n, int nh, int head_k, int head_v, int kv_group, const float *up,
                             const float *gdec, const float *beta, const float *gate, const float *a_log, const float *dt_bias,
@@ -141,9 +146,23 @@ extern "C" int cwk_gdn_scan(cwk_ctx *ctx, int B, int n, int nh, int head_k, int 
         return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "gdn_scan is built for key dims 64, 128 and value dims 32..128 (got %d, %d)", head_k, head_v);
     if (reinterpret_cast<uintptr_t>(S) & 15) return cwk_fail(ctx, CWK_ERR_ARGUMENT, "gdn_scan: the state must be 16-byte aligned");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
+    // A prompt (at least two chunks of 64 positions, head dims 128 x 128) goes through the chunk-parallel form; its last
+    // n % 64 positions, decode steps and every other shape through the position-serial kernel, which keeps the
+    // reference's summation order. cwk_ctx_force_mla_path(ctx, 0) keeps everything on the serial kernel.
+    int done = 0;
+    if (head_k == 128 && head_v == 128 && n >= 128 && ctx->force_mla_path != 0) {
+        const int nchunks = n / 64;
+        int s = cwk_gdn_scan_chunked(ctx, B, n, nchunks, nh, kv_group, up, gdec, beta, gate, a_log, dt_bias, norm, rms_eps, S, out);
+        if (s != CWK_OK) return s;
+        done = nchunks * 64;
+        if (done == n) return CWK_OK;
+    }
+    const int key_dim_h = (nh / kv_group) * head_k, val_dim_h = nh * head_v;
     GdnParams p;
-    p.up = up; p.gdec = gdec; p.beta = beta; p.gate = gate; p.a_log = a_log; p.dt_bias = dt_bias; p.norm = norm; p.S = S; p.out = out;
-    p.n = n; p.nh = nh; p.kv_group = kv_group; p.rms_eps = rms_eps;
+    p.up = up + (int64_t)done * (2 * key_dim_h + val_dim_h); p.gdec = gdec + (int64_t)done * nh; p.beta = beta + (int64_t)done * nh;
+    p.gate = gate + (int64_t)done * val_dim_h; p.a_log = a_log; p.dt_bias = dt_bias; p.norm = norm; p.S = S;
+    p.out = out + (int64_t)done * val_dim_h;
+    p.n = n - done; p.n_stride = n; p.nh = nh; p.kv_group = kv_group; p.rms_eps = rms_eps;
     const int nitems = B * nh;
     const int grid = std::min(nitems, 2 * ctx->sm_count);
     const size_t smem = (size_t)head_v * (head_k + 4) * sizeof(float);
