@@ -150,7 +150,7 @@ extern "C" int cwk_gdn_scan(cwk_ctx *ctx, int B, int n, int nh, int head_k, int 
     // n % 64 positions, decode steps and every other shape through the position-serial kernel, which keeps the
     // reference's summation order. cwk_ctx_force_mla_path(ctx, 0) keeps everything on the serial kernel.
     int done = 0;
-    if (head_k == 128 && head_v == 128 && n >= 128 && ctx->force_mla_path != 0) {
+    if (head_k == 128 && head_v == 128 && n >= 128 && ctx->force_mla_path != 0 && (reinterpret_cast<uintptr_t>(up) & 15) == 0) {
         const int nchunks = n / 64;
         int s = cwk_gdn_scan_chunked(ctx, B, n, nchunks, nh, kv_group, up, gdec, beta, gate, a_log, dt_bias, norm, rms_eps, S, out);
         if (s != CWK_OK) return s;

@@ -49,8 +49,8 @@ __device__ __forceinline__ float *ws_of(const GdnChunkParams &p, int b, int vh, 
 // ---- phase 1: grid (chunk, value head, slot), 256 threads
 __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnChunkParams p) {
     extern __shared__ float4 gsm4[];
-    float *sK = reinterpret_cast<float *>(gsm4), *sQ = sK + GC * GLD, *sV = sQ + GC * GLD;
-    float *sA = sV + GC * GLD, *sT = sA + GC * (GC + 1), *sG = sT + GC * (GC + 1), *sB = sG + GC;
+    float *sK = reinterpret_cast<float *>(gsm4), *sQ = sK + GC * GLD, *sV = sQ;      // V takes Q's place once M is formed
+    float *sA = sQ + GC * GLD, *sT = sA + GC * (GC + 1), *sG = sT + GC * (GC + 1), *sB = sG + GC;
     const int c = blockIdx.x, vh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
     const int kh = vh / p.kv_group;
     const int key_dim = (p.nh / p.kv_group) * GD, val_dim = p.nh * GD, qkv_dim = 2 * key_dim + val_dim;
@@ -60,7 +60,6 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnChunkParam
         const float *row = p.up + (pos0 + t) * qkv_dim;
         *reinterpret_cast<float4 *>(sQ + t * GLD + i4 * 4) = *reinterpret_cast<const float4 *>(row + (int64_t)kh * GD + i4 * 4);
         *reinterpret_cast<float4 *>(sK + t * GLD + i4 * 4) = *reinterpret_cast<const float4 *>(row + key_dim + (int64_t)kh * GD + i4 * 4);
-        *reinterpret_cast<float4 *>(sV + t * GLD + i4 * 4) = *reinterpret_cast<const float4 *>(row + 2 * key_dim + (int64_t)vh * GD + i4 * 4);
     }
     if (tid < GC) {
         const float ea = gc_exp(p.a_log[vh]);
@@ -100,21 +99,32 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnChunkParam
         wM[t * GC + s] = m;
     }
     __syncthreads();
-    // T = (I + A)^-1 by forward substitution, one thread per column
+    // T = (I + A)^-1 by forward substitution: one thread per column, the column in registers (both loops unrolled, so every
+    // index is a constant and the only chain is a row's sum). The other warps fetch V (times beta) into Q's place and
+    // scale K by beta e^G meanwhile.
     if (tid < GC) {
         const int col = tid;
+        float tc[GC];
+#pragma unroll
         for (int t = 0; t < GC; t++) {
             float v = (t == col) ? 1.f : 0.f;
-            for (int s = col; s < t; s++) v -= sA[t * (GC + 1) + s] * sT[s * (GC + 1) + col];      // T[s][col] = 0 for s < col
-            sT[t * (GC + 1) + col] = (t < col) ? 0.f : v;
+#pragma unroll
+            for (int s = 0; s < t; s++) v -= sA[t * (GC + 1) + s] * tc[s];       // tc[s] = 0 above the diagonal
+            tc[t] = (t < col) ? 0.f : v;
         }
-    }
-    // scale the rows the products below take: K by beta e^G, V by beta
-    __syncthreads();
-    for (int x = tid; x < GC * GD; x += 256) {
-        const int t = x / GD, i = x % GD;
-        sK[t * GLD + i] *= sB[t] * expf(sG[t]);
-        sV[t * GLD + i] *= sB[t];
+#pragma unroll
+        for (int t = 0; t < GC; t++) sT[t * (GC + 1) + col] = tc[t];
+    } else {
+        for (int x = tid - GC; x < GC * (GD / 4); x += 256 - GC) {
+            const int t = x / (GD / 4), i4 = x % (GD / 4);
+            const float bt = sB[t], be = bt * expf(sG[t]);
+            float4 v = *reinterpret_cast<const float4 *>(p.up + (pos0 + t) * qkv_dim + 2 * key_dim + (int64_t)vh * GD + i4 * 4);
+            v.x *= bt; v.y *= bt; v.z *= bt; v.w *= bt;
+            *reinterpret_cast<float4 *>(sV + t * GLD + i4 * 4) = v;
+            float4 k = *reinterpret_cast<float4 *>(sK + t * GLD + i4 * 4);
+            k.x *= be; k.y *= be; k.z *= be; k.w *= be;
+            *reinterpret_cast<float4 *>(sK + t * GLD + i4 * 4) = k;
+        }
     }
     __syncthreads();
     // W = T K', U~ = T V' (lower-triangular T): thread = one column, 32 rows
@@ -134,98 +144,141 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnChunkParam
     }
 }
 
-// ---- phase 2: grid (32-column block of the value dimension, value head, slot), 256 threads; chunks in order
-__global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnChunkParams p) {
+// ---- phase 2: grid (32-column block of the value dimension, value head, slot), 512 threads; chunks in order.
+// The chunk's operands arrive by 16-byte asynchronous copies issued as soon as their buffer is free: W, Q, U~ and G of
+// the next chunk after this chunk's first step, M after the second, K after the third; so a chunk's copies run under
+// the arithmetic of the chunk before.
+constexpr int GUL = GJ + 4;       // row stride of the U tiles (16-byte aligned rows)
+constexpr int GML = GC + 4;       // row stride of M
+constexpr int GT2 = 512;          // threads of a phase-2 block
+
+__device__ __forceinline__ void gc_cp16(float *dst, const float *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void gc_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+
+__global__ void __launch_bounds__(GT2) gdn_chunk_scan_kernel(const GdnChunkParams p) {
     extern __shared__ float4 gsm4[];
     float *sS = reinterpret_cast<float *>(gsm4);          // S0^T block [128 key][33]
     float *sW = sS + GD * (GJ + 1);                       // [64][132]
-    float *sK = sW + GC * GLD, *sQ = sK + GC * GLD;       // [64][132] each
-    float *sU = sQ + GC * GLD;                            // [64][33]: U~ block, then U, then U scaled for the state update
-    float *sM = sU + GC * (GJ + 1);                       // [64][65]
-    float *sG = sM + GC * (GC + 1);                       // [64] running log decay, then [64] e^G, [64] e^(G_last - G)
+    float *sQ = sW + GC * GLD, *sK = sQ + GC * GLD;       // [64][132] each
+    float *sU0 = sK + GC * GLD;                           // two [64][36] tiles: U~ of this chunk (then U, then U scaled) and of the next
+    float *sM = sU0 + 2 * GC * GUL;                       // [64][68]
+    float *sG = sM + GC * GML;                            // [64] running log decay, then [64] e^G, [64] e^(G_last - G)
     float *sE = sG + GC, *sF = sE + GC;
     const int jb = blockIdx.x, vh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
     const int kh = vh / p.kv_group;
     const int key_dim = (p.nh / p.kv_group) * GD, val_dim = p.nh * GD, qkv_dim = 2 * key_dim + val_dim;
     float *Sh = p.S + (((int64_t)b * p.nh + vh) * GD + (int64_t)jb * GJ) * GD;       // rows jb*32 .. +31 of the head's [value][key] state
-    for (int x = tid; x < GJ * GD; x += 256) {
+    auto issue_wqug = [&](int c) {
+        if (c < p.nchunks) {
+            const int64_t pos0 = (int64_t)b * p.n_stride + (int64_t)c * GC;
+            const float *w = ws_of(p, b, vh, c);
+            float *su = sU0 + (c & 1) * GC * GUL;
+            for (int x = tid; x < GC * (GD / 4); x += GT2) {
+                const int t = x / (GD / 4), i4 = x % (GD / 4);
+                gc_cp16(sW + t * GLD + i4 * 4, w + t * GD + i4 * 4);
+                gc_cp16(sQ + t * GLD + i4 * 4, p.up + (pos0 + t) * qkv_dim + (int64_t)kh * GD + i4 * 4);
+            }
+            for (int x = tid; x < GC * (GJ / 4); x += GT2)
+                gc_cp16(su + (x / (GJ / 4)) * GUL + (x % (GJ / 4)) * 4, w + GC * GD + (x / (GJ / 4)) * GD + jb * GJ + (x % (GJ / 4)) * 4);
+            if (tid < GC / 4) gc_cp16(sG + tid * 4, w + 2 * GC * GD + GC * GC + tid * 4);
+        }
+        gc_commit();
+    };
+    auto issue_m = [&](int c) {
+        if (c < p.nchunks) {
+            const float *wM = ws_of(p, b, vh, c) + 2 * GC * GD;
+            for (int x = tid; x < GC * (GC / 4); x += GT2) gc_cp16(sM + (x / (GC / 4)) * GML + (x % (GC / 4)) * 4, wM + (x / (GC / 4)) * GC + (x % (GC / 4)) * 4);
+        }
+        gc_commit();
+    };
+    auto issue_k = [&](int c) {
+        if (c < p.nchunks) {
+            const int64_t pos0 = (int64_t)b * p.n_stride + (int64_t)c * GC;
+            for (int x = tid; x < GC * (GD / 4); x += GT2) {
+                const int t = x / (GD / 4), i4 = x % (GD / 4);
+                gc_cp16(sK + t * GLD + i4 * 4, p.up + (pos0 + t) * qkv_dim + key_dim + (int64_t)kh * GD + i4 * 4);
+            }
+        }
+        gc_commit();
+    };
+    issue_wqug(0);
+    issue_m(0);
+    issue_k(0);
+    for (int x = tid; x < GJ * GD; x += GT2) {
         const int jj = x / GD, i = x % GD;
         sS[i * (GJ + 1) + jj] = Sh[(int64_t)jj * GD + i];
     }
-    const int jj = tid & 31, grp = tid >> 5;               // 8 groups of 32 lanes
+    const int jj = tid & 31, grp = tid >> 5;               // 16 warps: two per scheduler would leave shared-memory latency exposed
     for (int c = 0; c < p.nchunks; c++) {
         const int64_t pos0 = (int64_t)b * p.n_stride + (int64_t)c * GC;
-        const float *w = ws_of(p, b, vh, c);
-        const float *wW = w, *wU = w + GC * GD, *wM = wU + GC * GD, *wG = wM + GC * GC;
-        __syncthreads();                                   // the previous chunk is done with the tiles
-        for (int x = tid; x < GC * (GD / 4); x += 256) {
-            const int t = x / (GD / 4), i4 = x % (GD / 4);
-            const float *row = p.up + (pos0 + t) * qkv_dim;
-            *reinterpret_cast<float4 *>(sW + t * GLD + i4 * 4) = *reinterpret_cast<const float4 *>(wW + t * GD + i4 * 4);
-            *reinterpret_cast<float4 *>(sQ + t * GLD + i4 * 4) = *reinterpret_cast<const float4 *>(row + (int64_t)kh * GD + i4 * 4);
-            *reinterpret_cast<float4 *>(sK + t * GLD + i4 * 4) = *reinterpret_cast<const float4 *>(row + key_dim + (int64_t)kh * GD + i4 * 4);
-        }
-        for (int x = tid; x < GC * GJ; x += 256) sU[(x / GJ) * (GJ + 1) + (x % GJ)] = wU[(x / GJ) * GD + jb * GJ + (x % GJ)];
-        for (int x = tid; x < GC * GC; x += 256) sM[(x / GC) * (GC + 1) + (x % GC)] = wM[x];
+        float *sU = sU0 + (c & 1) * GC * GUL;
+        asm volatile("cp.async.wait_group 1;" ::: "memory");      // W, Q, U~, G and M of this chunk (K may still be on its way)
+        __syncthreads();
         if (tid < GC) {
-            const float gt = wG[tid], gl = wG[GC - 1];
-            sG[tid] = gt;
+            const float gt = sG[tid], gl = sG[GC - 1];
             sE[tid] = expf(gt);
             sF[tid] = expf(gl - gt);
         }
-        __syncthreads();
-        // U = U~ - W S0^T and the state's part of the output, e^G Q S0^T: rows t = grp + 8 e, column jj
-        float u[8], o[8];
+        // step 1: W S0^T and Q S0^T, rows t = grp + 16 e, column jj
+        float u[4], o[4];
 #pragma unroll
-        for (int e = 0; e < 8; e++) { u[e] = 0.f; o[e] = 0.f; }
+        for (int e = 0; e < 4; e++) { u[e] = 0.f; o[e] = 0.f; }
         for (int i = 0; i < GD; i += 4) {
             const float s0 = sS[(i + 0) * (GJ + 1) + jj], s1 = sS[(i + 1) * (GJ + 1) + jj], s2 = sS[(i + 2) * (GJ + 1) + jj],
                         s3 = sS[(i + 3) * (GJ + 1) + jj];
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const int t = grp + 8 * e;
+            for (int e = 0; e < 4; e++) {
+                const int t = grp + 16 * e;
                 const float4 wv = *reinterpret_cast<const float4 *>(sW + t * GLD + i), qv = *reinterpret_cast<const float4 *>(sQ + t * GLD + i);
                 u[e] += wv.x * s0 + wv.y * s1 + wv.z * s2 + wv.w * s3;
                 o[e] += qv.x * s0 + qv.y * s1 + qv.z * s2 + qv.w * s3;
             }
         }
-        __syncthreads();                                   // (everyone has read U~)
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            const int t = grp + 8 * e;
-            u[e] = sU[t * (GJ + 1) + jj] - u[e];
-            sU[t * (GJ + 1) + jj] = u[e];
+        for (int e = 0; e < 4; e++) {                      // U = U~ - W S0^T (a thread rewrites only what it alone reads)
+            const int t = grp + 16 * e;
+            u[e] = sU[t * GUL + jj] - u[e];
+            sU[t * GUL + jj] = u[e];
         }
-        __syncthreads();
-        // O = e^G (Q S0^T) + M U
+        __syncthreads();                                   // U complete; W, Q, G are free
+        issue_wqug(c + 1);
+        // step 2: O = e^G (Q S0^T) + M U
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            const int t = grp + 8 * e;
+        for (int e = 0; e < 4; e++) {
+            const int t = grp + 16 * e;
             float acc = sE[t] * o[e];
-            for (int s = 0; s <= t; s++) acc += sM[t * (GC + 1) + s] * sU[s * (GJ + 1) + jj];
+            for (int s = 0; s <= t; s++) acc += sM[t * GML + s] * sU[s * GUL + jj];
             p.out[(pos0 + t) * val_dim + (int64_t)vh * GD + jb * GJ + jj] = acc;
         }
-        __syncthreads();                                   // U has been read in its plain form
-        // S0^T <- e^(G_last) S0^T + K^T diag(e^(G_last - G)) U: scale U's rows once, then key rows i = grp * 16 .. + 15
-        for (int x = tid; x < GC * GJ; x += 256) sU[(x / GJ) * (GJ + 1) + (x % GJ)] *= sF[x / GJ];
-        __syncthreads();
-        float sacc[16];
         const float dl = sE[GC - 1];
+        __syncthreads();                                   // U has been read in its plain form; M is free
+        issue_m(c + 1);
+        // step 3: S0^T <- e^(G_last) S0^T + K^T diag(e^(G_last - G)) U: scale U's rows once, then key rows i = grp * 8 .. + 7
+        for (int x = tid; x < GC * GJ; x += GT2) sU[(x / GJ) * GUL + (x % GJ)] *= sF[x / GJ];
+        asm volatile("cp.async.wait_group 2;" ::: "memory");      // K of this chunk (the next chunk's two groups may be pending)
+        __syncthreads();
+        float sacc[8];
 #pragma unroll
-        for (int e = 0; e < 16; e++) sacc[e] = dl * sS[(grp * 16 + e) * (GJ + 1) + jj];
+        for (int e = 0; e < 8; e++) sacc[e] = dl * sS[(grp * 8 + e) * (GJ + 1) + jj];
+#pragma unroll 4
         for (int s = 0; s < GC; s++) {
-            const float us = sU[s * (GJ + 1) + jj];
+            const float us = sU[s * GUL + jj];
 #pragma unroll
-            for (int e4 = 0; e4 < 4; e4++) {
-                const float4 kv = *reinterpret_cast<const float4 *>(sK + s * GLD + grp * 16 + e4 * 4);
+            for (int e4 = 0; e4 < 2; e4++) {
+                const float4 kv = *reinterpret_cast<const float4 *>(sK + s * GLD + grp * 8 + e4 * 4);
                 sacc[e4 * 4 + 0] += kv.x * us; sacc[e4 * 4 + 1] += kv.y * us; sacc[e4 * 4 + 2] += kv.z * us; sacc[e4 * 4 + 3] += kv.w * us;
             }
         }
 #pragma unroll
-        for (int e = 0; e < 16; e++) sS[(grp * 16 + e) * (GJ + 1) + jj] = sacc[e];      // (a thread rewrites only what it read)
+        for (int e = 0; e < 8; e++) sS[(grp * 8 + e) * (GJ + 1) + jj] = sacc[e];      // (a thread rewrites only what it read)
+        __syncthreads();                                   // K is free; the new state is in place
+        issue_k(c + 1);
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    for (int x = tid; x < GJ * GD; x += 256) {
+    for (int x = tid; x < GJ * GD; x += GT2) {
         const int j2 = x / GD, i = x % GD;
         Sh[(int64_t)j2 * GD + i] = sS[i * (GJ + 1) + j2];
     }
@@ -250,8 +303,8 @@ __global__ void __launch_bounds__(128) gdn_chunk_norm_kernel(const GdnChunkParam
     (void)npos;
 }
 
-constexpr size_t PREP_SMEM = (size_t)(3 * GC * GLD + 2 * GC * (GC + 1) + 2 * GC) * sizeof(float);
-constexpr size_t SCAN_SMEM = (size_t)(GD * (GJ + 1) + 3 * GC * GLD + GC * (GJ + 1) + GC * (GC + 1) + 3 * GC) * sizeof(float);
+constexpr size_t PREP_SMEM = (size_t)(2 * GC * GLD + 2 * GC * (GC + 1) + 2 * GC) * sizeof(float);
+constexpr size_t SCAN_SMEM = (size_t)(GD * (GJ + 1) + 3 * GC * GLD + 2 * GC * GUL + GC * GML + 3 * GC) * sizeof(float);
 
 }  // namespace
 
@@ -275,7 +328,7 @@ int cwk_gdn_scan_chunked(cwk_ctx *ctx, int B, int n_stride, int nchunks, int nh,
     CWK_LAUNCH_CHECK(ctx, "gdn_chunk_prep_kernel");
     {
         CwkKernelTimer timer(ctx);
-        gdn_chunk_scan_kernel<<<dim3(GD / GJ, nh, B), 256, SCAN_SMEM, ctx->stream>>>(p);
+        gdn_chunk_scan_kernel<<<dim3(GD / GJ, nh, B), GT2, SCAN_SMEM, ctx->stream>>>(p);
         CWK_LAUNCH_CHECK(ctx, "gdn_chunk_scan_kernel");
     }
     gdn_chunk_norm_kernel<<<dim3(nchunks * GC, nh, B), 128, 0, ctx->stream>>>(p, nchunks * GC);
