@@ -406,7 +406,12 @@ CWK_API int cwk_kda_step(cwk_ctx *ctx, int B, int nh, int hd, float lower, float
  *   a_log, dt_bias f32 [nh], norm f32 [head_v]
  *   S     f32 [B][nh][head_v][head_k]  the layer's state, updated
  *   out   f32 [B][n][val_dim]    the input of out_proj
- * head_k 64 or 128, head_v a multiple of 32 up to 128. Positions are processed in order (a scan). */
+ * head_k 64 or 128, head_v a multiple of 32 up to 128. A decode step, a short call and a call's last n % 64
+ * positions run position by position, in the reference's summation order. A prompt (n >= 128, head dims
+ * 128 x 128, `up` 16-byte aligned) runs chunk-parallel, 64 positions at a time: the same recurrence with its f32
+ * sums in another order, so those results agree with the reference to rounding (about 1e-5 relative), not bit
+ * for bit; its workspace inside the context is 82 KB per (slot, head, chunk). cwk_ctx_force_mla_path(ctx, 0)
+ * keeps every call on the position-serial kernel. */
 CWK_API int cwk_gdn_scan(cwk_ctx *ctx, int B, int n, int nh, int head_k, int head_v, int kv_group, const float *up,
                          const float *gdec, const float *beta, const float *gate, const float *a_log, const float *dt_bias,
                          const float *norm, float rms_eps, float *S, float *out);
