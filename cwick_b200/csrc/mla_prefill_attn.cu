@@ -55,8 +55,8 @@ struct PaCfg {
     static constexpr int OFF_C = PA_OFF_K + PA_KST * K_BYTES;
     static constexpr int OFF_P = OFF_C + CST * PA_C_BYTES;
     static constexpr int OFF_BAR = OFF_P + 2 * PA_P_BYTES;
-    static constexpr int OFF_X = OFF_BAR + 512;        // [2][128] f32 maxima, [2][128] f32 sums exchanged between the two softmax groups; 8 item numbers
-    static constexpr int SMEM = OFF_X + 2048 + 64 + 1024;
+    static constexpr int OFF_X = OFF_BAR + 512;        // [4][128] f32 maxima, [4][128] f32 sums exchanged between the softmax groups; 8 item numbers
+    static constexpr int SMEM = OFF_X + 4096 + 64 + 1024;
     static_assert(SMEM <= 232448, "shared-memory budget");
     static_assert(384 + DQK / 2 <= 512, "tensor-memory budget");
 };
@@ -102,7 +102,7 @@ __device__ __forceinline__ AttnItem attn_item(int w, const AttnParams &p, int nq
 // Persistent: one block per SM takes items from a global counter until none is left. The first TMA operation of a
 // block waits several thousand cycles for its tensor map, tensor memory is allocated once, and the loads of the next
 // item run under the epilogue of this one.
-template <int NWG, class CFG, bool GQA>      // NWG softmax warp groups: 2 = fast form, 1 = exact form
+template <int NWG, class CFG, bool GQA>      // NWG softmax warp groups: 2 or 4 = fast form (a row's 64 keys shared by 2 or 4 threads), 1 = exact form
 __global__ void __launch_bounds__(128 + 128 * NWG, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_c, const AttnParams p) {
     constexpr int PA_DQK = CFG::DQK, PA_K_BYTES = CFG::K_BYTES, PA_CST = CFG::CST, PA_OFF_C = CFG::OFF_C, PA_OFF_P = CFG::OFF_P,
@@ -114,8 +114,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const uint32_t bar0 = base + PA_OFF_BAR;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(sm + PA_OFF_BAR + 8 * PB_COUNT + 8);
-    volatile int *s_item = reinterpret_cast<volatile int *>(sm + PA_OFF_X + 2048);      // ring of 8 item numbers
-    float *s_m = reinterpret_cast<float *>(sm + PA_OFF_X), *s_l = s_m + 256;              // [2][128] each
+    volatile int *s_item = reinterpret_cast<volatile int *>(sm + PA_OFF_X + 4096);      // ring of 8 item numbers
+    float *s_m = reinterpret_cast<float *>(sm + PA_OFF_X), *s_l = s_m + 512;              // [4][128] each
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (NWG == 1 && p.counter[2] == 0) return;                   // the repair pass: the fast form raised no flag
@@ -290,11 +290,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 // The query tile is the A operand of every score MMA of the item; it is kept in tensor memory (row =
                 // lane, two consecutive bf16 per 32-bit column), so that those MMAs read only the keys from shared
                 // memory. A thread copies its row's share: 96 columns split between the groups.
-                constexpr int QW = (PA_DQK / 2) / NWG;               // 32-bit words per thread
+                constexpr int QG = (NWG == 4 && ((PA_DQK / 2) / 4) % 16 != 0) ? 2 : NWG;      // groups that copy (16-word stores)
+                constexpr int QW = (PA_DQK / 2) / QG;                // 32-bit words per copying thread
                 const int t = q0 + row;
                 const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((int64_t)t * p.nh + h) * PA_DQK) + wg * (QW / 4);
 #pragma unroll
-                for (int c = 0; c < QW / 16; c++) {
+                for (int c = 0; c < (wg < QG ? QW / 16 : 0); c++) {
                     uint32_t wv[16];
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -333,13 +334,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                         mt = fmaxf(mt, s[j]);
                     }
                 }
-                if (NWG == 2) {
+                if (NWG >= 2) {
                     if (i == 0) {                                    // reference exponent of the row: its largest score of the first tile
                         s_m[wg * 128 + row] = mt;
                         mbar_arrive(bar(PB_XM));
                         ok = mbar_wait(bar(PB_XM), (uint32_t)(k & 1), p.err, 1026);
                         if (!ok) break;
                         m = fmaxf(s_m[row], s_m[128 + row]);         // key 0 is visible to every row: finite
+                        if (NWG == 4) m = fmaxf(m, fmaxf(s_m[256 + row], s_m[384 + row]));
                     } else if (mt > m + PA_RANGE) {
                         p.flags[w] = 1;                              // out of the range this form covers: the exact form redoes the item
                         atomicAdd(p.counter + 2, 1);
@@ -395,19 +397,21 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             ok = mbar_wait(bar(PB_ODONE), (uint32_t)(k & 1), p.err, 1024);
             if (!ok) break;
             tc_fence_after();
-            if (NWG == 2) {                                          // the row's sum is the two groups' sums
+            if (NWG >= 2) {                                          // the row's sum is the groups' sums
                 s_l[wg * 128 + row] = l;
                 mbar_arrive(bar(PB_XL));
                 ok = mbar_wait(bar(PB_XL), (uint32_t)(k & 1), p.err, 1027);
                 if (!ok) break;
                 l = s_l[row] + s_l[128 + row];
+                if (NWG == 4) l += s_l[256 + row] + s_l[384 + row];
             }
             const float inv = l > 0.f ? 1.f / l : 0.f;
             uint8_t *stg = sm + PA_OFF_P + (warp - 4) * 4096;         // 4 KB per warp: [32 rows][128 B], in the P buffers (idle: the item's value MMAs are done, and the next item's P comes from these threads)
             const int t0w = q0 + q4 * 32;
-            constexpr int NCH = PA_DV / 64 / NWG;                     // 64-column chunks per thread
+            constexpr int EG = NWG > 2 ? 2 : NWG;                     // groups that write out (the staging tiles are the two P buffers: eight warps)
+            constexpr int NCH = PA_DV / 64 / EG;                      // 64-column chunks per writing thread
 #pragma unroll 1
-            for (int c = 0; c < NCH; c++) {
+            for (int c = 0; c < (wg < EG ? NCH : 0); c++) {
                 const int col = (wg * NCH + c) * 64;
                 uint32_t o[64];
                 TMEM_LD16(o, 0, tlane + PA_COL_O + col);
@@ -638,7 +642,7 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
     if (!attr_set[ctx->device & 15]) {
         CWK_CUDA(ctx, cudaFuncSetAttribute(kexp_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KX_SMEM));
         CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<1, PaMla, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PaMla::SMEM));
-        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<2, PaMla, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PaMla::SMEM));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(prefill_attn_kernel<4, PaMla, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PaMla::SMEM));
         attr_set[ctx->device & 15] = true;
     }
     {
@@ -664,8 +668,8 @@ int cwk_mla_prefill_attn_tc(cwk_ctx *ctx, const void *Q, const void *cache, cons
         const int grid = std::min(total, ctx->sm_count);
         if (!exact_only) {
             CwkKernelTimer timer(ctx);
-            prefill_attn_kernel<2, PaMla, false><<<grid, 384, PaMla::SMEM, ctx->stream>>>(tm_k, tm_c, ap);
-            CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<2>");
+            prefill_attn_kernel<4, PaMla, false><<<grid, 640, PaMla::SMEM, ctx->stream>>>(tm_k, tm_c, ap);
+            CWK_LAUNCH_CHECK(ctx, "prefill_attn_kernel<4>");
         }
         // the repair pass: items whose flag is clear are skipped
         prefill_attn_kernel<1, PaMla, false><<<grid, 256, PaMla::SMEM, ctx->stream>>>(tm_k, tm_c, ap);

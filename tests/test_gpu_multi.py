@@ -111,6 +111,27 @@ def test_peer_exchange_entry_point_on_one_gpu():
     x.close()
 
 
+def test_peer_exchange_with_general_dimensions_on_one_gpu():
+    """16 heads of a 96-wide latent + 32 rope columns: the exchange kernel's blocks cover 128 columns each, so the
+    last (only) block of a head is ragged; the decode itself runs on the generic kernel."""
+    from cwick_b200 import dist as cd
+    from cwick_b200.ops import Attn
+    attn = Attn(0)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    nh, l, r, T = 16, 96, 32, 700
+    sc = 1.0 / math.sqrt(l)
+    q = torch.randn(nh, l + r, device="cuda", generator=g).to(torch.bfloat16)
+    cache = torch.randn(T, l + r, device="cuda", generator=g).to(torch.bfloat16)
+    x = cd.KvSplitExchange(attn, nh, l)
+    lens = torch.tensor([T], dtype=torch.int32, device="cuda")
+    want = attn.mla_decode_dims(q[None], cache[None], lens, l, r, sc, max_kv_len=T)[0]
+    for _ in range(2):
+        got = x.decode(q, cache, T, r, sc)
+        attn.ctx.sync()
+        assert float((got.float() - want.float()).abs().max()) <= 4e-3
+    x.close()
+
+
 def test_a_peer_that_never_publishes_is_reported_and_the_context_stays_usable():
     """Failure detection without a fault: rank 0 of a pretended world of 2 runs its step against a second local
     window standing in for the peer's. Nothing ever publishes the peer's slot of the own window, so the merge
