@@ -281,19 +281,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             const AttnItem it = attn_item(w, p, nq);
             const int q0 = it.q0, h = it.h, half = it.half, nt = it.nt;
             const int64_t tq = p.pos0 + q0 + row;                    // this row's position: keys 0..tq are visible
-            if (k > 0) {                                             // the score MMAs of the previous item are done with its query tile
-                ok = mbar_wait(bar(PB_QEMPTY), (uint32_t)((k - 1) & 1), p.err, 1025);
-                if (!ok) break;
-                tc_fence_after();
-            }
-            {
-                // The query tile is the A operand of every score MMA of the item; it is kept in tensor memory (row =
-                // lane, two consecutive bf16 per 32-bit column), so that those MMAs read only the keys from shared
-                // memory. A thread copies its row's share: 96 columns split between the groups.
+            // The query tile is the A operand of every score MMA of the item; it is kept in tensor memory (row = lane, two
+            // consecutive bf16 per 32-bit column), so that those MMAs read only the keys from shared memory. A thread
+            // copies its row's share: DQK / 2 columns split between the copying groups. The tile of item k + 1 is copied
+            // BEFORE the epilogue of item k (below), so that the next item's first scores are computed under that epilogue.
+            auto load_query = [&](int q0_, int h_) {
                 constexpr int QG = (NWG == 4 && ((PA_DQK / 2) / 4) % 16 != 0) ? 2 : NWG;      // groups that copy (16-word stores)
                 constexpr int QW = (PA_DQK / 2) / QG;                // 32-bit words per copying thread
-                const int t = q0 + row;
-                const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((int64_t)t * p.nh + h) * PA_DQK) + wg * (QW / 4);
+                const int t = q0_ + row;
+                const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((int64_t)t * p.nh + h_) * PA_DQK) + wg * (QW / 4);
 #pragma unroll
                 for (int c = 0; c < (wg < QG ? QW / 16 : 0); c++) {
                     uint32_t wv[16];
@@ -307,7 +303,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 mbar_arrive(bar(PB_QFULL));
-            }
+            };
+            if (k == 0) load_query(q0, h);
             float m = 0.f, l = 0.f;
             for (int i = 0; i < nt && ok; i++, tc++) {
                 const int sb = tc & 1, su = tc >> 1;             // P buffer of this tile
@@ -393,6 +390,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 mbar_arrive(bar(PB_PFULL + sb));
             }
             if (!ok) break;
+            {
+                // the next item's query tile: the score MMAs of this item are done with theirs (they precede its last value MMAs)
+                int wn;
+                ok = next_item(k + 1, wn);
+                if (!ok) break;
+                if (wn >= 0) {
+                    ok = mbar_wait(bar(PB_QEMPTY), (uint32_t)(k & 1), p.err, 1025);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const AttnItem nx = attn_item(wn, p, nq);
+                    load_query(nx.q0, nx.h);
+                }
+            }
             // ---- epilogue of the item: O / l -> bf16 -> out[t][h][half * 256 ..], full lines through a staging tile
             ok = mbar_wait(bar(PB_ODONE), (uint32_t)(k & 1), p.err, 1024);
             if (!ok) break;
