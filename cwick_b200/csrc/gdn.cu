@@ -14,7 +14,7 @@
 // through double.
 #include <algorithm>
 
-#include "cwk_common.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -34,56 +34,46 @@ struct GdnParams {
     float rms_eps;
 };
 
-// Row stride of the staged state tile in shared memory: 4 floats of padding make a thread's 16-byte reads of its own
-// row conflict-free (eight lanes of a quarter warp then cover all 32 banks).
-template <int HK> __host__ __device__ constexpr int gdn_ld() { return HK + 4; }
+constexpr int GDN_ERR_TILE = 0x6d01;
 
-template <int HK>
-__device__ __forceinline__ void gdn_prefetch(const GdnParams &p, int item, int hv, float *s_tile, int j, int nthreads) {
-    const int vh = item % p.nh, b = item / p.nh;
-    const float *src = p.S + (((int64_t)b * p.nh + vh) * hv) * HK;
-    const uint32_t tb = (uint32_t)__cvta_generic_to_shared(s_tile);
-    for (int ch = j; ch < hv * (HK / 4); ch += nthreads) {            // 16-byte chunks, coalesced
-        const int row = ch / (HK / 4), c4 = ch % (HK / 4);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tb + (uint32_t)(row * gdn_ld<HK>() + c4 * 4) * 4u), "l"(src + (int64_t)ch * 4) : "memory");
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+// Byte offset, inside an item's state tile in shared memory, of the 16-byte piece `m` (key entries 4m .. 4m + 3) of value
+// row `j`. The tile arrives by one TMA copy as hk / 32 column blocks of [hv rows][32 floats] under the 128-byte swizzle:
+// a row of a block is 128 bytes, its 16-byte pieces permuted by the row's low three bits -- which also makes a
+// thread-per-row access conflict-free (the eight lanes of a quarter warp cover all 32 banks).
+__device__ __forceinline__ uint32_t gdn_piece(int j, int m, int hv) {
+    return (uint32_t)((m >> 3) * hv * 128 + j * 128 + (((m & 7) ^ (j & 7)) << 4));
 }
 
-// Persistent blocks: block g works on items g, g + G, ... (item = slot * nh + value head). While an item's positions
-// are scanned with the state in registers, the next item's state tile streams into shared memory.
+// Persistent blocks: block g works on items g, g + G, ... (item = slot * nh + value head). An item's [hv][hk] state
+// comes into shared memory by one TMA copy, is scanned there over the call's positions (a thread owns one value row:
+// no other thread touches it), and goes back by one TMA copy. Few registers and one tile per block leave room for
+// three blocks per SM, which is what overlaps one item's copies with another's arithmetic.
 template <int HK>
-__global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnParams p, int nitems) {
-    extern __shared__ float4 s_dyn4[];
-    float *s_tile = reinterpret_cast<float *>(s_dyn4);                // [hv][HK + 4], the NEXT item's state
-    __shared__ float s_q[HK], s_k[HK], s_tmp[128];
+__global__ void __launch_bounds__(128) gdn_scan_kernel(const __grid_constant__ CUtensorMap tm_s, const GdnParams p, int nitems, int *err) {
+    extern __shared__ uint8_t s_dyn[];
+    __shared__ __align__(16) float s_q[HK], s_k[HK], s_tmp[128];
     __shared__ float s_rstd;
+    __shared__ __align__(8) uint64_t s_bar;
     const int j = threadIdx.x, hv = blockDim.x;
     const int key_dim = (p.nh / p.kv_group) * HK, val_dim = p.nh * hv, qkv_dim = 2 * key_dim + val_dim;
-    const bool single = nitems <= (int)gridDim.x;                     // one item per block: nothing to overlap with
     const float nw = p.norm[j];
-    if (!single) gdn_prefetch<HK>(p, blockIdx.x, hv, s_tile, j, hv);
+    const uint32_t bar = smem_u32(&s_bar);
+    const uint32_t tile = (smem_u32(s_dyn) + 1023u) & ~1023u;               // the swizzle pattern repeats every 1024 bytes
+    uint8_t *tile_g = s_dyn + (tile - smem_u32(s_dyn));
+    const int copier = hv > 32 ? 32 : 0;                                    // the thread that issues the tile copies
+    if (j == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    uint32_t phase = 0;
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
         const int vh = item % p.nh, b = item / p.nh;
         const int kh = vh / p.kv_group;
-        float *Srow = p.S + ((((int64_t)b * p.nh + vh) * hv) + j) * HK;
-        float sj[HK];
-        if (single) {
-#pragma unroll
-            for (int i = 0; i < HK; i += 4) {
-                const float4 v = *reinterpret_cast<const float4 *>(Srow + i);
-                sj[i] = v.x; sj[i + 1] = v.y; sj[i + 2] = v.z; sj[i + 3] = v.w;
-            }
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncthreads();
-#pragma unroll
-            for (int i = 0; i < HK; i += 4) {
-                const float4 v = *reinterpret_cast<const float4 *>(s_tile + j * gdn_ld<HK>() + i);
-                sj[i] = v.x; sj[i + 1] = v.y; sj[i + 2] = v.z; sj[i + 3] = v.w;
-            }
-            __syncthreads();
-            if (item + (int)gridDim.x < nitems) gdn_prefetch<HK>(p, item + gridDim.x, hv, s_tile, j, hv);
+        if (j == copier) {
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the last write-back has left the tile
+            mbar_expect_tx(bar, (uint32_t)(hv * HK * 4));
+            tma_load_3d(tile, &tm_s, 0, item * hv, 0, bar);
         }
         const float ea = g_exp(p.a_log[vh]), dtb = p.dt_bias[vh];
         for (int t = 0; t < p.n; t++) {
@@ -98,36 +88,69 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const GdnParams p, int ni
             const float sp = x > 20.0f ? x : (float)log1p((double)g_exp(x));
             const float decay = g_exp(__fmul_rn(-ea, sp));
             const float bet = __fdiv_rn(1.0f, __fadd_rn(1.0f, g_exp(-p.beta[((int64_t)b * p.n_stride + t) * p.nh + vh])));
+            const float silu = __fdiv_rn(zj, __fadd_rn(1.0f, g_exp(-zj)));
+            if (t == 0) {                                                   // the tile, under the loads and exps above
+                mbar_wait(bar, phase, err, GDN_ERR_TILE);                   // on giving up: carries on, the host reports the call as failed
+                phase ^= 1;
+            }
             __syncthreads();
             float dot = 0.f;
-#pragma unroll
-            for (int i = 0; i < HK; i++) {
-                sj[i] = __fmul_rn(sj[i], decay);
-                dot = __fadd_rn(dot, __fmul_rn(sj[i], s_k[i]));
+#pragma unroll 8
+            for (int m = 0; m < HK / 4; m++) {
+                const float4 s4 = *reinterpret_cast<const float4 *>(tile_g + gdn_piece(j, m, hv));
+                const float4 k4 = *reinterpret_cast<const float4 *>(s_k + 4 * m);
+                dot = __fadd_rn(dot, __fmul_rn(__fmul_rn(s4.x, decay), k4.x));
+                dot = __fadd_rn(dot, __fmul_rn(__fmul_rn(s4.y, decay), k4.y));
+                dot = __fadd_rn(dot, __fmul_rn(__fmul_rn(s4.z, decay), k4.z));
+                dot = __fadd_rn(dot, __fmul_rn(__fmul_rn(s4.w, decay), k4.w));
             }
             const float delta = __fmul_rn(bet, __fsub_rn(vj, dot));
             float acc = 0.f;
-#pragma unroll
-            for (int i = 0; i < HK; i++) {
-                sj[i] = __fadd_rn(sj[i], __fmul_rn(s_k[i], delta));
-                acc = __fadd_rn(acc, __fmul_rn(sj[i], s_q[i]));
+#pragma unroll 8
+            for (int m = 0; m < HK / 4; m++) {
+                float4 *sp4 = reinterpret_cast<float4 *>(tile_g + gdn_piece(j, m, hv));
+                float4 s4 = *sp4;
+                const float4 k4 = *reinterpret_cast<const float4 *>(s_k + 4 * m);
+                const float4 q4 = *reinterpret_cast<const float4 *>(s_q + 4 * m);
+                s4.x = __fadd_rn(__fmul_rn(s4.x, decay), __fmul_rn(k4.x, delta));
+                s4.y = __fadd_rn(__fmul_rn(s4.y, decay), __fmul_rn(k4.y, delta));
+                s4.z = __fadd_rn(__fmul_rn(s4.z, decay), __fmul_rn(k4.z, delta));
+                s4.w = __fadd_rn(__fmul_rn(s4.w, decay), __fmul_rn(k4.w, delta));
+                acc = __fadd_rn(acc, __fmul_rn(s4.x, q4.x));
+                acc = __fadd_rn(acc, __fmul_rn(s4.y, q4.y));
+                acc = __fadd_rn(acc, __fmul_rn(s4.z, q4.z));
+                acc = __fadd_rn(acc, __fmul_rn(s4.w, q4.w));
+                *sp4 = s4;
             }
+            const bool last = t == p.n - 1;
+            if (last) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the row, visible to the copy engine
             s_tmp[j] = acc;
             __syncthreads();
+            if (last && j == copier) {                                      // the tile goes back under the output's arithmetic
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&tm_s), "r"(0),
+                             "r"(item * hv), "r"(0), "r"(tile)
+                             : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
             if (j == 0) {
                 float ss = 0.f;
-                for (int r = 0; r < hv; r++) ss = __fadd_rn(ss, __fmul_rn(s_tmp[r], s_tmp[r]));
+                for (int r = 0; r < hv; r += 4) {
+                    const float4 a4 = *reinterpret_cast<const float4 *>(s_tmp + r);
+                    ss = __fadd_rn(ss, __fmul_rn(a4.x, a4.x));
+                    ss = __fadd_rn(ss, __fmul_rn(a4.y, a4.y));
+                    ss = __fadd_rn(ss, __fmul_rn(a4.z, a4.z));
+                    ss = __fadd_rn(ss, __fmul_rn(a4.w, a4.w));
+                }
                 s_rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hv), p.rms_eps)));
             }
             __syncthreads();
             float o = __fmul_rn(acc, s_rstd);
             o = __fmul_rn(o, nw);
-            o = __fmul_rn(o, __fdiv_rn(zj, __fadd_rn(1.0f, g_exp(-zj))));
+            o = __fmul_rn(o, silu);
             p.out[((int64_t)b * p.n_stride + t) * val_dim + (int64_t)vh * hv + j] = o;
         }
-#pragma unroll
-        for (int i = 0; i < HK; i += 4) *reinterpret_cast<float4 *>(Srow + i) = make_float4(sj[i], sj[i + 1], sj[i + 2], sj[i + 3]);
     }
+    if (j == copier) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 }  // namespace
@@ -164,17 +187,37 @@ extern "C" int cwk_gdn_scan(cwk_ctx *ctx, int B, int n, int nh, int head_k, int 
     p.out = out + (int64_t)done * val_dim_h;
     p.n = n - done; p.n_stride = n; p.nh = nh; p.kv_group = kv_group; p.rms_eps = rms_eps;
     const int nitems = B * nh;
-    const int grid = std::min(nitems, 2 * ctx->sm_count);
-    const size_t smem = (size_t)head_v * (head_k + 4) * sizeof(float);
-    static bool attr_set[16] = {false};
-    if (!attr_set[ctx->device & 15]) {
-        CWK_CUDA(ctx, cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 132 * 4));
-        CWK_CUDA(ctx, cudaFuncSetAttribute(gdn_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 68 * 4));
-        attr_set[ctx->device & 15] = true;
+    if ((int64_t)nitems * head_v > 0x7fffffffLL) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "gdn_scan: more than 2^31 state rows");
+    const size_t smem = (size_t)head_v * head_k * sizeof(float) + 1024;   // + slack to align the tile to the swizzle period
+    static int per_sm[16][2] = {{0}};                                   // resident blocks per SM, by device and key dim
+    int &resident = per_sm[ctx->device & 15][head_k == 128];
+    if (!resident) {
+        CWK_CUDA(ctx, cudaFuncSetAttribute(gdn_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 128 * 4 + 1024));
+        CWK_CUDA(ctx, cudaFuncSetAttribute(gdn_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 64 * 4 + 1024));
+        int nb = 0;
+        if (head_k == 128) CWK_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, gdn_scan_kernel<128>, 128, 128 * 128 * 4 + 1024));
+        else CWK_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, gdn_scan_kernel<64>, 128, 128 * 64 * 4 + 1024));
+        resident = std::max(nb, 1);
+    }
+    const int grid = std::min(nitems, resident * ctx->sm_count);
+    int es = cwk_ensure_err_word(ctx);
+    if (es != CWK_OK) return es;
+    // The state as [32 floats][rows = slot, head, value row][hk / 32 column blocks]; one box is one item's whole tile.
+    CwkEncodeTiledFn enc = cwk_encode_tiled_fn();
+    if (!enc) return cwk_fail(ctx, CWK_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled not available");
+    CUtensorMap tm_s;
+    {
+        cuuint64_t dims[3] = {32, (cuuint64_t)nitems * head_v, (cuuint64_t)(head_k / 32)};
+        cuuint64_t strides[2] = {(cuuint64_t)head_k * 4, 128};
+        cuuint32_t box[3] = {32, (cuuint32_t)head_v, (cuuint32_t)(head_k / 32)};
+        cuuint32_t es3[3] = {1, 1, 1};
+        CUresult r = enc(&tm_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, S, dims, strides, box, es3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cwk_fail(ctx, CWK_ERR_CUDA, "cuTensorMapEncodeTiled(state) failed: %d", (int)r);
     }
     CwkKernelTimer timer(ctx);
-    if (head_k == 128) gdn_scan_kernel<128><<<grid, head_v, smem, ctx->stream>>>(p, nitems);
-    else gdn_scan_kernel<64><<<grid, head_v, smem, ctx->stream>>>(p, nitems);
+    if (head_k == 128) gdn_scan_kernel<128><<<grid, head_v, smem, ctx->stream>>>(tm_s, p, nitems, ctx->dev_err);
+    else gdn_scan_kernel<64><<<grid, head_v, smem, ctx->stream>>>(tm_s, p, nitems, ctx->dev_err);
     CWK_LAUNCH_CHECK(ctx, "gdn_scan_kernel");
     return CWK_OK;
 }
