@@ -44,6 +44,30 @@ __device__ __forceinline__ uint32_t gdn_piece(int j, int m, int hv) {
     return (uint32_t)((m >> 3) * hv * 128 + j * 128 + (((m & 7) ^ (j & 7)) << 4));
 }
 
+// One position's inputs of one item, as thread j holds them: its value row's v and gate entry, the head's decay and beta
+// logits, and the entries j, j + hv, ... of the key head's q and k (the block shares those through shared memory).
+template <int HK> struct GdnPos {
+    static constexpr int PER = HK / 32;                                     // hv >= 32
+    float q[PER], k[PER], v, z, gdec, beta, a_log, dt_bias;
+};
+template <int HK> __device__ __forceinline__ void gdn_fetch(const GdnParams &p, int item, int t, int j, int hv, GdnPos<HK> &r) {
+    const int vh = item % p.nh, b = item / p.nh, kh = vh / p.kv_group;
+    const int key_dim = (p.nh / p.kv_group) * HK, val_dim = p.nh * hv;
+    const float *row = p.up + ((int64_t)b * p.n_stride + t) * (2 * key_dim + val_dim);
+#pragma unroll
+    for (int u = 0; u < GdnPos<HK>::PER; u++)
+        if (j + u * hv < HK) {
+            r.q[u] = __ldg(row + (int64_t)kh * HK + j + u * hv);
+            r.k[u] = __ldg(row + key_dim + (int64_t)kh * HK + j + u * hv);
+        }
+    r.v = __ldg(row + 2 * key_dim + (int64_t)vh * hv + j);
+    r.z = __ldg(p.gate + ((int64_t)b * p.n_stride + t) * val_dim + (int64_t)vh * hv + j);
+    r.gdec = __ldg(p.gdec + ((int64_t)b * p.n_stride + t) * p.nh + vh);
+    r.beta = __ldg(p.beta + ((int64_t)b * p.n_stride + t) * p.nh + vh);
+    r.a_log = __ldg(p.a_log + vh);
+    r.dt_bias = __ldg(p.dt_bias + vh);
+}
+
 // Persistent blocks: block g works on items g, g + G, ... (item = slot * nh + value head). An item's [hv][hk] state
 // comes into shared memory by one TMA copy, is scanned there over the call's positions (a thread owns one value row:
 // no other thread touches it), and goes back by one TMA copy. Few registers and one tile per block leave room for
@@ -55,7 +79,7 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const __grid_constant__ C
     __shared__ float s_rstd;
     __shared__ __align__(8) uint64_t s_bar;
     const int j = threadIdx.x, hv = blockDim.x;
-    const int key_dim = (p.nh / p.kv_group) * HK, val_dim = p.nh * hv, qkv_dim = 2 * key_dim + val_dim;
+    const int val_dim = p.nh * hv;
     const float nw = p.norm[j];
     const uint32_t bar = smem_u32(&s_bar);
     const uint32_t tile = (smem_u32(s_dyn) + 1023u) & ~1023u;               // the swizzle pattern repeats every 1024 bytes
@@ -67,27 +91,31 @@ __global__ void __launch_bounds__(128) gdn_scan_kernel(const __grid_constant__ C
     }
     __syncthreads();
     uint32_t phase = 0;
+    GdnPos<HK> nxt;
+    if ((int)blockIdx.x < nitems) gdn_fetch<HK>(p, blockIdx.x, 0, j, hv, nxt);
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
         const int vh = item % p.nh, b = item / p.nh;
-        const int kh = vh / p.kv_group;
         if (j == copier) {
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the last write-back has left the tile
             mbar_expect_tx(bar, (uint32_t)(hv * HK * 4));
             tma_load_3d(tile, &tm_s, 0, item * hv, 0, bar);
         }
-        const float ea = g_exp(p.a_log[vh]), dtb = p.dt_bias[vh];
         for (int t = 0; t < p.n; t++) {
-            const float *row = p.up + ((int64_t)b * p.n_stride + t) * qkv_dim;
-            for (int i = j; i < HK; i += hv) {
-                s_q[i] = row[(int64_t)kh * HK + i];
-                s_k[i] = row[key_dim + (int64_t)kh * HK + i];
+            const GdnPos<HK> cur = nxt;
+            {                                                               // the next position's inputs, a position ahead
+                const bool more = t + 1 < p.n;
+                const int nitem = more ? item : item + (int)gridDim.x;
+                if (nitem < nitems) gdn_fetch<HK>(p, nitem, more ? t + 1 : 0, j, hv, nxt);
             }
-            const float vj = row[2 * key_dim + (int64_t)vh * hv + j];
-            const float zj = p.gate[((int64_t)b * p.n_stride + t) * val_dim + (int64_t)vh * hv + j];
-            const float x = __fadd_rn(p.gdec[((int64_t)b * p.n_stride + t) * p.nh + vh], dtb);
+#pragma unroll
+            for (int u = 0; u < GdnPos<HK>::PER; u++)
+                if (j + u * hv < HK) { s_q[j + u * hv] = cur.q[u]; s_k[j + u * hv] = cur.k[u]; }
+            const float vj = cur.v, zj = cur.z;
+            const float ea = g_exp(cur.a_log);
+            const float x = __fadd_rn(cur.gdec, cur.dt_bias);
             const float sp = x > 20.0f ? x : (float)log1p((double)g_exp(x));
             const float decay = g_exp(__fmul_rn(-ea, sp));
-            const float bet = __fdiv_rn(1.0f, __fadd_rn(1.0f, g_exp(-p.beta[((int64_t)b * p.n_stride + t) * p.nh + vh])));
+            const float bet = __fdiv_rn(1.0f, __fadd_rn(1.0f, g_exp(-cur.beta)));
             const float silu = __fdiv_rn(zj, __fadd_rn(1.0f, g_exp(-zj)));
             if (t == 0) {                                                   // the tile, under the loads and exps above
                 mbar_wait(bar, phase, err, GDN_ERR_TILE);                   // on giving up: carries on, the host reports the call as failed
