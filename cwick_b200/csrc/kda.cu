@@ -2,23 +2,24 @@
 // cwick_attention_kda_decode between its projections and o_proj (src/attention.c:1243-1417), for B engine
 // slots at once. The projections either side are plain GEMVs and stay with the caller.
 //
-// One work item per (head, slot), one thread per channel of the head; blocks are persistent and the next item's
-// state tile and scalars stream into shared memory (asynchronous copies) while the current item is worked on:
+// One work item per (head, slot), one thread per channel of the head; blocks are persistent. An item's [hd][hd] state
+// comes into shared memory by one bulk copy, is updated there, and goes back by one bulk copy; the item's other inputs
+// are fetched into registers an item ahead. Few registers and one tile per block leave room for three blocks per SM,
+// which is what overlaps one item's copies with another's arithmetic:
 //   1. short convolution over the 3-deep window of projected values + SiLU for q, k, v; the window moves on
 //      (:1253-1281)
 //   2. L2 norm of q and k over the head, q also / sqrt(hd) (:1285-1301); the squared sums are formed in double
 //   3. decay exp(lower * sigmoid(exp(a_log[h]) * (gate_raw + dt_bias))) per key channel, beta = sigmoid (:1314-1342)
-//   4. the recurrence on the head's [hd][hd] state (:1352-1396): a thread owns one VALUE column of the state in
-//      registers (hd floats, taken from the staged tile), so the state is read once and written once, and the three
-//      passes over the key dimension -- delta = v - k.S, S += (beta k) delta, core = q.S -- run in the
-//      reference's order on it
+//   4. the recurrence on the head's [hd][hd] state (:1352-1396): a thread owns one VALUE column of the tile (lanes read
+//      neighbouring words: no bank conflicts), so the state is read once and written once, and the sums over the key
+//      dimension -- delta = v - k.S, then S += (beta k) delta with core = q.S -- run in the reference's order on it
 //   5. RMS norm of the head's core times o_norm times sigmoid(gate) (:1406-1417)
 // The state is the traffic: 2 x hd x hd x 4 bytes per head and token (8.4 MB per layer at 64 heads of 128).
 // Products and sums that the reference rounds separately use the _rn intrinsics (this file is compiled with
 // fast-math); exp goes through double, so results equal the C library's expf except in rare last-place cases.
 #include <algorithm>
 
-#include "cwk_common.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -55,92 +56,70 @@ struct KdaParams {
     float lower, rms_eps;
 };
 
-// Scalars of one item that come from memory written per slot or per channel, staged in shared memory by 4- and
-// 8-byte asynchronous copies together with the item's state tile: [SC_COUNT][HD] words.
-enum { SC_X = 0, SC_S = 3, SC_GRAW = 12, SC_GATE = 13, SC_DT = 14, SC_W = 15, SC_COUNT = 21 };      // SC_W: 3 x two words (4 bf16)
+constexpr int KDA_ERR_TILE = 0x6b01;
 
-template <int HD>
-__device__ __forceinline__ void kda_prefetch(const KdaParams &p, int item, float *s_tile, float *s_sc, int j) {
+// One item's inputs other than the state, as thread j (channel j of the head) holds them.
+struct KdaIn {
+    float x[3], sw[3][3], graw, gate_v, dt, a_log, beta_raw;
+    uint2 wbits[3];
+};
+template <int HD> __device__ __forceinline__ void kda_fetch(const KdaParams &p, int item, int j, KdaIn &r) {
     const int h = item % p.nh, b = item / p.nh;
     const int64_t proj = (int64_t)p.nh * HD, i = (int64_t)h * HD + j;
-    const float *r = p.rec + (((int64_t)b * p.nh + h) * HD) * HD;
-    const uint32_t tb = (uint32_t)__cvta_generic_to_shared(s_tile), sb = (uint32_t)__cvta_generic_to_shared(s_sc);
-#pragma unroll
-    for (int c = 0; c < HD / 4; c++) {
-        const int ch = c * HD + j;                                    // 16-byte chunk of the [HD][HD] tile
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tb + (uint32_t)ch * 16u), "l"(r + (int64_t)ch * 4) : "memory");
-    }
-    auto cp4 = [&](int slot, const float *g) {
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sb + (uint32_t)(slot * HD + j) * 4u), "l"(g) : "memory");
-    };
     const float *in[3] = {p.q, p.k, p.v};
     const uint16_t *cw[3] = {p.q_conv, p.k_conv, p.v_conv};
 #pragma unroll
     for (int w = 0; w < 3; w++) {
-        cp4(SC_X + w, in[w] + (int64_t)b * proj + i);
-        const float *s = p.conv + (((int64_t)b * 3 + w) * proj + i) * 3;
-        cp4(SC_S + 3 * w, s); cp4(SC_S + 3 * w + 1, s + 1); cp4(SC_S + 3 * w + 2, s + 2);
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(sb + (uint32_t)((SC_W + 2 * w) * HD + 2 * j) * 4u), "l"(cw[w] + i * 4) : "memory");
+        r.x[w] = __ldg(in[w] + (int64_t)b * proj + i);
+        const float *sp = p.conv + (((int64_t)b * 3 + w) * proj + i) * 3;      // written by this kernel, for this item only
+        r.sw[w][0] = sp[0]; r.sw[w][1] = sp[1]; r.sw[w][2] = sp[2];
+        r.wbits[w] = __ldg(reinterpret_cast<const uint2 *>(cw[w] + i * 4));
     }
-    cp4(SC_GRAW, p.gate_raw + (int64_t)b * proj + i);
-    cp4(SC_GATE, p.gate + (int64_t)b * proj + i);
-    cp4(SC_DT, p.dt_bias + i);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    r.graw = __ldg(p.gate_raw + (int64_t)b * proj + i);
+    r.gate_v = __ldg(p.gate + (int64_t)b * proj + i);
+    r.dt = __ldg(p.dt_bias + i);
+    r.a_log = __ldg(p.a_log + h);
+    r.beta_raw = __ldg(p.beta_raw + (int64_t)b * p.nh + h);
 }
 
-// Persistent blocks: block g works on items g, g + G, ... (item = slot * nh + head). While an item is worked on in
-// registers, the next item's state tile and scalars stream into shared memory.
+// Persistent blocks: block g works on items g, g + G, ... (item = slot * nh + head).
 template <int HD>
-__global__ void __launch_bounds__(HD) kda_step_kernel(const KdaParams p, int nitems) {
+__global__ void __launch_bounds__(HD) kda_step_kernel(const KdaParams p, int nitems, int *err) {
     extern __shared__ float4 s_dyn4[];
-    float *s_tile = reinterpret_cast<float *>(s_dyn4);                // [HD][HD], the NEXT item's state
-    float *s_sc = s_tile + HD * HD;                                   // [SC_COUNT][HD]
-    __shared__ float s_q[HD], s_k[HD], s_v[HD], s_eg[HD], s_core[HD];
+    float *s_tile = reinterpret_cast<float *>(s_dyn4);                // [HD][HD], this item's state
+    __shared__ __align__(16) float s_q[HD], s_k[HD], s_v[HD], s_eg[HD], s_core[HD];
     __shared__ double s_part[HD / 32];
+    __shared__ __align__(8) uint64_t s_bar;
     const int j = threadIdx.x;
     const int64_t proj = (int64_t)p.nh * HD;
-
-    // One item per block (few slots): nothing to overlap with, the column and the scalars come straight from
-    // global memory, the column first.
-    const bool single = nitems <= (int)gridDim.x;
-    if (!single && (int)blockIdx.x < nitems) kda_prefetch<HD>(p, blockIdx.x, s_tile, s_sc, j);
+    const uint32_t bar = smem_u32(&s_bar), tile = smem_u32(s_tile);
+    constexpr int COPIER = HD > 32 ? 32 : 0;                          // the thread that issues the tile copies
+    constexpr uint32_t TILE_BYTES = HD * HD * 4;
+    if (j == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    uint32_t phase = 0;
+    KdaIn nxt;
+    if ((int)blockIdx.x < nitems) kda_fetch<HD>(p, blockIdx.x, j, nxt);
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
         const int h = item % p.nh, b = item / p.nh;
         const int64_t i = (int64_t)h * HD + j;
-        float st[HD];
-        float x[3], sw[3][3], graw, gate_v, dt;
-        uint2 wbits[3];
-        if (single) {
-            const float *r = p.rec + (((int64_t)b * p.nh + h) * HD) * HD + j;
-#pragma unroll
-            for (int kk = 0; kk < HD; kk++) st[kk] = r[(int64_t)kk * HD];
-            const float *in[3] = {p.q, p.k, p.v};
-            const uint16_t *cw[3] = {p.q_conv, p.k_conv, p.v_conv};
-#pragma unroll
-            for (int w = 0; w < 3; w++) {
-                x[w] = in[w][(int64_t)b * proj + i];
-                const float *sp = p.conv + (((int64_t)b * 3 + w) * proj + i) * 3;
-                sw[w][0] = sp[0]; sw[w][1] = sp[1]; sw[w][2] = sp[2];
-                wbits[w] = *reinterpret_cast<const uint2 *>(cw[w] + i * 4);
-            }
-            graw = p.gate_raw[(int64_t)b * proj + i]; gate_v = p.gate[(int64_t)b * proj + i]; dt = p.dt_bias[i];
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncthreads();
-            // this thread's state column and scalars leave shared memory, which then takes the next item
-#pragma unroll
-            for (int kk = 0; kk < HD; kk++) st[kk] = s_tile[kk * HD + j];
-#pragma unroll
-            for (int w = 0; w < 3; w++) {
-                x[w] = s_sc[(SC_X + w) * HD + j];
-#pragma unroll
-                for (int t = 0; t < 3; t++) sw[w][t] = s_sc[(SC_S + 3 * w + t) * HD + j];
-                wbits[w] = *reinterpret_cast<const uint2 *>(s_sc + (SC_W + 2 * w) * HD + 2 * j);
-            }
-            graw = s_sc[SC_GRAW * HD + j]; gate_v = s_sc[SC_GATE * HD + j]; dt = s_sc[SC_DT * HD + j];
-            __syncthreads();
-            if (item + (int)gridDim.x < nitems) kda_prefetch<HD>(p, item + gridDim.x, s_tile, s_sc, j);
+        float *rec = p.rec + (((int64_t)b * p.nh + h) * HD) * HD;
+        if (j == COPIER) {
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the last write-back has left the tile
+            mbar_expect_tx(bar, TILE_BYTES);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(tile),
+                         "l"(rec), "r"(TILE_BYTES), "r"(bar)
+                         : "memory");
         }
+        const KdaIn cur = nxt;
+        if (item + (int)gridDim.x < nitems) kda_fetch<HD>(p, item + gridDim.x, j, nxt);
+        const float(&x)[3] = cur.x;
+        const float(&sw)[3][3] = cur.sw;
+        const uint2(&wbits)[3] = cur.wbits;
+        const float graw = cur.graw, gate_v = cur.gate_v, dt = cur.dt;
 
         // 1. convolution + SiLU
         {
@@ -161,7 +140,7 @@ __global__ void __launch_bounds__(HD) kda_step_kernel(const KdaParams p, int nit
         // 3. decay factor of this key channel
         {
             const float raw = __fadd_rn(graw, dt);
-            const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_f(__fmul_rn(-exp_f(p.a_log[h]), raw))));
+            const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_f(__fmul_rn(-exp_f(cur.a_log), raw))));
             s_eg[j] = exp_f(__fmul_rn(p.lower, sg));
         }
         __syncthreads();
@@ -179,25 +158,44 @@ __global__ void __launch_bounds__(HD) kda_step_kernel(const KdaParams p, int nit
             s_k[j] = kv;
         }
         __syncthreads();
-        // 4. recurrence: this thread owns value column j of the head's state
+        // 4. recurrence: this thread owns value column j of the head's state tile
         {
-            float *r = p.rec + (((int64_t)b * p.nh + h) * HD) * HD + j;
-            const float beta = sigmoid_ref(p.beta_raw[(int64_t)b * p.nh + h]);
-#pragma unroll
-            for (int kk = 0; kk < HD; kk++) st[kk] = __fmul_rn(st[kk], s_eg[kk]);
+            const float beta = sigmoid_ref(cur.beta_raw);
+            mbar_wait(bar, phase, err, KDA_ERR_TILE);                       // on giving up: carries on, the host reports the call as failed
+            phase ^= 1;
+            float *col = s_tile + j;
             float delta = s_v[j];
-#pragma unroll
-            for (int kk = 0; kk < HD; kk++) delta = __fsub_rn(delta, __fmul_rn(s_k[kk], st[kk]));
-#pragma unroll
-            for (int kk = 0; kk < HD; kk++) st[kk] = __fadd_rn(st[kk], __fmul_rn(__fmul_rn(beta, s_k[kk]), delta));
+#pragma unroll 8
+            for (int kk = 0; kk < HD; kk += 4) {
+                const float4 e4 = *reinterpret_cast<const float4 *>(s_eg + kk), k4 = *reinterpret_cast<const float4 *>(s_k + kk);
+                delta = __fsub_rn(delta, __fmul_rn(k4.x, __fmul_rn(col[(kk + 0) * HD], e4.x)));
+                delta = __fsub_rn(delta, __fmul_rn(k4.y, __fmul_rn(col[(kk + 1) * HD], e4.y)));
+                delta = __fsub_rn(delta, __fmul_rn(k4.z, __fmul_rn(col[(kk + 2) * HD], e4.z)));
+                delta = __fsub_rn(delta, __fmul_rn(k4.w, __fmul_rn(col[(kk + 3) * HD], e4.w)));
+            }
             float o = 0.f;
-#pragma unroll
-            for (int kk = 0; kk < HD; kk++) o = __fadd_rn(o, __fmul_rn(s_q[kk], st[kk]));
-#pragma unroll
-            for (int kk = 0; kk < HD; kk++) r[(int64_t)kk * HD] = st[kk];
+#pragma unroll 8
+            for (int kk = 0; kk < HD; kk += 4) {
+                const float4 e4 = *reinterpret_cast<const float4 *>(s_eg + kk), k4 = *reinterpret_cast<const float4 *>(s_k + kk);
+                const float4 q4 = *reinterpret_cast<const float4 *>(s_q + kk);
+                const float s0 = __fadd_rn(__fmul_rn(col[(kk + 0) * HD], e4.x), __fmul_rn(__fmul_rn(beta, k4.x), delta));
+                const float s1 = __fadd_rn(__fmul_rn(col[(kk + 1) * HD], e4.y), __fmul_rn(__fmul_rn(beta, k4.y), delta));
+                const float s2 = __fadd_rn(__fmul_rn(col[(kk + 2) * HD], e4.z), __fmul_rn(__fmul_rn(beta, k4.z), delta));
+                const float s3 = __fadd_rn(__fmul_rn(col[(kk + 3) * HD], e4.w), __fmul_rn(__fmul_rn(beta, k4.w), delta));
+                col[(kk + 0) * HD] = s0; col[(kk + 1) * HD] = s1; col[(kk + 2) * HD] = s2; col[(kk + 3) * HD] = s3;
+                o = __fadd_rn(o, __fmul_rn(q4.x, s0));
+                o = __fadd_rn(o, __fmul_rn(q4.y, s1));
+                o = __fadd_rn(o, __fmul_rn(q4.z, s2));
+                o = __fadd_rn(o, __fmul_rn(q4.w, s3));
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // the column, visible to the copy engine
             s_core[j] = o;
         }
         __syncthreads();
+        if (j == COPIER) {                                                  // the tile goes back under the gated norm
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(rec), "r"(tile), "r"(TILE_BYTES) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
         // 5. gated norm
         {
             const double ss = block_sum<HD>((double)s_core[j] * (double)s_core[j], s_part);
@@ -208,6 +206,7 @@ __global__ void __launch_bounds__(HD) kda_step_kernel(const KdaParams p, int nit
             p.core[(int64_t)b * proj + i] = __fmul_rn(o, sg);
         }
     }
+    if (j == COPIER) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 }  // namespace
@@ -229,18 +228,24 @@ extern "C" int cwk_kda_step(cwk_ctx *ctx, int B, int nh, int hd, float lower, fl
     if ((reinterpret_cast<uintptr_t>(rec) & 15) || (reinterpret_cast<uintptr_t>(q_conv) | reinterpret_cast<uintptr_t>(k_conv) | reinterpret_cast<uintptr_t>(v_conv)) & 7)
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "kda_step: the state must be 16-byte and the convolution weights 8-byte aligned");
     const int nitems = B * nh;
-    const int grid = std::min(nitems, 2 * ctx->sm_count);
-    const size_t smem = ((size_t)hd * hd + (size_t)SC_COUNT * hd) * sizeof(float);
-    static bool attr_set[16] = {false};
-    if (!attr_set[ctx->device & 15]) {
-        CWK_CUDA(ctx, cudaFuncSetAttribute(kda_step_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (128 * 128 + SC_COUNT * 128) * 4));
-        CWK_CUDA(ctx, cudaFuncSetAttribute(kda_step_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 * 64 + SC_COUNT * 64) * 4));
-        attr_set[ctx->device & 15] = true;
+    const size_t smem = (size_t)hd * hd * sizeof(float);
+    static int per_sm[16][3] = {{0}};                                   // resident blocks per SM, by device and head dim
+    int &resident = per_sm[ctx->device & 15][hd == 128 ? 2 : hd == 64 ? 1 : 0];
+    if (!resident) {
+        CWK_CUDA(ctx, cudaFuncSetAttribute(kda_step_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 128 * 4));
+        int nb = 0;
+        if (hd == 128) CWK_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kda_step_kernel<128>, 128, smem));
+        else if (hd == 64) CWK_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kda_step_kernel<64>, 64, smem));
+        else CWK_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kda_step_kernel<32>, 32, smem));
+        resident = std::max(nb, 1);
     }
+    const int grid = std::min(nitems, resident * ctx->sm_count);
+    int es = cwk_ensure_err_word(ctx);
+    if (es != CWK_OK) return es;
     CwkKernelTimer timer(ctx);
-    if (hd == 128) kda_step_kernel<128><<<grid, 128, smem, ctx->stream>>>(p, nitems);
-    else if (hd == 64) kda_step_kernel<64><<<grid, 64, smem, ctx->stream>>>(p, nitems);
-    else kda_step_kernel<32><<<grid, 32, smem, ctx->stream>>>(p, nitems);
+    if (hd == 128) kda_step_kernel<128><<<grid, 128, smem, ctx->stream>>>(p, nitems, ctx->dev_err);
+    else if (hd == 64) kda_step_kernel<64><<<grid, 64, smem, ctx->stream>>>(p, nitems, ctx->dev_err);
+    else kda_step_kernel<32><<<grid, 32, smem, ctx->stream>>>(p, nitems, ctx->dev_err);
     CWK_LAUNCH_CHECK(ctx, "kda_step_kernel");
     return CWK_OK;
 }
