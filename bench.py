@@ -798,6 +798,9 @@ def side_prefill(attn, dev, stream, peak):
                             "note": "after the attention: cwk_mla_unabsorb then cwk_fp8_linear (8192 -> 4096); not in ms_per_prefill"}}
 
 
+PROFILE_SLOTS = 0
+
+
 def side_kda(attn, dev, stream, peak):
     """KDA linear-attention decode step (not a BASELINE config; the layers next to the MLA ones): 64 heads of
     128, 1 and 64 slots; the traffic is the [hd][hd] state of every head, read and written once."""
@@ -808,6 +811,8 @@ def side_kda(attn, dev, stream, peak):
     proj = nh * hd
     out = {}
     for B, rot in ((1, 40), (64, 2)):                   # rot distinct state sets: > L2 between revisits
+        if PROFILE_SLOTS and B != PROFILE_SLOTS:
+            continue
         w = [(0.5 * torch.randn(proj, 4, device=dev, generator=g)).to(torch.bfloat16) for _ in range(3)]
         a_log = 0.5 * torch.randn(nh, device=dev, generator=g)
         dt = 0.5 * torch.randn(proj, device=dev, generator=g)
@@ -824,6 +829,10 @@ def side_kda(attn, dev, stream, peak):
             it[0] += 1
             attn.ctx.check(attn.lib.cwk_kda_step(attn.ctx.h, B, nh, hd, -5.0, 1e-6, p(ins[0]), p(ins[1]), p(ins[2]), p(w[0]), p(w[1]), p(w[2]),
                                                  p(convs[r]), p(ins[3]), p(dt), p(a_log), p(ins[4]), p(ins[5]), p(on), p(recs[r]), p(core)))
+        if PROFILE_SLOTS:                               # a capture wants few launches: 3 + 5 plain calls, nothing else
+            ms, k_ms, _ = _time_calls(attn, stream, call, n=5, warm=3)
+            out["slots_%d" % B] = {"us_per_step_eager_launches": ms * 1e3}
+            continue
         ms, k_ms, _ = _time_calls(attn, stream, call, n=40, warm=3)
         ms_g = _time_graph(stream, call, calls=rot)
         by = B * nh * hd * hd * 4 * 2
@@ -849,6 +858,8 @@ def side_gdn_mm(attn, dev, stream, peak):
     a_log, dtb, norm = (0.5 * torch.randn(nh, device=dev, generator=g), 0.5 * torch.randn(nh, device=dev, generator=g),
                         torch.ones(hv, device=dev))
     for B, rot in ((1, 80), (64, 3)):
+        if PROFILE_SLOTS and B != PROFILE_SLOTS:
+            continue
         up = torch.randn(B, 1, 2 * key_dim + val_dim, device=dev, generator=g) * 0.1
         gdec, beta = torch.randn(B, 1, nh, device=dev, generator=g), torch.randn(B, 1, nh, device=dev, generator=g)
         gate = torch.randn(B, 1, val_dim, device=dev, generator=g)
@@ -861,6 +872,10 @@ def side_gdn_mm(attn, dev, stream, peak):
             it[0] += 1
             attn.ctx.check(attn.lib.cwk_gdn_scan(attn.ctx.h, B, 1, nh, hk, hv, grp, p(up), p(gdec), p(beta), p(gate), p(a_log), p(dtb),
                                                  p(norm), 1e-6, p(S[r]), p(o)))
+        if PROFILE_SLOTS:
+            ms, k_ms, _ = _time_calls(attn, stream, call, n=5, warm=3)
+            out["gdn_slots_%d" % B] = {"us_per_step_eager_launches": ms * 1e3}
+            continue
         ms, k_ms, _ = _time_calls(attn, stream, call, n=40, warm=3)
         ms_g = _time_graph(stream, call, calls=rot)
         by = B * nh * hv * hk * 4 * 2
@@ -870,6 +885,8 @@ def side_gdn_mm(attn, dev, stream, peak):
                                    "us_per_step_eager_launches": ms * 1e3, "kernel_us_between_events": k_ms * 1e3}
         del S
         torch.cuda.empty_cache()
+    if PROFILE_SLOTS:
+        return out
     # a 4096-token prompt through the scan: chunk-parallel (64 positions at a time) against position-serial
     npr = 4096
     up = torch.randn(1, npr, 2 * key_dim + val_dim, device=dev, generator=g) * 0.1
@@ -1000,9 +1017,13 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="c5b: how partial records travel")
     ap.add_argument("--extra-only", default=None, choices=["c1", "gqa", "c3", "c4", "c5a", "kda", "gdn_mm"],
                     help="run one side measurement alone and print its JSON (for profiling that kernel)")
+    ap.add_argument("--profile-slots", type=int, default=0, choices=[0, 1, 64],
+                    help="with --extra-only kda / gdn_mm: only that slot count, 3 + 5 plain launches (for an ncu capture)")
     ap.add_argument("--mla-path", type=int, default=-1, help="force an MLA decode kernel (cwk_ctx_force_mla_path codes)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline")
     args = ap.parse_args()
+    global PROFILE_SLOTS
+    PROFILE_SLOTS = args.profile_slots
     if args.extra_only:
         import torch
         from cwick_b200 import build
