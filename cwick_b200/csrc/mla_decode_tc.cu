@@ -157,10 +157,15 @@ mla_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // A full wave of blocks with many tiles each: blocks that start together stay in lockstep for their first tiles
         // (every SM loads, then every SM computes, and HBM idles through the compute phases: 10 k cycles per tile against
         // 7 k once they have drifted apart), so eight groups of blocks start a fraction of a tile period apart.
-        // Blocks that have one tile more than the others start first.
+        // Blocks that have one tile more than the others start first when they are few; when they are most of the
+        // launch they are the ones to spread.
         if (p.stagger) {
-            const bool longest = (ntiles % p.nsplit) != 0 && n == (ntiles + p.nsplit - 1) / p.nsplit;
-            const int group = longest ? 0 : ((ntiles % p.nsplit) != 0 ? 1 + (split + 3 * b) % 7 : (split + 3 * b) & 7);
+            const int nlong = ntiles % p.nsplit;                            // blocks with one tile more (0: all alike)
+            const bool longest = nlong != 0 && n == (ntiles + p.nsplit - 1) / p.nsplit;
+            int group;
+            if (nlong == 0) group = (split + 3 * b) & 7;
+            else if (nlong * 4 <= p.nsplit) group = longest ? 0 : 1 + (split + 3 * b) % 7;      // a few long blocks: they go first
+            else group = longest ? (split + 3 * b) % 7 : 7;                 // mostly long blocks: they spread, the few short ones last
             const long long until = clock64() + (long long)group * p.stagger;
             while (clock64() < until) { }
         }
