@@ -35,7 +35,8 @@ def cu(a):
 
 
 @pytest.mark.parametrize("B,n,nh,hk,hv,grp", [(1, 1, 32, 128, 128, 2), (3, 1, 32, 128, 128, 2), (2, 37, 8, 128, 128, 2), (1, 5, 4, 64, 64, 1),
-                                                (12, 1, 32, 128, 128, 2), (80, 2, 4, 64, 64, 1)])      # the last two: more items than resident blocks
+                                                (12, 1, 32, 128, 128, 2), (80, 2, 4, 64, 64, 1),      # these two: more items than resident blocks
+                                                (2, 3, 4, 128, 32, 2), (2, 2, 4, 64, 96, 1)])          # value dims other than the key dim
 def test_gdn_scan_matches_the_oracle(attn, B, n, nh, hk, hv, grp):
     o = orc.oracle()
     key_dim, val_dim = (nh // grp) * hk, nh * hv
