@@ -84,6 +84,72 @@ __global__ void __launch_bounds__(256) norm_rope_rows_kernel(const float *in, in
     if (kv_len_out && threadIdx.x == 0) kv_len_out[r] = (int)(pos0 + r + 1);
 }
 
+// The same, one WARP per row, for rows whose normalised part is a multiple of 128 columns (at most 128 * MAXV4) and whose
+// rope part is at most 64 columns: a lane keeps its 16-byte pieces of the row in registers, so the row is read once;
+// the sum of squares goes through lane-wise doubles and five shuffles, with no shared memory and no block barrier.
+// 4096 rows are 4096 warps, all resident at once: the call takes about one row's latency.
+template <int MAXV4>
+__global__ void __launch_bounds__(256) norm_rope_rows_warp_kernel(const float *in, int64_t in_ld, int norm_cols, int rope_cols,
+                                                                  const uint16_t *weight, float eps, float rope_base, int64_t pos0,
+                                                                  uint16_t *out, int64_t out_ld, int *kv_len_out, int ref_narrow,
+                                                                  int64_t nrows) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= nrows) return;
+    const float *x = in + r * in_ld;
+    const int np = norm_cols / 128;
+    float4 v[MAXV4];
+    float ra = 0.f, rb = 0.f;
+    if (lane < rope_cols / 2) {
+        const float2 ab = *reinterpret_cast<const float2 *>(x + norm_cols + 2 * lane);
+        ra = ab.x; rb = ab.y;
+    }
+    double ss = 0.0;
+#pragma unroll
+    for (int c = 0; c < MAXV4; c++)
+        if (c < np) {
+            v[c] = *reinterpret_cast<const float4 *>(x + c * 128 + lane * 4);
+            ss += (double)v[c].x * (double)v[c].x;
+            ss += (double)v[c].y * (double)v[c].y;
+            ss += (double)v[c].z * (double)v[c].z;
+            ss += (double)v[c].w * (double)v[c].w;
+        }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = __fdiv_rn(1.0f, (float)sqrt(ss / (double)norm_cols + (double)eps));
+    uint16_t *y = out + r * out_ld;
+#pragma unroll
+    for (int c = 0; c < MAXV4; c++)
+        if (c < np) {
+            const uint2 wb = *reinterpret_cast<const uint2 *>(weight + c * 128 + lane * 4);
+            const float o0 = v[c].x * inv * __uint_as_float(wb.x << 16), o1 = v[c].y * inv * __uint_as_float(wb.x & 0xffff0000u);
+            const float o2 = v[c].z * inv * __uint_as_float(wb.y << 16), o3 = v[c].w * inv * __uint_as_float(wb.y & 0xffff0000u);
+            uint2 pk;
+            if (ref_narrow) {
+                pk.x = (uint32_t)narrow_bf16_like_reference(o0) | ((uint32_t)narrow_bf16_like_reference(o1) << 16);
+                pk.y = (uint32_t)narrow_bf16_like_reference(o2) | ((uint32_t)narrow_bf16_like_reference(o3) << 16);
+            } else {
+                pk.x = pack_bf16x2(o0, o1);
+                pk.y = pack_bf16x2(o2, o3);
+            }
+            *reinterpret_cast<uint2 *>(y + c * 128 + lane * 4) = pk;
+        }
+    if (lane < rope_cols / 2) {
+        float sn, cs;
+        rope_cos_sin(pos0 + r, lane, rope_cols, rope_base, cs, sn);
+        const float r0 = ra * cs - rb * sn, r1 = rb * cs + ra * sn;
+        *reinterpret_cast<uint32_t *>(y + norm_cols + 2 * lane) =
+            ref_narrow ? ((uint32_t)narrow_bf16_like_reference(r0) | ((uint32_t)narrow_bf16_like_reference(r1) << 16)) : pack_bf16x2(r0, r1);
+    }
+    if (kv_len_out && lane == 0) kv_len_out[r] = (int)(pos0 + r + 1);
+}
+
+static bool norm_rope_warp_ok(const float *in, int64_t in_ld, int norm_cols, int rope_cols, const void *weight, const void *out, int64_t out_ld) {
+    return norm_cols > 0 && norm_cols % 128 == 0 && norm_cols <= 128 * 12 && rope_cols <= 64 && (rope_cols & 1) == 0 && in_ld % 4 == 0 &&
+           out_ld % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(weight) & 7) == 0 &&
+           (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+}
+
 // Rope tail of the absorbed query: Qfull[t][h][L : L+rope] = RoPE(q[t][h][nope : nope+rope], pos0 + t).
 // The angle depends on (t, pair) only: one thread forms it once and rotates that pair of all heads.
 __global__ void __launch_bounds__(256) rope_tail_kernel(const uint16_t *q, uint16_t *qfull, int n, int nh, int nope, int n_rope, int L,
@@ -104,14 +170,24 @@ __global__ void __launch_bounds__(256) rope_tail_kernel(const uint16_t *q, uint1
 }
 
 // RoPE of the rope part of q, in place: q[t][h][nope : nope+rope] at position pos0 + t. One thread per (t, pair) and
-// group of heads (blockIdx.y): the angle is formed once per thread and applied to the group's heads.
+// group of heads (blockIdx.y): the angle is formed once per thread and applied to the group's heads. The pairs'
+// divisors base^(2j / n_rope) -- the same values rope_cos_sin forms -- are computed once per block (n_rope <= 256).
 __global__ void __launch_bounds__(256) rope_q_inplace_kernel(uint16_t *q, int n, int nh, int nope, int n_rope, int64_t pos0, float base) {
+    __shared__ float s_den[128];
+    for (int jj = threadIdx.x; jj < n_rope / 2; jj += 256) s_den[jj] = (float)pow((double)base, (double)(2.0f * (float)jj / (float)n_rope));
+    __syncthreads();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n * (n_rope / 2)) return;
     const int t = i / (n_rope / 2), j = i % (n_rope / 2);
     const int hpg = (nh + (int)gridDim.y - 1) / (int)gridDim.y, h0 = (int)blockIdx.y * hpg, h1 = min(nh, h0 + hpg);
     float cs, sn;
-    rope_cos_sin(pos0 + t, j, n_rope, base, cs, sn);
+    {
+        const float ang = __fdiv_rn((float)(pos0 + t), s_den[j]);
+        double sd, cd;
+        sincos((double)ang, &sd, &cd);
+        cs = (float)cd;
+        sn = (float)sd;
+    }
     uint16_t *src = q + (int64_t)t * nh * (nope + n_rope) + nope + 2 * j;
 #pragma unroll 8
     for (int h = h0; h < h1; h++) {
@@ -246,8 +322,12 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
     }
     if (!kva_done) s = cwk_fp8_linear(ctx, X, Wqa, Sqa, n, H, q_lora, QA, 0);
     if (s != CWK_OK) return s;
-    norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(QA, q_lora, q_lora, 0, (const uint16_t *)qa_norm, eps, rope_base,
-                                                      pos0, QAn, q_lora, nullptr, 0);
+    if (norm_rope_warp_ok(QA, q_lora, q_lora, 0, qa_norm, QAn, q_lora))
+        norm_rope_rows_warp_kernel<12><<<(n + 7) / 8, 256, 0, ctx->stream>>>(QA, q_lora, q_lora, 0, (const uint16_t *)qa_norm, eps, rope_base,
+                                                                             pos0, QAn, q_lora, nullptr, 0, n);
+    else
+        norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(QA, q_lora, q_lora, 0, (const uint16_t *)qa_norm, eps, rope_base,
+                                                          pos0, QAn, q_lora, nullptr, 0);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(q_a)");
     s = cwk_fp8_linear(ctx, QAn, Wqb, Sqb, n, q_lora, (int64_t)nh * qd, Q, 1);
     if (s != CWK_OK) return s;
@@ -255,11 +335,15 @@ extern "C" int cwk_mla_prefill(cwk_ctx *ctx, const void *X, const void *Wqa, con
         s = cwk_fp8_linear(ctx, X, Wkva, Skva, n, H, row, KVA, 0);
         if (s != CWK_OK) return s;
     }
-    norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(KVA, row, kv_lora, rope, (const uint16_t *)kva_norm, eps, rope_base,
-                                                      pos0, (uint16_t *)cache + pos0 * row, row, len, 1);
+    if (norm_rope_warp_ok(KVA, row, kv_lora, rope, kva_norm, (uint16_t *)cache + pos0 * row, row))
+        norm_rope_rows_warp_kernel<12><<<(n + 7) / 8, 256, 0, ctx->stream>>>(KVA, row, kv_lora, rope, (const uint16_t *)kva_norm, eps, rope_base,
+                                                                             pos0, (uint16_t *)cache + pos0 * row, row, len, 1, n);
+    else
+        norm_rope_rows_kernel<<<n, 256, 0, ctx->stream>>>(KVA, row, kv_lora, rope, (const uint16_t *)kva_norm, eps, rope_base,
+                                                          pos0, (uint16_t *)cache + pos0 * row, row, len, 1);
     CWK_LAUNCH_CHECK(ctx, "norm_rope_rows_kernel(kv_a)");
     if (expanded_keys && cwk_mla_prefill_attn_tc_ok(Q, cache, Wuk, Qf, out)) {
-        rope_q_inplace_kernel<<<dim3((n * (rope / 2) + 255) / 256, nh >= 8 ? 8 : 1), 256, 0, ctx->stream>>>(Q, n, nh, nope, rope, pos0, rope_base);
+        rope_q_inplace_kernel<<<dim3((n * (rope / 2) + 255) / 256, nh >= 8 ? 4 : 1), 256, 0, ctx->stream>>>(Q, n, nh, nope, rope, pos0, rope_base);
         CWK_LAUNCH_CHECK(ctx, "rope_q_inplace_kernel");
         return cwk_mla_prefill_attn_tc(ctx, Q, cache, Wuk, Qf, (int *)((uint8_t *)len + up((size_t)n * 4)), pos0, n, nh, scale, out, ctx->force_mla_path == 3);
     }
