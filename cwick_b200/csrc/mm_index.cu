@@ -14,7 +14,7 @@ namespace {
 // 128 keys per block: their rows (ID bf16 each) come into shared memory by 16-byte asynchronous copies, coalesced, into
 // rows padded by 4 words, so that a thread's 16-byte reads of its own row are conflict-free.
 template <int ID>
-__global__ void __launch_bounds__(128) mm_index_scores_kernel(const uint16_t *keys, int64_t n, const float *q, int ih, float *sc) {
+__global__ void __launch_bounds__(128, 5) mm_index_scores_kernel(const uint16_t *keys, int64_t n, const float *q, int ih, float *sc) {
     constexpr int WPR = ID / 2, LD = WPR + 4;      // words per key row, padded row stride
     extern __shared__ float s_dyn[];
     float *s_q = s_dyn;                            // [ih][ID]
@@ -34,23 +34,37 @@ __global__ void __launch_bounds__(128) mm_index_scores_kernel(const uint16_t *ke
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     if ((int)threadIdx.x >= nk) return;
-    float kf[ID];
+    uint32_t kw[WPR];                               // the key row as it is stored: two bf16 per word (half the registers of f32)
 #pragma unroll
     for (int c = 0; c < WPR / 4; c++) {
         const uint4 v = *reinterpret_cast<const uint4 *>(s_k + threadIdx.x * LD + c * 4);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int t = 0; t < 4; t++) {
-            kf[c * 8 + 2 * t] = __uint_as_float(w[t] << 16);
-            kf[c * 8 + 2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
-        }
+        kw[c * 4] = v.x; kw[c * 4 + 1] = v.y; kw[c * 4 + 2] = v.z; kw[c * 4 + 3] = v.w;
     }
+    auto kf = [&](int i) { return (i & 1) ? __uint_as_float(kw[i >> 1] & 0xFFFF0000u) : __uint_as_float(kw[i >> 1] << 16); };
+    // Four heads at a time: each head's dot stays one sequential chain (the reference's order), the four chains are
+    // independent of each other and fill the adder's latency; the heads' ReLU'd dots are then added in head order.
     float tot = 0.f;
-    for (int h = 0; h < ih; h++) {
+    int h = 0;
+    for (; h + 4 <= ih; h += 4) {
+        const float *q0 = s_q + h * ID, *q1 = q0 + ID, *q2 = q1 + ID, *q3 = q2 + ID;
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < ID; i++) {
+            d0 = __fadd_rn(d0, __fmul_rn(q0[i], kf(i)));
+            d1 = __fadd_rn(d1, __fmul_rn(q1[i], kf(i)));
+            d2 = __fadd_rn(d2, __fmul_rn(q2[i], kf(i)));
+            d3 = __fadd_rn(d3, __fmul_rn(q3[i], kf(i)));
+        }
+        if (d0 > 0.f) tot = __fadd_rn(tot, d0);
+        if (d1 > 0.f) tot = __fadd_rn(tot, d1);
+        if (d2 > 0.f) tot = __fadd_rn(tot, d2);
+        if (d3 > 0.f) tot = __fadd_rn(tot, d3);
+    }
+    for (; h < ih; h++) {
         const float *qh = s_q + h * ID;
         float d = 0.f;
 #pragma unroll
-        for (int i = 0; i < ID; i++) d = __fadd_rn(d, __fmul_rn(qh[i], kf[i]));
+        for (int i = 0; i < ID; i++) d = __fadd_rn(d, __fmul_rn(qh[i], kf(i)));
         if (d > 0.f) tot = __fadd_rn(tot, d);
     }
     sc[s0 + threadIdx.x] = tot;
