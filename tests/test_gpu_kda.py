@@ -64,11 +64,12 @@ def test_kda_step_follows_the_reference_over_tokens(attn, case):
     assert np.array_equal(conv.cpu().numpy()[0], G[p + "conv"])          # the window holds copies of the inputs
 
 
-def test_kda_step_batch_of_slots(attn):
-    """6 slots x 64 heads x 128 (more work items than resident blocks, so the persistent loop with its prefetch of the
-    next item's state runs), three tokens; every slot against the oracle run on it alone."""
+@pytest.mark.parametrize("B,nh,hd,steps", [(6, 64, 128, 3), (30, 3, 32, 2), (7, 64, 64, 2)])
+def test_kda_step_batch_of_slots(attn, B, nh, hd, steps):
+    """Slots x heads x head dim; the first case has more work items than resident blocks (the persistent loop with its
+    fetch of the next item's inputs runs), the others the smaller head dims; every slot against the oracle run on it
+    alone."""
     o = orc.oracle()
-    B, nh, hd, steps = 6, 64, 128, 3
     proj = nh * hd
     lower, rms_eps = -5.0, 1e-6
     qc, kc, vc = (synth.normal_bf16(SEED, 981 + i, (proj, 4), 0.5) for i in range(3))
