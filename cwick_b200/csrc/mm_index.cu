@@ -117,6 +117,162 @@ __global__ void __launch_bounds__(256) mm_expand_blocks_kernel(int32_t *blk, con
     }
 }
 
+// The whole selection in one launch, for up to 1024 blocks of a multiple of four scores: one block of 1024 threads.
+//   1. block maxima: a thread takes 16-byte groups t, t + 1024, ... of the scores (all its loads in flight at once) and
+//      folds each group's maximum into its block's slot with a shared-memory atomic on order-preserving keys;
+//   2. exact top blocks: the topk-th largest maximum by radix select; a block is kept when its maximum is larger, or
+//      equal and among the first of the equal ones in index order (the rule of the exact top-k kernel);
+//   3. the kept blocks in ascending order by a block-wide scan, the most recent block appended as the reference does,
+//      and the positions of the list written by all threads (a binary search per position over the blocks' offsets).
+__device__ __forceinline__ int mm_block_scan_1024(int v, int *s_warp, int &total) {      // exclusive scan over 1024 threads
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += u;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = s_warp[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += u;
+        }
+        s_warp[lane] = w;
+    }
+    __syncthreads();
+    total = s_warp[31];
+    const int base = warp ? s_warp[warp - 1] : 0;
+    __syncthreads();
+    return base + inc - v;
+}
+
+__global__ void __launch_bounds__(1024) mm_select_fused_kernel(const float *sc, int64_t limit, int bs, int topk, int cap, int32_t *sel,
+                                                               int32_t *nsel, int32_t *blk_out, int32_t *nblk_out) {
+    __shared__ uint32_t s_key[1024];
+    __shared__ int s_blk[1024 + 8], s_off[1024 + 8 + 1], s_warp[32], s_have, s_hist[256], s_pick[2];
+    const int tid = threadIdx.x;
+    const int nblk = (int)((limit + bs - 1) / bs);
+    auto key_of = [](float f) { const uint32_t u = __float_as_uint(f); return (u & 0x80000000u) ? ~u : (u | 0x80000000u); };
+    if (tid < nblk) s_key[tid] = key_of(-1e30f);
+    __syncthreads();
+    {
+        const int64_t ngroups = (limit + 3) / 4;
+        constexpr int AHEAD = 8;
+        for (int64_t g0 = tid; g0 < ngroups; g0 += 1024 * AHEAD) {
+            float4 v[AHEAD];
+#pragma unroll
+            for (int u = 0; u < AHEAD; u++) {
+                const int64_t g = g0 + (int64_t)u * 1024;
+                v[u] = make_float4(-1e30f, -1e30f, -1e30f, -1e30f);
+                if (g < ngroups) {
+                    if (g * 4 + 4 <= limit) v[u] = __ldg(reinterpret_cast<const float4 *>(sc) + g);
+                    else {
+                        v[u].x = sc[g * 4];
+                        if (g * 4 + 1 < limit) v[u].y = sc[g * 4 + 1];
+                        if (g * 4 + 2 < limit) v[u].z = sc[g * 4 + 2];
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < AHEAD; u++) {
+                const int64_t g = g0 + (int64_t)u * 1024;
+                if (g < ngroups) atomicMax(&s_key[(int)(g * 4 / bs)], key_of(fmaxf(fmaxf(fmaxf(fmaxf(-1e30f, v[u].x), v[u].y), v[u].z), v[u].w)));
+            }
+        }
+    }
+    __syncthreads();
+    // The topk-th largest key by radix select (four passes of eight bits over a 256-bin histogram in shared memory),
+    // then: kept = larger than it, or equal to it and among the first `need` equal ones in index order.
+    const uint32_t mine = tid < nblk ? s_key[tid] : 0u;
+    int keep = 0;
+    if (nblk <= topk) {
+        keep = tid < nblk;
+    } else {
+        uint32_t prefix = 0, mask = 0;
+        int need = topk;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            if (tid < 256) s_hist[tid] = 0;
+            __syncthreads();
+            if (tid < nblk && (mine & mask) == prefix) atomicAdd(&s_hist[(mine >> shift) & 255u], 1);
+            __syncthreads();
+            if (tid < 32) {                              // warp 0: the bin in which the `need`-th largest candidate lies
+                int c[8], mysum = 0;
+#pragma unroll
+                for (int u = 0; u < 8; u++) { c[u] = s_hist[tid * 8 + u]; mysum += c[u]; }
+                int above = mysum;                       // candidates in this lane's bins and in the bins of higher lanes
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int u = __shfl_down_sync(0xffffffffu, above, o);
+                    if (tid + o < 32) above += u;
+                }
+                const int higher = above - mysum;        // candidates in the bins of higher lanes only
+                if (higher < need && above >= need) {    // exactly one lane
+                    int left = need - higher, d = 7;
+                    for (; d > 0; d--) {
+                        if (c[d] >= left) break;
+                        left -= c[d];
+                    }
+                    s_pick[0] = tid * 8 + d;
+                    s_pick[1] = left;                    // still to take inside bin d
+                }
+            }
+            __syncthreads();
+            prefix |= (uint32_t)s_pick[0] << shift;
+            mask |= 255u << shift;
+            need = s_pick[1];
+            __syncthreads();
+        }
+        int ntie;
+        const int eq = tid < nblk && mine == prefix;
+        const int eqrank = mm_block_scan_1024(eq, s_warp, ntie);
+        keep = tid < nblk && (mine > prefix || (eq && eqrank < need));
+    }
+    const int last = (int)(limit / bs);                  // the block of the next position: always listed (it may hold no score yet)
+    if (tid == 0) s_have = 0;
+    int nb;
+    const int pos = mm_block_scan_1024(keep, s_warp, nb);      // (its barriers order the flag's reset before the write below)
+    if (keep) {
+        s_blk[pos] = tid;
+        if (tid == last) s_have = 1;
+    }
+    __syncthreads();
+    if (!s_have && nb < topk + 4) {                      // every thread takes the same branch
+        if (tid == 0) s_blk[nb] = last;
+        nb++;
+    }
+    __syncthreads();
+    // positions per listed block, their offsets
+    int len = 0;
+    if (tid < nb) {
+        const int64_t s0 = (int64_t)s_blk[tid] * bs, s1 = min(limit, s0 + bs);
+        len = (int)max((int64_t)0, s1 - s0);
+    }
+    int total;
+    const int off = mm_block_scan_1024(len, s_warp, total);
+    if (tid < nb) s_off[tid] = off;
+    if (tid == 0) s_off[nb] = total;
+    __syncthreads();                                     // (topk <= 1020: the list, the appended block included, fits the 1024 threads)
+    const int nout = min(total, cap);
+    for (int q = tid; q < nout; q += 1024) {
+        int lo = 0, hi = nb - 1;                         // the listed block that holds position q: s_off[lo] <= q < s_off[lo + 1]
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_off[mid] <= q) lo = mid; else hi = mid - 1;
+        }
+        sel[q] = (int32_t)((int64_t)s_blk[lo] * bs + (q - s_off[lo]));
+    }
+    if (blk_out)
+        for (int i = tid; i < nb; i += 1024) blk_out[i] = s_blk[i];
+    if (tid == 0) {
+        *nsel = nout;
+        if (nblk_out) *nblk_out = nb;
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -146,6 +302,12 @@ int cwk_mm_select_blocks(cwk_ctx *ctx, const float *sc, int64_t limit, int bs, i
         return cwk_fail(ctx, CWK_ERR_ARGUMENT, "mm_select_blocks: bad argument (topk <= 1020)");
     CWK_CUDA(ctx, cudaSetDevice(ctx->device));
     const int nblk = (int)((limit + bs - 1) / bs);
+    if (nblk <= 1024 && bs % 4 == 0 && (reinterpret_cast<uintptr_t>(sc) & 15) == 0) {      // one launch
+        CwkKernelTimer timer(ctx);
+        mm_select_fused_kernel<<<1, 1024, 0, ctx->stream>>>(sc, limit, bs, topk, cap, sel, nsel, blk_out, nblk_out);
+        CWK_LAUNCH_CHECK(ctx, "mm_select_fused_kernel");
+        return CWK_OK;
+    }
     // work: block maxima [nblk + 1] | kept blocks [topk + 4] | block count | kept count | blocks selected
     int s = cwk_reserve_work(ctx, ((size_t)nblk + 1 + topk + 4 + 3) * sizeof(float));
     if (s != CWK_OK) return s;

@@ -45,7 +45,9 @@ def test_index_scores_bit_exact(attn, n, idim, ih):
     assert np.array_equal(sc.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("limit,bs,topk", [(1, 64, 16), (64, 64, 16), (65, 64, 16), (5000, 64, 16), (70000, 128, 31), (4096, 128, 64)])
+@pytest.mark.parametrize("limit,bs,topk", [(1, 64, 16), (64, 64, 16), (65, 64, 16), (5000, 64, 16), (70000, 128, 31), (4096, 128, 64),
+                                            (65536, 64, 16), (900, 64, 1000),          # 1024 blocks in one launch; fewer blocks than topk
+                                            (200000, 128, 40), (5000, 50, 16)])        # more than 1024 blocks, a block size off four: three launches
 def test_block_selection(attn, limit, bs, topk):
     o = orc.oracle()
     sc = np.abs(synth.normal(SEED, 1210 + limit % 50, limit + 8)).astype(np.float32)
