@@ -4,7 +4,9 @@
 //   mm_index_scores_kernel   sc[s] = sum_h ReLU(q_h . k_s): one thread per key (rows staged through shared memory),
 //                            heads in order, sequential f32 dots (the reference's order, so block maxima and ties
 //                            are the reference's)
-//   mm_block_max_kernel      maximum of every block of `bs` scores (fmaxf from -1e30, partial last block included)
+//   mm_select_fused_kernel   block maxima, exact top blocks and the position list in one launch (up to 1024 blocks)
+//   mm_block_max_kernel      (longer rows: three launches) maximum of every block of `bs` scores (fmaxf from -1e30,
+//                            partial last block included)
 //   mm_expand_blocks_kernel  the top blocks (exact top-k of csrc/dsa.cu, ascending) plus the block holding the next
 //                            position when it is missing, expanded to the list of positions (at most `cap`)
 #include "cwk_common.cuh"
