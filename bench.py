@@ -398,7 +398,8 @@ def run_ours(args):
                              ("c3_mla_prefill_4096", side_prefill),
                              ("c4_dsa_8x65536_top2048", side_dsa),
                              ("kda_decode_step_64x128", side_kda),
-                             ("gdn_step_and_mm_indexer", side_gdn_mm)):
+                             ("gdn_step_and_mm_indexer", side_gdn_mm),
+                             ("dropin_mla_decode_call", side_dropin)):
                 try:
                     torch.cuda.empty_cache()
                     extra[name] = fn(attn, dev, stream, peak)
@@ -798,6 +799,57 @@ def side_prefill(attn, dev, stream, peak):
                             "note": "after the attention: cwk_mla_unabsorb then cwk_fp8_linear (8192 -> 4096); not in ms_per_prefill"}}
 
 
+def side_dropin(attn, dev, stream, peak):
+    """The reference-named entry point as a caller of the reference makes it (not a BASELINE config): one
+    cwick_attention_mla_decode call of one layer -- host x and out, the reference's structs, BF16 weights mirrored on first
+    use -- at GLM-like dimensions (hidden 4096, 64 heads of 128 + 128, q_lora 1536, latent 512) with 8191 cached rows.
+    Wall clock per call around the synchronous C call (it ends with the output in the caller's buffer)."""
+    import ctypes as C
+    import time
+    import numpy as np
+    from cwick_b200 import lib as cl, synth
+    from cwick_b200.compat import Err, make_spec, tensor
+    os.environ["CWICK_LATENT_BF16"] = "1"
+    L = cl.load()
+    H, nh, nope, vdim, q_lora, kv_lora = 4096, 64, 128, 128, 1536, 512
+    P0, calls = 8191, 60
+    T = P0 + calls + 4
+    s = 77
+    W = dict(qa=synth.normal_bf16(s, 1, (q_lora, H), 0.02), qb=synth.normal_bf16(s, 2, (nh * nope, q_lora), 0.02),
+             kva=synth.normal_bf16(s, 3, (kv_lora, H), 0.02), kvb=synth.normal_bf16(s, 4, (nh * (nope + vdim), kv_lora), 0.02),
+             o=synth.normal_bf16(s, 5, (H, nh * vdim), 0.02), qa_n=synth.f32_to_bf16(np.ones(q_lora, np.float32)),
+             kva_n=synth.f32_to_bf16(np.ones(kv_lora, np.float32)))
+    spec = make_spec(H, nh, nope, vdim, q_lora, kv_lora, 1e-6)
+    ts = [tensor(W["qa"], q_lora, H), tensor(W["qb"], nh * nope, q_lora), tensor(W["kva"], kv_lora, H),
+          tensor(W["kvb"], nh * (nope + vdim), kv_lora), tensor(W["o"], H, nh * vdim), tensor(W["qa_n"], 1, q_lora),
+          tensor(W["kva_n"], 1, kv_lora)]
+    cache = np.zeros((T, kv_lora), np.uint16)
+    cache[:P0] = synth.normal_bf16(s, 9, (P0, kv_lora), 1.0)
+    xs = synth.normal(s, 8, calls * H).reshape(calls, H).astype(np.float32)
+    out = np.zeros(H, np.float32)
+    err = Err()
+    fn = L.cwick_attention_mla_decode
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 9 + [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 5
+    times = []
+    for i in range(calls):
+        x = np.ascontiguousarray(xs[i])
+        t0 = time.perf_counter()
+        fn(C.addressof(spec), C.byref(ts[0]), C.byref(ts[1]), C.byref(ts[2]), C.byref(ts[3]), None, C.byref(ts[4]), C.byref(ts[5]),
+           C.byref(ts[6]), cache.ctypes.data, None, T, P0 + i, 0, None, None, x.ctypes.data, out.ctypes.data, C.byref(err))
+        times.append(time.perf_counter() - t0)
+        if err.status != 0:
+            raise RuntimeError(err.message.decode(errors="replace"))
+    L.cwk_dropin_reset()
+    weights_mb = sum(v.nbytes for k, v in W.items()) / 1e6
+    steady = sorted(times[5:])
+    med = steady[len(steady) // 2]
+    return {"us_per_call": med * 1e6, "us_per_call_min": steady[0] * 1e6, "first_call_ms": times[0] * 1e3,
+            "first_call_note": "mirrors %.0f MB of weights and the %d-row cache prefix from pageable host memory" % (weights_mb, P0),
+            "weights_read_per_call_mb": weights_mb, "weights_gbs": weights_mb / 1e3 / med, "cached_rows": P0,
+            "how": "median of %d synchronous calls through ctypes, wall clock" % (calls - 5)}
+
+
 PROFILE_SLOTS = 0
 
 
@@ -1015,7 +1067,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="c5b: how partial records travel")
-    ap.add_argument("--extra-only", default=None, choices=["c1", "gqa", "c3", "c4", "c5a", "kda", "gdn_mm"],
+    ap.add_argument("--extra-only", default=None, choices=["c1", "gqa", "c3", "c4", "c5a", "kda", "gdn_mm", "dropin"],
                     help="run one side measurement alone and print its JSON (for profiling that kernel)")
     ap.add_argument("--profile-slots", type=int, default=0, choices=[0, 1, 64],
                     help="with --extra-only kda / gdn_mm: only that slot count, 3 + 5 plain launches (for an ncu capture)")
@@ -1034,7 +1086,7 @@ def main():
         torch.cuda.set_stream(stream)
         attn = Attn(0)
         peak, _ = peaks()
-        fn = {"c1": side_gqa_decode, "gqa": side_gqa_batched_and_prefill, "c3": side_prefill, "c4": side_dsa, "kda": side_kda, "gdn_mm": side_gdn_mm,
+        fn = {"c1": side_gqa_decode, "gqa": side_gqa_batched_and_prefill, "c3": side_prefill, "c4": side_dsa, "kda": side_kda, "gdn_mm": side_gdn_mm, "dropin": side_dropin,
               "c5a": lambda a, d, s_, p_: side_measure(a, d, s_, 64, 32768, p_)}[args.extra_only]
         print(json.dumps({args.extra_only: fn(attn, dev, stream, peak)}))
     elif args.impl == "reference":

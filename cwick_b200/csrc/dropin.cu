@@ -24,8 +24,123 @@ int cwk_mla_decode(cwk_ctx *ctx, const void *q, const void *cache, int64_t seq_s
 namespace {
 
 // ---- projections ------------------------------------------------------------------------------------------------
-// y[t][r] = W[r] . x[t], W bf16 [rows][k] row-major, x f32. One warp per (row, token), f32 accumulate; blockIdx.y = t.
-// (cwick_linear on a BF16 tensor with rows == 1: src/tensor.c:745-765 -> gemv_bf16_range :143-176.)
+// y[t][r] = W[r] . x[t] for one token per blockIdx.y: W [rows][k] row-major in BF16, F32 or FP8-E4M3 (one F32 multiplier
+// per 128 x 128 block), x and y f32 (cwick_linear with rows == 1: src/tensor.c:745-765 -> gemv_bf16_range :143-176,
+// cwick_gemv_fp8 :674-691 -> gemv_fp8_range :495-532). A projection of one token is its weights read once: the kernel
+// is there to keep enough of them in flight. A block of eight warps takes RPB rows, 8 / RPB warps per row (the host
+// picks RPB so that the grid is several blocks per SM even for a 512-row matrix); a lane reads 16 bytes of its row per
+// step, eight steps ahead of their use, f32 accumulate; the row's warps add up through shared memory.
+__device__ __forceinline__ float e4m3_val(uint32_t b) {
+    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+    float mag;
+    if (e == 0) mag = (float)m * 0.001953125f;
+    else if (e == 15 && m == 7) mag = __int_as_float(0x7fc00000);
+    else mag = __uint_as_float(((e + 120u) << 23) | (m << 20));
+    return (b & 0x80u) ? -mag : mag;
+}
+
+enum { GEMV_BF16 = 0, GEMV_F32 = 1, GEMV_FP8 = 2 };
+
+template <int KIND>
+__device__ __forceinline__ float gemv_piece(const uint4 &v, const float *x, int j, const float *sc) {
+    // the 16 bytes at element j of the row against x[j ..]: 8 bf16, 4 f32 or 16 e4m3 (times their block's multiplier)
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    float a = 0.f;
+    if (KIND == GEMV_BF16) {
+        const float4 x0 = *reinterpret_cast<const float4 *>(x + j), x1 = *reinterpret_cast<const float4 *>(x + j + 4);
+        a += __uint_as_float(u[0] << 16) * x0.x + __uint_as_float(u[0] & 0xffff0000u) * x0.y;
+        a += __uint_as_float(u[1] << 16) * x0.z + __uint_as_float(u[1] & 0xffff0000u) * x0.w;
+        a += __uint_as_float(u[2] << 16) * x1.x + __uint_as_float(u[2] & 0xffff0000u) * x1.y;
+        a += __uint_as_float(u[3] << 16) * x1.z + __uint_as_float(u[3] & 0xffff0000u) * x1.w;
+    } else if (KIND == GEMV_F32) {
+        const float4 x0 = *reinterpret_cast<const float4 *>(x + j);
+        a = __uint_as_float(u[0]) * x0.x + __uint_as_float(u[1]) * x0.y + __uint_as_float(u[2]) * x0.z + __uint_as_float(u[3]) * x0.w;
+    } else {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const float4 xq = *reinterpret_cast<const float4 *>(x + j + 4 * q);
+            a += e4m3_val(u[q] & 0xffu) * xq.x + e4m3_val((u[q] >> 8) & 0xffu) * xq.y + e4m3_val((u[q] >> 16) & 0xffu) * xq.z +
+                 e4m3_val(u[q] >> 24) * xq.w;
+        }
+        a *= sc[j >> 7];                                  // 16 elements from a multiple of 16: inside one 128-wide block
+    }
+    return a;
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(256) gemv_rows_kernel(const void *Wv, const float *scales, const float *x, float *y, int rows, int k,
+                                                        int64_t ldx, int64_t ldy, int rpb) {
+    constexpr int E = KIND == GEMV_BF16 ? 8 : KIND == GEMV_F32 ? 4 : 16;      // elements per 16 bytes
+    constexpr int EB = 16 / E;                                                // bytes per element
+    __shared__ float s_part[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wpr = 8 / rpb;                               // warps per row
+    const int r = blockIdx.x * rpb + warp / wpr, part = warp % wpr;
+    x += (int64_t)blockIdx.y * ldx;
+    y += (int64_t)blockIdx.y * ldy;
+    float acc = 0.f;
+    if (r < rows) {
+        const uint8_t *w = reinterpret_cast<const uint8_t *>(Wv) + (int64_t)r * k * EB;
+        const float *sc = KIND == GEMV_FP8 ? scales + (int64_t)(r / 128) * ((k + 127) / 128) : nullptr;
+        const bool vec = (k % E) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
+        if (vec) {
+            const int step = wpr * 32 * E;                 // elements per step of the row's warps
+            int j = (part * 32 + lane) * E;
+            for (; j + 7 * step + E <= k; j += 8 * step) {       // eight loads in flight
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) v[u] = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)(j + u * step) * EB));
+#pragma unroll
+                for (int u = 0; u < 8; u++) acc += gemv_piece<KIND>(v[u], x, j + u * step, sc);
+            }
+            for (; j + 3 * step + E <= k; j += 4 * step) {       // four
+                const uint4 v0 = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)j * EB));
+                const uint4 v1 = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)(j + step) * EB));
+                const uint4 v2 = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)(j + 2 * step) * EB));
+                const uint4 v3 = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)(j + 3 * step) * EB));
+                acc += gemv_piece<KIND>(v0, x, j, sc) + gemv_piece<KIND>(v1, x, j + step, sc);
+                acc += gemv_piece<KIND>(v2, x, j + 2 * step, sc) + gemv_piece<KIND>(v3, x, j + 3 * step, sc);
+            }
+            for (; j + E <= k; j += step) acc += gemv_piece<KIND>(__ldg(reinterpret_cast<const uint4 *>(w + (int64_t)j * EB)), x, j, sc);
+        } else {
+            for (int j = part * 32 + lane; j < k; j += wpr * 32) {
+                float wv;
+                if (KIND == GEMV_BF16) wv = bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(w)[j]);
+                else if (KIND == GEMV_F32) wv = reinterpret_cast<const float *>(w)[j];
+                else wv = e4m3_val(w[j]) * sc[j >> 7];
+                acc += wv * x[j];
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (wpr == 1) {
+        if (lane == 0 && r < rows) y[r] = acc;
+        return;
+    }
+    if (lane == 0) s_part[warp] = acc;
+    __syncthreads();
+    if (part == 0 && lane == 0 && r < rows) {
+        float t = 0.f;
+        for (int i = 0; i < wpr; i++) t += s_part[warp + i];
+        y[r] = t;
+    }
+}
+
+// y[t][0..rows) = W . x[t] for n tokens. kind: GEMV_BF16 / GEMV_F32 / GEMV_FP8.
+void launch_gemv(cwk_ctx *ctx, int kind, const void *W, const float *scales, const float *x, float *y, int64_t rows, int64_t k, int n,
+                 int64_t ldx, int64_t ldy) {
+    int rpb = 8;                                           // fewer rows per block until the grid is a few blocks per SM
+    while (rpb > 1 && (rows + rpb - 1) / rpb * n < 4 * (int64_t)ctx->sm_count) rpb >>= 1;
+    const dim3 grid((unsigned)((rows + rpb - 1) / rpb), (unsigned)n);
+    if (kind == GEMV_BF16) gemv_rows_kernel<GEMV_BF16><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb);
+    else if (kind == GEMV_F32) gemv_rows_kernel<GEMV_F32><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb);
+    else gemv_rows_kernel<GEMV_FP8><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb);
+    ctx->launches++;
+}
+
+// The KDA layer's projections keep the one-warp-per-row form: a lane's strided partial sums and the shuffle tree are the
+// order in which the values of the convolution window (copies of these outputs) were pinned bit for bit.
 __global__ void __launch_bounds__(256) gemv_bf16_kernel(const uint16_t *W, const float *x, float *y, int rows, int k, int64_t ldx,
                                                         int64_t ldy) {
     const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -52,74 +167,22 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(const uint16_t *W, const
     if (lane == 0) y[r] = acc;
 }
 
-__global__ void __launch_bounds__(256) gemv_f32_kernel(const float *W, const float *x, float *y, int rows, int k, int64_t ldx, int64_t ldy) {
-    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (r >= rows) return;
-    x += (int64_t)blockIdx.y * ldx;
-    y += (int64_t)blockIdx.y * ldy;
-    float acc = 0.f;
-    for (int j = lane; j < k; j += 32) acc += W[(int64_t)r * k + j] * x[j];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) y[r] = acc;
-}
-
-__device__ __forceinline__ float e4m3_val(uint32_t b) {
-    const uint32_t e = (b >> 3) & 15u, m = b & 7u;
-    float mag;
-    if (e == 0) mag = (float)m * 0.001953125f;
-    else if (e == 15 && m == 7) mag = __int_as_float(0x7fc00000);
-    else mag = __uint_as_float(((e + 120u) << 23) | (m << 20));
-    return (b & 0x80u) ? -mag : mag;
-}
-
-// FP8-E4M3 weights with one F32 multiplier per 128x128 block (cwick_linear's FP8 branch with rows == 1,
-// src/tensor.c:745-765 -> cwick_gemv_fp8 :674-691 -> gemv_fp8_range :495-532): per output row, the 128-wide
-// block sums in f32, each times its block's scale. One warp per (row, token); a lane takes 4 weights of each block.
-__global__ void __launch_bounds__(256) gemv_fp8_kernel(const uint8_t *W, const float *scales, const float *x, float *y, int rows, int k,
-                                                       int64_t ldx, int64_t ldy) {
-    const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (r >= rows) return;
-    x += (int64_t)blockIdx.y * ldx;
-    y += (int64_t)blockIdx.y * ldy;
-    const int nkb = (k + 127) / 128;
-    const uint8_t *w = W + (int64_t)r * k;
-    const float *sc = scales + (int64_t)(r / 128) * nkb;
-    float acc = 0.f;
-    for (int kb = 0; kb < nkb; kb++) {
-        const int j = kb * 128 + lane * 4;
-        float part = 0.f;
-        if (j + 4 <= k && (k & 3) == 0) {
-            const uint32_t v = *reinterpret_cast<const uint32_t *>(w + j);
-#pragma unroll
-            for (int e = 0; e < 4; e++) part += e4m3_val((v >> (8 * e)) & 0xffu) * x[j + e];
-        } else {
-            for (int e = 0; e < 4 && j + e < k; e++) part += e4m3_val(w[j + e]) * x[j + e];
-        }
-        acc += part * sc[kb];
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) y[r] = acc;
-}
-
 // In place: x <- x / sqrt(mean(x^2) + eps) * w (cwick_rms_norm + apply_bf16_vec, src/tensor.c:780-791,
 // src/attention.c:70-73), one block per row (blockIdx.x). Optionally also narrows the result to bf16 the way the
 // reference narrows a latent-cache row (src/util.c:202-210) into row_out + row * row_ld.
 __global__ void __launch_bounds__(256) rms_scale_kernel(float *x, int n, int64_t ldx, const uint16_t *w, float eps, uint16_t *row_out,
                                                         int64_t row_ld) {
-    __shared__ double red[256];
+    __shared__ double red[8];
     x += (int64_t)blockIdx.x * ldx;
     if (row_out) row_out += (int64_t)blockIdx.x * row_ld;
     double ss = 0.0;
     for (int i = threadIdx.x; i < n; i += 256) ss += (double)x[i] * (double)x[i];
-    red[threadIdx.x] = ss;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
-    for (int o = 128; o > 0; o >>= 1) {
-        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
-        __syncthreads();
-    }
-    const float inv = __fdiv_rn(1.0f, (float)sqrt(red[0] / (double)n + (double)eps));
+    const double tot = ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+    const float inv = __fdiv_rn(1.0f, (float)sqrt(tot / (double)n + (double)eps));
     for (int i = threadIdx.x; i < n; i += 256) {
         const float v = x[i] * inv * bf16_bits_to_f32(w[i]);
         x[i] = v;
@@ -142,6 +205,55 @@ __global__ void absorb_q_kernel(const float *q, const uint16_t *kvb, int nh, int
         for (int r = 0; r < nope; r++) acc += q[h * nope + r] * bf16_bits_to_f32(wk[(int64_t)r * kv_lora + c]);
         qabs[(int64_t)h * kv_lora + c] = (uint16_t)(pack_bf16x2(acc, 0.f) & 0xffffu);
     }
+}
+
+// The same for a latent width that is a multiple of 8 with 512 % (kv_lora / 8) == 0 (512: 64 threads across a row of
+// W_k, 8 columns = 16 bytes each, eight groups of rows): a head is 128 KB of weights read once by one block, so what
+// counts is loads in flight -- eight rows ahead per thread -- not the arithmetic. The row groups add up through shared
+// memory. grid (nh, tokens), 512 threads, dynamic shared memory (512 / (kv_lora / 8)) * kv_lora floats.
+__global__ void __launch_bounds__(512) absorb_q_rows_kernel(const float *q, const uint16_t *kvb, int nh, int nope, int kv_dim, int kv_lora,
+                                                            uint16_t *qabs) {
+    extern __shared__ float s_abs[];
+    const int h = blockIdx.x;
+    q += (int64_t)blockIdx.y * nh * nope + (int64_t)h * nope;
+    qabs += (int64_t)blockIdx.y * nh * kv_lora + (int64_t)h * kv_lora;
+    const int tpr = kv_lora / 8, ng = 512 / tpr;           // threads per row, row groups
+    const int rg = threadIdx.x / tpr, c8 = (threadIdx.x % tpr) * 8;
+    const uint16_t *wk = kvb + (int64_t)h * kv_dim * kv_lora + c8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto fma8 = [&](const uint4 &v, float qv) {
+        acc[0] += qv * __uint_as_float(v.x << 16); acc[1] += qv * __uint_as_float(v.x & 0xffff0000u);
+        acc[2] += qv * __uint_as_float(v.y << 16); acc[3] += qv * __uint_as_float(v.y & 0xffff0000u);
+        acc[4] += qv * __uint_as_float(v.z << 16); acc[5] += qv * __uint_as_float(v.z & 0xffff0000u);
+        acc[6] += qv * __uint_as_float(v.w << 16); acc[7] += qv * __uint_as_float(v.w & 0xffff0000u);
+    };
+    int r = rg;
+    for (; r + 7 * ng < nope; r += 8 * ng) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = __ldg(reinterpret_cast<const uint4 *>(wk + (int64_t)(r + u * ng) * kv_lora));
+#pragma unroll
+        for (int u = 0; u < 8; u++) fma8(v[u], q[r + u * ng]);
+    }
+    for (; r < nope; r += ng) fma8(__ldg(reinterpret_cast<const uint4 *>(wk + (int64_t)r * kv_lora)), q[r]);
+#pragma unroll
+    for (int e = 0; e < 8; e++) s_abs[rg * kv_lora + c8 + e] = acc[e];
+    __syncthreads();
+    for (int c = threadIdx.x; c < kv_lora; c += 512) {
+        float t = 0.f;
+        for (int gi = 0; gi < ng; gi++) t += s_abs[gi * kv_lora + c];
+        qabs[c] = (uint16_t)(pack_bf16x2(t, 0.f) & 0xffffu);
+    }
+}
+
+void launch_absorb_q(cudaStream_t st, const float *q, const uint16_t *kvb, int nh, int nope, int kv_dim, int kv_lora, uint16_t *qabs,
+                     int tokens) {
+    const int tpr = kv_lora / 8;
+    if (kv_lora % 8 == 0 && tpr <= 512 && 512 % tpr == 0 && (reinterpret_cast<uintptr_t>(kvb) & 15) == 0 &&
+        (size_t)(512 / tpr) * kv_lora * 4 <= 48 * 1024)
+        absorb_q_rows_kernel<<<dim3(nh, tokens), 512, (size_t)(512 / tpr) * kv_lora * 4, st>>>(q, kvb, nh, nope, kv_dim, kv_lora, qabs);
+    else
+        absorb_q_kernel<<<dim3(nh, tokens), 256, 0, st>>>(q, kvb, nh, nope, kv_dim, kv_lora, qabs);
 }
 
 // attn_out[t][h][r] = W_v[h][r] . c_acc[t][h] (src/attention.c:812-815). One warp per (h, r); blockIdx.y = token.
@@ -275,14 +387,8 @@ const WeightMirror *mirror_weight(const cwkc_tensor *t) {
 
 // y[t][0..rows) = W . x[t] for n tokens (cwick_linear, src/tensor.c:745-765), whatever the weight's kind.
 void dev_linear(cwk_ctx *ctx, const WeightMirror *w, const float *x, float *y, int n, int64_t ldx, int64_t ldy) {
-    const dim3 grid((unsigned)((w->rows + 7) / 8), (unsigned)n);
-    if (w->kind == CWKC_WEIGHT_BF16)
-        gemv_bf16_kernel<<<grid, 256, 0, ctx->stream>>>((const uint16_t *)w->data, x, y, (int)w->rows, (int)w->cols, ldx, ldy);
-    else if (w->kind == CWKC_WEIGHT_F32)
-        gemv_f32_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)w->data, x, y, (int)w->rows, (int)w->cols, ldx, ldy);
-    else
-        gemv_fp8_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)w->data, w->scales, x, y, (int)w->rows, (int)w->cols, ldx, ldy);
-    ctx->launches++;
+    const int kind = w->kind == CWKC_WEIGHT_BF16 ? GEMV_BF16 : w->kind == CWKC_WEIGHT_F32 ? GEMV_F32 : GEMV_FP8;
+    launch_gemv(ctx, kind, w->data, w->scales, x, y, w->rows, w->cols, n, ldx, ldy);
 }
 
 // Values of a small vector tensor as f32 on the device (cwick_tensor_value, src/tensor.c:767-774).
@@ -462,7 +568,7 @@ int token_step(cwk_ctx *ctx, Layer &ly, int64_t capacity, int64_t pos, const flo
     // the caller's array stays the source of truth: the row goes back in the caller's element width
     if (ly.lbf) cudaMemcpyAsync(p_row, cm.dev + (size_t)pos * kv_lora, (size_t)kv_lora * 2, cudaMemcpyDeviceToHost, st);
     else cudaMemcpyAsync(p_row, d_kva, (size_t)kv_lora * 4, cudaMemcpyDeviceToHost, st);
-    absorb_q_kernel<<<dim3(nh, 1), 256, 0, st>>>(d_q, (const uint16_t *)ly.kvb->data, nh, nope, kv_dim, kv_lora, d_qabs);
+    launch_absorb_q(st, d_q, (const uint16_t *)ly.kvb->data, nh, nope, kv_dim, kv_lora, d_qabs, 1);
     ctx->launches += 3;
 
     // ---- DSA indexer (src/attention.c:716-735): absorb this position, then pick the rows to attend to ----
@@ -585,7 +691,7 @@ int chunk_steps(cwk_ctx *ctx, Layer &ly, int64_t capacity, int64_t pos0, int64_t
     rms_scale_kernel<<<(unsigned)n, 256, 0, st>>>(d_qa, q_lora, q_lora, ly.qa_n, ly.spec->rms_norm_eps_f, nullptr, 0);
     rms_scale_kernel<<<(unsigned)n, 256, 0, st>>>(d_kva, kv_lora, kv_lora, ly.kva_n, ly.spec->rms_norm_eps_f, cm.dev + (size_t)pos0 * kv_lora, kv_lora);
     dev_linear(ctx, ly.qb, d_qa, d_q, (int)n, q_lora, (int64_t)nh * nope);
-    absorb_q_kernel<<<dim3(nh, (unsigned)n), 256, 0, st>>>(d_q, (const uint16_t *)ly.kvb->data, nh, nope, kv_dim, kv_lora, d_qabs);
+    launch_absorb_q(st, d_q, (const uint16_t *)ly.kvb->data, nh, nope, kv_dim, kv_lora, d_qabs, (int)n);
     ctx->launches += 3;
     s = cwk_mla_decode(ctx, d_qabs, cm.dev, 0, kv_lora, d_len, (int)(pos0 + n), nullptr, 0, (int)n, nh, kv_lora, 0, 1.0f / sqrtf((float)nope),
                        d_cacc, 0);
