@@ -67,15 +67,19 @@ __device__ __forceinline__ float gemv_piece(const uint4 &v, const float *x, int 
     return a;
 }
 
+// (A second matrix over the same x may ride in the same launch: blocks [nb1, gridDim.x) belong to it.)
 template <int KIND>
 __global__ void __launch_bounds__(256) gemv_rows_kernel(const void *Wv, const float *scales, const float *x, float *y, int rows, int k,
-                                                        int64_t ldx, int64_t ldy, int rpb) {
+                                                        int64_t ldx, int64_t ldy, int rpb, int nb1, const void *W2, const float *scales2,
+                                                        float *y2, int rows2, int64_t ldy2) {
     constexpr int E = KIND == GEMV_BF16 ? 8 : KIND == GEMV_F32 ? 4 : 16;      // elements per 16 bytes
     constexpr int EB = 16 / E;                                                // bytes per element
     __shared__ float s_part[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wpr = 8 / rpb;                               // warps per row
-    const int r = blockIdx.x * rpb + warp / wpr, part = warp % wpr;
+    int bx = blockIdx.x;
+    if (bx >= nb1) { bx -= nb1; Wv = W2; scales = scales2; y = y2; rows = rows2; ldy = ldy2; }
+    const int r = bx * rpb + warp / wpr, part = warp % wpr;
     x += (int64_t)blockIdx.y * ldx;
     y += (int64_t)blockIdx.y * ldy;
     float acc = 0.f;
@@ -127,15 +131,21 @@ __global__ void __launch_bounds__(256) gemv_rows_kernel(const void *Wv, const fl
     }
 }
 
-// y[t][0..rows) = W . x[t] for n tokens. kind: GEMV_BF16 / GEMV_F32 / GEMV_FP8.
+// y[t][0..rows) = W . x[t] for n tokens. kind: GEMV_BF16 / GEMV_F32 / GEMV_FP8. W2 != NULL: also y2 = W2 . x[t] (same kind,
+// same k) in the same launch.
 void launch_gemv(cwk_ctx *ctx, int kind, const void *W, const float *scales, const float *x, float *y, int64_t rows, int64_t k, int n,
-                 int64_t ldx, int64_t ldy) {
+                 int64_t ldx, int64_t ldy, const void *W2 = nullptr, const float *scales2 = nullptr, float *y2 = nullptr, int64_t rows2 = 0,
+                 int64_t ldy2 = 0) {
     int rpb = 8;                                           // fewer rows per block until the grid is a few blocks per SM
-    while (rpb > 1 && (rows + rpb - 1) / rpb * n < 4 * (int64_t)ctx->sm_count) rpb >>= 1;
-    const dim3 grid((unsigned)((rows + rpb - 1) / rpb), (unsigned)n);
-    if (kind == GEMV_BF16) gemv_rows_kernel<GEMV_BF16><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb);
-    else if (kind == GEMV_F32) gemv_rows_kernel<GEMV_F32><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb);
-    else gemv_rows_kernel<GEMV_FP8><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb);
+    while (rpb > 1 && ((rows + rpb - 1) / rpb + (rows2 + rpb - 1) / rpb) * n < 4 * (int64_t)ctx->sm_count) rpb >>= 1;
+    const int nb1 = (int)((rows + rpb - 1) / rpb), nb2 = W2 ? (int)((rows2 + rpb - 1) / rpb) : 0;
+    const dim3 grid((unsigned)(nb1 + nb2), (unsigned)n);
+    if (kind == GEMV_BF16)
+        gemv_rows_kernel<GEMV_BF16><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2);
+    else if (kind == GEMV_F32)
+        gemv_rows_kernel<GEMV_F32><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2);
+    else
+        gemv_rows_kernel<GEMV_FP8><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2);
     ctx->launches++;
 }
 
@@ -170,11 +180,8 @@ __global__ void __launch_bounds__(256) gemv_bf16_kernel(const uint16_t *W, const
 // In place: x <- x / sqrt(mean(x^2) + eps) * w (cwick_rms_norm + apply_bf16_vec, src/tensor.c:780-791,
 // src/attention.c:70-73), one block per row (blockIdx.x). Optionally also narrows the result to bf16 the way the
 // reference narrows a latent-cache row (src/util.c:202-210) into row_out + row * row_ld.
-__global__ void __launch_bounds__(256) rms_scale_kernel(float *x, int n, int64_t ldx, const uint16_t *w, float eps, uint16_t *row_out,
-                                                        int64_t row_ld) {
+__device__ __forceinline__ void rms_scale_row(float *x, int n, const uint16_t *w, float eps, uint16_t *row_out, void *host_row, int host_bf16) {
     __shared__ double red[8];
-    x += (int64_t)blockIdx.x * ldx;
-    if (row_out) row_out += (int64_t)blockIdx.x * row_ld;
     double ss = 0.0;
     for (int i = threadIdx.x; i < n; i += 256) ss += (double)x[i] * (double)x[i];
 #pragma unroll
@@ -186,11 +193,26 @@ __global__ void __launch_bounds__(256) rms_scale_kernel(float *x, int n, int64_t
     for (int i = threadIdx.x; i < n; i += 256) {
         const float v = x[i] * inv * bf16_bits_to_f32(w[i]);
         x[i] = v;
-        if (row_out) {
-            const uint32_t u = __float_as_uint(v);
-            row_out[i] = (uint16_t)((u + ((u >> 15) & 1u) + ((u >> 16) & 1u)) >> 16);
+        const uint32_t u = __float_as_uint(v);
+        const uint16_t nb = (uint16_t)((u + ((u >> 15) & 1u) + ((u >> 16) & 1u)) >> 16);
+        if (row_out) row_out[i] = nb;
+        if (host_row) {                                    // the caller's copy of the row, in the caller's element width
+            if (host_bf16) reinterpret_cast<uint16_t *>(host_row)[i] = nb;
+            else reinterpret_cast<float *>(host_row)[i] = v;
         }
     }
+}
+__global__ void __launch_bounds__(256) rms_scale_kernel(float *x, int n, int64_t ldx, const uint16_t *w, float eps, uint16_t *row_out,
+                                                        int64_t row_ld) {
+    rms_scale_row(x + (int64_t)blockIdx.x * ldx, n, w, eps, row_out ? row_out + (int64_t)blockIdx.x * row_ld : nullptr, nullptr, 0);
+}
+// The two norms of a decode step in one launch: block 0 the q_a row, block 1 the kv_a row (which is also the new cache row,
+// on the device and -- through page-locked memory the device can address -- in the staging buffer the caller's array is
+// filled from).
+__global__ void __launch_bounds__(256) rms_scale_pair_kernel(float *xa, int na, const uint16_t *wa, float *xb, int nb, const uint16_t *wb,
+                                                             float eps, uint16_t *row_out, void *host_row, int host_bf16) {
+    if (blockIdx.x == 0) rms_scale_row(xa, na, wa, eps, nullptr, nullptr, 0);
+    else rms_scale_row(xb, nb, wb, eps, row_out, host_row, host_bf16);
 }
 
 // q_abs[t][h][c] = sum_r q[t][h][r] * W_k[h][r][c] (src/attention.c:741-744), W_k = rows [h*kv_dim, +nope) of
@@ -342,7 +364,8 @@ struct Registry {
     std::map<const void *, IndexMirror> indexers;
     float *d_buf = nullptr;       // activations
     size_t d_buf_bytes = 0;
-    void *pin = nullptr;
+    void *pin = nullptr;          // page-locked staging; pin_dev: the same memory as the device addresses it (NULL: not addressable)
+    void *pin_dev = nullptr;
     size_t pin_bytes = 0;
 } g;
 
@@ -429,6 +452,7 @@ bool ensure_bufs(size_t dev_bytes, size_t pin_bytes, cwkc_error *err) {
         if (g.pin) { cudaStreamSynchronize(g.ctx->stream); cudaFreeHost(g.pin); }
         if (cudaMallocHost(&g.pin, pin_bytes) != cudaSuccess) { g.pin = nullptr; g.pin_bytes = 0; set_err(err, CWK_ERR_MEMORY, "pinned staging"); return false; }
         g.pin_bytes = pin_bytes;
+        if (cudaHostGetDevicePointer(&g.pin_dev, g.pin, 0) != cudaSuccess) { (void)cudaGetLastError(); g.pin_dev = nullptr; }
     }
     return true;
 }
@@ -558,18 +582,31 @@ int token_step(cwk_ctx *ctx, Layer &ly, int64_t capacity, int64_t pos, const flo
     if (s != CWK_OK) { set_err(err, s, "latent cache mirror failed"); return s; }
     CacheMirror &cm = *ly.cm;
 
+    // Outputs the host reads after the call's one synchronise -- the new cache row, the layer's output -- are written by
+    // the kernels straight into the page-locked staging buffer when the device can address it: two copy operations less.
+    uint8_t *pin_dev = (uint8_t *)g.pin_dev;
+    void *a_row = pin_dev ? (void *)(pin_dev + ((uint8_t *)p_row - (uint8_t *)g.pin)) : nullptr;
+    float *a_out = pin_dev ? (float *)(pin_dev + ((uint8_t *)p_out - (uint8_t *)g.pin)) : nullptr;
     memcpy(p_x, x_host, (size_t)H * 4);
     cudaMemcpyAsync(d_x, p_x, (size_t)H * 4, cudaMemcpyHostToDevice, st);
-    dev_linear(ctx, ly.qa, d_x, d_qa, 1, 0, 0);
-    dev_linear(ctx, ly.kva, d_x, d_kva, 1, 0, 0);
-    rms_scale_kernel<<<1, 256, 0, st>>>(d_qa, q_lora, 0, ly.qa_n, ly.spec->rms_norm_eps_f, nullptr, 0);
-    dev_linear(ctx, ly.qb, d_qa, d_q, 1, 0, 0);
-    rms_scale_kernel<<<1, 256, 0, st>>>(d_kva, kv_lora, 0, ly.kva_n, ly.spec->rms_norm_eps_f, cm.dev + (size_t)pos * kv_lora, 0);
+    if (ly.qa->kind == ly.kva->kind && ly.qa->cols == ly.kva->cols) {      // q_a and kv_a read the same x: one launch
+        const int kind = ly.qa->kind == CWKC_WEIGHT_BF16 ? GEMV_BF16 : ly.qa->kind == CWKC_WEIGHT_F32 ? GEMV_F32 : GEMV_FP8;
+        launch_gemv(ctx, kind, ly.qa->data, ly.qa->scales, d_x, d_qa, ly.qa->rows, ly.qa->cols, 1, 0, 0, ly.kva->data, ly.kva->scales, d_kva,
+                    ly.kva->rows, 0);
+    } else {
+        dev_linear(ctx, ly.qa, d_x, d_qa, 1, 0, 0);
+        dev_linear(ctx, ly.kva, d_x, d_kva, 1, 0, 0);
+    }
     // the caller's array stays the source of truth: the row goes back in the caller's element width
-    if (ly.lbf) cudaMemcpyAsync(p_row, cm.dev + (size_t)pos * kv_lora, (size_t)kv_lora * 2, cudaMemcpyDeviceToHost, st);
-    else cudaMemcpyAsync(p_row, d_kva, (size_t)kv_lora * 4, cudaMemcpyDeviceToHost, st);
+    rms_scale_pair_kernel<<<2, 256, 0, st>>>(d_qa, q_lora, ly.qa_n, d_kva, kv_lora, ly.kva_n, ly.spec->rms_norm_eps_f,
+                                             cm.dev + (size_t)pos * kv_lora, a_row, ly.lbf ? 1 : 0);
+    dev_linear(ctx, ly.qb, d_qa, d_q, 1, 0, 0);
+    if (!a_row) {
+        if (ly.lbf) cudaMemcpyAsync(p_row, cm.dev + (size_t)pos * kv_lora, (size_t)kv_lora * 2, cudaMemcpyDeviceToHost, st);
+        else cudaMemcpyAsync(p_row, d_kva, (size_t)kv_lora * 4, cudaMemcpyDeviceToHost, st);
+    }
     launch_absorb_q(st, d_q, (const uint16_t *)ly.kvb->data, nh, nope, kv_dim, kv_lora, d_qabs, 1);
-    ctx->launches += 3;
+    ctx->launches += 2;
 
     // ---- DSA indexer (src/attention.c:716-735): absorb this position, then pick the rows to attend to ----
     int64_t nlist = pos + 1;
@@ -649,8 +686,11 @@ int token_step(cwk_ctx *ctx, Layer &ly, int64_t capacity, int64_t pos, const flo
     if (s != CWK_OK) { set_err(err, s, "%s", cwk_last_error(ctx)); return s; }
     unabsorb_kernel<<<dim3((nh * vdim + 7) / 8, 1), 256, 0, st>>>(d_cacc, (const uint16_t *)ly.kvb->data, nh, nope, vdim, kv_lora, d_attn);
     ctx->launches += 1;
-    dev_linear(ctx, ly.o, d_attn, d_out, 1, 0, 0);
-    cudaMemcpyAsync(p_out, d_out, (size_t)H * 4, cudaMemcpyDeviceToHost, st);
+    if (a_out) dev_linear(ctx, ly.o, d_attn, a_out, 1, 0, 0);
+    else {
+        dev_linear(ctx, ly.o, d_attn, d_out, 1, 0, 0);
+        cudaMemcpyAsync(p_out, d_out, (size_t)H * 4, cudaMemcpyDeviceToHost, st);
+    }
     if (cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess) {
         set_err(err, CWK_ERR_CUDA, "GPU decode failed: %s", cudaGetErrorString(cudaGetLastError()));
         return CWK_ERR_CUDA;
