@@ -801,58 +801,75 @@ def side_prefill(attn, dev, stream, peak):
 
 def side_dropin(attn, dev, stream, peak):
     """The reference-named entry point as a caller of the reference makes it (not a BASELINE config): one
-    cwick_attention_mla_decode call of one layer -- host x and out, the reference's structs, BF16 weights mirrored on first
+    cwick_attention_mla_decode call of one layer -- host x and out, the reference's structs, weights mirrored on first
     use -- at GLM-like dimensions (hidden 4096, 64 heads of 128 + 128, q_lora 1536, latent 512) with 8191 cached rows, three
-    such layers in rotation so that a call finds its weights in HBM, not in L2.
-    Wall clock per call around the synchronous C call (it ends with the output in the caller's buffer)."""
+    such layers in rotation so that a call finds its weights in HBM, not in L2. BF16 projections, then FP8-E4M3 ones
+    (128 x 128 block multipliers; kv_b stays BF16 as in the reference's checkpoints). Wall clock per call around the
+    synchronous C call (it ends with the output in the caller's buffer)."""
     import ctypes as C
     import time
     import numpy as np
     from cwick_b200 import lib as cl, synth
-    from cwick_b200.compat import Err, make_spec, tensor
+    from cwick_b200.compat import Err, make_spec, tensor, tensor_fp8
     os.environ["CWICK_LATENT_BF16"] = "1"
     L = cl.load()
     H, nh, nope, vdim, q_lora, kv_lora = 4096, 64, 128, 128, 1536, 512
-    P0, calls, nlayers = 8191, 90, 3                       # three layers in rotation: 378 MB of weights, so none stays in L2
+    P0, calls, nlayers = 8191, 90, 3                       # three layers in rotation: 378 MB of BF16 weights, so none stays in L2
     T = P0 + calls + 4
-    layers = []
-    for ly in range(nlayers):
-        s = 77 + 10 * ly
-        W = dict(qa=synth.normal_bf16(s, 1, (q_lora, H), 0.02), qb=synth.normal_bf16(s, 2, (nh * nope, q_lora), 0.02),
-                 kva=synth.normal_bf16(s, 3, (kv_lora, H), 0.02), kvb=synth.normal_bf16(s, 4, (nh * (nope + vdim), kv_lora), 0.02),
-                 o=synth.normal_bf16(s, 5, (H, nh * vdim), 0.02), qa_n=synth.f32_to_bf16(np.ones(q_lora, np.float32)),
-                 kva_n=synth.f32_to_bf16(np.ones(kv_lora, np.float32)))
-        ts = [tensor(W["qa"], q_lora, H), tensor(W["qb"], nh * nope, q_lora), tensor(W["kva"], kv_lora, H),
-              tensor(W["kvb"], nh * (nope + vdim), kv_lora), tensor(W["o"], H, nh * vdim), tensor(W["qa_n"], 1, q_lora),
-              tensor(W["kva_n"], 1, kv_lora)]
-        cache = np.zeros((T, kv_lora), np.uint16)
-        cache[:P0] = synth.normal_bf16(s, 9, (P0, kv_lora), 1.0)
-        layers.append((W, ts, cache))
     spec = make_spec(H, nh, nope, vdim, q_lora, kv_lora, 1e-6)
-    xs = synth.normal(77, 8, calls * H).reshape(calls, H).astype(np.float32)
-    out = np.zeros(H, np.float32)
-    err = Err()
     fn = L.cwick_attention_mla_decode
     fn.restype = None
     fn.argtypes = [C.c_void_p] * 9 + [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 5
-    times = []
-    for i in range(calls):
-        W, ts, cache = layers[i % nlayers]
-        x = np.ascontiguousarray(xs[i])
-        t0 = time.perf_counter()
-        fn(C.addressof(spec), C.byref(ts[0]), C.byref(ts[1]), C.byref(ts[2]), C.byref(ts[3]), None, C.byref(ts[4]), C.byref(ts[5]),
-           C.byref(ts[6]), cache.ctypes.data, None, T, P0 + i // nlayers, 0, None, None, x.ctypes.data, out.ctypes.data, C.byref(err))
-        times.append(time.perf_counter() - t0)
-        if err.status != 0:
-            raise RuntimeError(err.message.decode(errors="replace"))
-    L.cwk_dropin_reset()
-    weights_mb = sum(v.nbytes for k, v in layers[0][0].items()) / 1e6
-    steady = sorted(times[3 * nlayers:])
-    med = steady[len(steady) // 2]
-    return {"us_per_call": med * 1e6, "us_per_call_min": steady[0] * 1e6, "first_call_ms": times[0] * 1e3,
-            "first_call_note": "mirrors %.0f MB of weights and the %d-row cache prefix from pageable host memory" % (weights_mb, P0),
-            "weights_read_per_call_mb": weights_mb, "weights_gbs": weights_mb / 1e3 / med, "cached_rows": P0,
-            "how": "median of %d synchronous calls through ctypes, wall clock, %d layers in rotation" % (calls - 3 * nlayers, nlayers)}
+    xs = synth.normal(77, 8, calls * H).reshape(calls, H).astype(np.float32)
+    out = np.zeros(H, np.float32)
+    result = {}
+    for fp8 in (False, True):
+        layers = []
+        for ly in range(nlayers):
+            s = 77 + 10 * ly
+            keep = {}
+
+            def proj(tag, stream_id, rows, cols):
+                if not fp8:
+                    keep[tag] = synth.normal_bf16(s, stream_id, (rows, cols), 0.02)
+                    return tensor(keep[tag], rows, cols)
+                rng = np.random.default_rng(1000 * s + stream_id)
+                codes = rng.integers(0, 255, (rows, cols), dtype=np.uint8)
+                codes[(codes & 0x7F) == 0x7F] = 0          # no NaN codes
+                keep[tag] = (codes, np.full((rows // 128, cols // 128), 1e-4, np.float32))
+                return tensor_fp8(keep[tag][0], keep[tag][1], rows, cols)
+            ts = [proj("qa", 1, q_lora, H), proj("qb", 2, nh * nope, q_lora), proj("kva", 3, kv_lora, H)]
+            keep["kvb"] = synth.normal_bf16(s, 4, (nh * (nope + vdim), kv_lora), 0.02)
+            ts.append(tensor(keep["kvb"], nh * (nope + vdim), kv_lora))
+            ts.append(proj("o", 5, H, nh * vdim))
+            keep["qa_n"], keep["kva_n"] = synth.f32_to_bf16(np.ones(q_lora, np.float32)), synth.f32_to_bf16(np.ones(kv_lora, np.float32))
+            ts += [tensor(keep["qa_n"], 1, q_lora), tensor(keep["kva_n"], 1, kv_lora)]
+            cache = np.zeros((T, kv_lora), np.uint16)
+            cache[:P0] = synth.normal_bf16(s, 9, (P0, kv_lora), 1.0)
+            layers.append((keep, ts, cache))
+        err = Err()
+        times = []
+        for i in range(calls):
+            keep, ts, cache = layers[i % nlayers]
+            x = np.ascontiguousarray(xs[i])
+            t0 = time.perf_counter()
+            fn(C.addressof(spec), C.byref(ts[0]), C.byref(ts[1]), C.byref(ts[2]), C.byref(ts[3]), None, C.byref(ts[4]), C.byref(ts[5]),
+               C.byref(ts[6]), cache.ctypes.data, None, T, P0 + i // nlayers, 0, None, None, x.ctypes.data, out.ctypes.data, C.byref(err))
+            times.append(time.perf_counter() - t0)
+            if err.status != 0:
+                raise RuntimeError(err.message.decode(errors="replace"))
+        L.cwk_dropin_reset()
+        weights_mb = sum((v[0].nbytes + v[1].nbytes) if isinstance(v, tuple) else v.nbytes for v in layers[0][0].values()) / 1e6
+        steady = sorted(times[3 * nlayers:])
+        med = steady[len(steady) // 2]
+        result["fp8_projections" if fp8 else "bf16_projections"] = {
+            "us_per_call": med * 1e6, "us_per_call_min": steady[0] * 1e6, "first_call_ms": times[0] * 1e3,
+            "weights_read_per_call_mb": weights_mb, "weights_gbs": weights_mb / 1e3 / med}
+        if not np.all(np.isfinite(out)):
+            raise RuntimeError("drop-in output not finite")
+    result["cached_rows"] = P0
+    result["how"] = "median of %d synchronous calls through ctypes, wall clock, %d layers in rotation; the first call mirrors the layer's weights and cache prefix from pageable host memory" % (calls - 3 * nlayers, nlayers)
+    return result
 
 
 PROFILE_SLOTS = 0

@@ -49,3 +49,12 @@ def tensor(arr, rows, cols):
     t.rows, t.cols, t.kind, t.data = rows, cols, 1, arr.ctypes.data
     t.data_bytes = arr.nbytes
     return t
+
+
+def tensor_fp8(codes, scales, rows, cols):
+    """An FP8-E4M3 weight: uint8 codes [rows][cols] and one f32 multiplier per 128 x 128 block [rows/128][cols/128]."""
+    t = Tensor()
+    t.rows, t.cols, t.kind, t.data, t.scales = rows, cols, 4, codes.ctypes.data, scales.ctypes.data
+    t.data_bytes, t.scale_bytes = codes.nbytes, scales.nbytes
+    return t
+

@@ -12,6 +12,8 @@
 #include <unordered_map>
 
 #include "../../include/cwick_compat.h"
+#include <cuda_fp16.h>
+
 #include "cwk_common.cuh"
 
 int cwk_mla_decode_rows(cwk_ctx *ctx, const void *q, const void *cache, int64_t ld, int rows, int nh, int L, int R,
@@ -41,6 +43,23 @@ __device__ __forceinline__ float e4m3_val(uint32_t b) {
 
 enum { GEMV_BF16 = 0, GEMV_F32 = 1, GEMV_FP8 = 2 };
 
+// Four E4M3 codes against four activations, 256 times too small. A code's seven magnitude bits, moved to bits 7..13 of a
+// half, are a half of 2^-8 times the code's value -- subnormal codes land on subnormal halves -- so two codes widen with one
+// half2 -> float2 conversion and no table or branch; the power of two goes into the block's multiplier. Only the NaN code
+// (magnitude 0x7f) has no such half: a word that holds one takes the code-by-code path.
+__device__ __forceinline__ float e4m3x4_dot_by_256th(uint32_t v, const float4 &xq) {
+    const uint32_t mag = v & 0x7f7f7f7fu;
+    if (__vcmpeq4(mag, 0x7f7f7f7fu))
+        return (e4m3_val(v & 0xffu) * xq.x + e4m3_val((v >> 8) & 0xffu) * xq.y + e4m3_val((v >> 16) & 0xffu) * xq.z + e4m3_val(v >> 24) * xq.w) *
+               0.00390625f;
+    const uint32_t sg = v & 0x80808080u;
+    const uint32_t h01 = ((mag & 0x7fu) << 7) | ((mag & 0x7f00u) << 15) | ((sg & 0x80u) << 8) | ((sg & 0x8000u) << 16);
+    const uint32_t h23 = ((mag >> 9) & 0x3f80u) | ((mag >> 1) & 0x3f800000u) | ((sg >> 8) & 0x8000u) | (sg & 0x80000000u);
+    const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&h01));
+    const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&h23));
+    return f01.x * xq.x + f01.y * xq.y + f23.x * xq.z + f23.y * xq.w;
+}
+
 template <int KIND>
 __device__ __forceinline__ float gemv_piece(const uint4 &v, const float *x, int j, const float *sc) {
     // the 16 bytes at element j of the row against x[j ..]: 8 bf16, 4 f32 or 16 e4m3 (times their block's multiplier)
@@ -57,12 +76,8 @@ __device__ __forceinline__ float gemv_piece(const uint4 &v, const float *x, int 
         a = __uint_as_float(u[0]) * x0.x + __uint_as_float(u[1]) * x0.y + __uint_as_float(u[2]) * x0.z + __uint_as_float(u[3]) * x0.w;
     } else {
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const float4 xq = *reinterpret_cast<const float4 *>(x + j + 4 * q);
-            a += e4m3_val(u[q] & 0xffu) * xq.x + e4m3_val((u[q] >> 8) & 0xffu) * xq.y + e4m3_val((u[q] >> 16) & 0xffu) * xq.z +
-                 e4m3_val(u[q] >> 24) * xq.w;
-        }
-        a *= sc[j >> 7];                                  // 16 elements from a multiple of 16: inside one 128-wide block
+        for (int q = 0; q < 4; q++) a += e4m3x4_dot_by_256th(u[q], *reinterpret_cast<const float4 *>(x + j + 4 * q));
+        a *= sc[j >> 7] * 256.0f;                         // 16 elements from a multiple of 16: inside one 128-wide block
     }
     return a;
 }
