@@ -43,6 +43,13 @@ __device__ __forceinline__ float e4m3_val(uint32_t b) {
 
 enum { GEMV_BF16 = 0, GEMV_F32 = 1, GEMV_FP8 = 2 };
 
+// 16 bytes of a weight row: read once, so they are kept out of L1, where the activations they meet are read again and again
+__device__ __forceinline__ uint4 ld_weight16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 // Four E4M3 codes against four activations, 256 times too small. A code's seven magnitude bits, moved to bits 7..13 of a
 // half, are a half of 2^-8 times the code's value -- subnormal codes land on subnormal halves -- so two codes widen with one
 // half2 -> float2 conversion and no table or branch; the power of two goes into the block's multiplier. Only the NaN code
@@ -82,86 +89,223 @@ __device__ __forceinline__ float gemv_piece(const uint4 &v, const float *x, int 
     return a;
 }
 
-// (A second matrix over the same x may ride in the same launch: blocks [nb1, gridDim.x) belong to it.)
-template <int KIND>
+// (A second matrix over the same x may ride in the same launch: blocks [nb1, gridDim.x) belong to it. A chunk's tokens are
+// taken TOK at a time, blockIdx.y = group of tokens: a weight piece is read once for the group's tokens -- each token's sum
+// runs in the same order as when it is alone.)
+template <int KIND, int TOK>
 __global__ void __launch_bounds__(256) gemv_rows_kernel(const void *Wv, const float *scales, const float *x, float *y, int rows, int k,
                                                         int64_t ldx, int64_t ldy, int rpb, int nb1, const void *W2, const float *scales2,
-                                                        float *y2, int rows2, int64_t ldy2) {
+                                                        float *y2, int rows2, int64_t ldy2, int ntok) {
     constexpr int E = KIND == GEMV_BF16 ? 8 : KIND == GEMV_F32 ? 4 : 16;      // elements per 16 bytes
     constexpr int EB = 16 / E;                                                // bytes per element
-    __shared__ float s_part[8];
+    __shared__ float s_part[TOK][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wpr = 8 / rpb;                               // warps per row
     int bx = blockIdx.x;
     if (bx >= nb1) { bx -= nb1; Wv = W2; scales = scales2; y = y2; rows = rows2; ldy = ldy2; }
     const int r = bx * rpb + warp / wpr, part = warp % wpr;
-    x += (int64_t)blockIdx.y * ldx;
-    y += (int64_t)blockIdx.y * ldy;
-    float acc = 0.f;
+    const int t0 = blockIdx.y * TOK;
+    const float *xt[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; t++) xt[t] = x + (int64_t)min(t0 + t, ntok - 1) * ldx;      // a group's missing tokens repeat the last one
+    float acc[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; t++) acc[t] = 0.f;
     if (r < rows) {
         const uint8_t *w = reinterpret_cast<const uint8_t *>(Wv) + (int64_t)r * k * EB;
         const float *sc = KIND == GEMV_FP8 ? scales + (int64_t)(r / 128) * ((k + 127) / 128) : nullptr;
-        const bool vec = (k % E) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
+        const bool vec = (k % E) == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 && (ldx & 3) == 0;
         if (vec) {
             const int step = wpr * 32 * E;                 // elements per step of the row's warps
             int j = (part * 32 + lane) * E;
             for (; j + 7 * step + E <= k; j += 8 * step) {       // eight loads in flight
                 uint4 v[8];
 #pragma unroll
-                for (int u = 0; u < 8; u++) v[u] = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)(j + u * step) * EB));
+                for (int u = 0; u < 8; u++) v[u] = ld_weight16(w + (int64_t)(j + u * step) * EB);
 #pragma unroll
-                for (int u = 0; u < 8; u++) acc += gemv_piece<KIND>(v[u], x, j + u * step, sc);
+                for (int t = 0; t < TOK; t++)
+#pragma unroll
+                    for (int u = 0; u < 8; u++) acc[t] += gemv_piece<KIND>(v[u], xt[t], j + u * step, sc);
             }
             for (; j + 3 * step + E <= k; j += 4 * step) {       // four
-                const uint4 v0 = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)j * EB));
-                const uint4 v1 = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)(j + step) * EB));
-                const uint4 v2 = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)(j + 2 * step) * EB));
-                const uint4 v3 = __ldg(reinterpret_cast<const uint4 *>(w + (int64_t)(j + 3 * step) * EB));
-                acc += gemv_piece<KIND>(v0, x, j, sc) + gemv_piece<KIND>(v1, x, j + step, sc);
-                acc += gemv_piece<KIND>(v2, x, j + 2 * step, sc) + gemv_piece<KIND>(v3, x, j + 3 * step, sc);
+                const uint4 v0 = ld_weight16(w + (int64_t)j * EB);
+                const uint4 v1 = ld_weight16(w + (int64_t)(j + step) * EB);
+                const uint4 v2 = ld_weight16(w + (int64_t)(j + 2 * step) * EB);
+                const uint4 v3 = ld_weight16(w + (int64_t)(j + 3 * step) * EB);
+#pragma unroll
+                for (int t = 0; t < TOK; t++) {
+                    acc[t] += gemv_piece<KIND>(v0, xt[t], j, sc) + gemv_piece<KIND>(v1, xt[t], j + step, sc);
+                    acc[t] += gemv_piece<KIND>(v2, xt[t], j + 2 * step, sc) + gemv_piece<KIND>(v3, xt[t], j + 3 * step, sc);
+                }
             }
-            for (; j + E <= k; j += step) acc += gemv_piece<KIND>(__ldg(reinterpret_cast<const uint4 *>(w + (int64_t)j * EB)), x, j, sc);
+            for (; j + E <= k; j += step) {
+                const uint4 v0 = ld_weight16(w + (int64_t)j * EB);
+#pragma unroll
+                for (int t = 0; t < TOK; t++) acc[t] += gemv_piece<KIND>(v0, xt[t], j, sc);
+            }
         } else {
             for (int j = part * 32 + lane; j < k; j += wpr * 32) {
                 float wv;
                 if (KIND == GEMV_BF16) wv = bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(w)[j]);
                 else if (KIND == GEMV_F32) wv = reinterpret_cast<const float *>(w)[j];
                 else wv = e4m3_val(w[j]) * sc[j >> 7];
-                acc += wv * x[j];
+#pragma unroll
+                for (int t = 0; t < TOK; t++) acc[t] += wv * xt[t][j];
             }
         }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    for (int t = 0; t < TOK; t++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
     if (wpr == 1) {
-        if (lane == 0 && r < rows) y[r] = acc;
+        if (lane == 0 && r < rows)
+#pragma unroll
+            for (int t = 0; t < TOK; t++)
+                if (t0 + t < ntok) y[(int64_t)(t0 + t) * ldy + r] = acc[t];
         return;
     }
-    if (lane == 0) s_part[warp] = acc;
+    if (lane == 0)
+#pragma unroll
+        for (int t = 0; t < TOK; t++) s_part[t][warp] = acc[t];
     __syncthreads();
     if (part == 0 && lane == 0 && r < rows) {
-        float t = 0.f;
-        for (int i = 0; i < wpr; i++) t += s_part[warp + i];
-        y[r] = t;
+#pragma unroll
+        for (int t = 0; t < TOK; t++) {
+            float sum = 0.f;
+            for (int i = 0; i < wpr; i++) sum += s_part[t][warp + i];
+            if (t0 + t < ntok) y[(int64_t)(t0 + t) * ldy + r] = sum;
+        }
     }
+}
+
+// A chunk of tokens: four rows x four tokens per warp, so that a lane's 16 bytes of a weight row meet four tokens' activations
+// and a token's activations meet four rows -- the one-token form, run per token, reads every activation from L1 once per row
+// and is bound by that. A warp covers the whole width of its rows (lane l takes pieces l, l + 32, ...), eight warps = 32 rows
+// per block, blockIdx.y = group of four tokens; f32 accumulate, the lanes' sums by shuffles.
+template <int KIND>
+__device__ __forceinline__ void unpack16(const uint4 &v, float *o) {      // 8 bf16, 4 f32 or 16 e4m3 (those 256 times too small)
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    if (KIND == GEMV_BF16) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) { o[2 * q] = __uint_as_float(u[q] << 16); o[2 * q + 1] = __uint_as_float(u[q] & 0xffff0000u); }
+    } else if (KIND == GEMV_F32) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) o[q] = __uint_as_float(u[q]);
+    } else {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint32_t mag = u[q] & 0x7f7f7f7fu, sg = u[q] & 0x80808080u;
+            if (__vcmpeq4(mag, 0x7f7f7f7fu)) {             // a NaN code in the word: code by code
+#pragma unroll
+                for (int e = 0; e < 4; e++) o[4 * q + e] = e4m3_val((u[q] >> (8 * e)) & 0xffu) * 0.00390625f;
+            } else {
+                const uint32_t h01 = ((mag & 0x7fu) << 7) | ((mag & 0x7f00u) << 15) | ((sg & 0x80u) << 8) | ((sg & 0x8000u) << 16);
+                const uint32_t h23 = ((mag >> 9) & 0x3f80u) | ((mag >> 1) & 0x3f800000u) | ((sg >> 8) & 0x8000u) | (sg & 0x80000000u);
+                const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&h01));
+                const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&h23));
+                o[4 * q] = f01.x; o[4 * q + 1] = f01.y; o[4 * q + 2] = f23.x; o[4 * q + 3] = f23.y;
+            }
+        }
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(256) gemm_rows_kernel(const void *Wv, const float *scales, const float *x, float *y, int rows, int k,
+                                                        int64_t ldx, int64_t ldy, int ntok) {
+    constexpr int E = KIND == GEMV_BF16 ? 8 : KIND == GEMV_F32 ? 4 : 16, EB = 16 / E, R = 4, TOK = 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r0 = (blockIdx.x * 8 + warp) * R, t0 = blockIdx.y * TOK;
+    if (r0 >= rows) return;
+    const float *xt[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; t++) xt[t] = x + (int64_t)min(t0 + t, ntok - 1) * ldx;
+    const uint8_t *w[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) w[r] = reinterpret_cast<const uint8_t *>(Wv) + (int64_t)min(r0 + r, rows - 1) * k * EB;
+    const int nkb = (k + 127) / 128;
+    float acc[R][TOK];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int t = 0; t < TOK; t++) acc[r][t] = 0.f;
+    // (loads of the next step issued ahead of this step's arithmetic were measured: the registers they hold cost more
+    // in resident warps than the overlap gives -- 2.37 against 1.67 ms for the widest projection of a 512-token chunk)
+    for (int j = lane * E; j + E <= k; j += 32 * E) {
+        uint4 wv[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) wv[r] = ld_weight16(w[r] + (int64_t)j * EB);
+        float xv[TOK][E];
+#pragma unroll
+        for (int t = 0; t < TOK; t++)
+#pragma unroll
+            for (int q = 0; q < E / 4; q++) {
+                const float4 f = *reinterpret_cast<const float4 *>(xt[t] + j + 4 * q);
+                xv[t][4 * q] = f.x; xv[t][4 * q + 1] = f.y; xv[t][4 * q + 2] = f.z; xv[t][4 * q + 3] = f.w;
+            }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            float o[E];
+            unpack16<KIND>(wv[r], o);
+            float m = 1.f;
+            if (KIND == GEMV_FP8) m = scales[(int64_t)(min(r0 + r, rows - 1) / 128) * nkb + (j >> 7)] * 256.0f;
+#pragma unroll
+            for (int t = 0; t < TOK; t++) {
+                float d = 0.f;
+#pragma unroll
+                for (int e = 0; e < E; e++) d += o[e] * xv[t][e];
+                acc[r][t] += KIND == GEMV_FP8 ? d * m : d;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int t = 0; t < TOK; t++) {
+            float a = acc[r][t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            if (lane == 0 && r0 + r < rows && t0 + t < ntok) y[(int64_t)(t0 + t) * ldy + r0 + r] = a;
+        }
+}
+
+// Whether gemm_rows_kernel takes the operands: whole 16-byte pieces, aligned rows.
+bool gemm_rows_ok(const void *W, const float *x, int64_t k, int64_t ldx, int kind) {
+    const int E = kind == GEMV_BF16 ? 8 : kind == GEMV_F32 ? 4 : 16;
+    return k % (32 * E) == 0 && (ldx & 3) == 0 && ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(x)) & 15) == 0;
 }
 
 // y[t][0..rows) = W . x[t] for n tokens. kind: GEMV_BF16 / GEMV_F32 / GEMV_FP8. W2 != NULL: also y2 = W2 . x[t] (same kind,
 // same k) in the same launch.
+template <int TOK>
+void launch_gemv_tok(cwk_ctx *ctx, int kind, const void *W, const float *scales, const float *x, float *y, int64_t rows, int64_t k, int n,
+                     int64_t ldx, int64_t ldy, const void *W2, const float *scales2, float *y2, int64_t rows2, int64_t ldy2) {
+    const int groups = (n + TOK - 1) / TOK;
+    int rpb = 8;                                           // fewer rows per block until the grid is a few blocks per SM
+    while (rpb > 1 && ((rows + rpb - 1) / rpb + (rows2 + rpb - 1) / rpb) * groups < 4 * (int64_t)ctx->sm_count) rpb >>= 1;
+    const int nb1 = (int)((rows + rpb - 1) / rpb), nb2 = W2 ? (int)((rows2 + rpb - 1) / rpb) : 0;
+    const dim3 grid((unsigned)(nb1 + nb2), (unsigned)groups);
+    if (kind == GEMV_BF16)
+        gemv_rows_kernel<GEMV_BF16, TOK><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2, n);
+    else if (kind == GEMV_F32)
+        gemv_rows_kernel<GEMV_F32, TOK><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2, n);
+    else
+        gemv_rows_kernel<GEMV_FP8, TOK><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2, n);
+    ctx->launches++;
+}
 void launch_gemv(cwk_ctx *ctx, int kind, const void *W, const float *scales, const float *x, float *y, int64_t rows, int64_t k, int n,
                  int64_t ldx, int64_t ldy, const void *W2 = nullptr, const float *scales2 = nullptr, float *y2 = nullptr, int64_t rows2 = 0,
                  int64_t ldy2 = 0) {
-    int rpb = 8;                                           // fewer rows per block until the grid is a few blocks per SM
-    while (rpb > 1 && ((rows + rpb - 1) / rpb + (rows2 + rpb - 1) / rpb) * n < 4 * (int64_t)ctx->sm_count) rpb >>= 1;
-    const int nb1 = (int)((rows + rpb - 1) / rpb), nb2 = W2 ? (int)((rows2 + rpb - 1) / rpb) : 0;
-    const dim3 grid((unsigned)(nb1 + nb2), (unsigned)n);
-    if (kind == GEMV_BF16)
-        gemv_rows_kernel<GEMV_BF16><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2);
-    else if (kind == GEMV_F32)
-        gemv_rows_kernel<GEMV_F32><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2);
-    else
-        gemv_rows_kernel<GEMV_FP8><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, rpb, nb1, W2, scales2, y2, (int)rows2, ldy2);
-    ctx->launches++;
+    if (n >= 4 && !W2 && gemm_rows_ok(W, x, k, ldx, kind)) {
+        const dim3 grid((unsigned)((rows + 31) / 32), (unsigned)((n + 3) / 4));
+        if (kind == GEMV_BF16) gemm_rows_kernel<GEMV_BF16><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, n);
+        else if (kind == GEMV_F32) gemm_rows_kernel<GEMV_F32><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, n);
+        else gemm_rows_kernel<GEMV_FP8><<<grid, 256, 0, ctx->stream>>>(W, scales, x, y, (int)rows, (int)k, ldx, ldy, n);
+        ctx->launches++;
+        return;
+    }
+    if (n >= 4) launch_gemv_tok<4>(ctx, kind, W, scales, x, y, rows, k, n, ldx, ldy, W2, scales2, y2, rows2, ldy2);
+    else launch_gemv_tok<1>(ctx, kind, W, scales, x, y, rows, k, n, ldx, ldy, W2, scales2, y2, rows2, ldy2);
 }
 
 // The KDA layer's projections keep the one-warp-per-row form: a lane's strided partial sums and the shuffle tree are the
@@ -283,12 +427,70 @@ __global__ void __launch_bounds__(512) absorb_q_rows_kernel(const float *q, cons
     }
 }
 
+// For a chunk: four tokens per block (blockIdx.y = group of four), so that a thread's 16 bytes of a W_k row meet four
+// tokens' q values: 32 multiply-adds per load instead of 8. Otherwise as absorb_q_rows_kernel; dynamic shared memory
+// 4 x (512 / (kv_lora / 8)) * kv_lora floats would be too much, so the row groups add up token by token through one
+// token's worth of it.
+__global__ void __launch_bounds__(512) absorb_q_rows4_kernel(const float *q, const uint16_t *kvb, int nh, int nope, int kv_dim, int kv_lora,
+                                                             uint16_t *qabs, int ntok) {
+    extern __shared__ float s_abs[];
+    constexpr int TOK = 4;
+    const int h = blockIdx.x, t0 = blockIdx.y * TOK;
+    const float *qt[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; t++) qt[t] = q + (int64_t)min(t0 + t, ntok - 1) * nh * nope + (int64_t)h * nope;
+    const int tpr = kv_lora / 8, ng = 512 / tpr;           // threads per row, row groups
+    const int rg = threadIdx.x / tpr, c8 = (threadIdx.x % tpr) * 8;
+    const uint16_t *wk = kvb + (int64_t)h * kv_dim * kv_lora + c8;
+    float acc[TOK][8];
+#pragma unroll
+    for (int t = 0; t < TOK; t++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[t][e] = 0.f;
+    auto fma8 = [&](const uint4 &v, int r) {
+        const float wv[8] = {__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u),
+                             __uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u), __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u)};
+#pragma unroll
+        for (int t = 0; t < TOK; t++) {
+            const float qv = qt[t][r];
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[t][e] += qv * wv[e];
+        }
+    };
+    int r = rg;
+    for (; r + 3 * ng < nope; r += 4 * ng) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = ld_weight16(wk + (int64_t)(r + u * ng) * kv_lora);
+#pragma unroll
+        for (int u = 0; u < 4; u++) fma8(v[u], r + u * ng);
+    }
+    for (; r < nope; r += ng) fma8(ld_weight16(wk + (int64_t)r * kv_lora), r);
+#pragma unroll
+    for (int t = 0; t < TOK; t++) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) s_abs[rg * kv_lora + c8 + e] = acc[t][e];
+        __syncthreads();
+        if (t0 + t < ntok)
+            for (int c = threadIdx.x; c < kv_lora; c += 512) {
+                float sum = 0.f;
+                for (int gi = 0; gi < ng; gi++) sum += s_abs[gi * kv_lora + c];
+                qabs[((int64_t)(t0 + t) * nh + h) * kv_lora + c] = (uint16_t)(pack_bf16x2(sum, 0.f) & 0xffffu);
+            }
+        __syncthreads();
+    }
+}
+
 void launch_absorb_q(cudaStream_t st, const float *q, const uint16_t *kvb, int nh, int nope, int kv_dim, int kv_lora, uint16_t *qabs,
                      int tokens) {
     const int tpr = kv_lora / 8;
     if (kv_lora % 8 == 0 && tpr <= 512 && 512 % tpr == 0 && (reinterpret_cast<uintptr_t>(kvb) & 15) == 0 &&
-        (size_t)(512 / tpr) * kv_lora * 4 <= 48 * 1024)
-        absorb_q_rows_kernel<<<dim3(nh, tokens), 512, (size_t)(512 / tpr) * kv_lora * 4, st>>>(q, kvb, nh, nope, kv_dim, kv_lora, qabs);
+        (size_t)(512 / tpr) * kv_lora * 4 <= 48 * 1024) {
+        if (tokens >= 4)
+            absorb_q_rows4_kernel<<<dim3(nh, (tokens + 3) / 4), 512, (size_t)(512 / tpr) * kv_lora * 4, st>>>(q, kvb, nh, nope, kv_dim, kv_lora, qabs, tokens);
+        else
+            absorb_q_rows_kernel<<<dim3(nh, tokens), 512, (size_t)(512 / tpr) * kv_lora * 4, st>>>(q, kvb, nh, nope, kv_dim, kv_lora, qabs);
+    }
     else
         absorb_q_kernel<<<dim3(nh, tokens), 256, 0, st>>>(q, kvb, nh, nope, kv_dim, kv_lora, qabs);
 }
@@ -308,6 +510,64 @@ __global__ void __launch_bounds__(256) unabsorb_kernel(const uint16_t *cacc, con
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0) attn[idx] = acc;
+}
+
+// The same for a chunk of tokens: four value rows x four tokens per warp (a lane's 16 bytes of a W_v row meet four tokens'
+// accumulators and the other way round), eight warps = 32 rows per block; grid (vdim / 32, groups of four tokens, heads).
+// kv_lora a multiple of 256, vdim a multiple of 4, 16-byte aligned operands.
+__global__ void __launch_bounds__(256) unabsorb_rows_kernel(const uint16_t *cacc, const uint16_t *kvb, int nh, int nope, int vdim,
+                                                            int kv_lora, float *attn, int ntok) {
+    constexpr int R = 4, TOK = 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.z, r0 = (blockIdx.x * 8 + warp) * R, t0 = blockIdx.y * TOK;
+    if (r0 >= vdim) return;
+    const uint16_t *w[R], *c[TOK];
+#pragma unroll
+    for (int r = 0; r < R; r++) w[r] = kvb + ((int64_t)h * (nope + vdim) + nope + min(r0 + r, vdim - 1)) * kv_lora;
+#pragma unroll
+    for (int t = 0; t < TOK; t++) c[t] = cacc + ((int64_t)min(t0 + t, ntok - 1) * nh + h) * kv_lora;
+    float acc[R][TOK];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int t = 0; t < TOK; t++) acc[r][t] = 0.f;
+    for (int j = lane * 8; j + 8 <= kv_lora; j += 256) {
+        uint4 wv[R], cv[TOK];
+#pragma unroll
+        for (int r = 0; r < R; r++) wv[r] = ld_weight16(w[r] + j);
+#pragma unroll
+        for (int t = 0; t < TOK; t++) cv[t] = *reinterpret_cast<const uint4 *>(c[t] + j);
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const uint32_t wu[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+#pragma unroll
+            for (int t = 0; t < TOK; t++) {
+                const uint32_t cu[4] = {cv[t].x, cv[t].y, cv[t].z, cv[t].w};
+                float d = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                    d += __uint_as_float(wu[q] << 16) * __uint_as_float(cu[q] << 16) +
+                         __uint_as_float(wu[q] & 0xffff0000u) * __uint_as_float(cu[q] & 0xffff0000u);
+                acc[r][t] += d;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int t = 0; t < TOK; t++) {
+            float a = acc[r][t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            if (lane == 0 && r0 + r < vdim && t0 + t < ntok) attn[((int64_t)(t0 + t) * nh + h) * vdim + r0 + r] = a;
+        }
+}
+
+void launch_unabsorb(cudaStream_t st, const uint16_t *cacc, const uint16_t *kvb, int nh, int nope, int vdim, int kv_lora, float *attn, int tokens) {
+    if (tokens >= 4 && kv_lora % 256 == 0 && ((reinterpret_cast<uintptr_t>(kvb) | reinterpret_cast<uintptr_t>(cacc)) & 15) == 0)
+        unabsorb_rows_kernel<<<dim3((vdim + 31) / 32, (tokens + 3) / 4, nh), 256, 0, st>>>(cacc, kvb, nh, nope, vdim, kv_lora, attn, tokens);
+    else
+        unabsorb_kernel<<<dim3((nh * vdim + 7) / 8, tokens), 256, 0, st>>>(cacc, kvb, nh, nope, vdim, kv_lora, attn);
 }
 
 // Indexer scores over the f32 pool rows, the reference's order (src/attention.c:573-582 with dot_f32's scalar
@@ -751,7 +1011,7 @@ int chunk_steps(cwk_ctx *ctx, Layer &ly, int64_t capacity, int64_t pos0, int64_t
     s = cwk_mla_decode(ctx, d_qabs, cm.dev, 0, kv_lora, d_len, (int)(pos0 + n), nullptr, 0, (int)n, nh, kv_lora, 0, 1.0f / sqrtf((float)nope),
                        d_cacc, 0);
     if (s != CWK_OK) { set_err(err, s, "%s", cwk_last_error(ctx)); return s; }
-    unabsorb_kernel<<<dim3((nh * vdim + 7) / 8, (unsigned)n), 256, 0, st>>>(d_cacc, (const uint16_t *)ly.kvb->data, nh, nope, vdim, kv_lora, d_attn);
+    launch_unabsorb(st, d_cacc, (const uint16_t *)ly.kvb->data, nh, nope, vdim, kv_lora, d_attn, (int)n);
     ctx->launches += 1;
     dev_linear(ctx, ly.o, d_attn, d_out, (int)n, (int64_t)nh * vdim, H);
     // results and the chunk's cache rows back to the caller (pageable memory: synchronous copies)
