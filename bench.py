@@ -858,6 +858,25 @@ def side_dropin(attn, dev, stream, peak):
             times.append(time.perf_counter() - t0)
             if err.status != 0:
                 raise RuntimeError(err.message.decode(errors="replace"))
+        if not fp8:                                        # and a 512-token chunk of a fresh sequence through the chunk entry point
+            nck = 512
+            chunk = L.cwick_attention_mla_prefill_chunk
+            chunk.restype = C.c_int
+            chunk.argtypes = [C.c_void_p] * 8 + [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 5
+            keep, ts, _ = layers[0]
+            Xc = synth.normal(78, 8, nck * H).reshape(nck, H).astype(np.float32)
+            Oc = np.zeros((nck, H), np.float32)
+            ctimes = []
+            for rep in range(3):
+                ccache = np.zeros((nck + 8, kv_lora), np.uint16)
+                t0 = time.perf_counter()
+                st = chunk(C.addressof(spec), C.byref(ts[0]), C.byref(ts[1]), C.byref(ts[2]), C.byref(ts[3]), C.byref(ts[4]), C.byref(ts[5]),
+                           C.byref(ts[6]), ccache.ctypes.data, None, nck + 8, 0, nck, 0, None, None, Xc.ctypes.data, Oc.ctypes.data, C.byref(err))
+                ctimes.append(time.perf_counter() - t0)
+                if st != 0 or err.status != 0:
+                    raise RuntimeError("chunk entry point: status %d %s" % (st, err.message.decode(errors="replace")))
+            result["chunk_512_tokens_bf16"] = {"ms_per_chunk": min(ctimes) * 1e3, "tokens_per_s": nck / min(ctimes),
+                                               "how": "cwick_attention_mla_prefill_chunk, host X and Out, best of 3"}
         L.cwk_dropin_reset()
         weights_mb = sum((v[0].nbytes + v[1].nbytes) if isinstance(v, tuple) else v.nbytes for v in layers[0][0].values()) / 1e6
         steady = sorted(times[3 * nlayers:])
